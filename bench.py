@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Decode throughput of the B200 engine on the Qwen2.5-0.5B-architecture workload.
+
+    python bench.py --gpus N --steps K --warmup W            # this engine
+    python bench.py --impl reference --gpus N --steps K ...   # the reference's algorithm on host cores
+
+A step is one greedy decode step (one new token per sequence, batch 1 per GPU) after a
+128-token prompt, on seeded random-init bf16 weights written as config.json + safetensors
+(no checkpoints or datasets exist where this runs).  With N > 1 every rank holds a replica on
+its own GPU and decodes its own sequence; there is no collective on the token path, the ranks
+only meet at the barriers around the timed region (weak scaling).
+
+Prints ONE JSON line (rank 0):
+  value      whole-job tokens/s with everything resident in HBM, device-timed (CUDA events on the
+             engine's stream, max over ranks);
+  e2e        the same metric through the per-token C-ABI call with host buffers: token id in,
+             next token id out, one synchronisation per token;
+  roofline   the projection kernel (all weight streaming of a step): algorithmic bytes / device
+             time of its launches, against the measured HBM copy bandwidth;
+  cpu_baseline  the CPU oracle (a restatement of Homura's CPU path) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "oracle")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+
+PROMPT_LEN = 128
+SEED = 20251
+FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def model_dir(cfg, seed, rank, world):
+    """Rank 0 writes the seeded checkpoint once; the other ranks wait for the marker file."""
+    from homura_b200 import synth
+
+    d = os.path.join(tempfile.gettempdir(), f"homura_b200_bench_qwen25_05b_seed{seed}")
+    marker = os.path.join(d, ".complete")
+    if rank == 0 and not os.path.exists(marker):
+        t = time.time()
+        synth.write_hf_model(d, cfg, seed)
+        open(marker, "w").write("ok")
+        log(f"[bench] wrote synthetic checkpoint to {d} in {time.time() - t:.1f}s")
+    while not os.path.exists(marker):
+        time.sleep(0.5)
+    return d
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU during the timed region."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except Exception:
+                continue
+            for nm, v in zip(names, r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_setup(n_gpus):
+    """(rank, world, local_rank, barrier, max_over_ranks).  torch.distributed only as plumbing."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1:
+        return 0, 1, 0, (lambda: None), (lambda v: v)
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def vmax(v):
+        t = torch.tensor([float(v)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    return rank, world, local, barrier, vmax
+
+
+def cpu_sample(d, cfg, steps, warmup, prompt_len):
+    """Decode tokens/s of the CPU oracle on the same checkpoint (all host threads)."""
+    import oracle as orc
+    from homura_b200 import synth
+
+    om = orc.OracleModel.from_hf_dir(d, max_seq_len=prompt_len + warmup + steps + 1)
+    ids = synth.prompt_ids(SEED, prompt_len, cfg.vocab_size)
+    tok, _ = om.prefill(ids)
+    for _ in range(warmup):
+        tok = orc.argmax(om.decode_step(tok))
+    t = time.perf_counter()
+    for _ in range(steps):
+        tok = orc.argmax(om.decode_step(tok))
+    dt = time.perf_counter() - t
+    return steps / dt, dt, orc.num_threads()
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path = the oracle port, timed on host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from homura_b200 import synth
+
+    cfg = synth.QWEN25_05B
+    d = model_dir(cfg, SEED, 0, 1)
+    steps, warmup = min(args.steps, 64), min(args.warmup, 3)
+    prompt = 8  # bounded sample: a short prompt keeps the CPU prefill to about a second
+    tps, dt, threads = cpu_sample(d, cfg, steps, warmup, prompt)
+    sample = f"{steps} greedy decode steps after an {prompt}-token prompt, same seeded Qwen2.5-0.5B-architecture weights (bf16), {threads} OpenMP threads"
+    out = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over bf16 weights",
+        "data": "synthetic", "config": {"workload": "Qwen2.5-0.5B-architecture batch-1 greedy decode (CPU oracle = restated Homura CPU path, not Homura's binary)"},
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kv-dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode steps (128 = the headline workload)")
+    ap.add_argument("--device-only", action="store_true", help="only the device-timed region: skips the end-to-end loop, the per-kernel pass and the CPU baseline (for profiler runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import homura_b200 as hm
+    from homura_b200 import synth
+
+    rank, world, local, barrier, vmax = dist_setup(args.gpus)
+    K, W = args.steps, max(args.warmup, 3)
+    cfg = synth.QWEN25_05B
+    d = model_dir(cfg, SEED, rank, world)
+    barrier()
+
+    t0 = time.time()
+    m = hm.HfModel.load_with_dtype(d, hm.DType.BF16, device=local)
+    kv_dtype = hm.DType.F32 if args.kv_dtype == "f32" else hm.DType.BF16
+    PL = args.prompt_len
+    max_seq = PL + 2 * (W + K) + 24
+    if max_seq > cfg.max_position_embeddings:
+        raise SystemExit(f"--steps/--warmup need {max_seq} positions; the checkpoint has {cfg.max_position_embeddings}")
+    m.init_kv_cache(max_seq, batch=1, kv_dtype=kv_dtype)
+    if rank == 0:
+        log(f"[bench] engine ready in {time.time() - t0:.1f}s; {m.launches_per_step()} launches/step; weight bytes/step {m.weight_bytes()}")
+    ids = synth.prompt_ids(SEED + rank, PL, cfg.vocab_size)  # each rank decodes its own sequence
+
+    # ---- device-timed region: K steps, inputs resident, token fed back on the device ----
+    first = m.prefill(ids)
+    m.decode_greedy_n([first], 0)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = m.time_decode(W, K)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    ms_max = vmax(ms)
+    tok_per_s = world * K / (ms_max / 1e3)
+
+    if args.device_only:
+        if rank == 0:
+            print(json.dumps({"metric": "decode_tokens_per_s", "value": tok_per_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_max / K,
+                              "config": {"workload": f"device-only run, prompt {PL}"}, "clocks": clocks}), flush=True)
+        return
+
+    # ---- end to end through the per-token C-ABI call (host token in, host token out) ----
+    m.reset_kv_cache()
+    cur = m.prefill(ids)
+    for _ in range(W):
+        _, nxt = m.decode_step([cur], want_logits=False)
+        cur = int(nxt[0])
+    barrier()
+    t = time.perf_counter()
+    for _ in range(K):
+        _, nxt = m.decode_step([cur], want_logits=False)
+        cur = int(nxt[0])
+    e2e_s = time.perf_counter() - t
+    barrier()
+    e2e_tps = world * K / vmax(e2e_s)
+
+    # ---- per-kernel-class device times (launch by launch, CUDA events) ----
+    prof = m.profile_decode(8)
+    proj = [p for p in prof if p["name"] in ("qkv_rope_kvwrite", "o_proj_residual", "gate_up_swiglu", "down_residual", "lm_head")]
+    proj_bytes = sum(p["bytes_per_step"] for p in proj)
+    proj_ms = sum(p["ms_per_step"] for p in proj)
+    proj_launches = sum(p["launches_per_step"] for p in proj)
+    peak, peak_kind = measured_peak()
+    achieved = proj_bytes / (proj_ms * 1e-3) / 1e9 if proj_ms > 0 else 0.0
+
+    if rank != 0:
+        return
+    T_avg = PL + W + (K + 1) / 2.0
+    kv_bytes_tok = cfg.num_hidden_layers * 2 * cfg.kv_dim * (4 if args.kv_dtype == "f32" else 2)
+    step_bytes = m.weight_bytes() + kv_bytes_tok * T_avg + kv_bytes_tok
+    step_gbs = step_bytes * (tok_per_s / world) / 1e9
+    out = {
+        "metric": "decode_tokens_per_s", "value": tok_per_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 accumulate over bf16 weights", "data": "synthetic",
+        "config": {
+            "workload": "Qwen2.5-0.5B-architecture decoder (24 layers, hidden 896, 14/2 heads, hd 64, SwiGLU 4864, vocab 151936, tied, QKV bias), batch 1 per GPU, " + f"{PL}-token prompt, greedy decode",
+            "kv_cache": f"paged, 16 tokens/page, {args.kv_dtype}", "l2": "inputs larger than L2: 988 MB of weights are streamed once per step (L2 is 126 MB)",
+            "parallelism": f"replicas x{world}, independent sequences, no collective on the token path", "seed": SEED,
+        },
+        "clocks": clocks,
+        "e2e": {"value": e2e_tps, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "api": "hm_decode_step (host token id in, greedy next token id out, one stream sync per token)"},
+        "gpu_launches": m.launches_per_step() * K,
+        "roofline": {
+            "bound": "hbm", "kernel": "gemv_bf16_kernel<1> (QKV, O, gate/up, down and LM-head projections)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+            "launches_per_step": proj_launches, "algorithmic_bytes_per_step": proj_bytes, "device_ms_per_step": proj_ms,
+        },
+        "step_roofline": {"bytes_per_token": step_bytes, "achieved_gbs": step_gbs, "frac_of_measured": step_gbs / peak, "frac_of_nominal_8TBs": step_gbs / NOMINAL_HBM_GBS},
+        "kernels": [{"name": p["name"], "launches": p["launches_per_step"], "us": round(1e3 * p["ms_per_step"], 2), "MB": round(p["bytes_per_step"] / 1e6, 3),
+                     "GBs": round(p["bytes_per_step"] / (p["ms_per_step"] * 1e-3) / 1e9, 1) if p["ms_per_step"] > 0 else None} for p in prof],
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        m.close()
+        steps_c, prompt_c = 32, 8
+        tps, dt, threads = cpu_sample(d, cfg, steps_c, 2, prompt_c)
+        out["cpu_baseline"] = {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                               "sample": f"{steps_c} greedy decode steps after an {prompt_c}-token prompt on the same weights ({dt:.1f} s of CPU time, {threads} OpenMP threads)"}
+    else:
+        out["cpu_baseline"] = None
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,181 @@
+// Shared device helpers and kernel-launch argument blocks (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hm {
+
+constexpr int SLAB = 128;       // output columns per weight slab
+constexpr int GEMV_THREADS = 256;
+constexpr int ROWS_PER_PASS = 16;  // 256 threads x 16 B = 16 rows x 256 B
+constexpr int MAX_M = 8;
+
+// ---- programmatic dependent launch ----------------------------------------------------
+// Kernels in the decode chain call pdl_launch_dependents() first (so the next kernel's CTAs
+// may be placed and start fetching weights) and pdl_wait() before touching anything a
+// previous kernel wrote.  Both are no-ops when the launch carries no programmatic edge.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// 128-bit streaming load of read-only weights: bypass L1 (each weight
+// byte is used once per token and the working set is far larger than L2).
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ld_stream_u2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+// Loads that must observe other CTAs' writes of the same launch (split reductions).
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+// f32 -> bf16 round-to-nearest-even (KV pages in bf16 mode).
+__device__ __forceinline__ uint16_t f32_to_bf16_rne(float f) {
+    uint32_t u = __float_as_uint(f);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
+    float f;
+    asm("{ .reg .b16 t; mov.b16 t, %1; cvt.f32.f16 %0, t; }" : "=f"(f) : "h"(h));
+    return f;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---- GEMV argument block ---------------------------------------------------------------
+enum Prologue { PRO_PLAIN = 0, PRO_RMSNORM = 1 };
+enum Epilogue { EPI_STORE = 0, EPI_QKV_ROPE = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
+
+struct KvDesc {
+    void* k_pool;            // this layer's K pages [n_pages][kv_heads][page_tokens][hd]
+    void* v_pool;
+    const int32_t* page_table;  // [n_seq][max_pages]
+    int max_pages;
+    int page_tokens;
+    int kv_heads;
+    int hd;
+    int bf16;                // page element type: 0 = f32, 1 = bf16
+};
+
+struct GemvArgs {
+    // weights: element (k, n) of slab s = n / 128 at byte  s*slab_stride + k*row_stride + (n%128)*2
+    const uint16_t* W;
+    long long slab_stride;  // bytes
+    long long row_stride;   // bytes
+    int K, N;
+    int m_valid;            // rows >= m_valid are padding: computed, never stored
+    int ksplit, rows_per_split;
+    // input rows [M][ldx]
+    const float* x;
+    int ldx;
+    int pro;
+    const float* norm_w;
+    float eps;
+    // epilogue
+    int epi;
+    float* y;
+    int ldy;
+    const float* bias;   // [N] or null
+    const float* resid;  // [M][ldy] or null (EPI_STORE: y = resid + acc)
+    // EPI_QKV_ROPE
+    int q_dim, kv_dim, hd, has_qk_norm;
+    const float* q_norm_w;
+    const float* k_norm_w;
+    const float* rope_cos;  // [max_pos][hd]
+    const float* rope_sin;
+    const int32_t* row_pos;  // [M] position of each row's token
+    const int32_t* row_seq;  // [M] sequence (page-table row) of each row
+    KvDesc kv;
+    // EPI_LOGITS: per-slab argmax partials
+    float* amax_val;     // [M][nslabs]
+    int32_t* amax_idx;   // [M][nslabs]
+    // split-K scratch
+    float* partial;      // [nslabs*ksplit][M][128]
+    unsigned int* tickets;  // [nslabs], zero between launches
+};
+
+struct AttnArgs {
+    const float* q;       // [M][heads*hd]
+    const void* k_pool;
+    const void* v_pool;
+    const int32_t* page_table;
+    const int32_t* row_seq;  // null => row index
+    const int32_t* row_pos;  // kv length - 1 per row (the row's own position); see kv_len
+    const int32_t* kv_len;   // when non-null used instead of row_pos+1
+    int max_pages, page_tokens, heads, kv_heads, hd, nsplit;
+    float scale;
+    float* out;           // [M][heads*hd]
+    float* part_acc;      // [M][heads][nsplit][hd]
+    float* part_ml;       // [M][heads][nsplit][2]
+    unsigned int* tickets;  // [M*kv_heads]
+};
+
+struct QuantArgs {
+    const uint16_t* scales;  // [N][K/32] f16 bits
+    const uint8_t* codes;    // Q8_0: [N][K]; Q4_0: [N][K/2]
+    int q4;                  // 0 = Q8_0, 1 = Q4_0
+    int K, N, m_valid;
+    const float* x;
+    int ldx;
+    int pro;                 // PRO_PLAIN / PRO_RMSNORM (f64 sum of squares, emitter_quant.rs:713-791)
+    const float* norm_w;
+    float eps;
+    float* y;
+    int ldy;
+    const float* bias;
+    const float* resid;
+};
+
+// ---- launchers (defined in the .cu files) ----------------------------------------------
+cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl);
+size_t gemv_partial_floats(int N, int ksplit, int M);
+void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_per_split);
+cudaError_t launch_attn_decode(const AttnArgs& a, int M, bool kv_bf16, cudaStream_t st, bool pdl);
+int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count);
+
+cudaError_t launch_pack_slabs_from_nk(const uint16_t* src_nk, int N, int K, uint16_t* dst, int n_off, int interleave_which, cudaStream_t st);
+cudaError_t launch_pack_slabs_from_kn(const uint16_t* src_kn, int K, int N, uint16_t* dst, cudaStream_t st);
+cudaError_t launch_embed_gather(const void* table, int table_dtype, const uint32_t* tokens, int M, int H, int V, float* out, int* err_flag, cudaStream_t st, bool pdl);
+cudaError_t launch_argmax_finish(const float* amax_val, const int32_t* amax_idx, int nslabs, int M, uint32_t* next_tok, uint32_t* feed_tok, int32_t* pos, uint32_t* hist, int hist_stride, cudaStream_t st, bool pdl);
+cudaError_t launch_argmax_rows(const float* logits, int rows, int n, uint32_t* out, cudaStream_t st);
+cudaError_t launch_rms_norm(const float* x, const float* w, float eps, int rows, int n, float* out, cudaStream_t st);
+cudaError_t launch_qknorm_rope(float* x, int rows, int heads, int hd, const float* norm_w, float eps, const float* cos_rows, const float* sin_rows, cudaStream_t st);
+cudaError_t launch_kv_write_rows(const KvDesc& kv, int seq, int pos0, const float* k_rows, const float* v_rows, int n_new, cudaStream_t st);
+cudaError_t launch_kv_read_rows(const KvDesc& kv, int seq, int len, float* k_out, float* v_out, cudaStream_t st);
+cudaError_t launch_convert_to_f32(const void* src, int dtype, size_t n, float* dst, cudaStream_t st);
+
+cudaError_t launch_split_blocks(const uint8_t* blocks, size_t nblocks, int q4, uint16_t* scales, uint8_t* codes, cudaStream_t st);
+cudaError_t launch_dequant(const uint8_t* blocks, size_t nblocks, int q4, float* out, cudaStream_t st);
+cudaError_t launch_gemv_quant(const QuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
+// quant plan helpers: PostQKV (src/hf/emitter_quant.rs:800-905) and SiLU*Up (:1078-1099)
+cudaError_t launch_post_qkv(const float* qkv, int M, int heads, int kv_heads, int hd, int has_qk_norm, const float* q_norm_w, const float* k_norm_w, float eps, const float* rope_cos, const float* rope_sin, const int32_t* row_pos, const int32_t* row_seq, const KvDesc& kv, float* q_out, cudaStream_t st, bool pdl);
+cudaError_t launch_silu_mul(const float* gate_up, int M, int I, float* act, cudaStream_t st, bool pdl);
+
+}  // namespace hm

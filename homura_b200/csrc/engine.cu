@@ -1,0 +1,944 @@
+// Engine implementation.  See engine.h.
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+#include "loaders.h"
+
+namespace hm {
+
+#define HM_CUDA(call)                                      \
+    do {                                                   \
+        cudaError_t _e = (call);                           \
+        if (_e != cudaSuccess) return cuda_fail(_e, #call); \
+    } while (0)
+
+size_t LinearW::bytes() const {
+    if (kind == HM_BF16) return (size_t)((N + SLAB - 1) / SLAB) * K * SLAB * 2;
+    if (kind == HM_Q8_0) return (size_t)N * (K / 32) * 34;
+    if (kind == HM_Q4_0) return (size_t)N * (K / 32) * 18;
+    return 0;
+}
+
+int Engine::fail(int code, const std::string& msg) {
+    err = msg;
+    return code;
+}
+int Engine::cuda_fail(cudaError_t e, const char* what) {
+    err = std::string("CUDA error: ") + cudaGetErrorString(e) + " in " + what;
+    return HM_ERR_CUDA;
+}
+bool Engine::set_device() { return cudaSetDevice(device_) == cudaSuccess; }
+
+int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* err) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        *err = "no CUDA device available (this engine has no CPU fallback)";
+        return HM_ERR_CUDA;
+    }
+    if (device < 0 || device >= ndev) {
+        *err = "device index out of range";
+        return HM_ERR_INVALID;
+    }
+    if (cfg.hidden_size <= 0 || cfg.num_attention_heads <= 0 || cfg.num_hidden_layers <= 0 || cfg.vocab_size <= 0 || cfg.intermediate_size <= 0) {
+        *err = "config has a non-positive dimension";
+        return HM_ERR_INVALID;
+    }
+    Engine* e = new Engine();
+    e->cfg_ = cfg;
+    e->device_ = device;
+    e->H_ = cfg.hidden_size;
+    e->I_ = cfg.intermediate_size;
+    e->heads_ = cfg.num_attention_heads;
+    e->kvh_ = cfg.num_key_value_heads > 0 ? cfg.num_key_value_heads : cfg.num_attention_heads;
+    e->hd_ = cfg.head_dim > 0 ? cfg.head_dim : cfg.hidden_size / cfg.num_attention_heads;
+    e->cfg_.num_key_value_heads = e->kvh_;
+    e->cfg_.head_dim = e->hd_;
+    e->qdim_ = e->heads_ * e->hd_;
+    e->kvdim_ = e->kvh_ * e->hd_;
+    e->L_ = cfg.num_hidden_layers;
+    e->V_ = cfg.vocab_size;
+    e->cfg_.has_qkv_bias = 0;
+    e->cfg_.has_qk_norm = 0;
+    e->cfg_.weight_dtype = -1;
+    auto bad = [&](const char* m) {
+        *err = m;
+        delete e;
+        return HM_ERR_UNSUPPORTED;
+    };
+    if (e->hd_ != 64 && e->hd_ != 128) return bad("head_dim must be 64 or 128");
+    if (e->heads_ % e->kvh_ != 0 || e->heads_ / e->kvh_ > 8) return bad("heads / kv_heads must be an integer <= 8");
+    if (e->H_ % 32 != 0 || e->I_ % 64 != 0) return bad("hidden_size must be a multiple of 32 and intermediate_size of 64");
+    if (cudaSetDevice(device) != cudaSuccess) return bad("cudaSetDevice failed");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) e->sm_count_ = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&e->stream_, cudaStreamNonBlocking) != cudaSuccess) return bad("cudaStreamCreate failed");
+    e->layers_.resize(e->L_);
+    const char* nopdl = std::getenv("HM_NO_PDL");
+    e->pdl_ = !(nopdl && nopdl[0] == '1');
+    *out = e;
+    return HM_OK;
+}
+
+Engine::~Engine() {
+    if (!set_device()) return;
+    if (stream_) cudaStreamSynchronize(stream_);
+    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    if (graph_) cudaGraphDestroy(graph_);
+    auto fr = [](void* p) {
+        if (p) cudaFree(p);
+    };
+    fr(embed_); fr(final_norm_); fr(rope_cos_); fr(rope_sin_);
+    for (auto& l : layers_) {
+        fr(l.in_ln); fr(l.post_ln); fr(l.qkv_bias); fr(l.q_norm); fr(l.k_norm);
+        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->scales); fr(w->codes); }
+    }
+    fr(lm_head_.slabs); fr(lm_head_.scales); fr(lm_head_.codes);
+    fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
+    fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
+    for (void* p : k_pool_) fr(p);
+    for (void* p : v_pool_) fr(p);
+    fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
+    if (pin_u32_) cudaFreeHost(pin_u32_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+// ---- weight loading -----------------------------------------------------------------------
+
+int Engine::stage(const void* host, size_t nbytes, void** dev) {
+    HM_CUDA(cudaMalloc(dev, nbytes));
+    cudaError_t e = cudaMemcpyAsync(*dev, host, nbytes, cudaMemcpyHostToDevice, stream_);
+    if (e != cudaSuccess) {
+        cudaFree(*dev);
+        return cuda_fail(e, "cudaMemcpyAsync(H2D weights)");
+    }
+    return HM_OK;
+}
+
+// One part (n_part outputs starting at n_off) of a possibly fused projection with N_total
+// outputs.  bf16 [out,in] goes to the slab layout; GGUF blocks [out, in/32] are split into
+// scale and code arrays (rows of the parts are simply concatenated).
+int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes) {
+    if (dtype != HM_BF16 && dtype != HM_Q8_0 && dtype != HM_Q4_0)
+        return fail(HM_ERR_UNSUPPORTED, "projection weights must be bf16, Q8_0 or Q4_0 (f32/f16 projections are outside this engine's path)");
+    if (L.kind >= 0 && L.kind != dtype) return fail(HM_ERR_UNSUPPORTED, "parts of a fused projection have different dtypes");
+    if (cfg_.weight_dtype >= 0 && cfg_.weight_dtype != dtype && &L != &lm_head_)
+        return fail(HM_ERR_UNSUPPORTED, "projection weights of one model must share a dtype");
+    if (&L != &lm_head_) cfg_.weight_dtype = dtype;
+    const bool q = dtype != HM_BF16;
+    if (q && K % 32 != 0) return fail(HM_ERR_INVALID, "quantised projection: in_features must be a multiple of 32");
+    const size_t expect = q ? (size_t)n_part * (K / 32) * (dtype == HM_Q8_0 ? 34 : 18) : (size_t)n_part * K * 2;
+    if (nbytes != expect) return fail(HM_ERR_INVALID, "tensor byte size does not match its shape");
+    L.K = K;
+    L.N = N_total;
+    L.kind = dtype;
+    void* tmp = nullptr;
+    int rc = stage(host, nbytes, &tmp);
+    if (rc) return rc;
+    cudaError_t ce = cudaSuccess;
+    if (!q) {
+        if (!L.slabs) {
+            const size_t bytes = (size_t)((N_total + SLAB - 1) / SLAB) * K * SLAB * 2;
+            ce = cudaMalloc(&L.slabs, bytes);
+            if (ce == cudaSuccess) ce = cudaMemsetAsync(L.slabs, 0, bytes, stream_);
+        }
+        if (ce == cudaSuccess) ce = launch_pack_slabs_from_nk((const uint16_t*)tmp, n_part, K, L.slabs, n_off, interleave_which, stream_);
+    } else {
+        const int q4 = dtype == HM_Q4_0;
+        const size_t nb = K / 32;
+        if (!L.scales) {
+            ce = cudaMalloc(&L.scales, (size_t)N_total * nb * 2);
+            if (ce == cudaSuccess) ce = cudaMalloc(&L.codes, (size_t)N_total * nb * (q4 ? 16 : 32));
+        }
+        if (ce == cudaSuccess)
+            ce = launch_split_blocks((const uint8_t*)tmp, (size_t)n_part * nb, q4, L.scales + (size_t)n_off * nb, L.codes + (size_t)n_off * nb * (q4 ? 16 : 32), stream_);
+        quant_ = true;
+    }
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
+    cudaFree(tmp);
+    if (ce != cudaSuccess) return cuda_fail(ce, "load_linear");
+    L.loaded_parts++;
+    return HM_OK;
+}
+
+int Engine::load_vec_f32(float** dst, size_t n_total, size_t off, int dtype, const void* host, size_t n, size_t nbytes) {
+    size_t esz = dtype == HM_F32 ? 4 : (dtype == HM_BF16 || dtype == HM_F16) ? 2 : 0;
+    if (!esz) return fail(HM_ERR_UNSUPPORTED, "norm / bias tensors must be f32, bf16 or f16");
+    if (nbytes != n * esz || off + n > n_total) return fail(HM_ERR_INVALID, "tensor byte size does not match its shape");
+    if (!*dst) {
+        HM_CUDA(cudaMalloc(dst, n_total * 4));
+        HM_CUDA(cudaMemsetAsync(*dst, 0, n_total * 4, stream_));
+    }
+    void* tmp = nullptr;
+    int rc = stage(host, nbytes, &tmp);
+    if (rc) return rc;
+    cudaError_t ce = launch_convert_to_f32(tmp, dtype, n, *dst + off, stream_);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
+    cudaFree(tmp);
+    if (ce != cudaSuccess) return cuda_fail(ce, "load_vec_f32");
+    return HM_OK;
+}
+
+static bool parse_layer_name(const std::string& name, const char* prefix, int* layer, std::string* rest) {
+    const size_t pl = std::strlen(prefix);
+    if (name.compare(0, pl, prefix) != 0) return false;
+    const size_t dot = name.find('.', pl);
+    if (dot == std::string::npos) return false;
+    *layer = std::atoi(name.substr(pl, dot - pl).c_str());
+    *rest = name.substr(dot + 1);
+    return true;
+}
+
+// Names and rules of load_transformer_weights (src/hf/weights.rs:267-417) and of the GGUF
+// variant (src/gguf.rs:589-708).
+int Engine::load_tensor(const char* cname, int dtype, const int64_t* shape, int ndim, const void* host, size_t nbytes) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (finalized_) return fail(HM_ERR_STATE, "weights already finalised");
+    if (!cname || !shape || !host || ndim < 1 || ndim > 2) return fail(HM_ERR_INVALID, "load_tensor: bad arguments");
+    const std::string name(cname);
+    size_t n = 1;
+    for (int i = 0; i < ndim; ++i) {
+        if (shape[i] <= 0) return fail(HM_ERR_INVALID, "load_tensor: non-positive dimension in " + name);
+        n *= (size_t)shape[i];
+    }
+    auto shape2 = [&](int64_t a, int64_t b) { return ndim == 2 && shape[0] == a && shape[1] == b; };
+    auto shape1 = [&](int64_t a) { return ndim == 1 && shape[0] == a; };
+    auto bad_shape = [&]() { return fail(HM_ERR_INVALID, "unexpected shape for tensor " + name); };
+
+    if (name == "model.embed_tokens.weight" || name == "token_embd.weight") {
+        if (!shape2(V_, H_)) return bad_shape();
+        if (embed_) return fail(HM_ERR_STATE, "embedding loaded twice");
+        // Gather table: kept as bf16 rows when the file is bf16 (widening a bf16 row to f32 on
+        // the fly equals Homura's up-front conversion, src/hf/weights.rs:284-292), else f32.
+        if (dtype == HM_BF16) {
+            if (nbytes != n * 2) return bad_shape();
+            int rc = stage(host, nbytes, &embed_);
+            if (rc) return rc;
+            HM_CUDA(cudaStreamSynchronize(stream_));
+            embed_dtype_ = HM_BF16;
+        } else if (dtype == HM_F32 || dtype == HM_F16) {
+            float* t = nullptr;
+            int rc = load_vec_f32(&t, n, 0, dtype, host, n, nbytes);
+            if (rc) return rc;
+            embed_ = t;
+            embed_dtype_ = HM_F32;
+        } else if (dtype == HM_Q8_0 || dtype == HM_Q4_0) {
+            if (nbytes != n / 32 * (dtype == HM_Q8_0 ? 34u : 18u)) return bad_shape();
+            void* tmp = nullptr;
+            int rc = stage(host, nbytes, &tmp);
+            if (rc) return rc;
+            cudaError_t ce = cudaMalloc(&embed_, n * 4);
+            if (ce == cudaSuccess) ce = launch_dequant((const uint8_t*)tmp, n / 32, dtype == HM_Q4_0, (float*)embed_, stream_);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
+            cudaFree(tmp);
+            if (ce != cudaSuccess) return cuda_fail(ce, "embedding dequant");
+            embed_dtype_ = HM_F32;
+        } else {
+            return fail(HM_ERR_UNSUPPORTED, "unsupported embedding dtype");
+        }
+        // Tied LM head = the embedding, transposed (src/hf/weights.rs:101-113).
+        if (cfg_.tie_word_embeddings) {
+            if (dtype == HM_F32 || dtype == HM_F16)
+                return fail(HM_ERR_UNSUPPORTED, "tied LM head from an f32/f16 embedding is outside this engine's path (bf16 or quantised only)");
+            return load_linear(lm_head_, H_, V_, 0, V_, -1, dtype, host, nbytes);
+        }
+        return HM_OK;
+    }
+    if (name == "model.norm.weight" || name == "output_norm.weight") {
+        if (!shape1(H_)) return bad_shape();
+        return load_vec_f32(&final_norm_, H_, 0, dtype, host, n, nbytes);
+    }
+    if (name == "lm_head.weight" || name == "output.weight") {
+        if (!shape2(V_, H_)) return bad_shape();
+        if (cfg_.tie_word_embeddings) return HM_OK;  // ignored, as in src/hf/weights.rs:383-387
+        return load_linear(lm_head_, H_, V_, 0, V_, -1, dtype, host, nbytes);
+    }
+    int li = -1;
+    std::string rest;
+    const bool hf = parse_layer_name(name, "model.layers.", &li, &rest);
+    const bool gg = !hf && parse_layer_name(name, "blk.", &li, &rest);
+    if (!hf && !gg) return fail(HM_ERR_INVALID, "unknown tensor name: " + name);
+    if (li < 0 || li >= L_) return fail(HM_ERR_INVALID, "layer index out of range in " + name);
+    LayerW& Lw = layers_[li];
+    auto is = [&](const char* a, const char* b) { return rest == (hf ? a : b); };
+    const int QKV = qdim_ + 2 * kvdim_;
+    if (is("input_layernorm.weight", "attn_norm.weight")) return shape1(H_) ? load_vec_f32(&Lw.in_ln, H_, 0, dtype, host, n, nbytes) : bad_shape();
+    if (is("post_attention_layernorm.weight", "ffn_norm.weight")) return shape1(H_) ? load_vec_f32(&Lw.post_ln, H_, 0, dtype, host, n, nbytes) : bad_shape();
+    if (is("self_attn.q_proj.weight", "attn_q.weight")) return shape2(qdim_, H_) ? load_linear(Lw.qkv, H_, QKV, 0, qdim_, -1, dtype, host, nbytes) : bad_shape();
+    if (is("self_attn.k_proj.weight", "attn_k.weight")) return shape2(kvdim_, H_) ? load_linear(Lw.qkv, H_, QKV, qdim_, kvdim_, -1, dtype, host, nbytes) : bad_shape();
+    if (is("self_attn.v_proj.weight", "attn_v.weight")) return shape2(kvdim_, H_) ? load_linear(Lw.qkv, H_, QKV, qdim_ + kvdim_, kvdim_, -1, dtype, host, nbytes) : bad_shape();
+    if (is("self_attn.o_proj.weight", "attn_output.weight")) return shape2(H_, qdim_) ? load_linear(Lw.o, qdim_, H_, 0, H_, -1, dtype, host, nbytes) : bad_shape();
+    if (is("mlp.gate_proj.weight", "ffn_gate.weight")) return shape2(I_, H_) ? load_linear(Lw.gu, H_, 2 * I_, 0, I_, 0, dtype, host, nbytes) : bad_shape();
+    if (is("mlp.up_proj.weight", "ffn_up.weight")) return shape2(I_, H_) ? load_linear(Lw.gu, H_, 2 * I_, I_, I_, 1, dtype, host, nbytes) : bad_shape();
+    if (is("mlp.down_proj.weight", "ffn_down.weight")) return shape2(H_, I_) ? load_linear(Lw.down, I_, H_, 0, H_, -1, dtype, host, nbytes) : bad_shape();
+    if (is("self_attn.q_proj.bias", "attn_q.bias")) {
+        cfg_.has_qkv_bias = 1;
+        return shape1(qdim_) ? load_vec_f32(&Lw.qkv_bias, QKV, 0, dtype, host, n, nbytes) : bad_shape();
+    }
+    if (is("self_attn.k_proj.bias", "attn_k.bias")) return shape1(kvdim_) ? load_vec_f32(&Lw.qkv_bias, QKV, qdim_, dtype, host, n, nbytes) : bad_shape();
+    if (is("self_attn.v_proj.bias", "attn_v.bias")) return shape1(kvdim_) ? load_vec_f32(&Lw.qkv_bias, QKV, qdim_ + kvdim_, dtype, host, n, nbytes) : bad_shape();
+    if (is("self_attn.q_norm.weight", "attn_q_norm.weight")) {
+        cfg_.has_qk_norm = 1;
+        return shape1(hd_) ? load_vec_f32(&Lw.q_norm, hd_, 0, dtype, host, n, nbytes) : bad_shape();
+    }
+    if (is("self_attn.k_norm.weight", "attn_k_norm.weight")) return shape1(hd_) ? load_vec_f32(&Lw.k_norm, hd_, 0, dtype, host, n, nbytes) : bad_shape();
+    return fail(HM_ERR_INVALID, "unknown tensor name: " + name);
+}
+
+int Engine::finalize() {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (finalized_) return HM_OK;
+    if (!embed_) return fail(HM_ERR_STATE, "missing weight: model.embed_tokens.weight");
+    if (!final_norm_) return fail(HM_ERR_STATE, "missing weight: model.norm.weight");
+    if (lm_head_.kind < 0) return fail(HM_ERR_STATE, "missing weight: lm_head.weight");
+    for (int i = 0; i < L_; ++i) {
+        const LayerW& l = layers_[i];
+        const std::string p = "missing weight in layer " + std::to_string(i) + ": ";
+        if (!l.in_ln) return fail(HM_ERR_STATE, p + "input_layernorm");
+        if (!l.post_ln) return fail(HM_ERR_STATE, p + "post_attention_layernorm");
+        if (l.qkv.loaded_parts != 3) return fail(HM_ERR_STATE, p + "q/k/v projection");
+        if (l.o.loaded_parts != 1) return fail(HM_ERR_STATE, p + "o projection");
+        if (l.gu.loaded_parts != 2) return fail(HM_ERR_STATE, p + "gate/up projection");
+        if (l.down.loaded_parts != 1) return fail(HM_ERR_STATE, p + "down projection");
+        if (cfg_.has_qk_norm && (!l.q_norm || !l.k_norm)) return fail(HM_ERR_STATE, p + "q_norm/k_norm");
+    }
+    std::vector<float> c, s;
+    build_rope_table(hd_, cfg_.max_position_embeddings, cfg_.rope_theta, &c, &s);
+    HM_CUDA(cudaMalloc(&rope_cos_, c.size() * 4));
+    HM_CUDA(cudaMalloc(&rope_sin_, s.size() * 4));
+    HM_CUDA(cudaMemcpy(rope_cos_, c.data(), c.size() * 4, cudaMemcpyHostToDevice));
+    HM_CUDA(cudaMemcpy(rope_sin_, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
+    HM_CUDA(cudaMalloc(&err_flag_, 4));
+    HM_CUDA(cudaMemset(err_flag_, 0, 4));
+    finalized_ = true;
+    return HM_OK;
+}
+
+uint64_t Engine::weight_bytes() const {
+    uint64_t b = lm_head_.bytes();
+    for (auto& l : layers_) b += l.qkv.bytes() + l.o.bytes() + l.gu.bytes() + l.down.bytes();
+    return b;
+}
+
+// ---- scratch ---------------------------------------------------------------------------------
+
+int Engine::ensure_scratch(int rows) {
+    const int cap = (rows + MAX_M - 1) / MAX_M * MAX_M;
+    if (cap <= scratch_rows_) return HM_OK;
+    auto re = [&](auto** p, size_t count) -> cudaError_t {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
+        cudaError_t e = cudaMalloc((void**)p, count * sizeof(**p));
+        if (e == cudaSuccess) e = cudaMemset(*p, 0, count * sizeof(**p));
+        return e;
+    };
+    const int nslabs_v = (V_ + SLAB - 1) / SLAB;
+    HM_CUDA(re(&h_, (size_t)cap * H_));
+    HM_CUDA(re(&q_, (size_t)cap * qdim_));
+    HM_CUDA(re(&attn_, (size_t)cap * qdim_));
+    HM_CUDA(re(&act_, (size_t)cap * I_));
+    HM_CUDA(re(&logits_, (size_t)cap * V_));
+    HM_CUDA(re(&amax_val_, (size_t)cap * nslabs_v));
+    HM_CUDA(re(&amax_idx_, (size_t)cap * nslabs_v));
+    if (quant_) {
+        HM_CUDA(re(&qkv_raw_, (size_t)cap * (qdim_ + 2 * kvdim_)));
+        HM_CUDA(re(&gu_raw_, (size_t)cap * 2 * I_));
+    }
+    // split-K scratch sized for the worst projection at M = 8
+    size_t pf = 0;
+    int max_slabs = nslabs_v;
+    auto acc = [&](const LinearW& w) {
+        if (w.kind != HM_BF16) return;
+        for (int M : {1, 2, 4, 8}) {
+            int ks, rps;
+            gemv_pick_split(w.K, w.N, M, sm_count_, &ks, &rps);
+            pf = std::max(pf, gemv_partial_floats(w.N, ks, M));
+        }
+        max_slabs = std::max(max_slabs, (w.N + SLAB - 1) / SLAB);
+    };
+    for (auto& l : layers_) { acc(l.qkv); acc(l.o); acc(l.gu); acc(l.down); }
+    acc(lm_head_);
+    partial_floats_ = std::max<size_t>(pf, 1);
+    HM_CUDA(re(&partial_, partial_floats_));
+    HM_CUDA(re(&tickets_, (size_t)max_slabs));
+    scratch_rows_ = cap;
+    return HM_OK;
+}
+
+// ---- KV cache --------------------------------------------------------------------------------
+
+int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (!finalized_) return fail(HM_ERR_STATE, "kv_alloc before weights are finalised");
+    if (batch_ > 0) return fail(HM_ERR_STATE, "KV cache already allocated");
+    if (batch < 1 || max_seq_len < 1) return fail(HM_ERR_INVALID, "kv_alloc: batch and max_seq_len must be positive");
+    if (page_tokens != 16) return fail(HM_ERR_UNSUPPORTED, "kv_alloc: page size must be 16 tokens");
+    if (kv_dtype != HM_F32 && kv_dtype != HM_BF16) return fail(HM_ERR_UNSUPPORTED, "kv_alloc: cache dtype must be f32 or bf16");
+    if (max_seq_len > cfg_.max_position_embeddings) return fail(HM_ERR_INVALID, "kv_alloc: max_seq_len exceeds max_position_embeddings (RoPE table)");
+    kv_bf16_ = kv_dtype == HM_BF16;
+    page_tokens_ = page_tokens;
+    max_pages_ = (max_seq_len + page_tokens - 1) / page_tokens;
+    const size_t n_pages = (size_t)batch * max_pages_;
+    const size_t page_elems = (size_t)kvh_ * page_tokens * hd_;
+    const size_t pool_bytes = n_pages * page_elems * (kv_bf16_ ? 2 : 4);
+    k_pool_.assign(L_, nullptr);
+    v_pool_.assign(L_, nullptr);
+    for (int l = 0; l < L_; ++l) {
+        HM_CUDA(cudaMalloc(&k_pool_[l], pool_bytes));
+        HM_CUDA(cudaMalloc(&v_pool_[l], pool_bytes));
+        HM_CUDA(cudaMemset(k_pool_[l], 0, pool_bytes));
+        HM_CUDA(cudaMemset(v_pool_[l], 0, pool_bytes));
+    }
+    // Every sequence owns max_pages pages; the mapping is a fixed pseudo-random permutation of
+    // the pool so that consecutive logical pages are not physically adjacent.
+    std::vector<int32_t> perm(n_pages);
+    for (size_t i = 0; i < n_pages; ++i) perm[i] = (int32_t)i;
+    uint64_t st = 0x9E3779B97F4A7C15ull;
+    for (size_t i = n_pages; i > 1; --i) {
+        st ^= st << 13; st ^= st >> 7; st ^= st << 17;
+        std::swap(perm[i - 1], perm[st % i]);
+    }
+    HM_CUDA(cudaMalloc(&page_table_, n_pages * 4));
+    HM_CUDA(cudaMemcpy(page_table_, perm.data(), n_pages * 4, cudaMemcpyHostToDevice));
+    HM_CUDA(cudaMalloc(&pos_dev_, batch * 4));
+    HM_CUDA(cudaMemset(pos_dev_, 0, batch * 4));
+    HM_CUDA(cudaMalloc(&tokens_dev_, batch * 4));
+    HM_CUDA(cudaMemset(tokens_dev_, 0, batch * 4));
+    HM_CUDA(cudaMalloc(&next_dev_, batch * 4));
+    HM_CUDA(cudaMemset(next_dev_, 0, batch * 4));
+    HM_CUDA(cudaMalloc(&hist_dev_, (size_t)batch * (max_seq_len + 1) * 4));
+    HM_CUDA(cudaMemset(hist_dev_, 0, (size_t)batch * (max_seq_len + 1) * 4));
+    HM_CUDA(cudaMalloc(&pf_tokens_, (size_t)max_seq_len * 4));
+    HM_CUDA(cudaMalloc(&pf_pos_, (size_t)max_seq_len * 4));
+    HM_CUDA(cudaMalloc(&pf_seq_, (size_t)max_seq_len * 4));
+    pin_u32_cap_ = std::max<size_t>((size_t)3 * max_seq_len, (size_t)batch * (max_seq_len + 2)) + 16;
+    HM_CUDA(cudaMallocHost(&pin_u32_, pin_u32_cap_ * 4));
+    len_.assign(batch, 0);
+    batch_ = batch;
+    max_seq_ = max_seq_len;
+    int rc = ensure_scratch(std::max(batch, MAX_M));
+    if (rc) return rc;
+    // attention split scratch
+    att_nsplit_ = attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);  // sized for the decode step (one row per sequence)
+    HM_CUDA(cudaMalloc(&att_acc_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * hd_ * 4));
+    HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
+    HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));
+    HM_CUDA(cudaMemset(att_tickets_, 0, (size_t)scratch_rows_ * kvh_ * 4));
+    return capture_decode_graph();
+}
+
+int Engine::kv_reset(int seq) {
+    if (batch_ == 0) return HM_OK;  // reset before first use is a no-op (src/hf/model.rs:232-237)
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (seq >= batch_) return fail(HM_ERR_INVALID, "kv_reset: sequence index out of range");
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    if (seq < 0) {
+        std::fill(len_.begin(), len_.end(), 0);
+        HM_CUDA(cudaMemset(pos_dev_, 0, batch_ * 4));
+    } else {
+        len_[seq] = 0;
+        HM_CUDA(cudaMemset(pos_dev_ + seq, 0, 4));
+    }
+    return HM_OK;
+}
+
+int Engine::kv_len(int seq, int* out) {
+    if (!out) return fail(HM_ERR_INVALID, "kv_len: null output");
+    if (batch_ == 0) {
+        *out = 0;
+        return HM_OK;
+    }
+    if (seq < 0 || seq >= batch_) return fail(HM_ERR_INVALID, "kv_len: sequence index out of range");
+    *out = len_[seq];
+    return HM_OK;
+}
+
+int Engine::kv_append(int seq, int layer, const float* k_rows, const float* v_rows, int n_new, int advance) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "kv_append before kv_alloc");
+    if (seq < 0 || seq >= batch_ || layer < 0 || layer >= L_ || n_new < 0) return fail(HM_ERR_INVALID, "kv_append: index out of range");
+    if (len_[seq] + n_new > max_seq_)
+        return fail(HM_ERR_KV_FULL, "KV cache full (" + std::to_string(len_[seq]) + " + " + std::to_string(n_new) + " > " + std::to_string(max_seq_) + ")");
+    if (n_new > 0 && (k_rows || v_rows)) {
+        const size_t bytes = (size_t)kvh_ * n_new * hd_ * 4;
+        float *dk = nullptr, *dv = nullptr;
+        if (k_rows) {
+            HM_CUDA(cudaMalloc(&dk, bytes));
+            HM_CUDA(cudaMemcpyAsync(dk, k_rows, bytes, cudaMemcpyHostToDevice, stream_));
+        }
+        if (v_rows) {
+            HM_CUDA(cudaMalloc(&dv, bytes));
+            HM_CUDA(cudaMemcpyAsync(dv, v_rows, bytes, cudaMemcpyHostToDevice, stream_));
+        }
+        KvDesc kv{k_pool_[layer], v_pool_[layer], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+        cudaError_t ce = launch_kv_write_rows(kv, seq, len_[seq], dk, dv, n_new, stream_);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
+        if (dk) cudaFree(dk);
+        if (dv) cudaFree(dv);
+        if (ce != cudaSuccess) return cuda_fail(ce, "kv_append");
+    }
+    if (advance) {
+        len_[seq] += n_new;
+        HM_CUDA(cudaMemcpy(pos_dev_ + seq, &len_[seq], 4, cudaMemcpyHostToDevice));
+    }
+    return HM_OK;
+}
+
+int Engine::kv_view(int seq, int layer, float* k_out, float* v_out) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "kv_view before kv_alloc");
+    if (seq < 0 || seq >= batch_ || layer < 0 || layer >= L_ || !k_out || !v_out) return fail(HM_ERR_INVALID, "kv_view: bad arguments");
+    const int len = len_[seq];
+    if (len == 0) return HM_OK;
+    const size_t bytes = (size_t)kvh_ * len * hd_ * 4;
+    float *dk = nullptr, *dv = nullptr;
+    HM_CUDA(cudaMalloc(&dk, bytes));
+    HM_CUDA(cudaMalloc(&dv, bytes));
+    KvDesc kv{k_pool_[layer], v_pool_[layer], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+    cudaError_t ce = launch_kv_read_rows(kv, seq, len, dk, dv, stream_);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(k_out, dk, bytes, cudaMemcpyDeviceToHost, stream_);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(v_out, dv, bytes, cudaMemcpyDeviceToHost, stream_);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
+    cudaFree(dk);
+    cudaFree(dv);
+    if (ce != cudaSuccess) return cuda_fail(ce, "kv_view");
+    return HM_OK;
+}
+
+// ---- the pass ----------------------------------------------------------------------------------
+
+enum ProfClass { PC_EMBED = 0, PC_QKV, PC_ATTN, PC_O, PC_GATE_UP, PC_DOWN, PC_LM_HEAD, PC_SAMPLE, PC_COUNT };
+static const char* kProfNames[PC_COUNT] = {"embed", "qkv_rope_kvwrite", "attention", "o_proj_residual", "gate_up_swiglu", "down_residual", "lm_head", "argmax"};
+
+void Engine::prof_mark(int cls) {
+    if (!profiling_) return;
+    cudaEvent_t ev;
+    if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, stream_);
+    prof_events_.push_back(ev);
+    prof_class_.push_back(cls);
+}
+
+static int pad_m(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
+
+int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer,
+                           const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches) {
+    for (int m0 = 0; m0 < M; m0 += MAX_M) {
+        const int mv = std::min(MAX_M, M - m0), mp = pad_m(mv);
+        cudaError_t ce;
+        if (L.kind == HM_BF16) {
+            GemvArgs a{};
+            a.W = L.slabs;
+            a.slab_stride = (long long)L.K * SLAB * 2;
+            a.row_stride = SLAB * 2;
+            a.K = L.K;
+            a.N = L.N;
+            a.m_valid = mv;
+            gemv_pick_split(L.K, L.N, mp, sm_count_, &a.ksplit, &a.rows_per_split);
+            a.x = x + (size_t)m0 * ldx;
+            a.ldx = ldx;
+            a.pro = pro;
+            a.norm_w = norm_w;
+            a.eps = (float)cfg_.rms_norm_eps;
+            a.epi = epi;
+            a.y = y + (size_t)m0 * ldy;
+            a.ldy = ldy;
+            a.bias = bias;
+            a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+            a.q_dim = qdim_;
+            a.kv_dim = kvdim_;
+            a.hd = hd_;
+            a.has_qk_norm = cfg_.has_qk_norm;
+            if (layer >= 0) {
+                a.q_norm_w = layers_[layer].q_norm;
+                a.k_norm_w = layers_[layer].k_norm;
+                a.kv = KvDesc{k_pool_[layer], v_pool_[layer], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+            }
+            a.rope_cos = rope_cos_;
+            a.rope_sin = rope_sin_;
+            a.row_pos = row_pos ? row_pos + m0 : nullptr;
+            a.row_seq = row_seq ? row_seq + m0 : nullptr;
+            const int nslabs = (L.N + SLAB - 1) / SLAB;
+            a.amax_val = amax_val ? amax_val + (size_t)m0 * nslabs : nullptr;
+            a.amax_idx = amax_idx ? amax_idx + (size_t)m0 * nslabs : nullptr;
+            a.partial = partial_;
+            a.tickets = tickets_;
+            if (gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
+            ce = launch_gemv_bf16(a, mp, stream_, pdl_);
+        } else {
+            QuantArgs a{};
+            a.scales = L.scales;
+            a.codes = L.codes;
+            a.q4 = L.kind == HM_Q4_0;
+            a.K = L.K;
+            a.N = L.N;
+            a.m_valid = mv;
+            a.x = x + (size_t)m0 * ldx;
+            a.ldx = ldx;
+            a.pro = pro;
+            a.norm_w = norm_w;
+            a.eps = (float)cfg_.rms_norm_eps;
+            a.y = y + (size_t)m0 * ldy;
+            a.ldy = ldy;
+            a.bias = bias;
+            a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+            ce = launch_gemv_quant(a, mp, sm_count_, stream_, pdl_);
+        }
+        if (ce != cudaSuccess) return cuda_fail(ce, "projection launch");
+        ++*launches;
+    }
+    return HM_OK;
+}
+
+int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev,
+                         int32_t* pos_dev, uint32_t* hist_dev, int* launches) {
+    (void)advance;
+    cudaError_t ce = launch_embed_gather(embed_, embed_dtype_ == HM_BF16 ? 1 : 0, tokens_dev, M, H_, V_, h_, err_flag_, stream_, pdl_);
+    if (ce != cudaSuccess) return cuda_fail(ce, "embed_gather");
+    ++*launches;
+    prof_mark(PC_EMBED);
+    const int QKV = qdim_ + 2 * kvdim_;
+    int rc;
+    for (int l = 0; l < L_; ++l) {
+        const LayerW& w = layers_[l];
+        KvDesc kv{k_pool_[l], v_pool_[l], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+        if (w.qkv.kind == HM_BF16) {
+            rc = enqueue_linear(w.qkv, M, h_, H_, PRO_RMSNORM, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
+            if (rc) return rc;
+            prof_mark(PC_QKV);
+        } else {
+            rc = enqueue_linear(w.qkv, M, h_, H_, PRO_RMSNORM, w.in_ln, EPI_STORE, qkv_raw_, QKV, w.qkv_bias, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
+            if (rc) return rc;
+            prof_mark(PC_QKV);
+            ce = launch_post_qkv(qkv_raw_, M, heads_, kvh_, hd_, cfg_.has_qk_norm, w.q_norm, w.k_norm, (float)cfg_.rms_norm_eps, rope_cos_, rope_sin_, row_pos, row_seq, kv, q_, stream_, pdl_);
+            if (ce != cudaSuccess) return cuda_fail(ce, "post_qkv");
+            ++*launches;
+            prof_mark(PC_QKV);
+        }
+        AttnArgs at{};
+        at.q = q_;
+        at.k_pool = k_pool_[l];
+        at.v_pool = v_pool_[l];
+        at.page_table = page_table_;
+        at.row_seq = row_seq;
+        at.row_pos = row_pos;
+        at.kv_len = nullptr;
+        at.max_pages = max_pages_;
+        at.page_tokens = page_tokens_;
+        at.heads = heads_;
+        at.kv_heads = kvh_;
+        at.hd = hd_;
+        at.nsplit = att_nsplit_;
+        at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
+        at.out = attn_;
+        at.part_acc = att_acc_;
+        at.part_ml = att_ml_;
+        at.tickets = att_tickets_;
+        ce = launch_attn_decode(at, M, kv_bf16_, stream_, pdl_);
+        if (ce != cudaSuccess) return cuda_fail(ce, "attention launch");
+        ++*launches;
+        prof_mark(PC_ATTN);
+        rc = enqueue_linear(w.o, M, attn_, qdim_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
+        if (rc) return rc;
+        prof_mark(PC_O);
+        if (w.gu.kind == HM_BF16) {
+            rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
+            if (rc) return rc;
+            prof_mark(PC_GATE_UP);
+        } else {
+            rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_STORE, gu_raw_, 2 * I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
+            if (rc) return rc;
+            prof_mark(PC_GATE_UP);
+            ce = launch_silu_mul(gu_raw_, M, I_, act_, stream_, pdl_);
+            if (ce != cudaSuccess) return cuda_fail(ce, "silu_mul");
+            ++*launches;
+            prof_mark(PC_GATE_UP);
+        }
+        rc = enqueue_linear(w.down, M, act_, I_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
+        if (rc) return rc;
+        prof_mark(PC_DOWN);
+    }
+    if (lm_rows > 0) {
+        const int nslabs = (V_ + SLAB - 1) / SLAB;
+        const float* x = h_ + (size_t)lm_row0 * H_;
+        if (lm_head_.kind == HM_BF16) {
+            rc = enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches);
+            if (rc) return rc;
+            prof_mark(PC_LM_HEAD);
+            ce = launch_argmax_finish(amax_val_, amax_idx_, nslabs, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_);
+        } else {
+            rc = enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_STORE, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, nullptr, nullptr, launches);
+            if (rc) return rc;
+            prof_mark(PC_LM_HEAD);
+            ce = launch_argmax_finish(logits_, nullptr, V_, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_);
+        }
+        if (ce != cudaSuccess) return cuda_fail(ce, "argmax_finish");
+        ++*launches;
+        prof_mark(PC_SAMPLE);
+    }
+    return HM_OK;
+}
+
+int Engine::capture_decode_graph() {
+    int launches = 0;
+    HM_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_pass(batch_, tokens_dev_, pos_dev_, nullptr, 0, batch_, true, next_dev_, tokens_dev_, pos_dev_, hist_dev_, &launches);
+    cudaGraph_t g = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(stream_, &g);
+    if (rc) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaStreamEndCapture");
+    graph_ = g;
+    HM_CUDA(cudaGraphInstantiate(&graph_exec_, graph_, 0));
+    launches_per_step_ = launches;
+    return HM_OK;
+}
+
+int Engine::check_device_error() {
+    int flag = 0;
+    HM_CUDA(cudaMemcpy(&flag, err_flag_, 4, cudaMemcpyDeviceToHost));
+    if (flag) {
+        cudaMemset(err_flag_, 0, 4);
+        return fail(HM_ERR_INVALID, "token id out of range (>= vocab_size)");
+    }
+    return HM_OK;
+}
+
+// ---- GenerativeModel ---------------------------------------------------------------------------
+
+int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t* first_token) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "prefill before kv_alloc");
+    if (seq < 0 || seq >= batch_ || !ids || n < 1) return fail(HM_ERR_INVALID, "prefill: bad arguments");
+    const int len0 = len_[seq];
+    if (len0 + n > max_seq_) return fail(HM_ERR_KV_FULL, "KV cache full (" + std::to_string(len0) + " + " + std::to_string(n) + " > " + std::to_string(max_seq_) + ")");
+    for (int i = 0; i < n; ++i)
+        if (ids[i] < 0 || ids[i] >= V_) return fail(HM_ERR_INVALID, "prefill: token id out of range");
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    uint32_t* st = pin_u32_;
+    for (int i = 0; i < n; ++i) {
+        st[i] = (uint32_t)ids[i];
+        st[n + i] = (uint32_t)(len0 + i);
+        st[2 * n + i] = (uint32_t)seq;
+    }
+    HM_CUDA(cudaMemcpyAsync(pf_tokens_, st, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
+    HM_CUDA(cudaMemcpyAsync(pf_pos_, st + n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
+    HM_CUDA(cudaMemcpyAsync(pf_seq_, st + 2 * n, (size_t)n * 4, cudaMemcpyHostToDevice, stream_));
+    // pos_dev[seq] = len0+n-1; the argmax finish of the last chunk advances it to len0+n
+    st[3 * n] = (uint32_t)(len0 + n - 1);
+    HM_CUDA(cudaMemcpyAsync(pos_dev_ + seq, st + 3 * n, 4, cudaMemcpyHostToDevice, stream_));
+    int launches = 0;
+    for (int c0 = 0; c0 < n; c0 += MAX_M) {
+        const int mc = std::min(MAX_M, n - c0);
+        const bool last = c0 + mc >= n;
+        int rc = enqueue_pass(mc, pf_tokens_ + c0, pf_pos_ + c0, pf_seq_ + c0, mc - 1, last ? 1 : 0, false, next_dev_ + seq, tokens_dev_ + seq, pos_dev_ + seq, hist_dev_ + (size_t)seq * (max_seq_ + 1),
+                              &launches);
+        if (rc) return rc;
+    }
+    uint32_t* tok_pin = st + 3 * n + 1;
+    HM_CUDA(cudaMemcpyAsync(tok_pin, next_dev_ + seq, 4, cudaMemcpyDeviceToHost, stream_));
+    if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, (size_t)V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    int rc = check_device_error();
+    if (rc) return rc;
+    if (first_token) *first_token = *tok_pin;
+    len_[seq] = len0 + n;
+    return HM_OK;
+}
+
+int Engine::decode_step(const uint32_t* tokens, float* logits, uint32_t* next_tokens) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "decode_step before kv_alloc");
+    if (!tokens) return fail(HM_ERR_INVALID, "decode_step: null tokens");
+    for (int b = 0; b < batch_; ++b) {
+        if (len_[b] + 1 > max_seq_) return fail(HM_ERR_KV_FULL, "KV cache full (" + std::to_string(len_[b]) + " + 1 > " + std::to_string(max_seq_) + ")");
+        if (tokens[b] >= (uint32_t)V_) return fail(HM_ERR_INVALID, "decode_step: token id out of range");
+    }
+    std::memcpy(pin_u32_, tokens, (size_t)batch_ * 4);
+    HM_CUDA(cudaMemcpyAsync(tokens_dev_, pin_u32_, (size_t)batch_ * 4, cudaMemcpyHostToDevice, stream_));
+    HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    HM_CUDA(cudaMemcpyAsync(pin_u32_ + batch_, next_dev_, (size_t)batch_ * 4, cudaMemcpyDeviceToHost, stream_));
+    if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, (size_t)batch_ * V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    if (next_tokens) std::memcpy(next_tokens, pin_u32_ + batch_, (size_t)batch_ * 4);
+    for (int b = 0; b < batch_; ++b) len_[b] += 1;
+    return HM_OK;
+}
+
+int Engine::decode_greedy_n(const uint32_t* first_tokens, int steps, uint32_t* out_ids) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "decode_greedy_n before kv_alloc");
+    if (steps < 0 || (steps > 0 && !out_ids)) return fail(HM_ERR_INVALID, "decode_greedy_n: bad arguments");
+    for (int b = 0; b < batch_; ++b)
+        if (len_[b] + steps > max_seq_) return fail(HM_ERR_KV_FULL, "KV cache full (" + std::to_string(len_[b]) + " + " + std::to_string(steps) + " > " + std::to_string(max_seq_) + ")");
+    if (first_tokens) {
+        for (int b = 0; b < batch_; ++b)
+            if (first_tokens[b] >= (uint32_t)V_) return fail(HM_ERR_INVALID, "decode_greedy_n: token id out of range");
+        std::memcpy(pin_u32_, first_tokens, (size_t)batch_ * 4);
+        HM_CUDA(cudaMemcpyAsync(tokens_dev_, pin_u32_, (size_t)batch_ * 4, cudaMemcpyHostToDevice, stream_));
+    }
+    for (int s = 0; s < steps; ++s) HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    // history rows: token at position p of sequence b is hist[b][p]; the new ones are len+1 .. len+steps
+    for (int b = 0; b < batch_; ++b)
+        HM_CUDA(cudaMemcpyAsync(pin_u32_ + batch_ + (size_t)b * steps, hist_dev_ + (size_t)b * (max_seq_ + 1) + len_[b] + 1, (size_t)steps * 4, cudaMemcpyDeviceToHost, stream_));
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    if (steps > 0) std::memcpy(out_ids, pin_u32_ + batch_, (size_t)batch_ * steps * 4);
+    for (int b = 0; b < batch_; ++b) len_[b] += steps;
+    return HM_OK;
+}
+
+int Engine::time_decode(int warmup, int steps, float* ms_total) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "time_decode before kv_alloc");
+    if (warmup < 0 || steps < 1 || !ms_total) return fail(HM_ERR_INVALID, "time_decode: bad arguments");
+    for (int b = 0; b < batch_; ++b)
+        if (len_[b] + warmup + steps > max_seq_) return fail(HM_ERR_KV_FULL, "KV cache full: not enough room for the timed steps");
+    cudaEvent_t e0, e1;
+    HM_CUDA(cudaEventCreate(&e0));
+    HM_CUDA(cudaEventCreate(&e1));
+    for (int s = 0; s < warmup; ++s) HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    HM_CUDA(cudaEventRecord(e0, stream_));
+    for (int s = 0; s < steps; ++s) HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    HM_CUDA(cudaEventRecord(e1, stream_));
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    HM_CUDA(cudaEventElapsedTime(ms_total, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    for (int b = 0; b < batch_; ++b) len_[b] += warmup + steps;
+    return HM_OK;
+}
+
+int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "profile_decode before kv_alloc");
+    if (steps < 1 || !out || !n_out || cap < PC_COUNT) return fail(HM_ERR_INVALID, "profile_decode: bad arguments (cap >= 8)");
+    for (int b = 0; b < batch_; ++b)
+        if (len_[b] + steps > max_seq_) return fail(HM_ERR_KV_FULL, "KV cache full: not enough room for the profiled steps");
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    const bool pdl_saved = pdl_;
+    pdl_ = false;
+    profiling_ = true;
+    prof_events_.clear();
+    prof_class_.clear();
+    double kv_tokens = 0.0;
+    int rc = HM_OK, launches = 0;
+    prof_mark(-1);
+    for (int s = 0; s < steps && rc == HM_OK; ++s) {
+        for (int b = 0; b < batch_; ++b) kv_tokens += len_[b] + s + 1;
+        rc = enqueue_pass(batch_, tokens_dev_, pos_dev_, nullptr, 0, batch_, true, next_dev_, tokens_dev_, pos_dev_, hist_dev_, &launches);
+    }
+    profiling_ = false;
+    pdl_ = pdl_saved;
+    cudaError_t ce = cudaStreamSynchronize(stream_);
+    double ms[PC_COUNT] = {0};
+    int count[PC_COUNT] = {0};
+    if (rc == HM_OK && ce == cudaSuccess) {
+        for (size_t i = 1; i < prof_events_.size(); ++i) {
+            float t = 0.f;
+            cudaEventElapsedTime(&t, prof_events_[i - 1], prof_events_[i]);
+            ms[prof_class_[i]] += t;
+            count[prof_class_[i]]++;
+        }
+    }
+    for (cudaEvent_t ev : prof_events_) cudaEventDestroy(ev);
+    prof_events_.clear();
+    prof_class_.clear();
+    if (rc) return rc;
+    if (ce != cudaSuccess) return cuda_fail(ce, "profile_decode");
+    for (int b = 0; b < batch_; ++b) len_[b] += steps;
+    uint64_t bytes[PC_COUNT] = {0};
+    bytes[PC_EMBED] = (uint64_t)batch_ * H_ * (embed_dtype_ == HM_BF16 ? 2 : 4);
+    for (auto& l : layers_) {
+        bytes[PC_QKV] += l.qkv.bytes();
+        bytes[PC_O] += l.o.bytes();
+        bytes[PC_GATE_UP] += l.gu.bytes();
+        bytes[PC_DOWN] += l.down.bytes();
+    }
+    bytes[PC_LM_HEAD] = lm_head_.bytes();
+    bytes[PC_ATTN] = (uint64_t)((kv_tokens / steps) * L_ * 2.0 * kvh_ * hd_ * (kv_bf16_ ? 2 : 4));
+    bytes[PC_SAMPLE] = 0;
+    for (int c = 0; c < PC_COUNT; ++c) {
+        std::memset(&out[c], 0, sizeof(out[c]));
+        std::strncpy(out[c].name, kProfNames[c], sizeof(out[c].name) - 1);
+        out[c].launches_per_step = count[c] / steps;
+        out[c].ms_per_step = (float)(ms[c] / steps);
+        out[c].bytes_per_step = bytes[c];
+    }
+    *n_out = PC_COUNT;
+    return HM_OK;
+}
+
+// sample_token on the host (defined in capi.cu)
+uint32_t host_sample_token(const float* logits, int n, const hm_sampling& cfg, const uint32_t* generated, int ngen, uint64_t* rng);
+
+// generate_streaming_core (src/generate.rs:100-315) without the text side.
+int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, const hm_sampling* sp, uint32_t* out_ids, int* n_out) {
+    if (!n_out || !out_ids) return fail(HM_ERR_INVALID, "generate: null output");
+    *n_out = 0;
+    if (n_prompt == 0 || max_new == 0) return HM_OK;  // src/generate.rs:111-113
+    if (batch_ != 1) return fail(HM_ERR_UNSUPPORTED, "generate drives a single sequence: allocate the cache with batch = 1");
+    hm_sampling s{};
+    if (sp) s = *sp; else { s.temperature = 0.f; s.repetition_penalty = 1.f; s.top_p = 1.f; }
+    const bool device_greedy = s.temperature <= 0.f && s.repetition_penalty == 1.0f && s.frequency_penalty == 0.f && s.presence_penalty == 0.f;
+    const uint32_t eos = cfg_.eos_token_id;
+    uint32_t first = 0;
+    int rc = prefill(seq, prompt, n_prompt, nullptr, &first);
+    if (rc) return rc;
+    if (first == eos) return HM_OK;  // "EOS after prefill", src/generate.rs:159-162
+    std::vector<uint32_t> gen;
+    gen.push_back(first);
+    int real_pos = len_[seq];
+    if (device_greedy) {
+        // Greedy tokens never leave the device between steps; EOS is looked for in blocks.
+        uint32_t cur = first;
+        bool stop = false;
+        std::vector<uint32_t> blk(32);
+        while (!stop && (int)gen.size() < max_new && real_pos < max_seq_) {
+            const int want = std::min({32, max_new - (int)gen.size(), max_seq_ - real_pos});
+            rc = decode_greedy_n(&cur, want, blk.data());
+            if (rc) return rc;
+            for (int i = 0; i < want; ++i) {
+                if (blk[i] == eos) {
+                    // tokens after EOS were speculative: roll the cache length back
+                    len_[seq] = real_pos + i + 1;
+                    HM_CUDA(cudaMemcpy(pos_dev_ + seq, &len_[seq], 4, cudaMemcpyHostToDevice));
+                    stop = true;
+                    break;
+                }
+                gen.push_back(blk[i]);
+            }
+            real_pos = len_[seq];
+            cur = gen.back();
+        }
+    } else {
+        uint64_t rng;
+        if (s.seed_set) rng = s.seed | 1ull;
+        else {
+            struct timespec ts;
+            clock_gettime(CLOCK_REALTIME, &ts);
+            rng = ((uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec) | 1ull;
+        }
+        std::vector<float> logits(V_);
+        uint32_t cur = first;
+        for (int step = 1; step < max_new; ++step) {
+            if (real_pos >= max_seq_) break;
+            rc = decode_step(&cur, logits.data(), nullptr);
+            if (rc) return rc;
+            cur = host_sample_token(logits.data(), V_, s, gen.data(), (int)gen.size(), &rng);
+            real_pos += 1;
+            if (cur == eos) break;
+            gen.push_back(cur);
+        }
+    }
+    std::memcpy(out_ids, gen.data(), gen.size() * 4);
+    *n_out = (int)gen.size();
+    return HM_OK;
+}
+
+}  // namespace hm

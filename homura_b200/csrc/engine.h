@@ -1,0 +1,135 @@
+// Device-resident decode engine: weights, paged KV cache, the decode step as a CUDA graph.
+//
+// Takes the place of HfModel + ExecutionPlan::run_kv on the decode path
+// (src/hf/model.rs:37-267, src/runtime.rs:1580-1892): instead of routing host Buffers
+// between ~5 compiled kernels per layer, the step is a fixed chain of fused kernels whose
+// activations never leave HBM, captured once and replayed per token.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/homura_b200.h"
+#include "common.cuh"
+
+namespace hm {
+
+struct LinearW {
+    int K = 0, N = 0;        // N = output count of the (possibly fused) projection
+    int kind = -1;           // HM_BF16 (slab layout) | HM_Q8_0 | HM_Q4_0 (split scales + codes)
+    uint16_t* slabs = nullptr;
+    uint16_t* scales = nullptr;
+    uint8_t* codes = nullptr;
+    int loaded_parts = 0;
+    size_t bytes() const;
+};
+
+struct LayerW {
+    float* in_ln = nullptr;
+    float* post_ln = nullptr;
+    float* qkv_bias = nullptr;  // fused [q_dim + 2 kv_dim]
+    float* q_norm = nullptr;
+    float* k_norm = nullptr;
+    LinearW qkv, o, gu, down;
+};
+
+class Engine {
+   public:
+    static int create(const hm_config& cfg, int device, Engine** out, std::string* err);
+    ~Engine();
+
+    int load_tensor(const char* name, int dtype, const int64_t* shape, int ndim, const void* host, size_t nbytes);
+    int finalize();
+
+    int kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype);
+    int kv_reset(int seq);
+    int kv_len(int seq, int* out);
+    int kv_append(int seq, int layer, const float* k_rows, const float* v_rows, int n_new, int advance);
+    int kv_view(int seq, int layer, float* k_out, float* v_out);
+
+    int prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t* first_token);
+    int decode_step(const uint32_t* tokens, float* logits, uint32_t* next_tokens);
+    int decode_greedy_n(const uint32_t* first_tokens, int steps, uint32_t* out_ids);
+    int generate(int seq, const int64_t* prompt, int n_prompt, int max_new, const hm_sampling* s, uint32_t* out_ids, int* n_out);
+    int time_decode(int warmup, int steps, float* ms_total);
+    int profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out);
+
+    const hm_config& config() const { return cfg_; }
+    uint64_t weight_bytes() const;
+    cudaStream_t stream() const { return stream_; }
+    int launches_per_step() const { return launches_per_step_; }
+    std::string err;
+
+   private:
+    Engine() = default;
+    int fail(int code, const std::string& msg);
+    int cuda_fail(cudaError_t e, const char* what);
+    bool set_device();
+    int stage(const void* host, size_t nbytes, void** dev);  // temp device copy of a host tensor
+    int load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes);
+    int load_vec_f32(float** dst, size_t n_total, size_t off, int dtype, const void* host, size_t n, size_t nbytes);
+    int ensure_scratch(int rows);
+    // Enqueue one pass over M rows (decode: one row per sequence; prefill: a chunk of one
+    // sequence).  lm_row0/lm_rows select the rows that go through the LM head.
+    int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);
+    int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches);
+    int capture_decode_graph();
+    int check_device_error();
+    void prof_mark(int cls);
+
+    hm_config cfg_{};
+    int device_ = 0, sm_count_ = 148;
+    int H_ = 0, I_ = 0, heads_ = 0, kvh_ = 0, hd_ = 0, qdim_ = 0, kvdim_ = 0, L_ = 0, V_ = 0;
+    bool finalized_ = false, quant_ = false, pdl_ = true;
+    cudaStream_t stream_ = nullptr;
+
+    // weights
+    void* embed_ = nullptr;  // [V,H] bf16 (embed_dtype_ == HM_BF16) or f32
+    int embed_dtype_ = -1;
+    float* final_norm_ = nullptr;
+    std::vector<LayerW> layers_;
+    LinearW lm_head_;
+    float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
+
+    // activations / scratch for up to scratch_rows_ rows
+    int scratch_rows_ = 0;
+    float *h_ = nullptr, *q_ = nullptr, *attn_ = nullptr, *act_ = nullptr, *qkv_raw_ = nullptr, *gu_raw_ = nullptr, *logits_ = nullptr;
+    float* amax_val_ = nullptr;
+    int32_t* amax_idx_ = nullptr;
+    float* partial_ = nullptr;
+    size_t partial_floats_ = 0;
+    unsigned int* tickets_ = nullptr;
+    float *att_acc_ = nullptr, *att_ml_ = nullptr;
+    unsigned int* att_tickets_ = nullptr;
+    int att_nsplit_ = 1;
+    int* err_flag_ = nullptr;
+
+    // KV cache
+    int batch_ = 0, max_seq_ = 0, page_tokens_ = 16, max_pages_ = 0;
+    bool kv_bf16_ = false;
+    std::vector<void*> k_pool_, v_pool_;
+    int32_t* page_table_ = nullptr;
+    int32_t* pos_dev_ = nullptr;      // [batch] current length = position of the next token
+    uint32_t* tokens_dev_ = nullptr;  // [batch] input token of the next decode step
+    uint32_t* next_dev_ = nullptr;    // [batch] argmax of the last step
+    uint32_t* hist_dev_ = nullptr;    // [batch][max_seq+1] token history by position
+    std::vector<int> len_;            // host mirror of pos_dev_
+    // prefill staging (device), capacity max_seq_
+    uint32_t* pf_tokens_ = nullptr;
+    int32_t *pf_pos_ = nullptr, *pf_seq_ = nullptr;
+    // pinned host staging
+    uint32_t* pin_u32_ = nullptr;
+    size_t pin_u32_cap_ = 0;
+
+    cudaGraph_t graph_ = nullptr;
+    cudaGraphExec_t graph_exec_ = nullptr;
+    int launches_per_step_ = 0;
+
+    // per-launch event trace (only while profile_decode runs)
+    bool profiling_ = false;
+    std::vector<cudaEvent_t> prof_events_;
+    std::vector<int> prof_class_;
+};
+
+}  // namespace hm

@@ -1,0 +1,368 @@
+// Weight-streaming bf16 GEMV / skinny GEMM (M <= 8 rows of f32 activations).
+//
+// Stands in for Homura's mixed bf16 x f32 -> f32 matmul (src/graph_builder/emit_linalg.rs:
+// 1928-2008, 2224-2307) on every projection of the decode step, fused with the work the
+// reference puts in the same compiled kernel:
+//   prologue  RMSNorm of the input row            (src/hf/emitter.rs:601,790,845)
+//   epilogue  bias + QK-norm + RoPE + KV append   (src/hf/emitter.rs:604-649, src/runtime.rs:1729-1755)
+//             residual add                        (src/hf/emitter.rs:787,804)
+//             SiLU(gate) * up                     (src/hf/emitter.rs:794-799)
+//             logits + per-slab argmax            (src/hf/emitter.rs:845-846, src/generate.rs:457-468)
+//
+// HBM-bound by design: a CTA streams one contiguous run of a 128-column weight slab with
+// 128-bit loads (thread t always reads bytes [16t, 16t+16) of each 4 KB pass, so a warp
+// covers 512 contiguous bytes), keeps 8 column accumulators per thread in f32, and never
+// re-reads a weight byte.  K is split across CTAs so that even the 1.6 MB projections put
+// work on every SM; partial sums go through global scratch and the CTA that arrives last at
+// the slab's ticket adds them in split order (deterministic, no float atomics) and runs the
+// epilogue.  Nothing here spins: a CTA that is not last simply exits.
+#include "common.cuh"
+
+namespace hm {
+
+namespace {
+
+constexpr int U = 8;  // 128-bit loads in flight per thread
+
+template <int M>
+__device__ __forceinline__ void fma_row(float (&acc)[M][8], const uint4& w, const float* __restrict__ xs, int rps, int row) {
+    float f[8];
+    f[0] = bf16_lo(w.x); f[1] = bf16_hi(w.x);
+    f[2] = bf16_lo(w.y); f[3] = bf16_hi(w.y);
+    f[4] = bf16_lo(w.z); f[5] = bf16_hi(w.z);
+    f[6] = bf16_lo(w.w); f[7] = bf16_hi(w.w);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        float xv = xs[m * rps + row];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[m][j] = fmaf(xv, f[j], acc[m][j]);
+    }
+}
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i > bi); }
+
+template <int M>
+__global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    const int rps = a.rows_per_split;
+    float* xs = smem;                 // [M][rps]
+    float* red = smem + M * rps;      // [8][M][128], later vals[M][128]
+    __shared__ float s_inv[MAX_M];
+    __shared__ float s_warp[8][MAX_M];
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int slab = blockIdx.x / a.ksplit;
+    const int split = blockIdx.x - slab * a.ksplit;
+    const int k0 = split * rps;
+    const int nrows = max(0, min(a.K, k0 + rps) - k0);
+    const int cg = tid & 15, rl = tid >> 4;
+    const int niter = (nrows + ROWS_PER_PASS - 1) / ROWS_PER_PASS;
+    const bool col_ok = (slab * SLAB + cg * 8) < a.N;
+    const char* wbase = (const char*)a.W + (long long)slab * a.slab_stride + (long long)(k0 + rl) * a.row_stride + cg * 16;
+    const long long pass_stride = (long long)ROWS_PER_PASS * a.row_stride;
+
+    pdl_launch_dependents();
+
+    // First batch of weight loads is issued before the dependency wait: weights never depend
+    // on a previous kernel, so their DRAM latency overlaps the predecessor's tail.
+    uint4 w[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const bool ok = col_ok && (u * ROWS_PER_PASS + rl) < nrows;
+        w[u] = ok ? ld_stream_u4(wbase + u * pass_stride) : make_uint4(0, 0, 0, 0);
+    }
+
+    pdl_wait();
+
+    // ---- prologue: activation slice [k0, k0+nrows) of every row into shared memory ----
+    if (a.pro == PRO_RMSNORM) {
+        float ss[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            float s = 0.f;
+            const float* xr = a.x + (size_t)m * a.ldx;
+            for (int k = tid; k < a.K; k += GEMV_THREADS) {
+                float v = __ldg(xr + k);
+                s = fmaf(v, v, s);
+            }
+            ss[m] = warp_sum(s);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int m = 0; m < M; ++m) s_warp[warp][m] = ss[m];
+        }
+        __syncthreads();
+        if (tid < M) {
+            float s = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < 8; ++wv) s += s_warp[wv][tid];
+            s_inv[tid] = 1.0f / sqrtf(s / (float)a.K + a.eps);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float inv = s_inv[m];
+            const float* xr = a.x + (size_t)m * a.ldx + k0;
+            for (int r = tid; r < nrows; r += GEMV_THREADS) xs[m * rps + r] = (__ldg(xr + r) * inv) * __ldg(a.norm_w + k0 + r);
+        }
+    } else {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float* xr = a.x + (size_t)m * a.ldx + k0;
+            for (int r = tid; r < nrows; r += GEMV_THREADS) xs[m * rps + r] = __ldg(xr + r);
+        }
+    }
+    __syncthreads();
+
+    // ---- main loop: stream the slab run, 8 column accumulators per row per thread ----
+    float acc[M][8];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[m][j] = 0.f;
+
+    for (int it = 0; it < niter; it += U) {
+        uint4 cur[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) cur[u] = w[u];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int p = it + U + u;
+            const bool ok = col_ok && p < niter && (p * ROWS_PER_PASS + rl) < nrows;
+            w[u] = ok ? ld_stream_u4(wbase + (long long)p * pass_stride) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int row = (it + u) * ROWS_PER_PASS + rl;
+            if (row < nrows) fma_row<M>(acc, cur[u], xs, rps, row);
+        }
+    }
+
+    // ---- reduce the 16 row lanes: xor-16 shuffle, then across the 8 warps in smem ----
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[m][j] += __shfl_xor_sync(0xffffffffu, acc[m][j], 16);
+    if (lane < 16) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            float4* dst = reinterpret_cast<float4*>(red + ((warp * M + m) * SLAB + cg * 8));
+            dst[0] = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+            dst[1] = make_float4(acc[m][4], acc[m][5], acc[m][6], acc[m][7]);
+        }
+    }
+    __syncthreads();
+    float mine[(M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS];
+#pragma unroll
+    for (int i = 0; i < (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS; ++i) {
+        const int idx = tid + i * GEMV_THREADS;
+        float v = 0.f;
+        if (idx < M * SLAB) {
+#pragma unroll
+            for (int wv = 0; wv < 8; ++wv) v += red[wv * M * SLAB + idx];
+        }
+        mine[i] = v;
+    }
+    __syncthreads();
+    float* vals = red;  // [M][128]
+    if (a.ksplit == 1) {
+#pragma unroll
+        for (int i = 0; i < (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS; ++i) {
+            const int idx = tid + i * GEMV_THREADS;
+            if (idx < M * SLAB) vals[idx] = mine[i];
+        }
+    } else {
+        float* part = a.partial + (size_t)(slab * a.ksplit + split) * (M * SLAB);
+#pragma unroll
+        for (int i = 0; i < (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS; ++i) {
+            const int idx = tid + i * GEMV_THREADS;
+            if (idx < M * SLAB) part[idx] = mine[i];
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned int t = atomicAdd(a.tickets + slab, 1u);
+            s_last = (t == (unsigned int)(a.ksplit - 1));
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        const float* pbase = a.partial + (size_t)slab * a.ksplit * (M * SLAB);
+        for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
+            float v = 0.f;
+            for (int s = 0; s < a.ksplit; ++s) v += ld_cg_f32(pbase + (size_t)s * (M * SLAB) + idx);
+            vals[idx] = v;
+        }
+        if (tid == 0) a.tickets[slab] = 0u;  // leave the ticket clean for the next launch
+    }
+    __syncthreads();
+
+    // ---- epilogues on vals[M][128] (columns n0 .. n0+127 of the output) ----
+    const int n0 = slab * SLAB;
+    if (a.epi == EPI_STORE) {
+        for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
+            const int m = idx / SLAB, n = n0 + (idx % SLAB);
+            if (n < a.N && m < a.m_valid) {
+                float v = vals[idx];
+                if (a.bias) v += __ldg(a.bias + n);
+                if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
+                a.y[(size_t)m * a.ldy + n] = v;
+            }
+        }
+    } else if (a.epi == EPI_SWIGLU) {
+        // slab = 64 gate columns followed by the 64 matching up columns
+        for (int idx = tid; idx < M * 64; idx += GEMV_THREADS) {
+            const int m = idx / 64, c = idx % 64;
+            const int j = slab * 64 + c;
+            if (j < a.N / 2 && m < a.m_valid) {
+                const float g = vals[m * SLAB + c], u = vals[m * SLAB + 64 + c];
+                const float act = g / (1.0f + expf(-g));
+                a.y[(size_t)m * a.ldy + j] = act * u;
+            }
+        }
+    } else if (a.epi == EPI_LOGITS) {
+        for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
+            const int m = idx / SLAB, n = n0 + (idx % SLAB);
+            if (n < a.N && m < a.m_valid) a.y[(size_t)m * a.ldy + n] = vals[idx];
+        }
+        if (warp < M && warp < a.m_valid) {
+            const int m = warp;
+            float bv = -INFINITY;
+            int bi = -1;
+#pragma unroll
+            for (int i = 0; i < SLAB / 32; ++i) {
+                const int c = lane + i * 32;
+                const int n = n0 + c;
+                if (n < a.N) {
+                    const float v = vals[m * SLAB + c];
+                    if (bi < 0 || better(v, n, bv, bi)) { bv = v; bi = n; }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi >= 0 && (bi < 0 || better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) {
+                const int nslabs = (a.N + SLAB - 1) / SLAB;
+                a.amax_val[m * nslabs + slab] = bv;
+                a.amax_idx[m * nslabs + slab] = bi;
+            }
+        }
+    } else {  // EPI_QKV_ROPE
+        const int hd = a.hd, half = hd >> 1, hps = SLAB / hd;
+        // bias
+        if (a.bias) {
+            for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
+                const int n = n0 + (idx % SLAB);
+                if (n < a.N) vals[idx] += __ldg(a.bias + n);
+            }
+            __syncthreads();
+        }
+        // per-head RMSNorm of Q and K heads (Qwen3), before the rotation
+        if (a.has_qk_norm) {
+            for (int p = warp; p < M * hps; p += 8) {
+                const int m = p / hps, hh = p % hps;
+                const int nh = n0 + hh * hd;
+                if (nh >= a.q_dim + a.kv_dim || nh >= a.N) continue;  // V heads are not normalised
+                float* v = vals + m * SLAB + hh * hd;
+                float s = 0.f;
+                for (int d = lane; d < hd; d += 32) s = fmaf(v[d], v[d], s);
+                s = warp_sum(s);
+                const float inv = 1.0f / sqrtf(s / (float)hd + a.eps);
+                const float* nw = (nh < a.q_dim) ? a.q_norm_w : a.k_norm_w;
+                for (int d = lane; d < hd; d += 32) v[d] = (v[d] * inv) * __ldg(nw + d);
+            }
+            __syncthreads();
+        }
+        for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
+            const int m = idx / SLAB, c = idx % SLAB;
+            const int n = n0 + c;
+            if (n >= a.N || m >= a.m_valid) continue;
+            const int hh = c / hd, d = c % hd;
+            const int nh = n0 + hh * hd;
+            const int pos = a.row_pos[m];
+            float v = vals[idx];
+            if (nh < a.q_dim + a.kv_dim) {
+                const float other = (d < half) ? -vals[idx + half] : vals[idx - half];
+                const float cs = __ldg(a.rope_cos + (size_t)pos * hd + d);
+                const float sn = __ldg(a.rope_sin + (size_t)pos * hd + d);
+                v = fmaf(other, sn, v * cs);
+            }
+            if (nh < a.q_dim) {
+                a.y[(size_t)m * a.ldy + n] = v;
+            } else {
+                const bool is_k = nh < a.q_dim + a.kv_dim;
+                const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
+                const int seq = a.row_seq ? a.row_seq[m] : m;
+                const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
+                const size_t off = (((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens + (pos % a.kv.page_tokens)) * hd + d;
+                void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
+                if (a.kv.bf16)
+                    reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(v);
+                else
+                    reinterpret_cast<float*>(pool)[off] = v;
+            }
+        }
+    }
+}
+
+template <int M>
+cudaError_t launch_m(const GemvArgs& a, cudaStream_t st, bool pdl) {
+    const int nslabs = (a.N + SLAB - 1) / SLAB;
+    const size_t smem = sizeof(float) * ((size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB);
+    if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
+        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(nslabs * a.ksplit));
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<M>, a);
+}
+
+}  // namespace
+
+size_t gemv_partial_floats(int N, int ksplit, int M) {
+    const int nslabs = (N + SLAB - 1) / SLAB;
+    return ksplit > 1 ? (size_t)nslabs * ksplit * M * SLAB : 0;
+}
+
+// Split K so that roughly two CTAs land on every SM, each streaming at least 32 rows, with
+// the activation slice of all M rows fitting 48 KB of shared memory.
+void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_per_split) {
+    const int nslabs = (N + SLAB - 1) / SLAB;
+    const int target = 2 * sm_count;
+    int ks = (target + nslabs - 1) / nslabs;
+    const int max_by_rows = K / 32 > 0 ? K / 32 : 1;
+    if (ks > max_by_rows) ks = max_by_rows;
+    if (ks < 1) ks = 1;
+    int rps = ((K + ks - 1) / ks + ROWS_PER_PASS - 1) / ROWS_PER_PASS * ROWS_PER_PASS;
+    const int max_rps = (12288 / M) / ROWS_PER_PASS * ROWS_PER_PASS;
+    if (rps > max_rps) rps = max_rps;
+    ks = (K + rps - 1) / rps;
+    *ksplit = ks;
+    *rows_per_split = rps;
+}
+
+cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl) {
+    switch (M) {
+        case 1: return launch_m<1>(a, st, pdl);
+        case 2: return launch_m<2>(a, st, pdl);
+        case 4: return launch_m<4>(a, st, pdl);
+        case 8: return launch_m<8>(a, st, pdl);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace hm
