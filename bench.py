@@ -116,27 +116,10 @@ class ClockSampler:
 
 def dist_setup(n_gpus):
     """(rank, world, local_rank, barrier, max_over_ranks).  torch.distributed only as plumbing."""
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world == 1:
-        return 0, 1, 0, (lambda: None), (lambda v: v)
-    import torch
-    import torch.distributed as dist
+    from homura_b200.replicas import Rendezvous
 
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
-    def barrier():
-        dist.barrier()
-        torch.cuda.synchronize()
-
-    def vmax(v):
-        t = torch.tensor([float(v)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    return rank, world, local, barrier, vmax
+    rv = Rendezvous()
+    return rv.rank, rv.world, rv.local, rv.barrier, rv.max
 
 
 def cpu_sample(d, cfg, steps, warmup, prompt_len):
