@@ -123,6 +123,7 @@ SIGNATURES = {
     "hm_engine_stream": (_vp, [_vp]),
     "hm_launches_per_step": (_i32, [_vp, _i32p]),
     "hm_gemv_bf16": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "hm_gemv_bf16_noalloc": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_pack_bf16_slabs": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "hm_gemv_quant": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_dequant": (_i32, [_vp, _i32, C.c_size_t, _vp, _vp]),
@@ -485,6 +486,13 @@ def gemv_bf16(x, w_bits, layout: int = LAYOUT_KN, K: Optional[int] = None, N: Op
     out = np.empty((M, N), np.float32)
     _check(lib.hm_gemv_bf16(_ptr(x), _ptr(w), layout, M, K, N, _ptr(out), _ptr(stream)))
     return out
+
+
+def gemv_bf16_noalloc(x_addr: int, w_addr: int, layout: int, M: int, K: int, N: int, y_addr: int, stream=None):
+    """The projection for callers that may not allocate: device addresses only, scratch built
+    into the library (see hm_gemv_bf16_noalloc in include/homura_b200.h for the limits)."""
+    lib = load_library()
+    _check(lib.hm_gemv_bf16_noalloc(_ptr(x_addr), _ptr(w_addr), layout, M, K, N, _ptr(y_addr), _ptr(stream)))
 
 
 def pack_bf16_slabs(w_bits) -> np.ndarray:

@@ -156,6 +156,8 @@ bool have_device() {
 }  // namespace
 
 namespace hm {
+int set_global_error(int code, const char* msg) { return gfail(code, msg ? msg : ""); }
+
 // sample_token, src/generate.rs:698-801.  Candidates are ordered by descending probability
 // with a stable sort (the reference uses sort_unstable_by, so ties may order differently).
 uint32_t host_sample_token(const float* logits_in, int n, const hm_sampling& cfg, const uint32_t* generated, int ngen, uint64_t* rng) {

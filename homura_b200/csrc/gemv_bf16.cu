@@ -16,6 +16,10 @@
 // work on every SM; partial sums go through global scratch and the CTA that arrives last at
 // the slab's ticket adds them in split order (deterministic, no float atomics) and runs the
 // epilogue.  Nothing here spins: a CTA that is not last simply exits.
+#include <atomic>
+#include <mutex>
+
+#include "../../include/homura_b200.h"
 #include "common.cuh"
 
 namespace hm {
@@ -366,3 +370,113 @@ cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl
 }
 
 }  // namespace hm
+
+// ---- projection without any allocation -----------------------------------------------------
+//
+// hm_gemv_bf16 borrows split-K scratch from a lazily grown cudaMalloc'd buffer.  Some callers
+// must never reach an allocator from the token path: a host that drives kernels the way
+// Homura's ExecutionPlan does hands each kernel nothing but memory it already owns, and a
+// serving loop with a latency budget cannot take the device-wide synchronisation (and the
+// unbounded time) that cudaMalloc / cudaFree may cost.  For them the same kernel runs here
+// with its partial sums and slab tickets in a fixed array that is part of the library image:
+// every GPU that loads the library holds kNoAllocBytes of it until the process exits.
+namespace hm {
+int set_global_error(int code, const char* msg);  // capi.cu
+}
+
+namespace {
+constexpr size_t kNoAllocPartialBytes = 4u << 20;  // split-K partial sums
+constexpr int kNoAllocMaxSlabs = 4096;             // one ticket per 128-column slab: N <= 524288
+constexpr size_t kNoAllocBytes = kNoAllocPartialBytes + kNoAllocMaxSlabs * sizeof(unsigned int);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address; the
+// address on each device comes from cudaGetSymbolAddress, asked once per device.
+constexpr int kNoAllocMaxDevices = 64;
+void* g_noalloc_addr[kNoAllocMaxDevices];
+std::atomic<int> g_noalloc_ready[kNoAllocMaxDevices];
+std::mutex g_noalloc_mu;
+
+bool on_device(const void* p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+}  // namespace
+
+extern "C" HM_API int hm_gemv_bf16_noalloc(const float* x, const void* w_bf16, int layout, int M, int K, int N, float* y, void* stream) {
+    using namespace hm;
+    if (!x || !w_bf16 || !y || K < 1 || N < 1) return set_global_error(HM_ERR_INVALID, "hm_gemv_bf16_noalloc: null pointer or non-positive size");
+    if (M != 1 && M != 2 && M != 4 && M != 8 && M != 16)
+        return set_global_error(HM_ERR_UNSUPPORTED, "hm_gemv_bf16_noalloc: M must be 1, 2, 4, 8 or 16 (other row counts need a padded copy of x, which this entry point cannot allocate)");
+    if (layout != HM_LAYOUT_KN && layout != HM_LAYOUT_SLAB128) return set_global_error(HM_ERR_INVALID, "hm_gemv_bf16_noalloc: unknown layout");
+    if (layout == HM_LAYOUT_KN && N % 8 != 0) return set_global_error(HM_ERR_UNSUPPORTED, "hm_gemv_bf16_noalloc: row-major [K,N] needs N to be a multiple of 8");
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return set_global_error(HM_ERR_CUDA, "hm_gemv_bf16_noalloc: no CUDA device available");
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return set_global_error(HM_ERR_UNSUPPORTED, "hm_gemv_bf16_noalloc: device index beyond 63");
+    if (!on_device(x) || !on_device(w_bf16) || !on_device(y))
+        return set_global_error(HM_ERR_INVALID, "hm_gemv_bf16_noalloc: x, w and y must be device pointers (staging host buffers would need an allocation)");
+
+    const int nslabs = (N + SLAB - 1) / SLAB;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int mp = M >= MAX_M ? MAX_M : M;
+    int ksplit = 1, rps = 0;
+    gemv_pick_split(K, N, mp, sms, &ksplit, &rps);
+    const size_t need = gemv_partial_floats(N, ksplit, mp) * sizeof(float);
+    if (nslabs > kNoAllocMaxSlabs || need > kNoAllocPartialBytes)
+        return set_global_error(HM_ERR_UNSUPPORTED,
+                                "hm_gemv_bf16_noalloc: this shape needs more split-K scratch than the built-in 4 MiB + 4096 tickets; use hm_gemv_bf16");
+
+    // One-time set-up per device (with that device current): resolve the array's address.
+    if (!g_noalloc_ready[dev].load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!g_noalloc_ready[dev].load(std::memory_order_relaxed)) {
+            void* p = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p) {
+                cudaGetLastError();
+                return set_global_error(HM_ERR_CUDA, "hm_gemv_bf16_noalloc: cudaGetSymbolAddress failed for the built-in scratch array");
+            }
+            g_noalloc_addr[dev] = p;
+            g_noalloc_ready[dev].store(1, std::memory_order_release);
+        }
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_noalloc_addr[dev]);
+    float* partial = reinterpret_cast<float*>(base);
+    unsigned int* tickets = reinterpret_cast<unsigned int*>(base + kNoAllocPartialBytes);
+    cudaStream_t st = (cudaStream_t)stream;
+    // The array keeps whatever the previous call left.  Partials are fully rewritten before they
+    // are read; the tickets must start at zero, so they are cleared on the caller's stream.
+    cudaError_t ce = ksplit > 1 ? cudaMemsetAsync(tickets, 0, (size_t)nslabs * sizeof(unsigned int), st) : cudaSuccess;
+    for (int m0 = 0; m0 < M && ce == cudaSuccess; m0 += MAX_M) {
+        GemvArgs a{};
+        a.W = static_cast<const uint16_t*>(w_bf16);
+        if (layout == HM_LAYOUT_KN) {
+            a.slab_stride = SLAB * 2;
+            a.row_stride = (long long)N * 2;
+        } else {
+            a.slab_stride = (long long)K * SLAB * 2;
+            a.row_stride = SLAB * 2;
+        }
+        a.K = K;
+        a.N = N;
+        a.m_valid = mp;
+        a.ksplit = ksplit;
+        a.rows_per_split = rps;
+        a.x = x + (size_t)m0 * K;
+        a.ldx = K;
+        a.pro = PRO_PLAIN;
+        a.epi = EPI_STORE;
+        a.y = y + (size_t)m0 * N;
+        a.ldy = N;
+        a.partial = partial;
+        a.tickets = tickets;
+        ce = launch_gemv_bf16(a, mp, st, false);
+    }
+    if (ce != cudaSuccess) return set_global_error(HM_ERR_CUDA, cudaGetErrorString(ce));
+    return HM_OK;
+}

@@ -177,6 +177,23 @@ HM_API int hm_launches_per_step(hm_engine* e, int* out);
 /* y[M,N] = x[M,K] @ W, bf16 weights, f32 activations and accumulation: the mixed matmul of
  * src/graph_builder/emit_linalg.rs:1928-2008,2224-2307.  M <= 16.  stream may be NULL. */
 HM_API int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, int K, int N, float* y, void* stream);
+/* The same projection for callers that must not allocate.  It has no counterpart in the
+ * reference (whose kernels run on the CPU and never needed device scratch); it exists so that a
+ * host with a "kernels only touch memory their caller owns" rule can keep that rule on the GPU.
+ * It calls no cudaMalloc / cudaFree and
+ * no allocating library routine: the split-K scratch is a fixed array inside the library
+ * (4 MiB of partial sums + 4096 slab tickets, held by every GPU that loads the library until
+ * the process exits), so it is meant for hosts whose token path may not reach an allocator --
+ * a plan runner that hands kernels nothing but pre-owned memory, or a serving loop that cannot
+ * absorb the device-wide synchronisation an allocation may cause.
+ *   - x, w_bf16 and y must be DEVICE pointers; M must be 1, 2, 4, 8 or 16;
+ *   - shapes whose split-K scratch would exceed the built-in array (or N > 524288) are rejected
+ *     with HM_ERR_UNSUPPORTED -- use hm_gemv_bf16 for those;
+ *   - the first call on each device resolves the array's device address; make that call
+ *     before starting any stream capture;
+ *   - every call on a device shares the one array: calls that may overlap on the GPU (different
+ *     streams, different threads) race on it -- issue them on one stream or serialise them. */
+HM_API int hm_gemv_bf16_noalloc(const float* x, const void* w_bf16, int layout, int M, int K, int N, float* y, void* stream);
 /* Re-layout row-major [K,N] bf16 into HM_LAYOUT_SLAB128 (dst holds ceil(N/128)*K*128 elements). */
 HM_API int hm_pack_bf16_slabs(const void* w_kn, int K, int N, void* dst, void* stream);
 /* Q8_0 / Q4_0 dequant-matmul on GGUF blocks [N, K/32] (src/graph_builder/emit_quant.rs:30-142;
