@@ -9,73 +9,74 @@
 // [kv_heads][16 tokens][hd] in f32 or bf16, and a per-sequence page table maps token t to
 // page_table[t / 16].
 //
-// One CTA = one (row, KV head, token split).  All g = heads/kv_heads query heads that share
-// the KV head are processed together, so every K/V byte is read once per g heads.  A warp
-// owns a page at a time: it stages the page's K and V tiles in shared memory with coalesced
-// 128-bit loads, computes the 16 x g scores, folds them into running (max, sum, acc) state
-// (online softmax), and accumulates p . v with each lane owning hd/32 output elements.
-// Splits are merged by the CTA that arrives last at the (row, KV head) ticket, in split
-// order; no CTA waits on another.
+// One CTA = one (row, KV head, split) and 8 warps.  All g = heads/kv_heads query heads that
+// share the KV head are served from the same K/V bytes: the CTA stages NSUB pages at a time in
+// shared memory with coalesced 128-bit loads issued by all threads (the next group's loads are
+// in flight while the current one is being used), and warp w works on query head w % g of page
+// slot w / g: 16 x hd scores with lane (token, half of hd), an online-softmax update, and
+// p . v with each lane owning hd/32 outputs.  Page slots are merged in shared memory; the
+// splits of one (row, KV head) are either the CTAs of one thread-block cluster, merged by rank 0
+// through distributed shared memory, or independent CTAs merged through global scratch by
+// whichever arrives last at a ticket.  No CTA ever waits for another outside the hardware
+// cluster barrier.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace hm {
 namespace {
 
-constexpr int PT = 16;      // tokens per page (the only supported page size)
-constexpr int ATT_WARPS = 4;
-constexpr int G_MAX = 8;    // query heads per KV head handled by one CTA
+constexpr int PT = 16;  // tokens per page (the only supported page size)
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_THREADS = ATT_WARPS * 32;
+constexpr int G_MAX = 8;   // query heads per KV head handled by one CTA
+constexpr int MAXP = 4;    // 16-byte pieces of K (and of V) a thread may hold in flight
+
+template <int HD, bool BF16>
+struct Tile {
+    static constexpr int PER16 = BF16 ? 8 : 4;              // elements per 16-byte piece
+    static constexpr int PIECES = PT * HD / PER16;          // 16-byte pieces per [16][HD] tile
+    static constexpr int KLD = HD + 4;                      // padded K row stride (floats)
+    static constexpr int SLOT_FLOATS = PT * KLD + PT * HD;  // K tile + V tile of one page slot
+    static constexpr int MAX_NSUB = MAXP * ATT_THREADS / PIECES;
+};
+
+template <int HD, bool BF16>
+__host__ __device__ inline int pick_nsub(int g) {
+    int n = ATT_WARPS / g;
+    if (n > Tile<HD, BF16>::MAX_NSUB) n = Tile<HD, BF16>::MAX_NSUB;
+    return n < 1 ? 1 : n;
+}
 
 template <bool BF16>
-struct KvElem;
-template <>
-struct KvElem<false> {
-    using T = float;
-    static constexpr int PER16 = 4;  // elements per 16-byte load
-};
-template <>
-struct KvElem<true> {
-    using T = uint16_t;
-    static constexpr int PER16 = 8;
-};
-
-// Stage one [16][HD] page tile into shared memory as f32 rows of stride LD.
-template <int HD, bool BF16, int LD>
-__device__ __forceinline__ void load_tile(const void* src, float* dst, int lane) {
-    constexpr int PER = KvElem<BF16>::PER16;
-    constexpr int N16 = PT * HD / PER;  // 16-byte pieces in the tile
-#pragma unroll
-    for (int i = 0; i < N16 / 32; ++i) {
-        const int piece = i * 32 + lane;
-        const int e = piece * PER;
-        const int t = e / HD, d = e % HD;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + piece);
-        float* o = dst + t * LD + d;
-        if (BF16) {
-            o[0] = bf16_lo(v.x); o[1] = bf16_hi(v.x); o[2] = bf16_lo(v.y); o[3] = bf16_hi(v.y);
-            o[4] = bf16_lo(v.z); o[5] = bf16_hi(v.z); o[6] = bf16_lo(v.w); o[7] = bf16_hi(v.w);
-        } else {
-            *reinterpret_cast<float4*>(o) = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
-        }
+__device__ __forceinline__ void unpack_store(float* o, const uint4& v) {
+    if (BF16) {
+        o[0] = bf16_lo(v.x); o[1] = bf16_hi(v.x); o[2] = bf16_lo(v.y); o[3] = bf16_hi(v.y);
+        o[4] = bf16_lo(v.z); o[5] = bf16_hi(v.z); o[6] = bf16_lo(v.w); o[7] = bf16_hi(v.w);
+    } else {
+        *reinterpret_cast<float4*>(o) = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
     }
 }
 
-template <int HD, bool BF16>
-__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const AttnArgs a) {
-    constexpr int KLD = HD + 4;   // padded K row: lanes reading different tokens spread over banks
+template <int HD, bool BF16, bool CL>
+__global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs a) {
+    using TL = Tile<HD, BF16>;
+    using T = typename std::conditional<BF16, uint16_t, float>::type;
     constexpr int EPL = HD / 32;  // output elements per lane
     extern __shared__ __align__(16) float sm[];
-    float* q_s = sm;                                   // [G_MAX][HD]
-    float* k_s = q_s + G_MAX * HD;                     // [warps][16][KLD]
-    float* v_s = k_s + ATT_WARPS * PT * KLD;           // [warps][16][HD]
-    float* p_s = v_s + ATT_WARPS * PT * HD;            // [warps][G_MAX][16]
-    float* w_m = p_s + ATT_WARPS * G_MAX * PT;         // [warps][G_MAX]
-    float* w_l = w_m + ATT_WARPS * G_MAX;              // [warps][G_MAX]
-    float* w_acc = w_l + ATT_WARPS * G_MAX;            // [warps][G_MAX][HD]
+    const int g = a.heads / a.kv_heads;
+    const int nsub = pick_nsub<HD, BF16>(g);  // page slots worked on concurrently
+    float* q_s = sm;                              // [G_MAX][HD]
+    float* tiles = q_s + G_MAX * HD;              // [nsub][K tile | V tile]
+    float* p_s = tiles + nsub * TL::SLOT_FLOATS;  // [ATT_WARPS][16]
+    float* w_ml = p_s + ATT_WARPS * PT;           // [ATT_WARPS][2]
+    float* w_acc = w_ml + ATT_WARPS * 2;          // [ATT_WARPS][HD]
+    float* c_o = w_acc + ATT_WARPS * HD;          // [G_MAX][HD]   CTA result (cluster mode)
+    float* c_ml = c_o + G_MAX * HD;               // [G_MAX][2]
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
-    const int g = a.heads / a.kv_heads;
     const int head0 = kvh * g;
 
     pdl_launch_dependents();
@@ -87,128 +88,136 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const AttnA
     const int pps = (npages + a.nsplit - 1) / a.nsplit;
     const int p0 = split * pps, p1 = min(npages, p0 + pps);
     const int32_t* pt = a.page_table + (size_t)seq * a.max_pages;
+    const T* kpool = reinterpret_cast<const T*>(a.k_pool);
+    const T* vpool = reinterpret_cast<const T*>(a.v_pool);
 
-    for (int i = tid; i < g * HD; i += ATT_WARPS * 32) q_s[i] = a.q[(size_t)m * a.heads * HD + head0 * HD + i];
-    __syncthreads();
-
-    float run_m[G_MAX], run_l[G_MAX], acc[G_MAX][EPL];
+    // cooperative tile loads: thread -> (slot, piece) pairs, the same mapping for every group
+    const int total_pieces = nsub * TL::PIECES;  // per K (and per V), <= MAXP * ATT_THREADS
+    uint4 kreg[MAXP], vreg[MAXP];
+    auto issue_loads = [&](int pbase) {
 #pragma unroll
-    for (int j = 0; j < G_MAX; ++j) {
-        run_m[j] = -INFINITY;
-        run_l[j] = 0.f;
+        for (int i = 0; i < MAXP; ++i) {
+            const int idx = tid + i * ATT_THREADS;
+            kreg[i] = make_uint4(0, 0, 0, 0);
+            vreg[i] = make_uint4(0, 0, 0, 0);
+            if (idx < total_pieces) {
+                const int slot = idx / TL::PIECES, piece = idx % TL::PIECES;
+                const int p = pbase + slot;
+                if (p < p1) {
+                    const size_t tile = ((size_t)pt[p] * a.kv_heads + kvh) * PT * HD;
+                    kreg[i] = __ldg(reinterpret_cast<const uint4*>(kpool + tile) + piece);
+                    vreg[i] = __ldg(reinterpret_cast<const uint4*>(vpool + tile) + piece);
+                }
+            }
+        }
+    };
+    auto store_tiles = [&]() {
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[j][e] = 0.f;
-    }
+        for (int i = 0; i < MAXP; ++i) {
+            const int idx = tid + i * ATT_THREADS;
+            if (idx < total_pieces) {
+                const int slot = idx / TL::PIECES, piece = idx % TL::PIECES;
+                const int e = piece * TL::PER16, t = e / HD, d = e % HD;
+                float* base = tiles + slot * TL::SLOT_FLOATS;
+                unpack_store<BF16>(base + t * TL::KLD + d, kreg[i]);
+                unpack_store<BF16>(base + PT * TL::KLD + t * HD + d, vreg[i]);
+            }
+        }
+    };
 
-    float* kw = k_s + warp * PT * KLD;
-    float* vw = v_s + warp * PT * HD;
-    float* pw = p_s + warp * G_MAX * PT;
+    if (p0 < p1) issue_loads(p0);
+    for (int i = tid; i < g * HD; i += ATT_THREADS) q_s[i] = a.q[(size_t)m * a.heads * HD + head0 * HD + i];
+
+    const int j = warp % g, sub = warp / g;  // this warp's query head and page slot
+    const bool active = sub < nsub;
+    float run_m = -INFINITY, run_l = 0.f, acc[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
     const int t = lane & 15, hf = lane >> 4;
-    using T = typename KvElem<BF16>::T;
+    float* pw = p_s + warp * PT;
 
-    for (int p = p0 + warp; p < p1; p += ATT_WARPS) {
-        const int page = pt[p];
-        const size_t tile = ((size_t)page * a.kv_heads + kvh) * PT * HD;
-        load_tile<HD, BF16, KLD>(reinterpret_cast<const T*>(a.k_pool) + tile, kw, lane);
-        load_tile<HD, BF16, HD>(reinterpret_cast<const T*>(a.v_pool) + tile, vw, lane);
-        __syncwarp();
-        // scores: lane (t, hf) covers half of the head dim of token t for every head
-        float s[G_MAX];
+    for (int pb = p0; pb < p1; pb += nsub) {
+        __syncthreads();  // previous group's tiles are no longer being read (also publishes q_s)
+        store_tiles();
+        __syncthreads();
+        if (pb + nsub < p1) issue_loads(pb + nsub);  // next group in flight during the math
+        const int p = pb + sub;
+        if (active && p < p1) {
+            const float* kt = tiles + sub * TL::SLOT_FLOATS;
+            const float* vt = kt + PT * TL::KLD;
+            const float* kr = kt + t * TL::KLD + hf * (HD / 2);
+            const float* qr = q_s + j * HD + hf * (HD / 2);
+            float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < G_MAX; ++j) s[j] = 0.f;
-        const float* kr = kw + t * KLD + hf * (HD / 2);
-#pragma unroll
-        for (int dc = 0; dc < HD / 2; dc += 4) {
-            const float4 kv4 = *reinterpret_cast<const float4*>(kr + dc);
-#pragma unroll
-            for (int j = 0; j < G_MAX; ++j) {
-                if (j < g) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(q_s + j * HD + hf * (HD / 2) + dc);
-                    s[j] = fmaf(q4.x, kv4.x, s[j]);
-                    s[j] = fmaf(q4.y, kv4.y, s[j]);
-                    s[j] = fmaf(q4.z, kv4.z, s[j]);
-                    s[j] = fmaf(q4.w, kv4.w, s[j]);
-                }
+            for (int dc = 0; dc < HD / 2; dc += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kr + dc);
+                const float4 q4 = *reinterpret_cast<const float4*>(qr + dc);
+                s = fmaf(q4.x, k4.x, s);
+                s = fmaf(q4.y, k4.y, s);
+                s = fmaf(q4.z, k4.z, s);
+                s = fmaf(q4.w, k4.w, s);
             }
-        }
-        const bool valid = (p * PT + t) < kvlen;
-        float corr[G_MAX];
+            s += __shfl_xor_sync(0xffffffffu, s, 16);
+            const bool valid = (p * PT + t) < kvlen;
+            const float sc = valid ? s * a.scale : -INFINITY;
+            float mx = sc;
 #pragma unroll
-        for (int j = 0; j < G_MAX; ++j) {
-            if (j < g) {
-                float sc = s[j] + __shfl_xor_sync(0xffffffffu, s[j], 16);
-                sc = valid ? sc * a.scale : -INFINITY;
-                float mx = sc;
+            for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_new = fmaxf(run_m, mx);
+            const float pr = valid ? expf(sc - m_new) : 0.f;
+            float ps = pr;
 #pragma unroll
-                for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-                const float m_new = fmaxf(run_m[j], mx);
-                const float pr = valid ? expf(sc - m_new) : 0.f;
-                float ps = pr;
+            for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+            const float corr = expf(run_m - m_new);  // exp(-inf) = 0 on the first page
+            run_l = run_l * corr + ps;
+            run_m = m_new;
+            if (hf == 0) pw[t] = pr;
+            __syncwarp();
 #pragma unroll
-                for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-                corr[j] = expf(run_m[j] - m_new);  // exp(-inf) = 0 on the first page
-                run_l[j] = run_l[j] * corr[j] + ps;
-                run_m[j] = m_new;
-                if (hf == 0) pw[j * PT + t] = pr;
+            for (int e = 0; e < EPL; ++e) acc[e] *= corr;
+#pragma unroll
+            for (int tt = 0; tt < PT; ++tt) {
+                const float pv = pw[tt];
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[e] = fmaf(pv, vt[tt * HD + lane * EPL + e], acc[e]);
             }
+            __syncwarp();
         }
-        __syncwarp();
-        // p . v : lane owns output elements [lane*EPL, lane*EPL + EPL)
-#pragma unroll
-        for (int j = 0; j < G_MAX; ++j) {
-            if (j < g) {
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[j][e] *= corr[j];
-            }
-        }
-#pragma unroll 4
-        for (int tt = 0; tt < PT; ++tt) {
-            float vv[EPL];
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) vv[e] = vw[tt * HD + lane * EPL + e];
-#pragma unroll
-            for (int j = 0; j < G_MAX; ++j) {
-                if (j < g) {
-                    const float pr = pw[j * PT + tt];
-#pragma unroll
-                    for (int e = 0; e < EPL; ++e) acc[j][e] = fmaf(pr, vv[e], acc[j][e]);
-                }
-            }
-        }
-        __syncwarp();
     }
 
-    // ---- merge the warps of this CTA ----
-#pragma unroll
-    for (int j = 0; j < G_MAX; ++j) {
-        if (j < g) {
-            if (lane == 0) {
-                w_m[warp * G_MAX + j] = run_m[j];
-                w_l[warp * G_MAX + j] = run_l[j];
-            }
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) w_acc[(warp * G_MAX + j) * HD + lane * EPL + e] = acc[j][e];
-        }
+    // ---- merge the page slots of this CTA: warp (sub, j) -> head j ----
+    if (lane == 0) {
+        w_ml[warp * 2 + 0] = active ? run_m : -INFINITY;
+        w_ml[warp * 2 + 1] = active ? run_l : 0.f;
     }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) w_acc[warp * HD + lane * EPL + e] = active ? acc[e] : 0.f;
     __syncthreads();
 
-    // thread -> (head j, element d); CTA-level (m, l, acc) for this split
-    for (int i = tid; i < g * HD; i += ATT_WARPS * 32) {
-        const int j = i / HD, d = i % HD;
+    for (int i = tid; i < g * HD; i += ATT_THREADS) {
+        const int jj = i / HD, d = i % HD;
         float M = -INFINITY;
-#pragma unroll
-        for (int wv = 0; wv < ATT_WARPS; ++wv) M = fmaxf(M, w_m[wv * G_MAX + j]);
+        for (int sb = 0; sb < nsub; ++sb) M = fmaxf(M, w_ml[(sb * g + jj) * 2]);
         float l = 0.f, o = 0.f;
         if (M > -INFINITY) {
-#pragma unroll
-            for (int wv = 0; wv < ATT_WARPS; ++wv) {
-                const float sc = expf(w_m[wv * G_MAX + j] - M);
-                l = fmaf(w_l[wv * G_MAX + j], sc, l);
-                o = fmaf(w_acc[(wv * G_MAX + j) * HD + d], sc, o);
+            for (int sb = 0; sb < nsub; ++sb) {
+                const int w = sb * g + jj;
+                const float ms = w_ml[w * 2];
+                if (ms > -INFINITY) {
+                    const float sc = expf(ms - M);
+                    l = fmaf(w_ml[w * 2 + 1], sc, l);
+                    o = fmaf(w_acc[w * HD + d], sc, o);
+                }
             }
         }
-        const int head = head0 + j;
-        if (a.nsplit == 1) {
+        const int head = head0 + jj;
+        if (CL) {
+            c_o[i] = o;
+            if (d == 0) {
+                c_ml[jj * 2 + 0] = M;
+                c_ml[jj * 2 + 1] = l;
+            }
+        } else if (a.nsplit == 1) {
             a.out[(size_t)m * a.heads * HD + head * HD + d] = o / l;
         } else {
             const size_t pi = ((size_t)m * a.heads + head) * a.nsplit + split;
@@ -218,6 +227,30 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const AttnA
                 a.part_ml[pi * 2 + 1] = l;
             }
         }
+    }
+    if (CL) {
+        // The splits of one (row, KV head) are the CTAs of one cluster: rank 0 merges their
+        // (max, sum, acc) triples straight out of the peers' shared memory, in rank order.
+        cluster_sync_all();
+        if (cluster_ctarank() == 0) {
+            for (int i = tid; i < g * HD; i += ATT_THREADS) {
+                const int jj = i / HD, d = i % HD;
+                float M = -INFINITY;
+                for (int r = 0; r < a.nsplit; ++r) M = fmaxf(M, ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r)));
+                float l = 0.f, o = 0.f;
+                for (int r = 0; r < a.nsplit; ++r) {
+                    const float ms = ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r));
+                    if (ms > -INFINITY) {
+                        const float sc = expf(ms - M);
+                        l = fmaf(ld_dsmem_f32(dsmem_addr(c_ml + jj * 2 + 1, (uint32_t)r)), sc, l);
+                        o = fmaf(ld_dsmem_f32(dsmem_addr(c_o + i, (uint32_t)r)), sc, o);
+                    }
+                }
+                a.out[(size_t)m * a.heads * HD + (head0 + jj) * HD + d] = o / l;
+            }
+        }
+        cluster_sync_all();
+        return;
     }
     if (a.nsplit == 1) return;
 
@@ -230,9 +263,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const AttnA
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int i = tid; i < g * HD; i += ATT_WARPS * 32) {
-        const int j = i / HD, d = i % HD;
-        const int head = head0 + j;
+    for (int i = tid; i < g * HD; i += ATT_THREADS) {
+        const int jj = i / HD, d = i % HD;
+        const int head = head0 + jj;
         const size_t base = ((size_t)m * a.heads + head) * a.nsplit;
         float M = -INFINITY;
         for (int s2 = 0; s2 < a.nsplit; ++s2) M = fmaxf(M, ld_cg_f32(a.part_ml + (base + s2) * 2));
@@ -251,25 +284,54 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const AttnA
 }
 
 template <int HD, bool BF16>
-cudaError_t launch_t(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
-    constexpr int KLD = HD + 4;
-    const size_t smem = sizeof(float) * (G_MAX * HD + ATT_WARPS * PT * KLD + ATT_WARPS * PT * HD + ATT_WARPS * G_MAX * PT +
-                                         2 * ATT_WARPS * G_MAX + ATT_WARPS * G_MAX * HD);
+size_t smem_bytes(int g) {
+    using TL = Tile<HD, BF16>;
+    const int nsub = pick_nsub<HD, BF16>(g);
+    return sizeof(float) * ((size_t)G_MAX * HD + (size_t)nsub * TL::SLOT_FLOATS + ATT_WARPS * PT + ATT_WARPS * 2 + ATT_WARPS * HD + G_MAX * HD + G_MAX * 2);
+}
+
+template <int HD, bool BF16, bool CL>
+cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
+    const size_t smem = smem_bytes<HD, BF16>(a.heads / a.kv_heads);
     if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    if (CL && a.nsplit > 8) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)a.nsplit, (unsigned)a.kv_heads, (unsigned)M);
-    cfg.blockDim = dim3(ATT_WARPS * 32);
+    cfg.blockDim = dim3(ATT_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (CL) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = (unsigned)a.nsplit;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = at;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, BF16>, a);
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, BF16, CL>, a);
+}
+
+template <int HD, bool BF16>
+cudaError_t launch_t(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
+    if (a.cluster) {
+        if (a.nsplit < 1 || a.nsplit > 16) return cudaErrorInvalidValue;
+        return launch_tc<HD, BF16, true>(a, M, st, pdl);
+    }
+    return launch_tc<HD, BF16, false>(a, M, st, pdl);
 }
 
 }  // namespace
@@ -280,6 +342,15 @@ int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
     const int by_pages = (max_pages + 1) / 2;
     if (n > by_pages) n = by_pages;
     if (n > 64) n = 64;
+    if (n < 1) n = 1;
+    return n;
+}
+
+// Cluster variant: the splits of a (row, KV head) form one cluster; about two pages per CTA when
+// the context allows, at most max_cluster CTAs.
+int attn_pick_cluster(int max_pages, int max_cluster) {
+    int n = (max_pages + 1) / 2;
+    if (n > max_cluster) n = max_cluster;
     if (n < 1) n = 1;
     return n;
 }

@@ -17,6 +17,29 @@ constexpr int MAX_M = 8;
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// ---- thread-block clusters / distributed shared memory ------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Full cluster barrier with release/acquire ordering of shared-memory writes.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this CTA's shared-memory location `p` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t dsmem_addr(const void* p, uint32_t rank) {
+    uint32_t local = (uint32_t)__cvta_generic_to_shared(p), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
 // 128-bit streaming load of read-only weights: bypass L1 (each weight
 // byte is used once per token and the working set is far larger than L2).
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
@@ -92,6 +115,8 @@ struct GemvArgs {
     int K, N;
     int m_valid;            // rows >= m_valid are padding: computed, never stored
     int ksplit, rows_per_split;
+    int cluster;            // > 1: the ksplit CTAs of a slab form one thread-block cluster and reduce through
+                            // distributed shared memory (ksplit == cluster); else partial/tickets are used
     // input rows [M][ldx]
     const float* x;
     int ldx;
@@ -130,6 +155,7 @@ struct AttnArgs {
     const int32_t* row_pos;  // kv length - 1 per row (the row's own position); see kv_len
     const int32_t* kv_len;   // when non-null used instead of row_pos+1
     int max_pages, page_tokens, heads, kv_heads, hd, nsplit;
+    int cluster;          // != 0: the nsplit CTAs of a (row, KV head) are one cluster and merge through DSMEM
     float scale;
     float* out;           // [M][heads*hd]
     float* part_acc;      // [M][heads][nsplit][hd]
@@ -157,8 +183,12 @@ struct QuantArgs {
 cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl);
 size_t gemv_partial_floats(int N, int ksplit, int M);
 void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_per_split);
+// Cluster variant: ksplit = cluster size (<= max_cluster), sized so that all CTAs are resident at once.
+void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* cluster, int* rows_per_split);
+int gemv_max_cluster();  // largest cluster size the device schedules for the projection kernel (8 or 16)
 cudaError_t launch_attn_decode(const AttnArgs& a, int M, bool kv_bf16, cudaStream_t st, bool pdl);
 int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count);
+int attn_pick_cluster(int max_pages, int max_cluster);
 
 cudaError_t launch_pack_slabs_from_nk(const uint16_t* src_nk, int N, int K, uint16_t* dst, int n_off, int interleave_which, cudaStream_t st);
 cudaError_t launch_pack_slabs_from_kn(const uint16_t* src_kn, int K, int N, uint16_t* dst, cudaStream_t st);

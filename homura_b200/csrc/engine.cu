@@ -79,6 +79,9 @@ int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* 
     e->layers_.resize(e->L_);
     const char* nopdl = std::getenv("HM_NO_PDL");
     e->pdl_ = !(nopdl && nopdl[0] == '1');
+    const char* nocl = std::getenv("HM_NO_CLUSTER");
+    e->use_clusters_ = !(nocl && nocl[0] == '1');
+    e->max_cluster_ = gemv_max_cluster();
     *out = e;
     return HM_OK;
 }
@@ -422,7 +425,8 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     int rc = ensure_scratch(std::max(batch, MAX_M));
     if (rc) return rc;
     // attention split scratch
-    att_nsplit_ = attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);  // sized for the decode step (one row per sequence)
+    // sized for the decode step (one row per sequence)
+    att_nsplit_ = use_clusters_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 8)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
     HM_CUDA(cudaMalloc(&att_acc_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * hd_ * 4));
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
     HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));
@@ -513,14 +517,7 @@ int Engine::kv_view(int seq, int layer, float* k_out, float* v_out) {
 enum ProfClass { PC_EMBED = 0, PC_QKV, PC_ATTN, PC_O, PC_GATE_UP, PC_DOWN, PC_LM_HEAD, PC_SAMPLE, PC_COUNT };
 static const char* kProfNames[PC_COUNT] = {"embed", "qkv_rope_kvwrite", "attention", "o_proj_residual", "gate_up_swiglu", "down_residual", "lm_head", "argmax"};
 
-void Engine::prof_mark(int cls) {
-    if (!profiling_) return;
-    cudaEvent_t ev;
-    if (cudaEventCreate(&ev) != cudaSuccess) return;
-    cudaEventRecord(ev, stream_);
-    prof_events_.push_back(ev);
-    prof_class_.push_back(cls);
-}
+void Engine::prof_mark(int) {}
 
 static int pad_m(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 
@@ -537,7 +534,14 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.K = L.K;
             a.N = L.N;
             a.m_valid = mv;
-            gemv_pick_split(L.K, L.N, mp, sm_count_, &a.ksplit, &a.rows_per_split);
+            if (use_clusters_) {
+                gemv_pick_cluster(L.K, L.N, mp, sm_count_, max_cluster_, &a.ksplit, &a.rows_per_split);
+                a.cluster = a.ksplit > 1 && a.ksplit <= max_cluster_ ? a.ksplit : 0;
+            }
+            if (!use_clusters_ || (a.ksplit > 1 && a.cluster == 0)) {
+                a.cluster = 0;
+                gemv_pick_split(L.K, L.N, mp, sm_count_, &a.ksplit, &a.rows_per_split);
+            }
             a.x = x + (size_t)m0 * ldx;
             a.ldx = ldx;
             a.pro = pro;
@@ -566,7 +570,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.amax_idx = amax_idx ? amax_idx + (size_t)m0 * nslabs : nullptr;
             a.partial = partial_;
             a.tickets = tickets_;
-            if (gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
+            if (a.cluster == 0 && gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
             ce = launch_gemv_bf16(a, mp, stream_, pdl_);
         } else {
             QuantArgs a{};
@@ -596,27 +600,28 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
 int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev,
                          int32_t* pos_dev, uint32_t* hist_dev, int* launches) {
     (void)advance;
-    cudaError_t ce = launch_embed_gather(embed_, embed_dtype_ == HM_BF16 ? 1 : 0, tokens_dev, M, H_, V_, h_, err_flag_, stream_, pdl_);
-    if (ce != cudaSuccess) return cuda_fail(ce, "embed_gather");
-    ++*launches;
-    prof_mark(PC_EMBED);
+    cudaError_t ce = cudaSuccess;
+    auto want = [&](int cls) { return only_class_ < 0 || only_class_ == cls; };
+    if (want(PC_EMBED)) {
+        ce = launch_embed_gather(embed_, embed_dtype_ == HM_BF16 ? 1 : 0, tokens_dev, M, H_, V_, h_, err_flag_, stream_, pdl_);
+        if (ce != cudaSuccess) return cuda_fail(ce, "embed_gather");
+        ++*launches;
+    }
     const int QKV = qdim_ + 2 * kvdim_;
     int rc;
     for (int l = 0; l < L_; ++l) {
         const LayerW& w = layers_[l];
         KvDesc kv{k_pool_[l], v_pool_[l], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
-        if (w.qkv.kind == HM_BF16) {
+        if (!want(PC_QKV)) {
+        } else if (w.qkv.kind == HM_BF16) {
             rc = enqueue_linear(w.qkv, M, h_, H_, PRO_RMSNORM, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
-            prof_mark(PC_QKV);
         } else {
             rc = enqueue_linear(w.qkv, M, h_, H_, PRO_RMSNORM, w.in_ln, EPI_STORE, qkv_raw_, QKV, w.qkv_bias, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
-            prof_mark(PC_QKV);
             ce = launch_post_qkv(qkv_raw_, M, heads_, kvh_, hd_, cfg_.has_qk_norm, w.q_norm, w.k_norm, (float)cfg_.rms_norm_eps, rope_cos_, rope_sin_, row_pos, row_seq, kv, q_, stream_, pdl_);
             if (ce != cudaSuccess) return cuda_fail(ce, "post_qkv");
             ++*launches;
-            prof_mark(PC_QKV);
         }
         AttnArgs at{};
         at.q = q_;
@@ -632,52 +637,52 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.kv_heads = kvh_;
         at.hd = hd_;
         at.nsplit = att_nsplit_;
+        at.cluster = use_clusters_ ? 1 : 0;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
         at.out = attn_;
         at.part_acc = att_acc_;
         at.part_ml = att_ml_;
         at.tickets = att_tickets_;
-        ce = launch_attn_decode(at, M, kv_bf16_, stream_, pdl_);
-        if (ce != cudaSuccess) return cuda_fail(ce, "attention launch");
-        ++*launches;
-        prof_mark(PC_ATTN);
-        rc = enqueue_linear(w.o, M, attn_, qdim_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
-        if (rc) return rc;
-        prof_mark(PC_O);
-        if (w.gu.kind == HM_BF16) {
+        if (want(PC_ATTN)) {
+            ce = launch_attn_decode(at, M, kv_bf16_, stream_, pdl_);
+            if (ce != cudaSuccess) return cuda_fail(ce, "attention launch");
+            ++*launches;
+        }
+        if (want(PC_O)) {
+            rc = enqueue_linear(w.o, M, attn_, qdim_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
+            if (rc) return rc;
+        }
+        if (!want(PC_GATE_UP)) {
+        } else if (w.gu.kind == HM_BF16) {
             rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
-            prof_mark(PC_GATE_UP);
         } else {
             rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_STORE, gu_raw_, 2 * I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
-            prof_mark(PC_GATE_UP);
             ce = launch_silu_mul(gu_raw_, M, I_, act_, stream_, pdl_);
             if (ce != cudaSuccess) return cuda_fail(ce, "silu_mul");
             ++*launches;
-            prof_mark(PC_GATE_UP);
         }
-        rc = enqueue_linear(w.down, M, act_, I_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
-        if (rc) return rc;
-        prof_mark(PC_DOWN);
+        if (want(PC_DOWN)) {
+            rc = enqueue_linear(w.down, M, act_, I_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
+            if (rc) return rc;
+        }
     }
     if (lm_rows > 0) {
         const int nslabs = (V_ + SLAB - 1) / SLAB;
         const float* x = h_ + (size_t)lm_row0 * H_;
-        if (lm_head_.kind == HM_BF16) {
-            rc = enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches);
+        const bool slab_argmax = lm_head_.kind == HM_BF16;
+        if (want(PC_LM_HEAD)) {
+            rc = slab_argmax ? enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches)
+                             : enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_STORE, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, nullptr, nullptr, launches);
             if (rc) return rc;
-            prof_mark(PC_LM_HEAD);
-            ce = launch_argmax_finish(amax_val_, amax_idx_, nslabs, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_);
-        } else {
-            rc = enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_STORE, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, nullptr, nullptr, launches);
-            if (rc) return rc;
-            prof_mark(PC_LM_HEAD);
-            ce = launch_argmax_finish(logits_, nullptr, V_, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_);
         }
-        if (ce != cudaSuccess) return cuda_fail(ce, "argmax_finish");
-        ++*launches;
-        prof_mark(PC_SAMPLE);
+        if (want(PC_SAMPLE)) {
+            ce = slab_argmax ? launch_argmax_finish(amax_val_, amax_idx_, nslabs, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_)
+                             : launch_argmax_finish(logits_, nullptr, V_, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_);
+            if (ce != cudaSuccess) return cuda_fail(ce, "argmax_finish");
+            ++*launches;
+        }
     }
     return HM_OK;
 }
@@ -814,6 +819,10 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
     return HM_OK;
 }
 
+// Per class: a CUDA graph holding only that class's launches of one decode step (the real
+// arguments, programmatic edges included) is replayed `steps` times between two events on the
+// engine's stream.  The argmax class advances the device position, so it runs last and the
+// sequences do move forward by `steps` tokens.
 int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) {
     if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
     if (batch_ == 0) return fail(HM_ERR_STATE, "profile_decode before kv_alloc");
@@ -821,36 +830,47 @@ int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) 
     for (int b = 0; b < batch_; ++b)
         if (len_[b] + steps > max_seq_) return fail(HM_ERR_KV_FULL, "KV cache full: not enough room for the profiled steps");
     HM_CUDA(cudaStreamSynchronize(stream_));
-    const bool pdl_saved = pdl_;
-    pdl_ = false;
-    profiling_ = true;
-    prof_events_.clear();
-    prof_class_.clear();
     double kv_tokens = 0.0;
-    int rc = HM_OK, launches = 0;
-    prof_mark(-1);
-    for (int s = 0; s < steps && rc == HM_OK; ++s) {
-        for (int b = 0; b < batch_; ++b) kv_tokens += len_[b] + s + 1;
-        rc = enqueue_pass(batch_, tokens_dev_, pos_dev_, nullptr, 0, batch_, true, next_dev_, tokens_dev_, pos_dev_, hist_dev_, &launches);
-    }
-    profiling_ = false;
-    pdl_ = pdl_saved;
-    cudaError_t ce = cudaStreamSynchronize(stream_);
-    double ms[PC_COUNT] = {0};
+    for (int b = 0; b < batch_; ++b) kv_tokens += len_[b] + 1;
+    cudaEvent_t e0, e1;
+    HM_CUDA(cudaEventCreate(&e0));
+    HM_CUDA(cudaEventCreate(&e1));
+    float ms[PC_COUNT] = {0};
     int count[PC_COUNT] = {0};
-    if (rc == HM_OK && ce == cudaSuccess) {
-        for (size_t i = 1; i < prof_events_.size(); ++i) {
-            float t = 0.f;
-            cudaEventElapsedTime(&t, prof_events_[i - 1], prof_events_[i]);
-            ms[prof_class_[i]] += t;
-            count[prof_class_[i]]++;
+    int rc = HM_OK;
+    for (int c = 0; c < PC_COUNT && rc == HM_OK; ++c) {
+        int launches = 0;
+        only_class_ = c;
+        cudaError_t ce = cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal);
+        if (ce == cudaSuccess) rc = enqueue_pass(batch_, tokens_dev_, pos_dev_, nullptr, 0, batch_, true, next_dev_, tokens_dev_, pos_dev_, hist_dev_, &launches);
+        only_class_ = -1;
+        cudaGraph_t g = nullptr;
+        cudaError_t ce2 = cudaStreamEndCapture(stream_, &g);
+        if (ce != cudaSuccess || ce2 != cudaSuccess || rc != HM_OK) {
+            if (g) cudaGraphDestroy(g);
+            if (rc == HM_OK) rc = cuda_fail(ce != cudaSuccess ? ce : ce2, "profile capture");
+            break;
         }
+        count[c] = launches;
+        if (launches > 0) {
+            cudaGraphExec_t ge = nullptr;
+            ce = cudaGraphInstantiate(&ge, g, 0);
+            if (ce == cudaSuccess) {
+                for (int w = 0; w < 2 && c != PC_SAMPLE; ++w) cudaGraphLaunch(ge, stream_);  // warm-up (not for the class that moves the position)
+                cudaEventRecord(e0, stream_);
+                for (int s = 0; s < steps; ++s) cudaGraphLaunch(ge, stream_);
+                cudaEventRecord(e1, stream_);
+                ce = cudaStreamSynchronize(stream_);
+                if (ce == cudaSuccess) cudaEventElapsedTime(&ms[c], e0, e1);
+                cudaGraphExecDestroy(ge);
+            }
+            if (ce != cudaSuccess) rc = cuda_fail(ce, "profile replay");
+        }
+        cudaGraphDestroy(g);
     }
-    for (cudaEvent_t ev : prof_events_) cudaEventDestroy(ev);
-    prof_events_.clear();
-    prof_class_.clear();
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
     if (rc) return rc;
-    if (ce != cudaSuccess) return cuda_fail(ce, "profile_decode");
     for (int b = 0; b < batch_; ++b) len_[b] += steps;
     uint64_t bytes[PC_COUNT] = {0};
     bytes[PC_EMBED] = (uint64_t)batch_ * H_ * (embed_dtype_ == HM_BF16 ? 2 : 4);
@@ -861,13 +881,12 @@ int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) 
         bytes[PC_DOWN] += l.down.bytes();
     }
     bytes[PC_LM_HEAD] = lm_head_.bytes();
-    bytes[PC_ATTN] = (uint64_t)((kv_tokens / steps) * L_ * 2.0 * kvh_ * hd_ * (kv_bf16_ ? 2 : 4));
-    bytes[PC_SAMPLE] = 0;
+    bytes[PC_ATTN] = (uint64_t)(kv_tokens * L_ * 2.0 * kvh_ * hd_ * (kv_bf16_ ? 2 : 4));
     for (int c = 0; c < PC_COUNT; ++c) {
         std::memset(&out[c], 0, sizeof(out[c]));
         std::strncpy(out[c].name, kProfNames[c], sizeof(out[c].name) - 1);
-        out[c].launches_per_step = count[c] / steps;
-        out[c].ms_per_step = (float)(ms[c] / steps);
+        out[c].launches_per_step = count[c];
+        out[c].ms_per_step = ms[c] / steps;
         out[c].bytes_per_step = bytes[c];
     }
     *n_out = PC_COUNT;

@@ -82,6 +82,8 @@ class Engine {
     int device_ = 0, sm_count_ = 148;
     int H_ = 0, I_ = 0, heads_ = 0, kvh_ = 0, hd_ = 0, qdim_ = 0, kvdim_ = 0, L_ = 0, V_ = 0;
     bool finalized_ = false, quant_ = false, pdl_ = true;
+    bool use_clusters_ = true;  // split reductions through thread-block clusters / DSMEM (HM_NO_CLUSTER=1: global scratch + tickets)
+    int max_cluster_ = 8;
     cudaStream_t stream_ = nullptr;
 
     // weights
@@ -126,10 +128,7 @@ class Engine {
     cudaGraphExec_t graph_exec_ = nullptr;
     int launches_per_step_ = 0;
 
-    // per-launch event trace (only while profile_decode runs)
-    bool profiling_ = false;
-    std::vector<cudaEvent_t> prof_events_;
-    std::vector<int> prof_class_;
+    int only_class_ = -1;  // >= 0 while profile_decode captures the launches of one kernel class
 };
 
 }  // namespace hm

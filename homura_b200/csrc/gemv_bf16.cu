@@ -45,7 +45,7 @@ __device__ __forceinline__ void fma_row(float (&acc)[M][8], const uint4& w, cons
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i > bi); }
 
-template <int M>
+template <int M, bool CL>
 __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) float smem[];
     const int rps = a.rows_per_split;
@@ -171,7 +171,37 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
     }
     __syncthreads();
     float* vals = red;  // [M][128]
-    if (a.ksplit == 1) {
+    if (CL) {
+        // The CTAs of one cluster hold the K-splits of this slab.  Each leaves its partial in
+        // its own shared memory; after a cluster barrier rank 0 adds them in rank order through
+        // distributed shared memory (no global round trip, no atomics) and runs the epilogue.
+        constexpr int PER = (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int idx = tid + i * GEMV_THREADS;
+            if (idx < M * SLAB) vals[idx] = mine[i];
+        }
+        cluster_sync_all();
+        const uint32_t rank = cluster_ctarank();
+        if (rank == 0) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int idx = tid + i * GEMV_THREADS;
+                if (idx < M * SLAB) {
+                    float v = mine[i];
+                    for (int r = 1; r < a.ksplit; ++r) v += ld_dsmem_f32(dsmem_addr(vals + idx, (uint32_t)r));
+                    mine[i] = v;
+                }
+            }
+        }
+        cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
+        if (rank != 0) return;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int idx = tid + i * GEMV_THREADS;
+            if (idx < M * SLAB) vals[idx] = mine[i];
+        }
+    } else if (a.ksplit == 1) {
 #pragma unroll
         for (int i = 0; i < (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS; ++i) {
             const int idx = tid + i * GEMV_THREADS;
@@ -314,12 +344,16 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
     }
 }
 
-template <int M>
-cudaError_t launch_m(const GemvArgs& a, cudaStream_t st, bool pdl) {
+template <int M, bool CL>
+cudaError_t launch_mc(const GemvArgs& a, cudaStream_t st, bool pdl) {
     const int nslabs = (a.N + SLAB - 1) / SLAB;
     const size_t smem = sizeof(float) * ((size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB);
     if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
-        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    if (CL && a.cluster > 8) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
@@ -327,12 +361,32 @@ cudaError_t launch_m(const GemvArgs& a, cudaStream_t st, bool pdl) {
     cfg.blockDim = dim3(GEMV_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (CL) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = (unsigned)a.cluster;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = at;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<M>, a);
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<M, CL>, a);
+}
+
+template <int M>
+cudaError_t launch_m(const GemvArgs& a, cudaStream_t st, bool pdl) {
+    if (a.cluster > 1) {
+        if (a.cluster != a.ksplit || a.cluster > 16) return cudaErrorInvalidValue;
+        return launch_mc<M, true>(a, st, pdl);
+    }
+    return launch_mc<M, false>(a, st, pdl);
 }
 
 }  // namespace
@@ -357,6 +411,46 @@ void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_p
     ks = (K + rps - 1) / rps;
     *ksplit = ks;
     *rows_per_split = rps;
+}
+
+// Cluster split: as many K-splits per slab as keep every CTA resident in one wave (two CTAs per
+// SM), at most max_cluster, at least 32 rows each.
+void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* cluster, int* rows_per_split) {
+    const int nslabs = (N + SLAB - 1) / SLAB;
+    int cs = (2 * sm_count) / nslabs;
+    if (cs > max_cluster) cs = max_cluster;
+    if (cs < 1) cs = 1;
+    while (cs > 1 && K / cs < 32) --cs;
+    int rps = ((K + cs - 1) / cs + ROWS_PER_PASS - 1) / ROWS_PER_PASS * ROWS_PER_PASS;
+    const int max_rps = (12288 / M) / ROWS_PER_PASS * ROWS_PER_PASS;
+    if (rps > max_rps) {  // activation slice would not fit: fall back to no split-limit via more, smaller clusters is impossible, so cap
+        rps = max_rps;
+    }
+    cs = (K + rps - 1) / rps;
+    *cluster = cs;
+    *rows_per_split = rps;
+}
+
+int gemv_max_cluster() {
+    static int cached = 0;
+    if (cached) return cached;
+    cudaFuncSetAttribute(gemv_bf16_kernel<1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(16);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = 8 * 1024;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 16;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemv_bf16_kernel<1, true>, &cfg);
+    if (e != cudaSuccess) cudaGetLastError();
+    cached = (e == cudaSuccess && n >= 4) ? 16 : 8;
+    return cached;
 }
 
 cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl) {

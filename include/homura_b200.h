@@ -157,10 +157,11 @@ HM_API int hm_sample_token(const float* logits, int n, const hm_sampling* cfg, c
  * of the timed steps in milliseconds. */
 HM_API int hm_time_decode(hm_engine* e, int warmup, int steps, float* ms_total);
 /* Per-kernel-class timing of the decode step, the counterpart of HOMURA_PROFILE=1
- * (src/runtime.rs:1351-1353,1849-1873; classes as in scripts/profile.py:339-369): runs `steps`
- * decode steps launch by launch (no graph, no programmatic overlap) with a CUDA event after
- * every launch and reports, per class, launches and mean device time per step plus the
- * algorithmic bytes the class moves per step. */
+ * (src/runtime.rs:1351-1353,1849-1873; classes as in scripts/profile.py:339-369): for every
+ * class a CUDA graph with only that class's launches of one decode step is replayed `steps`
+ * times between two CUDA events on the engine's stream; reports, per class, launches and mean
+ * device time per step plus the algorithmic bytes the class moves per step.  The sequences
+ * advance by `steps` tokens. */
 typedef struct hm_kernel_stat {
     char name[32];
     int32_t launches_per_step;
