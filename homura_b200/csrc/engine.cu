@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
 
 #include "loaders.h"
@@ -104,6 +105,7 @@ Engine::~Engine() {
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
+    fr(mk_layers_dev_); fr(mk_scratch_); fr(mk_bar_); fr(mk_trace_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -431,7 +433,145 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
     HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));
     HM_CUDA(cudaMemset(att_tickets_, 0, (size_t)scratch_rows_ * kvh_ * 4));
+    // The persistent single-launch decode kernel is opt-in (HM_PERSISTENT=1): on this hardware its
+    // step time is no better than the captured kernel chain, which stays the default.
+    const char* mega = std::getenv("HM_PERSISTENT");
+    if (mega && mega[0] == '1') {
+        rc = setup_persistent();
+        if (rc) return rc;
+    }
     return capture_decode_graph();
+}
+
+// Smallest K-split count whose per-CTA critical path (items per CTA x rows per item) is within
+// 15 % of the best one: fewer splits mean fewer partials for the next phase to add up.
+static void pick_persistent_split(int nslabs, int K, int nb, int* S, int* R) {
+    const int smax = std::max(1, std::min(24, K / 16));
+    long best = -1;
+    std::vector<long> cost(smax + 1, 0);
+    for (int sp = 1; sp <= smax; ++sp) {
+        const long rows = (K + sp - 1) / sp, items = (long)nslabs * sp, per = (items + nb - 1) / nb;
+        cost[sp] = per * rows;
+        if (best < 0 || cost[sp] < best) best = cost[sp];
+    }
+    int pick = smax;
+    for (int sp = 1; sp <= smax; ++sp)
+        if (cost[sp] * 100 <= best * 115) {
+            pick = sp;
+            break;
+        }
+    *S = pick;
+    *R = (K + pick - 1) / pick;
+}
+
+int Engine::setup_persistent() {
+    use_persistent_ = false;
+    if (batch_ != 1 || quant_ || lm_head_.kind != HM_BF16) return HM_OK;
+    for (auto& l : layers_)
+        if (l.qkv.kind != HM_BF16 || l.o.kind != HM_BF16 || l.gu.kind != HM_BF16 || l.down.kind != HM_BF16) return HM_OK;
+    if (H_ > mk_xs_max() || heads_ / kvh_ > G_MAX_MK) return HM_OK;
+    int per_sm = 0;
+    if (mk_prepare(&per_sm) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        return HM_OK;
+    }
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device_);
+    if (!coop) return HM_OK;
+    const int nb = sm_count_;
+    MkArgs& a = mk_;
+    a = MkArgs{};
+    a.H = H_; a.I = I_; a.heads = heads_; a.kvh = kvh_; a.hd = hd_; a.qdim = qdim_; a.kvdim = kvdim_; a.L = L_; a.V = V_;
+    a.eps = (float)cfg_.rms_norm_eps;
+    a.scale = (float)(1.0 / std::sqrt((double)hd_));
+    a.has_qk_norm = cfg_.has_qk_norm;
+    a.kv_bf16 = kv_bf16_ ? 1 : 0;
+    a.embed_bf16 = embed_dtype_ == HM_BF16 ? 1 : 0;
+    a.slabs_qkv = (qdim_ + 2 * kvdim_ + SLAB - 1) / SLAB;
+    a.slabs_h = (H_ + SLAB - 1) / SLAB;
+    a.slabs_gu = (2 * I_ + SLAB - 1) / SLAB;
+    a.slabs_v = (V_ + SLAB - 1) / SLAB;
+    pick_persistent_split(a.slabs_qkv, H_, nb, &a.S1, &a.R1);
+    pick_persistent_split(a.slabs_h, qdim_, nb, &a.S3, &a.R3);
+    pick_persistent_split(a.slabs_gu, H_, nb, &a.S4, &a.R4);
+    pick_persistent_split(a.slabs_h, I_, nb, &a.S5, &a.R5);
+    if (std::max({a.R1, a.R3, a.R4, a.R5}) > mk_xs_max()) return HM_OK;
+    a.att_cap = std::max(1, nb / kvh_);
+    a.barriers_per_launch = 5 * L_ + 1;
+    std::vector<MkLayer> hl(L_);
+    for (int l = 0; l < L_; ++l) {
+        const LayerW& w = layers_[l];
+        hl[l] = MkLayer{w.qkv.slabs, w.o.slabs, w.gu.slabs, w.down.slabs, w.in_ln, w.post_ln, w.qkv_bias, w.q_norm, w.k_norm, k_pool_[l], v_pool_[l]};
+    }
+    HM_CUDA(cudaMalloc(&mk_layers_dev_, sizeof(MkLayer) * L_));
+    HM_CUDA(cudaMemcpy(mk_layers_dev_, hl.data(), sizeof(MkLayer) * L_, cudaMemcpyHostToDevice));
+    a.layers = mk_layers_dev_;
+    a.embed = embed_;
+    a.wlm = lm_head_.slabs;
+    a.final_norm = final_norm_;
+    a.rope_cos = rope_cos_;
+    a.rope_sin = rope_sin_;
+    a.page_table = page_table_;
+    a.token = tokens_dev_;
+    a.pos = pos_dev_;
+    a.next_tok = next_dev_;
+    a.feed_tok = tokens_dev_;
+    a.hist = hist_dev_;
+    const int g = heads_ / kvh_;
+    const size_t n_h = (size_t)a.slabs_h * SLAB;
+    a.att_cap = std::max(1, std::min(a.att_cap, max_pages_));
+    size_t off = 0;
+    auto take = [&](size_t n) { size_t o = off; off += (n + 15) / 16 * 16; return o; };
+    a.o_hcur = take(n_h); a.o_hmid = take(n_h); a.o_pqkv = take((size_t)a.S1 * a.slabs_qkv * SLAB); a.o_ssin = take(a.S1);
+    a.o_attml = take((size_t)kvh_ * a.att_cap * g * 2); a.o_attacc = take((size_t)kvh_ * a.att_cap * g * hd_); a.o_po = take((size_t)a.S3 * n_h);
+    a.o_pgu = take((size_t)a.S4 * a.slabs_gu * SLAB); a.o_sspost = take(a.S4); a.o_pdown = take((size_t)a.S5 * n_h);
+    a.layer_stride = off;
+    const size_t total = a.layer_stride * L_ + 2 * (size_t)((nb + 15) / 16 * 16);
+    HM_CUDA(cudaMalloc(&mk_scratch_, total * sizeof(LL)));
+    HM_CUDA(cudaMemset(mk_scratch_, 0, total * sizeof(LL)));  // generation 0 = never valid
+    a.ll = reinterpret_cast<LL*>(mk_scratch_);
+    a.amax_v = a.ll + a.layer_stride * L_;
+    a.amax_i = a.amax_v + (nb + 15) / 16 * 16;
+    a.logits = logits_;
+    HM_CUDA(cudaMalloc(&mk_bar_, 512));
+    HM_CUDA(cudaMemset(mk_bar_, 0, 512));
+    a.launch_idx = reinterpret_cast<unsigned int*>(mk_bar_);
+    a.err_flag = err_flag_;
+    const char* tr = std::getenv("HM_MK_TRACE");
+    if (tr && tr[0] == '1') {
+        HM_CUDA(cudaMalloc(&mk_trace_, (size_t)(a.barriers_per_launch + 1) * 3 * 8));
+        HM_CUDA(cudaMemset(mk_trace_, 0, (size_t)(a.barriers_per_launch + 1) * 3 * 8));
+        a.trace = mk_trace_;
+    }
+    mk_nb_ = nb;
+    use_persistent_ = true;
+    return HM_OK;
+}
+
+int Engine::launch_step() {
+    if (use_persistent_ && persistent_direct_) {
+        cudaError_t ce = launch_decode_persistent(mk_, mk_nb_, stream_);
+        if (ce != cudaSuccess) return cuda_fail(ce, "persistent decode launch");
+        return HM_OK;
+    }
+    HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    return HM_OK;
+}
+
+// After a synchronisation: a bounded device-side wait that ran out leaves the barrier counters
+// of the persistent kernel inconsistent, so they are reset before the error is reported.
+int Engine::check_step_error() {
+    if (!use_persistent_) return HM_OK;
+    int flag = 0;
+    HM_CUDA(cudaMemcpy(&flag, err_flag_, 4, cudaMemcpyDeviceToHost));
+    if (flag == 0) return HM_OK;
+    cudaMemset(err_flag_, 0, 4);
+    if (flag == 2) {
+        // half-written exchange slots of the failed step would look valid to a retry: invalidate them all
+        cudaMemset(mk_scratch_, 0, (mk_.layer_stride * L_ + 2 * (size_t)((mk_nb_ + 15) / 16 * 16)) * sizeof(LL));
+        return fail(HM_ERR_TIMEOUT, "a bounded device-side wait in the persistent decode kernel ran out");
+    }
+    return fail(HM_ERR_INVALID, "token id out of range (>= vocab_size)");
 }
 
 int Engine::kv_reset(int seq) {
@@ -689,6 +829,28 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
 
 int Engine::capture_decode_graph() {
     int launches = 0;
+    if (use_persistent_) {
+        // One cooperative launch per step.  Captured into a graph when the runtime accepts a
+        // cooperative kernel node; otherwise launched directly.
+        persistent_direct_ = true;
+        launches_per_step_ = 1;
+        if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            cudaError_t le = launch_decode_persistent(mk_, mk_nb_, stream_);
+            cudaGraph_t g = nullptr;
+            cudaError_t ce = cudaStreamEndCapture(stream_, &g);
+            if (le == cudaSuccess && ce == cudaSuccess && g && cudaGraphInstantiate(&graph_exec_, g, 0) == cudaSuccess) {
+                graph_ = g;
+                persistent_direct_ = false;
+            } else {
+                if (g) cudaGraphDestroy(g);
+                graph_exec_ = nullptr;
+                cudaGetLastError();
+            }
+        } else {
+            cudaGetLastError();
+        }
+        return HM_OK;
+    }
     HM_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_pass(batch_, tokens_dev_, pos_dev_, nullptr, 0, batch_, true, next_dev_, tokens_dev_, pos_dev_, hist_dev_, &launches);
     cudaGraph_t g = nullptr;
@@ -766,10 +928,17 @@ int Engine::decode_step(const uint32_t* tokens, float* logits, uint32_t* next_to
     }
     std::memcpy(pin_u32_, tokens, (size_t)batch_ * 4);
     HM_CUDA(cudaMemcpyAsync(tokens_dev_, pin_u32_, (size_t)batch_ * 4, cudaMemcpyHostToDevice, stream_));
-    HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    {
+        int lrc = launch_step();
+        if (lrc) return lrc;
+    }
     HM_CUDA(cudaMemcpyAsync(pin_u32_ + batch_, next_dev_, (size_t)batch_ * 4, cudaMemcpyDeviceToHost, stream_));
     if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, (size_t)batch_ * V_ * 4, cudaMemcpyDeviceToHost, stream_));
     HM_CUDA(cudaStreamSynchronize(stream_));
+    {
+        int erc = check_step_error();
+        if (erc) return erc;
+    }
     if (next_tokens) std::memcpy(next_tokens, pin_u32_ + batch_, (size_t)batch_ * 4);
     for (int b = 0; b < batch_; ++b) len_[b] += 1;
     return HM_OK;
@@ -787,11 +956,18 @@ int Engine::decode_greedy_n(const uint32_t* first_tokens, int steps, uint32_t* o
         std::memcpy(pin_u32_, first_tokens, (size_t)batch_ * 4);
         HM_CUDA(cudaMemcpyAsync(tokens_dev_, pin_u32_, (size_t)batch_ * 4, cudaMemcpyHostToDevice, stream_));
     }
-    for (int s = 0; s < steps; ++s) HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    for (int s = 0; s < steps; ++s) {
+        int lrc = launch_step();
+        if (lrc) return lrc;
+    }
     // history rows: token at position p of sequence b is hist[b][p]; the new ones are len+1 .. len+steps
     for (int b = 0; b < batch_; ++b)
         HM_CUDA(cudaMemcpyAsync(pin_u32_ + batch_ + (size_t)b * steps, hist_dev_ + (size_t)b * (max_seq_ + 1) + len_[b] + 1, (size_t)steps * 4, cudaMemcpyDeviceToHost, stream_));
     HM_CUDA(cudaStreamSynchronize(stream_));
+    {
+        int erc = check_step_error();
+        if (erc) return erc;
+    }
     if (steps > 0) std::memcpy(out_ids, pin_u32_ + batch_, (size_t)batch_ * steps * 4);
     for (int b = 0; b < batch_; ++b) len_[b] += steps;
     return HM_OK;
@@ -806,15 +982,42 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
     cudaEvent_t e0, e1;
     HM_CUDA(cudaEventCreate(&e0));
     HM_CUDA(cudaEventCreate(&e1));
-    for (int s = 0; s < warmup; ++s) HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    for (int s = 0; s < warmup; ++s) {
+        int lrc = launch_step();
+        if (lrc) return lrc;
+    }
     HM_CUDA(cudaStreamSynchronize(stream_));
     HM_CUDA(cudaEventRecord(e0, stream_));
-    for (int s = 0; s < steps; ++s) HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    for (int s = 0; s < steps; ++s) {
+        int lrc = launch_step();
+        if (lrc) return lrc;
+    }
     HM_CUDA(cudaEventRecord(e1, stream_));
     HM_CUDA(cudaStreamSynchronize(stream_));
     HM_CUDA(cudaEventElapsedTime(ms_total, e0, e1));
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
+    {
+        int erc = check_step_error();
+        if (erc) return erc;
+    }
+    if (use_persistent_ && mk_trace_) {
+        // phase times of the last step as seen by CTA 0 (globaltimer stamps at each grid barrier)
+        std::vector<unsigned long long> t((size_t)(mk_.barriers_per_launch + 1) * 3);
+        HM_CUDA(cudaMemcpy(t.data(), mk_trace_, t.size() * 8, cudaMemcpyDeviceToHost));
+        double sum[5] = {0, 0, 0, 0, 0}, pre[5] = {0, 0, 0, 0, 0};
+        const int nb1 = mk_.barriers_per_launch + 1;
+        for (int l = 0; l < L_; ++l)
+            for (int p = 0; p < 5; ++p) {
+                sum[p] += (double)(t[l * 5 + p + 1] - t[l * 5 + p]);
+                const unsigned long long sm = t[nb1 + (l * 5 + p) * 2];  // stamp after the input slices were built
+                if (sm) pre[p] += (double)(sm - t[l * 5 + p]);
+            }
+        std::fprintf(stderr, "[hm trace] of which waiting for / building inputs: qkv %.2f o %.2f gate_up %.2f down %.2f\n", pre[0] / L_ / 1e3, pre[2] / L_ / 1e3, pre[3] / L_ / 1e3, pre[4] / L_ / 1e3);
+        const double lm = (double)(t[5 * L_ + 1] - t[5 * L_]);
+        std::fprintf(stderr, "[hm trace] per-layer mean us: qkv %.2f attn %.2f o %.2f gate_up %.2f down %.2f | lm_head %.2f | step %.2f\n", sum[0] / L_ / 1e3, sum[1] / L_ / 1e3,
+                     sum[2] / L_ / 1e3, sum[3] / L_ / 1e3, sum[4] / L_ / 1e3, lm / 1e3, (double)(t[5 * L_ + 1] - t[0]) / 1e3);
+    }
     for (int b = 0; b < batch_; ++b) len_[b] += warmup + steps;
     return HM_OK;
 }
@@ -832,6 +1035,21 @@ int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) 
     HM_CUDA(cudaStreamSynchronize(stream_));
     double kv_tokens = 0.0;
     for (int b = 0; b < batch_; ++b) kv_tokens += len_[b] + 1;
+    if (use_persistent_) {
+        // the whole step is one launch of the persistent kernel
+        float ms = 0.f;
+        const int l0 = len_[0];
+        int prc = time_decode(2, steps, &ms);
+        if (prc) return prc;
+        std::memset(&out[0], 0, sizeof(out[0]));
+        std::strncpy(out[0].name, "decode_persistent", sizeof(out[0].name) - 1);
+        out[0].launches_per_step = 1;
+        out[0].ms_per_step = ms / steps;
+        const double t_avg = l0 + 2 + (steps + 1) / 2.0;
+        out[0].bytes_per_step = weight_bytes() + (uint64_t)(t_avg * L_ * 2.0 * kvh_ * hd_ * (kv_bf16_ ? 2 : 4));
+        *n_out = 1;
+        return HM_OK;
+    }
     cudaEvent_t e0, e1;
     HM_CUDA(cudaEventCreate(&e0));
     HM_CUDA(cudaEventCreate(&e1));

@@ -12,6 +12,7 @@
 
 #include "../../include/homura_b200.h"
 #include "common.cuh"
+#include "persistent.h"
 
 namespace hm {
 
@@ -75,6 +76,9 @@ class Engine {
     int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);
     int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches);
     int capture_decode_graph();
+    int setup_persistent();   // batch-1 bf16 models: one cooperative launch per decode step
+    int launch_step();        // replay the captured graph, or launch the persistent kernel directly
+    int check_step_error();
     int check_device_error();
     void prof_mark(int cls);
 
@@ -128,7 +132,16 @@ class Engine {
     cudaGraphExec_t graph_exec_ = nullptr;
     int launches_per_step_ = 0;
 
-    int only_class_ = -1;  // >= 0 while profile_decode captures the launches of one kernel class
+    int only_class_ = -1;
+
+    // persistent decode kernel (decode_persistent.cu)
+    bool use_persistent_ = false, persistent_direct_ = false;
+    MkArgs mk_{};
+    MkLayer* mk_layers_dev_ = nullptr;
+    float* mk_scratch_ = nullptr;
+    unsigned long long* mk_bar_ = nullptr;  // step counter of the persistent kernel (u32 at offset 0)
+    int mk_nb_ = 0;
+    unsigned long long* mk_trace_ = nullptr;  // >= 0 while profile_decode captures the launches of one kernel class
 };
 
 }  // namespace hm
