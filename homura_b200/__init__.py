@@ -125,6 +125,9 @@ SIGNATURES = {
     "hm_gemv_bf16": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_gemv_bf16_noalloc": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_pack_bf16_slabs": (_i32, [_vp, _i32, _i32, _vp, _vp]),
+    "hm_gemm_bf16_tc": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "hm_tc_packed_elems": (C.c_size_t, [_i32, _i32]),
+    "hm_pack_bf16_tc": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "hm_gemv_quant": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_dequant": (_i32, [_vp, _i32, C.c_size_t, _vp, _vp]),
     "hm_rms_norm": (_i32, [_vp, _vp, C.c_float, _i32, _i32, _vp, _vp]),
@@ -501,6 +504,29 @@ def pack_bf16_slabs(w_bits) -> np.ndarray:
     K, N = w.shape
     out = np.empty(((N + 127) // 128, K, 128), np.uint16)
     _check(lib.hm_pack_bf16_slabs(_ptr(w), K, N, _ptr(out), None))
+    return out
+
+
+def pack_bf16_tc(w_bits) -> np.ndarray:
+    """Row-major [K, N] bf16 bit patterns -> the tensor-core tile layout (flat uint16 array)."""
+    lib = load_library()
+    w = np.ascontiguousarray(w_bits, dtype=np.uint16)
+    K, N = w.shape
+    out = np.empty(int(lib.hm_tc_packed_elems(K, N)), np.uint16)
+    _check(lib.hm_pack_bf16_tc(_ptr(w), K, N, _ptr(out), None))
+    return out
+
+
+def gemm_bf16_tc(x, w_tc, N: int, ksplit: int = 0) -> np.ndarray:
+    """y = x @ W for 1..64 rows on the tcgen05 path; `w_tc` comes from pack_bf16_tc."""
+    lib = load_library()
+    x = np.ascontiguousarray(np.atleast_2d(x), dtype=np.float32)
+    M, K = x.shape
+    w = np.ascontiguousarray(w_tc, dtype=np.uint16)
+    if w.size != int(lib.hm_tc_packed_elems(K, N)):
+        raise ValueError("w_tc does not match a packed [K, N] weight")
+    out = np.empty((M, N), np.float32)
+    _check(lib.hm_gemm_bf16_tc(_ptr(x), _ptr(w), M, K, N, int(ksplit), _ptr(out), None))
     return out
 
 

@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "engine.h"
+#include "gemm_tc.h"
 #include "loaders.h"
 
 using namespace hm;
@@ -568,6 +569,53 @@ int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, int K, i
         }
         ce = launch_gemv_bf16(a, mp, st, false);
     }
+    return sg.finish(ce);
+}
+
+int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int ksplit, float* y, void* stream) {
+    if (!x || !w_tc || !y || M < 1 || M > 64 || K < 1 || N < 1 || ksplit < 0 || ksplit > 8) return gfail(HM_ERR_INVALID, "hm_gemm_bf16_tc: bad arguments (1 <= M <= 64, 0 <= ksplit <= 8)");
+    NEED_DEVICE();
+    cudaStream_t st = (cudaStream_t)stream;
+    Staging sg(st);
+    const float* xd = sg.in(x, (size_t)M * K);
+    const uint16_t* wd = sg.in((const uint16_t*)w_tc, tc_packed_elems(K, N));
+    float* yd = sg.out(y, (size_t)M * N);
+    int* err = (int*)sg.scratch(sizeof(int), true);
+    if (!xd || !wd || !yd || !err) return sg.finish(cudaErrorMemoryAllocation);
+    TcArgs a{};
+    a.W = wd;
+    a.K = K;
+    a.Kp = tc_padded_k(K);
+    a.N = N;
+    a.M = M;
+    a.ksplit = ksplit ? ksplit : tc_pick_split(K, N, sm_count_of_current_device());
+    a.x = xd;
+    a.ldx = K;
+    a.y = yd;
+    a.ldy = N;
+    a.err_flag = err;
+    cudaError_t ce = launch_gemm_tc(a, st, false);
+    int herr = 0;
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(&herr, err, sizeof(int), cudaMemcpyDeviceToHost, st);
+    const int rc = sg.finish(ce);  // scratch was used, so this synchronises
+    if (rc != HM_OK) return rc;
+    if (herr) return gfail(HM_ERR_TIMEOUT, "hm_gemm_bf16_tc: a bounded device-side wait ran out");
+    return HM_OK;
+}
+
+size_t hm_tc_packed_elems(int K, int N) { return (K < 1 || N < 1) ? 0 : tc_packed_elems(K, N); }
+
+int hm_pack_bf16_tc(const void* w_kn, int K, int N, void* dst, void* stream) {
+    if (!w_kn || !dst || K < 1 || N < 1) return gfail(HM_ERR_INVALID, "hm_pack_bf16_tc: bad arguments");
+    NEED_DEVICE();
+    cudaStream_t st = (cudaStream_t)stream;
+    Staging sg(st);
+    const uint16_t* sd = sg.in((const uint16_t*)w_kn, (size_t)K * N);
+    const size_t n = tc_packed_elems(K, N);
+    uint16_t* dd = sg.out((uint16_t*)dst, n);
+    if (!sd || !dd) return sg.finish(cudaErrorMemoryAllocation);
+    cudaError_t ce = cudaMemsetAsync(dd, 0, n * 2, st);
+    if (ce == cudaSuccess) ce = launch_pack_tc(sd, N, K, true, dd, 0, -1, st);
     return sg.finish(ce);
 }
 

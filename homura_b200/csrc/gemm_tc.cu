@@ -1,0 +1,368 @@
+// Skinny tensor-core GEMM for 9..64 activation rows: y[M,N] = x[M,K] @ W with bf16 weights, f32
+// activations and f32 accumulation -- Homura's mixed matmul (src/graph_builder/emit_linalg.rs:
+// 1928-2008, 2224-2307) where the contraction is dense enough for the 5th-generation tensor cores
+// (batched decode, prefill chunks).
+//
+// Shape of the problem on a B200: the weights are streamed once from HBM (still the bound:
+// 64 rows give 64 flop/B against a ridge of ~210), so the kernel is built like the streaming
+// GEMV, with tcgen05 doing the math:
+//   * "swap AB": the 128 output features of a CTA are the MMA's M, the <= 64 activation rows are
+//     its N, so one tcgen05.mma (M=128, N=64*T, K=16) consumes a 128x16 weight tile.
+//   * weights live in HBM as the exact shared-memory image of their tiles: [n-block][k-block]
+//     [128 rows][64 k] bf16, K-major, with the 128-byte swizzle already applied, so one 16 KB
+//     cp.async.bulk per stage lands them where the UMMA descriptor expects (no tensor map, no
+//     multicast).
+//   * activations stay f32 in the model (the reference multiplies f32 x bf16).  To keep that
+//     precision on bf16 tensor cores each activation is split into T = 3 bf16 terms
+//     (x = hi + mid + lo exactly to 2^-24 relative), stacked along the MMA's N; the epilogue adds
+//     the three 64-column groups of the accumulator.  The tensor pipe has the headroom.
+//   * accumulator in TMEM (128 lanes x 256 columns), read back with tcgen05.ld by four warps.
+//   * K can be split across the CTAs of a thread-block cluster; the split accumulators are
+//     reduce-scattered by activation row through distributed shared memory, so every CTA ends up
+//     with complete 128-column rows for its share of the rows and runs the epilogue on them.
+// Roles: warp 0 = bulk-copy producer, warp 1 = TMEM owner + MMA issuer, warps 2-5 = activation
+// staging (f32 -> 3 x bf16, swizzled) and epilogue.  Every mbarrier wait is bounded.
+#include "common.cuh"
+#include "gemm_tc.h"
+
+namespace hm {
+namespace {
+
+constexpr int TC_THREADS = 192;
+constexpr int BM = 128;  // output features per CTA (MMA M)
+constexpr int BK = 64;   // k per stage (128 B of bf16)
+constexpr int MR = 64;   // activation rows (MMA N = MR * terms)
+constexpr int TERMS = 3;
+constexpr int W_TILE = BM * BK * 2;          // 16 KB
+constexpr int X_TILE = MR * TERMS * BK * 2;  // 24 KB
+constexpr int NSTG = 4;
+constexpr unsigned long long TC_SPIN = 20000000ULL;
+constexpr int TMEM_COLS = 256;
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n) : "memory"); }
+__device__ __forceinline__ void mb_arrive(uint64_t* b) { asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(s32(b)) : "memory"); }
+__device__ __forceinline__ void mb_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; on overrun raises *err and returns false (callers skip the work that needed the data).
+__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* err, volatile int* abort_flag) {
+    unsigned long long it = 0;
+    while (!mb_try(b, parity)) {
+        if (*abort_flag) return false;
+        if (++it > TC_SPIN) {
+            *abort_flag = 1;
+            if (err) atomicExch(err, 2);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand with 128-byte swizzle: rows of 128 B, groups of
+// 8 rows 1024 B apart (stride byte offset), descriptor version 1, layout type SWIZZLE_128B (2).
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);  // start address
+    d |= (uint64_t)1 << 16;                      // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset
+    d |= (uint64_t)1 << 46;                      // version
+    d |= (uint64_t)2 << 61;                      // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+
+struct TcShared {
+    uint64_t w_full[NSTG], x_full[NSTG], empty[NSTG], acc_full;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+template <bool CL>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) {
+    extern __shared__ __align__(1024) unsigned char dsm[];
+    __shared__ TcShared sh;
+    // dynamic smem: [NSTG][W tile | X tile], then the f32 tile [MR][BM] for the epilogue
+    unsigned char* stage0 = dsm + ((1024u - (s32(dsm) & 1023u)) & 1023u);  // swizzle atoms need 1024-byte alignment
+    float* out_tile = reinterpret_cast<float*>(stage0 + (size_t)NSTG * (W_TILE + X_TILE));
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cs = CL ? a.ksplit : 1;
+    const int nblk = blockIdx.x / cs;
+    const int split = blockIdx.x - nblk * cs;
+    const int kb_total = a.Kp / BK;
+    const int kb_per = (kb_total + cs - 1) / cs;
+    const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
+    const int nkb = max(0, kb1 - kb0);
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTG; ++s) {
+            mb_init(&sh.w_full[s], 1);
+            mb_init(&sh.x_full[s], 128);
+            mb_init(&sh.empty[s], 1);
+        }
+        mb_init(&sh.acc_full, 1);
+        sh.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {  // TMEM: 256 columns, allocated and later freed by this warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sh.tmem_base;
+
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ---- producer: one 16 KB bulk copy per k-block (weights never depend on a previous kernel)
+        if (lane == 0) {
+            const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(a.W) + ((size_t)nblk * kb_total + kb0) * W_TILE;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % NSTG;
+                const uint32_t par = ((i / NSTG) & 1u) ^ 1u;
+                if (!mb_wait(&sh.empty[s], par, a.err_flag, &sh.abort_flag)) break;
+                mb_expect_tx(&sh.w_full[s], W_TILE);
+                bulk_copy(stage0 + (size_t)s * (W_TILE + X_TILE), wsrc + (size_t)i * W_TILE, W_TILE, &sh.w_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(MR * TERMS);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % NSTG;
+                const uint32_t par = (i / NSTG) & 1u;
+                const bool ok = mb_wait(&sh.w_full[s], par, a.err_flag, &sh.abort_flag) && mb_wait(&sh.x_full[s], par, a.err_flag, &sh.abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t wa = s32(stage0 + (size_t)s * (W_TILE + X_TILE));
+                const uint32_t xa = wa + W_TILE;
+#pragma unroll
+                for (int ks = 0; ks < BK / 16; ++ks)
+                    umma_f16(tmem, umma_desc_k_sw128(wa + ks * 32), umma_desc_k_sw128(xa + ks * 32), idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(&sh.empty[s]);  // stage reusable once these MMAs have read it
+            }
+            umma_commit(&sh.acc_full);
+        }
+    } else {
+        // ---- warps 2..5: stage activations, then epilogue
+        const int st = tid - 64;  // 0..127
+        pdl_wait();
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % NSTG;
+            const uint32_t par = ((i / NSTG) & 1u) ^ 1u;
+            if (!mb_wait(&sh.empty[s], par, a.err_flag, &sh.abort_flag)) break;
+            unsigned char* xt = stage0 + (size_t)s * (W_TILE + X_TILE) + W_TILE;
+            const int k0 = (kb0 + i) * BK;
+            // thread -> (row m = st / 2, 32 k's): 4 x (8 elements = one 16-byte chunk per term)
+            const int m = st >> 1, kh = (st & 1) * 32;
+            const bool row_ok = m < a.M;
+            const float scale = (row_ok && a.row_scale) ? a.row_scale[m] : 1.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int kk = kh + c * 8;  // k within the block
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int k = k0 + kk + e;
+                    float x = (row_ok && k < a.K) ? a.x[(size_t)m * a.ldx + k] : 0.f;
+                    if (a.col_scale && k < a.K) x = (x * scale) * __ldg(a.col_scale + k);
+                    v[e] = x;
+                }
+                uint32_t hi[4], mid[4], lo[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    uint16_t h0, h1, m0, m1, l0, l1;
+                    {
+                        const float x = v[2 * e];
+                        h0 = f32_to_bf16_rne(x);
+                        const float r1 = x - bf16_bits_to_f32(h0);
+                        m0 = f32_to_bf16_rne(r1);
+                        l0 = f32_to_bf16_rne(r1 - bf16_bits_to_f32(m0));
+                    }
+                    {
+                        const float x = v[2 * e + 1];
+                        h1 = f32_to_bf16_rne(x);
+                        const float r1 = x - bf16_bits_to_f32(h1);
+                        m1 = f32_to_bf16_rne(r1);
+                        l1 = f32_to_bf16_rne(r1 - bf16_bits_to_f32(m1));
+                    }
+                    hi[e] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+                    mid[e] = (uint32_t)m0 | ((uint32_t)m1 << 16);
+                    lo[e] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+                }
+                const int chunk = kk >> 3;
+#pragma unroll
+                for (int t = 0; t < TERMS; ++t) {
+                    const int row = t * MR + m;  // row of the B tile (MMA N index)
+                    const uint32_t off = (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+                    const uint32_t* src = t == 0 ? hi : (t == 1 ? mid : lo);
+                    *reinterpret_cast<uint4*>(xt + off) = make_uint4(src[0], src[1], src[2], src[3]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+            mb_arrive(&sh.x_full[s]);
+        }
+        // ---- accumulator -> registers -> f32 tile in shared memory [m][128]
+        const bool acc_ok = __all_sync(0xffffffffu, mb_wait(&sh.acc_full, 0, a.err_flag, &sh.abort_flag));
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int lane_base = (warp & 3) * 32;  // a warp may only touch its own quarter of the TMEM lanes
+        const int n_local = lane_base + lane;   // output feature within the CTA's 128
+        if (acc_ok && nkb > 0) {
+#pragma unroll
+            for (int c0 = 0; c0 < MR; c0 += 16) {
+                uint32_t r[TERMS][16];
+#pragma unroll
+                for (int t = 0; t < TERMS; ++t) {
+                    const uint32_t taddr = tmem + ((uint32_t)lane_base << 16) + (uint32_t)(t * MR + c0);
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                        : "=r"(r[t][0]), "=r"(r[t][1]), "=r"(r[t][2]), "=r"(r[t][3]), "=r"(r[t][4]), "=r"(r[t][5]), "=r"(r[t][6]), "=r"(r[t][7]), "=r"(r[t][8]), "=r"(r[t][9]),
+                          "=r"(r[t][10]), "=r"(r[t][11]), "=r"(r[t][12]), "=r"(r[t][13]), "=r"(r[t][14]), "=r"(r[t][15])
+                        : "r"(taddr));
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    // small terms first: lo + mid, then + hi
+                    const float v = (__uint_as_float(r[2][j]) + __uint_as_float(r[1][j])) + __uint_as_float(r[0][j]);
+                    out_tile[(c0 + j) * BM + n_local] = v;
+                }
+            }
+        } else {
+            for (int mm = 0; mm < MR; ++mm) out_tile[mm * BM + n_local] = 0.f;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+
+    // ---- epilogue; with split-K the accumulators are first reduce-scattered by activation row
+    //      through distributed shared memory (each CTA sums, in rank order, its share of the rows)
+    pdl_wait();
+    const int n0 = nblk * BM;
+    int m_lo = 0, m_hi = a.M;
+    if (CL) {
+        cluster_sync_all();
+        const int rows_per = (a.M + cs - 1) / cs;
+        m_lo = min(a.M, split * rows_per);
+        m_hi = min(a.M, m_lo + rows_per);
+    }
+    for (int idx = tid; idx < (m_hi - m_lo) * BM; idx += TC_THREADS) {
+        const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
+        float v;
+        if (CL) {
+            v = 0.f;
+            for (int r = 0; r < cs; ++r) v += ld_dsmem_f32(dsmem_addr(out_tile + m * BM + c, (uint32_t)r));
+        } else {
+            v = out_tile[m * BM + c];
+        }
+        if (n < a.N) {
+            if (a.bias) v += __ldg(a.bias + n);
+            if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
+            a.y[(size_t)m * a.ldy + n] = v;
+        }
+    }
+    if (CL) cluster_sync_all();  // a CTA may exit only after its tile was read by its peers
+}
+
+}  // namespace
+
+size_t tc_smem_bytes() { return (size_t)NSTG * (W_TILE + X_TILE) + (size_t)MR * BM * 4 + 1024; }
+size_t tc_packed_elems(int K, int N) { return (size_t)((N + BM - 1) / BM) * ((K + BK - 1) / BK) * BM * BK; }
+int tc_padded_k(int K) { return (K + BK - 1) / BK * BK; }
+int tc_pick_split(int K, int N, int sm_count) {
+    const int nblk = (N + BM - 1) / BM, kb = (K + BK - 1) / BK;
+    int s = sm_count / nblk;  // CTAs per n-block that still fit one wave (1 CTA per SM)
+    if (s > 8) s = 8;
+    while (s > 1 && kb / s < 4) --s;  // keep at least 4 k-blocks per CTA
+    return s < 1 ? 1 : s;
+}
+
+cudaError_t launch_gemm_tc(const TcArgs& a, cudaStream_t st, bool pdl) {
+    if (a.M < 1 || a.M > MR || a.Kp % BK != 0) return cudaErrorInvalidValue;
+    const int nblk = (a.N + BM - 1) / BM;
+    const bool cl = a.ksplit > 1;
+    const size_t smem = tc_smem_bytes();
+    cudaError_t e = cl ? cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                       : cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(nblk * (cl ? a.ksplit : 1)));
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cl) {
+        if (a.ksplit > 8) return cudaErrorInvalidValue;
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = (unsigned)a.ksplit;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = n;
+    return cl ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, a) : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, a);
+}
+
+// ---- weight packing: [N][K] (HF [out,in]) or [K][N] bf16 -> swizzled K-major tiles ----------
+namespace {
+__global__ void pack_tc_kernel(const uint16_t* __restrict__ src, int N, int K, int src_is_kn, uint16_t* __restrict__ dst, int n_off, int interleave_which) {
+    const int kb_total = (K + BK - 1) / BK;
+    const size_t total = (size_t)N * kb_total * BK;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int kk = (int)(i % BK);
+        const int kb = (int)((i / BK) % kb_total);
+        const int n = (int)(i / ((size_t)BK * kb_total));
+        const int k = kb * BK + kk;
+        const uint16_t v = k < K ? (src_is_kn ? src[(size_t)k * N + n] : src[(size_t)n * K + k]) : (uint16_t)0;
+        const int no = interleave_which >= 0 ? (n / 64) * BM + interleave_which * 64 + (n % 64) : n + n_off;
+        const int nb = no / BM, row = no % BM;
+        const int chunk = kk >> 3, e = kk & 7;
+        const size_t tile = ((size_t)nb * kb_total + kb) * (BM * BK);
+        dst[tile + (size_t)row * BK + (size_t)((chunk ^ (row & 7)) << 3) + e] = v;
+    }
+}
+}  // namespace
+
+cudaError_t launch_pack_tc(const uint16_t* src, int N, int K, bool src_is_kn, uint16_t* dst, int n_off, int interleave_which, cudaStream_t st) {
+    const size_t total = (size_t)N * ((K + BK - 1) / BK) * BK;
+    size_t g = (total + 255) / 256;
+    if (g > 148 * 32) g = 148 * 32;
+    if (g < 1) g = 1;
+    pack_tc_kernel<<<(unsigned)g, 256, 0, st>>>(src, N, K, src_is_kn ? 1 : 0, dst, n_off, interleave_which);
+    return cudaGetLastError();
+}
+
+}  // namespace hm

@@ -1,0 +1,33 @@
+// Argument block and launchers of the tensor-core skinny GEMM (gemm_tc.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hm {
+
+struct TcArgs {
+    const uint16_t* W;  // swizzled K-major tiles [n-block][k-block][128][64] bf16 (launch_pack_tc)
+    int K, Kp, N;       // contraction length, K rounded up to 64, output features
+    int M;              // activation rows, 1..64
+    int ksplit;         // CTAs per cluster sharing one n-block (1 = no split, at most 8)
+    const float* x;     // [M][ldx] f32
+    int ldx;
+    const float* row_scale;  // optional [M]: 1/rms of each row  } x' = (x * row_scale[m]) * col_scale[k]
+    const float* col_scale;  // optional [K]: RMSNorm weight     }
+    const float* bias;       // optional [N]
+    const float* resid;      // optional [M][ldy], added as resid + y
+    float* y;                // [M][ldy]
+    int ldy;
+    int* err_flag;  // set to 2 when a bounded wait ran out
+};
+
+size_t tc_smem_bytes();
+size_t tc_packed_elems(int K, int N);  // bf16 elements of the packed weight (both dims padded)
+int tc_padded_k(int K);
+int tc_pick_split(int K, int N, int sm_count);  // cluster size that fills the SMs once
+cudaError_t launch_gemm_tc(const TcArgs& a, cudaStream_t st, bool pdl);
+// src is [N][K] (src_is_kn = false) or [K][N]; rows land at n_off + n, or interleaved 64/64 per
+// 128-row block when interleave_which is 0 (gate) or 1 (up).
+cudaError_t launch_pack_tc(const uint16_t* src, int N, int K, bool src_is_kn, uint16_t* dst, int n_off, int interleave_which, cudaStream_t st);
+
+}  // namespace hm

@@ -197,6 +197,17 @@ HM_API int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, i
 HM_API int hm_gemv_bf16_noalloc(const float* x, const void* w_bf16, int layout, int M, int K, int N, float* y, void* stream);
 /* Re-layout row-major [K,N] bf16 into HM_LAYOUT_SLAB128 (dst holds ceil(N/128)*K*128 elements). */
 HM_API int hm_pack_bf16_slabs(const void* w_kn, int K, int N, void* dst, void* stream);
+/* The same mixed matmul for 1 <= M <= 64 rows on the 5th-generation tensor cores (tcgen05 with the
+ * accumulator in tensor memory).  w_tc is the weight packed by hm_pack_bf16_tc.  f32 activations are
+ * split into three bf16 terms inside the kernel, so results agree with the f32 x bf16 product of
+ * emit_linalg.rs:1928-2008 to f32 rounding (accumulation order differs from the CPU loop).
+ * ksplit = CTAs per 128-feature block sharing K through a thread-block cluster: 0 = choose, else 1..8. */
+HM_API int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int ksplit, float* y, void* stream);
+/* Elements (bf16) of the packed tensor-core weight for a [K,N] matrix: both dims padded to tiles. */
+HM_API size_t hm_tc_packed_elems(int K, int N);
+/* Re-layout bf16 weights, row-major [K,N] (layout HM_LAYOUT_KN) into the tensor-core tile layout:
+ * [ceil(N/128)][ceil(K/64)][128][64], K-major, 128-byte swizzled (the shared-memory image of a tile). */
+HM_API int hm_pack_bf16_tc(const void* w_kn, int K, int N, void* dst, void* stream);
 /* Q8_0 / Q4_0 dequant-matmul on GGUF blocks [N, K/32] (src/graph_builder/emit_quant.rs:30-142;
  * Q4_0 has no counterpart in Homura, see src/gguf.rs:94-109,141).  M <= 8. */
 HM_API int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, int N, float* y, void* stream);
