@@ -517,9 +517,14 @@ def pack_bf16_tc(w_bits) -> np.ndarray:
     return out
 
 
-def gemm_bf16_tc(x, w_tc, N: int, ksplit: int = 0) -> np.ndarray:
-    """y = x @ W for 1..64 rows on the tcgen05 path; `w_tc` comes from pack_bf16_tc."""
+def gemm_bf16_tc(x, w_tc, N: int, ksplit: int = 0, K: Optional[int] = None, y=None, stream=None):
+    """y = x @ W for 1..64 rows on the tcgen05 path; `w_tc` comes from pack_bf16_tc.
+    Device mode (asynchronous): x=(addr, M), w_tc and y integer device addresses, K given."""
     lib = load_library()
+    if isinstance(x, tuple):
+        (xa, M) = x
+        _check(lib.hm_gemm_bf16_tc(_ptr(xa), _ptr(w_tc), M, K, N, int(ksplit), _ptr(y), _ptr(stream)))
+        return None
     x = np.ascontiguousarray(np.atleast_2d(x), dtype=np.float32)
     M, K = x.shape
     w = np.ascontiguousarray(w_tc, dtype=np.uint16)

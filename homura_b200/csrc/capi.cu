@@ -1,6 +1,7 @@
 // extern "C" surface declared in include/homura_b200.h.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -69,6 +70,7 @@ class Staging {
         if (zero) ok(cudaMemsetAsync(d, 0, bytes, st_));
         return d;
     }
+    bool staged() const { return !owned_.empty(); }
     bool ok(cudaError_t e) {
         if (e != cudaSuccess && err_ == cudaSuccess) err_ = e;
         return e == cudaSuccess;
@@ -101,6 +103,7 @@ struct DeviceScratch {
     float* partial = nullptr;
     size_t partial_floats = 0;
     unsigned int* tickets = nullptr;  // kMaxTickets entries
+    int* wait_err = nullptr;          // raised by a kernel whose bounded wait ran out
 };
 constexpr size_t kMaxTickets = 1 << 16;
 std::mutex g_scratch_mu;
@@ -132,6 +135,40 @@ cudaError_t get_scratch(size_t partial_floats, size_t ntickets, float** partial,
     *partial = s.partial;
     *tickets = s.tickets;
     return cudaSuccess;
+}
+
+// Device word that kernels with bounded waits raise; allocated once per device.
+cudaError_t get_wait_err(int** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    DeviceScratch& s = g_scratch[dev];
+    if (!s.wait_err) {
+        e = cudaMalloc(&s.wait_err, sizeof(int));
+        if (e != cudaSuccess) return e;
+        e = cudaMemset(s.wait_err, 0, sizeof(int));
+        if (e != cudaSuccess) return e;
+    }
+    *out = s.wait_err;
+    return cudaSuccess;
+}
+
+// After a synchronisation: reads and clears the word; true when a wait had run out.
+bool take_wait_err() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    int* p = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_scratch_mu);
+        auto it = g_scratch.find(dev);
+        if (it == g_scratch.end() || !it->second.wait_err) return false;
+        p = it->second.wait_err;
+    }
+    int h = 0;
+    if (cudaMemcpy(&h, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+    if (h) cudaMemset(p, 0, sizeof(int));
+    return h != 0;
 }
 
 int sm_count_of_current_device() {
@@ -555,14 +592,25 @@ int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, int K, i
         a.K = K;
         a.N = N;
         a.m_valid = mv;
-        gemv_pick_split(K, N, mp, sms, &a.ksplit, &a.rows_per_split);
+        // same split policy as the engine: K shared by the CTAs of a cluster, reduced through
+        // distributed shared memory; global partials + tickets when clusters are switched off
+        static const bool no_cluster = [] { const char* e = std::getenv("HM_NO_CLUSTER"); return e && e[0] == '1'; }();
+        const int max_cl = gemv_max_cluster();
+        if (!no_cluster) {
+            gemv_pick_cluster(K, N, mp, sms, max_cl, &a.ksplit, &a.rows_per_split);
+            a.cluster = a.ksplit > 1 && a.ksplit <= max_cl ? a.ksplit : 0;
+        }
+        if (no_cluster || (a.ksplit > 1 && a.cluster == 0)) {
+            a.cluster = 0;
+            gemv_pick_split(K, N, mp, sms, &a.ksplit, &a.rows_per_split);
+        }
         a.x = xd + (size_t)m0 * K;
         a.ldx = K;
         a.pro = PRO_PLAIN;
         a.epi = EPI_STORE;
         a.y = yd + (size_t)m0 * N;
         a.ldy = N;
-        const size_t pf = gemv_partial_floats(N, a.ksplit, mp);
+        const size_t pf = a.cluster ? 0 : gemv_partial_floats(N, a.ksplit, mp);
         if (pf) {
             ce = get_scratch(pf, (size_t)nslabs, &a.partial, &a.tickets);
             if (ce != cudaSuccess) break;
@@ -580,8 +628,9 @@ int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int k
     const float* xd = sg.in(x, (size_t)M * K);
     const uint16_t* wd = sg.in((const uint16_t*)w_tc, tc_packed_elems(K, N));
     float* yd = sg.out(y, (size_t)M * N);
-    int* err = (int*)sg.scratch(sizeof(int), true);
-    if (!xd || !wd || !yd || !err) return sg.finish(cudaErrorMemoryAllocation);
+    if (!xd || !wd || !yd) return sg.finish(cudaErrorMemoryAllocation);
+    int* err = nullptr;
+    if (!sg.ok(get_wait_err(&err))) return sg.finish(cudaSuccess);
     TcArgs a{};
     a.W = wd;
     a.K = K;
@@ -589,17 +638,21 @@ int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int k
     a.N = N;
     a.M = M;
     a.ksplit = ksplit ? ksplit : tc_pick_split(K, N, sm_count_of_current_device());
-    a.x = xd;
-    a.ldx = K;
     a.y = yd;
     a.ldy = N;
     a.err_flag = err;
-    cudaError_t ce = launch_gemm_tc(a, st, false);
-    int herr = 0;
-    if (ce == cudaSuccess) ce = cudaMemcpyAsync(&herr, err, sizeof(int), cudaMemcpyDeviceToHost, st);
-    const int rc = sg.finish(ce);  // scratch was used, so this synchronises
+    // packed activations live in the per-device scratch (grown on demand, shared by calls on this device)
+    float* xp = nullptr;
+    unsigned int* unused = nullptr;
+    if (!sg.ok(get_scratch((tc_xpack_bytes(M, K) + 3) / 4, 1, &xp, &unused))) return sg.finish(cudaSuccess);
+    a.xp = (const unsigned char*)xp;
+    cudaError_t ce = launch_tc_pack_x(xd, K, M, K, nullptr, 0.f, xp, st, false);
+    if (ce == cudaSuccess) ce = launch_gemm_tc(a, st, false);
+    const bool synced = sg.staged();
+    const int rc = sg.finish(ce);
     if (rc != HM_OK) return rc;
-    if (herr) return gfail(HM_ERR_TIMEOUT, "hm_gemm_bf16_tc: a bounded device-side wait ran out");
+    // with device pointers only the call stays asynchronous; hm_dev_sync reports a wait that ran out
+    if (synced && take_wait_err()) return gfail(HM_ERR_TIMEOUT, "hm_gemm_bf16_tc: a bounded device-side wait ran out");
     return HM_OK;
 }
 
@@ -709,17 +762,15 @@ int hm_attn_decode_paged(const float* q, const void* k_pages, const void* v_page
     if (!is_device_ptr(k_pages) || !is_device_ptr(v_pages)) return gfail(HM_ERR_INVALID, "hm_attn_decode_paged: the page pools must live in device memory");
     cudaStream_t st = (cudaStream_t)stream;
     Staging sg(st);
-    // kv_len is needed on the host to reject empty rows and pick the split count
-    std::vector<int32_t> lens(B);
-    if (is_device_ptr(kv_len)) {
-        if (cudaMemcpy(lens.data(), kv_len, (size_t)B * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return gfail(HM_ERR_CUDA, "cannot read kv_len");
-    } else {
-        std::memcpy(lens.data(), kv_len, (size_t)B * 4);
-    }
-    int longest = 0;
-    for (int b = 0; b < B; ++b) {
-        if (lens[b] < 1 || lens[b] > max_pages * page_tokens) return gfail(HM_ERR_INVALID, "hm_attn_decode_paged: kv_len must be in [1, max_pages*page_tokens]");
-        longest = std::max(longest, lens[b]);
+    // A host kv_len is validated and sizes the split; a device kv_len is trusted (reading it back would
+    // serialise the stream) and the split is sized for max_pages.
+    int longest = max_pages * page_tokens;
+    if (!is_device_ptr(kv_len)) {
+        longest = 0;
+        for (int b = 0; b < B; ++b) {
+            if (kv_len[b] < 1 || kv_len[b] > max_pages * page_tokens) return gfail(HM_ERR_INVALID, "hm_attn_decode_paged: kv_len must be in [1, max_pages*page_tokens]");
+            longest = std::max(longest, kv_len[b]);
+        }
     }
     AttnArgs a{};
     a.q = sg.in(q, (size_t)B * heads * hd);
@@ -780,6 +831,7 @@ int hm_dev_sync(void) {
     NEED_DEVICE();
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return gfail(HM_ERR_CUDA, std::string("cudaDeviceSynchronize: ") + cudaGetErrorString(e));
+    if (take_wait_err()) return gfail(HM_ERR_TIMEOUT, "hm_dev_sync: a bounded device-side wait ran out in an earlier kernel");
     return HM_OK;
 }
 

@@ -1,5 +1,6 @@
 // Engine implementation.  See engine.h.
 #include "engine.h"
+#include "gemm_tc.h"
 
 #include <algorithm>
 #include <cmath>
@@ -83,6 +84,8 @@ int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* 
     const char* nocl = std::getenv("HM_NO_CLUSTER");
     e->use_clusters_ = !(nocl && nocl[0] == '1');
     e->max_cluster_ = gemv_max_cluster();
+    const char* notc = std::getenv("HM_NO_TC");
+    e->use_tc_ = !(notc && notc[0] == '1');
     *out = e;
     return HM_OK;
 }
@@ -98,10 +101,10 @@ Engine::~Engine() {
     fr(embed_); fr(final_norm_); fr(rope_cos_); fr(rope_sin_);
     for (auto& l : layers_) {
         fr(l.in_ln); fr(l.post_ln); fr(l.qkv_bias); fr(l.q_norm); fr(l.k_norm);
-        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->scales); fr(w->codes); }
+        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->tc); fr(w->scales); fr(w->codes); }
     }
-    fr(lm_head_.slabs); fr(lm_head_.scales); fr(lm_head_.codes);
-    fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
+    fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes);
+    fr(xpack_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
@@ -151,6 +154,17 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
             if (ce == cudaSuccess) ce = cudaMemsetAsync(L.slabs, 0, bytes, stream_);
         }
         if (ce == cudaSuccess) ce = launch_pack_slabs_from_nk((const uint16_t*)tmp, n_part, K, L.slabs, n_off, interleave_which, stream_);
+        if (use_tc_ && ce == cudaSuccess) {
+            // second copy for passes over more than 8 rows; gate and up stay un-interleaved here
+            // (rows [0, I) gate, [I, 2I) up) because that path applies SwiGLU in a kernel of its own
+            if (!L.tc) {
+                const size_t bytes = tc_packed_elems(K, N_total) * 2;
+                ce = cudaMalloc(&L.tc, bytes);
+                if (ce == cudaSuccess) ce = cudaMemsetAsync(L.tc, 0, bytes, stream_);
+            }
+            const int tc_off = interleave_which >= 0 ? interleave_which * n_part : n_off;
+            if (ce == cudaSuccess) ce = launch_pack_tc((const uint16_t*)tmp, n_part, K, false, L.tc, tc_off, -1, stream_);
+        }
     } else {
         const int q4 = dtype == HM_Q4_0;
         const size_t nb = K / 32;
@@ -331,6 +345,8 @@ uint64_t Engine::weight_bytes() const {
 // ---- scratch ---------------------------------------------------------------------------------
 
 int Engine::ensure_scratch(int rows) {
+    const bool tall = use_tc_ && !quant_;  // prefill chunks of TC_ROWS rows
+    if (tall) rows = std::max(rows, TC_ROWS);
     const int cap = (rows + MAX_M - 1) / MAX_M * MAX_M;
     if (cap <= scratch_rows_) return HM_OK;
     auto re = [&](auto** p, size_t count) -> cudaError_t {
@@ -348,9 +364,13 @@ int Engine::ensure_scratch(int rows) {
     HM_CUDA(re(&logits_, (size_t)cap * V_));
     HM_CUDA(re(&amax_val_, (size_t)cap * nslabs_v));
     HM_CUDA(re(&amax_idx_, (size_t)cap * nslabs_v));
-    if (quant_) {
+    if (quant_ || tall) {
         HM_CUDA(re(&qkv_raw_, (size_t)cap * (qdim_ + 2 * kvdim_)));
         HM_CUDA(re(&gu_raw_, (size_t)cap * 2 * I_));
+        if (tall) {
+            xpack_bytes_ = tc_xpack_bytes(TC_ROWS, std::max(std::max(H_, qdim_), I_));
+            HM_CUDA(re(&xpack_, xpack_bytes_));
+        }
     }
     // split-K scratch sized for the worst projection at M = 8
     size_t pf = 0;
@@ -661,6 +681,36 @@ void Engine::prof_mark(int) {}
 
 static int pad_m(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 
+// Projection over up to TC_ROWS rows per launch on the tensor cores (gemm_tc.cu): one kernel packs
+// the activations (folding an RMSNorm when norm_w is given), the GEMM applies bias and residual on store.
+int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, float* y, int ldy, const float* bias, const float* resid, int* launches) {
+    if (!L.tc) return fail(HM_ERR_STATE, "tensor-core weight copy missing");
+    for (int m0 = 0; m0 < M; m0 += TC_ROWS) {
+        const int mc = std::min(TC_ROWS, M - m0);
+        if (tc_xpack_bytes(mc, L.K) > xpack_bytes_) return fail(HM_ERR_STATE, "activation pack scratch too small");
+        cudaError_t ce = launch_tc_pack_x(x + (size_t)m0 * ldx, ldx, mc, L.K, norm_w, (float)cfg_.rms_norm_eps, xpack_, stream_, pdl_);
+        if (ce != cudaSuccess) return cuda_fail(ce, "activation pack launch");
+        ++*launches;
+        TcArgs a{};
+        a.W = L.tc;
+        a.K = L.K;
+        a.Kp = tc_padded_k(L.K);
+        a.N = L.N;
+        a.M = mc;
+        a.ksplit = tc_pick_split(L.K, L.N, sm_count_);
+        a.xp = xpack_;
+        a.bias = bias;
+        a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+        a.y = y + (size_t)m0 * ldy;
+        a.ldy = ldy;
+        a.err_flag = err_flag_;
+        ce = launch_gemm_tc(a, stream_, pdl_);
+        if (ce != cudaSuccess) return cuda_fail(ce, "tensor-core projection launch");
+        ++*launches;
+    }
+    return HM_OK;
+}
+
 int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer,
                            const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches) {
     for (int m0 = 0; m0 < M; m0 += MAX_M) {
@@ -748,11 +798,20 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         ++*launches;
     }
     const int QKV = qdim_ + 2 * kvdim_;
+    const float eps = (float)cfg_.rms_norm_eps;
+    // more than 8 rows of a bf16 model: tensor-core projections with the epilogues as kernels of their own
+    const bool tall = use_tc_ && !quant_ && M > MAX_M;
     int rc;
     for (int l = 0; l < L_; ++l) {
         const LayerW& w = layers_[l];
         KvDesc kv{k_pool_[l], v_pool_[l], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
         if (!want(PC_QKV)) {
+        } else if (tall) {
+            rc = enqueue_linear_tc(w.qkv, M, h_, H_, w.in_ln, qkv_raw_, QKV, w.qkv_bias, nullptr, launches);
+            if (rc) return rc;
+            ce = launch_post_qkv(qkv_raw_, M, heads_, kvh_, hd_, cfg_.has_qk_norm, w.q_norm, w.k_norm, eps, rope_cos_, rope_sin_, row_pos, row_seq, kv, q_, stream_, pdl_);
+            if (ce != cudaSuccess) return cuda_fail(ce, "post_qkv");
+            ++*launches;
         } else if (w.qkv.kind == HM_BF16) {
             rc = enqueue_linear(w.qkv, M, h_, H_, PRO_RMSNORM, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
@@ -788,11 +847,20 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             if (ce != cudaSuccess) return cuda_fail(ce, "attention launch");
             ++*launches;
         }
-        if (want(PC_O)) {
+        if (want(PC_O) && tall) {
+            rc = enqueue_linear_tc(w.o, M, attn_, qdim_, nullptr, h_, H_, nullptr, h_, launches);
+            if (rc) return rc;
+        } else if (want(PC_O)) {
             rc = enqueue_linear(w.o, M, attn_, qdim_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
         }
         if (!want(PC_GATE_UP)) {
+        } else if (tall) {
+            rc = enqueue_linear_tc(w.gu, M, h_, H_, w.post_ln, gu_raw_, 2 * I_, nullptr, nullptr, launches);
+            if (rc) return rc;
+            ce = launch_silu_mul(gu_raw_, M, I_, act_, stream_, pdl_);
+            if (ce != cudaSuccess) return cuda_fail(ce, "silu_mul");
+            ++*launches;
         } else if (w.gu.kind == HM_BF16) {
             rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
@@ -803,7 +871,10 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             if (ce != cudaSuccess) return cuda_fail(ce, "silu_mul");
             ++*launches;
         }
-        if (want(PC_DOWN)) {
+        if (want(PC_DOWN) && tall) {
+            rc = enqueue_linear_tc(w.down, M, act_, I_, nullptr, h_, H_, nullptr, h_, launches);
+            if (rc) return rc;
+        } else if (want(PC_DOWN)) {
             rc = enqueue_linear(w.down, M, act_, I_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
         }
@@ -811,8 +882,12 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
     if (lm_rows > 0) {
         const int nslabs = (V_ + SLAB - 1) / SLAB;
         const float* x = h_ + (size_t)lm_row0 * H_;
-        const bool slab_argmax = lm_head_.kind == HM_BF16;
-        if (want(PC_LM_HEAD)) {
+        const bool lm_tall = use_tc_ && lm_head_.kind == HM_BF16 && lm_head_.tc && lm_rows > MAX_M;
+        const bool slab_argmax = lm_head_.kind == HM_BF16 && !lm_tall;
+        if (want(PC_LM_HEAD) && lm_tall) {
+            rc = enqueue_linear_tc(lm_head_, lm_rows, x, H_, final_norm_, logits_, V_, nullptr, nullptr, launches);
+            if (rc) return rc;
+        } else if (want(PC_LM_HEAD)) {
             rc = slab_argmax ? enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches)
                              : enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_STORE, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, nullptr, nullptr, launches);
             if (rc) return rc;
@@ -871,6 +946,7 @@ int Engine::check_device_error() {
     HM_CUDA(cudaMemcpy(&flag, err_flag_, 4, cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(err_flag_, 0, 4);
+        if (flag == 2) return fail(HM_ERR_TIMEOUT, "a bounded device-side wait ran out (tensor-core projection)");
         return fail(HM_ERR_INVALID, "token id out of range (>= vocab_size)");
     }
     return HM_OK;
@@ -900,8 +976,9 @@ int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t*
     st[3 * n] = (uint32_t)(len0 + n - 1);
     HM_CUDA(cudaMemcpyAsync(pos_dev_ + seq, st + 3 * n, 4, cudaMemcpyHostToDevice, stream_));
     int launches = 0;
-    for (int c0 = 0; c0 < n; c0 += MAX_M) {
-        const int mc = std::min(MAX_M, n - c0);
+    const int chunk = (use_tc_ && !quant_) ? TC_ROWS : MAX_M;
+    for (int c0 = 0; c0 < n; c0 += chunk) {
+        const int mc = std::min(chunk, n - c0);
         const bool last = c0 + mc >= n;
         int rc = enqueue_pass(mc, pf_tokens_ + c0, pf_pos_ + c0, pf_seq_ + c0, mc - 1, last ? 1 : 0, false, next_dev_ + seq, tokens_dev_ + seq, pos_dev_ + seq, hist_dev_ + (size_t)seq * (max_seq_ + 1),
                               &launches);

@@ -20,6 +20,7 @@ struct LinearW {
     int K = 0, N = 0;        // N = output count of the (possibly fused) projection
     int kind = -1;           // HM_BF16 (slab layout) | HM_Q8_0 | HM_Q4_0 (split scales + codes)
     uint16_t* slabs = nullptr;
+    uint16_t* tc = nullptr;  // second copy in the tensor-core tile layout (gemm_tc.h), used for passes over more than 8 rows
     uint16_t* scales = nullptr;
     uint8_t* codes = nullptr;
     int loaded_parts = 0;
@@ -75,6 +76,7 @@ class Engine {
     // sequence).  lm_row0/lm_rows select the rows that go through the LM head.
     int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);
     int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches);
+    int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, float* y, int ldy, const float* bias, const float* resid, int* launches);
     int capture_decode_graph();
     int setup_persistent();   // batch-1 bf16 models: one cooperative launch per decode step
     int launch_step();        // replay the captured graph, or launch the persistent kernel directly
@@ -88,6 +90,7 @@ class Engine {
     bool finalized_ = false, quant_ = false, pdl_ = true;
     bool use_clusters_ = true;  // split reductions through thread-block clusters / DSMEM (HM_NO_CLUSTER=1: global scratch + tickets)
     int max_cluster_ = 8;
+    bool use_tc_ = true;  // bf16 models: passes over more than 8 rows run the tcgen05 GEMM (HM_NO_TC=1: 8-row groups of the streaming kernel)
     cudaStream_t stream_ = nullptr;
 
     // weights
@@ -101,6 +104,8 @@ class Engine {
     // activations / scratch for up to scratch_rows_ rows
     int scratch_rows_ = 0;
     float *h_ = nullptr, *q_ = nullptr, *attn_ = nullptr, *act_ = nullptr, *qkv_raw_ = nullptr, *gu_raw_ = nullptr, *logits_ = nullptr;
+    unsigned char* xpack_ = nullptr;  // packed activations of one tensor-core projection (gemm_tc.h)
+    size_t xpack_bytes_ = 0;
     float* amax_val_ = nullptr;
     int32_t* amax_idx_ = nullptr;
     float* partial_ = nullptr;

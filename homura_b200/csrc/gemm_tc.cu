@@ -34,10 +34,8 @@ constexpr int BK = 64;   // k per stage (128 B of bf16)
 constexpr int MR = 64;   // activation rows (MMA N = MR * terms)
 constexpr int TERMS = 3;
 constexpr int W_TILE = BM * BK * 2;          // 16 KB
-constexpr int X_TILE = MR * TERMS * BK * 2;  // 24 KB
-constexpr int NSTG = 4;
-constexpr unsigned long long TC_SPIN = 20000000ULL;
-constexpr int TMEM_COLS = 256;
+constexpr int NSTG = 8;  // barrier slots; stages in use depend on the row padding
+constexpr unsigned long long TC_SPIN = 4000000ULL;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n) : "memory"); }
@@ -93,18 +91,79 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 
 struct TcShared {
-    uint64_t w_full[NSTG], x_full[NSTG], empty[NSTG], acc_full;
+    uint64_t full[NSTG], empty[NSTG], acc_full;
     uint32_t tmem_base;
     volatile int abort_flag;
 };
 
+// ---- activation packing: f32 rows -> three bf16 terms in the shared-memory image of the B tiles ----
+// out: [k-block][term][mpad][64] bf16, rows of 128 B, 16-byte chunks XOR-swizzled by (row & 7) where
+// row = term * mpad + m.  One block per padded row; an RMSNorm is folded in when norm_w is given
+// (x' = (x * inv_rms) * w, src/graph_builder/emit_linalg.rs:7-26).
+__global__ void __launch_bounds__(256) tc_pack_x_kernel(const float* __restrict__ x, int ldx, int M, int mpad, int K, int Kp, const float* __restrict__ norm_w, float eps, unsigned char* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const bool row_ok = m < M;
+    const float* xr = x + (size_t)m * ldx;
+    __shared__ float sw[8];
+    __shared__ float s_inv;
+    float inv = 1.0f;
+    if (norm_w) {
+        float s = 0.f;
+        if (row_ok)
+            for (int i = tid; i < K; i += 256) s = fmaf(xr[i], xr[i], s);
+        s = warp_sum(s);
+        if ((tid & 31) == 0) sw[tid >> 5] = s;
+        __syncthreads();
+        if (tid == 0) {
+            float t = 0.f;
+            for (int i = 0; i < 8; ++i) t += sw[i];
+            s_inv = 1.0f / sqrtf(t / (float)K + eps);
+        }
+        __syncthreads();
+        inv = s_inv;
+    }
+    const size_t tile_bytes = (size_t)TERMS * mpad * 128;
+    for (int c = tid; c < Kp / 8; c += 256) {  // one 16-byte chunk (8 k) per term per iteration
+        const int k0 = c * 8, kb = k0 / BK, chunk = (k0 % BK) >> 3;
+        uint32_t term[TERMS][4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            uint16_t h[2], md[2], l[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int k = k0 + 2 * e + u;
+                float v = (row_ok && k < K) ? xr[k] : 0.f;
+                if (norm_w && k < K) v = (v * inv) * __ldg(norm_w + k);
+                h[u] = f32_to_bf16_rne(v);
+                const float r1 = v - bf16_bits_to_f32(h[u]);
+                md[u] = f32_to_bf16_rne(r1);
+                l[u] = f32_to_bf16_rne(r1 - bf16_bits_to_f32(md[u]));
+            }
+            term[0][e] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+            term[1][e] = (uint32_t)md[0] | ((uint32_t)md[1] << 16);
+            term[2][e] = (uint32_t)l[0] | ((uint32_t)l[1] << 16);
+        }
+#pragma unroll
+        for (int t = 0; t < TERMS; ++t) {
+            const int row = t * mpad + m;
+            const size_t off = (size_t)kb * tile_bytes + (size_t)row * 128 + (size_t)((chunk ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(out + off) = make_uint4(term[t][0], term[t][1], term[t][2], term[t][3]);
+        }
+    }
+}
+
+// ---- the GEMM: warp 0 = bulk-copy producer, warp 1 = TMEM owner + MMA issuer, warps 2-5 = epilogue ----
 template <bool CL>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) {
     extern __shared__ __align__(1024) unsigned char dsm[];
     __shared__ TcShared sh;
-    // dynamic smem: [NSTG][W tile | X tile], then the f32 tile [MR][BM] for the epilogue
     unsigned char* stage0 = dsm + ((1024u - (s32(dsm) & 1023u)) & 1023u);  // swizzle atoms need 1024-byte alignment
-    float* out_tile = reinterpret_cast<float*>(stage0 + (size_t)NSTG * (W_TILE + X_TILE));
+    const int mpad = a.mpad;
+    const uint32_t x_tile = (uint32_t)(TERMS * mpad * 128);
+    const uint32_t stage_bytes = W_TILE + x_tile;  // multiple of 1024 for mpad in {16, 32, 64}
+    float* out_tile = reinterpret_cast<float*>(stage0 + (size_t)a.nstage * stage_bytes);  // [mpad][BM] f32
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cs = CL ? a.ksplit : 1;
@@ -114,11 +173,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     const int kb_per = (kb_total + cs - 1) / cs;
     const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
     const int nkb = max(0, kb1 - kb0);
+    const int nst = a.nstage;
 
     if (tid == 0) {
-        for (int s = 0; s < NSTG; ++s) {
-            mb_init(&sh.w_full[s], 1);
-            mb_init(&sh.x_full[s], 128);
+        for (int s = 0; s < nst; ++s) {
+            mb_init(&sh.full[s], 1);
             mb_init(&sh.empty[s], 1);
         }
         mb_init(&sh.acc_full, 1);
@@ -126,8 +185,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 1) {  // TMEM: 256 columns, allocated and later freed by this warp
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh.tmem_base)), "r"(TMEM_COLS) : "memory");
+    if (warp == 1) {  // TMEM: allocated and later freed by this warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh.tmem_base)), "r"(a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -138,28 +197,36 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     pdl_launch_dependents();
 
     if (warp == 0) {
-        // ---- producer: one 16 KB bulk copy per k-block (weights never depend on a previous kernel)
         if (lane == 0) {
             const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(a.W) + ((size_t)nblk * kb_total + kb0) * W_TILE;
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % NSTG;
-                const uint32_t par = ((i / NSTG) & 1u) ^ 1u;
+            const unsigned char* xsrc = a.xp + (size_t)kb0 * x_tile;
+            // weights never depend on the previous kernel: fill the ring with them first, then wait for
+            // the packed activations
+            const int pre = min(nkb, nst);
+            for (int i = 0; i < pre; ++i) {
+                mb_expect_tx(&sh.full[i], stage_bytes);
+                bulk_copy(stage0 + (size_t)i * stage_bytes, wsrc + (size_t)i * W_TILE, W_TILE, &sh.full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) bulk_copy(stage0 + (size_t)i * stage_bytes + W_TILE, xsrc + (size_t)i * x_tile, x_tile, &sh.full[i]);
+            for (int i = pre; i < nkb; ++i) {
+                const int s = i % nst;
+                const uint32_t par = ((i / nst) & 1u) ^ 1u;
                 if (!mb_wait(&sh.empty[s], par, a.err_flag, &sh.abort_flag)) break;
-                mb_expect_tx(&sh.w_full[s], W_TILE);
-                bulk_copy(stage0 + (size_t)s * (W_TILE + X_TILE), wsrc + (size_t)i * W_TILE, W_TILE, &sh.w_full[s]);
+                mb_expect_tx(&sh.full[s], stage_bytes);
+                bulk_copy(stage0 + (size_t)s * stage_bytes, wsrc + (size_t)i * W_TILE, W_TILE, &sh.full[s]);
+                bulk_copy(stage0 + (size_t)s * stage_bytes + W_TILE, xsrc + (size_t)i * x_tile, x_tile, &sh.full[s]);
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(MR * TERMS);
+            const uint32_t idesc = umma_idesc(TERMS * mpad);
             for (int i = 0; i < nkb; ++i) {
-                const int s = i % NSTG;
-                const uint32_t par = (i / NSTG) & 1u;
-                const bool ok = mb_wait(&sh.w_full[s], par, a.err_flag, &sh.abort_flag) && mb_wait(&sh.x_full[s], par, a.err_flag, &sh.abort_flag);
-                if (!ok) break;
+                const int s = i % nst;
+                const uint32_t par = (i / nst) & 1u;
+                if (!mb_wait(&sh.full[s], par, a.err_flag, &sh.abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t wa = s32(stage0 + (size_t)s * (W_TILE + X_TILE));
+                const uint32_t wa = s32(stage0 + (size_t)s * stage_bytes);
                 const uint32_t xa = wa + W_TILE;
 #pragma unroll
                 for (int ks = 0; ks < BK / 16; ++ks)
@@ -169,76 +236,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
             umma_commit(&sh.acc_full);
         }
     } else {
-        // ---- warps 2..5: stage activations, then epilogue
-        const int st = tid - 64;  // 0..127
-        pdl_wait();
-        for (int i = 0; i < nkb; ++i) {
-            const int s = i % NSTG;
-            const uint32_t par = ((i / NSTG) & 1u) ^ 1u;
-            if (!mb_wait(&sh.empty[s], par, a.err_flag, &sh.abort_flag)) break;
-            unsigned char* xt = stage0 + (size_t)s * (W_TILE + X_TILE) + W_TILE;
-            const int k0 = (kb0 + i) * BK;
-            // thread -> (row m = st / 2, 32 k's): 4 x (8 elements = one 16-byte chunk per term)
-            const int m = st >> 1, kh = (st & 1) * 32;
-            const bool row_ok = m < a.M;
-            const float scale = (row_ok && a.row_scale) ? a.row_scale[m] : 1.0f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int kk = kh + c * 8;  // k within the block
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int k = k0 + kk + e;
-                    float x = (row_ok && k < a.K) ? a.x[(size_t)m * a.ldx + k] : 0.f;
-                    if (a.col_scale && k < a.K) x = (x * scale) * __ldg(a.col_scale + k);
-                    v[e] = x;
-                }
-                uint32_t hi[4], mid[4], lo[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    uint16_t h0, h1, m0, m1, l0, l1;
-                    {
-                        const float x = v[2 * e];
-                        h0 = f32_to_bf16_rne(x);
-                        const float r1 = x - bf16_bits_to_f32(h0);
-                        m0 = f32_to_bf16_rne(r1);
-                        l0 = f32_to_bf16_rne(r1 - bf16_bits_to_f32(m0));
-                    }
-                    {
-                        const float x = v[2 * e + 1];
-                        h1 = f32_to_bf16_rne(x);
-                        const float r1 = x - bf16_bits_to_f32(h1);
-                        m1 = f32_to_bf16_rne(r1);
-                        l1 = f32_to_bf16_rne(r1 - bf16_bits_to_f32(m1));
-                    }
-                    hi[e] = (uint32_t)h0 | ((uint32_t)h1 << 16);
-                    mid[e] = (uint32_t)m0 | ((uint32_t)m1 << 16);
-                    lo[e] = (uint32_t)l0 | ((uint32_t)l1 << 16);
-                }
-                const int chunk = kk >> 3;
-#pragma unroll
-                for (int t = 0; t < TERMS; ++t) {
-                    const int row = t * MR + m;  // row of the B tile (MMA N index)
-                    const uint32_t off = (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
-                    const uint32_t* src = t == 0 ? hi : (t == 1 ? mid : lo);
-                    *reinterpret_cast<uint4*>(xt + off) = make_uint4(src[0], src[1], src[2], src[3]);
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
-            mb_arrive(&sh.x_full[s]);
-        }
-        // ---- accumulator -> registers -> f32 tile in shared memory [m][128]
+        // ---- accumulator -> registers (three terms summed) -> f32 tile in shared memory [m][128]
         const bool acc_ok = __all_sync(0xffffffffu, mb_wait(&sh.acc_full, 0, a.err_flag, &sh.abort_flag));
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int lane_base = (warp & 3) * 32;  // a warp may only touch its own quarter of the TMEM lanes
         const int n_local = lane_base + lane;   // output feature within the CTA's 128
         if (acc_ok && nkb > 0) {
-#pragma unroll
-            for (int c0 = 0; c0 < MR; c0 += 16) {
+            for (int c0 = 0; c0 < mpad; c0 += 16) {
                 uint32_t r[TERMS][16];
 #pragma unroll
                 for (int t = 0; t < TERMS; ++t) {
-                    const uint32_t taddr = tmem + ((uint32_t)lane_base << 16) + (uint32_t)(t * MR + c0);
+                    const uint32_t taddr = tmem + ((uint32_t)lane_base << 16) + (uint32_t)(t * mpad + c0);
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                         : "=r"(r[t][0]), "=r"(r[t][1]), "=r"(r[t][2]), "=r"(r[t][3]), "=r"(r[t][4]), "=r"(r[t][5]), "=r"(r[t][6]), "=r"(r[t][7]), "=r"(r[t][8]), "=r"(r[t][9]),
@@ -254,12 +262,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
                 }
             }
         } else {
-            for (int mm = 0; mm < MR; ++mm) out_tile[mm * BM + n_local] = 0.f;
+            for (int mm = 0; mm < mpad; ++mm) out_tile[mm * BM + n_local] = 0.f;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
 
     // ---- epilogue; with split-K the accumulators are first reduce-scattered by activation row
     //      through distributed shared memory (each CTA sums, in rank order, its share of the rows)
@@ -292,9 +300,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 
 }  // namespace
 
-size_t tc_smem_bytes() { return (size_t)NSTG * (W_TILE + X_TILE) + (size_t)MR * BM * 4 + 1024; }
+static int tc_mpad(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+static int tc_nstage(int mpad) { return mpad == 64 ? 4 : 6; }
+static size_t tc_smem_for(int mpad) { return (size_t)tc_nstage(mpad) * (W_TILE + (size_t)TERMS * mpad * 128) + (size_t)mpad * BM * 4 + 1024; }
 size_t tc_packed_elems(int K, int N) { return (size_t)((N + BM - 1) / BM) * ((K + BK - 1) / BK) * BM * BK; }
 int tc_padded_k(int K) { return (K + BK - 1) / BK * BK; }
+size_t tc_xpack_bytes(int M, int K) { return (size_t)(tc_padded_k(K) / BK) * TERMS * tc_mpad(M) * 128; }
 int tc_pick_split(int K, int N, int sm_count) {
     const int nblk = (N + BM - 1) / BM, kb = (K + BK - 1) / BK;
     int s = sm_count / nblk;  // CTAs per n-block that still fit one wave (1 CTA per SM)
@@ -303,14 +314,37 @@ int tc_pick_split(int K, int N, int sm_count) {
     return s < 1 ? 1 : s;
 }
 
-cudaError_t launch_gemm_tc(const TcArgs& a, cudaStream_t st, bool pdl) {
-    if (a.M < 1 || a.M > MR || a.Kp % BK != 0) return cudaErrorInvalidValue;
+cudaError_t launch_tc_pack_x(const float* x, int ldx, int M, int K, const float* norm_w, float eps, void* xp, cudaStream_t st, bool pdl) {
+    if (M < 1 || M > MR) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tc_mpad(M));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, tc_pack_x_kernel, x, ldx, M, tc_mpad(M), K, tc_padded_k(K), norm_w, eps, (unsigned char*)xp);
+}
+
+cudaError_t launch_gemm_tc(const TcArgs& a_in, cudaStream_t st, bool pdl) {
+    TcArgs a = a_in;
+    if (a.M < 1 || a.M > MR || a.Kp % BK != 0 || !a.xp) return cudaErrorInvalidValue;
+    a.mpad = tc_mpad(a.M);
+    a.nstage = tc_nstage(a.mpad);
+    a.tmem_cols = a.mpad == 16 ? 64 : a.mpad == 32 ? 128 : 256;  // power of two >= 3 * mpad
     const int nblk = (a.N + BM - 1) / BM;
     const bool cl = a.ksplit > 1;
-    const size_t smem = tc_smem_bytes();
-    cudaError_t e = cl ? cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                       : cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    const size_t smem = tc_smem_for(a.mpad);
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[cl ? 1 : 0]) {
+        const size_t mx = tc_smem_for(64) > tc_smem_for(32) ? tc_smem_for(64) : tc_smem_for(32);
+        cudaError_t e = cl ? cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mx)
+                           : cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mx);
+        if (e != cudaSuccess) return e;
+        attr_set[cl ? 1 : 0] = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(nblk * (cl ? a.ksplit : 1)));
     cfg.blockDim = dim3(TC_THREADS);

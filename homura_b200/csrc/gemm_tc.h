@@ -5,15 +5,15 @@
 
 namespace hm {
 
+constexpr int TC_ROWS = 64;  // activation rows one launch covers
+
 struct TcArgs {
     const uint16_t* W;  // swizzled K-major tiles [n-block][k-block][128][64] bf16 (launch_pack_tc)
     int K, Kp, N;       // contraction length, K rounded up to 64, output features
     int M;              // activation rows, 1..64
     int ksplit;         // CTAs per cluster sharing one n-block (1 = no split, at most 8)
-    const float* x;     // [M][ldx] f32
-    int ldx;
-    const float* row_scale;  // optional [M]: 1/rms of each row  } x' = (x * row_scale[m]) * col_scale[k]
-    const float* col_scale;  // optional [K]: RMSNorm weight     }
+    const unsigned char* xp;  // activations packed by launch_tc_pack_x (tc_xpack_bytes(M, K) bytes)
+    int mpad, nstage, tmem_cols;  // filled in by launch_gemm_tc
     const float* bias;       // optional [N]
     const float* resid;      // optional [M][ldy], added as resid + y
     float* y;                // [M][ldy]
@@ -21,10 +21,13 @@ struct TcArgs {
     int* err_flag;  // set to 2 when a bounded wait ran out
 };
 
-size_t tc_smem_bytes();
+size_t tc_xpack_bytes(int M, int K);  // bytes of the packed activations of M rows
 size_t tc_packed_elems(int K, int N);  // bf16 elements of the packed weight (both dims padded)
 int tc_padded_k(int K);
 int tc_pick_split(int K, int N, int sm_count);  // cluster size that fills the SMs once
+// f32 rows -> three bf16 terms per element in the tile layout the GEMM copies in bulk; folds an
+// RMSNorm (weight norm_w, epsilon eps) when norm_w is not NULL.
+cudaError_t launch_tc_pack_x(const float* x, int ldx, int M, int K, const float* norm_w, float eps, void* xp, cudaStream_t st, bool pdl);
 cudaError_t launch_gemm_tc(const TcArgs& a, cudaStream_t st, bool pdl);
 // src is [N][K] (src_is_kn = false) or [K][N]; rows land at n_off + n, or interleaved 64/64 per
 // 128-row block when interleave_which is 0 (gate) or 1 (up).

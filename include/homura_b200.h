@@ -221,7 +221,9 @@ HM_API int hm_qknorm_rope(float* x, int rows, int heads, int hd, const float* no
 /* GQA decode attention over a paged cache (src/hf/emitter.rs:683-737, floordiv head map of
  * src/graph_builder/emit_linalg.rs:93-245): q [B, heads, hd] f32; k_pages / v_pages
  * [n_pages, kv_heads, page_tokens, hd] of kv_dtype; page_table [B, max_pages] int32;
- * kv_len [B] int32; out [B, heads*hd] f32. */
+ * kv_len [B] int32; out [B, heads*hd] f32.  A host kv_len is range-checked; a kv_len in device
+ * memory is trusted (entries must lie in [1, max_pages*page_tokens]) and the call stays asynchronous
+ * when every pointer is a device pointer. */
 HM_API int hm_attn_decode_paged(const float* q, const void* k_pages, const void* v_pages, int kv_dtype, const int32_t* page_table, const int32_t* kv_len, int B, int heads, int kv_heads, int hd, int page_tokens, int max_pages, float* out, void* stream);
 /* argmax with ties to the highest index (src/generate.rs:457-468): logits [rows, n]. */
 HM_API int hm_argmax(const float* logits, int rows, int n, uint32_t* out, void* stream);

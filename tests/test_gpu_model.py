@@ -344,3 +344,81 @@ def test_persistent_decode_kernel_matches_oracle(hm, oracle, monkeypatch):
         lg, _ = m.decode_step([cur])
         assert_logits_close(lg[0], lo, scale_tol=False)
         cur = oracle.argmax(lo)
+
+
+# ---- passes over more than 8 rows: the tensor-core projections ---------------------------------
+
+
+@pytest.mark.parametrize("name", list(HF_CASES))
+def test_long_prefill_on_tensor_cores_matches_oracle(hm, oracle, name):
+    # 150 tokens = two full 64-row chunks and a ragged one; every chunk runs the tcgen05 projections
+    cfg, d = make_hf(name, max_position_embeddings=256)
+    om = oracle.OracleModel.from_hf_dir(d, max_seq_len=192)
+    m = hm.HfModel.load(d)
+    m.init_kv_cache(192)
+    ids = synth.prompt_ids(13, 150, cfg.vocab_size)
+    tok_o, lg_o = om.prefill(ids)
+    tok_g, lg_g = m.prefill(ids, want_logits=True)
+    assert_logits_close(lg_g, lg_o)
+    assert float(np.abs(lg_g - lg_o).max()) < 2e-4
+    assert tok_g == tok_o and m.kv_cache_len() == 150
+    for layer in range(cfg.num_hidden_layers):
+        gk, gv = m.kv_view(layer)
+        ok, ov = om.kv_view(layer)
+        np.testing.assert_allclose(gk[0], ok, atol=5e-5)
+        np.testing.assert_allclose(gv[0], ov, atol=5e-5)
+    # decode continues from the tensor-core prefill exactly as from the oracle's
+    cur = tok_o
+    for _ in range(8):
+        lo = om.decode_step(cur)
+        lgd, nxt = m.decode_step([cur])
+        assert_logits_close(lgd[0], lo)
+        cur = oracle.argmax(lo)
+        assert int(nxt[0]) == cur
+
+
+def test_prefill_paths_agree(hm, oracle, monkeypatch):
+    # the 8-row streaming path (HM_NO_TC=1) and the tensor-core path give the same first token and logits
+    cfg, d = make_hf("qwen2", max_position_embeddings=256)
+    ids = synth.prompt_ids(17, 100, cfg.vocab_size)
+    m = hm.HfModel.load(d)
+    m.init_kv_cache(128)
+    tok_tc, lg_tc = m.prefill(ids, want_logits=True)
+    m.close()
+    monkeypatch.setenv("HM_NO_TC", "1")
+    m2 = hm.HfModel.load(d)
+    m2.init_kv_cache(128)
+    tok_st, lg_st = m2.prefill(ids, want_logits=True)
+    assert tok_tc == tok_st
+    assert float(np.abs(lg_tc - lg_st).max()) < 2e-4
+
+
+def test_batch_20_decode_on_tensor_cores(hm, oracle):
+    # more than 8 sequences per step: projections and the LM head run on the tensor cores
+    cfg, d = make_hf("qwen2")
+    B = 20
+    m = hm.HfModel.load(d)
+    m.init_kv_cache(48, batch=B)
+    oms = [oracle.OracleModel.from_hf_dir(d, max_seq_len=48) for _ in range(B)]
+    cur = []
+    for b in range(B):
+        ids = synth.prompt_ids(40 + b, 3 + (b % 7), cfg.vocab_size)
+        t_o, _ = oms[b].prefill(ids)
+        assert m.prefill(ids, seq=b) == t_o
+        cur.append(t_o)
+    for _ in range(6):
+        lg, nxt = m.decode_step(cur)
+        for b in range(B):
+            lo = oms[b].decode_step(cur[b])
+            assert_logits_close(lg[b], lo)
+            cur[b] = oracle.argmax(lo)
+            assert int(nxt[b]) == cur[b]
+    # the on-device greedy loop agrees with per-step decoding
+    out = m.decode_greedy_n(cur, 5)
+    for b in range(B):
+        want = []
+        t = cur[b]
+        for _ in range(5):
+            t = oracle.argmax(oms[b].decode_step(t))
+            want.append(t)
+        assert [int(v) for v in out[b]] == want
