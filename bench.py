@@ -48,20 +48,37 @@ def log(*a):
     print(*a, file=sys.stderr, flush=True)
 
 
-def model_dir(cfg, seed, rank, world):
-    """Rank 0 writes the seeded checkpoint once; the other ranks wait for the marker file."""
+# name -> (config attribute in homura_b200.synth, checkpoint format, sequences per GPU, description)
+WORKLOADS = {
+    "qwen25-05b": ("QWEN25_05B", "bf16", 1, "Qwen2.5-0.5B-architecture decoder (24 layers, hidden 896, 14/2 heads, hd 64, SwiGLU 4864, vocab 151936, tied, QKV bias), batch 1 per GPU"),
+    "tinyllama-q8_0": ("TINYLLAMA_11B", "q8_0", 1, "TinyLlama-1.1B-architecture decoder (22 layers, hidden 2048, 32/4 heads, hd 64, SwiGLU 5632, vocab 32000), GGUF Q8_0, batch 1 per GPU"),
+    "tinyllama-q4_0": ("TINYLLAMA_11B", "q4_0", 1, "TinyLlama-1.1B-architecture decoder (22 layers, hidden 2048, 32/4 heads, hd 64, SwiGLU 5632, vocab 32000), GGUF Q4_0, batch 1 per GPU"),
+    "qwen25-15b-x64": ("QWEN25_15B", "bf16", 64, "Qwen2.5-1.5B-architecture decoder (28 layers, hidden 1536, 12/2 heads, hd 128, SwiGLU 8960, vocab 151936, tied, QKV bias), 64 sequences per GPU"),
+}
+HEADLINE = "qwen25-05b"
+
+
+def model_dir(cfg, seed, rank, world, name=HEADLINE, fmt="bf16"):
+    """Rank 0 writes the seeded checkpoint once; the other ranks wait for the marker file.
+    Returns a directory (config.json + safetensors) or, for the GGUF formats, the file's path."""
     from homura_b200 import synth
 
-    d = os.path.join(tempfile.gettempdir(), f"homura_b200_bench_qwen25_05b_seed{seed}")
+    tag = "qwen25_05b" if name == HEADLINE else name.replace("-", "_")
+    d = os.path.join(tempfile.gettempdir(), f"homura_b200_bench_{tag}_seed{seed}")
     marker = os.path.join(d, ".complete")
+    gguf = os.path.join(d, "model.gguf")
     if rank == 0 and not os.path.exists(marker):
         t = time.time()
-        synth.write_hf_model(d, cfg, seed)
+        if fmt == "bf16":
+            synth.write_hf_model(d, cfg, seed)
+        else:
+            os.makedirs(d, exist_ok=True)
+            synth.write_gguf_model(gguf, cfg, seed, synth.GGML_Q8_0 if fmt == "q8_0" else synth.GGML_Q4_0)
         open(marker, "w").write("ok")
         log(f"[bench] wrote synthetic checkpoint to {d} in {time.time() - t:.1f}s")
     while not os.path.exists(marker):
         time.sleep(0.5)
-    return d
+    return d if fmt == "bf16" else gguf
 
 
 def measured_peak():
@@ -123,11 +140,12 @@ def dist_setup(n_gpus):
 
 
 def cpu_sample(d, cfg, steps, warmup, prompt_len):
-    """Decode tokens/s of the CPU oracle on the same checkpoint (all host threads)."""
+    """Decode tokens/s of the CPU oracle on the same checkpoint (all host threads, one sequence)."""
     import oracle as orc
     from homura_b200 import synth
 
-    om = orc.OracleModel.from_hf_dir(d, max_seq_len=prompt_len + warmup + steps + 1)
+    n = prompt_len + warmup + steps + 1
+    om = orc.OracleModel.from_hf_dir(d, max_seq_len=n) if os.path.isdir(d) else orc.OracleModel.from_gguf(d, max_seq_len=n)
     ids = synth.prompt_ids(SEED, prompt_len, cfg.vocab_size)
     tok, _ = om.prefill(ids)
     for _ in range(warmup):
@@ -171,6 +189,7 @@ def main():
     ap.add_argument("--kv-dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode steps (128 = the headline workload)")
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="default: the headline workload; the others are the remaining measured configurations")
     ap.add_argument("--device-only", action="store_true", help="only the device-timed region: skips the end-to-end loop, the per-kernel pass and the CPU baseline (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -181,32 +200,34 @@ def main():
 
     rank, world, local, barrier, vmax = dist_setup(args.gpus)
     K, W = args.steps, max(args.warmup, 3)
-    cfg = synth.QWEN25_05B
-    d = model_dir(cfg, SEED, rank, world)
+    cfg_name, fmt, B, wl_desc = WORKLOADS[args.workload]
+    cfg = getattr(synth, cfg_name)
+    d = model_dir(cfg, SEED, rank, world, args.workload, fmt)
     barrier()
 
     t0 = time.time()
-    m = hm.HfModel.load_with_dtype(d, hm.DType.BF16, device=local)
+    m = hm.HfModel.load_with_dtype(d, hm.DType.BF16, device=local) if fmt == "bf16" else hm.HfModel.load_gguf(d, device=local)
     kv_dtype = hm.DType.F32 if args.kv_dtype == "f32" else hm.DType.BF16
     PL = args.prompt_len
     max_seq = PL + 2 * (W + K) + 24
     if max_seq > cfg.max_position_embeddings:
         raise SystemExit(f"--steps/--warmup need {max_seq} positions; the checkpoint has {cfg.max_position_embeddings}")
-    m.init_kv_cache(max_seq, batch=1, kv_dtype=kv_dtype)
+    m.init_kv_cache(max_seq, batch=B, kv_dtype=kv_dtype)
     if rank == 0:
         log(f"[bench] engine ready in {time.time() - t0:.1f}s; {m.launches_per_step()} launches/step; weight bytes/step {m.weight_bytes()}")
-    ids = synth.prompt_ids(SEED + rank, PL, cfg.vocab_size)  # each rank decodes its own sequence
+    # every sequence of every rank decodes its own prompt
+    prompts = [synth.prompt_ids(SEED + rank * B + b, PL, cfg.vocab_size) for b in range(B)]
 
     # ---- device-timed region: K steps, inputs resident, token fed back on the device ----
-    first = m.prefill(ids)
-    m.decode_greedy_n([first], 0)
+    first = [m.prefill(prompts[b], seq=b) for b in range(B)]
+    m.decode_greedy_n(first, 0)
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
     ms = m.time_decode(W, K)
     barrier()
     clocks = sampler.stop() if sampler else None
     ms_max = vmax(ms)
-    tok_per_s = world * K / (ms_max / 1e3)
+    tok_per_s = world * B * K / (ms_max / 1e3)
 
     if args.device_only:
         if rank == 0:
@@ -215,19 +236,20 @@ def main():
         return
 
     # ---- end to end through the per-token C-ABI call (host token in, host token out) ----
-    m.reset_kv_cache()
-    cur = m.prefill(ids)
+    for b in range(B):
+        m.reset_kv_cache(seq=b)
+    cur = [m.prefill(prompts[b], seq=b) for b in range(B)]
     for _ in range(W):
-        _, nxt = m.decode_step([cur], want_logits=False)
-        cur = int(nxt[0])
+        _, nxt = m.decode_step(cur, want_logits=False)
+        cur = [int(v) for v in nxt]
     barrier()
     t = time.perf_counter()
     for _ in range(K):
-        _, nxt = m.decode_step([cur], want_logits=False)
-        cur = int(nxt[0])
+        _, nxt = m.decode_step(cur, want_logits=False)
+        cur = [int(v) for v in nxt]
     e2e_s = time.perf_counter() - t
     barrier()
-    e2e_tps = world * K / vmax(e2e_s)
+    e2e_tps = world * B * K / vmax(e2e_s)
 
     # ---- per-kernel-class device times (launch by launch, CUDA events) ----
     prof = m.profile_decode(8)
@@ -242,35 +264,46 @@ def main():
         return
     T_avg = PL + W + (K + 1) / 2.0
     kv_bytes_tok = cfg.num_hidden_layers * 2 * cfg.kv_dim * (4 if args.kv_dtype == "f32" else 2)
-    step_bytes = m.weight_bytes() + kv_bytes_tok * T_avg + kv_bytes_tok
-    step_gbs = step_bytes * (tok_per_s / world) / 1e9
+    step_bytes = m.weight_bytes() + B * (kv_bytes_tok * T_avg + kv_bytes_tok)  # weights once per step, every sequence's cache
+    step_gbs = step_bytes * (tok_per_s / world / B) / 1e9
+    if fmt != "bf16":
+        kern = "gemv_quant_kernel<1> (Q8_0/Q4_0 dequantising projections; LM head included)"
+    elif B > 8:
+        kern = "gemm_tc_kernel (tcgen05 projections over 64 rows; LM head included)"
+    else:
+        kern = "gemv_bf16_kernel<1> (QKV, O, gate/up, down and LM-head projections)"
+    # DRAM bytes per projection launch from the ncu capture summarised under profiles/ (headline workload
+    # only): 997.0 MB summed over the 97 projection launches of a step, against 987.9 MB algorithmic.
+    traffic = 997.0e6 / 97 if (args.workload == HEADLINE and proj_launches == 97) else None
     out = {
         "metric": "decode_tokens_per_s", "value": tok_per_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32 accumulate over bf16 weights", "data": "synthetic",
+        "dtype": "f32 accumulate over bf16 weights" if fmt == "bf16" else f"f32 accumulate over {fmt} blocks", "data": "synthetic",
         "config": {
-            "workload": "Qwen2.5-0.5B-architecture decoder (24 layers, hidden 896, 14/2 heads, hd 64, SwiGLU 4864, vocab 151936, tied, QKV bias), batch 1 per GPU, " + f"{PL}-token prompt, greedy decode",
-            "kv_cache": f"paged, 16 tokens/page, {args.kv_dtype}", "l2": "inputs larger than L2: 988 MB of weights are streamed once per step (L2 is 126 MB)",
+            "workload": wl_desc + f", {PL}-token prompt, greedy decode",
+            "kv_cache": f"paged, 16 tokens/page, {args.kv_dtype}", "l2": f"inputs larger than L2: {m.weight_bytes() / 1e6:.0f} MB of weights are streamed once per step (L2 is 126 MB)",
             "parallelism": f"replicas x{world}, independent sequences, no collective on the token path", "seed": SEED,
         },
         "clocks": clocks,
-        "e2e": {"value": e2e_tps, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "api": "hm_decode_step (host token id in, greedy next token id out, one stream sync per token)"},
+        "e2e": {"value": e2e_tps, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "api": "hm_decode_step (host token ids in, greedy next token ids out, one stream sync per step)"},
         "gpu_launches": m.launches_per_step() * K,
         "roofline": {
-            "bound": "hbm", "kernel": "gemv_bf16_kernel<1> (QKV, O, gate/up, down and LM-head projections)", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+            "bound": "hbm", "kernel": kern, "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": traffic,
+            "per_launch": {"algorithmic_bytes": proj_bytes / max(proj_launches, 1), "device_us": 1e3 * proj_ms / max(proj_launches, 1)},
+            "timing": "CUDA events on the engine's stream around graph replays of each kernel class (8 steps each), run after the timed region",
             "launches_per_step": proj_launches, "algorithmic_bytes_per_step": proj_bytes, "device_ms_per_step": proj_ms,
         },
-        "step_roofline": {"bytes_per_token": step_bytes, "achieved_gbs": step_gbs, "frac_of_measured": step_gbs / peak, "frac_of_nominal_8TBs": step_gbs / NOMINAL_HBM_GBS},
+        "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_gbs, "frac_of_measured": step_gbs / peak, "frac_of_nominal_8TBs": step_gbs / NOMINAL_HBM_GBS},
         "kernels": [{"name": p["name"], "launches": p["launches_per_step"], "us": round(1e3 * p["ms_per_step"], 2), "MB": round(p["bytes_per_step"] / 1e6, 3),
                      "GBs": round(p["bytes_per_step"] / (p["ms_per_step"] * 1e-3) / 1e9, 1) if p["ms_per_step"] > 0 else None} for p in prof],
     }
     if world == 1 and not args.no_cpu_baseline:
         m.close()
-        steps_c, prompt_c = 32, 8
+        steps_c, prompt_c = (32, 8) if args.workload == HEADLINE else (12, 4)
         tps, dt, threads = cpu_sample(d, cfg, steps_c, 2, prompt_c)
         out["cpu_baseline"] = {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
-                               "sample": f"{steps_c} greedy decode steps after an {prompt_c}-token prompt on the same weights ({dt:.1f} s of CPU time, {threads} OpenMP threads)"}
+                               "sample": f"{steps_c} greedy decode steps of one sequence after an {prompt_c}-token prompt on the same weights ({dt:.1f} s of CPU time, {threads} OpenMP threads)"}
     else:
         out["cpu_baseline"] = None
     print(json.dumps(out), flush=True)

@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     const int head0 = kvh * g;
 
     pdl_launch_dependents();
+    if (a.pf_bytes && tid < 32)
+        l2_prefetch_slice(a.pf_ptr, a.pf_bytes, (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x), (int)(gridDim.x * gridDim.y * gridDim.z), tid);
     pdl_wait();
 
     const int seq = a.row_seq ? a.row_seq[m] : m;

@@ -594,7 +594,8 @@ int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, int K, i
         a.m_valid = mv;
         // same split policy as the engine: K shared by the CTAs of a cluster, reduced through
         // distributed shared memory; global partials + tickets when clusters are switched off
-        static const bool no_cluster = [] { const char* e = std::getenv("HM_NO_CLUSTER"); return e && e[0] == '1'; }();
+        const char* ncl = std::getenv("HM_NO_CLUSTER");  // read per call so a host can switch paths at run time
+        const bool no_cluster = ncl && ncl[0] == '1';
         const int max_cl = gemv_max_cluster();
         if (!no_cluster) {
             gemv_pick_cluster(K, N, mp, sms, max_cl, &a.ksplit, &a.rows_per_split);
@@ -638,6 +639,7 @@ int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int k
     a.N = N;
     a.M = M;
     a.ksplit = ksplit ? ksplit : tc_pick_split(K, N, sm_count_of_current_device());
+    a.epi = EPI_STORE;
     a.y = yd;
     a.ldy = N;
     a.err_flag = err;
@@ -682,14 +684,14 @@ int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, i
     const int q4 = dtype == HM_Q4_0;
     const size_t nb = (size_t)N * (K / 32);
     const uint8_t* bd = sg.in((const uint8_t*)blocks, nb * (q4 ? 18 : 34));
-    uint16_t* scales = (uint16_t*)sg.scratch(nb * 2, false);
-    uint8_t* codes = (uint8_t*)sg.scratch(nb * (q4 ? 16 : 32), false);
+    uint16_t* scales = (uint16_t*)sg.scratch(quant_scale_elems(K, N) * 2, true);
+    uint8_t* codes = (uint8_t*)sg.scratch(quant_code_bytes(K, N, q4), true);
     const int mp = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
     float* xp = (float*)sg.scratch((size_t)mp * K * 4, true);
     float* yd = sg.out(y, (size_t)M * N);
     if (!bd || !scales || !codes || !xp || !yd) return sg.finish(cudaErrorMemoryAllocation);
     sg.ok(cudaMemcpyAsync(xp, x, (size_t)M * K * 4, cudaMemcpyDefault, st));
-    cudaError_t ce = launch_split_blocks(bd, nb, q4, scales, codes, st);
+    cudaError_t ce = launch_split_blocks(bd, N, K, q4, 0, -1, scales, codes, st);
     if (ce == cudaSuccess) {
         QuantArgs a{};
         a.scales = scales;
@@ -701,6 +703,7 @@ int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, i
         a.x = xp;
         a.ldx = K;
         a.pro = PRO_PLAIN;
+        a.epi = EPI_STORE;
         a.y = yd;
         a.ldy = N;
         ce = launch_gemv_quant(a, mp, sm_count_of_current_device(), st, false);

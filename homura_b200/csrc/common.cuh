@@ -42,6 +42,21 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
 
 // 128-bit streaming load of read-only weights: bypass L1 (each weight
 // byte is used once per token and the working set is far larger than L2).
+// Ask the L2 to fetch [base + off, base + off + bytes) from HBM; returns at once (fire and forget).
+// Used to pull the weights of a LATER kernel of the decode chain into the L2 while the current,
+// latency-bound kernel runs: weights never depend on activations, so the HBM stream can run ahead.
+__device__ __forceinline__ void l2_prefetch_slice(const void* base, unsigned long long total, int part, int nparts, int tid) {
+    constexpr unsigned long long CH = 8192;
+    const unsigned long long per = ((total + nparts - 1) / nparts + CH - 1) / CH * CH;
+    const unsigned long long lo = (unsigned long long)part * per;
+    if (lo >= total) return;
+    const unsigned long long hi = lo + per < total ? lo + per : total;
+    for (unsigned long long o = lo + (unsigned long long)tid * CH; o < hi; o += 32ull * CH) {
+        const unsigned long long n = (hi - o < CH ? hi - o : CH) & ~15ull;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)base + o), "r"((unsigned)n) : "memory");
+    }
+}
+
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -108,6 +123,8 @@ struct KvDesc {
 };
 
 struct GemvArgs {
+    const void* pf_ptr;            // optional: weights of a later kernel to pull into the L2 (see l2_prefetch_slice)
+    unsigned long long pf_bytes;
     // weights: element (k, n) of slab s = n / 128 at byte  s*slab_stride + k*row_stride + (n%128)*2
     const uint16_t* W;
     long long slab_stride;  // bytes
@@ -147,6 +164,8 @@ struct GemvArgs {
 };
 
 struct AttnArgs {
+    const void* pf_ptr;  // optional: weights of a later kernel to pull into the L2
+    unsigned long long pf_bytes;
     const float* q;       // [M][heads*hd]
     const void* k_pool;
     const void* v_pool;
@@ -164,15 +183,17 @@ struct AttnArgs {
 };
 
 struct QuantArgs {
-    const uint16_t* scales;  // [N][K/32] f16 bits
-    const uint8_t* codes;    // Q8_0: [N][K]; Q4_0: [N][K/2]
+    const uint16_t* scales;  // [N/32][K/32][32] f16 bits (launch_split_blocks)
+    const uint8_t* codes;    // [N/32][K/32][chunk][32][16 B]: 2 chunks per Q8_0 block, 1 per Q4_0 block
     int q4;                  // 0 = Q8_0, 1 = Q4_0
     int K, N, m_valid;
+    int ksplit, kb_per_split;  // filled in by launch_gemv_quant: CTAs per 32-row tile and k-blocks per CTA
     const float* x;
     int ldx;
     int pro;                 // PRO_PLAIN / PRO_RMSNORM (f64 sum of squares, emitter_quant.rs:713-791)
     const float* norm_w;
     float eps;
+    int epi;                 // EPI_STORE, or EPI_SWIGLU (gate/up rows interleaved 16 + 16 per tile, y = silu(gate) * up, [M][N/2])
     float* y;
     int ldy;
     const float* bias;
@@ -201,7 +222,11 @@ cudaError_t launch_kv_write_rows(const KvDesc& kv, int seq, int pos0, const floa
 cudaError_t launch_kv_read_rows(const KvDesc& kv, int seq, int len, float* k_out, float* v_out, cudaStream_t st);
 cudaError_t launch_convert_to_f32(const void* src, int dtype, size_t n, float* dst, cudaStream_t st);
 
-cudaError_t launch_split_blocks(const uint8_t* blocks, size_t nblocks, int q4, uint16_t* scales, uint8_t* codes, cudaStream_t st);
+// GGUF blocks of n_rows output rows (stored at rows n_off.. of the projection) -> the tiled arrays, which
+// must hold quant_scale_elems / quant_code_bytes of the whole projection and start zeroed.
+size_t quant_scale_elems(int K, int N);
+size_t quant_code_bytes(int K, int N, int q4);
+cudaError_t launch_split_blocks(const uint8_t* blocks, int n_rows, int K, int q4, int n_off, int interleave_which, uint16_t* scales, uint8_t* codes, cudaStream_t st);
 cudaError_t launch_dequant(const uint8_t* blocks, size_t nblocks, int q4, float* out, cudaStream_t st);
 cudaError_t launch_gemv_quant(const QuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
 // quant plan helpers: PostQKV (src/hf/emitter_quant.rs:800-905) and SiLU*Up (:1078-1099)

@@ -84,6 +84,8 @@ int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* 
     const char* nocl = std::getenv("HM_NO_CLUSTER");
     e->use_clusters_ = !(nocl && nocl[0] == '1');
     e->max_cluster_ = gemv_max_cluster();
+    const char* nopf = std::getenv("HM_NO_PREFETCH");
+    e->use_prefetch_ = !(nopf && nopf[0] == '1');
     const char* notc = std::getenv("HM_NO_TC");
     e->use_tc_ = !(notc && notc[0] == '1');
     *out = e;
@@ -155,25 +157,23 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
         }
         if (ce == cudaSuccess) ce = launch_pack_slabs_from_nk((const uint16_t*)tmp, n_part, K, L.slabs, n_off, interleave_which, stream_);
         if (use_tc_ && ce == cudaSuccess) {
-            // second copy for passes over more than 8 rows; gate and up stay un-interleaved here
-            // (rows [0, I) gate, [I, 2I) up) because that path applies SwiGLU in a kernel of its own
+            // second copy for passes over more than 8 rows (same 64 + 64 gate/up interleave per 128 features)
             if (!L.tc) {
                 const size_t bytes = tc_packed_elems(K, N_total) * 2;
                 ce = cudaMalloc(&L.tc, bytes);
                 if (ce == cudaSuccess) ce = cudaMemsetAsync(L.tc, 0, bytes, stream_);
             }
-            const int tc_off = interleave_which >= 0 ? interleave_which * n_part : n_off;
-            if (ce == cudaSuccess) ce = launch_pack_tc((const uint16_t*)tmp, n_part, K, false, L.tc, tc_off, -1, stream_);
+            if (ce == cudaSuccess) ce = launch_pack_tc((const uint16_t*)tmp, n_part, K, false, L.tc, n_off, interleave_which, stream_);
         }
     } else {
         const int q4 = dtype == HM_Q4_0;
-        const size_t nb = K / 32;
         if (!L.scales) {
-            ce = cudaMalloc(&L.scales, (size_t)N_total * nb * 2);
-            if (ce == cudaSuccess) ce = cudaMalloc(&L.codes, (size_t)N_total * nb * (q4 ? 16 : 32));
+            ce = cudaMalloc(&L.scales, quant_scale_elems(K, N_total) * 2);
+            if (ce == cudaSuccess) ce = cudaMalloc(&L.codes, quant_code_bytes(K, N_total, q4));
+            if (ce == cudaSuccess) ce = cudaMemsetAsync(L.scales, 0, quant_scale_elems(K, N_total) * 2, stream_);
+            if (ce == cudaSuccess) ce = cudaMemsetAsync(L.codes, 0, quant_code_bytes(K, N_total, q4), stream_);
         }
-        if (ce == cudaSuccess)
-            ce = launch_split_blocks((const uint8_t*)tmp, (size_t)n_part * nb, q4, L.scales + (size_t)n_off * nb, L.codes + (size_t)n_off * nb * (q4 ? 16 : 32), stream_);
+        if (ce == cudaSuccess) ce = launch_split_blocks((const uint8_t*)tmp, n_part, K, q4, n_off, interleave_which, L.scales, L.codes, stream_);
         quant_ = true;
     }
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
@@ -683,7 +683,8 @@ static int pad_m(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 
 // Projection over up to TC_ROWS rows per launch on the tensor cores (gemm_tc.cu): one kernel packs
 // the activations (folding an RMSNorm when norm_w is given), the GEMM applies bias and residual on store.
-int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, float* y, int ldy, const float* bias, const float* resid, int* launches) {
+int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos,
+                              const int32_t* row_seq, int* launches) {
     if (!L.tc) return fail(HM_ERR_STATE, "tensor-core weight copy missing");
     for (int m0 = 0; m0 < M; m0 += TC_ROWS) {
         const int mc = std::min(TC_ROWS, M - m0);
@@ -699,10 +700,30 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
         a.M = mc;
         a.ksplit = tc_pick_split(L.K, L.N, sm_count_);
         a.xp = xpack_;
+        a.epi = epi;
         a.bias = bias;
         a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
         a.y = y + (size_t)m0 * ldy;
         a.ldy = ldy;
+        a.q_dim = qdim_;
+        a.kv_dim = kvdim_;
+        a.hd = hd_;
+        a.has_qk_norm = cfg_.has_qk_norm;
+        a.eps = (float)cfg_.rms_norm_eps;
+        if (layer >= 0) {
+            a.q_norm_w = layers_[layer].q_norm;
+            a.k_norm_w = layers_[layer].k_norm;
+            a.kv = KvDesc{k_pool_[layer], v_pool_[layer], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+        }
+        a.rope_cos = rope_cos_;
+        a.rope_sin = rope_sin_;
+        a.row_pos = row_pos ? row_pos + m0 : nullptr;
+        a.row_seq = row_seq ? row_seq + m0 : nullptr;
+        if (epi == EPI_LOGITS) {
+            const int nblocks = (L.N + SLAB - 1) / SLAB;
+            a.amax_val = amax_val_ + (size_t)m0 * nblocks;
+            a.amax_idx = amax_idx_ + (size_t)m0 * nblocks;
+        }
         a.err_flag = err_flag_;
         ce = launch_gemm_tc(a, stream_, pdl_);
         if (ce != cudaSuccess) return cuda_fail(ce, "tensor-core projection launch");
@@ -719,6 +740,10 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
         if (L.kind == HM_BF16) {
             GemvArgs a{};
             a.W = L.slabs;
+            if (m0 == 0) {
+                a.pf_ptr = pf_ptr_;
+                a.pf_bytes = pf_bytes_;
+            }
             a.slab_stride = (long long)L.K * SLAB * 2;
             a.row_stride = SLAB * 2;
             a.K = L.K;
@@ -775,6 +800,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.pro = pro;
             a.norm_w = norm_w;
             a.eps = (float)cfg_.rms_norm_eps;
+            a.epi = epi;
             a.y = y + (size_t)m0 * ldy;
             a.ldy = ldy;
             a.bias = bias;
@@ -784,6 +810,8 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
         if (ce != cudaSuccess) return cuda_fail(ce, "projection launch");
         ++*launches;
     }
+    pf_ptr_ = nullptr;
+    pf_bytes_ = 0;
     return HM_OK;
 }
 
@@ -801,18 +829,27 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
     const float eps = (float)cfg_.rms_norm_eps;
     // more than 8 rows of a bf16 model: tensor-core projections with the epilogues as kernels of their own
     const bool tall = use_tc_ && !quant_ && M > MAX_M;
+    // Weight prefetch, decode passes of bf16 models: every kernel asks the L2 for the weights of the
+    // kernel two launches ahead, so HBM keeps streaming while the short dependent kernels run.
+    const bool pf = use_prefetch_ && !quant_ && !tall && only_class_ < 0;
+    auto prefetch = [&](const LinearW* w, size_t off = 0, size_t cap = ~(size_t)0) {
+        pf_ptr_ = nullptr;
+        pf_bytes_ = 0;
+        if (!pf || !w || !w->slabs || off >= w->bytes()) return;
+        pf_ptr_ = (const char*)w->slabs + off;
+        pf_bytes_ = std::min(cap, w->bytes() - off);
+    };
+    constexpr size_t LM_PF = 24u << 20;  // the LM head does not fit the L2: only its first 2 x 24 MB are fetched early
     int rc;
     for (int l = 0; l < L_; ++l) {
         const LayerW& w = layers_[l];
         KvDesc kv{k_pool_[l], v_pool_[l], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
         if (!want(PC_QKV)) {
         } else if (tall) {
-            rc = enqueue_linear_tc(w.qkv, M, h_, H_, w.in_ln, qkv_raw_, QKV, w.qkv_bias, nullptr, launches);
+            rc = enqueue_linear_tc(w.qkv, M, h_, H_, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, launches);
             if (rc) return rc;
-            ce = launch_post_qkv(qkv_raw_, M, heads_, kvh_, hd_, cfg_.has_qk_norm, w.q_norm, w.k_norm, eps, rope_cos_, rope_sin_, row_pos, row_seq, kv, q_, stream_, pdl_);
-            if (ce != cudaSuccess) return cuda_fail(ce, "post_qkv");
-            ++*launches;
         } else if (w.qkv.kind == HM_BF16) {
+            prefetch(&w.o);
             rc = enqueue_linear(w.qkv, M, h_, H_, PRO_RMSNORM, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
         } else {
@@ -835,46 +872,49 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.heads = heads_;
         at.kv_heads = kvh_;
         at.hd = hd_;
-        at.nsplit = att_nsplit_;
+        at.nsplit = std::min(att_nsplit_, attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));  // fewer splits when the rows alone fill the SMs
         at.cluster = use_clusters_ ? 1 : 0;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
         at.out = attn_;
         at.part_acc = att_acc_;
         at.part_ml = att_ml_;
         at.tickets = att_tickets_;
+        if (pf) {
+            at.pf_ptr = w.gu.slabs;
+            at.pf_bytes = w.gu.bytes();
+        }
         if (want(PC_ATTN)) {
             ce = launch_attn_decode(at, M, kv_bf16_, stream_, pdl_);
             if (ce != cudaSuccess) return cuda_fail(ce, "attention launch");
             ++*launches;
         }
         if (want(PC_O) && tall) {
-            rc = enqueue_linear_tc(w.o, M, attn_, qdim_, nullptr, h_, H_, nullptr, h_, launches);
+            rc = enqueue_linear_tc(w.o, M, attn_, qdim_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches);
             if (rc) return rc;
         } else if (want(PC_O)) {
+            prefetch(&w.down);
             rc = enqueue_linear(w.o, M, attn_, qdim_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
         }
         if (!want(PC_GATE_UP)) {
         } else if (tall) {
-            rc = enqueue_linear_tc(w.gu, M, h_, H_, w.post_ln, gu_raw_, 2 * I_, nullptr, nullptr, launches);
+            rc = enqueue_linear_tc(w.gu, M, h_, H_, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, launches);
             if (rc) return rc;
-            ce = launch_silu_mul(gu_raw_, M, I_, act_, stream_, pdl_);
-            if (ce != cudaSuccess) return cuda_fail(ce, "silu_mul");
-            ++*launches;
         } else if (w.gu.kind == HM_BF16) {
+            if (l + 1 < L_) prefetch(&layers_[l + 1].qkv);
+            else if (lm_rows > 0) prefetch(&lm_head_, 0, LM_PF);
             rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
         } else {
-            rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_STORE, gu_raw_, 2 * I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
+            // gate and up rows sit interleaved 16 + 16 in every 32-row tile: SwiGLU in the epilogue
+            rc = enqueue_linear(w.gu, M, h_, H_, PRO_RMSNORM, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
-            ce = launch_silu_mul(gu_raw_, M, I_, act_, stream_, pdl_);
-            if (ce != cudaSuccess) return cuda_fail(ce, "silu_mul");
-            ++*launches;
         }
         if (want(PC_DOWN) && tall) {
-            rc = enqueue_linear_tc(w.down, M, act_, I_, nullptr, h_, H_, nullptr, h_, launches);
+            rc = enqueue_linear_tc(w.down, M, act_, I_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches);
             if (rc) return rc;
         } else if (want(PC_DOWN)) {
+            if (l + 1 == L_ && lm_rows > 0) prefetch(&lm_head_, LM_PF, LM_PF);
             rc = enqueue_linear(w.down, M, act_, I_, PRO_PLAIN, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
         }
@@ -883,9 +923,9 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         const int nslabs = (V_ + SLAB - 1) / SLAB;
         const float* x = h_ + (size_t)lm_row0 * H_;
         const bool lm_tall = use_tc_ && lm_head_.kind == HM_BF16 && lm_head_.tc && lm_rows > MAX_M;
-        const bool slab_argmax = lm_head_.kind == HM_BF16 && !lm_tall;
+        const bool slab_argmax = lm_head_.kind == HM_BF16;  // per-block argmax partials from the projection's epilogue
         if (want(PC_LM_HEAD) && lm_tall) {
-            rc = enqueue_linear_tc(lm_head_, lm_rows, x, H_, final_norm_, logits_, V_, nullptr, nullptr, launches);
+            rc = enqueue_linear_tc(lm_head_, lm_rows, x, H_, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, launches);
             if (rc) return rc;
         } else if (want(PC_LM_HEAD)) {
             rc = slab_argmax ? enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches)

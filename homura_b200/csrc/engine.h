@@ -76,7 +76,7 @@ class Engine {
     // sequence).  lm_row0/lm_rows select the rows that go through the LM head.
     int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);
     int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches);
-    int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, float* y, int ldy, const float* bias, const float* resid, int* launches);
+    int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, int* launches);
     int capture_decode_graph();
     int setup_persistent();   // batch-1 bf16 models: one cooperative launch per decode step
     int launch_step();        // replay the captured graph, or launch the persistent kernel directly
@@ -90,6 +90,9 @@ class Engine {
     bool finalized_ = false, quant_ = false, pdl_ = true;
     bool use_clusters_ = true;  // split reductions through thread-block clusters / DSMEM (HM_NO_CLUSTER=1: global scratch + tickets)
     int max_cluster_ = 8;
+    bool use_prefetch_ = true;  // decode kernels pull the weights of the kernel two launches ahead into the L2 (HM_NO_PREFETCH=1 disables)
+    const void* pf_ptr_ = nullptr;  // prefetch target handed to the next projection launch
+    unsigned long long pf_bytes_ = 0;
     bool use_tc_ = true;  // bf16 models: passes over more than 8 rows run the tcgen05 GEMM (HM_NO_TC=1: 8-row groups of the streaming kernel)
     cudaStream_t stream_ = nullptr;
 

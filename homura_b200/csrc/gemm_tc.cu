@@ -154,6 +154,116 @@ __global__ void __launch_bounds__(256) tc_pack_x_kernel(const float* __restrict_
     }
 }
 
+// ---- epilogues on rows [m_lo, m_hi) of the f32 tile [m][128] (output features n0 .. n0+127) ----
+// The same four epilogues as the streaming projection kernel (gemv_bf16.cu), for up to 64 rows.
+__device__ __forceinline__ bool tc_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i > bi); }
+
+__device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, int nblk, int tid) {
+    const int n0 = nblk * BM, rows = m_hi - m_lo;
+    const int lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = TC_THREADS / 32;
+    if (a.epi == EPI_STORE) {
+        for (int idx = tid; idx < rows * BM; idx += TC_THREADS) {
+            const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
+            if (n < a.N) {
+                float v = tile[m * BM + c];
+                if (a.bias) v += __ldg(a.bias + n);
+                if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
+                a.y[(size_t)m * a.ldy + n] = v;
+            }
+        }
+    } else if (a.epi == EPI_SWIGLU) {
+        // block = 64 gate features followed by the 64 matching up features (src/hf/emitter.rs SwiGLU)
+        for (int idx = tid; idx < rows * 64; idx += TC_THREADS) {
+            const int m = m_lo + idx / 64, c = idx % 64, j = nblk * 64 + c;
+            if (j < a.N / 2) {
+                const float g = tile[m * BM + c], u = tile[m * BM + 64 + c];
+                a.y[(size_t)m * a.ldy + j] = (g / (1.0f + expf(-g))) * u;
+            }
+        }
+    } else if (a.epi == EPI_LOGITS) {
+        for (int idx = tid; idx < rows * BM; idx += TC_THREADS) {
+            const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
+            if (n < a.N) a.y[(size_t)m * a.ldy + n] = tile[m * BM + c];
+        }
+        const int nblocks = (a.N + BM - 1) / BM;
+        for (int m = m_lo + warp; m < m_hi; m += NW) {  // per-row argmax of this block, ties to the higher index
+            float bv = -INFINITY;
+            int bi = -1;
+#pragma unroll
+            for (int i = 0; i < BM / 32; ++i) {
+                const int c = lane + i * 32, n = n0 + c;
+                if (n < a.N) {
+                    const float v = tile[m * BM + c];
+                    if (bi < 0 || tc_better(v, n, bv, bi)) { bv = v; bi = n; }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi >= 0 && (bi < 0 || tc_better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) {
+                a.amax_val[(size_t)m * nblocks + nblk] = bv;
+                a.amax_idx[(size_t)m * nblocks + nblk] = bi;
+            }
+        }
+    } else {  // EPI_QKV_ROPE: bias, per-head QK RMSNorm, RoPE half rotation, K/V page write (src/hf/emitter.rs:604-649)
+        const int hd = a.hd, half = hd >> 1, hps = BM / hd;
+        if (a.bias) {
+            for (int idx = tid; idx < rows * BM; idx += TC_THREADS) {
+                const int m = m_lo + idx / BM, c = idx % BM;
+                if (n0 + c < a.N) tile[m * BM + c] += __ldg(a.bias + n0 + c);
+            }
+            __syncthreads();
+        }
+        if (a.has_qk_norm) {
+            for (int p = warp; p < rows * hps; p += NW) {
+                const int m = m_lo + p / hps, hh = p % hps;
+                const int nh = n0 + hh * hd;
+                if (nh >= a.q_dim + a.kv_dim || nh >= a.N) continue;  // V heads are not normalised
+                float* v = tile + m * BM + hh * hd;
+                float s = 0.f;
+                for (int d = lane; d < hd; d += 32) s = fmaf(v[d], v[d], s);
+                s = warp_sum(s);
+                const float inv = 1.0f / sqrtf(s / (float)hd + a.eps);
+                const float* nw = (nh < a.q_dim) ? a.q_norm_w : a.k_norm_w;
+                for (int d = lane; d < hd; d += 32) v[d] = (v[d] * inv) * __ldg(nw + d);
+            }
+            __syncthreads();
+        }
+        for (int idx = tid; idx < rows * BM; idx += TC_THREADS) {
+            const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
+            if (n >= a.N) continue;
+            const int hh = c / hd, d = c % hd;
+            const int nh = n0 + hh * hd;
+            const int pos = a.row_pos[m];
+            float v = tile[m * BM + c];
+            if (nh < a.q_dim + a.kv_dim) {
+                const float other = (d < half) ? -tile[m * BM + c + half] : tile[m * BM + c - half];
+                const float cs = __ldg(a.rope_cos + (size_t)pos * hd + d);
+                const float sn = __ldg(a.rope_sin + (size_t)pos * hd + d);
+                v = fmaf(other, sn, v * cs);
+            }
+            if (nh < a.q_dim) {
+                a.y[(size_t)m * a.ldy + n] = v;
+            } else {
+                const bool is_k = nh < a.q_dim + a.kv_dim;
+                const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
+                const int seq = a.row_seq ? a.row_seq[m] : m;
+                const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
+                const size_t off = (((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens + (pos % a.kv.page_tokens)) * hd + d;
+                void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
+                if (a.kv.bf16)
+                    reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(v);
+                else
+                    reinterpret_cast<float*>(pool)[off] = v;
+            }
+        }
+    }
+}
+
 // ---- the GEMM: warp 0 = bulk-copy producer, warp 1 = TMEM owner + MMA issuer, warps 2-5 = epilogue ----
 template <bool CL>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) {
@@ -269,32 +379,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
 
-    // ---- epilogue; with split-K the accumulators are first reduce-scattered by activation row
-    //      through distributed shared memory (each CTA sums, in rank order, its share of the rows)
+    // ---- with split-K the accumulators are first reduce-scattered by activation row through
+    //      distributed shared memory: each CTA sums, in rank order, its share of the rows (peers only
+    //      read rows that are not theirs, so the sums can be written back in place)
     pdl_wait();
-    const int n0 = nblk * BM;
     int m_lo = 0, m_hi = a.M;
     if (CL) {
         cluster_sync_all();
         const int rows_per = (a.M + cs - 1) / cs;
         m_lo = min(a.M, split * rows_per);
         m_hi = min(a.M, m_lo + rows_per);
-    }
-    for (int idx = tid; idx < (m_hi - m_lo) * BM; idx += TC_THREADS) {
-        const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
-        float v;
-        if (CL) {
-            v = 0.f;
-            for (int r = 0; r < cs; ++r) v += ld_dsmem_f32(dsmem_addr(out_tile + m * BM + c, (uint32_t)r));
-        } else {
-            v = out_tile[m * BM + c];
+        for (int idx = tid; idx < (m_hi - m_lo) * BM; idx += TC_THREADS) {
+            const int off = (m_lo + idx / BM) * BM + (idx % BM);
+            float v = 0.f;
+            for (int r = 0; r < cs; ++r) v += ld_dsmem_f32(dsmem_addr(out_tile + off, (uint32_t)r));
+            out_tile[off] = v;
         }
-        if (n < a.N) {
-            if (a.bias) v += __ldg(a.bias + n);
-            if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
-            a.y[(size_t)m * a.ldy + n] = v;
-        }
+        __syncthreads();
     }
+    tc_epilogue(a, out_tile, m_lo, m_hi, nblk, tid);
     if (CL) cluster_sync_all();  // a CTA may exit only after its tile was read by its peers
 }
 

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "common.cuh"
+
 namespace hm {
 
 constexpr int TC_ROWS = 64;  // activation rows one launch covers
@@ -14,10 +16,20 @@ struct TcArgs {
     int ksplit;         // CTAs per cluster sharing one n-block (1 = no split, at most 8)
     const unsigned char* xp;  // activations packed by launch_tc_pack_x (tc_xpack_bytes(M, K) bytes)
     int mpad, nstage, tmem_cols;  // filled in by launch_gemm_tc
+    int epi;                 // EPI_STORE (bias, residual), EPI_SWIGLU, EPI_LOGITS or EPI_QKV_ROPE: as in GemvArgs
     const float* bias;       // optional [N]
     const float* resid;      // optional [M][ldy], added as resid + y
     float* y;                // [M][ldy]
     int ldy;
+    // EPI_QKV_ROPE
+    int q_dim, kv_dim, hd, has_qk_norm;
+    float eps;
+    const float *q_norm_w, *k_norm_w, *rope_cos, *rope_sin;
+    const int32_t *row_pos, *row_seq;
+    KvDesc kv;
+    // EPI_LOGITS: per-row argmax of every 128-feature block
+    float* amax_val;
+    int32_t* amax_idx;
     int* err_flag;  // set to 2 when a bounded wait ran out
 };
 

@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     const long long pass_stride = (long long)ROWS_PER_PASS * a.row_stride;
 
     pdl_launch_dependents();
+    if (a.pf_bytes && tid < 32) l2_prefetch_slice(a.pf_ptr, a.pf_bytes, blockIdx.x, gridDim.x, tid);
 
     // First batch of weight loads is issued before the dependency wait: weights never depend
     // on a previous kernel, so their DRAM latency overlaps the predecessor's tail.

@@ -353,7 +353,7 @@ cudaError_t launch_embed_gather(const void* table, int table_dtype, const uint32
     return launch_pdl(embed_gather_kernel, dim3(M), dim3(256), st, pdl, table, table_dtype, tokens, H, V, out, err_flag);
 }
 cudaError_t launch_argmax_finish(const float* amax_val, const int32_t* amax_idx, int nslabs, int M, uint32_t* next_tok, uint32_t* feed_tok, int32_t* pos, uint32_t* hist, int hist_stride, cudaStream_t st, bool pdl) {
-    return launch_pdl(argmax_finish_kernel, dim3(M), dim3(256), st, pdl, amax_val, amax_idx, nslabs, next_tok, feed_tok, pos, hist, hist_stride);
+    return launch_pdl(argmax_finish_kernel, dim3(M), dim3(nslabs > 4096 ? 1024 : 256), st, pdl, amax_val, amax_idx, nslabs, next_tok, feed_tok, pos, hist, hist_stride);
 }
 cudaError_t launch_argmax_rows(const float* logits, int rows, int n, uint32_t* out, cudaStream_t st) {
     argmax_rows_kernel<<<rows, 1024, 0, st>>>(logits, n, out);

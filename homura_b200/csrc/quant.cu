@@ -5,12 +5,17 @@
 // value = (nibble - 8) * d).
 //
 // GGUF stores blocks [N, K/32] of 34 (Q8_0) or 18 (Q4_0) bytes, which no 128-bit load can
-// address.  At load the blocks are split into two arrays (same bytes, same order):
-//   scales f16 [N][K/32]    codes int8 [N][K]  (Q8_0)  or  nibble bytes [N][K/2]  (Q4_0)
-// The GEMV is a row dot product per output: a warp owns an output row, every lane reads
-// 16 bytes of codes per step (coalesced 512 B per warp), dequantises in registers
-// (integer code -> f32, one multiply by the block scale) and the 32 lane partials are merged
-// with xor shuffles.  Activations sit in shared memory as f32.
+// address.  At load the blocks are re-laid in tiles of 32 output rows (same bits, new order):
+//   scales f16 [N/32][K/32][32 rows]
+//   codes      [N/32][K/32][chunk][32 rows][16 B]   chunk = 2 halves of a Q8_0 block, 1 for Q4_0
+// so that the 32 lanes of a warp, each owning one output row, read 512 contiguous bytes per
+// load and all need the SAME 32 activations (one broadcast read from shared memory, no bank
+// conflicts, no shuffle reduction).  A CTA's 8 warps take the k-blocks of its K range round-robin
+// and are summed through shared memory in warp order; K may further be split over the CTAs of a
+// thread-block cluster, summed in rank order through distributed shared memory.  Codes become
+// f32 with a byte permute into the mantissa of 2^23 and one subtraction (exact).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace hm {
@@ -20,12 +25,26 @@ namespace {
 
 constexpr int QT = 256;
 
-__global__ void split_blocks_kernel(const uint8_t* __restrict__ blocks, size_t nblocks, int q4, uint16_t* __restrict__ scales, uint8_t* __restrict__ codes) {
-    const int bsz = q4 ? 18 : 34, csz = q4 ? 16 : 32;
+// blocks: rows [0, n_part) of a projection part, stored at rows n_off.. of the tiled arrays.
+// interleave_which 0 / 1: gate / up rows of a fused SwiGLU projection, 16 + 16 per 32-row tile.
+__global__ void split_blocks_kernel(const uint8_t* __restrict__ blocks, size_t nblocks, int nb, int q4, int n_off, int interleave_which, uint16_t* __restrict__ scales, uint8_t* __restrict__ codes) {
+    const int bsz = q4 ? 18 : 34;
     for (size_t b = blockIdx.x * (size_t)blockDim.x + threadIdx.x; b < nblocks; b += (size_t)gridDim.x * blockDim.x) {
         const uint8_t* s = blocks + b * bsz;
-        scales[b] = (uint16_t)(s[0] | (s[1] << 8));
-        for (int j = 0; j < csz; ++j) codes[b * csz + j] = s[2 + j];
+        const int nl = (int)(b / nb), kb = (int)(b % nb);
+        const int n = interleave_which >= 0 ? (nl >> 4) * 32 + interleave_which * 16 + (nl & 15) : n_off + nl;
+        const size_t tk = (size_t)(n >> 5) * nb + kb;
+        const int r = n & 31;
+        scales[tk * 32 + r] = (uint16_t)(s[0] | (s[1] << 8));
+        if (q4) {
+            uint8_t* d = codes + (tk * 32 + r) * 16;
+            for (int j = 0; j < 16; ++j) d[j] = s[2 + j];
+        } else {
+            for (int c = 0; c < 2; ++c) {
+                uint8_t* d = codes + ((tk * 2 + c) * 32 + r) * 16;
+                for (int j = 0; j < 16; ++j) d[j] = s[2 + c * 16 + j];
+            }
+        }
     }
 }
 
@@ -48,15 +67,103 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ blocks, size_t nblock
     }
 }
 
-template <int M>
-__global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a, int rows_per_warp) {
-    extern __shared__ __align__(16) float xs[];  // [M][K]
+constexpr int QU = 4;  // k-blocks a warp keeps in flight
+
+// four packed codes -> f32, exact: the byte lands in the mantissa of 2^23, then 2^23 + bias is subtracted
+__device__ __forceinline__ float code_f32(uint32_t w, int b, float magic) { return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + b)) - magic; }
+
+template <int M, bool Q4>
+__device__ __forceinline__ void q_block(const uint4 (&c)[2], float d, const float* __restrict__ xb, int xstride, float (&acc)[M]) {
+    float p[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) p[m] = 0.f;
+    if (Q4) {
+        // byte j = element j (low nibble) | element j + 16 (high nibble); value = nibble - 8
+        const uint32_t w[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
+            float fl[4], fh[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                fl[b] = code_f32(lo, b, 8388616.0f);
+                fh[b] = code_f32(hi, b, 8388616.0f);
+            }
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const float4 xl = *reinterpret_cast<const float4*>(xb + m * xstride + i * 4);
+                const float4 xh = *reinterpret_cast<const float4*>(xb + m * xstride + 16 + i * 4);
+                p[m] = fmaf(fl[0], xl.x, p[m]);
+                p[m] = fmaf(fl[1], xl.y, p[m]);
+                p[m] = fmaf(fl[2], xl.z, p[m]);
+                p[m] = fmaf(fl[3], xl.w, p[m]);
+                p[m] = fmaf(fh[0], xh.x, p[m]);
+                p[m] = fmaf(fh[1], xh.y, p[m]);
+                p[m] = fmaf(fh[2], xh.z, p[m]);
+                p[m] = fmaf(fh[3], xh.w, p[m]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t w[4] = {c[h].x, c[h].y, c[h].z, c[h].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t u = w[i] ^ 0x80808080u;  // int8 -> offset-128 byte
+                float f[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) f[b] = code_f32(u, b, 8388736.0f);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xb + m * xstride + h * 16 + i * 4);
+                    p[m] = fmaf(f[0], xv.x, p[m]);
+                    p[m] = fmaf(f[1], xv.y, p[m]);
+                    p[m] = fmaf(f[2], xv.z, p[m]);
+                    p[m] = fmaf(f[3], xv.w, p[m]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = fmaf(d, p[m], acc[m]);
+}
+
+template <int M, bool Q4, bool CL>
+__global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
+    extern __shared__ __align__(16) float qsm[];
+    const int kspan = a.kb_per_split * 32;  // activations this CTA needs
+    float* xs = qsm;                        // [M][kspan]
+    float* red = qsm + M * kspan;           // [8 warps][M][32], then vals [M][32] at red[0..]
     __shared__ double s_wsum[8][MAX_M];
     __shared__ float s_inv[MAX_M];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nb = a.K / 32;
+    const int tile = blockIdx.x / a.ksplit, split = blockIdx.x - tile * a.ksplit;
+    const int kb0 = split * a.kb_per_split, kb1 = min(nb, kb0 + a.kb_per_split);
+    const int nkb = max(0, kb1 - kb0);
+    constexpr int CH = Q4 ? 1 : 2;
+    const uint4* cbase = reinterpret_cast<const uint4*>(a.codes) + ((size_t)tile * nb + kb0) * (CH * 32) + lane;
+    const uint16_t* sbase = a.scales + ((size_t)tile * nb + kb0) * 32 + lane;
+
     pdl_launch_dependents();
+
+    // first batch of weight loads before the dependency wait: weights never depend on a previous kernel
+    uint4 c[QU][2];
+    uint16_t sc[QU];
+#pragma unroll
+    for (int u = 0; u < QU; ++u) {
+        const int kb = warp + 8 * u;
+        const bool ok = kb < nkb;
+#pragma unroll
+        for (int h = 0; h < CH; ++h) c[u][h] = ok ? ld_stream_u4(cbase + ((size_t)kb * CH + h) * 32) : make_uint4(0, 0, 0, 0);
+        sc[u] = ok ? sbase[(size_t)kb * 32] : (uint16_t)0;
+    }
+
     pdl_wait();
+
+    // ---- prologue: this CTA's K range of every activation row into shared memory ----
     if (a.pro == PRO_RMSNORM) {
+        // sum of squares in f64 over the whole row (emitter_quant.rs:713-791)
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             double s = 0.0;
@@ -80,121 +187,150 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a, int r
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const float inv = s_inv[m];
-            const float* xr = a.x + (size_t)m * a.ldx;
-            for (int k = tid; k < a.K; k += QT) xs[m * a.K + k] = (xr[k] * inv) * a.norm_w[k];
+            const float* xr = a.x + (size_t)m * a.ldx + kb0 * 32;
+            for (int k = tid; k < nkb * 32; k += QT) xs[m * kspan + k] = (xr[k] * inv) * a.norm_w[kb0 * 32 + k];
         }
     } else {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const float* xr = a.x + (size_t)m * a.ldx;
-            for (int k = tid; k < a.K; k += QT) xs[m * a.K + k] = xr[k];
+            const float* xr = a.x + (size_t)m * a.ldx + kb0 * 32;
+            for (int k = tid; k < nkb * 32; k += QT) xs[m * kspan + k] = xr[k];
         }
     }
     __syncthreads();
 
-    const int nb = a.K / 32;
-    const int row0 = (blockIdx.x * 8 + warp) * rows_per_warp;
-    for (int r = 0; r < rows_per_warp; ++r) {
-        const int n = row0 + r;
-        if (n >= a.N) break;
-        float acc[M];
+    float acc[M];
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[m] = 0.f;
-        if (a.q4) {
-            // 16 bytes = one block of 32 values
-            const uint4* cp = reinterpret_cast<const uint4*>(a.codes + (size_t)n * (a.K / 2));
-            for (int c = lane; c < nb; c += 32) {
-                const uint4 v = ld_stream_u4(cp + c);
-                const float d = f16_bits_to_f32(a.scales[(size_t)n * nb + c]);
-                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    for (int base = warp; base < nkb; base += 8 * QU) {
+        // issue the next batch, then consume the current one
+        uint4 cn[QU][2];
+        uint16_t sn[QU];
 #pragma unroll
-                for (int m = 0; m < M; ++m) {
-                    const float* xb = xs + m * a.K + c * 32;
-                    float p = 0.f;
+        for (int u = 0; u < QU; ++u) {
+            const int kb = base + 8 * (QU + u);
+            const bool ok = kb < nkb;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            const uint32_t byte = (wv[i] >> (8 * b)) & 0xFFu;
-                            const int j = i * 4 + b;
-                            p = fmaf((float)((int)(byte & 0x0Fu) - 8), xb[j], p);
-                            p = fmaf((float)((int)(byte >> 4) - 8), xb[j + 16], p);
-                        }
-                    }
-                    acc[m] = fmaf(d, p, acc[m]);
-                }
-            }
-        } else {
-            // 16 bytes = half a block (16 values); two lanes share a scale
-            const uint4* cp = reinterpret_cast<const uint4*>(a.codes + (size_t)n * a.K);
-            for (int c = lane; c < nb * 2; c += 32) {
-                const uint4 v = ld_stream_u4(cp + c);
-                const float d = f16_bits_to_f32(a.scales[(size_t)n * nb + (c >> 1)]);
-                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int m = 0; m < M; ++m) {
-                    const float* xb = xs + m * a.K + c * 16;
-                    float p = 0.f;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            const int q = (int)(int8_t)((wv[i] >> (8 * b)) & 0xFFu);
-                            p = fmaf((float)q, xb[i * 4 + b], p);
-                        }
-                    }
-                    acc[m] = fmaf(d, p, acc[m]);
-                }
-            }
+            for (int h = 0; h < CH; ++h) cn[u][h] = ok ? ld_stream_u4(cbase + ((size_t)kb * CH + h) * 32) : make_uint4(0, 0, 0, 0);
+            sn[u] = ok ? sbase[(size_t)kb * 32] : (uint16_t)0;
         }
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[m] = warp_sum(acc[m]);
-        if (lane == 0) {
+        for (int u = 0; u < QU; ++u) {
+            const int kb = base + 8 * u;
+            if (kb < nkb) q_block<M, Q4>(c[u], f16_bits_to_f32(sc[u]), xs + kb * 32, kspan, acc);
+        }
 #pragma unroll
-            for (int m = 0; m < M; ++m) {
-                if (m < a.m_valid) {
-                    float v = acc[m];
-                    if (a.bias) v += a.bias[n];
-                    if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
-                    a.y[(size_t)m * a.ldy + n] = v;
-                }
-            }
+        for (int u = 0; u < QU; ++u) {
+            c[u][0] = cn[u][0];
+            if (!Q4) c[u][1] = cn[u][1];
+            sc[u] = sn[u];
         }
     }
+
+    // ---- sum the 8 warps (fixed order), then the cluster ranks (fixed order) ----
+    __syncthreads();  // xs is dead; red aliases nothing of it but keep the phases apart
+#pragma unroll
+    for (int m = 0; m < M; ++m) red[(warp * M + m) * 32 + lane] = acc[m];
+    __syncthreads();
+    float v = 0.f;
+    if (tid < M * 32) {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w * M * 32 + tid];
+    }
+    __syncthreads();
+    if (tid < M * 32) red[tid] = v;  // vals [M][32]
+    bool writer = true;
+    if (CL) {
+        cluster_sync_all();
+        writer = split == 0;
+        if (writer && tid < M * 32) {
+            for (int r = 1; r < a.ksplit; ++r) v += ld_dsmem_f32(dsmem_addr(red + tid, (uint32_t)r));
+        }
+    }
+    if (a.epi == EPI_SWIGLU) {
+        // tile = 16 gate rows followed by the 16 matching up rows
+        if (writer && tid < M * 32) red[tid] = v;
+        __syncthreads();
+        if (writer && tid < M * 32 && (tid & 31) < 16) {
+            const int m = tid >> 5, j = tile * 16 + (tid & 31);
+            if (m < a.m_valid && j < a.N / 2) {
+                const float g = red[tid], u = red[tid + 16];
+                a.y[(size_t)m * a.ldy + j] = (g / (1.0f + expf(-g))) * u;
+            }
+        }
+    } else if (writer && tid < M * 32) {
+        const int m = tid >> 5, n = tile * 32 + (tid & 31);
+        if (m < a.m_valid && n < a.N) {
+            if (a.bias) v += a.bias[n];
+            if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
+            a.y[(size_t)m * a.ldy + n] = v;
+        }
+    }
+    if (CL) cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
 }
 
-template <int M>
-cudaError_t launch_qm(const QuantArgs& a, int sm_count, cudaStream_t st, bool pdl) {
-    const size_t smem = sizeof(float) * (size_t)M * a.K;
+template <int M, bool Q4, bool CL>
+cudaError_t launch_q3(const QuantArgs& a, cudaStream_t st, bool pdl) {
+    const size_t smem = sizeof(float) * ((size_t)M * a.kb_per_split * 32 + 8 * M * 32);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
-        cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<M, Q4, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    // about four CTAs per SM when the matrix is large enough, one row per warp at least
-    int rpw = (a.N + sm_count * 4 * 8 - 1) / (sm_count * 4 * 8);
-    if (rpw < 1) rpw = 1;
-    const int grid = (a.N + 8 * rpw - 1) / (8 * rpw);
+    const int tiles = (a.N + 31) / 32;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)(tiles * a.ksplit));
     cfg.blockDim = dim3(QT);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (CL) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = (unsigned)a.ksplit;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = at;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_quant_kernel<M>, a, rpw);
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, gemv_quant_kernel<M, Q4, CL>, a);
+}
+
+template <int M>
+cudaError_t launch_qm(const QuantArgs& a_in, int sm_count, cudaStream_t st, bool pdl) {
+    QuantArgs a = a_in;
+    const int nb = a.K / 32, tiles = (a.N + 31) / 32;
+    // K split: enough CTAs for two per SM, at most 8 per cluster, at least one k-block per warp, and
+    // an activation slice of at most 48 KB
+    int ks = (2 * sm_count + tiles - 1) / tiles;
+    if (ks > 8) ks = 8;
+    while (ks > 1 && nb / ks < 8) --ks;
+    const int max_kb = std::max(1, (12288 / M) / 32);
+    while (ks < 8 && (nb + ks - 1) / ks > max_kb) ++ks;
+    if (ks < 1) ks = 1;
+    a.kb_per_split = (nb + ks - 1) / ks;
+    a.ksplit = (nb + a.kb_per_split - 1) / a.kb_per_split;
+    if (a.q4) return a.ksplit > 1 ? launch_q3<M, true, true>(a, st, pdl) : launch_q3<M, true, false>(a, st, pdl);
+    return a.ksplit > 1 ? launch_q3<M, false, true>(a, st, pdl) : launch_q3<M, false, false>(a, st, pdl);
 }
 
 }  // namespace
 
-cudaError_t launch_split_blocks(const uint8_t* blocks, size_t nblocks, int q4, uint16_t* scales, uint8_t* codes, cudaStream_t st) {
+size_t quant_scale_elems(int K, int N) { return (size_t)((N + 31) / 32) * (K / 32) * 32; }
+size_t quant_code_bytes(int K, int N, int q4) { return quant_scale_elems(K, N) * (q4 ? 16 : 32); }
+
+cudaError_t launch_split_blocks(const uint8_t* blocks, int n_rows, int K, int q4, int n_off, int interleave_which, uint16_t* scales, uint8_t* codes, cudaStream_t st) {
+    const size_t nblocks = (size_t)n_rows * (K / 32);
     size_t g = (nblocks + 255) / 256;
     if (g > 148 * 32) g = 148 * 32;
     if (g < 1) g = 1;
-    split_blocks_kernel<<<(unsigned)g, 256, 0, st>>>(blocks, nblocks, q4, scales, codes);
+    split_blocks_kernel<<<(unsigned)g, 256, 0, st>>>(blocks, nblocks, K / 32, q4, n_off, interleave_which, scales, codes);
     return cudaGetLastError();
 }
 

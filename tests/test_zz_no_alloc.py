@@ -9,7 +9,10 @@ shapes that would need more than the array holds.
 
 The test calls both entry points through the C ABI on the same device-resident inputs and
 expects identical outputs (same kernel, same split, same reduction order), twice in a row and
-across a larger-then-smaller shape so stale scratch contents would show.  It lives in a file
+across a larger-then-smaller shape so stale scratch contents would show.  The ordinary entry
+point is switched to its global-scratch reduction (HM_NO_CLUSTER=1) for the comparison, since
+that is the reduction the allocation-free variant uses; its default, the reduction through a
+thread-block cluster, sums in a different order and is compared by tolerance.  The file is one
 that pytest collects last."""
 import numpy as np
 import pytest
@@ -35,7 +38,8 @@ def _both(hm, x, w, M, K, N, layout):
     return y_ref.download(np.float32, M * N), y_new.download(np.float32, M * N)
 
 
-def test_noalloc_matches_regular_entry_point_twice_in_a_row(hm, oracle):
+def test_noalloc_matches_regular_entry_point_twice_in_a_row(hm, oracle, monkeypatch):
+    monkeypatch.setenv("HM_NO_CLUSTER", "1")
     rng = np.random.default_rng(2024)
     # (M, K, N): split-K shapes of the decode step, a larger one, then a small one again
     shapes = [(1, 896, 1152), (1, 896, 1152), (8, 4864, 896), (16, 1536, 17920), (1, 896, 896), (4, 896, 9728)]
@@ -48,6 +52,15 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(hm, oracle):
             # and both are the right answer (tolerance of the kernel parity tests)
             want = oracle.matmul_bf16(x, w).ravel()
             assert np.abs(new - want).max() <= 2e-5 * np.abs(want).max()
+
+
+def test_noalloc_agrees_with_cluster_reduction_within_tolerance(hm):
+    rng = np.random.default_rng(77)
+    M, K, N = 4, 4864, 896
+    w = synth.f32_to_bf16_rne(rng.standard_normal((K, N), dtype=np.float32) * np.float32(0.02))
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    ref, new = _both(hm, x, hm.pack_bf16_slabs(w), M, K, N, hm.LAYOUT_SLAB128)
+    assert np.abs(new - ref).max() <= 2e-5 * np.abs(ref).max()
 
 
 def test_noalloc_rejects_what_it_cannot_serve(hm):
