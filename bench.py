@@ -1,5 +1,6 @@
 #!/usr/bin/env python
-"""Decode throughput of the B200 engine on the Qwen2.5-0.5B-architecture workload.
+"""Decode throughput of the B200 engine on the Qwen2.5-0.5B-architecture workload
+(--workload selects the other measured configurations; the default is the headline).
 
     python bench.py --gpus N --steps K --warmup W            # this engine
     python bench.py --impl reference --gpus N --steps K ...   # the reference's algorithm on host cores
@@ -16,7 +17,8 @@ Prints ONE JSON line (rank 0):
   e2e        the same metric through the per-token C-ABI call with host buffers: token id in,
              next token id out, one synchronisation per token;
   roofline   the projection kernel (all weight streaming of a step): algorithmic bytes / device
-             time of its launches, against the measured HBM copy bandwidth;
+             time of its launches (CUDA events around graph replays of each kernel class, taken
+             live after the timed region), against the measured HBM copy bandwidth;
   cpu_baseline  the CPU oracle (a restatement of Homura's CPU path) on a bounded sample.
 """
 from __future__ import annotations

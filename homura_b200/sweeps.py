@@ -67,9 +67,9 @@ def _time_launches(fn, n_rot: int, target_ms: float = 30.0):
         reps = min(4096, max(reps * 2, int(reps * target_ms / max(ms, 1e-3)) + 1))
 
 
-def projections(ms: list[int], peak_gbs: float):
+def projections(ms: list[int], peak_gbs: float, shapes=None, profile_launches: int = 0):
     rng = np.random.default_rng(5)
-    for (K, N) in PROJECTION_SHAPES:
+    for (K, N) in (shapes or PROJECTION_SHAPES):
         w = synth.f32_to_bf16_rne(rng.standard_normal((K, N), dtype=np.float32) * np.float32(0.02))
         slab = hm.pack_bf16_slabs(w).reshape(-1)
         tc = hm.pack_bf16_tc(w)
@@ -96,6 +96,12 @@ def projections(ms: list[int], peak_gbs: float):
                 else:
                     b, nb = bufs["tc"]
                     fn = lambda i, st: hm.gemm_bf16_tc((xb.ptr, M), b.ptr + (i % n_rot) * nb, N, K=K, y=yb.ptr, stream=st)
+                if profile_launches:  # a few plain launches for a profiler run, no timing
+                    for i in range(profile_launches):
+                        fn(i, None)
+                    hm.dev_sync()
+                    print(json.dumps({"sweep": "projection", "path": path, "M": M, "K": K, "N": N, "profile_launches": profile_launches}), flush=True)
+                    continue
                 us, iters, mode = _time_launches(fn, n_rot)
                 alg = 2 * K * N  # weight bytes, read once per launch
                 gbs = alg / us / 1e3
@@ -165,10 +171,13 @@ def main(argv=None):
     ap.add_argument("--kv-len", type=int, nargs="*", default=[512, 4096, 32768])
     ap.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64])
     ap.add_argument("--kv-dtype", choices=["f32", "bf16"], default="f32")
+    ap.add_argument("--shape", action="append", default=None, help="K,N of a projection; repeatable; default: the built-in shapes")
+    ap.add_argument("--profile-launches", type=int, default=0, help="projections: issue this many plain launches per case and exit (for ncu)")
     ap.add_argument("--hbm-peak-gbs", type=float, default=6545.6, help="copy bandwidth to report fractions against")
     a = ap.parse_args(argv)
     if a.which == "projections":
-        projections(a.m, a.hbm_peak_gbs)
+        shapes = [tuple(int(v) for v in sh.split(",")) for sh in a.shape] if a.shape else None
+        projections(a.m, a.hbm_peak_gbs, shapes, a.profile_launches)
     else:
         attention(a.kv_len, a.batch, a.kv_dtype, a.hbm_peak_gbs)
     return 0
