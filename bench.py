@@ -50,6 +50,28 @@ def log(*a):
     print(*a, file=sys.stderr, flush=True)
 
 
+# The contract is ONE JSON line on stdout.  Libraries (NCCL prints its version there) must not add
+# to it, so file descriptor 1 is pointed at stderr for the whole run and the line goes to the saved one.
+_OUT_FD = None
+
+
+def claim_stdout():
+    global _OUT_FD
+    if _OUT_FD is None:
+        sys.stdout.flush()
+        _OUT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    data = (json.dumps(obj) + "\n").encode()
+    if _OUT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_OUT_FD, data)
+
+
 # name -> (config attribute in homura_b200.synth, checkpoint format, sequences per GPU, description)
 WORKLOADS = {
     "qwen25-05b": ("QWEN25_05B", "bf16", 1, "Qwen2.5-0.5B-architecture decoder (24 layers, hidden 896, 14/2 heads, hd 64, SwiGLU 4864, vocab 151936, tied, QKV bias), batch 1 per GPU"),
@@ -134,11 +156,11 @@ class ClockSampler:
 
 
 def dist_setup(n_gpus):
-    """(rank, world, local_rank, barrier, max_over_ranks).  torch.distributed only as plumbing."""
+    """(rank, world, local_rank, barrier, max_over_ranks, close).  torch.distributed only as plumbing."""
     from homura_b200.replicas import Rendezvous
 
     rv = Rendezvous()
-    return rv.rank, rv.world, rv.local, rv.barrier, rv.max
+    return rv.rank, rv.world, rv.local, rv.barrier, rv.max, rv.close
 
 
 def cpu_sample(d, cfg, steps, warmup, prompt_len):
@@ -179,7 +201,7 @@ def run_reference(args):
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 def main():
@@ -194,13 +216,14 @@ def main():
     ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="default: the headline workload; the others are the remaining measured configurations")
     ap.add_argument("--device-only", action="store_true", help="only the device-timed region: skips the end-to-end loop, the per-kernel pass and the CPU baseline (for profiler runs)")
     args = ap.parse_args()
+    claim_stdout()
     if args.impl == "reference":
         return run_reference(args)
 
     import homura_b200 as hm
     from homura_b200 import synth
 
-    rank, world, local, barrier, vmax = dist_setup(args.gpus)
+    rank, world, local, barrier, vmax, close = dist_setup(args.gpus)
     K, W = args.steps, max(args.warmup, 3)
     cfg_name, fmt, B, wl_desc = WORKLOADS[args.workload]
     cfg = getattr(synth, cfg_name)
@@ -233,8 +256,9 @@ def main():
 
     if args.device_only:
         if rank == 0:
-            print(json.dumps({"metric": "decode_tokens_per_s", "value": tok_per_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_max / K,
-                              "config": {"workload": f"device-only run, prompt {PL}"}, "clocks": clocks}), flush=True)
+            emit({"metric": "decode_tokens_per_s", "value": tok_per_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_max / K,
+                  "config": {"workload": f"device-only run, prompt {PL}"}, "clocks": clocks})
+        close()
         return
 
     # ---- end to end through the per-token C-ABI call (host token in, host token out) ----
@@ -262,6 +286,7 @@ def main():
     peak, peak_kind = measured_peak()
     achieved = proj_bytes / (proj_ms * 1e-3) / 1e9 if proj_ms > 0 else 0.0
 
+    close()
     if rank != 0:
         return
     T_avg = PL + W + (K + 1) / 2.0
@@ -308,7 +333,7 @@ def main():
                                "sample": f"{steps_c} greedy decode steps of one sequence after an {prompt_c}-token prompt on the same weights ({dt:.1f} s of CPU time, {threads} OpenMP threads)"}
     else:
         out["cpu_baseline"] = None
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 if __name__ == "__main__":
