@@ -22,6 +22,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 namespace hm {
 namespace {
@@ -56,6 +57,127 @@ __device__ __forceinline__ void unpack_store(float* o, const uint4& v) {
     } else {
         *reinterpret_cast<float4*>(o) = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
     }
+}
+
+// Merge the per-warp (max, sum, acc) triples of a CTA (warp = page slot * g + query head), then the
+// splits of the (row, KV head): through the cluster (rank 0 reads its peers' shared memory in rank
+// order), or through global scratch by whichever CTA arrives last at the ticket.
+template <int HD, bool CL>
+__device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p);
+
+// One-head-per-warp kernels: publish the warp's triple at entry (slot * g + head) = warp, then merge.
+template <int HD, bool CL>
+__device__ __forceinline__ void merge_and_write(const AttnArgs& a, bool active, float run_m, float run_l, const float (&acc)[HD / 32], int nsub, int g, int head0, int split, int kvh, int m, float* w_ml,
+                                                float* w_acc, float* c_o, float* c_ml, int* s_last_p) {
+    constexpr int EPL = HD / 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (warp < ATT_WARPS) {
+        if (lane == 0) {
+            w_ml[warp * 2 + 0] = active ? run_m : -INFINITY;
+            w_ml[warp * 2 + 1] = active ? run_l : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) w_acc[warp * HD + lane * EPL + e] = active ? acc[e] : 0.f;
+    }
+    __syncthreads();
+    merge_slots_and_write<HD, CL>(a, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, s_last_p);
+}
+
+// Merge the (max, sum, acc) triples of nsub page slots per head (entry slot * g + head), then the
+// splits of the (row, KV head): through the cluster (rank 0 reads its peers' shared memory in rank
+// order), or through global scratch by whichever CTA arrives last at the ticket.
+template <int HD, bool CL>
+__device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p) {
+    const int tid = threadIdx.x;
+    const int nthreads = blockDim.x;
+    int& s_last = *s_last_p;
+    for (int i = tid; i < g * HD; i += nthreads) {
+        const int jj = i / HD, d = i % HD;
+        float M = -INFINITY;
+        for (int sb = 0; sb < nsub; ++sb) M = fmaxf(M, w_ml[(sb * g + jj) * 2]);
+        float l = 0.f, o = 0.f;
+        if (M > -INFINITY) {
+            for (int sb = 0; sb < nsub; ++sb) {
+                const int w = sb * g + jj;
+                const float ms = w_ml[w * 2];
+                if (ms > -INFINITY) {
+                    const float sc = expf(ms - M);
+                    l = fmaf(w_ml[w * 2 + 1], sc, l);
+                    o = fmaf(w_acc[w * HD + d], sc, o);
+                }
+            }
+        }
+        const int head = head0 + jj;
+        if (CL) {
+            c_o[i] = o;
+            if (d == 0) {
+                c_ml[jj * 2 + 0] = M;
+                c_ml[jj * 2 + 1] = l;
+            }
+        } else if (a.nsplit == 1) {
+            a.out[(size_t)m * a.heads * HD + head * HD + d] = o / l;
+        } else {
+            const size_t pi = ((size_t)m * a.heads + head) * a.nsplit + split;
+            a.part_acc[pi * HD + d] = o;
+            if (d == 0) {
+                a.part_ml[pi * 2 + 0] = M;
+                a.part_ml[pi * 2 + 1] = l;
+            }
+        }
+    }
+    if (CL) {
+        // The splits of one (row, KV head) are the CTAs of one cluster: rank 0 merges their
+        // (max, sum, acc) triples straight out of the peers' shared memory, in rank order.
+        cluster_sync_all();
+        if (cluster_ctarank() == 0) {
+            for (int i = tid; i < g * HD; i += nthreads) {
+                const int jj = i / HD, d = i % HD;
+                float M = -INFINITY;
+                for (int r = 0; r < a.nsplit; ++r) M = fmaxf(M, ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r)));
+                float l = 0.f, o = 0.f;
+                for (int r = 0; r < a.nsplit; ++r) {
+                    const float ms = ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r));
+                    if (ms > -INFINITY) {
+                        const float sc = expf(ms - M);
+                        l = fmaf(ld_dsmem_f32(dsmem_addr(c_ml + jj * 2 + 1, (uint32_t)r)), sc, l);
+                        o = fmaf(ld_dsmem_f32(dsmem_addr(c_o + i, (uint32_t)r)), sc, o);
+                    }
+                }
+                a.out[(size_t)m * a.heads * HD + (head0 + jj) * HD + d] = o / l;
+            }
+        }
+        cluster_sync_all();
+        return;
+    }
+    if (a.nsplit == 1) return;
+
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int tk = atomicAdd(a.tickets + (m * a.kv_heads + kvh), 1u);
+        s_last = (tk == (unsigned int)(a.nsplit - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int i = tid; i < g * HD; i += nthreads) {
+        const int jj = i / HD, d = i % HD;
+        const int head = head0 + jj;
+        const size_t base = ((size_t)m * a.heads + head) * a.nsplit;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < a.nsplit; ++s2) M = fmaxf(M, ld_cg_f32(a.part_ml + (base + s2) * 2));
+        float l = 0.f, o = 0.f;
+        for (int s2 = 0; s2 < a.nsplit; ++s2) {
+            const float ms = ld_cg_f32(a.part_ml + (base + s2) * 2);
+            if (ms > -INFINITY) {
+                const float sc = expf(ms - M);
+                l = fmaf(ld_cg_f32(a.part_ml + (base + s2) * 2 + 1), sc, l);
+                o = fmaf(ld_cg_f32(a.part_acc + (base + s2) * HD + d), sc, o);
+            }
+        }
+        a.out[(size_t)m * a.heads * HD + head * HD + d] = o / l;
+    }
+    if (tid == 0) a.tickets[m * a.kv_heads + kvh] = 0u;
 }
 
 template <int HD, bool BF16, bool CL>
@@ -121,7 +243,15 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
                 const int slot = idx / TL::PIECES, piece = idx % TL::PIECES;
                 const int e = piece * TL::PER16, t = e / HD, d = e % HD;
                 float* base = tiles + slot * TL::SLOT_FLOATS;
-                unpack_store<BF16>(base + t * TL::KLD + d, kreg[i]);
+                // K pages are chunk-major (k_tile_off): a piece is one 4-element chunk of one token
+                // (f32) or of two neighbouring tokens (bf16); the shared-memory tile stays [token][KLD]
+                float* ko = base + ((e >> 2) & 15) * TL::KLD + (e >> 6) * 4;
+                if (BF16) {
+                    ko[0] = bf16_lo(kreg[i].x); ko[1] = bf16_hi(kreg[i].x); ko[2] = bf16_lo(kreg[i].y); ko[3] = bf16_hi(kreg[i].y);
+                    ko[TL::KLD + 0] = bf16_lo(kreg[i].z); ko[TL::KLD + 1] = bf16_hi(kreg[i].z); ko[TL::KLD + 2] = bf16_lo(kreg[i].w); ko[TL::KLD + 3] = bf16_hi(kreg[i].w);
+                } else {
+                    unpack_store<false>(ko, kreg[i]);
+                }
                 unpack_store<BF16>(base + PT * TL::KLD + t * HD + d, vreg[i]);
             }
         }
@@ -187,102 +317,242 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
         }
     }
 
-    // ---- merge the page slots of this CTA: warp (sub, j) -> head j ----
-    if (lane == 0) {
-        w_ml[warp * 2 + 0] = active ? run_m : -INFINITY;
-        w_ml[warp * 2 + 1] = active ? run_l : 0.f;
+    merge_and_write<HD, CL>(a, active, run_m, run_l, acc, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, &s_last);
+}
+
+// ---- streaming variant for long contexts ---------------------------------------------------------
+// Same (row, KV head, split) decomposition, but built for bandwidth: the pages arrive through a ring
+// of shared-memory stages filled by cp.async.bulk (a K tile or a V tile of a page is one contiguous
+// block of the pool, so the ninth warp's elected thread issues two bulk copies per page, up to
+// ST_RING_BYTES ahead) and each of the eight consumer warps takes whole pages, round-robin, for ALL g
+// query heads of the KV head: a K chunk is read from shared memory once and used g times (the
+// chunk-major K tile makes that read conflict-free while the query chunk is a broadcast), and a V row
+// is read once per token for g heads.  That cuts shared-memory traffic per page by about 3x against
+// one-warp-per-head, which is what bounds the kernel above on long contexts.  Used when a CTA has at
+// least ST_MIN_PAGES pages to read.
+constexpr int ST_THREADS = ATT_THREADS + 32;
+constexpr int ST_MIN_PAGES = 8;
+constexpr int ST_MAX_STAGES = 16;
+constexpr int ST_RING_BYTES = 64 * 1024;  // per CTA; two CTAs per SM keep 128 KB of pages in flight
+constexpr int ST_MAX_PT = 4096;  // page-table entries of one CTA staged in shared memory
+
+template <int HD, bool BF16>
+struct StTile {
+    static constexpr int ESZ = BF16 ? 2 : 4;
+    static constexpr int TILE_BYTES = PT * HD * ESZ;  // one K or V tile
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int STAGES = (ST_RING_BYTES / STAGE_BYTES) < ST_MAX_STAGES ? (ST_RING_BYTES / STAGE_BYTES) : ST_MAX_STAGES;
+    // Consumer warps that take pages round-robin.  Every phase of a stage must be consumed by the same
+    // warp (a parity wait cannot tell phase k from phase k + 2), so the stage count is a multiple of it.
+    static constexpr int CW = STAGES < ATT_WARPS ? STAGES : ATT_WARPS;
+    static_assert(STAGES % CW == 0, "stage count must be a multiple of the consumer warp count");
+};
+
+template <bool BF16>
+__device__ __forceinline__ float4 ld_chunk4(const void* tile, int elem) {  // 4 consecutive elements as f32
+    if (BF16) {
+        const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(tile) + elem);
+        return make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
     }
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) w_acc[warp * HD + lane * EPL + e] = active ? acc[e] : 0.f;
+    return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(tile) + elem);
+}
+
+template <int HD, bool BF16, bool CL>
+__global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnArgs a) {
+    using ST = StTile<HD, BF16>;
+    using T = typename std::conditional<BF16, uint16_t, float>::type;
+    constexpr int EPL = HD / 32;
+    constexpr int NCH = HD / 8;  // 4-element chunks per half row (lane = token, half)
+    extern __shared__ __align__(128) unsigned char st_sm[];
+    unsigned char* ring = st_sm;                                                 // [STAGES][K tile | V tile]
+    float* q_s = reinterpret_cast<float*>(ring + ST::STAGES * ST::STAGE_BYTES);  // [G_MAX][NCH][2 halves][4]
+    float* p_s = q_s + G_MAX * HD;                                               // [ATT_WARPS][G_MAX][16]
+    float* c_o = p_s + ATT_WARPS * G_MAX * PT;                                   // [G_MAX][HD]
+    float* c_ml = c_o + G_MAX * HD;                                              // [G_MAX][2]
+    // the per-warp results reuse the ring once every page has been consumed
+    float* w_ml = reinterpret_cast<float*>(ring);                                // [ATT_WARPS * g][2]
+    float* w_acc = w_ml + ATT_WARPS * G_MAX * 2;                                 // [ATT_WARPS * g][HD]
+    static_assert(sizeof(float) * (ATT_WARPS * G_MAX * 2 + ATT_WARPS * G_MAX * HD) <= (size_t)ST::STAGES * ST::STAGE_BYTES, "ring too small for the merge scratch");
+    int32_t* pt_s = reinterpret_cast<int32_t*>(c_ml + G_MAX * 2);                // [pages of this CTA]
+    __shared__ uint64_t full[ST_MAX_STAGES], empty[ST_MAX_STAGES];
+    __shared__ int s_last;
+    __shared__ volatile int s_abort;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+    const int g = a.heads / a.kv_heads;
+    const int head0 = kvh * g;
+
+    if (tid == 0) {
+        for (int s = 0; s < ST::STAGES; ++s) {
+            mb_init(&full[s], 1);
+            mb_init(&empty[s], 1);
+        }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_launch_dependents();
+    if (a.pf_bytes && tid < 32)
+        l2_prefetch_slice(a.pf_ptr, a.pf_bytes, (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x), (int)(gridDim.x * gridDim.y * gridDim.z), tid);
+    pdl_wait();
+
+    const int seq = a.row_seq ? a.row_seq[m] : m;
+    const int kvlen = a.kv_len ? a.kv_len[m] : a.row_pos[m] + 1;
+    const int npages = (kvlen + PT - 1) / PT;
+    const int pps = (npages + a.nsplit - 1) / a.nsplit;
+    const int p0 = split * pps, p1 = min(npages, p0 + pps);
+    const int np = max(0, p1 - p0);
+    const int32_t* pt = a.page_table + (size_t)seq * a.max_pages;
+    for (int i = tid; i < np; i += ST_THREADS) pt_s[i] = pt[p0 + i];
+    // query rows re-ordered so that the two halves' copies of chunk c are adjacent: q_s[j][c][half][4]
+    for (int i = tid; i < g * HD; i += ST_THREADS) {
+        const int jj = i / HD, d = i % HD;
+        const int hfq = d / (HD / 2), c = (d % (HD / 2)) >> 2;
+        q_s[jj * HD + (c * 2 + hfq) * 4 + (d & 3)] = a.q[(size_t)m * a.heads * HD + (head0 + jj) * HD + d];
+    }
     __syncthreads();
 
-    for (int i = tid; i < g * HD; i += ATT_THREADS) {
-        const int jj = i / HD, d = i % HD;
-        float M = -INFINITY;
-        for (int sb = 0; sb < nsub; ++sb) M = fmaxf(M, w_ml[(sb * g + jj) * 2]);
-        float l = 0.f, o = 0.f;
-        if (M > -INFINITY) {
-            for (int sb = 0; sb < nsub; ++sb) {
-                const int w = sb * g + jj;
-                const float ms = w_ml[w * 2];
-                if (ms > -INFINITY) {
-                    const float sc = expf(ms - M);
-                    l = fmaf(w_ml[w * 2 + 1], sc, l);
-                    o = fmaf(w_acc[w * HD + d], sc, o);
-                }
-            }
-        }
-        const int head = head0 + jj;
-        if (CL) {
-            c_o[i] = o;
-            if (d == 0) {
-                c_ml[jj * 2 + 0] = M;
-                c_ml[jj * 2 + 1] = l;
-            }
-        } else if (a.nsplit == 1) {
-            a.out[(size_t)m * a.heads * HD + head * HD + d] = o / l;
-        } else {
-            const size_t pi = ((size_t)m * a.heads + head) * a.nsplit + split;
-            a.part_acc[pi * HD + d] = o;
-            if (d == 0) {
-                a.part_ml[pi * 2 + 0] = M;
-                a.part_ml[pi * 2 + 1] = l;
-            }
-        }
+    // per-warp running softmax state of every head; the page loop leaves warps with different maxima
+    float run_m[G_MAX], run_l[G_MAX], acc[G_MAX][EPL];
+#pragma unroll
+    for (int jj = 0; jj < G_MAX; ++jj) {
+        run_m[jj] = -INFINITY;
+        run_l[jj] = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[jj][e] = 0.f;
     }
-    if (CL) {
-        // The splits of one (row, KV head) are the CTAs of one cluster: rank 0 merges their
-        // (max, sum, acc) triples straight out of the peers' shared memory, in rank order.
-        cluster_sync_all();
-        if (cluster_ctarank() == 0) {
-            for (int i = tid; i < g * HD; i += ATT_THREADS) {
-                const int jj = i / HD, d = i % HD;
-                float M = -INFINITY;
-                for (int r = 0; r < a.nsplit; ++r) M = fmaxf(M, ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r)));
-                float l = 0.f, o = 0.f;
-                for (int r = 0; r < a.nsplit; ++r) {
-                    const float ms = ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r));
-                    if (ms > -INFINITY) {
-                        const float sc = expf(ms - M);
-                        l = fmaf(ld_dsmem_f32(dsmem_addr(c_ml + jj * 2 + 1, (uint32_t)r)), sc, l);
-                        o = fmaf(ld_dsmem_f32(dsmem_addr(c_o + i, (uint32_t)r)), sc, o);
+
+    if (warp == ATT_WARPS) {
+        // ---- producer: two bulk copies per page, as far ahead as the ring allows ----
+        if (lane == 0) {
+            const T* kpool = reinterpret_cast<const T*>(a.k_pool);
+            const T* vpool = reinterpret_cast<const T*>(a.v_pool);
+            for (int i = 0; i < np; ++i) {
+                const int s = i % ST::STAGES;
+                const uint32_t par = ((i / ST::STAGES) & 1u) ^ 1u;
+                if (!mb_wait(&empty[s], par, a.err_flag, &s_abort)) break;
+                const size_t tile = ((size_t)pt_s[i] * a.kv_heads + kvh) * PT * HD;
+                unsigned char* dst = ring + (size_t)s * ST::STAGE_BYTES;
+                mb_expect_tx(&full[s], ST::STAGE_BYTES);
+                bulk_copy(dst, kpool + tile, ST::TILE_BYTES, &full[s]);
+                bulk_copy(dst + ST::TILE_BYTES, vpool + tile, ST::TILE_BYTES, &full[s]);
+            }
+        }
+    } else if (warp < ST::CW) {
+        const int t = lane & 15, hf = lane >> 4;
+        float* pw = p_s + warp * (G_MAX * PT);
+        for (int i = warp; i < np; i += ST::CW) {  // this warp's pages
+            const int s = i % ST::STAGES;
+            const uint32_t par = (i / ST::STAGES) & 1u;
+            const bool ok = __all_sync(0xffffffffu, mb_wait(&full[s], par, a.err_flag, &s_abort));
+            if (!ok) break;
+            const unsigned char* kt = ring + (size_t)s * ST::STAGE_BYTES;
+            const unsigned char* vt = kt + ST::TILE_BYTES;
+            const int p = p0 + i;
+            // ---- scores of the 16 tokens against all g heads: lane = (token, half of hd) ----
+            // packed f32x2 FMAs: even and odd elements of a chunk accumulate in the two halves of a pair
+            float2 sc2[G_MAX];
+#pragma unroll
+            for (int jj = 0; jj < G_MAX; ++jj) sc2[jj] = make_float2(0.f, 0.f);
+#pragma unroll 4
+            for (int c = 0; c < NCH; ++c) {
+                const float4 k4 = ld_chunk4<BF16>(kt, (((hf * NCH + c) << 4) + t) << 2);  // chunk-major K tile
+#pragma unroll
+                for (int jj = 0; jj < G_MAX; ++jj) {
+                    if (jj < g) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(q_s + jj * HD + (c * 2 + hf) * 4);
+                        sc2[jj] = __ffma2_rn(make_float2(q4.x, q4.y), make_float2(k4.x, k4.y), sc2[jj]);
+                        sc2[jj] = __ffma2_rn(make_float2(q4.z, q4.w), make_float2(k4.z, k4.w), sc2[jj]);
                     }
                 }
-                a.out[(size_t)m * a.heads * HD + (head0 + jj) * HD + d] = o / l;
+            }
+            float sc[G_MAX];
+#pragma unroll
+            for (int jj = 0; jj < G_MAX; ++jj) sc[jj] = sc2[jj].x + sc2[jj].y;
+            const bool valid = (p * PT + t) < kvlen;
+            float corr[G_MAX];
+#pragma unroll
+            for (int jj = 0; jj < G_MAX; ++jj) {
+                if (jj < g) {
+                    float sv = sc[jj] + __shfl_xor_sync(0xffffffffu, sc[jj], 16);
+                    sv = valid ? sv * a.scale : -INFINITY;
+                    float mx = sv;
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    const float m_new = fmaxf(run_m[jj], mx);
+                    const float pr = valid ? expf(sv - m_new) : 0.f;
+                    float ps = pr;
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                    corr[jj] = expf(run_m[jj] - m_new);  // exp(-inf) = 0 on the first page
+                    run_l[jj] = run_l[jj] * corr[jj] + ps;
+                    run_m[jj] = m_new;
+                    if (hf == 0) pw[jj * PT + t] = pr;
+                }
+            }
+            __syncwarp();
+            // ---- p . v: lane owns EPL output dims of every head; a V row is read once for all heads ----
+#pragma unroll
+            for (int jj = 0; jj < G_MAX; ++jj)
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[jj][e] *= (jj < g) ? corr[jj] : 1.f;
+#pragma unroll
+            for (int t4 = 0; t4 < PT; t4 += 4) {
+                float vv[4][EPL];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (BF16) {
+                        const uint16_t* vr = reinterpret_cast<const uint16_t*>(vt) + (t4 + u) * HD + lane * EPL;
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) vv[u][e] = bf16_bits_to_f32(vr[e]);
+                    } else {
+                        const float* vr = reinterpret_cast<const float*>(vt) + (t4 + u) * HD + lane * EPL;
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) vv[u][e] = vr[e];
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < G_MAX; ++jj) {
+                    if (jj < g) {
+                        const float4 p4 = *reinterpret_cast<const float4*>(pw + jj * PT + t4);  // broadcast
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) {
+                            acc[jj][e] = fmaf(p4.x, vv[0][e], acc[jj][e]);
+                            acc[jj][e] = fmaf(p4.y, vv[1][e], acc[jj][e]);
+                            acc[jj][e] = fmaf(p4.z, vv[2][e], acc[jj][e]);
+                            acc[jj][e] = fmaf(p4.w, vv[3][e], acc[jj][e]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mb_arrive(&empty[s]);  // the stage may be refilled
+        }
+    }
+    __syncthreads();  // every page consumed: the ring becomes the merge scratch
+    if (warp < ST::CW) {
+        // publish this warp's state: slot = warp, entry (warp * g + head)
+#pragma unroll
+        for (int jj = 0; jj < G_MAX; ++jj) {
+            if (jj < g) {
+                const int w = warp * g + jj;
+                if (lane == 0) {
+                    w_ml[w * 2 + 0] = run_m[jj];
+                    w_ml[w * 2 + 1] = run_l[jj];
+                }
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) w_acc[w * HD + lane * EPL + e] = acc[jj][e];
             }
         }
-        cluster_sync_all();
-        return;
     }
-    if (a.nsplit == 1) return;
+    __syncthreads();
+    merge_slots_and_write<HD, CL>(a, ST::CW, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, &s_last);
+}
 
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned int tk = atomicAdd(a.tickets + (m * a.kv_heads + kvh), 1u);
-        s_last = (tk == (unsigned int)(a.nsplit - 1));
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    for (int i = tid; i < g * HD; i += ATT_THREADS) {
-        const int jj = i / HD, d = i % HD;
-        const int head = head0 + jj;
-        const size_t base = ((size_t)m * a.heads + head) * a.nsplit;
-        float M = -INFINITY;
-        for (int s2 = 0; s2 < a.nsplit; ++s2) M = fmaxf(M, ld_cg_f32(a.part_ml + (base + s2) * 2));
-        float l = 0.f, o = 0.f;
-        for (int s2 = 0; s2 < a.nsplit; ++s2) {
-            const float ms = ld_cg_f32(a.part_ml + (base + s2) * 2);
-            if (ms > -INFINITY) {
-                const float sc = expf(ms - M);
-                l = fmaf(ld_cg_f32(a.part_ml + (base + s2) * 2 + 1), sc, l);
-                o = fmaf(ld_cg_f32(a.part_acc + (base + s2) * HD + d), sc, o);
-            }
-        }
-        a.out[(size_t)m * a.heads * HD + head * HD + d] = o / l;
-    }
-    if (tid == 0) a.tickets[m * a.kv_heads + kvh] = 0u;
+template <int HD, bool BF16>
+size_t stream_smem_bytes(int pages_per_cta) {
+    using ST = StTile<HD, BF16>;
+    return (size_t)ST::STAGES * ST::STAGE_BYTES + sizeof(float) * ((size_t)G_MAX * HD + ATT_WARPS * G_MAX * PT + G_MAX * HD + G_MAX * 2) + (size_t)pages_per_cta * 4 + 128;
 }
 
 template <int HD, bool BF16>
@@ -294,18 +564,27 @@ size_t smem_bytes(int g) {
 
 template <int HD, bool BF16, bool CL>
 cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
-    const size_t smem = smem_bytes<HD, BF16>(a.heads / a.kv_heads);
-    if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int g = a.heads / a.kv_heads;
+    const int pages_per_cta = (a.max_pages + a.nsplit - 1) / a.nsplit;
+    // long contexts: the bulk-copy ring; a slot layout needs ATT_WARPS / g >= 1 as in the kernel above
+    const bool stream = a.stream_pages > 0 && pages_per_cta >= ST_MIN_PAGES && pages_per_cta <= ST_MAX_PT;
+    const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta) : smem_bytes<HD, BF16>(g);
+    // the opt-in limit only ever grows: launches captured in a graph must stay valid after later calls
+    static size_t opted[2] = {40 * 1024, 40 * 1024};  // static shared memory counts against the 48 KB default too
+    if (smem > opted[stream ? 1 : 0]) {
+        cudaError_t e = stream ? cudaFuncSetAttribute(attn_stream_kernel<HD, BF16, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                               : cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
+        opted[stream ? 1 : 0] = smem;
     }
     if (CL && a.nsplit > 8) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaError_t e = stream ? cudaFuncSetAttribute(attn_stream_kernel<HD, BF16, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)
+                               : cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)a.nsplit, (unsigned)a.kv_heads, (unsigned)M);
-    cfg.blockDim = dim3(ATT_THREADS);
+    cfg.blockDim = dim3(stream ? ST_THREADS : ATT_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute at[2];
@@ -324,7 +603,7 @@ cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
     }
     cfg.attrs = at;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, BF16, CL>, a);
+    return stream ? cudaLaunchKernelEx(&cfg, attn_stream_kernel<HD, BF16, CL>, a) : cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, BF16, CL>, a);
 }
 
 template <int HD, bool BF16>

@@ -788,6 +788,8 @@ int hm_attn_decode_paged(const float* q, const void* k_pages, const void* v_page
     a.hd = hd;
     a.nsplit = attn_pick_nsplit(B, kv_heads, (longest + page_tokens - 1) / page_tokens, sm_count_of_current_device());
     a.scale = (float)(1.0 / std::sqrt((double)hd));
+    a.stream_pages = 1;
+    if (!sg.ok(get_wait_err(&a.err_flag))) return sg.finish(cudaSuccess);
     a.out = sg.out(out, (size_t)B * heads * hd);
     if (a.nsplit > 1) {
         const size_t acc_f = (size_t)B * heads * a.nsplit * hd, ml_f = (size_t)B * heads * a.nsplit * 2;

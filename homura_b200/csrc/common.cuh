@@ -111,6 +111,14 @@ __device__ __forceinline__ float warp_max(float v) {
 enum Prologue { PRO_PLAIN = 0, PRO_RMSNORM = 1 };
 enum Epilogue { EPI_STORE = 0, EPI_QKV_ROPE = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
 
+// Element offsets inside one [16 tokens][hd] page tile.  V tiles are row-major (token, dim).  K tiles
+// are chunk-major: the 4-element chunk c = d / 4 of every token is stored together,
+// K[c][token][d % 4], so the 16 tokens' copies of one chunk are 256 contiguous bytes: attention lanes
+// that own one token each read them without bank conflicts while the matching query chunk is a
+// broadcast.  The tile is still one contiguous block of the pool (one bulk copy).
+__host__ __device__ __forceinline__ int k_tile_off(int t, int d) { return ((((d >> 2) << 4) + t) << 2) | (d & 3); }
+__host__ __device__ __forceinline__ int v_tile_off(int t, int d, int hd) { return t * hd + d; }
+
 struct KvDesc {
     void* k_pool;            // this layer's K pages [n_pages][kv_heads][page_tokens][hd]
     void* v_pool;
@@ -166,6 +174,8 @@ struct GemvArgs {
 struct AttnArgs {
     const void* pf_ptr;  // optional: weights of a later kernel to pull into the L2
     unsigned long long pf_bytes;
+    int stream_pages;    // > 0: long contexts may use the bulk-copy ring variant (pages per CTA decided from max_pages / nsplit)
+    int* err_flag;       // raised to 2 when a bounded wait of that variant runs out
     const float* q;       // [M][heads*hd]
     const void* k_pool;
     const void* v_pool;

@@ -527,11 +527,14 @@ __device__ void phase_attention(Ctx& c, int layer, int npages, int ppc, int nc) 
                 const int pc = c.tid + u * CONSUMERS;
                 if (pc < pieces) {
                     const int e = pc * per16, tt = e / hd, d = e - tt * hd;
-                    float* ko = kt + tt * KLD + d;
                     float* vo = vt + tt * hd + d;
+                    // K pages are chunk-major (k_tile_off): a 16-byte piece is one 4-element chunk of one
+                    // token (f32) or of two neighbouring tokens (bf16)
+                    const int kc = e >> 6, ktok = (e >> 2) & 15;
+                    float* ko = kt + ktok * KLD + kc * 4;
                     if (a.kv_bf16) {
                         ko[0] = bf16_lo(kq[u].x); ko[1] = bf16_hi(kq[u].x); ko[2] = bf16_lo(kq[u].y); ko[3] = bf16_hi(kq[u].y);
-                        ko[4] = bf16_lo(kq[u].z); ko[5] = bf16_hi(kq[u].z); ko[6] = bf16_lo(kq[u].w); ko[7] = bf16_hi(kq[u].w);
+                        ko[KLD + 0] = bf16_lo(kq[u].z); ko[KLD + 1] = bf16_hi(kq[u].z); ko[KLD + 2] = bf16_lo(kq[u].w); ko[KLD + 3] = bf16_hi(kq[u].w);
                         vo[0] = bf16_lo(vq[u].x); vo[1] = bf16_hi(vq[u].x); vo[2] = bf16_lo(vq[u].y); vo[3] = bf16_hi(vq[u].y);
                         vo[4] = bf16_lo(vq[u].z); vo[5] = bf16_hi(vq[u].z); vo[6] = bf16_lo(vq[u].w); vo[7] = bf16_hi(vq[u].w);
                     } else {
@@ -599,14 +602,15 @@ __device__ void phase_attention(Ctx& c, int layer, int npages, int ppc, int nc) 
         }
         consumer_sync();
         if (pnew >= p0 && pnew < p1) {  // append to the cache (KvCache::append_*, src/runtime.rs:521-570)
-            const size_t off = (((size_t)pt[pnew] * a.kvh + kh) * PTK + (pos % PTK)) * hd;
+            const size_t tile = ((size_t)pt[pnew] * a.kvh + kh) * PTK * hd;
             for (int d = c.tid; d < hd; d += CONSUMERS) {
+                const size_t ko = tile + k_tile_off(pos % PTK, d), vo = tile + v_tile_off(pos % PTK, d, hd);
                 if (a.kv_bf16) {
-                    reinterpret_cast<uint16_t*>(w.k_pool)[off + d] = f32_to_bf16_rne(kn[d]);
-                    reinterpret_cast<uint16_t*>(w.v_pool)[off + d] = f32_to_bf16_rne(vn[d]);
+                    reinterpret_cast<uint16_t*>(w.k_pool)[ko] = f32_to_bf16_rne(kn[d]);
+                    reinterpret_cast<uint16_t*>(w.v_pool)[vo] = f32_to_bf16_rne(vn[d]);
                 } else {
-                    reinterpret_cast<float*>(w.k_pool)[off + d] = kn[d];
-                    reinterpret_cast<float*>(w.v_pool)[off + d] = vn[d];
+                    reinterpret_cast<float*>(w.k_pool)[ko] = kn[d];
+                    reinterpret_cast<float*>(w.v_pool)[vo] = vn[d];
                 }
             }
         }

@@ -448,7 +448,10 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     if (rc) return rc;
     // attention split scratch
     // sized for the decode step (one row per sequence)
-    att_nsplit_ = use_clusters_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 8)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
+    // up to 1024 tokens of capacity the splits of a (row, KV head) are one cluster of at most 8 CTAs;
+    // longer caches need more CTAs than a cluster holds and merge through global scratch + ticket
+    att_cluster_ = use_clusters_ && max_pages_ <= 64;
+    att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 8)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
     HM_CUDA(cudaMalloc(&att_acc_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * hd_ * 4));
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
     HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));
@@ -873,7 +876,9 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.kv_heads = kvh_;
         at.hd = hd_;
         at.nsplit = std::min(att_nsplit_, attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));  // fewer splits when the rows alone fill the SMs
-        at.cluster = use_clusters_ ? 1 : 0;
+        at.cluster = att_cluster_ ? 1 : 0;
+        at.stream_pages = 1;
+        at.err_flag = err_flag_;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
         at.out = attn_;
         at.part_acc = att_acc_;

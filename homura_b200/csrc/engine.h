@@ -117,6 +117,7 @@ class Engine {
     float *att_acc_ = nullptr, *att_ml_ = nullptr;
     unsigned int* att_tickets_ = nullptr;
     int att_nsplit_ = 1;
+    bool att_cluster_ = true;
     int* err_flag_ = nullptr;
 
     // KV cache

@@ -24,6 +24,7 @@
 // staging (f32 -> 3 x bf16, swizzled) and epilogue.  Every mbarrier wait is bounded.
 #include "common.cuh"
 #include "gemm_tc.h"
+#include "mbarrier.cuh"
 
 namespace hm {
 namespace {
@@ -35,35 +36,6 @@ constexpr int MR = 64;   // activation rows (MMA N = MR * terms)
 constexpr int TERMS = 3;
 constexpr int W_TILE = BM * BK * 2;          // 16 KB
 constexpr int NSTG = 8;  // barrier slots; stages in use depend on the row padding
-constexpr unsigned long long TC_SPIN = 4000000ULL;
-
-__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n) : "memory"); }
-__device__ __forceinline__ void mb_arrive(uint64_t* b) { asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(s32(b)) : "memory"); }
-__device__ __forceinline__ void mb_expect_tx(uint64_t* b, uint32_t bytes) {
-    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(s32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait; on overrun raises *err and returns false (callers skip the work that needed the data).
-__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* err, volatile int* abort_flag) {
-    unsigned long long it = 0;
-    while (!mb_try(b, parity)) {
-        if (*abort_flag) return false;
-        if (++it > TC_SPIN) {
-            *abort_flag = 1;
-            if (err) atomicExch(err, 2);
-            return false;
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
-}
 
 // Shared-memory matrix descriptor, K-major operand with 128-byte swizzle: rows of 128 B, groups of
 // 8 rows 1024 B apart (stride byte offset), descriptor version 1, layout type SWIZZLE_128B (2).
@@ -253,7 +225,8 @@ __device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, in
                 const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
                 const int seq = a.row_seq ? a.row_seq[m] : m;
                 const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
-                const size_t off = (((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens + (pos % a.kv.page_tokens)) * hd + d;
+                const int tok = pos % a.kv.page_tokens;
+                const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd));
                 void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
                 if (a.kv.bf16)
                     reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(v);

@@ -337,7 +337,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
                 const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
                 const int seq = a.row_seq ? a.row_seq[m] : m;
                 const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
-                const size_t off = (((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens + (pos % a.kv.page_tokens)) * hd + d;
+                const int tok = pos % a.kv.page_tokens;
+                const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd));
                 void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
                 if (a.kv.bf16)
                     reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(v);

@@ -212,13 +212,14 @@ __global__ void kv_write_rows_kernel(KvDesc kv, int seq, int pos0, const float* 
         const int h = (int)(i / ((size_t)kv.hd * n_new));
         const int pos = pos0 + s;
         const int page = kv.page_table[(size_t)seq * kv.max_pages + pos / kv.page_tokens];
-        const size_t off = (((size_t)page * kv.kv_heads + h) * kv.page_tokens + pos % kv.page_tokens) * kv.hd + d;
+        const size_t tile = ((size_t)page * kv.kv_heads + h) * kv.page_tokens * kv.hd;
+        const size_t ko = tile + k_tile_off(pos % kv.page_tokens, d), vo = tile + v_tile_off(pos % kv.page_tokens, d, kv.hd);
         if (kv.bf16) {
-            if (k_rows) reinterpret_cast<uint16_t*>(kv.k_pool)[off] = f32_to_bf16_rne(k_rows[i]);
-            if (v_rows) reinterpret_cast<uint16_t*>(kv.v_pool)[off] = f32_to_bf16_rne(v_rows[i]);
+            if (k_rows) reinterpret_cast<uint16_t*>(kv.k_pool)[ko] = f32_to_bf16_rne(k_rows[i]);
+            if (v_rows) reinterpret_cast<uint16_t*>(kv.v_pool)[vo] = f32_to_bf16_rne(v_rows[i]);
         } else {
-            if (k_rows) reinterpret_cast<float*>(kv.k_pool)[off] = k_rows[i];
-            if (v_rows) reinterpret_cast<float*>(kv.v_pool)[off] = v_rows[i];
+            if (k_rows) reinterpret_cast<float*>(kv.k_pool)[ko] = k_rows[i];
+            if (v_rows) reinterpret_cast<float*>(kv.v_pool)[vo] = v_rows[i];
         }
     }
 }
@@ -230,13 +231,14 @@ __global__ void kv_read_rows_kernel(KvDesc kv, int seq, int len, float* k_out, f
         const int pos = (int)((i / kv.hd) % len);
         const int h = (int)(i / ((size_t)kv.hd * len));
         const int page = kv.page_table[(size_t)seq * kv.max_pages + pos / kv.page_tokens];
-        const size_t off = (((size_t)page * kv.kv_heads + h) * kv.page_tokens + pos % kv.page_tokens) * kv.hd + d;
+        const size_t tile = ((size_t)page * kv.kv_heads + h) * kv.page_tokens * kv.hd;
+        const size_t ko = tile + k_tile_off(pos % kv.page_tokens, d), vo = tile + v_tile_off(pos % kv.page_tokens, d, kv.hd);
         if (kv.bf16) {
-            k_out[i] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(kv.k_pool)[off]);
-            v_out[i] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(kv.v_pool)[off]);
+            k_out[i] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(kv.k_pool)[ko]);
+            v_out[i] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(kv.v_pool)[vo]);
         } else {
-            k_out[i] = reinterpret_cast<const float*>(kv.k_pool)[off];
-            v_out[i] = reinterpret_cast<const float*>(kv.v_pool)[off];
+            k_out[i] = reinterpret_cast<const float*>(kv.k_pool)[ko];
+            v_out[i] = reinterpret_cast<const float*>(kv.v_pool)[vo];
         }
     }
 }
@@ -296,12 +298,13 @@ __global__ void post_qkv_kernel(const float* qkv, int M, int heads, int kv_heads
         const int kvh = is_k ? h - heads : h - heads - kv_heads;
         const int seq = row_seq ? row_seq[m] : m;
         const int page = kv.page_table[(size_t)seq * kv.max_pages + pos / kv.page_tokens];
-        const size_t off = (((size_t)page * kv.kv_heads + kvh) * kv.page_tokens + pos % kv.page_tokens) * hd;
+        const size_t tile = ((size_t)page * kv.kv_heads + kvh) * kv.page_tokens * hd;
         void* pool = is_k ? kv.k_pool : kv.v_pool;
         for (int e = 0; e < per; ++e) {
             const int d = lane + 32 * e;
-            if (kv.bf16) reinterpret_cast<uint16_t*>(pool)[off + d] = f32_to_bf16_rne(val[e]);
-            else reinterpret_cast<float*>(pool)[off + d] = val[e];
+            const size_t off = tile + (is_k ? k_tile_off(pos % kv.page_tokens, d) : v_tile_off(pos % kv.page_tokens, d, hd));
+            if (kv.bf16) reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(val[e]);
+            else reinterpret_cast<float*>(pool)[off] = val[e];
         }
     }
 }

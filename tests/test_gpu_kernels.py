@@ -150,7 +150,8 @@ def _paged(rng, B, kvh, hd, lens, bf16, hm):
         ks.append(k)
         vs.append(v)
     kd, vd = hm.DeviceBuffer(kpool.nbytes), hm.DeviceBuffer(vpool.nbytes)
-    kd.upload(kpool)
+    # K tiles are stored chunk-major inside a page: [hd/4][16 tokens][4]; V tiles are [16 tokens][hd]
+    kd.upload(np.ascontiguousarray(kpool.reshape(n_pages, kvh, PT, hd // 4, 4).transpose(0, 1, 3, 2, 4)))
     vd.upload(vpool)
     return kd, vd, perm, max_pages, ks, vs
 
@@ -168,6 +169,25 @@ def test_attention_matches_oracle(hm, oracle, heads, kvh, hd, bf16):
         want = oracle.gqa_attention(q[b : b + 1], ks[b], vs[b], np.zeros((1, L), np.float32), heads, kvh)
         # online softmax vs two-pass softmax: same math, different rounding order
         np.testing.assert_allclose(got[b], want[0], rtol=0, atol=3e-6 * max(1.0, float(np.abs(want).max())))
+
+
+@pytest.mark.parametrize("heads,kvh,hd", [(14, 2, 64), (12, 2, 128), (16, 8, 128), (4, 4, 64), (32, 4, 64), (8, 1, 64)])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_attention_streaming_variant_matches_oracle(hm, oracle, heads, kvh, hd, bf16):
+    # contexts of thousands of tokens and enough sequences that every CTA owns >= 8 pages: the
+    # bulk-copy ring kernel; ragged lengths leave some CTAs with a partial or empty page range
+    rng = np.random.default_rng(heads * 5 + hd + 3 * bf16)
+    lens = [4096, 2500, 4000, 17, 3333, 4096, 1, 2049]
+    B = len(lens)
+    kd, vd, perm, max_pages, ks, vs = _paged(rng, B, kvh, hd, lens, bf16, hm)
+    q = rng.standard_normal((B, heads, hd), dtype=np.float32)
+    got = hm.attn_decode_paged(q, kd, vd, hm.DType.BF16 if bf16 else hm.DType.F32, perm, lens, heads, kvh, hd, max_pages)
+    for b, L in enumerate(lens):
+        want = oracle.gqa_attention(q[b : b + 1], ks[b], vs[b], np.zeros((1, L), np.float32), heads, kvh)
+        np.testing.assert_allclose(got[b], want[0], rtol=0, atol=3e-6 * max(1.0, float(np.abs(want).max())))
+    # deterministic: same bits on a second launch
+    again = hm.attn_decode_paged(q, kd, vd, hm.DType.BF16 if bf16 else hm.DType.F32, perm, lens, heads, kvh, hd, max_pages)
+    np.testing.assert_array_equal(got, again)
 
 
 def test_attention_long_context_property(hm):
