@@ -32,6 +32,7 @@ constexpr int ATT_WARPS = 8;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int G_MAX = 8;   // query heads per KV head handled by one CTA
 constexpr int MAXP = 4;    // 16-byte pieces of K (and of V) a thread may hold in flight
+constexpr int ST_MIN_PAGES = 8;  // pages per CTA from which the streaming variant is used
 
 template <int HD, bool BF16>
 struct Tile {
@@ -331,7 +332,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
 // one-warp-per-head, which is what bounds the kernel above on long contexts.  Used when a CTA has at
 // least ST_MIN_PAGES pages to read.
 constexpr int ST_THREADS = ATT_THREADS + 32;
-constexpr int ST_MIN_PAGES = 8;
 constexpr int ST_MAX_STAGES = 16;
 constexpr int ST_RING_BYTES = 64 * 1024;  // per CTA; two CTAs per SM keep 128 KB of pages in flight
 constexpr int ST_MAX_PT = 4096;  // page-table entries of one CTA staged in shared memory
@@ -619,12 +619,27 @@ cudaError_t launch_t(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
 
 // Enough (row, KV head, split) CTAs to cover the SMs about twice, at least two pages each.
 int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
-    int n = (2 * sm_count + M * kv_heads - 1) / (M * kv_heads);
-    const int by_pages = (max_pages + 1) / 2;
-    if (n > by_pages) n = by_pages;
-    if (n > 64) n = 64;
-    if (n < 1) n = 1;
-    return n;
+    // Splits per (row, KV head): minimise waves x (fixed cost per CTA + pages per CTA) + merge cost.
+    // Units are "pages streamed by one CTA": the fixed cost (launch, query and page-table loads) is
+    // worth about eight pages, merging one more partial about half a page.  The streaming variant
+    // (>= ST_MIN_PAGES pages per CTA) keeps two CTAs per SM resident, the short-context kernel four.
+    const long pairs = (long)M * kv_heads;
+    int cap = (max_pages + 1) / 2;  // at least two pages per split
+    if (cap > sm_count) cap = sm_count;
+    if (cap < 1) cap = 1;
+    int best = 1;
+    long best_cost = -1;
+    for (int n = 1; n <= cap; ++n) {
+        const int ppc = (max_pages + n - 1) / n;
+        const long slots = (ppc >= ST_MIN_PAGES ? 2L : 4L) * sm_count;
+        const long waves = (pairs * n + slots - 1) / slots;
+        const long cost = 2 * waves * (8 + ppc) + n;  // doubled so that the half page per partial stays an integer
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = n;
+        }
+    }
+    return best;
 }
 
 // Cluster variant: the splits of a (row, KV head) form one cluster; about two pages per CTA when

@@ -452,6 +452,10 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     // longer caches need more CTAs than a cluster holds and merge through global scratch + ticket
     att_cluster_ = use_clusters_ && max_pages_ <= 64;
     att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 8)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
+    if (const char* ns = std::getenv("HM_ATT_NSPLIT")) {  // tuning knob: CTAs per (row, KV head)
+        const int v = std::atoi(ns);
+        if (v >= 1 && v <= (att_cluster_ ? 8 : sm_count_)) att_nsplit_ = v;
+    }
     HM_CUDA(cudaMalloc(&att_acc_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * hd_ * 4));
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
     HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));
@@ -875,7 +879,9 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.heads = heads_;
         at.kv_heads = kvh_;
         at.hd = hd_;
-        at.nsplit = std::min(att_nsplit_, attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));  // fewer splits when the rows alone fill the SMs
+        // fewer splits when the rows alone fill the SMs: about two CTAs per SM on the cluster path, the
+        // cost model of the long-context path otherwise
+        at.nsplit = std::min(att_nsplit_, att_cluster_ ? std::max(1, (2 * sm_count_ + M * kvh_ - 1) / (M * kvh_)) : attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));
         at.cluster = att_cluster_ ? 1 : 0;
         at.stream_pages = 1;
         at.err_flag = err_flag_;
