@@ -72,7 +72,8 @@ def emit(obj):
         os.write(_OUT_FD, data)
 
 
-# name -> (config attribute in homura_b200.synth, checkpoint format, sequences per GPU, description)
+# name -> (config attribute in homura_b200.synth, checkpoint format, sequences per GPU, description);
+# prompt lengths of the workloads: PROMPTS below
 WORKLOADS = {
     "qwen25-05b": ("QWEN25_05B", "bf16", 1, "Qwen2.5-0.5B-architecture decoder (24 layers, hidden 896, 14/2 heads, hd 64, SwiGLU 4864, vocab 151936, tied, QKV bias), batch 1 per GPU"),
     "tinyllama-q8_0": ("TINYLLAMA_11B", "q8_0", 1, "TinyLlama-1.1B-architecture decoder (22 layers, hidden 2048, 32/4 heads, hd 64, SwiGLU 5632, vocab 32000), GGUF Q8_0, batch 1 per GPU"),
@@ -80,6 +81,7 @@ WORKLOADS = {
     "qwen25-15b-x64": ("QWEN25_15B", "bf16", 64, "Qwen2.5-1.5B-architecture decoder (28 layers, hidden 1536, 12/2 heads, hd 128, SwiGLU 8960, vocab 151936, tied, QKV bias), 64 sequences per GPU"),
 }
 HEADLINE = "qwen25-05b"
+PROMPTS = {"qwen25-05b": 128, "tinyllama-q8_0": 256, "tinyllama-q4_0": 256, "qwen25-15b-x64": 512}
 
 
 def model_dir(cfg, seed, rank, world, name=HEADLINE, fmt="bf16"):
@@ -212,7 +214,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kv-dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode steps (128 = the headline workload)")
+    ap.add_argument("--prompt-len", type=int, default=None, help="prompt tokens before the timed decode steps (default: the workload's own, 128 for the headline)")
     ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="default: the headline workload; the others are the remaining measured configurations")
     ap.add_argument("--device-only", action="store_true", help="only the device-timed region: skips the end-to-end loop, the per-kernel pass and the CPU baseline (for profiler runs)")
     args = ap.parse_args()
@@ -233,7 +235,7 @@ def main():
     t0 = time.time()
     m = hm.HfModel.load_with_dtype(d, hm.DType.BF16, device=local) if fmt == "bf16" else hm.HfModel.load_gguf(d, device=local)
     kv_dtype = hm.DType.F32 if args.kv_dtype == "f32" else hm.DType.BF16
-    PL = args.prompt_len
+    PL = args.prompt_len if args.prompt_len is not None else PROMPTS[args.workload]
     max_seq = PL + 2 * (W + K) + 24
     if max_seq > cfg.max_position_embeddings:
         raise SystemExit(f"--steps/--warmup need {max_seq} positions; the checkpoint has {cfg.max_position_embeddings}")

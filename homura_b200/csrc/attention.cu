@@ -32,7 +32,7 @@ constexpr int ATT_WARPS = 8;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int G_MAX = 8;   // query heads per KV head handled by one CTA
 constexpr int MAXP = 4;    // 16-byte pieces of K (and of V) a thread may hold in flight
-constexpr int ST_MIN_PAGES = 8;  // pages per CTA from which the streaming variant is used
+constexpr int ST_MIN_PAGES = 16;  // pages per CTA from which the streaming variant is used
 
 template <int HD, bool BF16>
 struct Tile {
@@ -244,15 +244,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
                 const int slot = idx / TL::PIECES, piece = idx % TL::PIECES;
                 const int e = piece * TL::PER16, t = e / HD, d = e % HD;
                 float* base = tiles + slot * TL::SLOT_FLOATS;
-                // K pages are chunk-major (k_tile_off): a piece is one 4-element chunk of one token
-                // (f32) or of two neighbouring tokens (bf16); the shared-memory tile stays [token][KLD]
-                float* ko = base + ((e >> 2) & 15) * TL::KLD + (e >> 6) * 4;
-                if (BF16) {
-                    ko[0] = bf16_lo(kreg[i].x); ko[1] = bf16_hi(kreg[i].x); ko[2] = bf16_lo(kreg[i].y); ko[3] = bf16_hi(kreg[i].y);
-                    ko[TL::KLD + 0] = bf16_lo(kreg[i].z); ko[TL::KLD + 1] = bf16_hi(kreg[i].z); ko[TL::KLD + 2] = bf16_lo(kreg[i].w); ko[TL::KLD + 3] = bf16_hi(kreg[i].w);
-                } else {
-                    unpack_store<false>(ko, kreg[i]);
-                }
+                // K pages are chunk-major (k_tile_off) and stay so in shared memory: a straight copy
+                unpack_store<BF16>(base + e, kreg[i]);
                 unpack_store<BF16>(base + PT * TL::KLD + t * HD + d, vreg[i]);
             }
         }
@@ -278,12 +271,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
         if (active && p < p1) {
             const float* kt = tiles + sub * TL::SLOT_FLOATS;
             const float* vt = kt + PT * TL::KLD;
-            const float* kr = kt + t * TL::KLD + hf * (HD / 2);
+            const float* kr = kt + ((hf * (HD / 8) * PT + t) << 2);  // chunk-major: chunk c of token t at (c * 16 + t) * 4
             const float* qr = q_s + j * HD + hf * (HD / 2);
             float s = 0.f;
 #pragma unroll
             for (int dc = 0; dc < HD / 2; dc += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(kr + dc);
+                const float4 k4 = *reinterpret_cast<const float4*>(kr + dc * PT);
                 const float4 q4 = *reinterpret_cast<const float4*>(qr + dc);
                 s = fmaf(q4.x, k4.x, s);
                 s = fmaf(q4.y, k4.y, s);
@@ -341,7 +334,10 @@ struct StTile {
     static constexpr int ESZ = BF16 ? 2 : 4;
     static constexpr int TILE_BYTES = PT * HD * ESZ;  // one K or V tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int STAGES = (ST_RING_BYTES / STAGE_BYTES) < ST_MAX_STAGES ? (ST_RING_BYTES / STAGE_BYTES) : ST_MAX_STAGES;
+    // 64 KB of pages per CTA (two CTAs per SM); f32 pages of head_dim 128 get 128 KB so that eight warps
+    // still have a stage each
+    static constexpr int RING = STAGE_BYTES * ATT_WARPS > ST_RING_BYTES ? STAGE_BYTES * ATT_WARPS : ST_RING_BYTES;
+    static constexpr int STAGES = (RING / STAGE_BYTES) < ST_MAX_STAGES ? (RING / STAGE_BYTES) : ST_MAX_STAGES;
     // Consumer warps that take pages round-robin.  Every phase of a stage must be consumed by the same
     // warp (a parity wait cannot tell phase k from phase k + 2), so the stage count is a multiple of it.
     static constexpr int CW = STAGES < ATT_WARPS ? STAGES : ATT_WARPS;
@@ -623,6 +619,7 @@ int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
     // Units are "pages streamed by one CTA": the fixed cost (launch, query and page-table loads) is
     // worth about eight pages, merging one more partial about half a page.  The streaming variant
     // (>= ST_MIN_PAGES pages per CTA) keeps two CTAs per SM resident, the short-context kernel four.
+    // max_pages is the capacity the launch is sized for (a captured graph cannot follow the length).
     const long pairs = (long)M * kv_heads;
     int cap = (max_pages + 1) / 2;  // at least two pages per split
     if (cap > sm_count) cap = sm_count;
@@ -631,9 +628,12 @@ int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
     long best_cost = -1;
     for (int n = 1; n <= cap; ++n) {
         const int ppc = (max_pages + n - 1) / n;
-        const long slots = (ppc >= ST_MIN_PAGES ? 2L : 4L) * sm_count;
+        const bool streaming = ppc >= ST_MIN_PAGES;
+        const long slots = (streaming ? 2L : 4L) * sm_count;
         const long waves = (pairs * n + slots - 1) / slots;
-        const long cost = 2 * waves * (8 + ppc) + n;  // doubled so that the half page per partial stays an integer
+        // doubled so that the half page per partial stays an integer; a page costs the short-context
+        // kernel about twice what it costs the streaming one (every query head re-reads the tile)
+        const long cost = 2 * waves * (8 + (streaming ? ppc : 2 * ppc)) + n;
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best = n;

@@ -879,8 +879,8 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.heads = heads_;
         at.kv_heads = kvh_;
         at.hd = hd_;
-        // fewer splits when the rows alone fill the SMs: about two CTAs per SM on the cluster path, the
-        // cost model of the long-context path otherwise
+        // fewer splits when the rows alone fill the SMs: about two CTAs per SM on the cluster path (caches
+        // of up to 1024 tokens), the kernel's cost model on the long-context path
         at.nsplit = std::min(att_nsplit_, att_cluster_ ? std::max(1, (2 * sm_count_ + M * kvh_ - 1) / (M * kvh_)) : attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));
         at.cluster = att_cluster_ ? 1 : 0;
         at.stream_pages = 1;

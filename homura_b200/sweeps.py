@@ -3,7 +3,8 @@
 Each line of output is one JSON record.  Timing is by CUDA events around replays of a CUDA graph
 that holds one rotation of launches; the weights (or KV pages) of consecutive launches come from a rotation of copies
 larger than the L2 cache, so every launch streams from HBM.  Shapes are the projection and attention
-shapes of Qwen2.5-0.5B / 1.5B / Qwen3-0.6B (src/hf/config.rs:11-38 gives the fields they come from).
+shapes of Qwen2.5-0.5B / 1.5B / Qwen3-0.6B (src/hf/config.rs:11-38 gives the fields they come from); the
+attention sweep defaults to the Qwen3-0.6B geometry (16 query / 8 KV heads, head_dim 128) on bf16 pages.
 """
 from __future__ import annotations
 
@@ -112,8 +113,12 @@ def projections(ms: list[int], peak_gbs: float, shapes=None, profile_launches: i
         yb.free()
 
 
-def attention(kv_lens: list[int], batches: list[int], kv_dtype: str, peak_gbs: float):
-    heads, kvh, hd, page = 14, 2, 64, 16  # Qwen2.5-0.5B geometry
+ATTENTION_GEOMETRY = {"qwen3-0.6b": (16, 8, 128), "qwen2.5-0.5b": (14, 2, 64), "qwen2.5-1.5b": (12, 2, 128), "tinyllama-1.1b": (32, 4, 64)}
+
+
+def attention(kv_lens: list[int], batches: list[int], kv_dtype: str, peak_gbs: float, geometry: str = "qwen3-0.6b"):
+    heads, kvh, hd = ATTENTION_GEOMETRY[geometry]  # query heads, KV heads, head_dim
+    page = 16
     rng = np.random.default_rng(6)
     dt = hm.DType.F32 if kv_dtype == "f32" else hm.DType.BF16
     esz = 4 if kv_dtype == "f32" else 2
@@ -159,7 +164,7 @@ def attention(kv_lens: list[int], batches: list[int], kv_dtype: str, peak_gbs: f
             us, iters, mode = _time_launches(fn, n_rot, target_ms=20.0)
             alg = 2 * B * L * kvh * hd * esz
             gbs = alg / us / 1e3
-            print(json.dumps({"sweep": "attention", "kv_dtype": kv_dtype, "kv_len": L, "batch": B, "us": round(us, 2), "GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak_gbs, 3), "launches": iters, "rotation": n_rot, "timing": mode}), flush=True)
+            print(json.dumps({"sweep": "attention", "geometry": geometry, "kv_dtype": kv_dtype, "kv_len": L, "batch": B, "us": round(us, 2), "GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak_gbs, 3), "launches": iters, "rotation": n_rot, "timing": mode}), flush=True)
             for b in (kb, vb, pt, kl, q, out):
                 b.free()
 
@@ -170,7 +175,8 @@ def main(argv=None):
     ap.add_argument("--m", type=int, nargs="*", default=[1, 4, 16, 64])
     ap.add_argument("--kv-len", type=int, nargs="*", default=[512, 4096, 32768])
     ap.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64])
-    ap.add_argument("--kv-dtype", choices=["f32", "bf16"], default="f32")
+    ap.add_argument("--kv-dtype", choices=["f32", "bf16"], default="bf16")
+    ap.add_argument("--geometry", choices=sorted(ATTENTION_GEOMETRY), default="qwen3-0.6b", help="attention: query heads / KV heads / head_dim of the named architecture")
     ap.add_argument("--shape", action="append", default=None, help="K,N of a projection; repeatable; default: the built-in shapes")
     ap.add_argument("--profile-launches", type=int, default=0, help="projections: issue this many plain launches per case and exit (for ncu)")
     ap.add_argument("--hbm-peak-gbs", type=float, default=6545.6, help="copy bandwidth to report fractions against")
@@ -179,7 +185,7 @@ def main(argv=None):
         shapes = [tuple(int(v) for v in sh.split(",")) for sh in a.shape] if a.shape else None
         projections(a.m, a.hbm_peak_gbs, shapes, a.profile_launches)
     else:
-        attention(a.kv_len, a.batch, a.kv_dtype, a.hbm_peak_gbs)
+        attention(a.kv_len, a.batch, a.kv_dtype, a.hbm_peak_gbs, a.geometry)
     return 0
 
 
