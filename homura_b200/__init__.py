@@ -39,6 +39,8 @@ class DType(enum.IntEnum):
     I64 = 5
     I32 = 6
     U8 = 7
+    Q4_K = 8
+    Q6_K = 9
 
 
 class HomuraError(RuntimeError):
@@ -548,8 +550,9 @@ def gemv_quant(x, blocks, dtype: DType, N: int):
 def dequant(blocks, dtype: DType) -> np.ndarray:
     lib = load_library()
     b = np.ascontiguousarray(blocks, dtype=np.uint8)
-    nb = b.size // (34 if dtype == DType.Q8_0 else 18)
-    out = np.empty(nb * 32, np.float32)
+    bsz, vals = {DType.Q8_0: (34, 32), DType.Q4_0: (18, 32), DType.Q4_K: (144, 256), DType.Q6_K: (210, 256)}[DType(dtype)]
+    nb = b.size // bsz
+    out = np.empty(nb * vals, np.float32)
     _check(lib.hm_dequant(_ptr(b), int(dtype), nb, _ptr(out), None))
     return out
 

@@ -10,6 +10,7 @@
 
 #include "engine.h"
 #include "gemm_tc.h"
+#include "kquant.h"
 #include "loaders.h"
 
 using namespace hm;
@@ -676,21 +677,48 @@ int hm_pack_bf16_tc(const void* w_kn, int K, int N, void* dst, void* stream) {
 
 int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, int N, float* y, void* stream) {
     if (!x || !blocks || !y || M < 1 || M > 8 || K < 32 || N < 1) return gfail(HM_ERR_INVALID, "hm_gemv_quant: bad arguments (1 <= M <= 8)");
-    if (dtype != HM_Q8_0 && dtype != HM_Q4_0) return gfail(HM_ERR_UNSUPPORTED, "hm_gemv_quant: dtype must be HM_Q8_0 or HM_Q4_0");
-    if (K % 32 != 0) return gfail(HM_ERR_INVALID, "hm_gemv_quant: K must be a multiple of 32");
+    const bool kq = dtype == HM_Q4_K || dtype == HM_Q6_K;
+    if (dtype != HM_Q8_0 && dtype != HM_Q4_0 && !kq) return gfail(HM_ERR_UNSUPPORTED, "hm_gemv_quant: dtype must be HM_Q8_0, HM_Q4_0, HM_Q4_K or HM_Q6_K");
+    if (K % (kq ? 256 : 32) != 0) return gfail(HM_ERR_INVALID, "hm_gemv_quant: K must be a multiple of the block size (32, or 256 for the K-quants)");
     NEED_DEVICE();
     cudaStream_t st = (cudaStream_t)stream;
     Staging sg(st);
+    const int mp = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
+    float* xp = (float*)sg.scratch((size_t)mp * K * 4, true);
+    float* yd = sg.out(y, (size_t)M * N);
+    if (!xp || !yd) return sg.finish(cudaErrorMemoryAllocation);
+    sg.ok(cudaMemcpyAsync(xp, x, (size_t)M * K * 4, cudaMemcpyDefault, st));
+    if (kq) {
+        const size_t nsb = (size_t)N * (K / 256);
+        const uint8_t* bd = sg.in((const uint8_t*)blocks, nsb * (dtype == HM_Q4_K ? 144 : 210));
+        uint8_t* data = (uint8_t*)sg.scratch(kquant_data_bytes(K, N), true);
+        uint8_t* types = (uint8_t*)sg.scratch(kquant_tiles(N), true);
+        if (!bd || !data || !types) return sg.finish(cudaErrorMemoryAllocation);
+        cudaError_t ce = launch_kquant_split(bd, N, K, dtype == HM_Q6_K, 0, -1, data, types, st);
+        if (ce == cudaSuccess) {
+            KQuantArgs a{};
+            a.data = data;
+            a.tile_type = types;
+            a.K = K;
+            a.N = N;
+            a.m_valid = M;
+            a.act_quant = 1;
+            a.x = xp;
+            a.ldx = K;
+            a.pro = PRO_PLAIN;
+            a.epi = EPI_STORE;
+            a.y = yd;
+            a.ldy = N;
+            ce = launch_gemv_kquant(a, mp, sm_count_of_current_device(), st, false);
+        }
+        return sg.finish(ce);
+    }
     const int q4 = dtype == HM_Q4_0;
     const size_t nb = (size_t)N * (K / 32);
     const uint8_t* bd = sg.in((const uint8_t*)blocks, nb * (q4 ? 18 : 34));
     uint16_t* scales = (uint16_t*)sg.scratch(quant_scale_elems(K, N) * 2, true);
     uint8_t* codes = (uint8_t*)sg.scratch(quant_code_bytes(K, N, q4), true);
-    const int mp = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-    float* xp = (float*)sg.scratch((size_t)mp * K * 4, true);
-    float* yd = sg.out(y, (size_t)M * N);
-    if (!bd || !scales || !codes || !xp || !yd) return sg.finish(cudaErrorMemoryAllocation);
-    sg.ok(cudaMemcpyAsync(xp, x, (size_t)M * K * 4, cudaMemcpyDefault, st));
+    if (!bd || !scales || !codes) return sg.finish(cudaErrorMemoryAllocation);
     cudaError_t ce = launch_split_blocks(bd, N, K, q4, 0, -1, scales, codes, st);
     if (ce == cudaSuccess) {
         QuantArgs a{};
@@ -713,11 +741,18 @@ int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, i
 
 int hm_dequant(const void* blocks, int dtype, size_t n_blocks, float* out, void* stream) {
     if (!blocks || !out) return gfail(HM_ERR_INVALID, "hm_dequant: null argument");
-    if (dtype != HM_Q8_0 && dtype != HM_Q4_0) return gfail(HM_ERR_UNSUPPORTED, "hm_dequant: dtype must be HM_Q8_0 or HM_Q4_0");
+    const bool kq = dtype == HM_Q4_K || dtype == HM_Q6_K;
+    if (dtype != HM_Q8_0 && dtype != HM_Q4_0 && !kq) return gfail(HM_ERR_UNSUPPORTED, "hm_dequant: dtype must be HM_Q8_0, HM_Q4_0, HM_Q4_K or HM_Q6_K");
     if (n_blocks == 0) return HM_OK;
     NEED_DEVICE();
     cudaStream_t st = (cudaStream_t)stream;
     Staging sg(st);
+    if (kq) {
+        const uint8_t* bd = sg.in((const uint8_t*)blocks, n_blocks * (dtype == HM_Q4_K ? 144 : 210));
+        float* od = sg.out(out, n_blocks * 256);
+        if (!bd || !od) return sg.finish(cudaErrorMemoryAllocation);
+        return sg.finish(launch_dequant_k(bd, n_blocks, dtype == HM_Q6_K, od, st));
+    }
     const int q4 = dtype == HM_Q4_0;
     const uint8_t* bd = sg.in((const uint8_t*)blocks, n_blocks * (q4 ? 18 : 34));
     float* od = sg.out(out, n_blocks * 32);

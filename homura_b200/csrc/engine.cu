@@ -1,6 +1,7 @@
 // Engine implementation.  See engine.h.
 #include "engine.h"
 #include "gemm_tc.h"
+#include "kquant.h"
 
 #include <algorithm>
 #include <cmath>
@@ -22,6 +23,7 @@ size_t LinearW::bytes() const {
     if (kind == HM_BF16) return (size_t)((N + SLAB - 1) / SLAB) * K * SLAB * 2;
     if (kind == HM_Q8_0) return (size_t)N * (K / 32) * 34;
     if (kind == HM_Q4_0) return (size_t)N * (K / 32) * 18;
+    if (kind == HM_Q4_K) return kq_bytes;
     return 0;
 }
 
@@ -103,9 +105,9 @@ Engine::~Engine() {
     fr(embed_); fr(final_norm_); fr(rope_cos_); fr(rope_sin_);
     for (auto& l : layers_) {
         fr(l.in_ln); fr(l.post_ln); fr(l.qkv_bias); fr(l.q_norm); fr(l.k_norm);
-        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->tc); fr(w->scales); fr(w->codes); }
+        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->tc); fr(w->scales); fr(w->codes); fr(w->kq_data); fr(w->kq_tile_type); }
     }
-    fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes);
+    fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes); fr(lm_head_.kq_data); fr(lm_head_.kq_tile_type);
     fr(xpack_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
@@ -132,19 +134,25 @@ int Engine::stage(const void* host, size_t nbytes, void** dev) {
 // outputs.  bf16 [out,in] goes to the slab layout; GGUF blocks [out, in/32] are split into
 // scale and code arrays (rows of the parts are simply concatenated).
 int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes) {
-    if (dtype != HM_BF16 && dtype != HM_Q8_0 && dtype != HM_Q4_0)
-        return fail(HM_ERR_UNSUPPORTED, "projection weights must be bf16, Q8_0 or Q4_0 (f32/f16 projections are outside this engine's path)");
-    if (L.kind >= 0 && L.kind != dtype) return fail(HM_ERR_UNSUPPORTED, "parts of a fused projection have different dtypes");
-    if (cfg_.weight_dtype >= 0 && cfg_.weight_dtype != dtype && &L != &lm_head_)
-        return fail(HM_ERR_UNSUPPORTED, "projection weights of one model must share a dtype");
-    if (&L != &lm_head_) cfg_.weight_dtype = dtype;
+    const bool kq = dtype == HM_Q4_K || dtype == HM_Q6_K;
+    if (dtype != HM_BF16 && dtype != HM_Q8_0 && dtype != HM_Q4_0 && !kq)
+        return fail(HM_ERR_UNSUPPORTED, "projection weights must be bf16, Q8_0, Q4_0, Q4_K or Q6_K (f32/f16 projections are outside this engine's path)");
+    // Q4_K and Q6_K mix freely (per 32-row tile), as the Q4_K_M files of the Hub do; they are one family here
+    const int family = kq ? (int)HM_Q4_K : dtype;
+    if (L.kind >= 0 && L.kind != family) return fail(HM_ERR_UNSUPPORTED, "parts of a fused projection have different dtypes");
+    if (cfg_.weight_dtype >= 0 && cfg_.weight_dtype != family && &L != &lm_head_)
+        return fail(HM_ERR_UNSUPPORTED, "projection weights of one model must share a dtype family");
+    if (&L != &lm_head_) cfg_.weight_dtype = family;
     const bool q = dtype != HM_BF16;
     if (q && K % 32 != 0) return fail(HM_ERR_INVALID, "quantised projection: in_features must be a multiple of 32");
-    const size_t expect = q ? (size_t)n_part * (K / 32) * (dtype == HM_Q8_0 ? 34 : 18) : (size_t)n_part * K * 2;
+    if (kq && K % 256 != 0) return fail(HM_ERR_INVALID, "K-quant projection: in_features must be a multiple of 256");
+    if (kq && interleave_which < 0 && (n_off % 32 != 0 || (n_part % 32 != 0 && n_off + n_part != N_total)))
+        return fail(HM_ERR_UNSUPPORTED, "K-quant parts of a fused projection must start and end on multiples of 32 rows");
+    const size_t expect = kq ? (size_t)n_part * (K / 256) * (dtype == HM_Q4_K ? 144 : 210) : q ? (size_t)n_part * (K / 32) * (dtype == HM_Q8_0 ? 34 : 18) : (size_t)n_part * K * 2;
     if (nbytes != expect) return fail(HM_ERR_INVALID, "tensor byte size does not match its shape");
     L.K = K;
     L.N = N_total;
-    L.kind = dtype;
+    L.kind = family;
     void* tmp = nullptr;
     int rc = stage(host, nbytes, &tmp);
     if (rc) return rc;
@@ -165,6 +173,22 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
             }
             if (ce == cudaSuccess) ce = launch_pack_tc((const uint16_t*)tmp, n_part, K, false, L.tc, n_off, interleave_which, stream_);
         }
+    } else if (kq) {
+        if (!L.kq_data) {
+            ce = cudaMalloc(&L.kq_data, kquant_data_bytes(K, N_total));
+            if (ce == cudaSuccess) ce = cudaMalloc(&L.kq_tile_type, kquant_tiles(N_total));
+            if (ce == cudaSuccess) ce = cudaMemsetAsync(L.kq_data, 0, kquant_data_bytes(K, N_total), stream_);
+            if (ce == cudaSuccess) ce = cudaMemsetAsync(L.kq_tile_type, 0, kquant_tiles(N_total), stream_);
+        }
+        // gate and up share a tile (16 + 16 rows): they must be of one type for the tile's decode
+        if (interleave_which >= 0 && L.loaded_parts > 0 && L.kq_part_type != dtype) {
+            cudaFree(tmp);
+            return fail(HM_ERR_UNSUPPORTED, "gate and up projections of a layer must share one K-quant type");
+        }
+        L.kq_part_type = dtype;
+        if (ce == cudaSuccess) ce = launch_kquant_split((const uint8_t*)tmp, n_part, K, dtype == HM_Q6_K, n_off, interleave_which, L.kq_data, L.kq_tile_type, stream_);
+        L.kq_bytes += nbytes;
+        quant_ = true;
     } else {
         const int q4 = dtype == HM_Q4_0;
         if (!L.scales) {
@@ -251,6 +275,17 @@ int Engine::load_tensor(const char* cname, int dtype, const int64_t* shape, int 
             if (rc) return rc;
             cudaError_t ce = cudaMalloc(&embed_, n * 4);
             if (ce == cudaSuccess) ce = launch_dequant((const uint8_t*)tmp, n / 32, dtype == HM_Q4_0, (float*)embed_, stream_);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
+            cudaFree(tmp);
+            if (ce != cudaSuccess) return cuda_fail(ce, "embedding dequant");
+            embed_dtype_ = HM_F32;
+        } else if (dtype == HM_Q4_K || dtype == HM_Q6_K) {
+            if (n % 256 != 0 || nbytes != n / 256 * (dtype == HM_Q4_K ? 144u : 210u)) return bad_shape();
+            void* tmp = nullptr;
+            int rc = stage(host, nbytes, &tmp);
+            if (rc) return rc;
+            cudaError_t ce = cudaMalloc(&embed_, n * 4);
+            if (ce == cudaSuccess) ce = launch_dequant_k((const uint8_t*)tmp, n / 256, dtype == HM_Q6_K, (float*)embed_, stream_);
             if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
             cudaFree(tmp);
             if (ce != cudaSuccess) return cuda_fail(ce, "embedding dequant");
@@ -794,6 +829,26 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.tickets = tickets_;
             if (a.cluster == 0 && gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
             ce = launch_gemv_bf16(a, mp, stream_, pdl_);
+        } else if (L.kind == HM_Q4_K) {
+            KQuantArgs a{};
+            a.data = L.kq_data;
+            a.tile_type = L.kq_tile_type;
+            a.K = L.K;
+            a.N = L.N;
+            a.m_valid = mv;
+            // layer projections quantise the activation row to Q8_K; the LM head runs f32 x dequantised weights
+            a.act_quant = &L != &lm_head_;
+            a.x = x + (size_t)m0 * ldx;
+            a.ldx = ldx;
+            a.pro = pro;
+            a.norm_w = norm_w;
+            a.eps = (float)cfg_.rms_norm_eps;
+            a.epi = epi;
+            a.y = y + (size_t)m0 * ldy;
+            a.ldy = ldy;
+            a.bias = bias;
+            a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+            ce = launch_gemv_kquant(a, mp, sm_count_, stream_, pdl_);
         } else {
             QuantArgs a{};
             a.scales = L.scales;

@@ -23,6 +23,10 @@ struct LinearW {
     uint16_t* tc = nullptr;  // second copy in the tensor-core tile layout (gemm_tc.h), used for passes over more than 8 rows
     uint16_t* scales = nullptr;
     uint8_t* codes = nullptr;
+    uint8_t* kq_data = nullptr;       // K-quants (kind HM_Q4_K stands for the family): tiled super-blocks, kquant.h
+    uint8_t* kq_tile_type = nullptr;  // per 32-row tile: 1 = Q4_K, 2 = Q6_K
+    size_t kq_bytes = 0;              // GGUF bytes loaded into it (what a step streams)
+    int kq_part_type = -1;            // type of the part loaded last (gate and up must agree: they share tiles)
     int loaded_parts = 0;
     size_t bytes() const;
 };

@@ -474,6 +474,8 @@ bool parse_gguf(const MappedFile& file, GgufFile* out, std::string* err) {
             case 30: t.dtype = HM_BF16; break;
             case 8: t.dtype = HM_Q8_0; break;
             case 2: t.dtype = HM_Q4_0; break;
+            case 12: t.dtype = HM_Q4_K; break;
+            case 14: t.dtype = HM_Q6_K; break;
             default: t.dtype = -1;
         }
         size_t n = 1;

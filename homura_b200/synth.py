@@ -27,6 +27,7 @@ import numpy as np
 
 GGUF_MAGIC = 0x46554747  # "GGUF" little-endian
 GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q8_0, GGML_BF16 = 0, 1, 2, 8, 30
+GGML_Q4_K, GGML_Q6_K = 12, 14
 
 
 @dataclass
@@ -226,9 +227,25 @@ def read_safetensors(path: str) -> Dict[str, Tuple[str, Tuple[int, ...], np.ndar
 
 
 def quant_blocks(seed: int, name: str, n_out: int, n_in: int, ggml_type: int) -> np.ndarray:
-    """Random blocks [n_out, n_in/32] in GGUF byte order: f16 scale |N(0,0.01)| + codes."""
+    """Random blocks [n_out, n_in/32] in GGUF byte order: f16 scale |N(0,0.01)| + codes
+    (Q8_0 / Q4_0), or super-blocks [n_out, n_in/256] of 144 (Q4_K) / 210 (Q6_K) bytes."""
     assert n_in % 32 == 0
     g = _rng(seed, name)
+    if ggml_type in (GGML_Q4_K, GGML_Q6_K):
+        assert n_in % 256 == 0, "K-quants need in_features to be a multiple of 256"
+        nsb = n_out * (n_in // 256)
+        if ggml_type == GGML_Q4_K:
+            blk = g.integers(0, 256, size=(nsb, 144), dtype=np.uint8)  # packed 6-bit scales/mins and nibbles: any byte is valid
+            d = np.abs(g.standard_normal(nsb, dtype=np.float32) * np.float32(4e-4)).astype(np.float16)
+            dmin = np.abs(g.standard_normal(nsb, dtype=np.float32) * np.float32(1e-4)).astype(np.float16)
+            blk[:, 0:2] = d.view(np.uint8).reshape(nsb, 2)
+            blk[:, 2:4] = dmin.view(np.uint8).reshape(nsb, 2)
+        else:
+            blk = g.integers(0, 256, size=(nsb, 210), dtype=np.uint8)
+            blk[:, 192:208] = g.integers(-64, 64, size=(nsb, 16), dtype=np.int8).view(np.uint8)  # i8 sub-block scales
+            d = np.abs(g.standard_normal(nsb, dtype=np.float32) * np.float32(2e-5)).astype(np.float16)
+            blk[:, 208:210] = d.view(np.uint8).reshape(nsb, 2)
+        return blk.reshape(-1)
     nb = n_out * (n_in // 32)
     scale = np.abs(g.standard_normal(nb, dtype=np.float32) * np.float32(0.01)).astype(np.float16)
     if ggml_type == GGML_Q8_0:
@@ -310,9 +327,12 @@ def gguf_metadata(cfg: DecoderConfig, arch: str = "llama") -> Dict[str, object]:
     return md
 
 
-def write_gguf_model(path: str, cfg: DecoderConfig, seed: int, ggml_type: int, quant_lm_head: bool = True, norm_jitter: float = 0.0) -> str:
-    """GGUF file: all linears in ``ggml_type`` blocks, bf16 embedding/norms, optional biases (f32)."""
+def write_gguf_model(path: str, cfg: DecoderConfig, seed: int, ggml_type: int, quant_lm_head: bool = True, norm_jitter: float = 0.0, k_mix: bool = False, quant_embed: bool = False) -> str:
+    """GGUF file: all linears in ``ggml_type`` blocks, bf16 embedding/norms, optional biases (f32).
+    ``k_mix`` writes attn_v, ffn_down and output as Q6_K beside Q4_K elsewhere (the mix of a Q4_K_M
+    file); ``quant_embed`` quantises token_embd too (Q6_K, or ``ggml_type`` for the 32-value formats)."""
     H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    q6_names = ("attn_v.weight", "ffn_down.weight", "output.weight") if k_mix else ()
 
     def norm(name, n):
         if norm_jitter > 0:
@@ -321,10 +341,15 @@ def write_gguf_model(path: str, cfg: DecoderConfig, seed: int, ggml_type: int, q
         return (name, (n,), GGML_BF16, ones_bf16((n,)))
 
     def lin(name, out_f, in_f):
-        return (name, (out_f, in_f), ggml_type, quant_blocks(seed, name, out_f, in_f, ggml_type))
+        gt = GGML_Q6_K if name.endswith(q6_names) and q6_names else ggml_type
+        return (name, (out_f, in_f), gt, quant_blocks(seed, name, out_f, in_f, gt))
 
     def gen():
-        yield ("token_embd.weight", (V, H), GGML_BF16, normal_bf16(seed, "token_embd.weight", (V, H)))
+        if quant_embed:
+            gt = GGML_Q6_K if ggml_type in (GGML_Q4_K, GGML_Q6_K) else ggml_type
+            yield ("token_embd.weight", (V, H), gt, quant_blocks(seed, "token_embd.weight", V, H, gt))
+        else:
+            yield ("token_embd.weight", (V, H), GGML_BF16, normal_bf16(seed, "token_embd.weight", (V, H)))
         for i in range(cfg.num_hidden_layers):
             p = f"blk.{i}."
             yield norm(p + "attn_norm.weight", H)
@@ -402,7 +427,7 @@ def read_gguf(path: str):
         off = rd("Q")
         infos.append((name, tuple(dims), gt, off))
     data0 = (pos + align - 1) // align * align
-    bpe = {GGML_F32: (1, 4), GGML_F16: (1, 2), GGML_BF16: (1, 2), GGML_Q8_0: (32, 34), GGML_Q4_0: (32, 18)}
+    bpe = {GGML_F32: (1, 4), GGML_F16: (1, 2), GGML_BF16: (1, 2), GGML_Q8_0: (32, 34), GGML_Q4_0: (32, 18), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210)}
     tensors = {}
     for name, shape, gt, off in infos:
         bs, ts = bpe[gt]

@@ -43,7 +43,7 @@ enum hm_status {
 };
 
 /* DType subset on this path: src/dtype.rs:8-26 (+ Q4_0, which Homura has no DType for). */
-enum hm_dtype { HM_F32 = 0, HM_BF16 = 1, HM_F16 = 2, HM_Q8_0 = 3, HM_Q4_0 = 4, HM_I64 = 5, HM_I32 = 6, HM_U8 = 7 };
+enum hm_dtype { HM_F32 = 0, HM_BF16 = 1, HM_F16 = 2, HM_Q8_0 = 3, HM_Q4_0 = 4, HM_I64 = 5, HM_I32 = 6, HM_U8 = 7, HM_Q4_K = 8, HM_Q6_K = 9 };
 
 /* Weight layouts accepted by the standalone projection kernels. */
 enum hm_layout {
@@ -209,9 +209,12 @@ HM_API size_t hm_tc_packed_elems(int K, int N);
  * [ceil(N/128)][ceil(K/64)][128][64], K-major, 128-byte swizzled (the shared-memory image of a tile). */
 HM_API int hm_pack_bf16_tc(const void* w_kn, int K, int N, void* dst, void* stream);
 /* Q8_0 / Q4_0 dequant-matmul on GGUF blocks [N, K/32] (src/graph_builder/emit_quant.rs:30-142;
- * Q4_0 has no counterpart in Homura, see src/gguf.rs:94-109,141).  M <= 8. */
+ * Q4_0 has no counterpart in Homura, see src/gguf.rs:94-109,141), and the K-quants HM_Q4_K / HM_Q6_K
+ * on super-blocks [N, K/256] of 144 / 210 bytes with Homura's semantics for them: the activation row
+ * is quantised to Q8_K and the dot products run in integers (emit_quant.rs:165-567, 569-816).  M <= 8. */
 HM_API int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, int N, float* y, void* stream);
-/* CPU-visible dequantisation of GGUF blocks on the GPU (dequant_q8_0, src/gguf.rs:817-831). */
+/* CPU-visible dequantisation of GGUF blocks on the GPU (dequant_q8_0 / dequant_q4_k / dequant_q6_k,
+ * src/gguf.rs:817-917); n_blocks counts 32-value blocks, or 256-value super-blocks for the K-quants. */
 HM_API int hm_dequant(const void* blocks, int dtype, size_t n_blocks, float* out, void* stream);
 /* RMSNorm, src/graph_builder/emit_linalg.rs:7-26: rows x n. */
 HM_API int hm_rms_norm(const float* x, const float* w, float eps, int rows, int n, float* out, void* stream);

@@ -349,6 +349,150 @@ ORC_API void orc_matmul_q4_0(const float* x, const uint8_t* w, int M, int K, int
 }
 
 // ---------------------------------------------------------------------------------------
+// K-quants: Q4_K and Q6_K super-blocks of 256 values.
+//   dequantisation        src/gguf.rs:833-917 (embeddings and the LM head are widened to f32)
+//   Q8_K activation quantisation + integer dot product
+//                         src/graph_builder/emit_quant.rs:165-567 (Q4_K), 569-816 (Q6_K)
+// ---------------------------------------------------------------------------------------
+
+// get_scale_min_k4 as spelled out in src/gguf.rs:848-864.
+static inline void orc_q4k_scales(const uint8_t* sr, uint8_t sc[8], uint8_t mn[8]) {
+    for (int i = 0; i < 4; ++i) {
+        sc[i] = sr[i] & 0x3F;
+        mn[i] = sr[4 + i] & 0x3F;
+    }
+    for (int i = 0; i < 4; ++i) {
+        sc[4 + i] = (uint8_t)((sr[8 + i] & 0x0F) | ((sr[i] >> 6) << 4));
+        mn[4 + i] = (uint8_t)((sr[8 + i] >> 4) | ((sr[4 + i] >> 6) << 4));
+    }
+}
+
+ORC_API void orc_dequant_q4_k(const uint8_t* src, size_t nblocks, float* dst) {
+    for (size_t b = 0; b < nblocks; ++b) {
+        const uint8_t* blk = src + b * 144;
+        float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        float dmin = orc_f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+        uint8_t sc[8], mn[8];
+        orc_q4k_scales(blk + 4, sc, mn);
+        const uint8_t* qs = blk + 16;
+        for (int pair = 0; pair < 4; ++pair) {
+            float scale0 = d * (float)sc[2 * pair], min0 = dmin * (float)mn[2 * pair];
+            float scale1 = d * (float)sc[2 * pair + 1], min1 = dmin * (float)mn[2 * pair + 1];
+            const uint8_t* q = qs + pair * 32;
+            float* o = dst + b * 256 + pair * 64;
+            for (int l = 0; l < 32; ++l) o[l] = (float)(q[l] & 0x0F) * scale0 - min0;
+            for (int l = 0; l < 32; ++l) o[32 + l] = (float)(q[l] >> 4) * scale1 - min1;
+        }
+    }
+}
+
+// Signed 6-bit code of element e (0..255) of a Q6_K block (llama.cpp layout, src/gguf.rs:897-914).
+static inline int orc_q6k_code(const uint8_t* blk, int e) {
+    int chunk = e >> 7, r = e & 127, group = r >> 5, l = r & 31;
+    uint8_t qlb = blk[chunk * 64 + (group & 1) * 32 + l];
+    int lo = group >= 2 ? (qlb >> 4) : (qlb & 0x0F);
+    int hi = (blk[128 + chunk * 32 + l] >> (group * 2)) & 3;
+    return (lo | (hi << 4)) - 32;
+}
+
+ORC_API void orc_dequant_q6_k(const uint8_t* src, size_t nblocks, float* dst) {
+    for (size_t b = 0; b < nblocks; ++b) {
+        const uint8_t* blk = src + b * 210;
+        float d = orc_f16_to_f32((uint16_t)(blk[208] | (blk[209] << 8)));
+        for (int e = 0; e < 256; ++e) {
+            float sc = (float)(int8_t)blk[192 + (e >> 4)];
+            dst[b * 256 + e] = d * sc * (float)orc_q6k_code(blk, e);  // (d * sc) * q, as written in the reference
+        }
+    }
+}
+
+// Q8_K quantisation of one activation row (emit_quant.rs:409-460): per 256-value block
+// act_d = amax / 127, iscale = 127 / amax (0 when amax == 0), q = clamp(roundeven(x * iscale), -127, 127),
+// bsums[g] = sum of the 16 codes of group g.
+ORC_API void orc_quantize_q8_k(const float* x, int K, int8_t* q8, float* act_d, int32_t* bsums) {
+    int nb = K / 256;
+    for (int kb = 0; kb < nb; ++kb) {
+        const float* xb = x + kb * 256;
+        float amax = 0.0f;
+        for (int i = 0; i < 256; ++i) amax = std::fmax(amax, std::fabs(xb[i]));
+        act_d[kb] = amax / 127.0f;
+        float iscale = amax == 0.0f ? 0.0f : 127.0f / amax;
+        for (int g = 0; g < 16; ++g) bsums[kb * 16 + g] = 0;
+        for (int i = 0; i < 256; ++i) {
+            float r = std::nearbyintf(xb[i] * iscale);  // round half to even (math.roundeven)
+            r = std::fmin(r, 127.0f);
+            r = std::fmax(r, -127.0f);
+            int8_t q = (int8_t)(int32_t)r;
+            q8[kb * 256 + i] = q;
+            bsums[kb * 16 + (i >> 4)] += q;
+        }
+    }
+}
+
+ORC_API void orc_matmul_q4_k(const float* x, const uint8_t* w, int M, int K, int N, float* y) {
+    int nb = K / 256;
+    std::vector<int8_t> q8((size_t)M * K);
+    std::vector<float> ad((size_t)M * nb);
+    std::vector<int32_t> bs((size_t)M * nb * 16);
+    for (int m = 0; m < M; ++m) orc_quantize_q8_k(x + (size_t)m * K, K, q8.data() + (size_t)m * K, ad.data() + (size_t)m * nb, bs.data() + (size_t)m * nb * 16);
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n) {
+        for (int m = 0; m < M; ++m) {
+            float acc = 0.0f;
+            for (int kb = 0; kb < nb; ++kb) {
+                const uint8_t* blk = w + ((size_t)n * nb + kb) * 144;
+                float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+                float dmin = orc_f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+                uint8_t sc[8], mn[8];
+                orc_q4k_scales(blk + 4, sc, mn);
+                const int8_t* a = q8.data() + (size_t)m * K + kb * 256;
+                int32_t scale_accum = 0;
+                for (int sb = 0; sb < 8; ++sb) {
+                    const uint8_t* q = blk + 16 + (sb / 2) * 32;
+                    int32_t isum = 0;
+                    for (int l = 0; l < 32; ++l) isum += (int32_t)((sb & 1) ? (q[l] >> 4) : (q[l] & 0x0F)) * (int32_t)a[sb * 32 + l];
+                    scale_accum += (int32_t)sc[sb] * isum;
+                }
+                int32_t min_accum = 0;
+                for (int g = 0; g < 16; ++g) min_accum += (int32_t)mn[g / 2] * bs[((size_t)m * nb + kb) * 16 + g];
+                float act_d = ad[(size_t)m * nb + kb];
+                float scale_part = (d * act_d) * (float)scale_accum;
+                float min_part = (dmin * act_d) * (float)min_accum;
+                acc = acc + (scale_part - min_part);
+            }
+            y[(size_t)m * N + n] = acc;
+        }
+    }
+}
+
+ORC_API void orc_matmul_q6_k(const float* x, const uint8_t* w, int M, int K, int N, float* y) {
+    int nb = K / 256;
+    std::vector<int8_t> q8((size_t)M * K);
+    std::vector<float> ad((size_t)M * nb);
+    std::vector<int32_t> bs((size_t)M * nb * 16);
+    for (int m = 0; m < M; ++m) orc_quantize_q8_k(x + (size_t)m * K, K, q8.data() + (size_t)m * K, ad.data() + (size_t)m * nb, bs.data() + (size_t)m * nb * 16);
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n) {
+        for (int m = 0; m < M; ++m) {
+            float acc = 0.0f;
+            for (int kb = 0; kb < nb; ++kb) {
+                const uint8_t* blk = w + ((size_t)n * nb + kb) * 210;
+                float d = orc_f16_to_f32((uint16_t)(blk[208] | (blk[209] << 8)));
+                const int8_t* a = q8.data() + (size_t)m * K + kb * 256;
+                int32_t scale_accum = 0;
+                for (int sb = 0; sb < 16; ++sb) {
+                    int32_t isum = 0;
+                    for (int j = 0; j < 16; ++j) isum += orc_q6k_code(blk, sb * 16 + j) * (int32_t)a[sb * 16 + j];
+                    scale_accum += (int32_t)(int8_t)blk[192 + sb] * isum;
+                }
+                acc = acc + (d * ad[(size_t)m * nb + kb]) * (float)scale_accum;
+            }
+            y[(size_t)m * N + n] = acc;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // KV cache  (src/runtime.rs:375-650)
 // ---------------------------------------------------------------------------------------
 
@@ -561,7 +705,7 @@ struct OrcConfig {
     double rms_norm_eps, rope_theta;
 };
 
-enum { ORC_F32 = 0, ORC_BF16 = 1, ORC_F16 = 2, ORC_Q8_0 = 3, ORC_Q4_0 = 4 };
+enum { ORC_F32 = 0, ORC_BF16 = 1, ORC_F16 = 2, ORC_Q8_0 = 3, ORC_Q4_0 = 4, ORC_Q4_K = 5, ORC_Q6_K = 6 };
 
 struct Linear {
     int K = 0, N = 0, kind = -1;
@@ -574,6 +718,8 @@ struct Linear {
             case ORC_BF16: orc_matmul_bf16(x, bf16.data(), M, K, N, y); break;
             case ORC_Q8_0: orc_matmul_q8_0(x, q.data(), M, K, N, y); break;
             case ORC_Q4_0: orc_matmul_q4_0(x, q.data(), M, K, N, y); break;
+            case ORC_Q4_K: orc_matmul_q4_k(x, q.data(), M, K, N, y); break;
+            case ORC_Q6_K: orc_matmul_q6_k(x, q.data(), M, K, N, y); break;
             default: std::fprintf(stderr, "oracle: linear not loaded\n"); std::abort();
         }
     }
@@ -638,6 +784,10 @@ static void to_f32(const void* data, int dtype, size_t n, std::vector<float>& ou
         orc_dequant_q8_0((const uint8_t*)data, n / 32, out.data());
     } else if (dtype == ORC_Q4_0) {
         orc_dequant_q4_0((const uint8_t*)data, n / 32, out.data());
+    } else if (dtype == ORC_Q4_K) {
+        orc_dequant_q4_k((const uint8_t*)data, n / 256, out.data());
+    } else if (dtype == ORC_Q6_K) {
+        orc_dequant_q6_k((const uint8_t*)data, n / 256, out.data());
     }
 }
 
@@ -667,7 +817,9 @@ static void set_linear_gguf(Linear& L, const void* data, int dtype, int out_f, i
     L.K = in_f;
     L.N = out_f;
     L.kind = dtype;
-    size_t bytes = (size_t)out_f * (in_f / 32) * (dtype == ORC_Q8_0 ? 34 : 18);
+    size_t bytes = dtype == ORC_Q4_K   ? (size_t)out_f * (in_f / 256) * 144
+                   : dtype == ORC_Q6_K ? (size_t)out_f * (in_f / 256) * 210
+                                       : (size_t)out_f * (in_f / 32) * (dtype == ORC_Q8_0 ? 34 : 18);
     L.q.assign((const uint8_t*)data, (const uint8_t*)data + bytes);
 }
 
@@ -736,7 +888,7 @@ ORC_API int orc_model_set_tensor(OrcModel* m, const char* cname, int dtype, cons
         if (layer < 0 || layer >= (int)m->layers.size()) return 2;
         Layer& L = m->layers[layer];
         auto lin = [&](Linear& dst) {
-            if (dtype == ORC_Q8_0 || dtype == ORC_Q4_0) {
+            if (dtype == ORC_Q8_0 || dtype == ORC_Q4_0 || dtype == ORC_Q4_K || dtype == ORC_Q6_K) {
                 set_linear_gguf(dst, data, dtype, (int)shape[0], (int)shape[1]);
                 m->quant = true;
             } else {

@@ -18,7 +18,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libhomura_oracle.so")
 
-ORC_F32, ORC_BF16, ORC_F16, ORC_Q8_0, ORC_Q4_0 = 0, 1, 2, 3, 4
+ORC_F32, ORC_BF16, ORC_F16, ORC_Q8_0, ORC_Q4_0, ORC_Q4_K, ORC_Q6_K = 0, 1, 2, 3, 4, 5, 6
 
 
 def build(force: bool = False) -> str:
@@ -84,6 +84,11 @@ def lib():
         "orc_matmul_q4_0": (None, [vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "orc_dequant_q8_0": (None, [vp, C.c_size_t, vp]),
         "orc_dequant_q4_0": (None, [vp, C.c_size_t, vp]),
+        "orc_matmul_q4_k": (None, [vp, vp, C.c_int, C.c_int, C.c_int, vp]),
+        "orc_matmul_q6_k": (None, [vp, vp, C.c_int, C.c_int, C.c_int, vp]),
+        "orc_dequant_q4_k": (None, [vp, C.c_size_t, vp]),
+        "orc_dequant_q6_k": (None, [vp, C.c_size_t, vp]),
+        "orc_quantize_q8_k": (None, [vp, C.c_int, vp, vp, vp]),
         "orc_kv_new": (vp, [C.c_int, C.c_int, C.c_int, C.c_int]),
         "orc_kv_free": (None, [vp]),
         "orc_kv_append_key": (C.c_int, [vp, C.c_int, vp, C.c_int]),
@@ -199,17 +204,31 @@ def matmul_q(x, blocks, N, kind):
     M, K = x.shape
     blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
     y = np.empty((M, N), np.float32)
-    fn = lib().orc_matmul_q8_0 if kind == "q8_0" else lib().orc_matmul_q4_0
+    fn = getattr(lib(), "orc_matmul_" + kind)  # q8_0, q4_0, q4_k, q6_k
     fn(_p(x), _p(blocks), M, K, N, _p(y))
     return y
 
 
+QUANT_BLOCK = {"q8_0": (34, 32), "q4_0": (18, 32), "q4_k": (144, 256), "q6_k": (210, 256)}  # bytes, values
+
+
+def quantize_q8_k(x):
+    """Q8_K activation quantisation of one row: (int8 codes [K], f32 scales [K/256], int32 group sums [K/16])."""
+    x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    K = x.size
+    q8 = np.empty(K, np.int8)
+    d = np.empty(K // 256, np.float32)
+    bs = np.empty(K // 16, np.int32)
+    lib().orc_quantize_q8_k(_p(x), K, _p(q8), _p(d), _p(bs))
+    return q8, d, bs
+
+
 def dequant(blocks, kind):
     blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
-    bsz = 34 if kind == "q8_0" else 18
+    bsz, vals = QUANT_BLOCK[kind]
     nb = blocks.size // bsz
-    out = np.empty(nb * 32, np.float32)
-    (lib().orc_dequant_q8_0 if kind == "q8_0" else lib().orc_dequant_q4_0)(_p(blocks), nb, _p(out))
+    out = np.empty(nb * vals, np.float32)
+    getattr(lib(), "orc_dequant_" + kind)(_p(blocks), nb, _p(out))
     return out
 
 
@@ -282,7 +301,7 @@ class KvCache:
 
 # ---- whole-model oracle ------------------------------------------------------------------
 
-_GGML_TO_ORC = {0: ORC_F32, 1: ORC_F16, 30: ORC_BF16, 8: ORC_Q8_0, 2: ORC_Q4_0}
+_GGML_TO_ORC = {0: ORC_F32, 1: ORC_F16, 30: ORC_BF16, 8: ORC_Q8_0, 2: ORC_Q4_0, 12: ORC_Q4_K, 14: ORC_Q6_K}
 _ST_TO_ORC = {"F32": ORC_F32, "BF16": ORC_BF16, "F16": ORC_F16}
 
 

@@ -217,3 +217,40 @@ def test_attention_rejects_bad_arguments(hm):
         hm.attn_decode_paged(q, d, d, hm.DType.F32, [[0]], [17], 2, 2, 64, 1)  # longer than its pages
     with pytest.raises(hm.HomuraError):
         hm.attn_decode_paged(q, d, d, hm.DType.F32, [[0]], [1], 2, 2, 64, 1, page_tokens=32)
+
+
+# ---- K-quants (Q4_K / Q6_K): dequantisation bit-exact, Q8_K integer-dot projections ------------
+
+
+@pytest.mark.parametrize("kind,dt,gt", [("q4_k", "Q4_K", synth.GGML_Q4_K), ("q6_k", "Q6_K", synth.GGML_Q6_K)])
+def test_kquant_dequant_is_bit_exact(hm, oracle, kind, dt, gt):
+    blocks = synth.quant_blocks(5, "t", 48, 1024, gt)
+    np.testing.assert_array_equal(hm.dequant(blocks, hm.DType[dt]), oracle.dequant(blocks, kind))
+
+
+def test_kquant_known_answers(hm):
+    # emit_q4_k_correctness (src/graph_builder/emit_quant.rs:993-1100): d = 1, sc[0..3] = 1, nibbles 1, x = 1 -> 128
+    b4 = np.zeros((4, 144), np.uint8)
+    b4[:, 1] = 0x3C
+    b4[:, 4:8] = 1
+    b4[:, 16:] = 0x11
+    np.testing.assert_array_equal(hm.gemv_quant(np.ones((1, 256), np.float32), b4.ravel(), hm.DType.Q4_K, 4), np.full((1, 4), 128.0, np.float32))
+    # emit_q6_k_correctness (emit_quant.rs:1285-1360): d = 1, sc = 1, low nibbles 1, high bits 0 -> 256 * (1 - 32)
+    b6 = np.zeros((4, 210), np.uint8)
+    b6[:, 209] = 0x3C
+    b6[:, 192:208] = 1
+    b6[:, 0:128] = 0x11
+    np.testing.assert_array_equal(hm.gemv_quant(np.ones((1, 256), np.float32), b6.ravel(), hm.DType.Q6_K, 4), np.full((1, 4), -7936.0, np.float32))
+
+
+@pytest.mark.parametrize("kind,dt,gt", [("q4_k", "Q4_K", synth.GGML_Q4_K), ("q6_k", "Q6_K", synth.GGML_Q6_K)])
+@pytest.mark.parametrize("M,K,N", [(1, 2048, 2048), (1, 5632, 2048), (4, 2048, 512), (8, 256, 40), (2, 1024, 33), (1, 256, 1)])
+def test_kquant_gemv_matches_oracle(hm, oracle, kind, dt, gt, M, K, N):
+    blocks = synth.quant_blocks(7, f"w{K}x{N}", N, K, gt)
+    x = np.random.default_rng(K + N).standard_normal((M, K), dtype=np.float32)
+    want = oracle.matmul_q(x, blocks, N, kind)
+    got = hm.gemv_quant(x, blocks, hm.DType[dt], N)
+    # integer dot products are exact; only the f32 sum over super-blocks is in a different order
+    assert rel_err(got, want) < 1e-5
+    if K == 256:  # one super-block per row: no reordering at all
+        np.testing.assert_array_equal(got, want)

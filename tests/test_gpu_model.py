@@ -422,3 +422,31 @@ def test_batch_20_decode_on_tensor_cores(hm, oracle):
             t = oracle.argmax(oms[b].decode_step(t))
             want.append(t)
         assert [int(v) for v in out[b]] == want
+
+
+# ---- K-quant GGUF models (Q4_K / Q6_K, the mix of a Q4_K_M file) ---------------------------------
+
+
+@pytest.mark.parametrize("case", ["q4_k", "q6_k", "mix_quant_embed", "mix_tied"])
+def test_kquant_gguf_model_matches_oracle(hm, oracle, case):
+    tied = case == "mix_tied"
+    cfg = synth.tiny_config(qkv_bias=False, tie_word_embeddings=tied, rope_theta=1e4, rms_norm_eps=1e-5, intermediate_size=768)
+    p = os.path.join(tempfile.mkdtemp(), "m.gguf")
+    gt = synth.GGML_Q6_K if case == "q6_k" else synth.GGML_Q4_K
+    synth.write_gguf_model(p, cfg, seed=5, ggml_type=gt, norm_jitter=0.1, k_mix=case.startswith("mix"), quant_embed=case.startswith("mix"))
+    om = oracle.OracleModel.from_gguf(p, max_seq_len=96)
+    m = hm.HfModel.load_gguf(p)
+    assert m.config().weight_dtype == hm.DType.Q4_K  # the K-quant family
+    m.init_kv_cache(96)
+    ids = synth.prompt_ids(8, 19, cfg.vocab_size)
+    tok_o, lg_o = om.prefill(ids)
+    tok_g, lg_g = m.prefill(ids, want_logits=True)
+    assert_logits_close(lg_g, lg_o)
+    assert tok_g == tok_o
+    cur = tok_o
+    for _ in range(40):
+        lo = om.decode_step(cur)
+        lgd, nxt = m.decode_step([cur])
+        assert_logits_close(lgd[0], lo)
+        cur = oracle.argmax(lo)
+        assert int(nxt[0]) == cur

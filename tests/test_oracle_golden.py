@@ -318,3 +318,59 @@ def test_bf16_rne():
     t = torch.randn(4096, dtype=torch.float32)
     exp = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     np.testing.assert_array_equal(synth.f32_to_bf16_rne(t.numpy()), exp)
+
+
+# ---- K-quants: the reference's own known-answer tests -------------------------------------------
+
+
+def test_q4_k_matmul_known_answer(oracle):
+    # emit_q4_k_correctness, src/graph_builder/emit_quant.rs:993-1100: d = 1.0, dmin = 0, sc[0..3] = 1,
+    # sc[4..7] = 0, every nibble 1, activation 1.0 -> 4 sub-blocks x 32 = 128 per output
+    blk = np.zeros((4, 144), np.uint8)
+    blk[:, 1] = 0x3C
+    blk[:, 4:8] = 1
+    blk[:, 16:] = 0x11
+    np.testing.assert_array_equal(oracle.matmul_q(np.ones((1, 256), np.float32), blk.ravel(), 4, "q4_k"), np.full((1, 4), 128.0, np.float32))
+
+
+def test_q6_k_matmul_known_answer(oracle):
+    # emit_q6_k_correctness, emit_quant.rs:1285-1360: d = 1.0, every sub-block scale 1, low nibbles 1,
+    # high bits 0 -> code 1 - 32 = -31, 256 of them
+    blk = np.zeros((4, 210), np.uint8)
+    blk[:, 209] = 0x3C
+    blk[:, 192:208] = 1
+    blk[:, 0:128] = 0x11
+    np.testing.assert_array_equal(oracle.matmul_q(np.ones((1, 256), np.float32), blk.ravel(), 4, "q6_k"), np.full((1, 4), -7936.0, np.float32))
+
+
+def test_k_quant_geometry_and_dequant_layout(oracle):
+    # type sizes pinned by src/gguf.rs:1175-1182
+    assert oracle.QUANT_BLOCK["q4_k"] == (144, 256) and oracle.QUANT_BLOCK["q6_k"] == (210, 256)
+    # Q4_K: sub-block sb uses the low (even sb) or high (odd sb) nibbles of bytes [16 + (sb/2)*32, +32)
+    blk = np.zeros(144, np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(2.0).tobytes(), np.uint8)   # d
+    blk[2:4] = np.frombuffer(np.float16(0.5).tobytes(), np.uint8)   # dmin
+    blk[4] = 3       # sc[0] = 3
+    blk[8] = 2       # mn[0] = 2
+    blk[16] = 0x0A   # element 0 = low nibble 10, element 32 = high nibble 0
+    out = oracle.dequant(blk, "q4_k")
+    assert out[0] == 10 * (2.0 * 3) - 0.5 * 2 and out[1] == -1.0 and out[32] == 0.0
+    # Q6_K: element l of group 0 takes ql[l] low nibble and qh[l] bits 0-1; scale index e / 16
+    b6 = np.zeros(210, np.uint8)
+    b6[208:210] = np.frombuffer(np.float16(0.25).tobytes(), np.uint8)
+    b6[192] = np.uint8(np.int8(-3).view(np.uint8))
+    b6[0] = 0x05
+    b6[128] = 0x02
+    o6 = oracle.dequant(b6, "q6_k")
+    assert o6[0] == 0.25 * -3 * ((5 | (2 << 4)) - 32) and o6[1] == 0.25 * -3 * (0 - 32) and o6[16] == 0.0
+
+
+def test_q8_k_activation_quantisation(oracle):
+    # emit_quant.rs:409-460: act_d = amax / 127, codes roundeven(x * 127 / amax), sums of 16
+    x = np.zeros(256, np.float32)
+    x[0], x[1], x[2], x[17] = 127.0, 0.5, 1.5, -2.5   # halves round to even: 0, 2, -2
+    q8, d, bs = oracle.quantize_q8_k(x)
+    assert d[0] == 1.0 and list(q8[:3]) == [127, 0, 2] and q8[17] == -2
+    assert bs[0] == 129 and bs[1] == -2 and int(bs.sum()) == 127
+    q8z, dz, _ = oracle.quantize_q8_k(np.zeros(256, np.float32))
+    assert dz[0] == 0.0 and not q8z.any()
