@@ -78,10 +78,11 @@ WORKLOADS = {
     "qwen25-05b": ("QWEN25_05B", "bf16", 1, "Qwen2.5-0.5B-architecture decoder (24 layers, hidden 896, 14/2 heads, hd 64, SwiGLU 4864, vocab 151936, tied, QKV bias), batch 1 per GPU"),
     "tinyllama-q8_0": ("TINYLLAMA_11B", "q8_0", 1, "TinyLlama-1.1B-architecture decoder (22 layers, hidden 2048, 32/4 heads, hd 64, SwiGLU 5632, vocab 32000), GGUF Q8_0, batch 1 per GPU"),
     "tinyllama-q4_0": ("TINYLLAMA_11B", "q4_0", 1, "TinyLlama-1.1B-architecture decoder (22 layers, hidden 2048, 32/4 heads, hd 64, SwiGLU 5632, vocab 32000), GGUF Q4_0, batch 1 per GPU"),
+    "tinyllama-q4_k_m": ("TINYLLAMA_11B", "q4_k_m", 1, "TinyLlama-1.1B-architecture decoder (22 layers, hidden 2048, 32/4 heads, hd 64, SwiGLU 5632, vocab 32000), GGUF Q4_K with attn_v / ffn_down / output in Q6_K (the Q4_K_M mix), batch 1 per GPU"),
     "qwen25-15b-x64": ("QWEN25_15B", "bf16", 64, "Qwen2.5-1.5B-architecture decoder (28 layers, hidden 1536, 12/2 heads, hd 128, SwiGLU 8960, vocab 151936, tied, QKV bias), 64 sequences per GPU"),
 }
 HEADLINE = "qwen25-05b"
-PROMPTS = {"qwen25-05b": 128, "tinyllama-q8_0": 256, "tinyllama-q4_0": 256, "qwen25-15b-x64": 512}
+PROMPTS = {"qwen25-05b": 128, "tinyllama-q8_0": 256, "tinyllama-q4_0": 256, "tinyllama-q4_k_m": 256, "qwen25-15b-x64": 512}
 
 
 def model_dir(cfg, seed, rank, world, name=HEADLINE, fmt="bf16"):
@@ -99,7 +100,10 @@ def model_dir(cfg, seed, rank, world, name=HEADLINE, fmt="bf16"):
             synth.write_hf_model(d, cfg, seed)
         else:
             os.makedirs(d, exist_ok=True)
-            synth.write_gguf_model(gguf, cfg, seed, synth.GGML_Q8_0 if fmt == "q8_0" else synth.GGML_Q4_0)
+            if fmt == "q4_k_m":
+                synth.write_gguf_model(gguf, cfg, seed, synth.GGML_Q4_K, k_mix=True, quant_embed=True)
+            else:
+                synth.write_gguf_model(gguf, cfg, seed, synth.GGML_Q8_0 if fmt == "q8_0" else synth.GGML_Q4_0)
         open(marker, "w").write("ok")
         log(f"[bench] wrote synthetic checkpoint to {d} in {time.time() - t:.1f}s")
     while not os.path.exists(marker):
@@ -296,7 +300,7 @@ def main():
     step_bytes = m.weight_bytes() + B * (kv_bytes_tok * T_avg + kv_bytes_tok)  # weights once per step, every sequence's cache
     step_gbs = step_bytes * (tok_per_s / world / B) / 1e9
     if fmt != "bf16":
-        kern = "gemv_quant_kernel<1> (Q8_0/Q4_0 dequantising projections; LM head included)"
+        kern = "gemv_kquant_kernel<1> (Q4_K/Q6_K projections: Q8_K activations, dp4a; LM head in f32)" if fmt == "q4_k_m" else "gemv_quant_kernel<1> (Q8_0/Q4_0 dequantising projections; LM head included)"
     elif B > 8:
         kern = "gemm_tc_kernel (tcgen05 projections over 64 rows; LM head included)"
     else:
