@@ -120,6 +120,7 @@ SIGNATURES = {
     "hm_generate": (_i32, [_vp, _i32, _vp, _i32, _i32, C.POINTER(_Sampling), _vp, _i32p]),
     "hm_decode_greedy_n": (_i32, [_vp, _vp, _i32, _vp]),
     "hm_sample_token": (_i32, [_vp, _i32, C.POINTER(_Sampling), _vp, _i32, C.POINTER(C.c_uint64), _u32p]),
+    "hm_sample_token_device": (_i32, [_vp, _i32, C.POINTER(_Sampling), _vp, _i32, C.POINTER(C.c_uint64), _u32p]),
     "hm_time_decode": (_i32, [_vp, _i32, _i32, _f32p]),
     "hm_profile_decode": (_i32, [_vp, _i32, C.POINTER(_KernelStat), _i32, _i32p]),
     "hm_engine_stream": (_vp, [_vp]),
@@ -285,6 +286,18 @@ def sample_token(logits, config: SamplingConfig, generated_ids: Sequence[int], r
     out = C.c_uint32(0)
     cfg = config._to_c()
     _check(lib.hm_sample_token(_ptr(lg), lg.size, C.byref(cfg), _ptr(gen), gen.size, C.byref(st), C.byref(out)))
+    return int(out.value), int(st.value)
+
+
+def sample_token_device(logits, config: SamplingConfig, generated_ids: Sequence[int], rng_state: int):
+    """The same sampler as one GPU kernel (temperature > 0, 1 <= top_k <= 1024).  Returns (token, new rng state)."""
+    lib = load_library()
+    lg = np.ascontiguousarray(logits, dtype=np.float32)
+    gen = np.ascontiguousarray(generated_ids, dtype=np.uint32)
+    st = C.c_uint64(rng_state)
+    out = C.c_uint32(0)
+    cfg = config._to_c()
+    _check(lib.hm_sample_token_device(_ptr(lg), lg.size, C.byref(cfg), _ptr(gen) if gen.size else None, gen.size, C.byref(st), C.byref(out)))
     return int(out.value), int(st.value)
 
 

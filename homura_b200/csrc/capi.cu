@@ -11,6 +11,7 @@
 #include "engine.h"
 #include "gemm_tc.h"
 #include "kquant.h"
+#include "sampler.h"
 #include "loaders.h"
 
 using namespace hm;
@@ -526,6 +527,30 @@ int hm_sample_token(const float* logits, int n, const hm_sampling* cfg, const ui
     if (!logits || n < 1 || !cfg || !rng_state || !out || (n_generated > 0 && !generated)) return gfail(HM_ERR_INVALID, "hm_sample_token: bad arguments");
     *out = host_sample_token(logits, n, *cfg, generated, n_generated, rng_state);
     return HM_OK;
+}
+int hm_sample_token_device(const float* logits, int n, const hm_sampling* cfg, const uint32_t* generated, int n_generated, uint64_t* rng_state, uint32_t* out) {
+    if (!logits || n < 1 || !cfg || !rng_state || !out || n_generated < 0 || (n_generated > 0 && !generated)) return gfail(HM_ERR_INVALID, "hm_sample_token_device: bad arguments");
+    if (!(cfg->temperature > 0.f) || cfg->top_k < 1 || cfg->top_k > SAMPLER_MAX_K)
+        return gfail(HM_ERR_UNSUPPORTED, "hm_sample_token_device: needs temperature > 0 and 1 <= top_k <= 1024 (use hm_sample_token otherwise)");
+    NEED_DEVICE();
+    Staging sg(nullptr);
+    SamplerArgs a{};
+    a.logits = sg.in(logits, (size_t)n);
+    a.ld_logits = n;
+    a.n = n;
+    a.cfg = *cfg;
+    a.generated = n_generated ? sg.in(generated, (size_t)n_generated) : nullptr;
+    a.n_generated = n_generated;
+    a.rng = (unsigned long long*)sg.scratch(8, false);
+    a.scaled = (float*)sg.scratch((size_t)n * 4, false);
+    a.count = (int*)sg.scratch((size_t)n * 4, true);
+    a.next_tok = (uint32_t*)sg.scratch(4, false);
+    if (!a.logits || !a.rng || !a.scaled || !a.count || !a.next_tok || (n_generated && !a.generated)) return sg.finish(cudaErrorMemoryAllocation);
+    sg.ok(cudaMemcpyAsync(a.rng, rng_state, 8, cudaMemcpyHostToDevice, nullptr));
+    cudaError_t ce = launch_sample(a, 1, nullptr);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(rng_state, a.rng, 8, cudaMemcpyDeviceToHost, nullptr);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(out, a.next_tok, 4, cudaMemcpyDeviceToHost, nullptr);
+    return sg.finish(ce);
 }
 int hm_time_decode(hm_engine* e, int warmup, int steps, float* ms_total) { return e ? e->impl->time_decode(warmup, steps, ms_total) : gfail(HM_ERR_INVALID, "null engine"); }
 int hm_profile_decode(hm_engine* e, int steps, hm_kernel_stat* out, int cap, int* n_out) {

@@ -2,6 +2,7 @@
 #include "engine.h"
 #include "gemm_tc.h"
 #include "kquant.h"
+#include "sampler.h"
 
 #include <algorithm>
 #include <cmath>
@@ -112,6 +113,7 @@ Engine::~Engine() {
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
+    fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_);
     fr(mk_layers_dev_); fr(mk_scratch_); fr(mk_bar_); fr(mk_trace_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
@@ -1344,6 +1346,67 @@ int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, 
             clock_gettime(CLOCK_REALTIME, &ts);
             rng = ((uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec) | 1ull;
         }
+        const char* hs = std::getenv("HM_HOST_SAMPLER");
+        const bool device_sampler = s.temperature > 0.f && s.top_k >= 1 && s.top_k <= SAMPLER_MAX_K && !(hs && hs[0] == '1');
+        if (device_sampler) {
+            // Sampled tokens never leave the device between steps: every step replays the decode graph
+            // (which also leaves the greedy token in the feed slot) and then the sampler kernel
+            // replaces it; EOS is looked for in blocks, as on the greedy path.
+            if (!smp_scaled_) {
+                HM_CUDA(cudaMalloc(&smp_scaled_, (size_t)batch_ * V_ * 4));
+                HM_CUDA(cudaMalloc(&smp_count_, (size_t)batch_ * V_ * 4));
+                HM_CUDA(cudaMemset(smp_count_, 0, (size_t)batch_ * V_ * 4));
+                HM_CUDA(cudaMalloc(&smp_rng_, (size_t)batch_ * 8));
+                HM_CUDA(cudaMalloc(&smp_gen_start_, (size_t)batch_ * 4));
+            }
+            const int32_t gstart = real_pos;  // the first generated token sits at the position after the prompt
+            HM_CUDA(cudaMemcpyAsync(smp_gen_start_ + seq, &gstart, 4, cudaMemcpyHostToDevice, stream_));
+            HM_CUDA(cudaMemcpyAsync(smp_rng_ + seq, &rng, 8, cudaMemcpyHostToDevice, stream_));
+            HM_CUDA(cudaMemcpyAsync(tokens_dev_ + seq, &first, 4, cudaMemcpyHostToDevice, stream_));
+            SamplerArgs sa{};
+            sa.logits = logits_;
+            sa.ld_logits = V_;
+            sa.n = V_;
+            sa.cfg = s;
+            sa.hist = hist_dev_;
+            sa.hist_stride = max_seq_ + 1;
+            sa.gen_start = smp_gen_start_;
+            sa.pos = pos_dev_;
+            sa.rng = smp_rng_;
+            sa.scaled = smp_scaled_;
+            sa.count = smp_count_;
+            sa.next_tok = next_dev_;
+            sa.feed_tok = tokens_dev_;
+            bool stop = false;
+            std::vector<uint32_t> blk(32);
+            while (!stop && (int)gen.size() < max_new && real_pos < max_seq_) {
+                const int want = std::min({32, max_new - (int)gen.size(), max_seq_ - real_pos});
+                for (int i = 0; i < want; ++i) {
+                    rc = launch_step();
+                    if (rc) return rc;
+                    const cudaError_t ce = launch_sample(sa, batch_, stream_);
+                    if (ce != cudaSuccess) return cuda_fail(ce, "sampler launch");
+                }
+                // the sampled tokens of the block are the history entries after the last known position
+                HM_CUDA(cudaMemcpyAsync(blk.data(), hist_dev_ + (size_t)seq * (max_seq_ + 1) + real_pos + 1, (size_t)want * 4, cudaMemcpyDeviceToHost, stream_));
+                HM_CUDA(cudaStreamSynchronize(stream_));
+                rc = check_step_error();
+                if (rc) return rc;
+                rc = check_device_error();
+                if (rc) return rc;
+                len_[seq] = real_pos + want;
+                for (int i = 0; i < want; ++i) {
+                    if (blk[i] == eos) {
+                        len_[seq] = real_pos + i + 1;  // tokens after EOS were speculative: roll the cache length back
+                        HM_CUDA(cudaMemcpy(pos_dev_ + seq, &len_[seq], 4, cudaMemcpyHostToDevice));
+                        stop = true;
+                        break;
+                    }
+                    gen.push_back(blk[i]);
+                }
+                real_pos = len_[seq];
+            }
+        } else {
         std::vector<float> logits(V_);
         uint32_t cur = first;
         for (int step = 1; step < max_new; ++step) {
@@ -1354,6 +1417,7 @@ int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, 
             real_pos += 1;
             if (cur == eos) break;
             gen.push_back(cur);
+        }
         }
     }
     std::memcpy(out_ids, gen.data(), gen.size() * 4);

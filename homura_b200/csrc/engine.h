@@ -147,6 +147,12 @@ class Engine {
 
     int only_class_ = -1;
 
+    // device-side sampler scratch (sampler.cu), allocated on first sampled generation
+    float* smp_scaled_ = nullptr;
+    int* smp_count_ = nullptr;
+    unsigned long long* smp_rng_ = nullptr;
+    int32_t* smp_gen_start_ = nullptr;
+
     // persistent decode kernel (decode_persistent.cu)
     bool use_persistent_ = false, persistent_direct_ = false;
     MkArgs mk_{};

@@ -1,0 +1,255 @@
+// Device-side sample_token (src/generate.rs:698-801): repetition / frequency / presence penalties,
+// temperature, softmax, min-p, descending sort, top-k, top-p, and the xorshift64 draw, one CTA per
+// sequence, so that sampled generation (the reference's default: temperature 0.7, top-k 50, top-p 0.9,
+// repetition penalty 1.1) never copies the logits to the host.
+//
+// The reference sorts the whole vocabulary and truncates to top_k; here the k-th largest scaled logit
+// is found by a 4-pass radix select on the float's order-preserving bit pattern, the <= k survivors are
+// gathered and sorted (probability descending, index ascending on ties -- the reference's unstable sort
+// leaves ties unspecified), and one thread walks them exactly as the reference walks its sorted list.
+// Supported for 1 <= top_k <= SAMPLER_MAX_K; other settings stay on the host sampler.
+//
+// Exactness: the penalties, the maximum, the candidate order and the integer RNG are exact; the
+// softmax denominator is a tree sum (the reference adds 151k terms in sequence) and expf differs from
+// the host's in the last ulp, so a probability can differ in its last bits and the draw can land on
+// the other side of a boundary in rare cases.
+#include "common.cuh"
+#include "sampler.h"
+
+namespace hm {
+namespace {
+
+constexpr int ST = 1024;  // threads per CTA
+
+__device__ __forceinline__ uint32_t order_key(float f) {  // ascending uint order == ascending float order
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float block_max(float v, float* sw) {
+    v = warp_max(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) sw[warp] = v;
+    __syncthreads();
+    float r = sw[0];
+    for (int i = 1; i < ST / 32; ++i) r = fmaxf(r, sw[i]);  // every thread, same order
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ float block_sum_fixed(float v, float* sw) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) sw[warp] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int i = 0; i < ST / 32; ++i) r += sw[i];  // fixed order: the result does not depend on scheduling
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
+    __shared__ float sw[ST / 32];
+    __shared__ int hist[256];
+    __shared__ unsigned long long cand[SAMPLER_MAX_K];  // (order key << 32) | ~index: descending = prob desc, index asc
+    __shared__ int tie_idx[SAMPLER_MAX_K];
+    __shared__ int n_cand, n_tie, s_k, s_bin;
+    __shared__ uint32_t s_prefix;
+
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int V = a.n;
+    const float* logits = a.logits + (size_t)b * a.ld_logits;
+    float* sl = a.scaled + (size_t)b * V;
+    int* count = a.count + (size_t)b * V;
+    const uint32_t* gen = a.hist ? a.hist + (size_t)b * a.hist_stride + a.gen_start[b] : a.generated;
+    const int ngen = a.hist ? max(0, a.pos[b] - a.gen_start[b]) : a.n_generated;
+    const bool pen = a.cfg.repetition_penalty != 1.0f || a.cfg.frequency_penalty != 0.0f || a.cfg.presence_penalty != 0.0f;
+
+    // ---- occurrences of every generated token (the penalties apply per occurrence / per count) ----
+    if (pen) {
+        for (int i = tid; i < ngen; i += ST) {
+            const uint32_t t = gen[i];
+            if (t < (uint32_t)V) atomicAdd(count + t, 1);
+        }
+        __syncthreads();
+    }
+
+    // ---- penalties, temperature, maximum ----
+    const float inv_temp = 1.0f / a.cfg.temperature;
+    float mx = -INFINITY;
+    for (int v = tid; v < V; v += ST) {
+        float l = logits[v];
+        if (pen) {
+            const int c = count[v];
+            if (c > 0) {
+                if (a.cfg.repetition_penalty != 1.0f)
+                    for (int r = 0; r < c; ++r) l = l > 0.0f ? l / a.cfg.repetition_penalty : l * a.cfg.repetition_penalty;
+                if (a.cfg.frequency_penalty != 0.0f || a.cfg.presence_penalty != 0.0f) {
+                    l -= a.cfg.frequency_penalty * (float)c;
+                    l -= a.cfg.presence_penalty;
+                }
+            }
+        }
+        l *= inv_temp;
+        sl[v] = l;
+        mx = fmaxf(mx, l);
+    }
+    mx = block_max(mx, sw);
+
+    // ---- softmax denominator ----
+    float part = 0.f;
+    for (int v = tid; v < V; v += ST) part += expf(sl[v] - mx);
+    const float sum = block_sum_fixed(part, sw);
+
+    // ---- radix select: order key of the k-th largest scaled logit ----
+    const int k = min(a.cfg.top_k, V);
+    if (tid == 0) {
+        s_prefix = 0u;
+        s_k = k;
+    }
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        const uint32_t mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+        for (int v = tid; v < V; v += ST) {
+            const uint32_t key = order_key(sl[v]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int need = s_k, bin = 255;
+            for (; bin > 0; --bin) {
+                if (hist[bin] >= need) break;
+                need -= hist[bin];
+            }
+            s_k = need;  // rank of the wanted key among those sharing the extended prefix
+            s_bin = bin;
+            s_prefix = prefix | ((uint32_t)bin << shift);
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = s_prefix;  // full key of the k-th largest; s_k of the entries equal to it are wanted
+    const int want_ties = s_k;
+
+    // ---- gather: everything above the k-th key, then the lowest-index ties ----
+    if (tid == 0) {
+        n_cand = 0;
+        n_tie = 0;
+    }
+    __syncthreads();
+    for (int v = tid; v < V; v += ST) {
+        const uint32_t key = order_key(sl[v]);
+        if (key > kth) {
+            const int slot = atomicAdd(&n_cand, 1);
+            if (slot < SAMPLER_MAX_K) cand[slot] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)v);
+        } else if (key == kth) {
+            const int slot = atomicAdd(&n_tie, 1);
+            if (slot < SAMPLER_MAX_K) tie_idx[slot] = v;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        // ties: ascending index, the first want_ties of them (n_tie is tiny except for degenerate logits)
+        const int nt = min(n_tie, SAMPLER_MAX_K);
+        for (int i = 1; i < nt; ++i) {
+            const int x = tie_idx[i];
+            int j = i - 1;
+            while (j >= 0 && tie_idx[j] > x) {
+                tie_idx[j + 1] = tie_idx[j];
+                --j;
+            }
+            tie_idx[j + 1] = x;
+        }
+        int nc = min(n_cand, SAMPLER_MAX_K);
+        for (int i = 0; i < min(want_ties, nt) && nc < SAMPLER_MAX_K; ++i) cand[nc++] = ((unsigned long long)kth << 32) | (uint32_t)(~(uint32_t)tie_idx[i]);
+        n_cand = nc;
+    }
+    __syncthreads();
+    const int nc = n_cand;
+    for (int i = nc + tid; i < SAMPLER_MAX_K; i += ST) cand[i] = 0ull;  // padding sorts last
+    __syncthreads();
+
+    // ---- bitonic sort, descending ----
+    for (int size = 2; size <= SAMPLER_MAX_K; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < SAMPLER_MAX_K; i += ST) {
+                const int j = i ^ stride;
+                if (j > i) {
+                    const bool desc = (i & size) == 0;
+                    const unsigned long long x = cand[i], y = cand[j];
+                    if (desc ? (x < y) : (x > y)) {
+                        cand[i] = y;
+                        cand[j] = x;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---- min-p, top-p, draw: one thread walks the sorted list as the reference does ----
+    if (tid == 0) {
+        float* probs = reinterpret_cast<float*>(tie_idx);  // reuse
+        for (int i = 0; i < nc; ++i) {
+            const int v = (int)(~(uint32_t)(cand[i] & 0xFFFFFFFFull));
+            probs[i] = expf(sl[v] - mx) / sum;
+        }
+        if (a.cfg.min_p > 0.0f && nc > 0) {
+            const float thr = a.cfg.min_p * probs[0];  // the largest probability is the first of the sorted list
+            for (int i = 0; i < nc; ++i)
+                if (probs[i] < thr) probs[i] = 0.0f;
+        }
+        float cumulative = 0.0f;
+        int cutoff = nc;
+        for (int i = 0; i < nc; ++i) {
+            cumulative += probs[i];
+            if (cumulative >= a.cfg.top_p) {
+                cutoff = i + 1;
+                break;
+            }
+        }
+        float total = 0.0f;
+        for (int i = 0; i < cutoff; ++i) total += probs[i];
+        unsigned long long s = a.rng[b];  // xorshift64 (13, 7, 17), src/generate.rs:634-641
+        s ^= s << 13;
+        s ^= s >> 7;
+        s ^= s << 17;
+        a.rng[b] = s;
+        const float r = ((float)(s >> 40) / (float)(1ull << 24)) * total;
+        float accum = 0.0f;
+        int pick = cutoff ? cutoff - 1 : 0;
+        for (int i = 0; i < cutoff; ++i) {
+            accum += probs[i];
+            if (accum >= r) {
+                pick = i;
+                break;
+            }
+        }
+        const uint32_t tok = nc ? (uint32_t)(~(uint32_t)(cand[pick] & 0xFFFFFFFFull)) : 0u;
+        a.next_tok[b] = tok;
+        if (a.feed_tok) a.feed_tok[b] = tok;
+        if (a.hist && a.pos) a.hist[(size_t)b * a.hist_stride + a.pos[b]] = tok;  // replaces the greedy token of this step
+    }
+
+    // ---- leave the occurrence counts clean for the next call ----
+    if (pen) {
+        __syncthreads();
+        for (int i = tid; i < ngen; i += ST) {
+            const uint32_t t = gen[i];
+            if (t < (uint32_t)V) count[t] = 0;
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_sample(const SamplerArgs& a, int batch, cudaStream_t st) {
+    if (a.cfg.top_k < 1 || a.cfg.top_k > SAMPLER_MAX_K || !(a.cfg.temperature > 0.f)) return cudaErrorInvalidValue;
+    sample_kernel<<<batch, ST, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace hm

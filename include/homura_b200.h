@@ -151,6 +151,12 @@ HM_API int hm_generate(hm_engine* e, int seq, const int64_t* prompt, int n_promp
 HM_API int hm_decode_greedy_n(hm_engine* e, const uint32_t* first_tokens, int steps, uint32_t* out_ids);
 /* sample_token, src/generate.rs:698-801, on host logits (state is the xorshift64 word). */
 HM_API int hm_sample_token(const float* logits, int n, const hm_sampling* cfg, const uint32_t* generated, int n_generated, uint64_t* rng_state, uint32_t* out);
+/* The same sampler as one GPU kernel (what hm_generate uses when 1 <= top_k <= 1024 and
+ * temperature > 0): logits may be a host or a device pointer.  Penalties, candidate order and the
+ * xorshift64 draw are exact; probabilities can differ from the host path in their last bits (tree
+ * sum, device expf), so in rare cases the draw falls on the other side of a boundary.
+ * HM_ERR_UNSUPPORTED outside that range of settings. */
+HM_API int hm_sample_token_device(const float* logits, int n, const hm_sampling* cfg, const uint32_t* generated, int n_generated, uint64_t* rng_state, uint32_t* out);
 
 /* ---- timing on the engine's stream (CUDA events) ------------------------------------ */
 /* Runs `steps` greedy decode steps after `warmup` untimed ones and reports the device time
