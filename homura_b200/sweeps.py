@@ -116,7 +116,7 @@ def projections(ms: list[int], peak_gbs: float, shapes=None, profile_launches: i
 ATTENTION_GEOMETRY = {"qwen3-0.6b": (16, 8, 128), "qwen2.5-0.5b": (14, 2, 64), "qwen2.5-1.5b": (12, 2, 128), "tinyllama-1.1b": (32, 4, 64)}
 
 
-def attention(kv_lens: list[int], batches: list[int], kv_dtype: str, peak_gbs: float, geometry: str = "qwen3-0.6b"):
+def attention(kv_lens: list[int], batches: list[int], kv_dtype: str, peak_gbs: float, geometry: str = "qwen3-0.6b", profile_launches: int = 0):
     heads, kvh, hd = ATTENTION_GEOMETRY[geometry]  # query heads, KV heads, head_dim
     page = 16
     rng = np.random.default_rng(6)
@@ -161,6 +161,14 @@ def attention(kv_lens: list[int], batches: list[int], kv_dtype: str, peak_gbs: f
                 if rc != 0:
                     raise hm.HomuraError(lib.hm_last_error_global())
 
+            if profile_launches:  # a few plain launches for a profiler run, no timing
+                for i in range(profile_launches):
+                    fn(i, None)
+                hm.dev_sync()
+                print(json.dumps({"sweep": "attention", "geometry": geometry, "kv_dtype": kv_dtype, "kv_len": L, "batch": B, "profile_launches": profile_launches}), flush=True)
+                for b in (kb, vb, pt, kl, q, out):
+                    b.free()
+                continue
             us, iters, mode = _time_launches(fn, n_rot, target_ms=20.0)
             alg = 2 * B * L * kvh * hd * esz
             gbs = alg / us / 1e3
@@ -178,14 +186,14 @@ def main(argv=None):
     ap.add_argument("--kv-dtype", choices=["f32", "bf16"], default="bf16")
     ap.add_argument("--geometry", choices=sorted(ATTENTION_GEOMETRY), default="qwen3-0.6b", help="attention: query heads / KV heads / head_dim of the named architecture")
     ap.add_argument("--shape", action="append", default=None, help="K,N of a projection; repeatable; default: the built-in shapes")
-    ap.add_argument("--profile-launches", type=int, default=0, help="projections: issue this many plain launches per case and exit (for ncu)")
+    ap.add_argument("--profile-launches", type=int, default=0, help="issue this many plain launches per case and exit (for ncu)")
     ap.add_argument("--hbm-peak-gbs", type=float, default=6545.6, help="copy bandwidth to report fractions against")
     a = ap.parse_args(argv)
     if a.which == "projections":
         shapes = [tuple(int(v) for v in sh.split(",")) for sh in a.shape] if a.shape else None
         projections(a.m, a.hbm_peak_gbs, shapes, a.profile_launches)
     else:
-        attention(a.kv_len, a.batch, a.kv_dtype, a.hbm_peak_gbs, a.geometry)
+        attention(a.kv_len, a.batch, a.kv_dtype, a.hbm_peak_gbs, a.geometry, a.profile_launches)
     return 0
 
 
