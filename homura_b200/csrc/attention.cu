@@ -205,8 +205,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32)
         l2_prefetch_slice(a.pf_ptr, a.pf_bytes, (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x), (int)(gridDim.x * gridDim.y * gridDim.z), tid);
-    pdl_wait();
 
+    // Lengths, positions and the page table were written before the launch chain of this step began,
+    // so the page range can be worked out before the dependency wait.  With early_pages set (decode:
+    // one row per sequence) the pages BELOW the one that receives this step's token are final too and
+    // their loads are issued now; the page of the new token (written by the preceding QKV kernel)
+    // and the query are read after the wait.
     const int seq = a.row_seq ? a.row_seq[m] : m;
     const int kvlen = a.kv_len ? a.kv_len[m] : a.row_pos[m] + 1;
     const int npages = (kvlen + PT - 1) / PT;
@@ -215,20 +219,25 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     const int32_t* pt = a.page_table + (size_t)seq * a.max_pages;
     const T* kpool = reinterpret_cast<const T*>(a.k_pool);
     const T* vpool = reinterpret_cast<const T*>(a.v_pool);
+    const int safe_end = a.early_pages ? min(p1, (kvlen - 1) / PT) : p0;  // pages [p0, safe_end) may be read early
 
     // cooperative tile loads: thread -> (slot, piece) pairs, the same mapping for every group
     const int total_pieces = nsub * TL::PIECES;  // per K (and per V), <= MAXP * ATT_THREADS
     uint4 kreg[MAXP], vreg[MAXP];
-    auto issue_loads = [&](int pbase) {
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        kreg[i] = make_uint4(0, 0, 0, 0);
+        vreg[i] = make_uint4(0, 0, 0, 0);
+    }
+    // loads the slots of the group starting at page pbase whose page lies in [lo, hi)
+    auto issue_loads = [&](int pbase, int lo, int hi) {
 #pragma unroll
         for (int i = 0; i < MAXP; ++i) {
             const int idx = tid + i * ATT_THREADS;
-            kreg[i] = make_uint4(0, 0, 0, 0);
-            vreg[i] = make_uint4(0, 0, 0, 0);
             if (idx < total_pieces) {
                 const int slot = idx / TL::PIECES, piece = idx % TL::PIECES;
                 const int p = pbase + slot;
-                if (p < p1) {
+                if (p >= lo && p < hi) {
                     const size_t tile = ((size_t)pt[p] * a.kv_heads + kvh) * PT * HD;
                     kreg[i] = __ldg(reinterpret_cast<const uint4*>(kpool + tile) + piece);
                     vreg[i] = __ldg(reinterpret_cast<const uint4*>(vpool + tile) + piece);
@@ -236,6 +245,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
             }
         }
     };
+    if (p0 < safe_end) issue_loads(p0, p0, safe_end);
+    pdl_wait();
     auto store_tiles = [&]() {
 #pragma unroll
         for (int i = 0; i < MAXP; ++i) {
@@ -251,7 +262,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
         }
     };
 
-    if (p0 < p1) issue_loads(p0);
+    if (p0 < p1) issue_loads(p0, max(p0, safe_end), p1);
     for (int i = tid; i < g * HD; i += ATT_THREADS) q_s[i] = a.q[(size_t)m * a.heads * HD + head0 * HD + i];
 
     const int j = warp % g, sub = warp / g;  // this warp's query head and page slot
@@ -266,7 +277,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
         __syncthreads();  // previous group's tiles are no longer being read (also publishes q_s)
         store_tiles();
         __syncthreads();
-        if (pb + nsub < p1) issue_loads(pb + nsub);  // next group in flight during the math
+        if (pb + nsub < p1) issue_loads(pb + nsub, pb + nsub, p1);  // next group in flight during the math
         const int p = pb + sub;
         if (active && p < p1) {
             const float* kt = tiles + sub * TL::SLOT_FLOATS;

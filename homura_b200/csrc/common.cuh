@@ -174,6 +174,7 @@ struct GemvArgs {
 struct AttnArgs {
     const void* pf_ptr;  // optional: weights of a later kernel to pull into the L2
     unsigned long long pf_bytes;
+    int early_pages;     // 1: every row is its own sequence (decode), so the pages below the one of the new token may be read before the dependency wait
     int stream_pages;    // > 0: long contexts may use the bulk-copy ring variant (pages per CTA decided from max_pages / nsplit)
     int* err_flag;       // raised to 2 when a bounded wait of that variant runs out
     const float* q;       // [M][heads*hd]

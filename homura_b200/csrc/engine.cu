@@ -941,6 +941,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.nsplit = std::min(att_nsplit_, att_cluster_ ? std::max(1, (2 * sm_count_ + M * kvh_ - 1) / (M * kvh_)) : attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));
         at.cluster = att_cluster_ ? 1 : 0;
         at.stream_pages = 1;
+        at.early_pages = row_seq == nullptr ? 1 : 0;  // decode passes: one row per sequence; prefill chunks write several positions of one sequence
         at.err_flag = err_flag_;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
         at.out = attn_;
