@@ -20,6 +20,8 @@
 #include <mutex>
 
 #include "../../include/homura_b200.h"
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace hm {
@@ -422,7 +424,8 @@ void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_p
 // max_cluster, at least 32 rows each.
 void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* cluster, int* rows_per_split) {
     const int nslabs = (N + SLAB - 1) / SLAB;
-    int cs = (2 * sm_count) / nslabs;  // two CTAs per SM resident at once
+    static const int per_sm = [] { const char* e = std::getenv("HM_GEMV_CTAS_PER_SM"); const int v = e ? std::atoi(e) : 0; return v >= 1 && v <= 8 ? v : 2; }();
+    int cs = (per_sm * sm_count) / nslabs;  // two CTAs per SM resident at once (tuning knob: HM_GEMV_CTAS_PER_SM)
     if (cs > max_cluster) cs = max_cluster;
     if (cs < 1) cs = 1;
     while (cs > 1 && K / cs < 32) --cs;
