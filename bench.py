@@ -171,6 +171,13 @@ def dist_setup(n_gpus):
 
 def cpu_sample(d, cfg, steps, warmup, prompt_len):
     """Decode tokens/s of the CPU oracle on the same checkpoint (all host threads, one sequence)."""
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host core this
+    # process may run on, so the variable is reset before the OpenMP runtime of the oracle library loads
+    try:
+        ncores = len(os.sched_getaffinity(0))
+    except Exception:
+        ncores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(ncores)
     import oracle as orc
     from homura_b200 import synth
 
