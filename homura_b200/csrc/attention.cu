@@ -63,6 +63,14 @@ __device__ __forceinline__ void unpack_store(float* o, const uint4& v) {
 // Merge the per-warp (max, sum, acc) triples of a CTA (warp = page slot * g + query head), then the
 // splits of the (row, KV head): through the cluster (rank 0 reads its peers' shared memory in rank
 // order), or through global scratch by whichever CTA arrives last at the ticket.
+// Attention output of (row m, head, dim d): f32 [rows][heads * hd], or straight into the packed
+// activation tiles of the O-projection's tensor-core GEMM.
+template <int HD>
+__device__ __forceinline__ void store_out(const AttnArgs& a, int m, int head, int d, float v) {
+    if (a.xp_out) tc_xpack_store(a.xp_out, a.xp_mpad, m, head * HD + d, v);
+    else a.out[(size_t)m * a.heads * HD + head * HD + d] = v;
+}
+
 template <int HD, bool CL>
 __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p);
 
@@ -116,7 +124,7 @@ __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsu
                 c_ml[jj * 2 + 1] = l;
             }
         } else if (a.nsplit == 1) {
-            a.out[(size_t)m * a.heads * HD + head * HD + d] = o / l;
+            store_out<HD>(a, m, head, d, o / l);
         } else {
             const size_t pi = ((size_t)m * a.heads + head) * a.nsplit + split;
             a.part_acc[pi * HD + d] = o;
@@ -144,7 +152,7 @@ __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsu
                         o = fmaf(ld_dsmem_f32(dsmem_addr(c_o + i, (uint32_t)r)), sc, o);
                     }
                 }
-                a.out[(size_t)m * a.heads * HD + (head0 + jj) * HD + d] = o / l;
+                store_out<HD>(a, m, head0 + jj, d, o / l);
             }
         }
         cluster_sync_all();
@@ -176,7 +184,7 @@ __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsu
                 o = fmaf(ld_cg_f32(a.part_acc + (base + s2) * HD + d), sc, o);
             }
         }
-        a.out[(size_t)m * a.heads * HD + head * HD + d] = o / l;
+        store_out<HD>(a, m, head, d, o / l);
     }
     if (tid == 0) a.tickets[m * a.kv_heads + kvh] = 0u;
 }

@@ -119,6 +119,24 @@ enum Epilogue { EPI_STORE = 0, EPI_QKV_ROPE = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 
 __host__ __device__ __forceinline__ int k_tile_off(int t, int d) { return ((((d >> 2) << 4) + t) << 2) | (d & 3); }
 __host__ __device__ __forceinline__ int v_tile_off(int t, int d, int hd) { return t * hd + d; }
 
+// One activation value into the packed bf16 x 3 tile image the tensor-core GEMM copies in bulk
+// (gemm_tc.cu: [k-block][term][mpad rows][64 k], rows of 128 B, 16-byte chunks XOR-swizzled by row & 7):
+// lets a producer kernel hand its output to that GEMM without a packing launch in between.
+__device__ __forceinline__ void tc_xpack_store(unsigned char* xp, int mpad, int m, int k, float v) {
+    const uint16_t h = f32_to_bf16_rne(v);
+    const float r1 = v - bf16_bits_to_f32(h);
+    const uint16_t md = f32_to_bf16_rne(r1);
+    const uint16_t lo = f32_to_bf16_rne(r1 - bf16_bits_to_f32(md));
+    const int kb = k >> 6, kk = k & 63, chunk = kk >> 3, e = kk & 7;
+    unsigned char* tile = xp + (size_t)kb * (3 * mpad * 128);
+    const uint16_t term[3] = {h, md, lo};
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        const int row = t * mpad + m;
+        *reinterpret_cast<uint16_t*>(tile + (size_t)row * 128 + ((chunk ^ (row & 7)) << 4) + e * 2) = term[t];
+    }
+}
+
 struct KvDesc {
     void* k_pool;            // this layer's K pages [n_pages][kv_heads][page_tokens][hd]
     void* v_pool;
@@ -174,6 +192,8 @@ struct GemvArgs {
 struct AttnArgs {
     const void* pf_ptr;  // optional: weights of a later kernel to pull into the L2
     unsigned long long pf_bytes;
+    unsigned char* xp_out;  // optional: write the output as packed tensor-core activations (tc_xpack_store) instead of `out`
+    int xp_mpad;
     int early_pages;     // 1: every row is its own sequence (decode), so the pages below the one of the new token may be read before the dependency wait
     int stream_pages;    // > 0: long contexts may use the bulk-copy ring variant (pages per CTA decided from max_pages / nsplit)
     int* err_flag;       // raised to 2 when a bounded wait of that variant runs out

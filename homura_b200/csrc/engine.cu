@@ -109,7 +109,7 @@ Engine::~Engine() {
         for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->tc); fr(w->scales); fr(w->codes); fr(w->kq_data); fr(w->kq_tile_type); }
     }
     fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes); fr(lm_head_.kq_data); fr(lm_head_.kq_tile_type);
-    fr(xpack_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
+    fr(xpack_); fr(xpack_attn_); fr(xpack_act_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
@@ -407,6 +407,8 @@ int Engine::ensure_scratch(int rows) {
         if (tall) {
             xpack_bytes_ = tc_xpack_bytes(TC_ROWS, std::max(std::max(H_, qdim_), I_));
             HM_CUDA(re(&xpack_, xpack_bytes_));
+            HM_CUDA(re(&xpack_attn_, tc_xpack_bytes(TC_ROWS, qdim_)));
+            HM_CUDA(re(&xpack_act_, tc_xpack_bytes(TC_ROWS, I_)));
         }
     }
     // split-K scratch sized for the worst projection at M = 8
@@ -728,14 +730,17 @@ static int pad_m(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 // Projection over up to TC_ROWS rows per launch on the tensor cores (gemm_tc.cu): one kernel packs
 // the activations (folding an RMSNorm when norm_w is given), the GEMM applies bias and residual on store.
 int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos,
-                              const int32_t* row_seq, int* launches) {
+                              const int32_t* row_seq, int* launches, const unsigned char* prepacked, unsigned char* pack_out) {
     if (!L.tc) return fail(HM_ERR_STATE, "tensor-core weight copy missing");
     for (int m0 = 0; m0 < M; m0 += TC_ROWS) {
         const int mc = std::min(TC_ROWS, M - m0);
         if (tc_xpack_bytes(mc, L.K) > xpack_bytes_) return fail(HM_ERR_STATE, "activation pack scratch too small");
-        cudaError_t ce = launch_tc_pack_x(x + (size_t)m0 * ldx, ldx, mc, L.K, norm_w, (float)cfg_.rms_norm_eps, xpack_, stream_, pdl_);
-        if (ce != cudaSuccess) return cuda_fail(ce, "activation pack launch");
-        ++*launches;
+        cudaError_t ce = cudaSuccess;
+        if (!prepacked) {  // the producer did not write the tile image itself
+            ce = launch_tc_pack_x(x + (size_t)m0 * ldx, ldx, mc, L.K, norm_w, (float)cfg_.rms_norm_eps, xpack_, stream_, pdl_);
+            if (ce != cudaSuccess) return cuda_fail(ce, "activation pack launch");
+            ++*launches;
+        }
         TcArgs a{};
         a.W = L.tc;
         a.K = L.K;
@@ -743,7 +748,9 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
         a.N = L.N;
         a.M = mc;
         a.ksplit = tc_pick_split(L.K, L.N, sm_count_);
-        a.xp = xpack_;
+        a.xp = prepacked ? prepacked : xpack_;
+        a.xp_out = pack_out;
+        a.xp_mpad = tc_mpad(mc);
         a.epi = epi;
         a.bias = bias;
         a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
@@ -941,6 +948,13 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.nsplit = std::min(att_nsplit_, att_cluster_ ? std::max(1, (2 * sm_count_ + M * kvh_ - 1) / (M * kvh_)) : attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));
         at.cluster = att_cluster_ ? 1 : 0;
         at.stream_pages = 1;
+        // passes of 9..64 rows: the attention output and the SwiGLU output go straight into the packed
+        // activation tiles of the next tensor-core GEMM (no packing launch in between)
+        const bool direct_pack = tall && M <= TC_ROWS && qdim_ % 64 == 0 && I_ % 64 == 0;
+        if (direct_pack) {
+            at.xp_out = xpack_attn_;
+            at.xp_mpad = tc_mpad(M);
+        }
         at.early_pages = row_seq == nullptr ? 1 : 0;  // decode passes: one row per sequence; prefill chunks write several positions of one sequence
         at.err_flag = err_flag_;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
@@ -958,7 +972,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             ++*launches;
         }
         if (want(PC_O) && tall) {
-            rc = enqueue_linear_tc(w.o, M, attn_, qdim_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches);
+            rc = enqueue_linear_tc(w.o, M, attn_, qdim_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches, direct_pack ? xpack_attn_ : nullptr);
             if (rc) return rc;
         } else if (want(PC_O)) {
             prefetch(&w.down);
@@ -967,7 +981,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         }
         if (!want(PC_GATE_UP)) {
         } else if (tall) {
-            rc = enqueue_linear_tc(w.gu, M, h_, H_, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, launches);
+            rc = enqueue_linear_tc(w.gu, M, h_, H_, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, launches, nullptr, direct_pack ? xpack_act_ : nullptr);
             if (rc) return rc;
         } else if (w.gu.kind == HM_BF16) {
             if (l + 1 < L_) prefetch(&layers_[l + 1].qkv);
@@ -980,7 +994,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             if (rc) return rc;
         }
         if (want(PC_DOWN) && tall) {
-            rc = enqueue_linear_tc(w.down, M, act_, I_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches);
+            rc = enqueue_linear_tc(w.down, M, act_, I_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches, direct_pack ? xpack_act_ : nullptr);
             if (rc) return rc;
         } else if (want(PC_DOWN)) {
             if (l + 1 == L_ && lm_rows > 0) prefetch(&lm_head_, LM_PF, LM_PF);

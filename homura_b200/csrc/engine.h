@@ -80,7 +80,8 @@ class Engine {
     // sequence).  lm_row0/lm_rows select the rows that go through the LM head.
     int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);
     int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches);
-    int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, int* launches);
+    int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, int* launches,
+                          const unsigned char* prepacked = nullptr, unsigned char* pack_out = nullptr);
     int capture_decode_graph();
     int setup_persistent();   // batch-1 bf16 models: one cooperative launch per decode step
     int launch_step();        // replay the captured graph, or launch the persistent kernel directly
@@ -112,6 +113,7 @@ class Engine {
     int scratch_rows_ = 0;
     float *h_ = nullptr, *q_ = nullptr, *attn_ = nullptr, *act_ = nullptr, *qkv_raw_ = nullptr, *gu_raw_ = nullptr, *logits_ = nullptr;
     unsigned char* xpack_ = nullptr;  // packed activations of one tensor-core projection (gemm_tc.h)
+    unsigned char *xpack_attn_ = nullptr, *xpack_act_ = nullptr;  // written directly by the attention kernel / the SwiGLU epilogue
     size_t xpack_bytes_ = 0;
     float* amax_val_ = nullptr;
     int32_t* amax_idx_ = nullptr;

@@ -150,7 +150,9 @@ __device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, in
             const int m = m_lo + idx / 64, c = idx % 64, j = nblk * 64 + c;
             if (j < a.N / 2) {
                 const float g = tile[m * BM + c], u = tile[m * BM + 64 + c];
-                a.y[(size_t)m * a.ldy + j] = (g / (1.0f + expf(-g))) * u;
+                const float act = (g / (1.0f + expf(-g))) * u;
+                if (a.xp_out) tc_xpack_store(a.xp_out, a.xp_mpad, m, j, act);
+                else a.y[(size_t)m * a.ldy + j] = act;
             }
         }
     } else if (a.epi == EPI_LOGITS) {
@@ -376,7 +378,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 
 }  // namespace
 
-static int tc_mpad(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+int tc_mpad(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
 static int tc_nstage(int mpad) { return mpad == 64 ? 4 : 6; }
 static size_t tc_smem_for(int mpad) { return (size_t)tc_nstage(mpad) * (W_TILE + (size_t)TERMS * mpad * 128) + (size_t)mpad * BM * 4 + 1024; }
 size_t tc_packed_elems(int K, int N) { return (size_t)((N + BM - 1) / BM) * ((K + BK - 1) / BK) * BM * BK; }

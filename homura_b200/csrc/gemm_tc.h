@@ -21,6 +21,8 @@ struct TcArgs {
     const float* resid;      // optional [M][ldy], added as resid + y
     float* y;                // [M][ldy]
     int ldy;
+    unsigned char* xp_out;   // EPI_SWIGLU only, optional: write the result as packed activations for the next GEMM instead of y
+    int xp_mpad;
     // EPI_QKV_ROPE
     int q_dim, kv_dim, hd, has_qk_norm;
     float eps;
@@ -36,6 +38,7 @@ struct TcArgs {
 size_t tc_xpack_bytes(int M, int K);  // bytes of the packed activations of M rows
 size_t tc_packed_elems(int K, int N);  // bf16 elements of the packed weight (both dims padded)
 int tc_padded_k(int K);
+int tc_mpad(int M);  // rows padded to 16 / 32 / 64
 int tc_pick_split(int K, int N, int sm_count);  // cluster size that fills the SMs once
 // f32 rows -> three bf16 terms per element in the tile layout the GEMM copies in bulk; folds an
 // RMSNorm (weight norm_w, epsilon eps) when norm_w is not NULL.
