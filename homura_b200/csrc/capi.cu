@@ -648,7 +648,7 @@ int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, int K, i
 }
 
 int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int ksplit, float* y, void* stream) {
-    if (!x || !w_tc || !y || M < 1 || M > 64 || K < 1 || N < 1 || ksplit < 0 || ksplit > 8) return gfail(HM_ERR_INVALID, "hm_gemm_bf16_tc: bad arguments (1 <= M <= 64, 0 <= ksplit <= 8)");
+    if (!x || !w_tc || !y || M < 1 || M > 64 || K < 1 || N < 1 || ksplit < 0 || ksplit > 16) return gfail(HM_ERR_INVALID, "hm_gemm_bf16_tc: bad arguments (1 <= M <= 64, 0 <= ksplit <= 16)");
     NEED_DEVICE();
     cudaStream_t st = (cudaStream_t)stream;
     Staging sg(st);

@@ -22,6 +22,8 @@
 //     with complete 128-column rows for its share of the rows and runs the epilogue on them.
 // Roles: warp 0 = bulk-copy producer, warp 1 = TMEM owner + MMA issuer, warps 2-5 = activation
 // staging (f32 -> 3 x bf16, swizzled) and epilogue.  Every mbarrier wait is bounded.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_tc.h"
 #include "mbarrier.cuh"
@@ -386,8 +388,9 @@ int tc_padded_k(int K) { return (K + BK - 1) / BK * BK; }
 size_t tc_xpack_bytes(int M, int K) { return (size_t)(tc_padded_k(K) / BK) * TERMS * tc_mpad(M) * 128; }
 int tc_pick_split(int K, int N, int sm_count) {
     const int nblk = (N + BM - 1) / BM, kb = (K + BK - 1) / BK;
+    static const int cap = [] { const char* e = std::getenv("HM_TC_MAX_SPLIT"); const int v = e ? std::atoi(e) : 0; return v >= 1 && v <= 16 ? v : 8; }();  // tuning knob; clusters above 8 (non-portable size) measured slower
     int s = sm_count / nblk;  // CTAs per n-block that still fit one wave (1 CTA per SM)
-    if (s > 8) s = 8;
+    if (s > cap) s = cap;
     while (s > 1 && kb / s < 4) --s;  // keep at least 4 k-blocks per CTA
     return s < 1 ? 1 : s;
 }
@@ -436,7 +439,13 @@ cudaError_t launch_gemm_tc(const TcArgs& a_in, cudaStream_t st, bool pdl) {
         ++n;
     }
     if (cl) {
-        if (a.ksplit > 8) return cudaErrorInvalidValue;
+        if (a.ksplit > 16) return cudaErrorInvalidValue;
+        static bool nonportable_set = false;
+        if (a.ksplit > 8 && !nonportable_set) {  // clusters of 9..16 CTAs are allowed on request
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return e;
+            nonportable_set = true;
+        }
         at[n].id = cudaLaunchAttributeClusterDimension;
         at[n].val.clusterDim.x = (unsigned)a.ksplit;
         at[n].val.clusterDim.y = 1;

@@ -13,7 +13,7 @@ struct TcArgs {
     const uint16_t* W;  // swizzled K-major tiles [n-block][k-block][128][64] bf16 (launch_pack_tc)
     int K, Kp, N;       // contraction length, K rounded up to 64, output features
     int M;              // activation rows, 1..64
-    int ksplit;         // CTAs per cluster sharing one n-block (1 = no split, at most 8)
+    int ksplit;         // CTAs per cluster sharing one n-block (1 = no split, at most 16)
     const unsigned char* xp;  // activations packed by launch_tc_pack_x (tc_xpack_bytes(M, K) bytes)
     int mpad, nstage, tmem_cols;  // filled in by launch_gemm_tc
     int epi;                 // EPI_STORE (bias, residual), EPI_SWIGLU, EPI_LOGITS or EPI_QKV_ROPE: as in GemvArgs

@@ -207,7 +207,7 @@ HM_API int hm_pack_bf16_slabs(const void* w_kn, int K, int N, void* dst, void* s
  * accumulator in tensor memory).  w_tc is the weight packed by hm_pack_bf16_tc.  f32 activations are
  * split into three bf16 terms inside the kernel, so results agree with the f32 x bf16 product of
  * emit_linalg.rs:1928-2008 to f32 rounding (accumulation order differs from the CPU loop).
- * ksplit = CTAs per 128-feature block sharing K through a thread-block cluster: 0 = choose, else 1..8. */
+ * ksplit = CTAs per 128-feature block sharing K through a thread-block cluster: 0 = choose, else 1..16. */
 HM_API int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int ksplit, float* y, void* stream);
 /* Elements (bf16) of the packed tensor-core weight for a [K,N] matrix: both dims padded to tiles. */
 HM_API size_t hm_tc_packed_elems(int K, int N);

@@ -49,7 +49,7 @@ def test_gemm_tc_matches_oracle(hm, oracle, K, N, M):
     # deterministic: fixed-order cluster reduction
     np.testing.assert_array_equal(got, hm.gemm_bf16_tc(x, wt, N))
     # every split factor computes the same product
-    for ks in (1, 2, 4, 8):
+    for ks in (1, 2, 4, 8, 12, 16):
         assert rel_err(hm.gemm_bf16_tc(x, wt, N, ksplit=ks), want) < 2e-5
 
 
@@ -63,7 +63,7 @@ def test_gemm_tc_ragged_and_limits(hm, oracle):
     with pytest.raises(hm.HomuraError):
         hm.gemm_bf16_tc(np.ones((65, 64), np.float32), w, 128)  # M > 64
     with pytest.raises(hm.HomuraError):
-        hm.gemm_bf16_tc(np.ones((4, 64), np.float32), w, 128, ksplit=9)
+        hm.gemm_bf16_tc(np.ones((4, 64), np.float32), w, 128, ksplit=17)
 
 
 def test_gemm_tc_keeps_f32_activation_precision(hm, oracle):
