@@ -57,6 +57,12 @@ __device__ __forceinline__ void l2_prefetch_slice(const void* base, unsigned lon
     }
 }
 
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -149,6 +155,7 @@ struct KvDesc {
 };
 
 struct GemvArgs {
+    unsigned long long* trace;     // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA 0 of this launch
     const void* pf_ptr;            // optional: weights of a later kernel to pull into the L2 (see l2_prefetch_slice)
     unsigned long long pf_bytes;
     // weights: element (k, n) of slab s = n / 128 at byte  s*slab_stride + k*row_stride + (n%128)*2

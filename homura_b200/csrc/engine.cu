@@ -113,7 +113,7 @@ Engine::~Engine() {
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
-    fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_);
+    fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_);
     fr(mk_layers_dev_); fr(mk_scratch_); fr(mk_bar_); fr(mk_trace_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
@@ -501,6 +501,12 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     HM_CUDA(cudaMemset(att_tickets_, 0, (size_t)scratch_rows_ * kvh_ * 4));
     // The persistent single-launch decode kernel is opt-in (HM_PERSISTENT=1): on this hardware its
     // step time is no better than the captured kernel chain, which stays the default.
+    if (const char* gt = std::getenv("HM_GEMV_TRACE")) {
+        if (gt[0] == '1' && !gemv_trace_) {
+            HM_CUDA(cudaMalloc(&gemv_trace_, 512 * 8 * sizeof(unsigned long long)));
+            HM_CUDA(cudaMemset(gemv_trace_, 0, 512 * 8 * sizeof(unsigned long long)));
+        }
+    }
     const char* mega = std::getenv("HM_PERSISTENT");
     if (mega && mega[0] == '1') {
         rc = setup_persistent();
@@ -791,6 +797,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
         if (L.kind == HM_BF16) {
             GemvArgs a{};
             a.W = L.slabs;
+            if (gemv_trace_ && *launches < 512) a.trace = gemv_trace_ + (size_t)*launches * 8;
             if (m0 == 0) {
                 a.pf_ptr = pf_ptr_;
                 a.pf_bytes = pf_bytes_;
@@ -1217,6 +1224,32 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
         const double lm = (double)(t[5 * L_ + 1] - t[5 * L_]);
         std::fprintf(stderr, "[hm trace] per-layer mean us: qkv %.2f attn %.2f o %.2f gate_up %.2f down %.2f | lm_head %.2f | step %.2f\n", sum[0] / L_ / 1e3, sum[1] / L_ / 1e3,
                      sum[2] / L_ / 1e3, sum[3] / L_ / 1e3, sum[4] / L_ / 1e3, lm / 1e3, (double)(t[5 * L_ + 1] - t[0]) / 1e3);
+    }
+    if (gemv_trace_) {
+        // HM_GEMV_TRACE=1: %globaltimer stamps of CTA 0 of every projection launch of the last step:
+        // resident -> predecessor done -> activations staged -> weights multiplied -> partials published ->
+        // split-K reduced -> stored.  Averaged per launch position within a layer.
+        std::vector<unsigned long long> t(512 * 8);
+        HM_CUDA(cudaMemcpy(t.data(), gemv_trace_, t.size() * 8, cudaMemcpyDeviceToHost));
+        // launch indices of the projections in a decode pass: 1 + l*5 + {0: qkv, 2: o, 3: gate_up, 4: down}, then 1 + 5L: LM head
+        const char* names[4] = {"qkv", "o", "gate_up", "down"};
+        const int offs[4] = {0, 2, 3, 4};
+        for (int c = 0; c < 4; ++c) {
+            double d[6] = {0, 0, 0, 0, 0, 0}, gap = 0;
+            int n = 0;
+            for (int l = 0; l < L_; ++l) {
+                const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + offs[c]) * 8;
+                if (!r[0] || !r[6]) continue;
+                for (int i = 0; i < 6; ++i) d[i] += (double)(r[i + 1] - r[i]);
+                // time from the previous projection's store to this one seeing its predecessor done (attention sits between qkv and o)
+                const int prev = c == 0 ? (l == 0 ? -1 : 1 + (l - 1) * 5 + 4) : 1 + l * 5 + offs[c - 1];
+                if (prev >= 0 && t[(size_t)prev * 8 + 6]) gap += (double)(r[1] - t[(size_t)prev * 8 + 6]);
+                ++n;
+            }
+            if (n)
+                std::fprintf(stderr, "[hm gemv trace] %-8s resident->dep %.2f | stage x %.2f | multiply %.2f | publish+cluster barrier %.2f | reduce %.2f | epilogue %.2f | prev store -> dep seen %.2f us (mean of %d)\n", names[c],
+                             d[0] / n / 1e3, d[1] / n / 1e3, d[2] / n / 1e3, d[3] / n / 1e3, d[4] / n / 1e3, d[5] / n / 1e3, gap / n / 1e3, n);
+        }
     }
     for (int b = 0; b < batch_; ++b) len_[b] += warmup + steps;
     return HM_OK;

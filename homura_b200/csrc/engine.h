@@ -148,6 +148,7 @@ class Engine {
     int launches_per_step_ = 0;
 
     int only_class_ = -1;
+    unsigned long long* gemv_trace_ = nullptr;  // HM_GEMV_TRACE=1: [512][8] timestamps, one row per projection launch of a pass
 
     // device-side sampler scratch (sampler.cu), allocated on first sampled generation
     float* smp_scaled_ = nullptr;

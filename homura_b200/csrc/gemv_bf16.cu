@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     const char* wbase = (const char*)a.W + (long long)slab * a.slab_stride + (long long)(k0 + rl) * a.row_stride + cg * 16;
     const long long pass_stride = (long long)ROWS_PER_PASS * a.row_stride;
 
+    const bool tr = a.trace != nullptr && blockIdx.x == 0 && tid == 0;
+    if (tr) a.trace[0] = global_timer();  // CTA resident
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32) l2_prefetch_slice(a.pf_ptr, a.pf_bytes, blockIdx.x, gridDim.x, tid);
 
@@ -85,6 +87,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     }
 
     pdl_wait();
+    if (tr) a.trace[1] = global_timer();  // predecessor complete
 
     // ---- prologue: activation slice [k0, k0+nrows) of every row into shared memory ----
     if (a.pro == PRO_RMSNORM) {
@@ -125,6 +128,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
         }
     }
     __syncthreads();
+    if (tr) a.trace[2] = global_timer();  // activations in shared memory
 
     // ---- main loop: stream the slab run, 8 column accumulators per row per thread ----
     float acc[M][8];
@@ -150,6 +154,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
         }
     }
 
+    if (tr) a.trace[3] = global_timer();  // weights multiplied
     // ---- reduce the 16 row lanes: xor-16 shuffle, then across the 8 warps in smem ----
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -188,6 +193,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
             if (idx < M * SLAB) vals[idx] = mine[i];
         }
         cluster_sync_all();
+        if (tr) a.trace[4] = global_timer();  // all ranks' partials published
         const uint32_t rank = cluster_ctarank();
         if (rank == 0) {
 #pragma unroll
@@ -239,6 +245,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     }
     __syncthreads();
 
+    if (tr) a.trace[5] = global_timer();  // split-K reduced
     // ---- epilogues on vals[M][128] (columns n0 .. n0+127 of the output) ----
     const int n0 = slab * SLAB;
     if (a.epi == EPI_STORE) {
@@ -349,6 +356,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
             }
         }
     }
+    if (tr) a.trace[6] = global_timer();  // epilogue stored
 }
 
 template <int M, bool CL>
