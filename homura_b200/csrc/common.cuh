@@ -34,6 +34,9 @@ __device__ __forceinline__ uint32_t dsmem_addr(const void* p, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
     return remote;
 }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -155,6 +158,7 @@ struct KvDesc {
 };
 
 struct GemvArgs {
+    int xfull;                     // set by the launcher: RMSNorm prologue stages the whole rows in shared memory (one L2 trip)
     unsigned long long* trace;     // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA 0 of this launch
     const void* pf_ptr;            // optional: weights of a later kernel to pull into the L2 (see l2_prefetch_slice)
     unsigned long long pf_bytes;

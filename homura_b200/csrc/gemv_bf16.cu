@@ -56,6 +56,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     const int rps = a.rows_per_split;
     float* xs = smem;                 // [M][rps]
     float* red = smem + M * rps;      // [8][M][128], later vals[M][128]
+    float* slots = red + 8 * M * SLAB;  // cluster variant, rank 0: [ksplit][M][128] partials pushed by the ranks
+    // RMSNorm prologue: the whole rows, read once (sum of squares and the slice come from the same load)
+    float* xfull = CL ? slots + a.ksplit * M * SLAB : slots;  // [M][K] when it fits (a.xfull)
     __shared__ float s_inv[MAX_M];
     __shared__ float s_warp[8][MAX_M];
     __shared__ int s_last;
@@ -98,6 +101,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
             const float* xr = a.x + (size_t)m * a.ldx;
             for (int k = tid; k < a.K; k += GEMV_THREADS) {
                 float v = __ldg(xr + k);
+                if (a.xfull) xfull[m * a.K + k] = v;  // one trip to the L2 for both the sum and the slice
                 s = fmaf(v, v, s);
             }
             ss[m] = warp_sum(s);
@@ -118,7 +122,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
         for (int m = 0; m < M; ++m) {
             const float inv = s_inv[m];
             const float* xr = a.x + (size_t)m * a.ldx + k0;
-            for (int r = tid; r < nrows; r += GEMV_THREADS) xs[m * rps + r] = (__ldg(xr + r) * inv) * __ldg(a.norm_w + k0 + r);
+            for (int r = tid; r < nrows; r += GEMV_THREADS) {
+                const float xv = a.xfull ? xfull[m * a.K + k0 + r] : __ldg(xr + r);
+                xs[m * rps + r] = (xv * inv) * __ldg(a.norm_w + k0 + r);
+            }
         }
     } else {
 #pragma unroll
@@ -186,32 +193,31 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
         // The CTAs of one cluster hold the K-splits of this slab.  Each leaves its partial in
         // its own shared memory; after a cluster barrier rank 0 adds them in rank order through
         // distributed shared memory (no global round trip, no atomics) and runs the epilogue.
+        // Every rank PUSHES its partial into rank 0's shared memory (remote stores are posted), arrives at
+        // the cluster barrier and is done; rank 0 waits once and adds the slots in rank order from its own
+        // shared memory.  One barrier, no remote loads on the critical path.
         constexpr int PER = (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS;
+        const uint32_t rank = cluster_ctarank();
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int idx = tid + i * GEMV_THREADS;
-            if (idx < M * SLAB) vals[idx] = mine[i];
-        }
-        cluster_sync_all();
-        if (tr) a.trace[4] = global_timer();  // all ranks' partials published
-        const uint32_t rank = cluster_ctarank();
-        if (rank == 0) {
-#pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int idx = tid + i * GEMV_THREADS;
-                if (idx < M * SLAB) {
-                    float v = mine[i];
-                    for (int r = 1; r < a.ksplit; ++r) v += ld_dsmem_f32(dsmem_addr(vals + idx, (uint32_t)r));
-                    mine[i] = v;
-                }
+            if (idx < M * SLAB) {
+                if (rank == 0) slots[idx] = mine[i];
+                else st_dsmem_f32(dsmem_addr(slots + rank * (M * SLAB) + idx, 0u), mine[i]);
             }
         }
-        cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
+        cluster_arrive_release();
         if (rank != 0) return;
+        cluster_wait_acquire();
+        if (tr) a.trace[4] = global_timer();  // all ranks' partials have landed
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int idx = tid + i * GEMV_THREADS;
-            if (idx < M * SLAB) vals[idx] = mine[i];
+            if (idx < M * SLAB) {
+                float v = slots[idx];
+                for (int r = 1; r < a.ksplit; ++r) v += slots[r * (M * SLAB) + idx];
+                vals[idx] = v;
+            }
         }
     } else if (a.ksplit == 1) {
 #pragma unroll
@@ -360,9 +366,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
 }
 
 template <int M, bool CL>
-cudaError_t launch_mc(const GemvArgs& a, cudaStream_t st, bool pdl) {
+cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
+    GemvArgs a = a_in;
     const int nslabs = (a.N + SLAB - 1) / SLAB;
-    const size_t smem = sizeof(float) * ((size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB);
+    size_t floats = (size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB + (CL ? (size_t)a.ksplit * M * SLAB : 0);
+    a.xfull = a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;  // whole rows staged once when they fit
+    if (a.xfull) floats += (size_t)M * a.K;
+    const size_t smem = sizeof(float) * floats;
     if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
         cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
