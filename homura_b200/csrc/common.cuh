@@ -158,6 +158,7 @@ struct KvDesc {
 };
 
 struct GemvArgs {
+    int* err_flag;                 // optional: raised to 2 when the bounded wait for the staged weights runs out
     int xfull;                     // set by the launcher: RMSNorm prologue stages the whole rows in shared memory (one L2 trip)
     unsigned long long* trace;     // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA 0 of this launch
     const void* pf_ptr;            // optional: weights of a later kernel to pull into the L2 (see l2_prefetch_slice)

@@ -797,6 +797,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
         if (L.kind == HM_BF16) {
             GemvArgs a{};
             a.W = L.slabs;
+            a.err_flag = err_flag_;
             if (gemv_trace_ && *launches < 512) a.trace = gemv_trace_ + (size_t)*launches * 8;
             if (m0 == 0) {
                 a.pf_ptr = pf_ptr_;

@@ -23,6 +23,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 namespace hm {
 
@@ -50,10 +51,19 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { retur
 // The unsplit M = 1 variant (LM head: one long stream per CTA) runs three CTAs per SM (<= 85
 // registers) to keep ~96 KB of weight loads in flight per SM; measured 5.0 -> 5.3 TB/s.  The
 // clustered variants are latency chains and were slower under the tighter register budget.
-template <int M, bool CL>
+// ST (with CL): the CTA's whole weight slice (rows [k0, k0+nrows) of its slab, one contiguous byte range of
+// at most GEMV_STAGE_MAX bytes) is pulled into shared memory by bulk copies issued BEFORE the dependency
+// wait, so that by the time the predecessor has finished the multiply runs out of shared memory and HBM
+// latency is off the critical path of the dependent-kernel chain.
+template <int M, bool CL, bool ST>
 __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf16_kernel(const GemvArgs a) {
-    extern __shared__ __align__(16) float smem[];
+    extern __shared__ __align__(128) float smem_raw[];
     const int rps = a.rows_per_split;
+    // staged weights first (bulk copies want 16-byte aligned destinations), then the f32 scratch
+    float* smem = ST ? smem_raw + (size_t)rps * (SLAB * 2 / 4) : smem_raw;
+    const uint4* wst = reinterpret_cast<const uint4*>(smem_raw);  // [nrows][16] x 16 B
+    __shared__ uint64_t s_wbar;
+    __shared__ volatile int s_abort;
     float* xs = smem;                 // [M][rps]
     float* red = smem + M * rps;      // [8][M][128], later vals[M][128]
     float* slots = red + 8 * M * SLAB;  // cluster variant, rank 0: [ksplit][M][128] partials pushed by the ranks
@@ -80,13 +90,27 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32) l2_prefetch_slice(a.pf_ptr, a.pf_bytes, blockIdx.x, gridDim.x, tid);
 
-    // First batch of weight loads is issued before the dependency wait: weights never depend
-    // on a previous kernel, so their DRAM latency overlaps the predecessor's tail.
+    // Weights never depend on a previous kernel, so they are requested before the dependency wait:
+    // the whole slice into shared memory (ST), or the first batch of streaming loads into registers.
     uint4 w[U];
+    if (ST) {
+        if (tid == 0) {
+            mb_init(&s_wbar, 1);
+            s_abort = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            const uint32_t bytes = (uint32_t)nrows * (SLAB * 2);
+            if (bytes) {
+                mb_expect_tx(&s_wbar, bytes);
+                const char* src = (const char*)a.W + (long long)slab * a.slab_stride + (long long)k0 * a.row_stride;
+                for (uint32_t o = 0; o < bytes; o += 16384u) bulk_copy((char*)smem_raw + o, src + o, min(16384u, bytes - o), &s_wbar);
+            }
+        }
+    } else {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-        const bool ok = col_ok && (u * ROWS_PER_PASS + rl) < nrows;
-        w[u] = ok ? ld_stream_u4(wbase + u * pass_stride) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < U; ++u) {
+            const bool ok = col_ok && (u * ROWS_PER_PASS + rl) < nrows;
+            w[u] = ok ? ld_stream_u4(wbase + u * pass_stride) : make_uint4(0, 0, 0, 0);
+        }
     }
 
     pdl_wait();
@@ -144,6 +168,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[m][j] = 0.f;
 
+    if (ST) {
+        // every thread waits (bounded) for the bulk copies, then multiplies out of shared memory
+        const bool ok = nrows == 0 || mb_wait(&s_wbar, 0, a.err_flag, &s_abort);
+        if (ok) {
+#pragma unroll 4
+            for (int row = rl; row < nrows; row += ROWS_PER_PASS) fma_row<M>(acc, wst[row * 16 + cg], xs, rps, row);
+        }
+    } else
     for (int it = 0; it < niter; it += U) {
         uint4 cur[U];
 #pragma unroll
@@ -365,20 +397,18 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     if (tr) a.trace[6] = global_timer();  // epilogue stored
 }
 
-template <int M, bool CL>
-cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
-    GemvArgs a = a_in;
-    const int nslabs = (a.N + SLAB - 1) / SLAB;
-    size_t floats = (size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB + (CL ? (size_t)a.ksplit * M * SLAB : 0);
-    a.xfull = a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;  // whole rows staged once when they fit
-    if (a.xfull) floats += (size_t)M * a.K;
-    const size_t smem = sizeof(float) * floats;
-    if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
-        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+constexpr size_t GEMV_STAGE_MAX = 80 * 1024;  // largest weight slice staged in shared memory (two CTAs per SM stay resident)
+
+template <int M, bool CL, bool ST>
+cudaError_t launch_mcs(const GemvArgs& a, size_t smem, int nslabs, cudaStream_t st, bool pdl) {
+    static size_t opted = 40 * 1024;  // static shared memory counts against the 48 KB default too; only ever raised
+    if (smem > opted) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
+        opted = smem;
     }
     if (CL && a.cluster > 8) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL, ST>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
@@ -402,7 +432,25 @@ cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
     }
     cfg.attrs = at;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<M, CL>, a);
+    return cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<M, CL, ST>, a);
+}
+
+template <int M, bool CL>
+cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
+    GemvArgs a = a_in;
+    const int nslabs = (a.N + SLAB - 1) / SLAB;
+    size_t floats = (size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB + (CL ? (size_t)a.ksplit * M * SLAB : 0);
+    a.xfull = a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;  // whole rows staged once when they fit
+    if (a.xfull) floats += (size_t)M * a.K;
+    size_t smem = sizeof(float) * floats;
+    // cluster launches over the slab layout whose slice fits: weights staged in shared memory before the dependency wait
+    static const bool no_stage = [] { const char* e = std::getenv("HM_NO_STAGE"); return e && e[0] == '1'; }();
+    const size_t slice = (size_t)a.rows_per_split * SLAB * 2;
+    if (CL && !no_stage && a.row_stride == SLAB * 2 && slice <= GEMV_STAGE_MAX && ((uintptr_t)a.W & 15) == 0) {
+        smem += slice;
+        return launch_mcs<M, true, true>(a, smem, nslabs, st, pdl);
+    }
+    return launch_mcs<M, CL, false>(a, smem, nslabs, st, pdl);
 }
 
 template <int M>
@@ -460,7 +508,7 @@ void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* 
 int gemv_max_cluster() {
     static int cached = 0;
     if (cached) return cached;
-    cudaFuncSetAttribute(gemv_bf16_kernel<1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cudaFuncSetAttribute(gemv_bf16_kernel<1, true, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(16);
     cfg.blockDim = dim3(GEMV_THREADS);
@@ -473,7 +521,7 @@ int gemv_max_cluster() {
     cfg.attrs = at;
     cfg.numAttrs = 1;
     int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemv_bf16_kernel<1, true>, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemv_bf16_kernel<1, true, false>, &cfg);
     if (e != cudaSuccess) cudaGetLastError();
     cached = (e == cudaSuccess && n >= 4) ? 16 : 8;
     return cached;
