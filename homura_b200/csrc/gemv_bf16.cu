@@ -69,6 +69,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
     float* slots = red + 8 * M * SLAB;  // cluster variant, rank 0: [ksplit][M][128] partials pushed by the ranks
     // RMSNorm prologue: the whole rows, read once (sum of squares and the slice come from the same load)
     float* xfull = CL ? slots + a.ksplit * M * SLAB : slots;  // [M][K] when it fits (a.xfull)
+    // values that do not depend on the previous kernel, fetched before the dependency wait:
+    float* nws = xfull + (a.xfull ? M * a.K : 0);  // [rps] RMSNorm weights of this CTA's K range
+    float* cs_s = nws + rps;                        // [M][128] RoPE cos, [M][128] sin of this slab's columns (QKV epilogue)
+    float* sn_s = cs_s + M * SLAB;
+    __shared__ int s_page[MAX_M];                   // page of every row's new token
     __shared__ float s_inv[MAX_M];
     __shared__ float s_warp[8][MAX_M];
     __shared__ int s_last;
@@ -113,6 +118,25 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
         }
     }
 
+    if (a.pro == PRO_RMSNORM)
+        for (int r = tid; r < nrows; r += GEMV_THREADS) nws[r] = __ldg(a.norm_w + k0 + r);
+    if (a.epi == EPI_QKV_ROPE) {
+        // positions, the RoPE table and the page table were final before this step's launches began
+        const int n0e = slab * SLAB;
+        for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
+            const int m = idx / SLAB, c = idx % SLAB;
+            if (m < a.m_valid && n0e + c < a.q_dim + a.kv_dim) {  // V columns are not rotated
+                const int pos = a.row_pos[m], d = c % a.hd;
+                cs_s[idx] = __ldg(a.rope_cos + (size_t)pos * a.hd + d);
+                sn_s[idx] = __ldg(a.rope_sin + (size_t)pos * a.hd + d);
+            }
+        }
+        if (tid < M && tid < a.m_valid) {
+            const int pos = a.row_pos[tid], seq = a.row_seq ? a.row_seq[tid] : tid;
+            s_page[tid] = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
+        }
+    }
+
     pdl_wait();
     if (tr) a.trace[1] = global_timer();  // predecessor complete
 
@@ -148,7 +172,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
             const float* xr = a.x + (size_t)m * a.ldx + k0;
             for (int r = tid; r < nrows; r += GEMV_THREADS) {
                 const float xv = a.xfull ? xfull[m * a.K + k0 + r] : __ldg(xr + r);
-                xs[m * rps + r] = (xv * inv) * __ldg(a.norm_w + k0 + r);
+                xs[m * rps + r] = (xv * inv) * nws[r];
             }
         }
     } else {
@@ -373,17 +397,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf
             float v = vals[idx];
             if (nh < a.q_dim + a.kv_dim) {
                 const float other = (d < half) ? -vals[idx + half] : vals[idx - half];
-                const float cs = __ldg(a.rope_cos + (size_t)pos * hd + d);
-                const float sn = __ldg(a.rope_sin + (size_t)pos * hd + d);
-                v = fmaf(other, sn, v * cs);
+                v = fmaf(other, sn_s[idx], v * cs_s[idx]);
             }
             if (nh < a.q_dim) {
                 a.y[(size_t)m * a.ldy + n] = v;
             } else {
                 const bool is_k = nh < a.q_dim + a.kv_dim;
                 const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
-                const int seq = a.row_seq ? a.row_seq[m] : m;
-                const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
+                const int page = s_page[m];
                 const int tok = pos % a.kv.page_tokens;
                 const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd));
                 void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
@@ -442,6 +463,7 @@ cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
     size_t floats = (size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB + (CL ? (size_t)a.ksplit * M * SLAB : 0);
     a.xfull = a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;  // whole rows staged once when they fit
     if (a.xfull) floats += (size_t)M * a.K;
+    floats += (size_t)a.rows_per_split + 2 * (size_t)M * SLAB;  // pre-fetched RMSNorm weights and RoPE rows
     size_t smem = sizeof(float) * floats;
     // cluster launches over the slab layout whose slice fits: weights staged in shared memory before the dependency wait
     static const bool no_stage = [] { const char* e = std::getenv("HM_NO_STAGE"); return e && e[0] == '1'; }();
