@@ -118,10 +118,22 @@ __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsu
         }
         const int head = head0 + jj;
         if (CL) {
-            c_o[i] = o;
-            if (d == 0) {
-                c_ml[jj * 2 + 0] = M;
-                c_ml[jj * 2 + 1] = l;
+            // push this split's triple into slot `rank` of rank 0's shared memory (remote stores are posted)
+            const uint32_t rank = cluster_ctarank();
+            float* po = c_o + (size_t)rank * g * HD + i;
+            float* pm = c_ml + ((size_t)rank * g + jj) * 2;
+            if (rank == 0) {
+                *po = o;
+                if (d == 0) {
+                    pm[0] = M;
+                    pm[1] = l;
+                }
+            } else {
+                st_dsmem_f32(dsmem_addr(po, 0u), o);
+                if (d == 0) {
+                    st_dsmem_f32(dsmem_addr(pm, 0u), M);
+                    st_dsmem_f32(dsmem_addr(pm + 1, 0u), l);
+                }
             }
         } else if (a.nsplit == 1) {
             store_out<HD>(a, m, head, d, o / l);
@@ -135,27 +147,27 @@ __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsu
         }
     }
     if (CL) {
-        // The splits of one (row, KV head) are the CTAs of one cluster: rank 0 merges their
-        // (max, sum, acc) triples straight out of the peers' shared memory, in rank order.
-        cluster_sync_all();
-        if (cluster_ctarank() == 0) {
-            for (int i = tid; i < g * HD; i += nthreads) {
-                const int jj = i / HD, d = i % HD;
-                float M = -INFINITY;
-                for (int r = 0; r < a.nsplit; ++r) M = fmaxf(M, ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r)));
-                float l = 0.f, o = 0.f;
-                for (int r = 0; r < a.nsplit; ++r) {
-                    const float ms = ld_dsmem_f32(dsmem_addr(c_ml + jj * 2, (uint32_t)r));
-                    if (ms > -INFINITY) {
-                        const float sc = expf(ms - M);
-                        l = fmaf(ld_dsmem_f32(dsmem_addr(c_ml + jj * 2 + 1, (uint32_t)r)), sc, l);
-                        o = fmaf(ld_dsmem_f32(dsmem_addr(c_o + i, (uint32_t)r)), sc, o);
-                    }
+        // The splits of one (row, KV head) are the CTAs of one cluster: every rank has pushed its
+        // (max, sum, acc) triples into rank 0's shared memory; one barrier later rank 0 merges them in
+        // rank order from its own memory and the other ranks are already gone.
+        cluster_arrive_release();
+        if (cluster_ctarank() != 0) return;
+        cluster_wait_acquire();
+        for (int i = tid; i < g * HD; i += nthreads) {
+            const int jj = i / HD, d = i % HD;
+            float M = -INFINITY;
+            for (int r = 0; r < a.nsplit; ++r) M = fmaxf(M, c_ml[((size_t)r * g + jj) * 2]);
+            float l = 0.f, o = 0.f;
+            for (int r = 0; r < a.nsplit; ++r) {
+                const float ms = c_ml[((size_t)r * g + jj) * 2];
+                if (ms > -INFINITY) {
+                    const float sc = expf(ms - M);
+                    l = fmaf(c_ml[((size_t)r * g + jj) * 2 + 1], sc, l);
+                    o = fmaf(c_o[(size_t)r * g * HD + i], sc, o);
                 }
-                store_out<HD>(a, m, head0 + jj, d, o / l);
             }
+            store_out<HD>(a, m, head0 + jj, d, o / l);
         }
-        cluster_sync_all();
         return;
     }
     if (a.nsplit == 1) return;
@@ -202,8 +214,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     float* p_s = tiles + nsub * TL::SLOT_FLOATS;  // [ATT_WARPS][16]
     float* w_ml = p_s + ATT_WARPS * PT;           // [ATT_WARPS][2]
     float* w_acc = w_ml + ATT_WARPS * 2;          // [ATT_WARPS][HD]
-    float* c_o = w_acc + ATT_WARPS * HD;          // [G_MAX][HD]   CTA result (cluster mode)
-    float* c_ml = c_o + G_MAX * HD;               // [G_MAX][2]
+    float* c_o = w_acc + ATT_WARPS * HD;          // cluster mode, rank 0: [nsplit][g][HD] triples pushed by the ranks
+    float* c_ml = c_o + (CL ? a.nsplit : 1) * g * HD;  // [nsplit][g][2]
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -382,13 +394,14 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     unsigned char* ring = st_sm;                                                 // [STAGES][K tile | V tile]
     float* q_s = reinterpret_cast<float*>(ring + ST::STAGES * ST::STAGE_BYTES);  // [G_MAX][NCH][2 halves][4]
     float* p_s = q_s + G_MAX * HD;                                               // [ATT_WARPS][G_MAX][16]
-    float* c_o = p_s + ATT_WARPS * G_MAX * PT;                                   // [G_MAX][HD]
-    float* c_ml = c_o + G_MAX * HD;                                              // [G_MAX][2]
+    const int g_early = a.heads / a.kv_heads;
+    float* c_o = p_s + ATT_WARPS * G_MAX * PT;                                   // cluster mode, rank 0: [nsplit][g][HD]
+    float* c_ml = c_o + (CL ? a.nsplit : 1) * g_early * HD;                      // [nsplit][g][2]
     // the per-warp results reuse the ring once every page has been consumed
     float* w_ml = reinterpret_cast<float*>(ring);                                // [ATT_WARPS * g][2]
     float* w_acc = w_ml + ATT_WARPS * G_MAX * 2;                                 // [ATT_WARPS * g][HD]
     static_assert(sizeof(float) * (ATT_WARPS * G_MAX * 2 + ATT_WARPS * G_MAX * HD) <= (size_t)ST::STAGES * ST::STAGE_BYTES, "ring too small for the merge scratch");
-    int32_t* pt_s = reinterpret_cast<int32_t*>(c_ml + G_MAX * 2);                // [pages of this CTA]
+    int32_t* pt_s = reinterpret_cast<int32_t*>(c_ml + (CL ? a.nsplit : 1) * g_early * 2);  // [pages of this CTA]
     __shared__ uint64_t full[ST_MAX_STAGES], empty[ST_MAX_STAGES];
     __shared__ int s_last;
     __shared__ volatile int s_abort;
@@ -565,16 +578,16 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
 }
 
 template <int HD, bool BF16>
-size_t stream_smem_bytes(int pages_per_cta) {
+size_t stream_smem_bytes(int pages_per_cta, int g, int slots) {
     using ST = StTile<HD, BF16>;
-    return (size_t)ST::STAGES * ST::STAGE_BYTES + sizeof(float) * ((size_t)G_MAX * HD + ATT_WARPS * G_MAX * PT + G_MAX * HD + G_MAX * 2) + (size_t)pages_per_cta * 4 + 128;
+    return (size_t)ST::STAGES * ST::STAGE_BYTES + sizeof(float) * ((size_t)G_MAX * HD + ATT_WARPS * G_MAX * PT + (size_t)slots * g * (HD + 2)) + (size_t)pages_per_cta * 4 + 128;
 }
 
 template <int HD, bool BF16>
-size_t smem_bytes(int g) {
+size_t smem_bytes(int g, int slots) {
     using TL = Tile<HD, BF16>;
     const int nsub = pick_nsub<HD, BF16>(g);
-    return sizeof(float) * ((size_t)G_MAX * HD + (size_t)nsub * TL::SLOT_FLOATS + ATT_WARPS * PT + ATT_WARPS * 2 + ATT_WARPS * HD + G_MAX * HD + G_MAX * 2);
+    return sizeof(float) * ((size_t)G_MAX * HD + (size_t)nsub * TL::SLOT_FLOATS + ATT_WARPS * PT + ATT_WARPS * 2 + ATT_WARPS * HD + (size_t)slots * g * (HD + 2));
 }
 
 template <int HD, bool BF16, bool CL>
@@ -583,7 +596,8 @@ cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
     const int pages_per_cta = (a.max_pages + a.nsplit - 1) / a.nsplit;
     // long contexts: the bulk-copy ring; a slot layout needs ATT_WARPS / g >= 1 as in the kernel above
     const bool stream = a.stream_pages > 0 && pages_per_cta >= ST_MIN_PAGES && pages_per_cta <= ST_MAX_PT;
-    const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta) : smem_bytes<HD, BF16>(g);
+    const int slots = CL ? a.nsplit : 1;  // rank 0 of a cluster receives every split's triples
+    const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots) : smem_bytes<HD, BF16>(g, slots);
     // the opt-in limit only ever grows: launches captured in a graph must stay valid after later calls
     static size_t opted[2] = {40 * 1024, 40 * 1024};  // static shared memory counts against the 48 KB default too
     if (smem > opted[stream ? 1 : 0]) {
