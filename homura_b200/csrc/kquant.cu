@@ -356,10 +356,20 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
     if (tid < M * 32) red[tid] = v;
     bool writer = true;
     if (CL) {
-        cluster_sync_all();
-        writer = split == 0;
-        if (writer && tid < M * 32)
-            for (int r = 1; r < a.ksplit; ++r) v += ld_dsmem_f32(dsmem_addr(red + tid, (uint32_t)r));
+        // every rank pushes its partial into rank 0's shared memory, arrives at the cluster barrier and is
+        // done; rank 0 waits once and adds the slots in rank order from its own memory
+        float* slots = red + 8 * M * 32;  // [ksplit][M][32]
+        if (tid < M * 32) {
+            if (split == 0) slots[tid] = v;
+            else st_dsmem_f32(dsmem_addr(slots + split * (M * 32) + tid, 0u), v);
+        }
+        cluster_arrive_release();
+        if (split != 0) return;
+        cluster_wait_acquire();
+        if (tid < M * 32) {
+            v = slots[tid];
+            for (int r = 1; r < a.ksplit; ++r) v += slots[r * (M * 32) + tid];
+        }
     }
     if (a.epi == EPI_SWIGLU) {
         if (writer && tid < M * 32) red[tid] = v;
@@ -379,13 +389,12 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
             a.y[(size_t)m * a.ldy + n] = v;
         }
     }
-    if (CL) cluster_sync_all();
 }
 
 template <int M, bool ACTQ, bool CL>
 cudaError_t launch_k3(const KQuantArgs& a, cudaStream_t st, bool pdl) {
     const size_t nbs = (size_t)a.kb_per_split;
-    const size_t smem = (size_t)M * nbs * 256 * (ACTQ ? 1 : 4) + 4 * (size_t)M * nbs + 4 * (size_t)M * nbs * 16 + 4 * (size_t)8 * M * 32;
+    const size_t smem = (size_t)M * nbs * 256 * (ACTQ ? 1 : 4) + 4 * (size_t)M * nbs + 4 * (size_t)M * nbs * 16 + 4 * (size_t)8 * M * 32 + (CL ? 4 * (size_t)a.ksplit * M * 32 : 0);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     static size_t opted = 40 * 1024;
     if (smem > opted) {

@@ -241,10 +241,19 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
     if (tid < M * 32) red[tid] = v;  // vals [M][32]
     bool writer = true;
     if (CL) {
-        cluster_sync_all();
-        writer = split == 0;
-        if (writer && tid < M * 32) {
-            for (int r = 1; r < a.ksplit; ++r) v += ld_dsmem_f32(dsmem_addr(red + tid, (uint32_t)r));
+        // every rank pushes its partial into rank 0's shared memory, arrives at the cluster barrier and is
+        // done; rank 0 waits once and adds the slots in rank order from its own memory
+        float* slots = red + 8 * M * 32;  // [ksplit][M][32]
+        if (tid < M * 32) {
+            if (split == 0) slots[tid] = v;
+            else st_dsmem_f32(dsmem_addr(slots + split * (M * 32) + tid, 0u), v);
+        }
+        cluster_arrive_release();
+        if (split != 0) return;
+        cluster_wait_acquire();
+        if (tid < M * 32) {
+            v = slots[tid];
+            for (int r = 1; r < a.ksplit; ++r) v += slots[r * (M * 32) + tid];
         }
     }
     if (a.epi == EPI_SWIGLU) {
@@ -266,12 +275,11 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
             a.y[(size_t)m * a.ldy + n] = v;
         }
     }
-    if (CL) cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
 }
 
 template <int M, bool Q4, bool CL>
 cudaError_t launch_q3(const QuantArgs& a, cudaStream_t st, bool pdl) {
-    const size_t smem = sizeof(float) * ((size_t)M * a.kb_per_split * 32 + 8 * M * 32);
+    const size_t smem = sizeof(float) * ((size_t)M * a.kb_per_split * 32 + 8 * M * 32 + (CL ? (size_t)a.ksplit * M * 32 : 0));
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
         cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<M, Q4, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
