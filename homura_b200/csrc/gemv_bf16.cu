@@ -50,13 +50,14 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { retur
 
 // The unsplit M = 1 variant (LM head: one long stream per CTA) runs three CTAs per SM (<= 85
 // registers) to keep ~96 KB of weight loads in flight per SM; measured 5.0 -> 5.3 TB/s.  The
-// clustered variants are latency chains and were slower under the tighter register budget.
+// clustered variants are latency chains and were slower under the tighter register budget.  The unsplit
+// 2- and 4-row variants are held to 128 registers so that two CTAs stay resident per SM.
 // ST (with CL): the CTA's whole weight slice (rows [k0, k0+nrows) of its slab, one contiguous byte range of
 // at most GEMV_STAGE_MAX bytes) is pulled into shared memory by bulk copies issued BEFORE the dependency
 // wait, so that by the time the predecessor has finished the multiply runs out of shared memory and HBM
 // latency is off the critical path of the dependent-kernel chain.
 template <int M, bool CL, bool ST>
-__global__ void __launch_bounds__(GEMV_THREADS, (M == 1 && !CL) ? 3 : 1) gemv_bf16_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ? 2 : 1))) gemv_bf16_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) float smem_raw[];
     const int rps = a.rows_per_split;
     // staged weights first (bulk copies want 16-byte aligned destinations), then the f32 scratch
@@ -461,9 +462,12 @@ cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
     GemvArgs a = a_in;
     const int nslabs = (a.N + SLAB - 1) / SLAB;
     size_t floats = (size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB + (CL ? (size_t)a.ksplit * M * SLAB : 0);
-    a.xfull = a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;  // whole rows staged once when they fit
+    // latency-bound (cluster) launches stage the whole rows once when they fit; the long unsplit launches are
+    // bandwidth-bound and keep their shared memory small for occupancy
+    a.xfull = CL && a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;
     if (a.xfull) floats += (size_t)M * a.K;
-    floats += (size_t)a.rows_per_split + 2 * (size_t)M * SLAB;  // pre-fetched RMSNorm weights and RoPE rows
+    floats += (size_t)a.rows_per_split;                            // pre-fetched RMSNorm weights
+    if (a.epi == EPI_QKV_ROPE) floats += 2 * (size_t)M * SLAB;     // pre-fetched RoPE rows
     size_t smem = sizeof(float) * floats;
     // cluster launches over the slab layout whose slice fits: weights staged in shared memory before the dependency wait
     static const bool no_stage = [] { const char* e = std::getenv("HM_NO_STAGE"); return e && e[0] == '1'; }();
