@@ -27,7 +27,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhomura_b200.so")
 
 HM_OK, HM_ERR_INVALID, HM_ERR_CUDA, HM_ERR_KV_FULL, HM_ERR_IO, HM_ERR_UNSUPPORTED, HM_ERR_TIMEOUT, HM_ERR_STATE = range(8)
-LAYOUT_KN, LAYOUT_SLAB128 = 0, 1
+LAYOUT_KN, LAYOUT_SLAB128, LAYOUT_COLS8 = 0, 1, 2
 
 
 class DType(enum.IntEnum):
@@ -128,6 +128,7 @@ SIGNATURES = {
     "hm_gemv_bf16": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_gemv_bf16_noalloc": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_pack_bf16_slabs": (_i32, [_vp, _i32, _i32, _vp, _vp]),
+    "hm_pack_bf16_cols8": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "hm_gemm_bf16_tc": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_tc_packed_elems": (C.c_size_t, [_i32, _i32]),
     "hm_pack_bf16_tc": (_i32, [_vp, _i32, _i32, _vp, _vp]),
@@ -519,6 +520,16 @@ def pack_bf16_slabs(w_bits) -> np.ndarray:
     K, N = w.shape
     out = np.empty(((N + 127) // 128, K, 128), np.uint16)
     _check(lib.hm_pack_bf16_slabs(_ptr(w), K, N, _ptr(out), None))
+    return out
+
+
+def pack_bf16_cols8(w_bits) -> np.ndarray:
+    """Row-major [K,N] bf16 bits -> LAYOUT_COLS8: [ceil(N/8)][K][8], groups of 8 output columns."""
+    lib = load_library()
+    w = np.ascontiguousarray(w_bits, dtype=np.uint16)
+    K, N = w.shape
+    out = np.empty(((N + 7) // 8, K, 8), np.uint16)
+    _check(lib.hm_pack_bf16_cols8(_ptr(w), K, N, _ptr(out), None))
     return out
 
 

@@ -33,6 +33,7 @@ constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int G_MAX = 8;   // query heads per KV head handled by one CTA
 constexpr int MAXP = 4;    // 16-byte pieces of K (and of V) a thread may hold in flight
 constexpr int ST_MIN_PAGES = 16;  // pages per CTA from which the streaming variant is used
+constexpr int RES_MAX_PAGES = 8;  // decode launches with at most this many pages per CTA keep all of them in shared memory
 
 template <int HD, bool BF16>
 struct Tile {
@@ -48,6 +49,17 @@ __host__ __device__ inline int pick_nsub(int g) {
     int n = ATT_WARPS / g;
     if (n > Tile<HD, BF16>::MAX_NSUB) n = Tile<HD, BF16>::MAX_NSUB;
     return n < 1 ? 1 : n;
+}
+
+// Page slots of the short-context kernel: nsub slots reused group after group, or -- when a decode
+// launch gives a CTA at most RES_MAX_PAGES pages -- one slot per page, so that every page that is
+// final before the dependency wait is already in shared memory when the wait returns.
+template <int HD, bool BF16>
+__host__ __device__ inline int pick_nslots(int g, int early_pages, int max_pages, int nsplit) {
+    const int nsub = pick_nsub<HD, BF16>(g);
+    const int cap = (max_pages + nsplit - 1) / nsplit;
+    if (!early_pages || cap > RES_MAX_PAGES) return nsub;
+    return (cap + nsub - 1) / nsub * nsub;
 }
 
 template <bool BF16>
@@ -71,15 +83,105 @@ __device__ __forceinline__ void store_out(const AttnArgs& a, int m, int head, in
     else a.out[(size_t)m * a.heads * HD + head * HD + d] = v;
 }
 
+// Rank 0 of a (row, KV head) cluster, after every split's (max, sum, acc) triple has landed in its
+// shared memory: one scale factor per (split, head) first (g * nsplit exponentials instead of one per
+// output element and split), then every output element is a short multiply-add over the splits.
+template <int HD>
+__device__ __forceinline__ void cluster_rank0_merge(const AttnArgs& a, int g, int head0, int m, float* scratch, const float* c_o, const float* c_ml) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    if (a.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) a.trace[4] = a.trace[5] = global_timer();  // every split's triple has landed
+    float* sc_s = scratch;                 // [nsplit][g]
+    float* l_s = scratch + a.nsplit * g;   // [g] merged sums
+    // loops over the splits are unrolled to the largest cluster (16) with the bound as a predicate, so that
+    // their shared-memory loads are issued together instead of one round trip per split
+    constexpr int MAXS = 16;
+    for (int i = tid; i < g * a.nsplit; i += nthreads) {
+        const int r = i / g, jj = i - r * g;
+        float M = -INFINITY;
+#pragma unroll
+        for (int r2 = 0; r2 < MAXS; ++r2)
+            if (r2 < a.nsplit) M = fmaxf(M, c_ml[((size_t)r2 * g + jj) * 2]);
+        const float ms = c_ml[((size_t)r * g + jj) * 2];
+        sc_s[i] = ms > -INFINITY ? expf(ms - M) : 0.f;
+    }
+    __syncthreads();
+    if (tid < g) {
+        float l = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAXS; ++r)
+            if (r < a.nsplit) l = fmaf(c_ml[((size_t)r * g + tid) * 2 + 1], sc_s[r * g + tid], l);
+        l_s[tid] = l;
+    }
+    float o[(G_MAX * HD + ATT_THREADS - 1) / ATT_THREADS];
+#pragma unroll
+    for (int k = 0; k < (G_MAX * HD + ATT_THREADS - 1) / ATT_THREADS; ++k) {
+        const int i = tid + k * nthreads;
+        float v = 0.f;
+        if (i < g * HD) {
+            const int jj = i / HD;
+#pragma unroll
+            for (int r = 0; r < MAXS; ++r)
+                if (r < a.nsplit) v = fmaf(c_o[(size_t)r * g * HD + i], sc_s[r * g + jj], v);
+        }
+        o[k] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < (G_MAX * HD + ATT_THREADS - 1) / ATT_THREADS; ++k) {
+        const int i = tid + k * nthreads;
+        if (i < g * HD) store_out<HD>(a, m, head0 + i / HD, i % HD, o[k] / l_s[i / HD]);
+    }
+}
+
 template <int HD, bool CL>
-__device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p);
+__device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p,
+                                                      uint64_t* rbar = nullptr, volatile int* abortf = nullptr);
+
+// Cluster splits hand their triples to rank 0 either with plain remote stores followed by a cluster barrier
+// (rbar == nullptr), or -- when rank 0 armed an mbarrier for them before the dependency wait -- with
+// asynchronous stores that count bytes on that mbarrier, which takes the cluster barrier off the critical path.
+__device__ __forceinline__ void push_f32(float* slot_in_rank0, float v, uint32_t rank, uint32_t rbar0) {
+    if (rank == 0) *slot_in_rank0 = v;
+    else if (rbar0) st_async_f32(dsmem_addr(slot_in_rank0, 0u), v, rbar0);
+    else st_dsmem_f32(dsmem_addr(slot_in_rank0, 0u), v);
+}
+// after the pushes: false for the ranks that are done, true on rank 0 once every triple has landed
+__device__ __forceinline__ bool pushes_landed(const AttnArgs& a, uint64_t* rbar, volatile int* abortf) {
+    if (rbar) {
+        if (cluster_ctarank() != 0) return false;
+        return a.nsplit == 1 || mb_wait_cluster(rbar, 0, a.err_flag, abortf);  // bounded
+    }
+    cluster_arrive_release();
+    if (cluster_ctarank() != 0) return false;
+    cluster_wait_acquire();
+    return true;
+}
 
 // One-head-per-warp kernels: publish the warp's triple at entry (slot * g + head) = warp, then merge.
 template <int HD, bool CL>
 __device__ __forceinline__ void merge_and_write(const AttnArgs& a, bool active, float run_m, float run_l, const float (&acc)[HD / 32], int nsub, int g, int head0, int split, int kvh, int m, float* w_ml,
-                                                float* w_acc, float* c_o, float* c_ml, int* s_last_p) {
+                                                float* w_acc, float* c_o, float* c_ml, int* s_last_p, uint64_t* rbar = nullptr, volatile int* abortf = nullptr) {
     constexpr int EPL = HD / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (CL && nsub == 1) {
+        // one warp per query head and nothing to merge inside the CTA: every warp stores its triple straight
+        // from registers into slot `rank` of rank 0's shared memory
+        const uint32_t rank = cluster_ctarank();
+        const uint32_t rbar0 = rbar ? dsmem_addr(rbar, 0u) : 0u;
+        if (warp < g) {
+            float* po = c_o + ((size_t)rank * g + warp) * HD + lane * EPL;
+            float* pm = c_ml + ((size_t)rank * g + warp) * 2;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) push_f32(po + e, acc[e], rank, rbar0);
+            if (lane == 0) {
+                push_f32(pm, run_m, rank, rbar0);
+                push_f32(pm + 1, run_l, rank, rbar0);
+            }
+        }
+        if (!pushes_landed(a, rbar, abortf)) return;
+        cluster_rank0_merge<HD>(a, g, head0, m, w_acc, c_o, c_ml);
+        return;
+    }
     if (warp < ATT_WARPS) {
         if (lane == 0) {
             w_ml[warp * 2 + 0] = active ? run_m : -INFINITY;
@@ -89,14 +191,15 @@ __device__ __forceinline__ void merge_and_write(const AttnArgs& a, bool active, 
         for (int e = 0; e < EPL; ++e) w_acc[warp * HD + lane * EPL + e] = active ? acc[e] : 0.f;
     }
     __syncthreads();
-    merge_slots_and_write<HD, CL>(a, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, s_last_p);
+    merge_slots_and_write<HD, CL>(a, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, s_last_p, rbar, abortf);
 }
 
 // Merge the (max, sum, acc) triples of nsub page slots per head (entry slot * g + head), then the
 // splits of the (row, KV head): through the cluster (rank 0 reads its peers' shared memory in rank
 // order), or through global scratch by whichever CTA arrives last at the ticket.
 template <int HD, bool CL>
-__device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p) {
+__device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p, uint64_t* rbar,
+                                                      volatile int* abortf) {
     const int tid = threadIdx.x;
     const int nthreads = blockDim.x;
     int& s_last = *s_last_p;
@@ -118,22 +221,14 @@ __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsu
         }
         const int head = head0 + jj;
         if (CL) {
-            // push this split's triple into slot `rank` of rank 0's shared memory (remote stores are posted)
+            // push this split's triple into slot `rank` of rank 0's shared memory
             const uint32_t rank = cluster_ctarank();
-            float* po = c_o + (size_t)rank * g * HD + i;
-            float* pm = c_ml + ((size_t)rank * g + jj) * 2;
-            if (rank == 0) {
-                *po = o;
-                if (d == 0) {
-                    pm[0] = M;
-                    pm[1] = l;
-                }
-            } else {
-                st_dsmem_f32(dsmem_addr(po, 0u), o);
-                if (d == 0) {
-                    st_dsmem_f32(dsmem_addr(pm, 0u), M);
-                    st_dsmem_f32(dsmem_addr(pm + 1, 0u), l);
-                }
+            const uint32_t rbar0 = rbar ? dsmem_addr(rbar, 0u) : 0u;
+            push_f32(c_o + (size_t)rank * g * HD + i, o, rank, rbar0);
+            if (d == 0) {
+                float* pm = c_ml + ((size_t)rank * g + jj) * 2;
+                push_f32(pm, M, rank, rbar0);
+                push_f32(pm + 1, l, rank, rbar0);
             }
         } else if (a.nsplit == 1) {
             store_out<HD>(a, m, head, d, o / l);
@@ -150,24 +245,8 @@ __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsu
         // The splits of one (row, KV head) are the CTAs of one cluster: every rank has pushed its
         // (max, sum, acc) triples into rank 0's shared memory; one barrier later rank 0 merges them in
         // rank order from its own memory and the other ranks are already gone.
-        cluster_arrive_release();
-        if (cluster_ctarank() != 0) return;
-        cluster_wait_acquire();
-        for (int i = tid; i < g * HD; i += nthreads) {
-            const int jj = i / HD, d = i % HD;
-            float M = -INFINITY;
-            for (int r = 0; r < a.nsplit; ++r) M = fmaxf(M, c_ml[((size_t)r * g + jj) * 2]);
-            float l = 0.f, o = 0.f;
-            for (int r = 0; r < a.nsplit; ++r) {
-                const float ms = c_ml[((size_t)r * g + jj) * 2];
-                if (ms > -INFINITY) {
-                    const float sc = expf(ms - M);
-                    l = fmaf(c_ml[((size_t)r * g + jj) * 2 + 1], sc, l);
-                    o = fmaf(c_o[(size_t)r * g * HD + i], sc, o);
-                }
-            }
-            store_out<HD>(a, m, head0 + jj, d, o / l);
-        }
+        if (!pushes_landed(a, rbar, abortf)) return;
+        cluster_rank0_merge<HD>(a, g, head0, m, w_acc, c_o, c_ml);
         return;
     }
     if (a.nsplit == 1) return;
@@ -209,18 +288,24 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     extern __shared__ __align__(16) float sm[];
     const int g = a.heads / a.kv_heads;
     const int nsub = pick_nsub<HD, BF16>(g);  // page slots worked on concurrently
+    const int nslots = pick_nslots<HD, BF16>(g, a.early_pages, a.max_pages, a.nsplit);
+    const bool resident = nslots * a.nsplit >= a.max_pages && a.early_pages;  // one slot per page of this CTA
     float* q_s = sm;                              // [G_MAX][HD]
-    float* tiles = q_s + G_MAX * HD;              // [nsub][K tile | V tile]
-    float* p_s = tiles + nsub * TL::SLOT_FLOATS;  // [ATT_WARPS][16]
+    float* tiles = q_s + G_MAX * HD;              // [nslots][K tile | V tile]
+    float* p_s = tiles + nslots * TL::SLOT_FLOATS;  // [ATT_WARPS][16]
     float* w_ml = p_s + ATT_WARPS * PT;           // [ATT_WARPS][2]
     float* w_acc = w_ml + ATT_WARPS * 2;          // [ATT_WARPS][HD]
     float* c_o = w_acc + ATT_WARPS * HD;          // cluster mode, rank 0: [nsplit][g][HD] triples pushed by the ranks
     float* c_ml = c_o + (CL ? a.nsplit : 1) * g * HD;  // [nsplit][g][2]
     __shared__ int s_last;
+    __shared__ uint64_t s_rbar;  // cluster mode, rank 0: counts the bytes of the other splits' triples
+    __shared__ volatile int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
     const int head0 = kvh * g;
+    const bool tr = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
+    if (tr) a.trace[0] = global_timer();  // CTA resident
 
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32)
@@ -229,7 +314,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     // Lengths, positions and the page table were written before the launch chain of this step began,
     // so the page range can be worked out before the dependency wait.  With early_pages set (decode:
     // one row per sequence) the pages BELOW the one that receives this step's token are final too and
-    // their loads are issued now; the page of the new token (written by the preceding QKV kernel)
+    // are read now -- into their own slots when the CTA's pages all fit (resident), else only the
+    // first group's loads are issued; the page of the new token (written by the preceding QKV kernel)
     // and the query are read after the wait.
     const int seq = a.row_seq ? a.row_seq[m] : m;
     const int kvlen = a.kv_len ? a.kv_len[m] : a.row_pos[m] + 1;
@@ -265,25 +351,60 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
             }
         }
     };
-    if (p0 < safe_end) issue_loads(p0, p0, safe_end);
-    pdl_wait();
-    auto store_tiles = [&]() {
+    // stores the group's registers into slots slot_base.., only the pages in [lo, hi)
+    auto store_tiles = [&](int slot_base, int pbase, int lo, int hi) {
 #pragma unroll
         for (int i = 0; i < MAXP; ++i) {
             const int idx = tid + i * ATT_THREADS;
             if (idx < total_pieces) {
                 const int slot = idx / TL::PIECES, piece = idx % TL::PIECES;
-                const int e = piece * TL::PER16, t = e / HD, d = e % HD;
-                float* base = tiles + slot * TL::SLOT_FLOATS;
-                // K pages are chunk-major (k_tile_off) and stay so in shared memory: a straight copy
-                unpack_store<BF16>(base + e, kreg[i]);
-                unpack_store<BF16>(base + PT * TL::KLD + t * HD + d, vreg[i]);
+                const int p = pbase + slot;
+                if (p >= lo && p < hi) {
+                    const int e = piece * TL::PER16, t = e / HD, d = e % HD;
+                    float* base = tiles + (slot_base + slot) * TL::SLOT_FLOATS;
+                    // K pages are chunk-major (k_tile_off) and stay so in shared memory: a straight copy
+                    unpack_store<BF16>(base + e, kreg[i]);
+                    unpack_store<BF16>(base + PT * TL::KLD + t * HD + d, vreg[i]);
+                }
             }
         }
     };
+    if (CL) {
+        // arm rank 0's mbarrier for the triples of the other splits and publish it with a cluster barrier
+        // that happens before the dependency wait, off the dependent-kernel chain
+        if (tid == 0) {
+            s_abort = 0;
+            if (cluster_ctarank() == 0) {
+                mb_init(&s_rbar, 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                mb_expect_tx(&s_rbar, (uint32_t)(a.nsplit - 1) * (uint32_t)(g * (HD + 2)) * 4u);
+            }
+        }
+        cluster_arrive_release();
+        cluster_wait_acquire();
+    }
+    if (resident) {
+#pragma unroll 1
+        for (int pb = p0; pb < safe_end; pb += nsub) {
+            issue_loads(pb, pb, safe_end);
+            store_tiles(pb - p0, pb, pb, safe_end);
+        }
+    } else if (p0 < safe_end) {
+        issue_loads(p0, p0, safe_end);
+    }
+    pdl_wait();
+    if (tr) a.trace[1] = global_timer();  // predecessor complete
 
-    if (p0 < p1) issue_loads(p0, max(p0, safe_end), p1);
-    for (int i = tid; i < g * HD; i += ATT_THREADS) q_s[i] = a.q[(size_t)m * a.heads * HD + head0 * HD + i];
+    const int late0 = max(p0, safe_end);  // [late0, p1): at most the page that holds the new token
+    if (resident) {
+        if (late0 < p1) {
+            const int pb = p0 + (late0 - p0) / nsub * nsub;
+            issue_loads(pb, late0, p1);
+        }
+    } else if (p0 < p1) {
+        issue_loads(p0, late0, p1);
+    }
+    stage_row<ATT_THREADS, false>(a.q + (size_t)m * a.heads * HD + head0 * HD, q_s, g * HD, tid);
 
     const int j = warp % g, sub = warp / g;  // this warp's query head and page slot
     const bool active = sub < nsub;
@@ -293,56 +414,78 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     const int t = lane & 15, hf = lane >> 4;
     float* pw = p_s + warp * PT;
 
-    for (int pb = p0; pb < p1; pb += nsub) {
-        __syncthreads();  // previous group's tiles are no longer being read (also publishes q_s)
-        store_tiles();
-        __syncthreads();
-        if (pb + nsub < p1) issue_loads(pb + nsub, pb + nsub, p1);  // next group in flight during the math
-        const int p = pb + sub;
-        if (active && p < p1) {
-            const float* kt = tiles + sub * TL::SLOT_FLOATS;
-            const float* vt = kt + PT * TL::KLD;
-            const float* kr = kt + ((hf * (HD / 8) * PT + t) << 2);  // chunk-major: chunk c of token t at (c * 16 + t) * 4
-            const float* qr = q_s + j * HD + hf * (HD / 2);
-            float s = 0.f;
+    // one page of this warp's query head: 16 scores, online-softmax update, p . v
+    auto page = [&](int p, const float* kt) {
+        const float* vt = kt + PT * TL::KLD;
+        const float* kr = kt + ((hf * (HD / 8) * PT + t) << 2);  // chunk-major: chunk c of token t at (c * 16 + t) * 4
+        const float* qr = q_s + j * HD + hf * (HD / 2);
+        float s = 0.f, s2 = 0.f;  // two chains: the dot product is latency, not throughput
 #pragma unroll
-            for (int dc = 0; dc < HD / 2; dc += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(kr + dc * PT);
-                const float4 q4 = *reinterpret_cast<const float4*>(qr + dc);
-                s = fmaf(q4.x, k4.x, s);
-                s = fmaf(q4.y, k4.y, s);
-                s = fmaf(q4.z, k4.z, s);
-                s = fmaf(q4.w, k4.w, s);
-            }
-            s += __shfl_xor_sync(0xffffffffu, s, 16);
-            const bool valid = (p * PT + t) < kvlen;
-            const float sc = valid ? s * a.scale : -INFINITY;
-            float mx = sc;
+        for (int dc = 0; dc < HD / 2; dc += 8) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kr + dc * PT);
+            const float4 q4 = *reinterpret_cast<const float4*>(qr + dc);
+            const float4 k5 = *reinterpret_cast<const float4*>(kr + (dc + 4) * PT);
+            const float4 q5 = *reinterpret_cast<const float4*>(qr + dc + 4);
+            s = fmaf(q4.x, k4.x, s);
+            s2 = fmaf(q5.x, k5.x, s2);
+            s = fmaf(q4.y, k4.y, s);
+            s2 = fmaf(q5.y, k5.y, s2);
+            s = fmaf(q4.z, k4.z, s);
+            s2 = fmaf(q5.z, k5.z, s2);
+            s = fmaf(q4.w, k4.w, s);
+            s2 = fmaf(q5.w, k5.w, s2);
+        }
+        s += s2;
+        s += __shfl_xor_sync(0xffffffffu, s, 16);
+        const bool valid = (p * PT + t) < kvlen;
+        const float sc = valid ? s * a.scale : -INFINITY;
+        float mx = sc;
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float m_new = fmaxf(run_m, mx);
-            const float pr = valid ? expf(sc - m_new) : 0.f;
-            float ps = pr;
+        for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(run_m, mx);
+        const float pr = valid ? expf(sc - m_new) : 0.f;
+        float ps = pr;
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-            const float corr = expf(run_m - m_new);  // exp(-inf) = 0 on the first page
-            run_l = run_l * corr + ps;
-            run_m = m_new;
-            if (hf == 0) pw[t] = pr;
-            __syncwarp();
+        for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        const float corr = expf(run_m - m_new);  // exp(-inf) = 0 on the first page
+        run_l = run_l * corr + ps;
+        run_m = m_new;
+        if (hf == 0) pw[t] = pr;
+        __syncwarp();
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) acc[e] *= corr;
+        for (int e = 0; e < EPL; ++e) acc[e] *= corr;
 #pragma unroll
-            for (int tt = 0; tt < PT; ++tt) {
-                const float pv = pw[tt];
+        for (int tt = 0; tt < PT; ++tt) {
+            const float pv = pw[tt];
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[e] = fmaf(pv, vt[tt * HD + lane * EPL + e], acc[e]);
-            }
-            __syncwarp();
+            for (int e = 0; e < EPL; ++e) acc[e] = fmaf(pv, vt[tt * HD + lane * EPL + e], acc[e]);
+        }
+        __syncwarp();
+    };
+
+    if (resident) {
+        if (late0 < p1) {
+            const int pb = p0 + (late0 - p0) / nsub * nsub;
+            store_tiles(pb - p0, pb, late0, p1);
+        }
+        __syncthreads();  // every page of this CTA and the query are in shared memory
+        if (tr) a.trace[2] = global_timer();
+        if (active)
+            for (int p = p0 + sub; p < p1; p += nsub) page(p, tiles + (p - p0) * TL::SLOT_FLOATS);
+    } else {
+        for (int pb = p0; pb < p1; pb += nsub) {
+            __syncthreads();  // previous group's tiles are no longer being read (also publishes q_s)
+            store_tiles(0, pb, pb, p1);
+            __syncthreads();
+            if (pb + nsub < p1) issue_loads(pb + nsub, pb + nsub, p1);  // next group in flight during the math
+            const int p = pb + sub;
+            if (active && p < p1) page(p, tiles + sub * TL::SLOT_FLOATS);
         }
     }
 
-    merge_and_write<HD, CL>(a, active, run_m, run_l, acc, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, &s_last);
+    if (tr) a.trace[3] = global_timer();  // this warp's pages done
+    merge_and_write<HD, CL>(a, active, run_m, run_l, acc, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, &s_last, CL ? &s_rbar : nullptr, &s_abort);
+    if (tr) a.trace[6] = global_timer();  // merged and stored (rank 0 of the cluster)
 }
 
 // ---- streaming variant for long contexts ---------------------------------------------------------
@@ -584,10 +727,9 @@ size_t stream_smem_bytes(int pages_per_cta, int g, int slots) {
 }
 
 template <int HD, bool BF16>
-size_t smem_bytes(int g, int slots) {
+size_t smem_bytes(int g, int slots, int nslots) {
     using TL = Tile<HD, BF16>;
-    const int nsub = pick_nsub<HD, BF16>(g);
-    return sizeof(float) * ((size_t)G_MAX * HD + (size_t)nsub * TL::SLOT_FLOATS + ATT_WARPS * PT + ATT_WARPS * 2 + ATT_WARPS * HD + (size_t)slots * g * (HD + 2));
+    return sizeof(float) * ((size_t)G_MAX * HD + (size_t)nslots * TL::SLOT_FLOATS + ATT_WARPS * PT + ATT_WARPS * 2 + ATT_WARPS * HD + (size_t)slots * g * (HD + 2));
 }
 
 template <int HD, bool BF16, bool CL>
@@ -597,7 +739,7 @@ cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
     // long contexts: the bulk-copy ring; a slot layout needs ATT_WARPS / g >= 1 as in the kernel above
     const bool stream = a.stream_pages > 0 && pages_per_cta >= ST_MIN_PAGES && pages_per_cta <= ST_MAX_PT;
     const int slots = CL ? a.nsplit : 1;  // rank 0 of a cluster receives every split's triples
-    const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots) : smem_bytes<HD, BF16>(g, slots);
+    const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots) : smem_bytes<HD, BF16>(g, slots, pick_nslots<HD, BF16>(g, a.early_pages, a.max_pages, a.nsplit));
     // the opt-in limit only ever grows: launches captured in a graph must stay valid after later calls
     static size_t opted[2] = {40 * 1024, 40 * 1024};  // static shared memory counts against the 48 KB default too
     if (smem > opted[stream ? 1 : 0]) {

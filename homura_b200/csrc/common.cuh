@@ -9,6 +9,8 @@ constexpr int SLAB = 128;       // output columns per weight slab
 constexpr int GEMV_THREADS = 256;
 constexpr int ROWS_PER_PASS = 16;  // 256 threads x 16 B = 16 rows x 256 B
 constexpr int MAX_M = 8;
+constexpr int COLS_THREADS = 288;  // column-group projection kernel: nine warps, so that nine groups get a warp each
+constexpr size_t COLS_SMEM_MAX = 208 * 1024;
 
 // ---- programmatic dependent launch ----------------------------------------------------
 // Kernels in the decode chain call pdl_launch_dependents() first (so the next kernel's CTAs
@@ -37,6 +39,12 @@ __device__ __forceinline__ uint32_t dsmem_addr(const void* p, uint32_t rank) {
 __device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+// Asynchronous store into another CTA's shared memory that also counts 4 bytes on an mbarrier of that CTA
+// (both addresses are shared::cluster addresses of the same CTA): data and signal travel together, so the
+// receiver waits on its own mbarrier and the sender needs no release fence and no cluster barrier.
+__device__ __forceinline__ void st_async_f32(uint32_t addr, float v, uint32_t mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(__float_as_uint(v)), "r"(mbar) : "memory");
+}
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -88,6 +96,52 @@ __device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
     float4 v;
     asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
     return v;
+}
+
+// Cooperative copy of n floats written by a previous kernel into shared memory, NT threads, with up to
+// four loads per thread in flight before the first use (a loop of load-then-use would pay one L2
+// round trip per iteration).  128-bit loads when source, destination and n allow.  L2-only loads:
+// the rows are rewritten by other SMs every launch.  Returns this thread's share of the sum of squares.
+template <int NT, bool SQ>
+__device__ __forceinline__ float stage_row(const float* __restrict__ src, float* __restrict__ dst, int n, int tid) {
+    float s = 0.f;
+    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0 && (n & 3) == 0) {
+        const int n4 = n >> 2;
+        for (int b = tid; b < n4; b += 4 * NT) {
+            float4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = b + i * NT;
+                v[i] = idx < n4 ? ld_cg_f32x4(src + 4 * (size_t)idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = b + i * NT;
+                if (idx < n4) {
+                    reinterpret_cast<float4*>(dst)[idx] = v[i];
+                    if (SQ) s = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, s))));
+                }
+            }
+        }
+    } else {
+        for (int b = tid; b < n; b += 4 * NT) {
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = b + i * NT;
+                v[i] = idx < n ? ld_cg_f32(src + idx) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = b + i * NT;
+                if (idx < n) {
+                    dst[idx] = v[i];
+                    if (SQ) s = fmaf(v[i], v[i], s);
+                }
+            }
+        }
+    }
+    return s;
 }
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -169,6 +223,7 @@ struct GemvArgs {
     long long row_stride;   // bytes
     int K, N;
     int m_valid;            // rows >= m_valid are padding: computed, never stored
+    int n_groups;           // column-group kernel: groups of 8 output columns (filled in by its launcher)
     int ksplit, rows_per_split;
     int cluster;            // > 1: the ksplit CTAs of a slab form one thread-block cluster and reduce through
                             // distributed shared memory (ksplit == cluster); else partial/tickets are used
@@ -209,6 +264,7 @@ struct AttnArgs {
     int early_pages;     // 1: every row is its own sequence (decode), so the pages below the one of the new token may be read before the dependency wait
     int stream_pages;    // > 0: long contexts may use the bulk-copy ring variant (pages per CTA decided from max_pages / nsplit)
     int* err_flag;       // raised to 2 when a bounded wait of that variant runs out
+    unsigned long long* trace;  // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA (0,0,0) of the short-context kernel
     const float* q;       // [M][heads*hd]
     const void* k_pool;
     const void* v_pool;
@@ -245,6 +301,24 @@ struct QuantArgs {
 
 // ---- launchers (defined in the .cu files) ----------------------------------------------
 cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl);
+
+// Column-group layout (gemv_cols.cu): output column held at position c (0..7) of group g.  Plain stores:
+// 8 consecutive columns.  Fused QKV with RoPE: positions 0..3 are columns d..d+3 of a Q or K head,
+// positions 4..7 their rotation partners d+hd/2..; V columns are consecutive.  (SwiGLU groups hold
+// gate columns 4g..4g+3 and the matching up columns; their epilogue indexes them directly.)
+__host__ __device__ inline int cols_group_col(int epi, int g, int c, int q_dim, int kv_dim, int hd, int N) {
+    const int nb = g * 8;
+    if (epi == EPI_QKV_ROPE && nb < q_dim + kv_dim) {
+        const int h = nb / hd, d0 = ((nb % hd) >> 3) << 2;
+        return h * hd + (c < 4 ? d0 + c : (hd >> 1) + d0 + (c - 4));
+    }
+    (void)N;
+    return nb + c;
+}
+int cols_groups(int epi, int N);
+bool gemv_cols_plan(int epi, int pro, int K, int N, int M, int sm_count, int* grid, size_t* smem);
+cudaError_t launch_pack_cols(const uint16_t* slabs, int K, int N, int epi, int q_dim, int kv_dim, int hd, uint16_t* dst, cudaStream_t st);
+cudaError_t launch_gemv_cols(const GemvArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
 size_t gemv_partial_floats(int N, int ksplit, int M);
 void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_per_split);
 // Cluster variant: ksplit = cluster size (<= max_cluster), sized so that all CTAs are resident at once.

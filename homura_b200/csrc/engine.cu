@@ -87,6 +87,8 @@ int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* 
     const char* nocl = std::getenv("HM_NO_CLUSTER");
     e->use_clusters_ = !(nocl && nocl[0] == '1');
     e->max_cluster_ = gemv_max_cluster();
+    const char* nocols = std::getenv("HM_NO_COLS");
+    e->use_cols_ = e->use_clusters_ && !(nocols && nocols[0] == '1');
     const char* nopf = std::getenv("HM_NO_PREFETCH");
     e->use_prefetch_ = !(nopf && nopf[0] == '1');
     const char* notc = std::getenv("HM_NO_TC");
@@ -106,7 +108,7 @@ Engine::~Engine() {
     fr(embed_); fr(final_norm_); fr(rope_cos_); fr(rope_sin_);
     for (auto& l : layers_) {
         fr(l.in_ln); fr(l.post_ln); fr(l.qkv_bias); fr(l.q_norm); fr(l.k_norm);
-        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->tc); fr(w->scales); fr(w->codes); fr(w->kq_data); fr(w->kq_tile_type); }
+        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->cols); fr(w->tc); fr(w->scales); fr(w->codes); fr(w->kq_data); fr(w->kq_tile_type); }
     }
     fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes); fr(lm_head_.kq_data); fr(lm_head_.kq_tile_type);
     fr(xpack_); fr(xpack_attn_); fr(xpack_act_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
@@ -361,6 +363,28 @@ int Engine::finalize() {
         if (l.down.loaded_parts != 1) return fail(HM_ERR_STATE, p + "down projection");
         if (cfg_.has_qk_norm && (!l.q_norm || !l.k_norm)) return fail(HM_ERR_STATE, p + "q_norm/k_norm");
     }
+    // Decode passes of up to 8 rows run the layer projections from a copy grouped by output columns
+    // (no partial sum crosses a CTA); shapes that do not fit one CTA per SM stay on the slab kernels.
+    if (use_cols_ && cfg_.weight_dtype == HM_BF16) {
+        const char* mk = std::getenv("HM_COLS_MASK");  // tuning knob: 1 QKV, 2 O, 4 gate/up, 8 down
+        const int mask = mk ? std::atoi(mk) : 15;
+        for (int i = 0; i < L_; ++i) {
+            LayerW& l = layers_[i];
+            struct { LinearW* w; int epi, pro, bit; } jobs[4] = {{&l.qkv, EPI_QKV_ROPE, PRO_RMSNORM, 1}, {&l.o, EPI_STORE, PRO_PLAIN, 2}, {&l.gu, EPI_SWIGLU, PRO_RMSNORM, 4}, {&l.down, EPI_STORE, PRO_PLAIN, 8}};
+            for (auto& j : jobs) {
+                if (!(mask & j.bit)) continue;
+                int grid = 0;
+                size_t smem = 0;
+                if (j.epi == EPI_QKV_ROPE && (cfg_.has_qk_norm || hd_ % 8 != 0)) continue;
+                if (!j.w->slabs || !gemv_cols_plan(j.epi, j.pro, j.w->K, j.w->N, 1, sm_count_, &grid, &smem)) continue;
+                const size_t bytes = (size_t)cols_groups(j.epi, j.w->N) * j.w->K * 16;
+                HM_CUDA(cudaMalloc(&j.w->cols, bytes));
+                HM_CUDA(launch_pack_cols(j.w->slabs, j.w->K, j.w->N, j.epi, qdim_, kvdim_, hd_, j.w->cols, stream_));
+                j.w->cols_epi = j.epi;
+            }
+        }
+        HM_CUDA(cudaStreamSynchronize(stream_));
+    }
     std::vector<float> c, s;
     build_rope_table(hd_, cfg_.max_position_embeddings, cfg_.rope_theta, &c, &s);
     HM_CUDA(cudaMalloc(&rope_cos_, c.size() * 4));
@@ -493,7 +517,7 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 8)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
     if (const char* ns = std::getenv("HM_ATT_NSPLIT")) {  // tuning knob: CTAs per (row, KV head)
         const int v = std::atoi(ns);
-        if (v >= 1 && v <= (att_cluster_ ? 8 : sm_count_)) att_nsplit_ = v;
+        if (v >= 1 && v <= (att_cluster_ ? std::min(max_cluster_, 16) : sm_count_)) att_nsplit_ = v;
     }
     HM_CUDA(cudaMalloc(&att_acc_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * hd_ * 4));
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
@@ -844,8 +868,15 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.amax_idx = amax_idx ? amax_idx + (size_t)m0 * nslabs : nullptr;
             a.partial = partial_;
             a.tickets = tickets_;
-            if (a.cluster == 0 && gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
-            ce = launch_gemv_bf16(a, mp, stream_, pdl_);
+            int cgrid = 0;
+            size_t csmem = 0;
+            if (L.cols && L.cols_epi == epi && gemv_cols_plan(epi, pro, L.K, L.N, mp, sm_count_, &cgrid, &csmem)) {
+                a.W = L.cols;
+                ce = launch_gemv_cols(a, mp, sm_count_, stream_, pdl_);
+            } else {
+                if (a.cluster == 0 && gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
+                ce = launch_gemv_bf16(a, mp, stream_, pdl_);
+            }
         } else if (L.kind == HM_Q4_K) {
             KQuantArgs a{};
             a.data = L.kq_data;
@@ -915,7 +946,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         pf_ptr_ = nullptr;
         pf_bytes_ = 0;
         if (!pf || !w || !w->slabs || off >= w->bytes()) return;
-        pf_ptr_ = (const char*)w->slabs + off;
+        pf_ptr_ = (const char*)(w->cols ? w->cols : w->slabs) + off;
         pf_bytes_ = std::min(cap, w->bytes() - off);
     };
     constexpr size_t LM_PF = 24u << 20;  // the LM head does not fit the L2: only its first 2 x 24 MB are fetched early
@@ -963,6 +994,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             at.xp_out = xpack_attn_;
             at.xp_mpad = tc_mpad(M);
         }
+        if (gemv_trace_ && *launches < 512) at.trace = gemv_trace_ + (size_t)*launches * 8;
         at.early_pages = row_seq == nullptr ? 1 : 0;  // decode passes: one row per sequence; prefill chunks write several positions of one sequence
         at.err_flag = err_flag_;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
@@ -1233,22 +1265,23 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
         std::vector<unsigned long long> t(512 * 8);
         HM_CUDA(cudaMemcpy(t.data(), gemv_trace_, t.size() * 8, cudaMemcpyDeviceToHost));
         // launch indices of the projections in a decode pass: 1 + l*5 + {0: qkv, 2: o, 3: gate_up, 4: down}, then 1 + 5L: LM head
-        const char* names[4] = {"qkv", "o", "gate_up", "down"};
-        const int offs[4] = {0, 2, 3, 4};
-        for (int c = 0; c < 4; ++c) {
+        const char* names[5] = {"qkv", "attn", "o", "gate_up", "down"};
+        for (int c = 0; c < 5; ++c) {
             double d[6] = {0, 0, 0, 0, 0, 0}, gap = 0;
             int n = 0;
             for (int l = 0; l < L_; ++l) {
-                const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + offs[c]) * 8;
-                if (!r[0] || !r[6]) continue;
+                const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + c) * 8;
+                bool whole = true;
+                for (int i = 0; i < 7; ++i) whole = whole && r[i] != 0;
+                if (!whole) continue;
                 for (int i = 0; i < 6; ++i) d[i] += (double)(r[i + 1] - r[i]);
-                // time from the previous projection's store to this one seeing its predecessor done (attention sits between qkv and o)
-                const int prev = c == 0 ? (l == 0 ? -1 : 1 + (l - 1) * 5 + 4) : 1 + l * 5 + offs[c - 1];
+                // time from the previous launch's last store (as CTA 0 saw it) to this one seeing its predecessor done
+                const int prev = c == 0 ? (l == 0 ? -1 : 1 + (l - 1) * 5 + 4) : 1 + l * 5 + c - 1;
                 if (prev >= 0 && t[(size_t)prev * 8 + 6]) gap += (double)(r[1] - t[(size_t)prev * 8 + 6]);
                 ++n;
             }
             if (n)
-                std::fprintf(stderr, "[hm gemv trace] %-8s resident->dep %.2f | stage x %.2f | multiply %.2f | publish+cluster barrier %.2f | reduce %.2f | epilogue %.2f | prev store -> dep seen %.2f us (mean of %d)\n", names[c],
+                std::fprintf(stderr, "[hm gemv trace] %-8s resident->dep %.2f | stage inputs %.2f | multiply %.2f | publish+cluster barrier %.2f | reduce %.2f | epilogue %.2f | prev store -> dep seen %.2f us (mean of %d)\n", names[c],
                              d[0] / n / 1e3, d[1] / n / 1e3, d[2] / n / 1e3, d[3] / n / 1e3, d[4] / n / 1e3, d[5] / n / 1e3, gap / n / 1e3, n);
         }
     }

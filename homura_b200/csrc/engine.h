@@ -20,6 +20,8 @@ struct LinearW {
     int K = 0, N = 0;        // N = output count of the (possibly fused) projection
     int kind = -1;           // HM_BF16 (slab layout) | HM_Q8_0 | HM_Q4_0 (split scales + codes)
     uint16_t* slabs = nullptr;
+    uint16_t* cols = nullptr;  // copy in column groups of 8 (gemv_cols.cu) for decode passes of up to 8 rows; cols_epi = the epilogue it was grouped for
+    int cols_epi = -1;
     uint16_t* tc = nullptr;  // second copy in the tensor-core tile layout (gemm_tc.h), used for passes over more than 8 rows
     uint16_t* scales = nullptr;
     uint8_t* codes = nullptr;
@@ -95,6 +97,7 @@ class Engine {
     bool finalized_ = false, quant_ = false, pdl_ = true;
     bool use_clusters_ = true;  // split reductions through thread-block clusters / DSMEM (HM_NO_CLUSTER=1: global scratch + tickets)
     int max_cluster_ = 8;
+    bool use_cols_ = true;      // layer projections of up to 8 rows run the column-group kernel (HM_NO_COLS=1: cluster split-K over slabs)
     bool use_prefetch_ = true;  // decode kernels pull the weights of the kernel two launches ahead into the L2 (HM_NO_PREFETCH=1 disables)
     const void* pf_ptr_ = nullptr;  // prefetch target handed to the next projection launch
     unsigned long long pf_bytes_ = 0;

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     // staged weights first (bulk copies want 16-byte aligned destinations), then the f32 scratch
     float* smem = ST ? smem_raw + (size_t)rps * (SLAB * 2 / 4) : smem_raw;
     const uint4* wst = reinterpret_cast<const uint4*>(smem_raw);  // [nrows][16] x 16 B
-    __shared__ uint64_t s_wbar;
+    __shared__ uint64_t s_wbar, s_rbar;  // staged weights; split-K partials pushed into rank 0
     __shared__ volatile int s_abort;
     float* xs = smem;                 // [M][rps]
     float* red = smem + M * rps;      // [8][M][128], later vals[M][128]
@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     float* nws = xfull + (a.xfull ? M * a.K : 0);  // [rps] RMSNorm weights of this CTA's K range
     float* cs_s = nws + rps;                        // [M][128] RoPE cos, [M][128] sin of this slab's columns (QKV epilogue)
     float* sn_s = cs_s + M * SLAB;
-    __shared__ int s_page[MAX_M];                   // page of every row's new token
+    float* bias_s = sn_s + M * SLAB;                // [128] bias of this slab's columns (QKV epilogue with bias)
+    __shared__ int s_page[MAX_M], s_pos[MAX_M];     // page and position of every row's new token
     __shared__ float s_inv[MAX_M];
     __shared__ float s_warp[8][MAX_M];
     __shared__ int s_last;
@@ -119,6 +120,21 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         }
     }
 
+    if (CL) {
+        // Rank 0 of the cluster receives every other rank's partial by asynchronous stores that count bytes on
+        // its mbarrier; the barrier is armed here and published by a cluster barrier that costs nothing on the
+        // dependent-kernel chain because it happens before the dependency wait.
+        if (tid == 0) {
+            if (!ST) s_abort = 0;
+            if (cluster_ctarank() == 0) {
+                mb_init(&s_rbar, 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                mb_expect_tx(&s_rbar, (uint32_t)(a.ksplit - 1) * (uint32_t)(M * SLAB) * 4u);
+            }
+        }
+        cluster_arrive_release();
+        cluster_wait_acquire();
+    }
     if (a.pro == PRO_RMSNORM)
         for (int r = tid; r < nrows; r += GEMV_THREADS) nws[r] = __ldg(a.norm_w + k0 + r);
     if (a.epi == EPI_QKV_ROPE) {
@@ -134,12 +150,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         }
         if (tid < M && tid < a.m_valid) {
             const int pos = a.row_pos[tid], seq = a.row_seq ? a.row_seq[tid] : tid;
+            s_pos[tid] = pos;
             s_page[tid] = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
         }
+        if (a.bias && tid < SLAB) bias_s[tid] = n0e + tid < a.N ? __ldg(a.bias + n0e + tid) : 0.f;
     }
 
     pdl_wait();
     if (tr) a.trace[1] = global_timer();  // predecessor complete
+
+    // the residual element this thread adds in the epilogue (known epilogue CTA only): requested now, used after the reduction
+    float resid_v = 0.f;
+    const bool resid_early = a.epi == EPI_STORE && a.resid && tid < M * SLAB && (CL ? cluster_ctarank() == 0 : a.ksplit == 1);
+    if (resid_early) {
+        const int m = tid / SLAB, n = slab * SLAB + (tid % SLAB);
+        if (n < a.N && m < a.m_valid) resid_v = ld_cg_f32(a.resid + (size_t)m * a.ldy + n);
+    }
 
     // ---- prologue: activation slice [k0, k0+nrows) of every row into shared memory ----
     if (a.pro == PRO_RMSNORM) {
@@ -148,10 +174,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         for (int m = 0; m < M; ++m) {
             float s = 0.f;
             const float* xr = a.x + (size_t)m * a.ldx;
-            for (int k = tid; k < a.K; k += GEMV_THREADS) {
-                float v = __ldg(xr + k);
-                if (a.xfull) xfull[m * a.K + k] = v;  // one trip to the L2 for both the sum and the slice
-                s = fmaf(v, v, s);
+            if (a.xfull) {
+                s = stage_row<GEMV_THREADS, true>(xr, xfull + m * a.K, a.K, tid);  // one trip to the L2 for both the sum and the slice
+            } else {
+                for (int k = tid; k < a.K; k += GEMV_THREADS) {
+                    float v = __ldg(xr + k);
+                    s = fmaf(v, v, s);
+                }
             }
             ss[m] = warp_sum(s);
         }
@@ -178,10 +207,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         }
     } else {
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const float* xr = a.x + (size_t)m * a.ldx + k0;
-            for (int r = tid; r < nrows; r += GEMV_THREADS) xs[m * rps + r] = __ldg(xr + r);
-        }
+        for (int m = 0; m < M; ++m) stage_row<GEMV_THREADS, false>(a.x + (size_t)m * a.ldx + k0, xs + m * rps, nrows, tid);
     }
     __syncthreads();
     if (tr) a.trace[2] = global_timer();  // activations in shared memory
@@ -247,25 +273,23 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     __syncthreads();
     float* vals = red;  // [M][128]
     if (CL) {
-        // The CTAs of one cluster hold the K-splits of this slab.  Each leaves its partial in
-        // its own shared memory; after a cluster barrier rank 0 adds them in rank order through
-        // distributed shared memory (no global round trip, no atomics) and runs the epilogue.
-        // Every rank PUSHES its partial into rank 0's shared memory (remote stores are posted), arrives at
-        // the cluster barrier and is done; rank 0 waits once and adds the slots in rank order from its own
-        // shared memory.  One barrier, no remote loads on the critical path.
+        // The CTAs of one cluster hold the K-splits of this slab.  Every rank but 0 sends its partial into
+        // slot `rank` of rank 0's shared memory with asynchronous stores that count bytes on rank 0's
+        // mbarrier, and is done; rank 0 waits (bounded) for the byte count and adds the slots in rank order
+        // from its own shared memory.  No cluster barrier and no remote load on the critical path.
         constexpr int PER = (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS;
         const uint32_t rank = cluster_ctarank();
+        const uint32_t rbar0 = dsmem_addr(&s_rbar, 0u);
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int idx = tid + i * GEMV_THREADS;
             if (idx < M * SLAB) {
                 if (rank == 0) slots[idx] = mine[i];
-                else st_dsmem_f32(dsmem_addr(slots + rank * (M * SLAB) + idx, 0u), mine[i]);
+                else st_async_f32(dsmem_addr(slots + rank * (M * SLAB) + idx, 0u), mine[i], rbar0);
             }
         }
-        cluster_arrive_release();
-        if (rank != 0) return;
-        cluster_wait_acquire();
+        if (rank != 0) return;  // nothing reads this CTA's shared memory; its stores are on their way
+        if (a.ksplit > 1 && !mb_wait_cluster(&s_rbar, 0, a.err_flag, &s_abort)) return;  // bounded
         if (tr) a.trace[4] = global_timer();  // all ranks' partials have landed
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
@@ -317,7 +341,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
             if (n < a.N && m < a.m_valid) {
                 float v = vals[idx];
                 if (a.bias) v += __ldg(a.bias + n);
-                if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
+                if (a.resid) v = (resid_early && idx == tid ? resid_v : a.resid[(size_t)m * a.ldy + n]) + v;
                 a.y[(size_t)m * a.ldy + n] = v;
             }
         }
@@ -366,10 +390,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         const int hd = a.hd, half = hd >> 1, hps = SLAB / hd;
         // bias
         if (a.bias) {
-            for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
-                const int n = n0 + (idx % SLAB);
-                if (n < a.N) vals[idx] += __ldg(a.bias + n);
-            }
+            for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) vals[idx] += bias_s[idx % SLAB];
             __syncthreads();
         }
         // per-head RMSNorm of Q and K heads (Qwen3), before the rotation
@@ -394,7 +415,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
             if (n >= a.N || m >= a.m_valid) continue;
             const int hh = c / hd, d = c % hd;
             const int nh = n0 + hh * hd;
-            const int pos = a.row_pos[m];
+            const int pos = s_pos[m];
             float v = vals[idx];
             if (nh < a.q_dim + a.kv_dim) {
                 const float other = (d < half) ? -vals[idx + half] : vals[idx - half];
@@ -467,7 +488,7 @@ cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
     a.xfull = CL && a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;
     if (a.xfull) floats += (size_t)M * a.K;
     floats += (size_t)a.rows_per_split;                            // pre-fetched RMSNorm weights
-    if (a.epi == EPI_QKV_ROPE) floats += 2 * (size_t)M * SLAB;     // pre-fetched RoPE rows
+    if (a.epi == EPI_QKV_ROPE) floats += 2 * (size_t)M * SLAB + SLAB;  // pre-fetched RoPE rows and bias
     size_t smem = sizeof(float) * floats;
     // cluster launches over the slab layout whose slice fits: weights staged in shared memory before the dependency wait
     static const bool no_stage = [] { const char* e = std::getenv("HM_NO_STAGE"); return e && e[0] == '1'; }();

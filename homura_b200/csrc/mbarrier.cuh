@@ -19,6 +19,24 @@ __device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
     asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same poll with acquire semantics at cluster scope: for barriers completed by other CTAs' st.async stores.
+__device__ __forceinline__ bool mb_try_cluster(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mb_wait_cluster(uint64_t* b, uint32_t parity, int* err, volatile int* abort_flag) {
+    unsigned long long it = 0;
+    while (!mb_try_cluster(b, parity)) {
+        if (*abort_flag) return false;
+        if (++it > MB_SPIN_LIMIT) {
+            *abort_flag = 1;
+            if (err) atomicExch(err, 2);
+            return false;
+        }
+    }
+    return true;
+}
 // Bounded wait; on overrun raises *err and returns false (callers skip the work that needed the data).
 __device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* err, volatile int* abort_flag) {
     unsigned long long it = 0;
