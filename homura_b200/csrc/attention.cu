@@ -62,6 +62,12 @@ __host__ __device__ inline int pick_nslots(int g, int early_pages, int max_pages
     return (cap + nsub - 1) / nsub * nsub;
 }
 
+// Slots for the splits' (max, sum, acc) triples in rank 0 of a cluster are allocated in steps of 4 / 8 / 16,
+// the unused ones hold neutral triples, and the merge loops run to that compile-time count with
+// unconditional loads (a loop bounded by the run-time split count is compiled with one shared-memory round
+// trip per iteration, which tripled the merge time).
+__host__ __device__ inline int merge_slot_cap(int nsplit) { return nsplit <= 4 ? 4 : nsplit <= 8 ? 8 : 16; }
+
 template <bool BF16>
 __device__ __forceinline__ void unpack_store(float* o, const uint4& v) {
     if (BF16) {
@@ -86,30 +92,34 @@ __device__ __forceinline__ void store_out(const AttnArgs& a, int m, int head, in
 // Rank 0 of a (row, KV head) cluster, after every split's (max, sum, acc) triple has landed in its
 // shared memory: one scale factor per (split, head) first (g * nsplit exponentials instead of one per
 // output element and split), then every output element is a short multiply-add over the splits.
-template <int HD>
-__device__ __forceinline__ void cluster_rank0_merge(const AttnArgs& a, int g, int head0, int m, float* scratch, const float* c_o, const float* c_ml) {
+template <int HD, int NS>
+__device__ __forceinline__ void cluster_rank0_merge_n(const AttnArgs& a, int g, int head0, int m, float* scratch, const float* c_o, const float* c_ml) {
     const int tid = threadIdx.x, nthreads = blockDim.x;
-    if (a.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) a.trace[4] = a.trace[5] = global_timer();  // every split's triple has landed
-    float* sc_s = scratch;                 // [nsplit][g]
-    float* l_s = scratch + a.nsplit * g;   // [g] merged sums
-    // loops over the splits are unrolled to the largest cluster (16) with the bound as a predicate, so that
-    // their shared-memory loads are issued together instead of one round trip per split
-    constexpr int MAXS = 16;
-    for (int i = tid; i < g * a.nsplit; i += nthreads) {
-        const int r = i / g, jj = i - r * g;
-        float M = -INFINITY;
+    const bool tr = a.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    __syncthreads();  // rank 0's own triple and the neutral ones were written by its threads with plain stores
+    if (tr) a.trace[4] = a.trace[5] = global_timer();  // every split's triple has landed
+    float* sc_s = scratch;               // [g][NS] scale of every slot's triple (zero for a neutral one)
+    float* l_s = scratch + G_MAX * 16;   // [g] merged sums
+    for (int i = tid; i < g * NS; i += nthreads) {
+        const int jj = i / NS, r = i - jj * NS;
+        float ms[NS];
 #pragma unroll
-        for (int r2 = 0; r2 < MAXS; ++r2)
-            if (r2 < a.nsplit) M = fmaxf(M, c_ml[((size_t)r2 * g + jj) * 2]);
-        const float ms = c_ml[((size_t)r * g + jj) * 2];
-        sc_s[i] = ms > -INFINITY ? expf(ms - M) : 0.f;
+        for (int r2 = 0; r2 < NS; ++r2) ms[r2] = c_ml[((size_t)r2 * g + jj) * 2];
+        float M = ms[0];
+#pragma unroll
+        for (int r2 = 1; r2 < NS; ++r2) M = fmaxf(M, ms[r2]);
+        const float mine = c_ml[((size_t)r * g + jj) * 2];
+        sc_s[i] = mine > -INFINITY ? expf(mine - M) : 0.f;
     }
     __syncthreads();
+    if (tr) a.trace[10] = global_timer();
     if (tid < g) {
+        float lv[NS];
+#pragma unroll
+        for (int r = 0; r < NS; ++r) lv[r] = c_ml[((size_t)r * g + tid) * 2 + 1] * sc_s[tid * NS + r];
         float l = 0.f;
 #pragma unroll
-        for (int r = 0; r < MAXS; ++r)
-            if (r < a.nsplit) l = fmaf(c_ml[((size_t)r * g + tid) * 2 + 1], sc_s[r * g + tid], l);
+        for (int r = 0; r < NS; ++r) l += lv[r];
         l_s[tid] = l;
     }
     float o[(G_MAX * HD + ATT_THREADS - 1) / ATT_THREADS];
@@ -119,23 +129,54 @@ __device__ __forceinline__ void cluster_rank0_merge(const AttnArgs& a, int g, in
         float v = 0.f;
         if (i < g * HD) {
             const int jj = i / HD;
+            float sc[NS], cv[NS];
 #pragma unroll
-            for (int r = 0; r < MAXS; ++r)
-                if (r < a.nsplit) v = fmaf(c_o[(size_t)r * g * HD + i], sc_s[r * g + jj], v);
+            for (int r4 = 0; r4 < NS; r4 += 4) {
+                const float4 t4 = *reinterpret_cast<const float4*>(sc_s + jj * NS + r4);
+                sc[r4] = t4.x; sc[r4 + 1] = t4.y; sc[r4 + 2] = t4.z; sc[r4 + 3] = t4.w;
+            }
+#pragma unroll
+            for (int r = 0; r < NS; ++r) cv[r] = c_o[(size_t)r * g * HD + i];
+#pragma unroll
+            for (int r = 0; r < NS; ++r) v = fmaf(cv[r], sc[r], v);
         }
         o[k] = v;
     }
     __syncthreads();
+    if (tr) a.trace[11] = global_timer();
 #pragma unroll
     for (int k = 0; k < (G_MAX * HD + ATT_THREADS - 1) / ATT_THREADS; ++k) {
         const int i = tid + k * nthreads;
         if (i < g * HD) store_out<HD>(a, m, head0 + i / HD, i % HD, o[k] / l_s[i / HD]);
     }
+    if (tr) a.trace[12] = global_timer();
+}
+
+// Rank 0 of a (row, KV head) cluster, after every split's (max, sum, acc) triple has landed in its
+// shared memory: one scale factor per (slot, head) first (exponentials per slot and head instead of per
+// output element), then every output element is a short multiply-add over the slots.
+template <int HD>
+__device__ __forceinline__ void cluster_rank0_merge(const AttnArgs& a, int g, int head0, int m, float* scratch, const float* c_o, const float* c_ml) {
+    const int cap = merge_slot_cap(a.nsplit);
+    if (cap == 4) cluster_rank0_merge_n<HD, 4>(a, g, head0, m, scratch, c_o, c_ml);
+    else if (cap == 8) cluster_rank0_merge_n<HD, 8>(a, g, head0, m, scratch, c_o, c_ml);
+    else cluster_rank0_merge_n<HD, 16>(a, g, head0, m, scratch, c_o, c_ml);
+}
+
+// Neutral triples for the slots no split writes: [first, merge_slot_cap(nsplit)).  Rank 0 only, before its merge.
+template <int HD>
+__device__ __forceinline__ void fill_neutral_slots(const AttnArgs& a, int first, int g, float* c_o, float* c_ml) {
+    const int cap = merge_slot_cap(a.nsplit);
+    for (int i = first * g * HD + threadIdx.x; i < cap * g * HD; i += blockDim.x) c_o[i] = 0.f;
+    for (int i = first * g + threadIdx.x; i < cap * g; i += blockDim.x) {
+        c_ml[i * 2] = -INFINITY;
+        c_ml[i * 2 + 1] = 0.f;
+    }
 }
 
 template <int HD, bool CL>
 __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p,
-                                                      uint64_t* rbar = nullptr, volatile int* abortf = nullptr);
+                                                      uint64_t* rbar = nullptr, volatile int* abortf = nullptr, int nact = -1);
 
 // Cluster splits hand their triples to rank 0 either with plain remote stores followed by a cluster barrier
 // (rbar == nullptr), or -- when rank 0 armed an mbarrier for them before the dependency wait -- with
@@ -149,7 +190,7 @@ __device__ __forceinline__ void push_f32(float* slot_in_rank0, float v, uint32_t
 __device__ __forceinline__ bool pushes_landed(const AttnArgs& a, uint64_t* rbar, volatile int* abortf) {
     if (rbar) {
         if (cluster_ctarank() != 0) return false;
-        return a.nsplit == 1 || mb_wait_cluster(rbar, 0, a.err_flag, abortf);  // bounded
+        return mb_wait_cluster(rbar, 0, a.err_flag, abortf);  // bounded (completes at once when no other split is active)
     }
     cluster_arrive_release();
     if (cluster_ctarank() != 0) return false;
@@ -160,8 +201,9 @@ __device__ __forceinline__ bool pushes_landed(const AttnArgs& a, uint64_t* rbar,
 // One-head-per-warp kernels: publish the warp's triple at entry (slot * g + head) = warp, then merge.
 template <int HD, bool CL>
 __device__ __forceinline__ void merge_and_write(const AttnArgs& a, bool active, float run_m, float run_l, const float (&acc)[HD / 32], int nsub, int g, int head0, int split, int kvh, int m, float* w_ml,
-                                                float* w_acc, float* c_o, float* c_ml, int* s_last_p, uint64_t* rbar = nullptr, volatile int* abortf = nullptr) {
+                                                float* w_acc, float* c_o, float* c_ml, int* s_last_p, uint64_t* rbar = nullptr, volatile int* abortf = nullptr, int nact = -1) {
     constexpr int EPL = HD / 32;
+    if (nact < 0) nact = a.nsplit;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (CL && nsub == 1) {
         // one warp per query head and nothing to merge inside the CTA: every warp stores its triple straight
@@ -169,13 +211,35 @@ __device__ __forceinline__ void merge_and_write(const AttnArgs& a, bool active, 
         const uint32_t rank = cluster_ctarank();
         const uint32_t rbar0 = rbar ? dsmem_addr(rbar, 0u) : 0u;
         if (warp < g) {
-            float* po = c_o + ((size_t)rank * g + warp) * HD + lane * EPL;
+            // four consecutive output dims per store: a lane's own (hd 128) or an even lane's and its neighbour's (hd 64)
+            float4 v4;
+            bool sender = true;
+            int d0 = lane * EPL;
+            if constexpr (EPL == 4) {
+                v4 = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            } else {
+                const float nx = __shfl_down_sync(0xffffffffu, acc[0], 1), ny = __shfl_down_sync(0xffffffffu, acc[EPL - 1], 1);
+                v4 = make_float4(acc[0], acc[EPL - 1], nx, ny);
+                sender = (lane & 1) == 0;
+            }
+            float* po = c_o + ((size_t)rank * g + warp) * HD + d0;
             float* pm = c_ml + ((size_t)rank * g + warp) * 2;
+            if (rank == 0) {
+                if (sender) *reinterpret_cast<float4*>(po) = v4;
+                if (lane == 0) {
+                    pm[0] = run_m;
+                    pm[1] = run_l;
+                }
+            } else if (rbar0) {
+                if (sender) st_async_f32x4(dsmem_addr(po, 0u), v4, rbar0);
+                if (lane == 0) st_async_f32x2(dsmem_addr(pm, 0u), run_m, run_l, rbar0);
+            } else {
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) push_f32(po + e, acc[e], rank, rbar0);
-            if (lane == 0) {
-                push_f32(pm, run_m, rank, rbar0);
-                push_f32(pm + 1, run_l, rank, rbar0);
+                for (int e = 0; e < EPL; ++e) st_dsmem_f32(dsmem_addr(po + e, 0u), acc[e]);
+                if (lane == 0) {
+                    st_dsmem_f32(dsmem_addr(pm, 0u), run_m);
+                    st_dsmem_f32(dsmem_addr(pm + 1, 0u), run_l);
+                }
             }
         }
         if (!pushes_landed(a, rbar, abortf)) return;
@@ -191,7 +255,7 @@ __device__ __forceinline__ void merge_and_write(const AttnArgs& a, bool active, 
         for (int e = 0; e < EPL; ++e) w_acc[warp * HD + lane * EPL + e] = active ? acc[e] : 0.f;
     }
     __syncthreads();
-    merge_slots_and_write<HD, CL>(a, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, s_last_p, rbar, abortf);
+    merge_slots_and_write<HD, CL>(a, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, s_last_p, rbar, abortf, nact);
 }
 
 // Merge the (max, sum, acc) triples of nsub page slots per head (entry slot * g + head), then the
@@ -199,7 +263,8 @@ __device__ __forceinline__ void merge_and_write(const AttnArgs& a, bool active, 
 // order), or through global scratch by whichever CTA arrives last at the ticket.
 template <int HD, bool CL>
 __device__ __forceinline__ void merge_slots_and_write(const AttnArgs& a, int nsub, int g, int head0, int split, int kvh, int m, float* w_ml, float* w_acc, float* c_o, float* c_ml, int* s_last_p, uint64_t* rbar,
-                                                      volatile int* abortf) {
+                                                      volatile int* abortf, int nact) {
+    if (nact < 0) nact = a.nsplit;
     const int tid = threadIdx.x;
     const int nthreads = blockDim.x;
     int& s_last = *s_last_p;
@@ -296,7 +361,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     float* w_ml = p_s + ATT_WARPS * PT;           // [ATT_WARPS][2]
     float* w_acc = w_ml + ATT_WARPS * 2;          // [ATT_WARPS][HD]
     float* c_o = w_acc + ATT_WARPS * HD;          // cluster mode, rank 0: [nsplit][g][HD] triples pushed by the ranks
-    float* c_ml = c_o + (CL ? a.nsplit : 1) * g * HD;  // [nsplit][g][2]
+    float* c_ml = c_o + (CL ? merge_slot_cap(a.nsplit) : 1) * g * HD;  // [slots][g][2]
     __shared__ int s_last;
     __shared__ uint64_t s_rbar;  // cluster mode, rank 0: counts the bytes of the other splits' triples
     __shared__ volatile int s_abort;
@@ -306,6 +371,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     const int head0 = kvh * g;
     const bool tr = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
     if (tr) a.trace[0] = global_timer();  // CTA resident
+    if (a.trace && tid == 0) atomicMax(a.trace + 8, global_timer());  // the launch's last CTA to become resident
 
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32)
@@ -326,6 +392,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     const T* kpool = reinterpret_cast<const T*>(a.k_pool);
     const T* vpool = reinterpret_cast<const T*>(a.v_pool);
     const int safe_end = a.early_pages ? min(p1, (kvlen - 1) / PT) : p0;  // pages [p0, safe_end) may be read early
+    const int nact = pps > 0 ? (npages + pps - 1) / pps : 1;  // splits that have pages (known to every split: lengths are final before the chain starts)
 
     // cooperative tile loads: thread -> (slot, piece) pairs, the same mapping for every group
     const int total_pieces = nsub * TL::PIECES;  // per K (and per V), <= MAXP * ATT_THREADS
@@ -377,11 +444,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
             if (cluster_ctarank() == 0) {
                 mb_init(&s_rbar, 1);
                 asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-                mb_expect_tx(&s_rbar, (uint32_t)(a.nsplit - 1) * (uint32_t)(g * (HD + 2)) * 4u);
+                mb_expect_tx(&s_rbar, (uint32_t)(nact - 1) * (uint32_t)(g * (HD + 2)) * 4u);
             }
         }
+        if (cluster_ctarank() == 0) fill_neutral_slots<HD>(a, nact, g, c_o, c_ml);  // slots no split will write
         cluster_arrive_release();
         cluster_wait_acquire();
+        if (p0 >= p1 && cluster_ctarank() != 0) return;  // a split without pages sends nothing and is not waited for
     }
     if (resident) {
 #pragma unroll 1
@@ -484,8 +553,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     }
 
     if (tr) a.trace[3] = global_timer();  // this warp's pages done
-    merge_and_write<HD, CL>(a, active, run_m, run_l, acc, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, &s_last, CL ? &s_rbar : nullptr, &s_abort);
+    if (a.trace && tid == 0 && blockIdx.y == 0 && blockIdx.z == 0 && late0 < p1) a.trace[7] = global_timer();  // the split that holds the new token is done
+    merge_and_write<HD, CL>(a, active, run_m, run_l, acc, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, &s_last, CL ? &s_rbar : nullptr, &s_abort, CL ? nact : -1);
     if (tr) a.trace[6] = global_timer();  // merged and stored (rank 0 of the cluster)
+    if (a.trace && tid == 0) atomicMax(a.trace + 9, global_timer());  // the launch's last rank 0 to finish
 }
 
 // ---- streaming variant for long contexts ---------------------------------------------------------
@@ -539,12 +610,12 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     float* p_s = q_s + G_MAX * HD;                                               // [ATT_WARPS][G_MAX][16]
     const int g_early = a.heads / a.kv_heads;
     float* c_o = p_s + ATT_WARPS * G_MAX * PT;                                   // cluster mode, rank 0: [nsplit][g][HD]
-    float* c_ml = c_o + (CL ? a.nsplit : 1) * g_early * HD;                      // [nsplit][g][2]
+    float* c_ml = c_o + (CL ? merge_slot_cap(a.nsplit) : 1) * g_early * HD;     // [slots][g][2]
     // the per-warp results reuse the ring once every page has been consumed
     float* w_ml = reinterpret_cast<float*>(ring);                                // [ATT_WARPS * g][2]
     float* w_acc = w_ml + ATT_WARPS * G_MAX * 2;                                 // [ATT_WARPS * g][HD]
     static_assert(sizeof(float) * (ATT_WARPS * G_MAX * 2 + ATT_WARPS * G_MAX * HD) <= (size_t)ST::STAGES * ST::STAGE_BYTES, "ring too small for the merge scratch");
-    int32_t* pt_s = reinterpret_cast<int32_t*>(c_ml + (CL ? a.nsplit : 1) * g_early * 2);  // [pages of this CTA]
+    int32_t* pt_s = reinterpret_cast<int32_t*>(c_ml + (CL ? merge_slot_cap(a.nsplit) : 1) * g_early * 2);  // [pages of this CTA]
     __shared__ uint64_t full[ST_MAX_STAGES], empty[ST_MAX_STAGES];
     __shared__ int s_last;
     __shared__ volatile int s_abort;
@@ -565,6 +636,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32)
         l2_prefetch_slice(a.pf_ptr, a.pf_bytes, (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x), (int)(gridDim.x * gridDim.y * gridDim.z), tid);
+    if (CL && cluster_ctarank() == 0) fill_neutral_slots<HD>(a, a.nsplit, g, c_o, c_ml);  // merge slots past the split count
     pdl_wait();
 
     const int seq = a.row_seq ? a.row_seq[m] : m;
@@ -738,7 +810,7 @@ cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
     const int pages_per_cta = (a.max_pages + a.nsplit - 1) / a.nsplit;
     // long contexts: the bulk-copy ring; a slot layout needs ATT_WARPS / g >= 1 as in the kernel above
     const bool stream = a.stream_pages > 0 && pages_per_cta >= ST_MIN_PAGES && pages_per_cta <= ST_MAX_PT;
-    const int slots = CL ? a.nsplit : 1;  // rank 0 of a cluster receives every split's triples
+    const int slots = CL ? merge_slot_cap(a.nsplit) : 1;  // rank 0 of a cluster receives every split's triples
     const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots) : smem_bytes<HD, BF16>(g, slots, pick_nslots<HD, BF16>(g, a.early_pages, a.max_pages, a.nsplit));
     // the opt-in limit only ever grows: launches captured in a graph must stay valid after later calls
     static size_t opted[2] = {40 * 1024, 40 * 1024};  // static shared memory counts against the 48 KB default too
@@ -817,10 +889,10 @@ int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
     return best;
 }
 
-// Cluster variant: the splits of a (row, KV head) form one cluster; about two pages per CTA when
-// the context allows, at most max_cluster CTAs.
+// Cluster variant: the splits of a (row, KV head) form one cluster; one page per CTA when the
+// context allows, at most max_cluster CTAs.
 int attn_pick_cluster(int max_pages, int max_cluster) {
-    int n = (max_pages + 1) / 2;
+    int n = max_pages;
     if (n > max_cluster) n = max_cluster;
     if (n < 1) n = 1;
     return n;

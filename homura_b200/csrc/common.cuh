@@ -45,6 +45,14 @@ __device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) { asm volat
 __device__ __forceinline__ void st_async_f32(uint32_t addr, float v, uint32_t mbar) {
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(__float_as_uint(v)), "r"(mbar) : "memory");
 }
+__device__ __forceinline__ void st_async_f32x2(uint32_t addr, float a, float b, uint32_t mbar) {  // addr 8-byte aligned, counts 8 bytes
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(addr), "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void st_async_f32x4(uint32_t addr, float4 v, uint32_t mbar) {  // addr 16-byte aligned, counts 16 bytes
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(addr), "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)),
+                 "r"(__float_as_uint(v.z)), "r"(__float_as_uint(v.w)), "r"(mbar)
+                 : "memory");
+}
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");

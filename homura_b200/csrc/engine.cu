@@ -87,8 +87,6 @@ int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* 
     const char* nocl = std::getenv("HM_NO_CLUSTER");
     e->use_clusters_ = !(nocl && nocl[0] == '1');
     e->max_cluster_ = gemv_max_cluster();
-    const char* nocols = std::getenv("HM_NO_COLS");
-    e->use_cols_ = e->use_clusters_ && !(nocols && nocols[0] == '1');
     const char* nopf = std::getenv("HM_NO_PREFETCH");
     e->use_prefetch_ = !(nopf && nopf[0] == '1');
     const char* notc = std::getenv("HM_NO_TC");
@@ -363,11 +361,13 @@ int Engine::finalize() {
         if (l.down.loaded_parts != 1) return fail(HM_ERR_STATE, p + "down projection");
         if (cfg_.has_qk_norm && (!l.q_norm || !l.k_norm)) return fail(HM_ERR_STATE, p + "q_norm/k_norm");
     }
-    // Decode passes of up to 8 rows run the layer projections from a copy grouped by output columns
-    // (no partial sum crosses a CTA); shapes that do not fit one CTA per SM stay on the slab kernels.
-    if (use_cols_ && cfg_.weight_dtype == HM_BF16) {
-        const char* mk = std::getenv("HM_COLS_MASK");  // tuning knob: 1 QKV, 2 O, 4 gate/up, 8 down
-        const int mask = mk ? std::atoi(mk) : 15;
+    // Opt-in (HM_COLS_MASK, bits 1 QKV, 2 O, 4 gate/up, 8 down): decode passes of up to 8 rows run those layer
+    // projections from a copy grouped by output columns, where no partial sum crosses a CTA.  Off by default:
+    // with the split-K partials travelling by asynchronous stores the cluster kernels are as fast per launch,
+    // and the larger shared-memory footprint of whole columns delays the residency of the launches behind.
+    if (use_clusters_ && cfg_.weight_dtype == HM_BF16) {
+        const char* mk = std::getenv("HM_COLS_MASK");
+        const int mask = mk ? std::atoi(mk) : 0;
         for (int i = 0; i < L_; ++i) {
             LayerW& l = layers_[i];
             struct { LinearW* w; int epi, pro, bit; } jobs[4] = {{&l.qkv, EPI_QKV_ROPE, PRO_RMSNORM, 1}, {&l.o, EPI_STORE, PRO_PLAIN, 2}, {&l.gu, EPI_SWIGLU, PRO_RMSNORM, 4}, {&l.down, EPI_STORE, PRO_PLAIN, 8}};
@@ -511,10 +511,12 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     if (rc) return rc;
     // attention split scratch
     // sized for the decode step (one row per sequence)
-    // up to 1024 tokens of capacity the splits of a (row, KV head) are one cluster of at most 8 CTAs;
-    // longer caches need more CTAs than a cluster holds and merge through global scratch + ticket
+    // up to 1024 tokens of capacity the splits of a (row, KV head) are one cluster of at most 16 CTAs, one page
+    // per split while the context allows (a page is about 0.65 us of dependent instructions, so pages of a
+    // split cost more than the wider merge); longer caches need more CTAs than a cluster holds and merge
+    // through global scratch + ticket
     att_cluster_ = use_clusters_ && max_pages_ <= 64;
-    att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 8)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
+    att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 16)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
     if (const char* ns = std::getenv("HM_ATT_NSPLIT")) {  // tuning knob: CTAs per (row, KV head)
         const int v = std::atoi(ns);
         if (v >= 1 && v <= (att_cluster_ ? std::min(max_cluster_, 16) : sm_count_)) att_nsplit_ = v;
@@ -527,8 +529,8 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     // step time is no better than the captured kernel chain, which stays the default.
     if (const char* gt = std::getenv("HM_GEMV_TRACE")) {
         if (gt[0] == '1' && !gemv_trace_) {
-            HM_CUDA(cudaMalloc(&gemv_trace_, 512 * 8 * sizeof(unsigned long long)));
-            HM_CUDA(cudaMemset(gemv_trace_, 0, 512 * 8 * sizeof(unsigned long long)));
+            HM_CUDA(cudaMalloc(&gemv_trace_, 512 * 16 * sizeof(unsigned long long)));
+            HM_CUDA(cudaMemset(gemv_trace_, 0, 512 * 16 * sizeof(unsigned long long)));
         }
     }
     const char* mega = std::getenv("HM_PERSISTENT");
@@ -822,7 +824,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             GemvArgs a{};
             a.W = L.slabs;
             a.err_flag = err_flag_;
-            if (gemv_trace_ && *launches < 512) a.trace = gemv_trace_ + (size_t)*launches * 8;
+            if (gemv_trace_ && *launches < 512) a.trace = gemv_trace_ + (size_t)*launches * 16;
             if (m0 == 0) {
                 a.pf_ptr = pf_ptr_;
                 a.pf_bytes = pf_bytes_;
@@ -994,7 +996,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             at.xp_out = xpack_attn_;
             at.xp_mpad = tc_mpad(M);
         }
-        if (gemv_trace_ && *launches < 512) at.trace = gemv_trace_ + (size_t)*launches * 8;
+        if (gemv_trace_ && *launches < 512) at.trace = gemv_trace_ + (size_t)*launches * 16;
         at.early_pages = row_seq == nullptr ? 1 : 0;  // decode passes: one row per sequence; prefill chunks write several positions of one sequence
         at.err_flag = err_flag_;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
@@ -1262,7 +1264,7 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
         // HM_GEMV_TRACE=1: %globaltimer stamps of CTA 0 of every projection launch of the last step:
         // resident -> predecessor done -> activations staged -> weights multiplied -> partials published ->
         // split-K reduced -> stored.  Averaged per launch position within a layer.
-        std::vector<unsigned long long> t(512 * 8);
+        std::vector<unsigned long long> t(512 * 16);
         HM_CUDA(cudaMemcpy(t.data(), gemv_trace_, t.size() * 8, cudaMemcpyDeviceToHost));
         // launch indices of the projections in a decode pass: 1 + l*5 + {0: qkv, 2: o, 3: gate_up, 4: down}, then 1 + 5L: LM head
         const char* names[5] = {"qkv", "attn", "o", "gate_up", "down"};
@@ -1270,15 +1272,46 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
             double d[6] = {0, 0, 0, 0, 0, 0}, gap = 0;
             int n = 0;
             for (int l = 0; l < L_; ++l) {
-                const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + c) * 8;
+                const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + c) * 16;
                 bool whole = true;
                 for (int i = 0; i < 7; ++i) whole = whole && r[i] != 0;
                 if (!whole) continue;
                 for (int i = 0; i < 6; ++i) d[i] += (double)(r[i + 1] - r[i]);
                 // time from the previous launch's last store (as CTA 0 saw it) to this one seeing its predecessor done
                 const int prev = c == 0 ? (l == 0 ? -1 : 1 + (l - 1) * 5 + 4) : 1 + l * 5 + c - 1;
-                if (prev >= 0 && t[(size_t)prev * 8 + 6]) gap += (double)(r[1] - t[(size_t)prev * 8 + 6]);
+                if (prev >= 0 && t[(size_t)prev * 16 + 6]) gap += (double)(r[1] - t[(size_t)prev * 16 + 6]);
                 ++n;
+            }
+            if (n && c == 1) {
+                double late = 0;
+                int nl = 0;
+                for (int l = 0; l < L_; ++l) {
+                    const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + c) * 16;
+                    if (r[1] && r[7] > r[1]) { late += (double)(r[7] - r[1]); ++nl; }
+                }
+                double ph[4] = {0, 0, 0, 0};
+                int np = 0;
+                for (int l = 0; l < L_; ++l) {
+                    const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + c) * 16;
+                    if (!r[5] || !r[10] || !r[11] || !r[12] || !r[6]) continue;
+                    ph[0] += (double)(r[10] - r[5]); ph[1] += (double)(r[11] - r[10]); ph[2] += (double)(r[12] - r[11]); ph[3] += (double)(r[6] - r[12]);
+                    ++np;
+                }
+                if (np) std::fprintf(stderr, "[hm gemv trace] attn     rank-0 merge: scales %.2f | sums %.2f | divide+store %.2f | return %.2f us\n", ph[0] / np / 1e3, ph[1] / np / 1e3, ph[2] / np / 1e3, ph[3] / np / 1e3);
+                if (nl) std::fprintf(stderr, "[hm gemv trace] attn     split holding the new token: pages done %.2f us after dep seen (mean of %d)\n", late / nl / 1e3, nl);
+            }
+            if (n) {
+                // slots 8, 9: latest CTA of the launch to become resident / to finish (atomic maxima over all CTAs)
+                double lr = 0, lf = 0;
+                int nn = 0;
+                for (int l = 0; l < L_; ++l) {
+                    const unsigned long long* r = t.data() + (size_t)(1 + l * 5 + c) * 16;
+                    if (!r[1] || !r[6] || !r[8] || !r[9]) continue;
+                    lr += (double)r[8] - (double)r[1];
+                    lf += (double)r[9] - (double)r[6];
+                    ++nn;
+                }
+                if (nn) std::fprintf(stderr, "[hm gemv trace] %-8s last CTA resident %+.2f us relative to CTA 0 seeing its dependency; last CTA finished %+.2f us after CTA 0\n", names[c], lr / nn / 1e3, lf / nn / 1e3);
             }
             if (n)
                 std::fprintf(stderr, "[hm gemv trace] %-8s resident->dep %.2f | stage inputs %.2f | multiply %.2f | publish+cluster barrier %.2f | reduce %.2f | epilogue %.2f | prev store -> dep seen %.2f us (mean of %d)\n", names[c],

@@ -97,7 +97,6 @@ class Engine {
     bool finalized_ = false, quant_ = false, pdl_ = true;
     bool use_clusters_ = true;  // split reductions through thread-block clusters / DSMEM (HM_NO_CLUSTER=1: global scratch + tickets)
     int max_cluster_ = 8;
-    bool use_cols_ = true;      // layer projections of up to 8 rows run the column-group kernel (HM_NO_COLS=1: cluster split-K over slabs)
     bool use_prefetch_ = true;  // decode kernels pull the weights of the kernel two launches ahead into the L2 (HM_NO_PREFETCH=1 disables)
     const void* pf_ptr_ = nullptr;  // prefetch target handed to the next projection launch
     unsigned long long pf_bytes_ = 0;

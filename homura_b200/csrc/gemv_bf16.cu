@@ -46,6 +46,37 @@ __device__ __forceinline__ void fma_row(float (&acc)[M][8], const uint4& w, cons
     }
 }
 
+// Sum of NS partials `stride` floats apart, in slot order, with every load issued before the first add (a loop
+// bounded by a run-time count is compiled with one shared-memory round trip per iteration).
+template <int NS>
+__device__ __forceinline__ float sum_slots(const float* s, int stride) {
+    float v[NS];
+#pragma unroll
+    for (int r = 0; r < NS; ++r) v[r] = s[r * stride];
+    float t = v[0];
+#pragma unroll
+    for (int r = 1; r < NS; ++r) t += v[r];
+    return t;
+}
+__device__ __forceinline__ float sum_slots_any(const float* s, int stride, int n) {
+    switch (n) {
+        case 2: return sum_slots<2>(s, stride);
+        case 3: return sum_slots<3>(s, stride);
+        case 4: return sum_slots<4>(s, stride);
+        case 5: return sum_slots<5>(s, stride);
+        case 6: return sum_slots<6>(s, stride);
+        case 7: return sum_slots<7>(s, stride);
+        case 8: return sum_slots<8>(s, stride);
+        case 10: return sum_slots<10>(s, stride);
+        case 12: return sum_slots<12>(s, stride);
+        case 14: return sum_slots<14>(s, stride);
+        case 16: return sum_slots<16>(s, stride);
+    }
+    float t = s[0];
+    for (int r = 1; r < n; ++r) t += s[r * stride];
+    return t;
+}
+
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i > bi); }
 
 // The unsplit M = 1 variant (LM head: one long stream per CTA) runs three CTAs per SM (<= 85
@@ -94,6 +125,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
 
     const bool tr = a.trace != nullptr && blockIdx.x == 0 && tid == 0;
     if (tr) a.trace[0] = global_timer();  // CTA resident
+    if (a.trace && tid == 0) atomicMax(a.trace + 8, global_timer());  // the launch's last CTA to become resident
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32) l2_prefetch_slice(a.pf_ptr, a.pf_bytes, blockIdx.x, gridDim.x, tid);
 
@@ -260,44 +292,49 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     }
     __syncthreads();
     float mine[(M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS];
+    float4 mine4 = make_float4(0.f, 0.f, 0.f, 0.f);  // cluster variant: four consecutive columns per thread, sent as one 16-byte store
+    if (CL) {
+        if (tid < M * SLAB / 4) {
 #pragma unroll
-    for (int i = 0; i < (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS; ++i) {
-        const int idx = tid + i * GEMV_THREADS;
-        float v = 0.f;
-        if (idx < M * SLAB) {
-#pragma unroll
-            for (int wv = 0; wv < 8; ++wv) v += red[wv * M * SLAB + idx];
+            for (int wv = 0; wv < 8; ++wv) {
+                const float4 v = *reinterpret_cast<const float4*>(red + wv * M * SLAB + tid * 4);
+                mine4.x += v.x; mine4.y += v.y; mine4.z += v.z; mine4.w += v.w;
+            }
         }
-        mine[i] = v;
+    } else {
+#pragma unroll
+        for (int i = 0; i < (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS; ++i) {
+            const int idx = tid + i * GEMV_THREADS;
+            float v = 0.f;
+            if (idx < M * SLAB) {
+#pragma unroll
+                for (int wv = 0; wv < 8; ++wv) v += red[wv * M * SLAB + idx];
+            }
+            mine[i] = v;
+        }
     }
     __syncthreads();
     float* vals = red;  // [M][128]
     if (CL) {
         // The CTAs of one cluster hold the K-splits of this slab.  Every rank but 0 sends its partial into
-        // slot `rank` of rank 0's shared memory with asynchronous stores that count bytes on rank 0's
+        // slot `rank` of rank 0's shared memory with asynchronous 16-byte stores that count bytes on rank 0's
         // mbarrier, and is done; rank 0 waits (bounded) for the byte count and adds the slots in rank order
         // from its own shared memory.  No cluster barrier and no remote load on the critical path.
         constexpr int PER = (M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS;
         const uint32_t rank = cluster_ctarank();
-        const uint32_t rbar0 = dsmem_addr(&s_rbar, 0u);
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int idx = tid + i * GEMV_THREADS;
-            if (idx < M * SLAB) {
-                if (rank == 0) slots[idx] = mine[i];
-                else st_async_f32(dsmem_addr(slots + rank * (M * SLAB) + idx, 0u), mine[i], rbar0);
-            }
+        if (tid < M * SLAB / 4) {
+            if (rank == 0) *reinterpret_cast<float4*>(slots + tid * 4) = mine4;
+            else st_async_f32x4(dsmem_addr(slots + rank * (M * SLAB) + tid * 4, 0u), mine4, dsmem_addr(&s_rbar, 0u));
         }
         if (rank != 0) return;  // nothing reads this CTA's shared memory; its stores are on their way
+        __syncthreads();        // rank 0's own slot is read by other threads than those that wrote it
         if (a.ksplit > 1 && !mb_wait_cluster(&s_rbar, 0, a.err_flag, &s_abort)) return;  // bounded
         if (tr) a.trace[4] = global_timer();  // all ranks' partials have landed
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int idx = tid + i * GEMV_THREADS;
             if (idx < M * SLAB) {
-                float v = slots[idx];
-                for (int r = 1; r < a.ksplit; ++r) v += slots[r * (M * SLAB) + idx];
-                vals[idx] = v;
+                vals[idx] = sum_slots_any(slots + idx, M * SLAB, a.ksplit);
             }
         }
     } else if (a.ksplit == 1) {
@@ -438,6 +475,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         }
     }
     if (tr) a.trace[6] = global_timer();  // epilogue stored
+    if (a.trace && tid == 0) atomicMax(a.trace + 9, global_timer());  // the launch's last CTA to finish
 }
 
 constexpr size_t GEMV_STAGE_MAX = 80 * 1024;  // largest weight slice staged in shared memory (two CTAs per SM stay resident)

@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(COLS_THREADS, 1) gemv_cols_kernel(const GemvAr
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool tr = a.trace != nullptr && bid == 0 && tid == 0;
     if (tr) a.trace[0] = global_timer();  // CTA resident
+    if (a.trace && tid == 0) atomicMax(a.trace + 8, global_timer());  // the launch's last CTA to become resident
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32) l2_prefetch_slice(a.pf_ptr, a.pf_bytes, bid, gridDim.x, tid);
 
@@ -263,6 +264,7 @@ __global__ void __launch_bounds__(COLS_THREADS, 1) gemv_cols_kernel(const GemvAr
         }
     }
     if (tr) a.trace[6] = global_timer();  // epilogue stored
+    if (a.trace && tid == 0) atomicMax(a.trace + 9, global_timer());  // the launch's last CTA to finish
 }
 
 // Re-layout at load: slab layout (element (k, n) of slab n / 128 at [slab][k][n % 128]) -> column groups.
