@@ -531,7 +531,8 @@ cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
     // cluster launches over the slab layout whose slice fits: weights staged in shared memory before the dependency wait
     static const bool no_stage = [] { const char* e = std::getenv("HM_NO_STAGE"); return e && e[0] == '1'; }();
     const size_t slice = (size_t)a.rows_per_split * SLAB * 2;
-    if (CL && !no_stage && a.row_stride == SLAB * 2 && slice <= GEMV_STAGE_MAX && ((uintptr_t)a.W & 15) == 0) {
+    static const size_t stage_max = [] { const char* e = std::getenv("HM_STAGE_MAX_KB"); return e ? (size_t)std::atoi(e) * 1024 : GEMV_STAGE_MAX; }();  // tuning knob
+    if (CL && !no_stage && a.row_stride == SLAB * 2 && slice <= stage_max && ((uintptr_t)a.W & 15) == 0) {
         smem += slice;
         return launch_mcs<M, true, true>(a, smem, nslabs, st, pdl);
     }
