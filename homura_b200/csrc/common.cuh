@@ -108,12 +108,14 @@ __device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
 
 // Cooperative copy of n floats written by a previous kernel into shared memory, NT threads, with up to
 // four loads per thread in flight before the first use (a loop of load-then-use would pay one L2
-// round trip per iteration).  128-bit loads when source, destination and n allow.  L2-only loads:
-// the rows are rewritten by other SMs every launch.  Returns this thread's share of the sum of squares.
-template <int NT, bool SQ>
-__device__ __forceinline__ float stage_row(const float* __restrict__ src, float* __restrict__ dst, int n, int tid) {
+// round trip per iteration).  128-bit loads when the pointers and n allow.  L2-only loads: the rows are
+// rewritten by other SMs every launch.  Optionally multiplies by a per-element factor held in shared
+// memory (mul), optionally only sums (STORE = false).  Returns this thread's share of the sum of squares
+// of the loaded values (SQ).
+template <int NT, bool SQ, bool STORE = true>
+__device__ __forceinline__ float stage_row(const float* __restrict__ src, float* __restrict__ dst, int n, int tid, const float* __restrict__ mul = nullptr) {
     float s = 0.f;
-    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0 && (n & 3) == 0) {
+    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(mul)) & 15) == 0 && (n & 3) == 0) {
         const int n4 = n >> 2;
         for (int b = tid; b < n4; b += 4 * NT) {
             float4 v[4];
@@ -126,8 +128,14 @@ __device__ __forceinline__ float stage_row(const float* __restrict__ src, float*
             for (int i = 0; i < 4; ++i) {
                 const int idx = b + i * NT;
                 if (idx < n4) {
-                    reinterpret_cast<float4*>(dst)[idx] = v[i];
                     if (SQ) s = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, s))));
+                    if (STORE) {
+                        if (mul) {
+                            const float4 w = reinterpret_cast<const float4*>(mul)[idx];
+                            v[i] = make_float4(v[i].x * w.x, v[i].y * w.y, v[i].z * w.z, v[i].w * w.w);
+                        }
+                        reinterpret_cast<float4*>(dst)[idx] = v[i];
+                    }
                 }
             }
         }
@@ -143,8 +151,8 @@ __device__ __forceinline__ float stage_row(const float* __restrict__ src, float*
             for (int i = 0; i < 4; ++i) {
                 const int idx = b + i * NT;
                 if (idx < n) {
-                    dst[idx] = v[i];
                     if (SQ) s = fmaf(v[i], v[i], s);
+                    if (STORE) dst[idx] = mul ? v[i] * mul[idx] : v[i];
                 }
             }
         }
@@ -221,7 +229,6 @@ struct KvDesc {
 
 struct GemvArgs {
     int* err_flag;                 // optional: raised to 2 when the bounded wait for the staged weights runs out
-    int xfull;                     // set by the launcher: RMSNorm prologue stages the whole rows in shared memory (one L2 trip)
     unsigned long long* trace;     // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA 0 of this launch
     const void* pf_ptr;            // optional: weights of a later kernel to pull into the L2 (see l2_prefetch_slice)
     unsigned long long pf_bytes;

@@ -99,10 +99,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     float* xs = smem;                 // [M][rps]
     float* red = smem + M * rps;      // [8][M][128], later vals[M][128]
     float* slots = red + 8 * M * SLAB;  // cluster variant, rank 0: [ksplit][M][128] partials pushed by the ranks
-    // RMSNorm prologue: the whole rows, read once (sum of squares and the slice come from the same load)
-    float* xfull = CL ? slots + a.ksplit * M * SLAB : slots;  // [M][K] when it fits (a.xfull)
     // values that do not depend on the previous kernel, fetched before the dependency wait:
-    float* nws = xfull + (a.xfull ? M * a.K : 0);  // [rps] RMSNorm weights of this CTA's K range
+    float* nws = CL ? slots + a.ksplit * M * SLAB : slots;  // [rps] RMSNorm weights of this CTA's K range
     float* cs_s = nws + rps;                        // [M][128] RoPE cos, [M][128] sin of this slab's columns (QKV epilogue)
     float* sn_s = cs_s + M * SLAB;
     float* bias_s = sn_s + M * SLAB;                // [128] bias of this slab's columns (QKV epilogue with bias)
@@ -200,19 +198,37 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     }
 
     // ---- prologue: activation slice [k0, k0+nrows) of every row into shared memory ----
-    if (a.pro == PRO_RMSNORM) {
+    // Cluster launches apply the RMSNorm row factor AFTER the split-K sum: y = inv * sum_k W[k][n] * (x[k] * w[k]).
+    // Every rank stages its slice of x * w at once; only rank 0 reads the whole rows for their sums of squares,
+    // while the multiply is already running, and scales the reduced sums.  (The unsplit and ticket variants
+    // keep the reference's order, (x * inv) * w before the product.)
+    const bool defer_norm = CL && a.pro == PRO_RMSNORM && a.K <= 4096 && (a.K & 3) == 0 && (a.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
+    const bool norm_rank0 = defer_norm && cluster_ctarank() == 0;
+    float4 rowv[CL ? M : 1][4];
+    if (defer_norm) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) stage_row<GEMV_THREADS, false>(a.x + (size_t)m * a.ldx + k0, xs + m * rps, nrows, tid, nws);
+        // rank 0: the whole rows are requested now (up to four 16-byte loads per thread and row) and squared
+        // after the multiply, so that their latency and the reduction overlap it
+        if (norm_rank0) {
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int idx = tid + i * GEMV_THREADS;
+                    rowv[m][i] = idx < (a.K >> 2) ? ld_cg_f32x4(a.x + (size_t)m * a.ldx + 4 * (size_t)idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+        }
+    } else if (a.pro == PRO_RMSNORM) {
         float ss[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             float s = 0.f;
             const float* xr = a.x + (size_t)m * a.ldx;
-            if (a.xfull) {
-                s = stage_row<GEMV_THREADS, true>(xr, xfull + m * a.K, a.K, tid);  // one trip to the L2 for both the sum and the slice
-            } else {
-                for (int k = tid; k < a.K; k += GEMV_THREADS) {
-                    float v = __ldg(xr + k);
-                    s = fmaf(v, v, s);
-                }
+#pragma unroll 4
+            for (int k = tid; k < a.K; k += GEMV_THREADS) {
+                float v = __ldg(xr + k);
+                s = fmaf(v, v, s);
             }
             ss[m] = warp_sum(s);
         }
@@ -232,15 +248,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         for (int m = 0; m < M; ++m) {
             const float inv = s_inv[m];
             const float* xr = a.x + (size_t)m * a.ldx + k0;
-            for (int r = tid; r < nrows; r += GEMV_THREADS) {
-                const float xv = a.xfull ? xfull[m * a.K + k0 + r] : __ldg(xr + r);
-                xs[m * rps + r] = (xv * inv) * nws[r];
-            }
+            for (int r = tid; r < nrows; r += GEMV_THREADS) xs[m * rps + r] = (__ldg(xr + r) * inv) * nws[r];
         }
     } else {
 #pragma unroll
         for (int m = 0; m < M; ++m) stage_row<GEMV_THREADS, false>(a.x + (size_t)m * a.ldx + k0, xs + m * rps, nrows, tid);
     }
+    __syncthreads();
     __syncthreads();
     if (tr) a.trace[2] = global_timer();  // activations in shared memory
 
@@ -277,6 +291,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     }
 
     if (tr) a.trace[3] = global_timer();  // weights multiplied
+    if (norm_rank0) {  // sums of squares of the whole rows, published by the barrier of the reduction below
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s = fmaf(rowv[m][i].x, rowv[m][i].x, fmaf(rowv[m][i].y, rowv[m][i].y, fmaf(rowv[m][i].z, rowv[m][i].z, fmaf(rowv[m][i].w, rowv[m][i].w, s))));
+            s = warp_sum(s);
+            if (lane == 0) s_warp[warp][m] = s;
+        }
+    }
     // ---- reduce the 16 row lanes: xor-16 shuffle, then across the 8 warps in smem ----
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -291,6 +315,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         }
     }
     __syncthreads();
+    if (norm_rank0 && tid < M) {  // read by the rank-order sum, two barriers later
+        float s = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < 8; ++wv) s += s_warp[wv][tid];
+        s_inv[tid] = 1.0f / sqrtf(s / (float)a.K + a.eps);
+    }
     float mine[(M * SLAB + GEMV_THREADS - 1) / GEMV_THREADS];
     float4 mine4 = make_float4(0.f, 0.f, 0.f, 0.f);  // cluster variant: four consecutive columns per thread, sent as one 16-byte store
     if (CL) {
@@ -334,7 +364,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         for (int i = 0; i < PER; ++i) {
             const int idx = tid + i * GEMV_THREADS;
             if (idx < M * SLAB) {
-                vals[idx] = sum_slots_any(slots + idx, M * SLAB, a.ksplit);
+                const float v = sum_slots_any(slots + idx, M * SLAB, a.ksplit);
+                vals[idx] = defer_norm ? v * s_inv[idx / SLAB] : v;
             }
         }
     } else if (a.ksplit == 1) {
@@ -425,8 +456,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
         }
     } else {  // EPI_QKV_ROPE
         const int hd = a.hd, half = hd >> 1, hps = SLAB / hd;
-        // bias
-        if (a.bias) {
+        // head_dim and the page size are powers of two in every supported model: shifts instead of divisions
+        // (an integer division is ~20 instructions, and every instruction of this one-shot code is on the chain)
+        const bool p2 = (hd & (hd - 1)) == 0 && (a.kv.page_tokens & (a.kv.page_tokens - 1)) == 0;
+        const int hs = 31 - __clz(hd);
+        // bias: folded into the rotation below unless QK-norm needs the biased values first
+        const bool bias_late = a.bias && !a.has_qk_norm;
+        if (a.bias && !bias_late) {
             for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) vals[idx] += bias_s[idx % SLAB];
             __syncthreads();
         }
@@ -450,21 +486,26 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
             const int m = idx / SLAB, c = idx % SLAB;
             const int n = n0 + c;
             if (n >= a.N || m >= a.m_valid) continue;
-            const int hh = c / hd, d = c % hd;
+            const int hh = p2 ? c >> hs : c / hd, d = p2 ? c & (hd - 1) : c % hd;
             const int nh = n0 + hh * hd;
             const int pos = s_pos[m];
             float v = vals[idx];
+            if (bias_late) v += bias_s[c];
             if (nh < a.q_dim + a.kv_dim) {
-                const float other = (d < half) ? -vals[idx + half] : vals[idx - half];
+                const int oc = d < half ? half : -half;
+                float o = vals[idx + oc];
+                if (bias_late) o += bias_s[c + oc];
+                const float other = d < half ? -o : o;
                 v = fmaf(other, sn_s[idx], v * cs_s[idx]);
             }
             if (nh < a.q_dim) {
                 a.y[(size_t)m * a.ldy + n] = v;
             } else {
                 const bool is_k = nh < a.q_dim + a.kv_dim;
-                const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
+                const int rel = nh - a.q_dim - (is_k ? 0 : a.kv_dim);
+                const int kvh = p2 ? rel >> hs : rel / hd;
                 const int page = s_page[m];
-                const int tok = pos % a.kv.page_tokens;
+                const int tok = p2 ? pos & (a.kv.page_tokens - 1) : pos % a.kv.page_tokens;
                 const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd));
                 void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
                 if (a.kv.bf16)
@@ -521,10 +562,6 @@ cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
     GemvArgs a = a_in;
     const int nslabs = (a.N + SLAB - 1) / SLAB;
     size_t floats = (size_t)M * a.rows_per_split + 8 * (size_t)M * SLAB + (CL ? (size_t)a.ksplit * M * SLAB : 0);
-    // latency-bound (cluster) launches stage the whole rows once when they fit; the long unsplit launches are
-    // bandwidth-bound and keep their shared memory small for occupancy
-    a.xfull = CL && a.pro == PRO_RMSNORM && (size_t)M * a.K * 4 <= 32 * 1024 ? 1 : 0;
-    if (a.xfull) floats += (size_t)M * a.K;
     floats += (size_t)a.rows_per_split;                            // pre-fetched RMSNorm weights
     if (a.epi == EPI_QKV_ROPE) floats += 2 * (size_t)M * SLAB + SLAB;  // pre-fetched RoPE rows and bias
     size_t smem = sizeof(float) * floats;
