@@ -31,18 +31,23 @@ namespace {
 
 constexpr int U = 8;  // 128-bit loads in flight per thread
 
+// One weight row segment (8 bf16 columns) times the M activation values of that row.  The accumulators are
+// pairs, so that one packed FMA (two independent IEEE FMAs, same bits as two scalar ones) serves two columns:
+// the multiply of the staged kernels is bound by instruction issue, not by shared-memory bandwidth.
 template <int M>
-__device__ __forceinline__ void fma_row(float (&acc)[M][8], const uint4& w, const float* __restrict__ xs, int rps, int row) {
-    float f[8];
-    f[0] = bf16_lo(w.x); f[1] = bf16_hi(w.x);
-    f[2] = bf16_lo(w.y); f[3] = bf16_hi(w.y);
-    f[4] = bf16_lo(w.z); f[5] = bf16_hi(w.z);
-    f[6] = bf16_lo(w.w); f[7] = bf16_hi(w.w);
+__device__ __forceinline__ void fma_row(float2 (&acc)[M][4], const uint4& w, const float* __restrict__ xs, int rps, int row) {
+    const float2 f0 = make_float2(bf16_lo(w.x), bf16_hi(w.x));
+    const float2 f1 = make_float2(bf16_lo(w.y), bf16_hi(w.y));
+    const float2 f2 = make_float2(bf16_lo(w.z), bf16_hi(w.z));
+    const float2 f3 = make_float2(bf16_lo(w.w), bf16_hi(w.w));
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-        float xv = xs[m * rps + row];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[m][j] = fmaf(xv, f[j], acc[m][j]);
+        const float xv = xs[m * rps + row];
+        const float2 x2 = make_float2(xv, xv);
+        acc[m][0] = __ffma2_rn(x2, f0, acc[m][0]);
+        acc[m][1] = __ffma2_rn(x2, f1, acc[m][1]);
+        acc[m][2] = __ffma2_rn(x2, f2, acc[m][2]);
+        acc[m][3] = __ffma2_rn(x2, f3, acc[m][3]);
     }
 }
 
@@ -259,11 +264,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     if (tr) a.trace[2] = global_timer();  // activations in shared memory
 
     // ---- main loop: stream the slab run, 8 column accumulators per row per thread ----
-    float acc[M][8];
+    float2 acc[M][4];
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[m][j] = 0.f;
+        for (int j = 0; j < 4; ++j) acc[m][j] = make_float2(0.f, 0.f);
 
     if (ST) {
         // every thread waits (bounded) for the bulk copies, then multiplies out of shared memory
@@ -305,13 +310,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[m][j] += __shfl_xor_sync(0xffffffffu, acc[m][j], 16);
+        for (int j = 0; j < 4; ++j) {
+            acc[m][j].x += __shfl_xor_sync(0xffffffffu, acc[m][j].x, 16);
+            acc[m][j].y += __shfl_xor_sync(0xffffffffu, acc[m][j].y, 16);
+        }
     if (lane < 16) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             float4* dst = reinterpret_cast<float4*>(red + ((warp * M + m) * SLAB + cg * 8));
-            dst[0] = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
-            dst[1] = make_float4(acc[m][4], acc[m][5], acc[m][6], acc[m][7]);
+            dst[0] = make_float4(acc[m][0].x, acc[m][0].y, acc[m][1].x, acc[m][1].y);
+            dst[1] = make_float4(acc[m][2].x, acc[m][2].y, acc[m][3].x, acc[m][3].y);
         }
     }
     __syncthreads();
@@ -615,6 +623,8 @@ void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* 
     const int nslabs = (N + SLAB - 1) / SLAB;
     static const int per_sm = [] { const char* e = std::getenv("HM_GEMV_CTAS_PER_SM"); const int v = e ? std::atoi(e) : 0; return v >= 1 && v <= 8 ? v : 2; }();
     int cs = (per_sm * sm_count) / nslabs;  // two CTAs per SM resident at once (tuning knob: HM_GEMV_CTAS_PER_SM)
+    static const int wide_cs = [] { const char* e = std::getenv("HM_GEMV_WIDE_CLUSTER"); return e ? std::atoi(e) : 0; }();  // tuning knob: cluster size of projections with 32 slabs or more
+    if (wide_cs >= 1 && nslabs >= 32) cs = wide_cs;
     if (cs > max_cluster) cs = max_cluster;
     if (cs < 1) cs = 1;
     while (cs > 1 && K / cs < 32) --cs;
