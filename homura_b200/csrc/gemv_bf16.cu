@@ -192,6 +192,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     }
 
     pdl_wait();
+    // the RMSNorm weights fetched above are read below by other threads than those that stored them (a CTA that
+    // became resident just before its dependency resolved may still have those loads in flight)
+    if (CL && a.pro == PRO_RMSNORM) __syncthreads();
     if (tr) a.trace[1] = global_timer();  // predecessor complete
 
     // the residual element this thread adds in the epilogue (known epilogue CTA only): requested now, used after the reduction

@@ -69,3 +69,21 @@ def test_c1_greedy_64_tokens_and_logits(hm, oracle, c1_dir):
         lo = om.decode_step(want[i])
         lgd, _ = m2.decode_step([want[i]])
         assert float(np.abs(lgd[0] - lo).max()) <= 2e-2 and cosine(lgd[0], lo) >= 0.9995
+
+
+def test_c1_device_loop_is_deterministic(hm, c1_dir):
+    # the on-device decode loop replays one CUDA graph per token with programmatic dependent launches: kernels
+    # are resident long before their inputs exist, so anything they fetch early must be ordered before its
+    # use.  Repeating the same generation must give the same 64 tokens every time.
+    cfg = synth.QWEN25_05B
+    ids = synth.prompt_ids(11, 128, cfg.vocab_size)
+    m = hm.HfModel.load(c1_dir)
+    m.init_kv_cache(256)
+    first = None
+    for _ in range(12):
+        m.reset_kv_cache()
+        out = m.generate_ids(ids, 64, hm.SamplingConfig.greedy())
+        if first is None:
+            first = out
+        assert out == first
+    m.close()
