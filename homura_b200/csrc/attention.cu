@@ -58,7 +58,7 @@ template <int HD, bool BF16>
 __host__ __device__ inline int pick_nslots(int g, int early_pages, int max_pages, int nsplit) {
     const int nsub = pick_nsub<HD, BF16>(g);
     const int cap = (max_pages + nsplit - 1) / nsplit;
-    if (!early_pages || cap > RES_MAX_PAGES) return nsub;
+    if (early_pages < 2 || cap > RES_MAX_PAGES) return nsub;
     return (cap + nsub - 1) / nsub * nsub;
 }
 
@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     const int g = a.heads / a.kv_heads;
     const int nsub = pick_nsub<HD, BF16>(g);  // page slots worked on concurrently
     const int nslots = pick_nslots<HD, BF16>(g, a.early_pages, a.max_pages, a.nsplit);
-    const bool resident = nslots * a.nsplit >= a.max_pages && a.early_pages;  // one slot per page of this CTA
+    const bool resident = nslots * a.nsplit >= a.max_pages && a.early_pages >= 2;  // one slot per page of this CTA
     float* q_s = sm;                              // [G_MAX][HD]
     float* tiles = q_s + G_MAX * HD;              // [nslots][K tile | V tile]
     float* p_s = tiles + nslots * TL::SLOT_FLOATS;  // [ATT_WARPS][16]

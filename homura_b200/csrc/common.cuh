@@ -276,7 +276,8 @@ struct AttnArgs {
     unsigned long long pf_bytes;
     unsigned char* xp_out;  // optional: write the output as packed tensor-core activations (tc_xpack_store) instead of `out`
     int xp_mpad;
-    int early_pages;     // 1: every row is its own sequence (decode), so the pages below the one of the new token may be read before the dependency wait
+    int early_pages;     // >= 1: every row is its own sequence (decode), so the pages below the one of the new token may be read before the dependency wait;
+                         // 2: and every page of a split gets its own shared-memory slot (small launches, where latency counts and occupancy does not)
     int stream_pages;    // > 0: long contexts may use the bulk-copy ring variant (pages per CTA decided from max_pages / nsplit)
     int* err_flag;       // raised to 2 when a bounded wait of that variant runs out
     unsigned long long* trace;  // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA (0,0,0) of the short-context kernel

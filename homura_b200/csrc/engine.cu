@@ -997,7 +997,9 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             at.xp_mpad = tc_mpad(M);
         }
         if (gemv_trace_ && *launches < 512) at.trace = gemv_trace_ + (size_t)*launches * 16;
-        at.early_pages = row_seq == nullptr ? 1 : 0;  // decode passes: one row per sequence; prefill chunks write several positions of one sequence
+        // decode passes: one row per sequence (prefill chunks write several positions of one sequence); launches of at most two
+        // CTAs per SM are latency-bound and keep all their pages resident, larger ones keep their shared memory small
+        at.early_pages = row_seq == nullptr ? ((long)M * kvh_ * at.nsplit <= 2L * sm_count_ ? 2 : 1) : 0;
         at.err_flag = err_flag_;
         at.scale = (float)(1.0 / std::sqrt((double)hd_));  // src/hf/emitter.rs:719
         at.out = attn_;
