@@ -160,6 +160,34 @@ __device__ __forceinline__ float stage_row(const float* __restrict__ src, float*
     return s;
 }
 
+// The same for MR rows at once (row m at src + m * ld_src, stored at dst + m * ld_dst): the loads of all rows are
+// issued before the first store, so that staging MR rows costs one L2 round trip, not MR.  Meant for slices of
+// up to 4 * NT floats per row (one trip); longer rows take one trip per 4 * NT floats.
+template <int NT, int MR>
+__device__ __forceinline__ void stage_rows(const float* __restrict__ src, int ld_src, float* __restrict__ dst, int ld_dst, int n, int tid, const float* __restrict__ mul = nullptr) {
+    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(mul)) & 15) == 0 && ((n | ld_src | ld_dst) & 3) == 0) {
+        const int n4 = n >> 2;
+        for (int b = tid; b < n4; b += NT) {
+            float4 v[MR];
+#pragma unroll
+            for (int m = 0; m < MR; ++m) v[m] = ld_cg_f32x4(src + (size_t)m * ld_src + 4 * (size_t)b);
+            const float4 w = mul ? reinterpret_cast<const float4*>(mul)[b] : make_float4(1.f, 1.f, 1.f, 1.f);
+#pragma unroll
+            for (int m = 0; m < MR; ++m)
+                *reinterpret_cast<float4*>(dst + (size_t)m * ld_dst + 4 * (size_t)b) = mul ? make_float4(v[m].x * w.x, v[m].y * w.y, v[m].z * w.z, v[m].w * w.w) : v[m];
+        }
+    } else {
+        for (int b = tid; b < n; b += NT) {
+            float v[MR];
+#pragma unroll
+            for (int m = 0; m < MR; ++m) v[m] = ld_cg_f32(src + (size_t)m * ld_src + b);
+            const float w = mul ? mul[b] : 1.f;
+#pragma unroll
+            for (int m = 0; m < MR; ++m) dst[(size_t)m * ld_dst + b] = mul ? v[m] * w : v[m];
+        }
+    }
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }

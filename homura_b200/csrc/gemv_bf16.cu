@@ -86,14 +86,15 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { retur
 
 // The unsplit M = 1 variant (LM head: one long stream per CTA) runs three CTAs per SM (<= 85
 // registers) to keep ~96 KB of weight loads in flight per SM; measured 5.0 -> 5.3 TB/s.  The
-// clustered variants are latency chains and were slower under the tighter register budget.  The unsplit
-// 2- and 4-row variants are held to 128 registers so that two CTAs stay resident per SM.
+// clustered one-row variants are latency chains and were slower under a tighter register budget.  The
+// 2- and 4-row variants (split or not) are held to 128 registers so that two CTAs stay resident per SM:
+// wide projections launch more CTAs than there are SMs.
 // ST (with CL): the CTA's whole weight slice (rows [k0, k0+nrows) of its slab, one contiguous byte range of
 // at most GEMV_STAGE_MAX bytes) is pulled into shared memory by bulk copies issued BEFORE the dependency
 // wait, so that by the time the predecessor has finished the multiply runs out of shared memory and HBM
 // latency is off the critical path of the dependent-kernel chain.
 template <int M, bool CL, bool ST>
-__global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ? 2 : 1))) gemv_bf16_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 ? 3 : (M <= 4 ? 2 : 1))) gemv_bf16_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) float smem_raw[];
     const int rps = a.rows_per_split;
     // staged weights first (bulk copies want 16-byte aligned destinations), then the f32 scratch
@@ -214,8 +215,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
     const bool norm_rank0 = defer_norm && cluster_ctarank() == 0;
     float4 rowv[CL ? M : 1][4];
     if (defer_norm) {
-#pragma unroll
-        for (int m = 0; m < M; ++m) stage_row<GEMV_THREADS, false>(a.x + (size_t)m * a.ldx + k0, xs + m * rps, nrows, tid, nws);
+        stage_rows<GEMV_THREADS, M>(a.x + k0, a.ldx, xs, rps, nrows, tid, nws);
         // rank 0: the whole rows are requested now (up to four 16-byte loads per thread and row) and squared
         // after the multiply, so that their latency and the reduction overlap it
         if (norm_rank0) {
@@ -259,8 +259,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? 1 : (M == 1 ? 3 : (M <= 4 ?
             for (int r = tid; r < nrows; r += GEMV_THREADS) xs[m * rps + r] = (__ldg(xr + r) * inv) * nws[r];
         }
     } else {
-#pragma unroll
-        for (int m = 0; m < M; ++m) stage_row<GEMV_THREADS, false>(a.x + (size_t)m * a.ldx + k0, xs + m * rps, nrows, tid);
+        stage_rows<GEMV_THREADS, M>(a.x + k0, a.ldx, xs, rps, nrows, tid);
     }
     __syncthreads();
     __syncthreads();
