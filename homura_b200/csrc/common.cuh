@@ -289,7 +289,8 @@ struct GemvArgs {
     const float* rope_cos;  // [max_pos][hd]
     const float* rope_sin;
     const int32_t* row_pos;  // [M] position of each row's token
-    const int32_t* row_seq;  // [M] sequence (page-table row) of each row
+    const int32_t* row_seq;  // [M] sequence (page-table row) of each row; null: row m is sequence seq_base + m
+    int seq_base;            // first row's sequence when row_seq is null (launches over a group of a larger batch)
     KvDesc kv;
     // EPI_LOGITS: per-slab argmax partials
     float* amax_val;     // [M][nslabs]

@@ -802,6 +802,7 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
         a.rope_sin = rope_sin_;
         a.row_pos = row_pos ? row_pos + m0 : nullptr;
         a.row_seq = row_seq ? row_seq + m0 : nullptr;
+        a.seq_base = m0;
         if (epi == EPI_LOGITS) {
             const int nblocks = (L.N + SLAB - 1) / SLAB;
             a.amax_val = amax_val_ + (size_t)m0 * nblocks;
@@ -865,6 +866,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.rope_sin = rope_sin_;
             a.row_pos = row_pos ? row_pos + m0 : nullptr;
             a.row_seq = row_seq ? row_seq + m0 : nullptr;
+        a.seq_base = m0;
             const int nslabs = (L.N + SLAB - 1) / SLAB;
             a.amax_val = amax_val ? amax_val + (size_t)m0 * nslabs : nullptr;
             a.amax_idx = amax_idx ? amax_idx + (size_t)m0 * nslabs : nullptr;

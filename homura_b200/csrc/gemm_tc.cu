@@ -227,7 +227,7 @@ __device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, in
             } else {
                 const bool is_k = nh < a.q_dim + a.kv_dim;
                 const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
-                const int seq = a.row_seq ? a.row_seq[m] : m;
+                const int seq = a.row_seq ? a.row_seq[m] : a.seq_base + m;
                 const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
                 const int tok = pos % a.kv.page_tokens;
                 const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd));

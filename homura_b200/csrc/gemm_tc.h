@@ -28,6 +28,7 @@ struct TcArgs {
     float eps;
     const float *q_norm_w, *k_norm_w, *rope_cos, *rope_sin;
     const int32_t *row_pos, *row_seq;
+    int seq_base;  // row m is sequence seq_base + m when row_seq is null (a 64-row chunk of a larger batch)
     KvDesc kv;
     // EPI_LOGITS: per-row argmax of every 128-feature block
     float* amax_val;

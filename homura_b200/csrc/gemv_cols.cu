@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(COLS_THREADS, 1) gemv_cols_kernel(const GemvAr
             }
         }
         if (tid < M && tid < a.m_valid) {
-            const int pos = a.row_pos[tid], seq = a.row_seq ? a.row_seq[tid] : tid;
+            const int pos = a.row_pos[tid], seq = a.row_seq ? a.row_seq[tid] : a.seq_base + tid;
             s_pos[tid] = pos;
             s_page[tid] = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
         }

@@ -427,6 +427,32 @@ def test_batch_20_decode_on_tensor_cores(hm, oracle):
 # ---- K-quant GGUF models (Q4_K / Q6_K, the mix of a Q4_K_M file) ---------------------------------
 
 
+@pytest.mark.parametrize("B,no_tc", [(20, True), (70, False)])
+def test_decode_batches_spanning_launch_groups(hm, oracle, monkeypatch, B, no_tc):
+    # a projection over more rows than one launch takes (8 on the streaming kernels, 64 on the tensor
+    # cores) runs as several launches; each must write its rows' K/V into its own sequences' pages
+    if no_tc:
+        monkeypatch.setenv("HM_NO_TC", "1")
+    cfg, d = make_hf("qwen2")
+    m = hm.HfModel.load(d)
+    m.init_kv_cache(32, batch=B)
+    oms = [oracle.OracleModel.from_hf_dir(d, max_seq_len=32) for _ in range(B)]
+    cur = []
+    for b in range(B):
+        ids = synth.prompt_ids(300 + b, 2 + (b % 5), cfg.vocab_size)
+        t_o, _ = oms[b].prefill(ids)
+        assert m.prefill(ids, seq=b) == t_o
+        cur.append(t_o)
+    for _ in range(4):
+        lg, nxt = m.decode_step(cur)
+        for b in range(B):
+            lo = oms[b].decode_step(cur[b])
+            assert_logits_close(lg[b], lo)
+            cur[b] = oracle.argmax(lo)
+            assert int(nxt[b]) == cur[b]
+    m.close()
+
+
 @pytest.mark.parametrize("case", ["q4_k", "q6_k", "mix_quant_embed", "mix_tied"])
 def test_kquant_gguf_model_matches_oracle(hm, oracle, case):
     tied = case == "mix_tied"
