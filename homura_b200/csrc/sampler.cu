@@ -49,6 +49,27 @@ __device__ __forceinline__ float block_sum_fixed(float v, float* sw) {
     return r;
 }
 
+// Visit every element of a row of n floats with f(index, value): 128-bit loads, four of them in flight per
+// thread.  One CTA walks the vocabulary several times out of the L2; with one scalar load per iteration each
+// pass costs an L2 round trip per element of a thread, which is what made the kernel take ~190 us.
+template <typename F>
+__device__ __forceinline__ void scan_row(const float* __restrict__ p, int n, int tid, F f) {
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+        const int n4 = n >> 2;
+#pragma unroll 4
+        for (int i = tid; i < n4; i += ST) {
+            const float4 x = *reinterpret_cast<const float4*>(p + 4 * (size_t)i);
+            f(4 * i, x.x);
+            f(4 * i + 1, x.y);
+            f(4 * i + 2, x.z);
+            f(4 * i + 3, x.w);
+        }
+        done = n4 << 2;
+    }
+    for (int v = done + tid; v < n; v += ST) f(v, p[v]);
+}
+
 __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
     __shared__ float sw[ST / 32];
     __shared__ int hist[256];
@@ -78,28 +99,41 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
     // ---- penalties, temperature, maximum ----
     const float inv_temp = 1.0f / a.cfg.temperature;
     float mx = -INFINITY;
-    for (int v = tid; v < V; v += ST) {
-        float l = logits[v];
-        if (pen) {
-            const int c = count[v];
-            if (c > 0) {
-                if (a.cfg.repetition_penalty != 1.0f)
-                    for (int r = 0; r < c; ++r) l = l > 0.0f ? l / a.cfg.repetition_penalty : l * a.cfg.repetition_penalty;
-                if (a.cfg.frequency_penalty != 0.0f || a.cfg.presence_penalty != 0.0f) {
-                    l -= a.cfg.frequency_penalty * (float)c;
-                    l -= a.cfg.presence_penalty;
-                }
+    auto adjust = [&](float l, int c) {  // penalties per occurrence / per count, then temperature
+        if (c > 0) {
+            if (a.cfg.repetition_penalty != 1.0f)
+                for (int r = 0; r < c; ++r) l = l > 0.0f ? l / a.cfg.repetition_penalty : l * a.cfg.repetition_penalty;
+            if (a.cfg.frequency_penalty != 0.0f || a.cfg.presence_penalty != 0.0f) {
+                l -= a.cfg.frequency_penalty * (float)c;
+                l -= a.cfg.presence_penalty;
             }
         }
-        l *= inv_temp;
+        return l * inv_temp;
+    };
+    int done = 0;
+    if (((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(sl) | reinterpret_cast<uintptr_t>(count)) & 15) == 0) {
+        const int V4 = V >> 2;
+#pragma unroll 4
+        for (int i = tid; i < V4; i += ST) {
+            const float4 x = *reinterpret_cast<const float4*>(logits + 4 * (size_t)i);
+            const int4 c = pen ? *reinterpret_cast<const int4*>(count + 4 * (size_t)i) : make_int4(0, 0, 0, 0);
+            const float4 y = make_float4(adjust(x.x, c.x), adjust(x.y, c.y), adjust(x.z, c.z), adjust(x.w, c.w));
+            *reinterpret_cast<float4*>(sl + 4 * (size_t)i) = y;
+            mx = fmaxf(fmaxf(mx, fmaxf(y.x, y.y)), fmaxf(y.z, y.w));
+        }
+        done = V4 << 2;
+    }
+    for (int v = done + tid; v < V; v += ST) {
+        const float l = adjust(logits[v], pen ? count[v] : 0);
         sl[v] = l;
         mx = fmaxf(mx, l);
     }
+    __syncthreads();  // the passes below read sl with a different thread-to-element mapping than its stores (tail elements)
     mx = block_max(mx, sw);
 
     // ---- softmax denominator ----
     float part = 0.f;
-    for (int v = tid; v < V; v += ST) part += expf(sl[v] - mx);
+    scan_row(sl, V, tid, [&](int, float l) { part += expf(l - mx); });
     const float sum = block_sum_fixed(part, sw);
 
     // ---- radix select: order key of the k-th largest scaled logit ----
@@ -114,10 +148,10 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
         __syncthreads();
         const uint32_t prefix = s_prefix;
         const uint32_t mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-        for (int v = tid; v < V; v += ST) {
-            const uint32_t key = order_key(sl[v]);
+        scan_row(sl, V, tid, [&](int, float l) {
+            const uint32_t key = order_key(l);
             if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1);
-        }
+        });
         __syncthreads();
         if (tid == 0) {
             int need = s_k, bin = 255;
@@ -140,8 +174,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
         n_tie = 0;
     }
     __syncthreads();
-    for (int v = tid; v < V; v += ST) {
-        const uint32_t key = order_key(sl[v]);
+    scan_row(sl, V, tid, [&](int v, float l) {
+        const uint32_t key = order_key(l);
         if (key > kth) {
             const int slot = atomicAdd(&n_cand, 1);
             if (slot < SAMPLER_MAX_K) cand[slot] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)v);
@@ -149,7 +183,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
             const int slot = atomicAdd(&n_tie, 1);
             if (slot < SAMPLER_MAX_K) tie_idx[slot] = v;
         }
-    }
+    });
     __syncthreads();
     if (tid == 0) {
         // ties: ascending index, the first want_ties of them (n_tie is tiny except for degenerate logits)
