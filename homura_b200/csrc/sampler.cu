@@ -225,12 +225,15 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
     }
 
     // ---- min-p, top-p, draw: one thread walks the sorted list as the reference does ----
+    // the candidates' probabilities in parallel (an exponential and a division each, and a load that may miss);
+    // the walk itself is a few additions and comparisons per candidate
+    float* probs = reinterpret_cast<float*>(tie_idx);  // reuse
+    for (int i = tid; i < nc; i += ST) {
+        const int v = (int)(~(uint32_t)(cand[i] & 0xFFFFFFFFull));
+        probs[i] = expf(sl[v] - mx) / sum;
+    }
+    __syncthreads();
     if (tid == 0) {
-        float* probs = reinterpret_cast<float*>(tie_idx);  // reuse
-        for (int i = 0; i < nc; ++i) {
-            const int v = (int)(~(uint32_t)(cand[i] & 0xFFFFFFFFull));
-            probs[i] = expf(sl[v] - mx) / sum;
-        }
         if (a.cfg.min_p > 0.0f && nc > 0) {
             const float thr = a.cfg.min_p * probs[0];  // the largest probability is the first of the sorted list
             for (int i = 0; i < nc; ++i)
