@@ -27,7 +27,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhomura_b200.so")
 
 HM_OK, HM_ERR_INVALID, HM_ERR_CUDA, HM_ERR_KV_FULL, HM_ERR_IO, HM_ERR_UNSUPPORTED, HM_ERR_TIMEOUT, HM_ERR_STATE = range(8)
-LAYOUT_KN, LAYOUT_SLAB128, LAYOUT_COLS8 = 0, 1, 2
+LAYOUT_KN, LAYOUT_SLAB128 = 0, 1
 
 
 class DType(enum.IntEnum):
@@ -123,12 +123,12 @@ SIGNATURES = {
     "hm_sample_token_device": (_i32, [_vp, _i32, C.POINTER(_Sampling), _vp, _i32, C.POINTER(C.c_uint64), _u32p]),
     "hm_time_decode": (_i32, [_vp, _i32, _i32, _f32p]),
     "hm_profile_decode": (_i32, [_vp, _i32, C.POINTER(_KernelStat), _i32, _i32p]),
+    "hm_selftest_expire_wait": (_i32, [_vp]),
     "hm_engine_stream": (_vp, [_vp]),
     "hm_launches_per_step": (_i32, [_vp, _i32p]),
     "hm_gemv_bf16": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_gemv_bf16_noalloc": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_pack_bf16_slabs": (_i32, [_vp, _i32, _i32, _vp, _vp]),
-    "hm_pack_bf16_cols8": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "hm_gemm_bf16_tc": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "hm_tc_packed_elems": (C.c_size_t, [_i32, _i32]),
     "hm_pack_bf16_tc": (_i32, [_vp, _i32, _i32, _vp, _vp]),
@@ -450,6 +450,10 @@ class HfModel:
         _check(self._lib.hm_profile_decode(self._h, steps, arr, 16, C.byref(n)), self._h)
         return [dict(name=arr[i].name.decode(), launches_per_step=arr[i].launches_per_step, ms_per_step=arr[i].ms_per_step, bytes_per_step=arr[i].bytes_per_step) for i in range(n.value)]
 
+    def selftest_expire_wait(self):
+        """Queue the bounded-wait probe: the next pass on this model raises HomuraError(HM_ERR_TIMEOUT)."""
+        _check(self._lib.hm_selftest_expire_wait(self._h), self._h)
+
     def time_decode(self, warmup: int, steps: int) -> float:
         ms = C.c_float(0)
         _check(self._lib.hm_time_decode(self._h, warmup, steps, C.byref(ms)), self._h)
@@ -520,16 +524,6 @@ def pack_bf16_slabs(w_bits) -> np.ndarray:
     K, N = w.shape
     out = np.empty(((N + 127) // 128, K, 128), np.uint16)
     _check(lib.hm_pack_bf16_slabs(_ptr(w), K, N, _ptr(out), None))
-    return out
-
-
-def pack_bf16_cols8(w_bits) -> np.ndarray:
-    """Row-major [K,N] bf16 bits -> LAYOUT_COLS8: [ceil(N/8)][K][8], groups of 8 output columns."""
-    lib = load_library()
-    w = np.ascontiguousarray(w_bits, dtype=np.uint16)
-    K, N = w.shape
-    out = np.empty(((N + 7) // 8, K, 8), np.uint16)
-    _check(lib.hm_pack_bf16_cols8(_ptr(w), K, N, _ptr(out), None))
     return out
 
 

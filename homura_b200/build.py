@@ -11,8 +11,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhomura_b200.so")
-SOURCES = ["gemv_bf16.cu", "gemv_cols.cu", "gemm_tc.cu", "attention.cu", "quant.cu", "kquant.cu", "sampler.cu", "misc_kernels.cu", "decode_persistent.cu", "engine.cu", "capi.cu", "loaders.cpp"]
-HEADERS = ["common.cuh", "engine.h", "persistent.h", "gemm_tc.h", "mbarrier.cuh", "kquant.h", "sampler.h", "loaders.h", os.path.join("..", "..", "include", "homura_b200.h")]
+SOURCES = ["gemv_bf16.cu", "gemm_tc.cu", "attention.cu", "quant.cu", "kquant.cu", "sampler.cu", "misc_kernels.cu", "engine.cu", "capi.cu", "loaders.cpp", "launch_attrs.cpp"]
+HEADERS = ["common.cuh", "engine.h", "gemm_tc.h", "mbarrier.cuh", "kquant.h", "sampler.h", "loaders.h", "launch_attrs.h", os.path.join("..", "..", "include", "homura_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

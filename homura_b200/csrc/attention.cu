@@ -22,6 +22,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "launch_attrs.h"
 #include "mbarrier.cuh"
 
 namespace hm {
@@ -95,9 +96,9 @@ __device__ __forceinline__ void store_out(const AttnArgs& a, int m, int head, in
 template <int HD, int NS>
 __device__ __forceinline__ void cluster_rank0_merge_n(const AttnArgs& a, int g, int head0, int m, float* scratch, const float* c_o, const float* c_ml) {
     const int tid = threadIdx.x, nthreads = blockDim.x;
-    const bool tr = a.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    HM_TRACE(const bool tr = a.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;)
     __syncthreads();  // rank 0's own triple and the neutral ones were written by its threads with plain stores
-    if (tr) a.trace[4] = a.trace[5] = global_timer();  // every split's triple has landed
+    HM_TRACE(if (tr) a.trace[4] = a.trace[5] = global_timer();)  // every split's triple has landed
     float* sc_s = scratch;               // [g][NS] scale of every slot's triple (zero for a neutral one)
     float* l_s = scratch + G_MAX * 16;   // [g] merged sums
     for (int i = tid; i < g * NS; i += nthreads) {
@@ -112,7 +113,7 @@ __device__ __forceinline__ void cluster_rank0_merge_n(const AttnArgs& a, int g, 
         sc_s[i] = mine > -INFINITY ? expf(mine - M) : 0.f;
     }
     __syncthreads();
-    if (tr) a.trace[10] = global_timer();
+    HM_TRACE(if (tr) a.trace[10] = global_timer();)
     if (tid < g) {
         float lv[NS];
 #pragma unroll
@@ -143,13 +144,13 @@ __device__ __forceinline__ void cluster_rank0_merge_n(const AttnArgs& a, int g, 
         o[k] = v;
     }
     __syncthreads();
-    if (tr) a.trace[11] = global_timer();
+    HM_TRACE(if (tr) a.trace[11] = global_timer();)
 #pragma unroll
     for (int k = 0; k < (G_MAX * HD + ATT_THREADS - 1) / ATT_THREADS; ++k) {
         const int i = tid + k * nthreads;
         if (i < g * HD) store_out<HD>(a, m, head0 + i / HD, i % HD, o[k] / l_s[i / HD]);
     }
-    if (tr) a.trace[12] = global_timer();
+    HM_TRACE(if (tr) a.trace[12] = global_timer();)
 }
 
 // Rank 0 of a (row, KV head) cluster, after every split's (max, sum, acc) triple has landed in its
@@ -369,9 +370,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
     const int head0 = kvh * g;
-    const bool tr = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
-    if (tr) a.trace[0] = global_timer();  // CTA resident
-    if (a.trace && tid == 0) atomicMax(a.trace + 8, global_timer());  // the launch's last CTA to become resident
+    HM_TRACE(const bool tr = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;)
+    HM_TRACE(if (tr) a.trace[0] = global_timer();)  // CTA resident
+    HM_TRACE(if (a.trace && tid == 0) atomicMax(a.trace + 8, global_timer());)  // the launch's last CTA to become resident
 
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32)
@@ -462,7 +463,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
         issue_loads(p0, p0, safe_end);
     }
     pdl_wait();
-    if (tr) a.trace[1] = global_timer();  // predecessor complete
+    HM_TRACE(if (tr) a.trace[1] = global_timer();)  // predecessor complete
 
     const int late0 = max(p0, safe_end);  // [late0, p1): at most the page that holds the new token
     if (resident) {
@@ -538,7 +539,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
             store_tiles(pb - p0, pb, late0, p1);
         }
         __syncthreads();  // every page of this CTA and the query are in shared memory
-        if (tr) a.trace[2] = global_timer();
+        HM_TRACE(if (tr) a.trace[2] = global_timer();)
         if (active)
             for (int p = p0 + sub; p < p1; p += nsub) page(p, tiles + (p - p0) * TL::SLOT_FLOATS);
     } else {
@@ -552,11 +553,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
         }
     }
 
-    if (tr) a.trace[3] = global_timer();  // this warp's pages done
-    if (a.trace && tid == 0 && blockIdx.y == 0 && blockIdx.z == 0 && late0 < p1) a.trace[7] = global_timer();  // the split that holds the new token is done
+    HM_TRACE(if (tr) a.trace[3] = global_timer();)  // this warp's pages done
+    HM_TRACE(if (a.trace && tid == 0 && blockIdx.y == 0 && blockIdx.z == 0 && late0 < p1) a.trace[7] = global_timer();)  // the split that holds the new token is done
     merge_and_write<HD, CL>(a, active, run_m, run_l, acc, nsub, g, head0, split, kvh, m, w_ml, w_acc, c_o, c_ml, &s_last, CL ? &s_rbar : nullptr, &s_abort, CL ? nact : -1);
-    if (tr) a.trace[6] = global_timer();  // merged and stored (rank 0 of the cluster)
-    if (a.trace && tid == 0) atomicMax(a.trace + 9, global_timer());  // the launch's last rank 0 to finish
+    HM_TRACE(if (tr) a.trace[6] = global_timer();)  // merged and stored (rank 0 of the cluster)
+    HM_TRACE(if (a.trace && tid == 0) atomicMax(a.trace + 9, global_timer());)  // the launch's last rank 0 to finish
 }
 
 // ---- streaming variant for long contexts ---------------------------------------------------------
@@ -812,17 +813,10 @@ cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
     const bool stream = a.stream_pages > 0 && pages_per_cta >= ST_MIN_PAGES && pages_per_cta <= ST_MAX_PT;
     const int slots = CL ? merge_slot_cap(a.nsplit) : 1;  // rank 0 of a cluster receives every split's triples
     const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots) : smem_bytes<HD, BF16>(g, slots, pick_nslots<HD, BF16>(g, a.early_pages, a.max_pages, a.nsplit));
-    // the opt-in limit only ever grows: launches captured in a graph must stay valid after later calls
-    static size_t opted[2] = {40 * 1024, 40 * 1024};  // static shared memory counts against the 48 KB default too
-    if (smem > opted[stream ? 1 : 0]) {
-        cudaError_t e = stream ? cudaFuncSetAttribute(attn_stream_kernel<HD, BF16, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                               : cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        opted[stream ? 1 : 0] = smem;
-    }
-    if (CL && a.nsplit > 8) {
-        cudaError_t e = stream ? cudaFuncSetAttribute(attn_stream_kernel<HD, BF16, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)
-                               : cudaFuncSetAttribute(attn_decode_kernel<HD, BF16, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    // per device, and only ever raised: launches captured in a graph must stay valid after later calls
+    {
+        cudaError_t e = stream ? ensure_dyn_smem(attn_stream_kernel<HD, BF16, CL>, smem) : ensure_dyn_smem(attn_decode_kernel<HD, BF16, CL>, smem);
+        if (e == cudaSuccess && CL && a.nsplit > 8) e = stream ? ensure_nonportable_clusters(attn_stream_kernel<HD, BF16, CL>) : ensure_nonportable_clusters(attn_decode_kernel<HD, BF16, CL>);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};

@@ -556,6 +556,7 @@ int hm_time_decode(hm_engine* e, int warmup, int steps, float* ms_total) { retur
 int hm_profile_decode(hm_engine* e, int steps, hm_kernel_stat* out, int cap, int* n_out) {
     return e ? e->impl->profile_decode(steps, out, cap, n_out) : gfail(HM_ERR_INVALID, "null engine");
 }
+int hm_selftest_expire_wait(hm_engine* e) { return e ? e->impl->selftest_expire_wait() : gfail(HM_ERR_INVALID, "null engine"); }
 void* hm_engine_stream(hm_engine* e) { return e ? (void*)e->impl->stream() : nullptr; }
 int hm_launches_per_step(hm_engine* e, int* out) {
     if (!e || !out) return gfail(HM_ERR_INVALID, "null argument");
@@ -577,60 +578,11 @@ int hm_pack_bf16_slabs(const void* w_kn, int K, int N, void* dst, void* stream) 
     return sg.finish(launch_pack_slabs_from_kn(src, K, N, d, st));
 }
 
-int hm_pack_bf16_cols8(const void* w_kn, int K, int N, void* dst, void* stream) {
-    if (!w_kn || !dst || K < 1 || N < 1) return gfail(HM_ERR_INVALID, "hm_pack_bf16_cols8: bad arguments");
-    NEED_DEVICE();
-    cudaStream_t st = (cudaStream_t)stream;
-    Staging sg(st);
-    const size_t slab_elems = (size_t)((N + SLAB - 1) / SLAB) * K * SLAB;
-    const size_t dst_elems = (size_t)((N + 7) / 8) * K * 8;
-    const uint16_t* src = sg.in((const uint16_t*)w_kn, (size_t)K * N);
-    uint16_t* slabs = (uint16_t*)sg.scratch(slab_elems * 2, false);
-    uint16_t* d = sg.out((uint16_t*)dst, dst_elems);
-    if (!src || !d || !slabs) return sg.finish(cudaErrorMemoryAllocation);
-    if (!sg.ok(launch_pack_slabs_from_kn(src, K, N, slabs, st))) return sg.finish(cudaSuccess);
-    return sg.finish(launch_pack_cols(slabs, K, N, EPI_STORE, 0, 0, 8, d, st));
-}
-
-// HM_LAYOUT_COLS8: the column-group kernel of the decode step's layer projections, plain prologue and store.
-static int gemv_bf16_cols8(const float* x, const void* w, int M, int K, int N, float* y, cudaStream_t st) {
-    if (M > MAX_M) return gfail(HM_ERR_UNSUPPORTED, "hm_gemv_bf16: HM_LAYOUT_COLS8 takes at most 8 rows");
-    const int mp = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-    const int sms = sm_count_of_current_device();
-    int grid = 0;
-    size_t smem = 0;
-    if (!gemv_cols_plan(EPI_STORE, PRO_PLAIN, K, N, mp, sms, &grid, &smem))
-        return gfail(HM_ERR_UNSUPPORTED, "hm_gemv_bf16: HM_LAYOUT_COLS8 needs the weights of one CTA per SM to fit shared memory");
-    Staging sg(st);
-    float* xp = (float*)sg.scratch((size_t)mp * K * 4, true);  // padded rows read zeros
-    if (!xp) return sg.finish(cudaErrorMemoryAllocation);
-    sg.ok(cudaMemcpyAsync(xp, x, (size_t)M * K * 4, cudaMemcpyDefault, st));
-    const uint16_t* wd = sg.in((const uint16_t*)w, (size_t)((N + 7) / 8) * K * 8);
-    float* yd = sg.out(y, (size_t)M * N);
-    if (!wd || !yd) return sg.finish(cudaErrorMemoryAllocation);
-    int* err = nullptr;
-    if (!sg.ok(get_wait_err(&err))) return sg.finish(cudaSuccess);
-    GemvArgs a{};
-    a.W = wd;
-    a.K = K;
-    a.N = N;
-    a.m_valid = M;
-    a.x = xp;
-    a.ldx = K;
-    a.pro = PRO_PLAIN;
-    a.epi = EPI_STORE;
-    a.y = yd;
-    a.ldy = N;
-    a.err_flag = err;
-    return sg.finish(launch_gemv_cols(a, mp, sms, st, false));
-}
-
 int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, int K, int N, float* y, void* stream) {
     if (!x || !w_bf16 || !y || M < 1 || M > 16 || K < 1 || N < 1) return gfail(HM_ERR_INVALID, "hm_gemv_bf16: bad arguments (1 <= M <= 16)");
     if (layout == HM_LAYOUT_KN && N % 8 != 0) return gfail(HM_ERR_UNSUPPORTED, "hm_gemv_bf16: row-major [K,N] needs N to be a multiple of 8 (128-bit loads)");
-    if (layout != HM_LAYOUT_KN && layout != HM_LAYOUT_SLAB128 && layout != HM_LAYOUT_COLS8) return gfail(HM_ERR_INVALID, "hm_gemv_bf16: unknown layout");
+    if (layout != HM_LAYOUT_KN && layout != HM_LAYOUT_SLAB128) return gfail(HM_ERR_INVALID, "hm_gemv_bf16: unknown layout");
     NEED_DEVICE();
-    if (layout == HM_LAYOUT_COLS8) return gemv_bf16_cols8(x, w_bf16, M, K, N, y, (cudaStream_t)stream);
     cudaStream_t st = (cudaStream_t)stream;
     Staging sg(st);
     const int nslabs = (N + SLAB - 1) / SLAB;
@@ -691,9 +643,16 @@ int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, int K, i
             ce = get_scratch(pf, (size_t)nslabs, &a.partial, &a.tickets);
             if (ce != cudaSuccess) break;
         }
+        ce = get_wait_err(&a.err_flag);  // raised by the bounded waits of the staged / cluster variants
+        if (ce != cudaSuccess) break;
         ce = launch_gemv_bf16(a, mp, st, false);
     }
-    return sg.finish(ce);
+    const bool synced = sg.staged();
+    const int rc = sg.finish(ce);
+    if (rc != HM_OK) return rc;
+    // with device pointers only the call stays asynchronous; hm_dev_sync reports a wait that ran out
+    if (synced && take_wait_err()) return gfail(HM_ERR_TIMEOUT, "hm_gemv_bf16: a bounded device-side wait ran out");
+    return HM_OK;
 }
 
 int hm_gemm_bf16_tc(const float* x, const void* w_tc, int M, int K, int N, int ksplit, float* y, void* stream) {
@@ -909,7 +868,12 @@ int hm_attn_decode_paged(const float* q, const void* k_pages, const void* v_page
         a.part_ml = base + acc_f;
     }
     if (!a.q || !a.page_table || !a.kv_len || !a.out) return sg.finish(cudaErrorMemoryAllocation);
-    return sg.finish(launch_attn_decode(a, B, kv_dtype == HM_BF16, st, false));
+    const cudaError_t le = launch_attn_decode(a, B, kv_dtype == HM_BF16, st, false);
+    const bool synced = sg.staged();
+    const int rc = sg.finish(le);
+    if (rc != HM_OK) return rc;
+    if (synced && take_wait_err()) return gfail(HM_ERR_TIMEOUT, "hm_attn_decode_paged: a bounded device-side wait ran out");
+    return HM_OK;
 }
 
 int hm_argmax(const float* logits, int rows, int n, uint32_t* out, void* stream) {

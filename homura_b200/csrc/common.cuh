@@ -9,8 +9,6 @@ constexpr int SLAB = 128;       // output columns per weight slab
 constexpr int GEMV_THREADS = 256;
 constexpr int ROWS_PER_PASS = 16;  // 256 threads x 16 B = 16 rows x 256 B
 constexpr int MAX_M = 8;
-constexpr int COLS_THREADS = 288;  // column-group projection kernel: nine warps, so that nine groups get a warp each
-constexpr size_t COLS_SMEM_MAX = 208 * 1024;
 
 // ---- programmatic dependent launch ----------------------------------------------------
 // Kernels in the decode chain call pdl_launch_dependents() first (so the next kernel's CTAs
@@ -76,6 +74,13 @@ __device__ __forceinline__ void l2_prefetch_slice(const void* base, unsigned lon
     }
 }
 
+// Phase stamps (%globaltimer at the phase boundaries of a launch) exist only in builds with -DHM_PHASE_TRACE:
+// the decode kernels are chains of instructions executed once, so even a predicated-off stamp costs time.
+#ifdef HM_PHASE_TRACE
+#define HM_TRACE(...) __VA_ARGS__
+#else
+#define HM_TRACE(...)
+#endif
 __device__ __forceinline__ unsigned long long global_timer() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -266,7 +271,6 @@ struct GemvArgs {
     long long row_stride;   // bytes
     int K, N;
     int m_valid;            // rows >= m_valid are padding: computed, never stored
-    int n_groups;           // column-group kernel: groups of 8 output columns (filled in by its launcher)
     int ksplit, rows_per_split;
     int cluster;            // > 1: the ksplit CTAs of a slab form one thread-block cluster and reduce through
                             // distributed shared memory (ksplit == cluster); else partial/tickets are used
@@ -347,23 +351,6 @@ struct QuantArgs {
 // ---- launchers (defined in the .cu files) ----------------------------------------------
 cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl);
 
-// Column-group layout (gemv_cols.cu): output column held at position c (0..7) of group g.  Plain stores:
-// 8 consecutive columns.  Fused QKV with RoPE: positions 0..3 are columns d..d+3 of a Q or K head,
-// positions 4..7 their rotation partners d+hd/2..; V columns are consecutive.  (SwiGLU groups hold
-// gate columns 4g..4g+3 and the matching up columns; their epilogue indexes them directly.)
-__host__ __device__ inline int cols_group_col(int epi, int g, int c, int q_dim, int kv_dim, int hd, int N) {
-    const int nb = g * 8;
-    if (epi == EPI_QKV_ROPE && nb < q_dim + kv_dim) {
-        const int h = nb / hd, d0 = ((nb % hd) >> 3) << 2;
-        return h * hd + (c < 4 ? d0 + c : (hd >> 1) + d0 + (c - 4));
-    }
-    (void)N;
-    return nb + c;
-}
-int cols_groups(int epi, int N);
-bool gemv_cols_plan(int epi, int pro, int K, int N, int M, int sm_count, int* grid, size_t* smem);
-cudaError_t launch_pack_cols(const uint16_t* slabs, int K, int N, int epi, int q_dim, int kv_dim, int hd, uint16_t* dst, cudaStream_t st);
-cudaError_t launch_gemv_cols(const GemvArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
 size_t gemv_partial_floats(int N, int ksplit, int M);
 void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_per_split);
 // Cluster variant: ksplit = cluster size (<= max_cluster), sized so that all CTAs are resident at once.
@@ -393,6 +380,8 @@ cudaError_t launch_dequant(const uint8_t* blocks, size_t nblocks, int q4, float*
 cudaError_t launch_gemv_quant(const QuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
 // quant plan helpers: PostQKV (src/hf/emitter_quant.rs:800-905) and SiLU*Up (:1078-1099)
 cudaError_t launch_post_qkv(const float* qkv, int M, int heads, int kv_heads, int hd, int has_qk_norm, const float* q_norm_w, const float* k_norm_w, float eps, const float* rope_cos, const float* rope_sin, const int32_t* row_pos, const int32_t* row_seq, const KvDesc& kv, float* q_out, cudaStream_t st, bool pdl);
+// one-CTA kernel whose second mbarrier wait runs out after `limit` polls and raises *err_flag to 2 (self-test of the give-up path)
+cudaError_t launch_bounded_wait_probe(const void* src16, int* err_flag, unsigned long long limit, int* landed, cudaStream_t st);
 cudaError_t launch_silu_mul(const float* gate_up, int M, int I, float* act, cudaStream_t st, bool pdl);
 
 }  // namespace hm

@@ -106,7 +106,7 @@ Engine::~Engine() {
     fr(embed_); fr(final_norm_); fr(rope_cos_); fr(rope_sin_);
     for (auto& l : layers_) {
         fr(l.in_ln); fr(l.post_ln); fr(l.qkv_bias); fr(l.q_norm); fr(l.k_norm);
-        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->cols); fr(w->tc); fr(w->scales); fr(w->codes); fr(w->kq_data); fr(w->kq_tile_type); }
+        for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->tc); fr(w->scales); fr(w->codes); fr(w->kq_data); fr(w->kq_tile_type); }
     }
     fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes); fr(lm_head_.kq_data); fr(lm_head_.kq_tile_type);
     fr(xpack_); fr(xpack_attn_); fr(xpack_act_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
@@ -114,7 +114,6 @@ Engine::~Engine() {
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
     fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_);
-    fr(mk_layers_dev_); fr(mk_scratch_); fr(mk_bar_); fr(mk_trace_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -361,30 +360,6 @@ int Engine::finalize() {
         if (l.down.loaded_parts != 1) return fail(HM_ERR_STATE, p + "down projection");
         if (cfg_.has_qk_norm && (!l.q_norm || !l.k_norm)) return fail(HM_ERR_STATE, p + "q_norm/k_norm");
     }
-    // Opt-in (HM_COLS_MASK, bits 1 QKV, 2 O, 4 gate/up, 8 down): decode passes of up to 8 rows run those layer
-    // projections from a copy grouped by output columns, where no partial sum crosses a CTA.  Off by default:
-    // with the split-K partials travelling by asynchronous stores the cluster kernels are as fast per launch,
-    // and the larger shared-memory footprint of whole columns delays the residency of the launches behind.
-    if (use_clusters_ && cfg_.weight_dtype == HM_BF16) {
-        const char* mk = std::getenv("HM_COLS_MASK");
-        const int mask = mk ? std::atoi(mk) : 0;
-        for (int i = 0; i < L_; ++i) {
-            LayerW& l = layers_[i];
-            struct { LinearW* w; int epi, pro, bit; } jobs[4] = {{&l.qkv, EPI_QKV_ROPE, PRO_RMSNORM, 1}, {&l.o, EPI_STORE, PRO_PLAIN, 2}, {&l.gu, EPI_SWIGLU, PRO_RMSNORM, 4}, {&l.down, EPI_STORE, PRO_PLAIN, 8}};
-            for (auto& j : jobs) {
-                if (!(mask & j.bit)) continue;
-                int grid = 0;
-                size_t smem = 0;
-                if (j.epi == EPI_QKV_ROPE && (cfg_.has_qk_norm || hd_ % 8 != 0)) continue;
-                if (!j.w->slabs || !gemv_cols_plan(j.epi, j.pro, j.w->K, j.w->N, 1, sm_count_, &grid, &smem)) continue;
-                const size_t bytes = (size_t)cols_groups(j.epi, j.w->N) * j.w->K * 16;
-                HM_CUDA(cudaMalloc(&j.w->cols, bytes));
-                HM_CUDA(launch_pack_cols(j.w->slabs, j.w->K, j.w->N, j.epi, qdim_, kvdim_, hd_, j.w->cols, stream_));
-                j.w->cols_epi = j.epi;
-            }
-        }
-        HM_CUDA(cudaStreamSynchronize(stream_));
-    }
     std::vector<float> c, s;
     build_rope_table(hd_, cfg_.max_position_embeddings, cfg_.rope_theta, &c, &s);
     HM_CUDA(cudaMalloc(&rope_cos_, c.size() * 4));
@@ -502,8 +477,9 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     HM_CUDA(cudaMalloc(&pf_tokens_, (size_t)max_seq_len * 4));
     HM_CUDA(cudaMalloc(&pf_pos_, (size_t)max_seq_len * 4));
     HM_CUDA(cudaMalloc(&pf_seq_, (size_t)max_seq_len * 4));
-    pin_u32_cap_ = std::max<size_t>((size_t)3 * max_seq_len, (size_t)batch * (max_seq_len + 2)) + 16;
+    pin_u32_cap_ = std::max<size_t>((size_t)3 * max_seq_len, (size_t)batch * (max_seq_len + 2)) + 16;  // the last word receives the device error word
     HM_CUDA(cudaMallocHost(&pin_u32_, pin_u32_cap_ * 4));
+    pin_u32_[pin_u32_cap_ - 1] = 0;
     len_.assign(batch, 0);
     batch_ = batch;
     max_seq_ = max_seq_len;
@@ -525,151 +501,20 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
     HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));
     HM_CUDA(cudaMemset(att_tickets_, 0, (size_t)scratch_rows_ * kvh_ * 4));
-    // The persistent single-launch decode kernel is opt-in (HM_PERSISTENT=1): on this hardware its
-    // step time is no better than the captured kernel chain, which stays the default.
+#ifdef HM_PHASE_TRACE
     if (const char* gt = std::getenv("HM_GEMV_TRACE")) {
         if (gt[0] == '1' && !gemv_trace_) {
             HM_CUDA(cudaMalloc(&gemv_trace_, 512 * 16 * sizeof(unsigned long long)));
             HM_CUDA(cudaMemset(gemv_trace_, 0, 512 * 16 * sizeof(unsigned long long)));
         }
     }
-    const char* mega = std::getenv("HM_PERSISTENT");
-    if (mega && mega[0] == '1') {
-        rc = setup_persistent();
-        if (rc) return rc;
-    }
+#endif
     return capture_decode_graph();
 }
 
-// Smallest K-split count whose per-CTA critical path (items per CTA x rows per item) is within
-// 15 % of the best one: fewer splits mean fewer partials for the next phase to add up.
-static void pick_persistent_split(int nslabs, int K, int nb, int* S, int* R) {
-    const int smax = std::max(1, std::min(24, K / 16));
-    long best = -1;
-    std::vector<long> cost(smax + 1, 0);
-    for (int sp = 1; sp <= smax; ++sp) {
-        const long rows = (K + sp - 1) / sp, items = (long)nslabs * sp, per = (items + nb - 1) / nb;
-        cost[sp] = per * rows;
-        if (best < 0 || cost[sp] < best) best = cost[sp];
-    }
-    int pick = smax;
-    for (int sp = 1; sp <= smax; ++sp)
-        if (cost[sp] * 100 <= best * 115) {
-            pick = sp;
-            break;
-        }
-    *S = pick;
-    *R = (K + pick - 1) / pick;
-}
-
-int Engine::setup_persistent() {
-    use_persistent_ = false;
-    if (batch_ != 1 || quant_ || lm_head_.kind != HM_BF16) return HM_OK;
-    for (auto& l : layers_)
-        if (l.qkv.kind != HM_BF16 || l.o.kind != HM_BF16 || l.gu.kind != HM_BF16 || l.down.kind != HM_BF16) return HM_OK;
-    if (H_ > mk_xs_max() || heads_ / kvh_ > G_MAX_MK) return HM_OK;
-    int per_sm = 0;
-    if (mk_prepare(&per_sm) != cudaSuccess || per_sm < 1) {
-        cudaGetLastError();
-        return HM_OK;
-    }
-    int coop = 0;
-    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device_);
-    if (!coop) return HM_OK;
-    const int nb = sm_count_;
-    MkArgs& a = mk_;
-    a = MkArgs{};
-    a.H = H_; a.I = I_; a.heads = heads_; a.kvh = kvh_; a.hd = hd_; a.qdim = qdim_; a.kvdim = kvdim_; a.L = L_; a.V = V_;
-    a.eps = (float)cfg_.rms_norm_eps;
-    a.scale = (float)(1.0 / std::sqrt((double)hd_));
-    a.has_qk_norm = cfg_.has_qk_norm;
-    a.kv_bf16 = kv_bf16_ ? 1 : 0;
-    a.embed_bf16 = embed_dtype_ == HM_BF16 ? 1 : 0;
-    a.slabs_qkv = (qdim_ + 2 * kvdim_ + SLAB - 1) / SLAB;
-    a.slabs_h = (H_ + SLAB - 1) / SLAB;
-    a.slabs_gu = (2 * I_ + SLAB - 1) / SLAB;
-    a.slabs_v = (V_ + SLAB - 1) / SLAB;
-    pick_persistent_split(a.slabs_qkv, H_, nb, &a.S1, &a.R1);
-    pick_persistent_split(a.slabs_h, qdim_, nb, &a.S3, &a.R3);
-    pick_persistent_split(a.slabs_gu, H_, nb, &a.S4, &a.R4);
-    pick_persistent_split(a.slabs_h, I_, nb, &a.S5, &a.R5);
-    if (std::max({a.R1, a.R3, a.R4, a.R5}) > mk_xs_max()) return HM_OK;
-    a.att_cap = std::max(1, nb / kvh_);
-    a.barriers_per_launch = 5 * L_ + 1;
-    std::vector<MkLayer> hl(L_);
-    for (int l = 0; l < L_; ++l) {
-        const LayerW& w = layers_[l];
-        hl[l] = MkLayer{w.qkv.slabs, w.o.slabs, w.gu.slabs, w.down.slabs, w.in_ln, w.post_ln, w.qkv_bias, w.q_norm, w.k_norm, k_pool_[l], v_pool_[l]};
-    }
-    HM_CUDA(cudaMalloc(&mk_layers_dev_, sizeof(MkLayer) * L_));
-    HM_CUDA(cudaMemcpy(mk_layers_dev_, hl.data(), sizeof(MkLayer) * L_, cudaMemcpyHostToDevice));
-    a.layers = mk_layers_dev_;
-    a.embed = embed_;
-    a.wlm = lm_head_.slabs;
-    a.final_norm = final_norm_;
-    a.rope_cos = rope_cos_;
-    a.rope_sin = rope_sin_;
-    a.page_table = page_table_;
-    a.token = tokens_dev_;
-    a.pos = pos_dev_;
-    a.next_tok = next_dev_;
-    a.feed_tok = tokens_dev_;
-    a.hist = hist_dev_;
-    const int g = heads_ / kvh_;
-    const size_t n_h = (size_t)a.slabs_h * SLAB;
-    a.att_cap = std::max(1, std::min(a.att_cap, max_pages_));
-    size_t off = 0;
-    auto take = [&](size_t n) { size_t o = off; off += (n + 15) / 16 * 16; return o; };
-    a.o_hcur = take(n_h); a.o_hmid = take(n_h); a.o_pqkv = take((size_t)a.S1 * a.slabs_qkv * SLAB); a.o_ssin = take(a.S1);
-    a.o_attml = take((size_t)kvh_ * a.att_cap * g * 2); a.o_attacc = take((size_t)kvh_ * a.att_cap * g * hd_); a.o_po = take((size_t)a.S3 * n_h);
-    a.o_pgu = take((size_t)a.S4 * a.slabs_gu * SLAB); a.o_sspost = take(a.S4); a.o_pdown = take((size_t)a.S5 * n_h);
-    a.layer_stride = off;
-    const size_t total = a.layer_stride * L_ + 2 * (size_t)((nb + 15) / 16 * 16);
-    HM_CUDA(cudaMalloc(&mk_scratch_, total * sizeof(LL)));
-    HM_CUDA(cudaMemset(mk_scratch_, 0, total * sizeof(LL)));  // generation 0 = never valid
-    a.ll = reinterpret_cast<LL*>(mk_scratch_);
-    a.amax_v = a.ll + a.layer_stride * L_;
-    a.amax_i = a.amax_v + (nb + 15) / 16 * 16;
-    a.logits = logits_;
-    HM_CUDA(cudaMalloc(&mk_bar_, 512));
-    HM_CUDA(cudaMemset(mk_bar_, 0, 512));
-    a.launch_idx = reinterpret_cast<unsigned int*>(mk_bar_);
-    a.err_flag = err_flag_;
-    const char* tr = std::getenv("HM_MK_TRACE");
-    if (tr && tr[0] == '1') {
-        HM_CUDA(cudaMalloc(&mk_trace_, (size_t)(a.barriers_per_launch + 1) * 3 * 8));
-        HM_CUDA(cudaMemset(mk_trace_, 0, (size_t)(a.barriers_per_launch + 1) * 3 * 8));
-        a.trace = mk_trace_;
-    }
-    mk_nb_ = nb;
-    use_persistent_ = true;
-    return HM_OK;
-}
-
 int Engine::launch_step() {
-    if (use_persistent_ && persistent_direct_) {
-        cudaError_t ce = launch_decode_persistent(mk_, mk_nb_, stream_);
-        if (ce != cudaSuccess) return cuda_fail(ce, "persistent decode launch");
-        return HM_OK;
-    }
     HM_CUDA(cudaGraphLaunch(graph_exec_, stream_));
     return HM_OK;
-}
-
-// After a synchronisation: a bounded device-side wait that ran out leaves the barrier counters
-// of the persistent kernel inconsistent, so they are reset before the error is reported.
-int Engine::check_step_error() {
-    if (!use_persistent_) return HM_OK;
-    int flag = 0;
-    HM_CUDA(cudaMemcpy(&flag, err_flag_, 4, cudaMemcpyDeviceToHost));
-    if (flag == 0) return HM_OK;
-    cudaMemset(err_flag_, 0, 4);
-    if (flag == 2) {
-        // half-written exchange slots of the failed step would look valid to a retry: invalidate them all
-        cudaMemset(mk_scratch_, 0, (mk_.layer_stride * L_ + 2 * (size_t)((mk_nb_ + 15) / 16 * 16)) * sizeof(LL));
-        return fail(HM_ERR_TIMEOUT, "a bounded device-side wait in the persistent decode kernel ran out");
-    }
-    return fail(HM_ERR_INVALID, "token id out of range (>= vocab_size)");
 }
 
 int Engine::kv_reset(int seq) {
@@ -825,7 +670,9 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             GemvArgs a{};
             a.W = L.slabs;
             a.err_flag = err_flag_;
+#ifdef HM_PHASE_TRACE
             if (gemv_trace_ && *launches < 512) a.trace = gemv_trace_ + (size_t)*launches * 16;
+#endif
             if (m0 == 0) {
                 a.pf_ptr = pf_ptr_;
                 a.pf_bytes = pf_bytes_;
@@ -866,21 +713,14 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.rope_sin = rope_sin_;
             a.row_pos = row_pos ? row_pos + m0 : nullptr;
             a.row_seq = row_seq ? row_seq + m0 : nullptr;
-        a.seq_base = m0;
+            a.seq_base = m0;
             const int nslabs = (L.N + SLAB - 1) / SLAB;
             a.amax_val = amax_val ? amax_val + (size_t)m0 * nslabs : nullptr;
             a.amax_idx = amax_idx ? amax_idx + (size_t)m0 * nslabs : nullptr;
             a.partial = partial_;
             a.tickets = tickets_;
-            int cgrid = 0;
-            size_t csmem = 0;
-            if (L.cols && L.cols_epi == epi && gemv_cols_plan(epi, pro, L.K, L.N, mp, sm_count_, &cgrid, &csmem)) {
-                a.W = L.cols;
-                ce = launch_gemv_cols(a, mp, sm_count_, stream_, pdl_);
-            } else {
-                if (a.cluster == 0 && gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
-                ce = launch_gemv_bf16(a, mp, stream_, pdl_);
-            }
+            if (a.cluster == 0 && gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
+            ce = launch_gemv_bf16(a, mp, stream_, pdl_);
         } else if (L.kind == HM_Q4_K) {
             KQuantArgs a{};
             a.data = L.kq_data;
@@ -950,7 +790,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         pf_ptr_ = nullptr;
         pf_bytes_ = 0;
         if (!pf || !w || !w->slabs || off >= w->bytes()) return;
-        pf_ptr_ = (const char*)(w->cols ? w->cols : w->slabs) + off;
+        pf_ptr_ = (const char*)w->slabs + off;
         pf_bytes_ = std::min(cap, w->bytes() - off);
     };
     constexpr size_t LM_PF = 24u << 20;  // the LM head does not fit the L2: only its first 2 x 24 MB are fetched early
@@ -998,7 +838,9 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             at.xp_out = xpack_attn_;
             at.xp_mpad = tc_mpad(M);
         }
+#ifdef HM_PHASE_TRACE
         if (gemv_trace_ && *launches < 512) at.trace = gemv_trace_ + (size_t)*launches * 16;
+#endif
         // decode passes: one row per sequence (prefill chunks write several positions of one sequence); launches of at most two
         // CTAs per SM are latency-bound and keep all their pages resident, larger ones keep their shared memory small
         at.early_pages = row_seq == nullptr ? ((long)M * kvh_ * at.nsplit <= 2L * sm_count_ ? 2 : 1) : 0;
@@ -1073,28 +915,6 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
 
 int Engine::capture_decode_graph() {
     int launches = 0;
-    if (use_persistent_) {
-        // One cooperative launch per step.  Captured into a graph when the runtime accepts a
-        // cooperative kernel node; otherwise launched directly.
-        persistent_direct_ = true;
-        launches_per_step_ = 1;
-        if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-            cudaError_t le = launch_decode_persistent(mk_, mk_nb_, stream_);
-            cudaGraph_t g = nullptr;
-            cudaError_t ce = cudaStreamEndCapture(stream_, &g);
-            if (le == cudaSuccess && ce == cudaSuccess && g && cudaGraphInstantiate(&graph_exec_, g, 0) == cudaSuccess) {
-                graph_ = g;
-                persistent_direct_ = false;
-            } else {
-                if (g) cudaGraphDestroy(g);
-                graph_exec_ = nullptr;
-                cudaGetLastError();
-            }
-        } else {
-            cudaGetLastError();
-        }
-        return HM_OK;
-    }
     HM_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_pass(batch_, tokens_dev_, pos_dev_, nullptr, 0, batch_, true, next_dev_, tokens_dev_, pos_dev_, hist_dev_, &launches);
     cudaGraph_t g = nullptr;
@@ -1110,14 +930,33 @@ int Engine::capture_decode_graph() {
     return HM_OK;
 }
 
+// The device error word (raised by a token id out of range, or by a bounded device-side wait that ran out)
+// travels back with the results of every pass: queue_error_copy() before the pass's synchronisation,
+// check_device_error() after it.
+int Engine::queue_error_copy() {
+    HM_CUDA(cudaMemcpyAsync(pin_u32_ + pin_u32_cap_ - 1, err_flag_, 4, cudaMemcpyDeviceToHost, stream_));
+    return HM_OK;
+}
+
 int Engine::check_device_error() {
-    int flag = 0;
-    HM_CUDA(cudaMemcpy(&flag, err_flag_, 4, cudaMemcpyDeviceToHost));
+    const uint32_t flag = pin_u32_[pin_u32_cap_ - 1];
     if (flag) {
-        cudaMemset(err_flag_, 0, 4);
-        if (flag == 2) return fail(HM_ERR_TIMEOUT, "a bounded device-side wait ran out (tensor-core projection)");
+        pin_u32_[pin_u32_cap_ - 1] = 0;
+        cudaMemsetAsync(err_flag_, 0, 4, stream_);
+        cudaStreamSynchronize(stream_);
+        if (flag == 2) return fail(HM_ERR_TIMEOUT, "a bounded device-side wait ran out in a kernel of this pass; its results are not valid");
         return fail(HM_ERR_INVALID, "token id out of range (>= vocab_size)");
     }
+    return HM_OK;
+}
+
+// Queues the bounded-wait probe on the engine's stream with the engine's error word: the next pass
+// (prefill, decode step, ...) finds the word raised and reports HM_ERR_TIMEOUT; the one after is clean.
+int Engine::selftest_expire_wait() {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "selftest_expire_wait before kv_alloc");
+    // any 16 aligned device bytes serve as the source of the probe's real copy
+    HM_CUDA(launch_bounded_wait_probe(rope_cos_, err_flag_, 20000ull, nullptr, stream_));
     return HM_OK;
 }
 
@@ -1156,6 +995,7 @@ int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t*
     uint32_t* tok_pin = st + 3 * n + 1;
     HM_CUDA(cudaMemcpyAsync(tok_pin, next_dev_ + seq, 4, cudaMemcpyDeviceToHost, stream_));
     if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, (size_t)V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    if (int qrc = queue_error_copy()) return qrc;
     HM_CUDA(cudaStreamSynchronize(stream_));
     int rc = check_device_error();
     if (rc) return rc;
@@ -1180,9 +1020,10 @@ int Engine::decode_step(const uint32_t* tokens, float* logits, uint32_t* next_to
     }
     HM_CUDA(cudaMemcpyAsync(pin_u32_ + batch_, next_dev_, (size_t)batch_ * 4, cudaMemcpyDeviceToHost, stream_));
     if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, (size_t)batch_ * V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    if (int qrc = queue_error_copy()) return qrc;
     HM_CUDA(cudaStreamSynchronize(stream_));
     {
-        int erc = check_step_error();
+        int erc = check_device_error();
         if (erc) return erc;
     }
     if (next_tokens) std::memcpy(next_tokens, pin_u32_ + batch_, (size_t)batch_ * 4);
@@ -1209,9 +1050,10 @@ int Engine::decode_greedy_n(const uint32_t* first_tokens, int steps, uint32_t* o
     // history rows: token at position p of sequence b is hist[b][p]; the new ones are len+1 .. len+steps
     for (int b = 0; b < batch_; ++b)
         HM_CUDA(cudaMemcpyAsync(pin_u32_ + batch_ + (size_t)b * steps, hist_dev_ + (size_t)b * (max_seq_ + 1) + len_[b] + 1, (size_t)steps * 4, cudaMemcpyDeviceToHost, stream_));
+    if (int qrc = queue_error_copy()) return qrc;
     HM_CUDA(cudaStreamSynchronize(stream_));
     {
-        int erc = check_step_error();
+        int erc = check_device_error();
         if (erc) return erc;
     }
     if (steps > 0) std::memcpy(out_ids, pin_u32_ + batch_, (size_t)batch_ * steps * 4);
@@ -1239,31 +1081,16 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
         if (lrc) return lrc;
     }
     HM_CUDA(cudaEventRecord(e1, stream_));
+    if (int qrc = queue_error_copy()) return qrc;
     HM_CUDA(cudaStreamSynchronize(stream_));
     HM_CUDA(cudaEventElapsedTime(ms_total, e0, e1));
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     {
-        int erc = check_step_error();
+        int erc = check_device_error();
         if (erc) return erc;
     }
-    if (use_persistent_ && mk_trace_) {
-        // phase times of the last step as seen by CTA 0 (globaltimer stamps at each grid barrier)
-        std::vector<unsigned long long> t((size_t)(mk_.barriers_per_launch + 1) * 3);
-        HM_CUDA(cudaMemcpy(t.data(), mk_trace_, t.size() * 8, cudaMemcpyDeviceToHost));
-        double sum[5] = {0, 0, 0, 0, 0}, pre[5] = {0, 0, 0, 0, 0};
-        const int nb1 = mk_.barriers_per_launch + 1;
-        for (int l = 0; l < L_; ++l)
-            for (int p = 0; p < 5; ++p) {
-                sum[p] += (double)(t[l * 5 + p + 1] - t[l * 5 + p]);
-                const unsigned long long sm = t[nb1 + (l * 5 + p) * 2];  // stamp after the input slices were built
-                if (sm) pre[p] += (double)(sm - t[l * 5 + p]);
-            }
-        std::fprintf(stderr, "[hm trace] of which waiting for / building inputs: qkv %.2f o %.2f gate_up %.2f down %.2f\n", pre[0] / L_ / 1e3, pre[2] / L_ / 1e3, pre[3] / L_ / 1e3, pre[4] / L_ / 1e3);
-        const double lm = (double)(t[5 * L_ + 1] - t[5 * L_]);
-        std::fprintf(stderr, "[hm trace] per-layer mean us: qkv %.2f attn %.2f o %.2f gate_up %.2f down %.2f | lm_head %.2f | step %.2f\n", sum[0] / L_ / 1e3, sum[1] / L_ / 1e3,
-                     sum[2] / L_ / 1e3, sum[3] / L_ / 1e3, sum[4] / L_ / 1e3, lm / 1e3, (double)(t[5 * L_ + 1] - t[0]) / 1e3);
-    }
+#ifdef HM_PHASE_TRACE
     if (gemv_trace_) {
         // HM_GEMV_TRACE=1: %globaltimer stamps of CTA 0 of every projection launch of the last step:
         // resident -> predecessor done -> activations staged -> weights multiplied -> partials published ->
@@ -1322,6 +1149,7 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
                              d[0] / n / 1e3, d[1] / n / 1e3, d[2] / n / 1e3, d[3] / n / 1e3, d[4] / n / 1e3, d[5] / n / 1e3, gap / n / 1e3, n);
         }
     }
+#endif
     for (int b = 0; b < batch_; ++b) len_[b] += warmup + steps;
     return HM_OK;
 }
@@ -1339,21 +1167,6 @@ int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) 
     HM_CUDA(cudaStreamSynchronize(stream_));
     double kv_tokens = 0.0;
     for (int b = 0; b < batch_; ++b) kv_tokens += len_[b] + 1;
-    if (use_persistent_) {
-        // the whole step is one launch of the persistent kernel
-        float ms = 0.f;
-        const int l0 = len_[0];
-        int prc = time_decode(2, steps, &ms);
-        if (prc) return prc;
-        std::memset(&out[0], 0, sizeof(out[0]));
-        std::strncpy(out[0].name, "decode_persistent", sizeof(out[0].name) - 1);
-        out[0].launches_per_step = 1;
-        out[0].ms_per_step = ms / steps;
-        const double t_avg = l0 + 2 + (steps + 1) / 2.0;
-        out[0].bytes_per_step = weight_bytes() + (uint64_t)(t_avg * L_ * 2.0 * kvh_ * hd_ * (kv_bf16_ ? 2 : 4));
-        *n_out = 1;
-        return HM_OK;
-    }
     cudaEvent_t e0, e1;
     HM_CUDA(cudaEventCreate(&e0));
     HM_CUDA(cudaEventCreate(&e1));
@@ -1508,9 +1321,9 @@ int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, 
                 }
                 // the sampled tokens of the block are the history entries after the last known position
                 HM_CUDA(cudaMemcpyAsync(blk.data(), hist_dev_ + (size_t)seq * (max_seq_ + 1) + real_pos + 1, (size_t)want * 4, cudaMemcpyDeviceToHost, stream_));
-                HM_CUDA(cudaStreamSynchronize(stream_));
-                rc = check_step_error();
+                rc = queue_error_copy();
                 if (rc) return rc;
+                HM_CUDA(cudaStreamSynchronize(stream_));
                 rc = check_device_error();
                 if (rc) return rc;
                 len_[seq] = real_pos + want;

@@ -12,7 +12,6 @@
 
 #include "../../include/homura_b200.h"
 #include "common.cuh"
-#include "persistent.h"
 
 namespace hm {
 
@@ -20,8 +19,6 @@ struct LinearW {
     int K = 0, N = 0;        // N = output count of the (possibly fused) projection
     int kind = -1;           // HM_BF16 (slab layout) | HM_Q8_0 | HM_Q4_0 (split scales + codes)
     uint16_t* slabs = nullptr;
-    uint16_t* cols = nullptr;  // copy in column groups of 8 (gemv_cols.cu) for decode passes of up to 8 rows; cols_epi = the epilogue it was grouped for
-    int cols_epi = -1;
     uint16_t* tc = nullptr;  // second copy in the tensor-core tile layout (gemm_tc.h), used for passes over more than 8 rows
     uint16_t* scales = nullptr;
     uint8_t* codes = nullptr;
@@ -62,6 +59,7 @@ class Engine {
     int generate(int seq, const int64_t* prompt, int n_prompt, int max_new, const hm_sampling* s, uint32_t* out_ids, int* n_out);
     int time_decode(int warmup, int steps, float* ms_total);
     int profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out);
+    int selftest_expire_wait();
 
     const hm_config& config() const { return cfg_; }
     uint64_t weight_bytes() const;
@@ -85,10 +83,9 @@ class Engine {
     int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, int* launches,
                           const unsigned char* prepacked = nullptr, unsigned char* pack_out = nullptr);
     int capture_decode_graph();
-    int setup_persistent();   // batch-1 bf16 models: one cooperative launch per decode step
-    int launch_step();        // replay the captured graph, or launch the persistent kernel directly
-    int check_step_error();
-    int check_device_error();
+    int launch_step();        // replay the captured decode graph
+    int queue_error_copy();    // device error word -> pinned host word, on the engine's stream
+    int check_device_error();  // after the synchronisation that follows queue_error_copy()
     void prof_mark(int cls);
 
     hm_config cfg_{};
@@ -150,22 +147,13 @@ class Engine {
     int launches_per_step_ = 0;
 
     int only_class_ = -1;
-    unsigned long long* gemv_trace_ = nullptr;  // HM_GEMV_TRACE=1: [512][8] timestamps, one row per projection launch of a pass
+    unsigned long long* gemv_trace_ = nullptr;  // builds with -DHM_PHASE_TRACE and HM_GEMV_TRACE=1: [512][16] timestamps, one row per launch of a pass
 
     // device-side sampler scratch (sampler.cu), allocated on first sampled generation
     float* smp_scaled_ = nullptr;
     int* smp_count_ = nullptr;
     unsigned long long* smp_rng_ = nullptr;
     int32_t* smp_gen_start_ = nullptr;
-
-    // persistent decode kernel (decode_persistent.cu)
-    bool use_persistent_ = false, persistent_direct_ = false;
-    MkArgs mk_{};
-    MkLayer* mk_layers_dev_ = nullptr;
-    float* mk_scratch_ = nullptr;
-    unsigned long long* mk_bar_ = nullptr;  // step counter of the persistent kernel (u32 at offset 0)
-    int mk_nb_ = 0;
-    unsigned long long* mk_trace_ = nullptr;  // >= 0 while profile_decode captures the launches of one kernel class
 };
 
 }  // namespace hm

@@ -26,6 +26,7 @@
 
 #include "common.cuh"
 #include "gemm_tc.h"
+#include "launch_attrs.h"
 #include "mbarrier.cuh"
 
 namespace hm {
@@ -418,13 +419,10 @@ cudaError_t launch_gemm_tc(const TcArgs& a_in, cudaStream_t st, bool pdl) {
     const int nblk = (a.N + BM - 1) / BM;
     const bool cl = a.ksplit > 1;
     const size_t smem = tc_smem_for(a.mpad);
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[cl ? 1 : 0]) {
+    {
         const size_t mx = tc_smem_for(64) > tc_smem_for(32) ? tc_smem_for(64) : tc_smem_for(32);
-        cudaError_t e = cl ? cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mx)
-                           : cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mx);
+        cudaError_t e = cl ? ensure_dyn_smem(gemm_tc_kernel<true>, mx) : ensure_dyn_smem(gemm_tc_kernel<false>, mx);
         if (e != cudaSuccess) return e;
-        attr_set[cl ? 1 : 0] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(nblk * (cl ? a.ksplit : 1)));
@@ -440,11 +438,9 @@ cudaError_t launch_gemm_tc(const TcArgs& a_in, cudaStream_t st, bool pdl) {
     }
     if (cl) {
         if (a.ksplit > 16) return cudaErrorInvalidValue;
-        static bool nonportable_set = false;
-        if (a.ksplit > 8 && !nonportable_set) {  // clusters of 9..16 CTAs are allowed on request
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (a.ksplit > 8) {  // clusters of 9..16 CTAs are allowed on request
+            cudaError_t e = ensure_nonportable_clusters(gemm_tc_kernel<true>);
             if (e != cudaSuccess) return e;
-            nonportable_set = true;
         }
         at[n].id = cudaLaunchAttributeClusterDimension;
         at[n].val.clusterDim.x = (unsigned)a.ksplit;

@@ -23,6 +23,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "launch_attrs.h"
 #include "mbarrier.cuh"
 
 namespace hm {
@@ -127,9 +128,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
     const char* wbase = (const char*)a.W + (long long)slab * a.slab_stride + (long long)(k0 + rl) * a.row_stride + cg * 16;
     const long long pass_stride = (long long)ROWS_PER_PASS * a.row_stride;
 
-    const bool tr = a.trace != nullptr && blockIdx.x == 0 && tid == 0;
-    if (tr) a.trace[0] = global_timer();  // CTA resident
-    if (a.trace && tid == 0) atomicMax(a.trace + 8, global_timer());  // the launch's last CTA to become resident
+    HM_TRACE(const bool tr = a.trace != nullptr && blockIdx.x == 0 && tid == 0;)
+    HM_TRACE(if (tr) a.trace[0] = global_timer();)  // CTA resident
+    HM_TRACE(if (a.trace && tid == 0) atomicMax(a.trace + 8, global_timer());)  // the launch's last CTA to become resident
     pdl_launch_dependents();
     if (a.pf_bytes && tid < 32) l2_prefetch_slice(a.pf_ptr, a.pf_bytes, blockIdx.x, gridDim.x, tid);
 
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
     // the RMSNorm weights fetched above are read below by other threads than those that stored them (a CTA that
     // became resident just before its dependency resolved may still have those loads in flight)
     if (CL && a.pro == PRO_RMSNORM) __syncthreads();
-    if (tr) a.trace[1] = global_timer();  // predecessor complete
+    HM_TRACE(if (tr) a.trace[1] = global_timer();)  // predecessor complete
 
     // the residual element this thread adds in the epilogue (known epilogue CTA only): requested now, used after the reduction
     float resid_v = 0.f;
@@ -263,7 +264,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
     }
     __syncthreads();
     __syncthreads();
-    if (tr) a.trace[2] = global_timer();  // activations in shared memory
+    HM_TRACE(if (tr) a.trace[2] = global_timer();)  // activations in shared memory
 
     // ---- main loop: stream the slab run, 8 column accumulators per row per thread ----
     float2 acc[M][4];
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
         }
     }
 
-    if (tr) a.trace[3] = global_timer();  // weights multiplied
+    HM_TRACE(if (tr) a.trace[3] = global_timer();)  // weights multiplied
     if (norm_rank0) {  // sums of squares of the whole rows, published by the barrier of the reduction below
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -369,7 +370,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
         if (rank != 0) return;  // nothing reads this CTA's shared memory; its stores are on their way
         __syncthreads();        // rank 0's own slot is read by other threads than those that wrote it
         if (a.ksplit > 1 && !mb_wait_cluster(&s_rbar, 0, a.err_flag, &s_abort)) return;  // bounded
-        if (tr) a.trace[4] = global_timer();  // all ranks' partials have landed
+        HM_TRACE(if (tr) a.trace[4] = global_timer();)  // all ranks' partials have landed
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int idx = tid + i * GEMV_THREADS;
@@ -410,7 +411,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
     }
     __syncthreads();
 
-    if (tr) a.trace[5] = global_timer();  // split-K reduced
+    HM_TRACE(if (tr) a.trace[5] = global_timer();)  // split-K reduced
     // ---- epilogues on vals[M][128] (columns n0 .. n0+127 of the output) ----
     const int n0 = slab * SLAB;
     if (a.epi == EPI_STORE) {
@@ -525,22 +526,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
             }
         }
     }
-    if (tr) a.trace[6] = global_timer();  // epilogue stored
-    if (a.trace && tid == 0) atomicMax(a.trace + 9, global_timer());  // the launch's last CTA to finish
+    HM_TRACE(if (tr) a.trace[6] = global_timer();)  // epilogue stored
+    HM_TRACE(if (a.trace && tid == 0) atomicMax(a.trace + 9, global_timer());)  // the launch's last CTA to finish
 }
 
 constexpr size_t GEMV_STAGE_MAX = 80 * 1024;  // largest weight slice staged in shared memory (two CTAs per SM stay resident)
 
 template <int M, bool CL, bool ST>
 cudaError_t launch_mcs(const GemvArgs& a, size_t smem, int nslabs, cudaStream_t st, bool pdl) {
-    static size_t opted = 40 * 1024;  // static shared memory counts against the 48 KB default too; only ever raised
-    if (smem > opted) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        opted = smem;
-    }
-    if (CL && a.cluster > 8) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<M, CL, ST>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    {
+        cudaError_t e = ensure_dyn_smem(gemv_bf16_kernel<M, CL, ST>, smem);
+        if (e == cudaSuccess && CL && a.cluster > 8) e = ensure_nonportable_clusters(gemv_bf16_kernel<M, CL, ST>);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
@@ -640,10 +636,13 @@ void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* 
     *rows_per_split = rps;
 }
 
+// Asked of the current device every time (an occupancy query, no launch): engines on different GPUs of one
+// process each get their own answer.
 int gemv_max_cluster() {
-    static int cached = 0;
-    if (cached) return cached;
-    cudaFuncSetAttribute(gemv_bf16_kernel<1, true, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (ensure_nonportable_clusters(gemv_bf16_kernel<1, true, false>) != cudaSuccess) {
+        cudaGetLastError();
+        return 8;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(16);
     cfg.blockDim = dim3(GEMV_THREADS);
@@ -658,8 +657,7 @@ int gemv_max_cluster() {
     int n = 0;
     cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemv_bf16_kernel<1, true, false>, &cfg);
     if (e != cudaSuccess) cudaGetLastError();
-    cached = (e == cudaSuccess && n >= 4) ? 16 : 8;
-    return cached;
+    return (e == cudaSuccess && n >= 4) ? 16 : 8;
 }
 
 cudaError_t launch_gemv_bf16(const GemvArgs& a, int M, cudaStream_t st, bool pdl) {
@@ -700,13 +698,16 @@ void* g_noalloc_addr[kNoAllocMaxDevices];
 std::atomic<int> g_noalloc_ready[kNoAllocMaxDevices];
 std::mutex g_noalloc_mu;
 
-bool on_device(const void* p) {
+// Device (or managed) memory that the GPU `dev` can dereference: a buffer that lives on another GPU is
+// refused, because the kernel would read it without peer access.
+bool on_device(const void* p, int dev) {
     cudaPointerAttributes at;
     if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
-    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+    if (at.type == cudaMemoryTypeManaged) return true;
+    return at.type == cudaMemoryTypeDevice && at.device == dev;
 }
 }  // namespace
 
@@ -720,8 +721,8 @@ extern "C" HM_API int hm_gemv_bf16_noalloc(const float* x, const void* w_bf16, i
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return set_global_error(HM_ERR_CUDA, "hm_gemv_bf16_noalloc: no CUDA device available");
     if (dev < 0 || dev >= kNoAllocMaxDevices) return set_global_error(HM_ERR_UNSUPPORTED, "hm_gemv_bf16_noalloc: device index beyond 63");
-    if (!on_device(x) || !on_device(w_bf16) || !on_device(y))
-        return set_global_error(HM_ERR_INVALID, "hm_gemv_bf16_noalloc: x, w and y must be device pointers (staging host buffers would need an allocation)");
+    if (!on_device(x, dev) || !on_device(w_bf16, dev) || !on_device(y, dev))
+        return set_global_error(HM_ERR_INVALID, "hm_gemv_bf16_noalloc: x, w and y must be device pointers on the current device (staging host buffers would need an allocation)");
 
     const int nslabs = (N + SLAB - 1) / SLAB;
     int sms = 148;

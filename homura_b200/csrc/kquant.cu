@@ -21,6 +21,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "launch_attrs.h"
 #include "kquant.h"
 
 namespace hm {
@@ -396,11 +397,9 @@ cudaError_t launch_k3(const KQuantArgs& a, cudaStream_t st, bool pdl) {
     const size_t nbs = (size_t)a.kb_per_split;
     const size_t smem = (size_t)M * nbs * 256 * (ACTQ ? 1 : 4) + 4 * (size_t)M * nbs + 4 * (size_t)M * nbs * 16 + 4 * (size_t)8 * M * 32 + (CL ? 4 * (size_t)a.ksplit * M * 32 : 0);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    static size_t opted = 40 * 1024;
-    if (smem > opted) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kquant_kernel<M, ACTQ, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = ensure_dyn_smem(gemv_kquant_kernel<M, ACTQ, CL>, smem);
         if (e != cudaSuccess) return e;
-        opted = smem;
     }
     const int tiles = (a.N + 31) / 32;
     cudaLaunchConfig_t cfg = {};

@@ -38,11 +38,11 @@ __device__ __forceinline__ bool mb_wait_cluster(uint64_t* b, uint32_t parity, in
     return true;
 }
 // Bounded wait; on overrun raises *err and returns false (callers skip the work that needed the data).
-__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* err, volatile int* abort_flag) {
+__device__ __forceinline__ bool mb_wait_limit(uint64_t* b, uint32_t parity, int* err, volatile int* abort_flag, unsigned long long limit) {
     unsigned long long it = 0;
     while (!mb_try(b, parity)) {
         if (*abort_flag) return false;
-        if (++it > MB_SPIN_LIMIT) {
+        if (++it > limit) {
             *abort_flag = 1;
             if (err) atomicExch(err, 2);
             return false;
@@ -50,6 +50,7 @@ __device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* err, 
     }
     return true;
 }
+__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* err, volatile int* abort_flag) { return mb_wait_limit(b, parity, err, abort_flag, MB_SPIN_LIMIT); }
 __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
 }

@@ -1,6 +1,7 @@
 // Small kernels around the projections: weight re-layout at load, embedding gather, argmax
 // finish, standalone RMSNorm / QK-norm+RoPE, KV row access and dtype conversion.
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 namespace hm {
 namespace {
@@ -326,6 +327,27 @@ inline unsigned grid_for(size_t n, int block) {
     return (unsigned)(g > 148u * 16u ? 148u * 16u : (g ? g : 1));
 }
 
+// Self-test of the give-up path every bounded wait in this library takes.  One CTA: a real 16-byte bulk copy
+// completes on barrier A (waited for, so nothing is in flight when the CTA returns); barrier B is armed for 16
+// bytes that nobody sends, and its wait runs out after `limit` polls, raises the error word and returns.
+__global__ void bounded_wait_probe_kernel(const void* src16, int* err_flag, unsigned long long limit, int* landed) {
+    __shared__ __align__(16) unsigned char buf[16];
+    __shared__ uint64_t bar_a, bar_b;
+    __shared__ volatile int s_abort;
+    if (threadIdx.x == 0) {
+        mb_init(&bar_a, 1);
+        mb_init(&bar_b, 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mb_expect_tx(&bar_a, 16);
+        bulk_copy(buf, src16, 16, &bar_a);
+        mb_expect_tx(&bar_b, 16);  // never completed
+        const bool a_ok = mb_wait_limit(&bar_a, 0, nullptr, &s_abort, MB_SPIN_LIMIT);
+        if (landed) *landed = a_ok ? 1 : 0;
+        if (a_ok) mb_wait_limit(&bar_b, 0, err_flag, &s_abort, limit);
+    }
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, bool pdl, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -391,6 +413,10 @@ cudaError_t launch_post_qkv(const float* qkv, int M, int heads, int kv_heads, in
     if (hd != 64 && hd != 128) return cudaErrorInvalidValue;
     const int warps = M * (heads + 2 * kv_heads);
     return launch_pdl(post_qkv_kernel, dim3((warps + 3) / 4), dim3(128), st, pdl, qkv, M, heads, kv_heads, hd, has_qk_norm, q_norm_w, k_norm_w, eps, rope_cos, rope_sin, row_pos, row_seq, kv, q_out);
+}
+cudaError_t launch_bounded_wait_probe(const void* src16, int* err_flag, unsigned long long limit, int* landed, cudaStream_t st) {
+    bounded_wait_probe_kernel<<<1, 32, 0, st>>>(src16, err_flag, limit, landed);
+    return cudaGetLastError();
 }
 cudaError_t launch_silu_mul(const float* gate_up, int M, int I, float* act, cudaStream_t st, bool pdl) {
     return launch_pdl(silu_mul_kernel, dim3(grid_for((size_t)M * I, 256)), dim3(256), st, pdl, gate_up, M, I, act);

@@ -17,6 +17,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "launch_attrs.h"
 
 namespace hm {
 
@@ -281,8 +282,8 @@ template <int M, bool Q4, bool CL>
 cudaError_t launch_q3(const QuantArgs& a, cudaStream_t st, bool pdl) {
     const size_t smem = sizeof(float) * ((size_t)M * a.kb_per_split * 32 + 8 * M * 32 + (CL ? (size_t)a.ksplit * M * 32 : 0));
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    if (smem > 40 * 1024) {  // static shared memory counts against the 48 KB default too
-        cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<M, Q4, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = ensure_dyn_smem(gemv_quant_kernel<M, Q4, CL>, smem);
         if (e != cudaSuccess) return e;
     }
     const int tiles = (a.N + 31) / 32;

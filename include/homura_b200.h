@@ -48,10 +48,7 @@ enum hm_dtype { HM_F32 = 0, HM_BF16 = 1, HM_F16 = 2, HM_Q8_0 = 3, HM_Q4_0 = 4, H
 /* Weight layouts accepted by the standalone projection kernels. */
 enum hm_layout {
     HM_LAYOUT_KN = 0,      /* row-major [K, N]: Homura's matmul layout after load (src/hf/weights.rs:304-381) */
-    HM_LAYOUT_SLAB128 = 1, /* [ceil(N/128)][K][128]: the engine's streaming layout (see hm_pack_bf16_slabs) */
-    HM_LAYOUT_COLS8 = 2    /* [ceil(N/8)][K][8]: groups of 8 output columns, the decode layout of the layer projections
-                              (see hm_pack_bf16_cols8); every CTA owns whole columns, M <= 8, shapes whose share of one
-                              CTA per SM does not fit shared memory are HM_ERR_UNSUPPORTED */
+    HM_LAYOUT_SLAB128 = 1  /* [ceil(N/128)][K][128]: the engine's streaming layout (see hm_pack_bf16_slabs) */
 };
 
 /* Mirror of TransformerConfig, src/hf/config.rs:11-38.  num_key_value_heads / head_dim are
@@ -178,6 +175,13 @@ typedef struct hm_kernel_stat {
     uint64_t bytes_per_step;
 } hm_kernel_stat;
 HM_API int hm_profile_decode(hm_engine* e, int steps, hm_kernel_stat* out, int cap, int* n_out);
+/* Failure-path self-test (no counterpart in the reference, whose CPU kernels never wait on hardware): queues
+ * a one-CTA kernel on the engine's stream whose mbarrier is armed for bytes that nobody sends; its bounded
+ * wait gives up after 20000 polls and raises the engine's device error word.  The NEXT pass on this engine
+ * (hm_prefill, hm_decode_step, ...) therefore returns HM_ERR_TIMEOUT, and the call after that is clean
+ * again -- which is how a host learns that every device-side wait of this library is bounded and how the
+ * status surfaces.  Nothing faults or hangs; the context stays usable. */
+HM_API int hm_selftest_expire_wait(hm_engine* e);
 /* The engine's stream as a cudaStream_t, for callers that record their own events. */
 HM_API void* hm_engine_stream(hm_engine* e);
 /* Number of kernel launches one decode step of this engine issues. */
@@ -206,8 +210,6 @@ HM_API int hm_gemv_bf16(const float* x, const void* w_bf16, int layout, int M, i
 HM_API int hm_gemv_bf16_noalloc(const float* x, const void* w_bf16, int layout, int M, int K, int N, float* y, void* stream);
 /* Re-layout row-major [K,N] bf16 into HM_LAYOUT_SLAB128 (dst holds ceil(N/128)*K*128 elements). */
 HM_API int hm_pack_bf16_slabs(const void* w_kn, int K, int N, void* dst, void* stream);
-/* Re-layout row-major [K,N] bf16 into HM_LAYOUT_COLS8 (dst holds ceil(N/8)*K*8 elements). */
-HM_API int hm_pack_bf16_cols8(const void* w_kn, int K, int N, void* dst, void* stream);
 /* The same mixed matmul for 1 <= M <= 64 rows on the 5th-generation tensor cores (tcgen05 with the
  * accumulator in tensor memory).  w_tc is the weight packed by hm_pack_bf16_tc.  f32 activations are
  * split into three bf16 terms inside the kernel, so results agree with the f32 x bf16 product of

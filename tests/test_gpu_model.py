@@ -309,43 +309,6 @@ def test_error_statuses(hm):
     assert e.value.status == hm.HM_ERR_UNSUPPORTED
 
 
-def test_persistent_decode_kernel_matches_oracle(hm, oracle, monkeypatch):
-    # HM_PERSISTENT=1 selects the single-launch persistent decode kernel (bulk-copy weight ring,
-    # flag-carrying exchange buffers instead of grid barriers) for batch-1 bf16 models.
-    monkeypatch.setenv("HM_PERSISTENT", "1")
-    for name in ("qwen2", "qwen3", "llama"):
-        cfg, d = make_hf(name)
-        om = oracle.OracleModel.from_hf_dir(d, max_seq_len=128)
-        m = hm.HfModel.load(d)
-        m.init_kv_cache(128)
-        assert m.launches_per_step() == 1
-        ids = synth.prompt_ids(5, 32, cfg.vocab_size)
-        want = om.generate_greedy(ids, 64)
-        assert m.generate_ids(ids, 64, hm.SamplingConfig.greedy()) == want
-        om.reset()
-        m.reset_kv_cache()
-        tok_o, _ = om.prefill(ids[:20])
-        assert m.prefill(ids[:20]) == tok_o
-        lo = om.decode_step(tok_o)
-        lg, nxt = m.decode_step([tok_o])
-        assert_logits_close(lg[0], lo)
-        assert int(nxt[0]) == oracle.argmax(lo)
-        m.close()
-    # bf16 pages through the persistent kernel: teacher-forced logits
-    cfg, d = make_hf("qwen2")
-    om = oracle.OracleModel.from_hf_dir(d, max_seq_len=64)
-    m = hm.HfModel.load(d)
-    m.init_kv_cache(64, kv_dtype=hm.DType.BF16)
-    ids = synth.prompt_ids(4, 24, cfg.vocab_size)
-    cur, _ = om.prefill(ids)
-    m.prefill(ids)
-    for _ in range(10):
-        lo = om.decode_step(cur)
-        lg, _ = m.decode_step([cur])
-        assert_logits_close(lg[0], lo, scale_tol=False)
-        cur = oracle.argmax(lo)
-
-
 # ---- passes over more than 8 rows: the tensor-core projections ---------------------------------
 
 
