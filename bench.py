@@ -19,6 +19,10 @@ Prints ONE JSON line (rank 0):
   roofline   the projection kernel (all weight streaming of a step): algorithmic bytes / device
              time of its launches (CUDA events around graph replays of each kernel class, taken
              live after the timed region), against the measured HBM copy bandwidth;
+  e2e_logits the same per-token call with the [vocab] f32 logits copied back every step, which is what
+             the reference's trait returns (decode_step -> Vec<f32>, src/hf/model.rs:359-371);
+  c5         the batched configuration (Qwen2.5-1.5B architecture, 64 sequences per GPU, 512-token
+             prompts) timed the same way on bf16 and on f32 KV pages, with its prefill rate;
   cpu_baseline  the CPU oracle (a restatement of Homura's CPU path) on a bounded sample.
 """
 from __future__ import annotations
@@ -44,6 +48,12 @@ PROMPT_LEN = 128
 SEED = 20251
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0
+# DRAM bytes of the 97 projection launches of one headline decode step, summed from the ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum per launch) summarised in the file below; the algorithmic
+# figure is 987.9 MB, so every weight byte is read once.
+HEADLINE_PROJECTION_DRAM_BYTES_PER_STEP = 997.0e6
+HEADLINE_PROJECTION_LAUNCHES = 97
+TRAFFIC_SOURCE = "profiles/ncu_full_gemv_lmhead_and_small_kernels.md"
 
 
 def log(*a):
@@ -178,8 +188,15 @@ def cpu_sample(d, cfg, steps, warmup, prompt_len):
     except Exception:
         ncores = os.cpu_count() or 1
     os.environ["OMP_NUM_THREADS"] = str(ncores)
+    os.environ.setdefault("OMP_PROC_BIND", "close")
+    os.environ.setdefault("OMP_PLACES", "cores")
     import oracle as orc
     from homura_b200 import synth
+
+    try:
+        orc.use_native_build()  # -march=native on the machine that runs the baseline
+    except RuntimeError:
+        pass  # already loaded in this process
 
     n = prompt_len + warmup + steps + 1
     om = orc.OracleModel.from_hf_dir(d, max_seq_len=n) if os.path.isdir(d) else orc.OracleModel.from_gguf(d, max_seq_len=n)
@@ -194,8 +211,19 @@ def cpu_sample(d, cfg, steps, warmup, prompt_len):
     return steps / dt, dt, orc.num_threads()
 
 
+def headline_config(world, kv_dtype, weight_mb):
+    """The `config` object of the headline workload: identical for this engine and for the reference arm."""
+    _, _, _, wl_desc = WORKLOADS[HEADLINE]
+    return {
+        "workload": wl_desc + f", {PROMPTS[HEADLINE]}-token prompt, greedy decode",
+        "kv_cache": f"paged, 16 tokens/page, {kv_dtype}", "l2": f"inputs larger than L2: {weight_mb:.0f} MB of weights are streamed once per step (L2 is 126 MB)",
+        "parallelism": f"replicas x{world}, independent sequences, no collective on the token path", "seed": SEED,
+    }
+
+
 def run_reference(args):
-    """The reference's CPU implementation of the path = the oracle port, timed on host cores."""
+    """The reference's CPU implementation of the path = the oracle port, timed on host cores: same checkpoint,
+    same 128-token prompt, same warm-up and step counts as this engine's arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -203,18 +231,57 @@ def run_reference(args):
 
     cfg = synth.QWEN25_05B
     d = model_dir(cfg, SEED, 0, 1)
-    steps, warmup = min(args.steps, 64), min(args.warmup, 3)
-    prompt = 8  # bounded sample: a short prompt keeps the CPU prefill to about a second
+    steps, warmup = args.steps, max(args.warmup, 3)
+    prompt = PROMPTS[HEADLINE]
     tps, dt, threads = cpu_sample(d, cfg, steps, warmup, prompt)
-    sample = f"{steps} greedy decode steps after an {prompt}-token prompt, same seeded Qwen2.5-0.5B-architecture weights (bf16), {threads} OpenMP threads"
+    sample = f"{steps} greedy decode steps after a {prompt}-token prompt and {warmup} warm-up steps, same seeded weights (bf16), {threads} OpenMP threads (OMP_PROC_BIND=close), oracle built -march=native"
     out = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
         "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over bf16 weights",
-        "data": "synthetic", "config": {"workload": "Qwen2.5-0.5B-architecture batch-1 greedy decode (CPU oracle = restated Homura CPU path, not Homura's binary)"},
+        "data": "synthetic", "config": headline_config(args.gpus, "f32", 987_922_432 / 1e6),
+        "reference_kind": "CPU oracle = restated Homura CPU path (the reference itself needs Rust + LLVM 21, absent here)",
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     emit(out)
+
+
+def run_c5(hm, synth, rank, world, local, barrier, vmax, K, W, peak):
+    """The batched configuration: Qwen2.5-1.5B architecture, 64 sequences per GPU, 512-token prompts, greedy
+    decode, on bf16 and on f32 KV pages.  Every rank runs its own 64 sequences on its replica."""
+    name = "qwen25-15b-x64"
+    cfg_name, fmt, B, wl_desc = WORKLOADS[name]
+    cfg = getattr(synth, cfg_name)
+    PL = PROMPTS[name]
+    d = model_dir(cfg, SEED, rank, world, name, fmt)
+    barrier()
+    m = hm.HfModel.load_with_dtype(d, hm.DType.BF16, device=local)
+    prompts = [synth.prompt_ids(SEED + 1000 + rank * B + b, PL, cfg.vocab_size) for b in range(B)]
+    max_seq = PL + W + K + 8 + 24
+    out = {"workload": wl_desc + f", {PL}-token prompts, greedy decode", "sequences_per_gpu": B, "steps": K, "warmup": W, "weight_bytes_per_step": m.weight_bytes(), "pages": {}}
+    for kv in ("bf16", "f32"):
+        m.init_kv_cache(max_seq, batch=B, kv_dtype=hm.DType.BF16 if kv == "bf16" else hm.DType.F32)
+        barrier()
+        t = time.perf_counter()
+        first = [m.prefill(prompts[b], seq=b) for b in range(B)]
+        pf_s = vmax(time.perf_counter() - t)
+        m.decode_greedy_n(first, 0)
+        barrier()
+        ms = vmax(m.time_decode(W, K))
+        barrier()
+        prof = m.profile_decode(4)
+        T_avg = PL + W + (K + 1) / 2.0
+        kv_tok = cfg.num_hidden_layers * 2 * cfg.kv_dim * (2 if kv == "bf16" else 4)
+        step_bytes = m.weight_bytes() + B * (kv_tok * T_avg + kv_tok)
+        gbs = step_bytes / (ms / K * 1e-3) / 1e9
+        out["pages"][kv] = {
+            "tok_per_s": world * B * K / (ms / 1e3), "ms_per_step": ms / K, "bytes_per_step": step_bytes, "achieved_gbs": gbs, "frac_of_measured": gbs / peak,
+            "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "prefill_tok_per_s": world * B * PL / pf_s,
+            "kernels": [{"name": p["name"], "launches": p["launches_per_step"], "us": round(1e3 * p["ms_per_step"], 2), "MB": round(p["bytes_per_step"] / 1e6, 3)} for p in prof],
+        }
+    out["launches_per_step"] = m.launches_per_step()
+    m.close()
+    return out
 
 
 def main():
@@ -225,6 +292,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kv-dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-c5", action="store_true", help="skip the batched Qwen2.5-1.5B x 64 block of the headline line")
     ap.add_argument("--prompt-len", type=int, default=None, help="prompt tokens before the timed decode steps (default: the workload's own, 128 for the headline)")
     ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS), help="default: the headline workload; the others are the remaining measured configurations")
     ap.add_argument("--device-only", action="store_true", help="only the device-timed region: skips the end-to-end loop, the per-kernel pass and the CPU baseline (for profiler runs)")
@@ -247,7 +315,7 @@ def main():
     m = hm.HfModel.load_with_dtype(d, hm.DType.BF16, device=local) if fmt == "bf16" else hm.HfModel.load_gguf(d, device=local)
     kv_dtype = hm.DType.F32 if args.kv_dtype == "f32" else hm.DType.BF16
     PL = args.prompt_len if args.prompt_len is not None else PROMPTS[args.workload]
-    max_seq = PL + 2 * (W + K) + 24
+    max_seq = PL + 3 * (W + K) + 24
     if max_seq > cfg.max_position_embeddings:
         raise SystemExit(f"--steps/--warmup need {max_seq} positions; the checkpoint has {cfg.max_position_embeddings}")
     m.init_kv_cache(max_seq, batch=B, kv_dtype=kv_dtype)
@@ -289,6 +357,14 @@ def main():
     e2e_s = time.perf_counter() - t
     barrier()
     e2e_tps = world * B * K / vmax(e2e_s)
+    # the reference trait's decode_step returns the logits (Vec<f32> of vocab entries): the same loop with that copy
+    t = time.perf_counter()
+    for _ in range(K):
+        _, nxt = m.decode_step(cur, want_logits=True)
+        cur = [int(v) for v in nxt]
+    e2e_lg_s = time.perf_counter() - t
+    barrier()
+    e2e_lg_tps = world * B * K / vmax(e2e_lg_s)
 
     # ---- per-kernel-class device times (launch by launch, CUDA events) ----
     prof = m.profile_decode(8)
@@ -298,13 +374,20 @@ def main():
     proj_launches = sum(p["launches_per_step"] for p in proj)
     peak, peak_kind = measured_peak()
     achieved = proj_bytes / (proj_ms * 1e-3) / 1e9 if proj_ms > 0 else 0.0
+    weight_bytes, launches_per_step = m.weight_bytes(), m.launches_per_step()
+
+    c5 = None
+    if args.workload == HEADLINE and not args.no_c5:
+        m.close()
+        m = None
+        c5 = run_c5(hm, synth, rank, world, local, barrier, vmax, K, W, peak)
 
     close()
     if rank != 0:
         return
     T_avg = PL + W + (K + 1) / 2.0
     kv_bytes_tok = cfg.num_hidden_layers * 2 * cfg.kv_dim * (4 if args.kv_dtype == "f32" else 2)
-    step_bytes = m.weight_bytes() + B * (kv_bytes_tok * T_avg + kv_bytes_tok)  # weights once per step, every sequence's cache
+    step_bytes = weight_bytes + B * (kv_bytes_tok * T_avg + kv_bytes_tok)  # weights once per step, every sequence's cache
     step_gbs = step_bytes * (tok_per_s / world / B) / 1e9
     if fmt != "bf16":
         kern = "gemv_kquant_kernel<1> (Q4_K/Q6_K projections: Q8_K activations, dp4a; LM head in f32)" if fmt == "q4_k_m" else "gemv_quant_kernel<1> (Q8_0/Q4_0 dequantising projections; LM head included)"
@@ -314,22 +397,25 @@ def main():
         kern = "gemv_bf16_kernel<1> (QKV, O, gate/up, down and LM-head projections)"
     # DRAM bytes per projection launch from the ncu capture summarised under profiles/ (headline workload
     # only): 997.0 MB summed over the 97 projection launches of a step, against 987.9 MB algorithmic.
-    traffic = 997.0e6 / 97 if (args.workload == HEADLINE and proj_launches == 97) else None
+    known_traffic = args.workload == HEADLINE and proj_launches == HEADLINE_PROJECTION_LAUNCHES
+    traffic = HEADLINE_PROJECTION_DRAM_BYTES_PER_STEP / HEADLINE_PROJECTION_LAUNCHES if known_traffic else None
     out = {
         "metric": "decode_tokens_per_s", "value": tok_per_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 accumulate over bf16 weights" if fmt == "bf16" else f"f32 accumulate over {fmt} blocks", "data": "synthetic",
-        "config": {
+        "config": headline_config(world, args.kv_dtype, weight_bytes / 1e6) if (args.workload == HEADLINE and PL == PROMPTS[HEADLINE]) else {
             "workload": wl_desc + f", {PL}-token prompt, greedy decode",
-            "kv_cache": f"paged, 16 tokens/page, {args.kv_dtype}", "l2": f"inputs larger than L2: {m.weight_bytes() / 1e6:.0f} MB of weights are streamed once per step (L2 is 126 MB)",
+            "kv_cache": f"paged, 16 tokens/page, {args.kv_dtype}", "l2": f"inputs larger than L2: {weight_bytes / 1e6:.0f} MB of weights are streamed once per step (L2 is 126 MB)",
             "parallelism": f"replicas x{world}, independent sequences, no collective on the token path", "seed": SEED,
         },
         "clocks": clocks,
         "e2e": {"value": e2e_tps, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "api": "hm_decode_step (host token ids in, greedy next token ids out, one stream sync per step)"},
-        "gpu_launches": m.launches_per_step() * K,
+        "e2e_logits": {"value": e2e_lg_tps, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B + 4 * B * cfg.vocab_size,
+                       "api": "hm_decode_step with the [vocab] f32 logits returned (the reference trait's decode_step -> Vec<f32>)"},
+        "gpu_launches": launches_per_step * K,
         "roofline": {
             "bound": "hbm", "kernel": kern, "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": traffic,
+            "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": traffic, "traffic_source": TRAFFIC_SOURCE if known_traffic else None,
             "per_launch": {"algorithmic_bytes": proj_bytes / max(proj_launches, 1), "device_us": 1e3 * proj_ms / max(proj_launches, 1)},
             "timing": "CUDA events on the engine's stream around graph replays of each kernel class (8 steps each), run after the timed region",
             "launches_per_step": proj_launches, "algorithmic_bytes_per_step": proj_bytes, "device_ms_per_step": proj_ms,
@@ -338,8 +424,11 @@ def main():
         "kernels": [{"name": p["name"], "launches": p["launches_per_step"], "us": round(1e3 * p["ms_per_step"], 2), "MB": round(p["bytes_per_step"] / 1e6, 3),
                      "GBs": round(p["bytes_per_step"] / (p["ms_per_step"] * 1e-3) / 1e9, 1) if p["ms_per_step"] > 0 else None} for p in prof],
     }
+    if c5 is not None:
+        out["c5"] = c5
     if world == 1 and not args.no_cpu_baseline:
-        m.close()
+        if m is not None:
+            m.close()
         steps_c, prompt_c = (32, 8) if args.workload == HEADLINE else (12, 4)
         tps, dt, threads = cpu_sample(d, cfg, steps_c, 2, prompt_c)
         out["cpu_baseline"] = {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",

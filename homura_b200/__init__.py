@@ -111,12 +111,14 @@ SIGNATURES = {
     "hm_weight_bytes": (_i32, [_vp, C.POINTER(C.c_uint64)]),
     "hm_checkpoint_info": (_i32, [C.c_char_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "hm_kv_alloc": (_i32, [_vp, _i32, _i32, _i32, _i32]),
+    "hm_kv_free": (_i32, [_vp]),
     "hm_kv_reset": (_i32, [_vp, _i32]),
     "hm_kv_len": (_i32, [_vp, _i32, _i32p]),
     "hm_kv_append": (_i32, [_vp, _i32, _i32, _vp, _vp, _i32, _i32]),
     "hm_kv_view": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "hm_prefill": (_i32, [_vp, _i32, _vp, _i32, _vp, _u32p]),
     "hm_decode_step": (_i32, [_vp, _vp, _vp, _vp]),
+    "hm_decode_step_sampled": (_i32, [_vp, _vp, C.POINTER(_Sampling), _vp, _vp, _vp]),
     "hm_generate": (_i32, [_vp, _i32, _vp, _i32, _i32, C.POINTER(_Sampling), _vp, _i32p]),
     "hm_decode_greedy_n": (_i32, [_vp, _vp, _i32, _vp]),
     "hm_sample_token": (_i32, [_vp, _i32, C.POINTER(_Sampling), _vp, _i32, C.POINTER(C.c_uint64), _u32p]),
@@ -142,6 +144,8 @@ SIGNATURES = {
     "hm_dev_free": (_i32, [_vp]),
     "hm_dev_copy": (_i32, [_vp, _vp, C.c_size_t]),
     "hm_dev_sync": (_i32, []),
+    "hm_dev_set": (_i32, [_i32]),
+    "hm_dev_mem_info": (_i32, [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
 }
 
 _lib = None
@@ -291,7 +295,7 @@ def sample_token(logits, config: SamplingConfig, generated_ids: Sequence[int], r
 
 
 def sample_token_device(logits, config: SamplingConfig, generated_ids: Sequence[int], rng_state: int):
-    """The same sampler as one GPU kernel (temperature > 0, 1 <= top_k <= 1024).  Returns (token, new rng state)."""
+    """The same sampler as one GPU kernel, every setting.  Returns (token, new rng state)."""
     lib = load_library()
     lg = np.ascontiguousarray(logits, dtype=np.float32)
     gen = np.ascontiguousarray(generated_ids, dtype=np.uint32)
@@ -381,6 +385,10 @@ class HfModel:
 
     # -- KV cache --
     def init_kv_cache(self, max_seq_len: int, batch: int = 1, kv_dtype: DType = DType.F32, page_tokens: int = 16):
+        """init_kv_cache (src/hf/model.rs:221-229).  Calling it again replaces the cache."""
+        if self.batch:
+            _check(self._lib.hm_kv_free(self._h), self._h)
+            self.batch = 0
         _check(self._lib.hm_kv_alloc(self._h, batch, max_seq_len, page_tokens, int(kv_dtype)), self._h)
         self.batch, self.max_seq_len = batch, max_seq_len
 
@@ -426,6 +434,18 @@ class HfModel:
         logits = np.empty((self.batch, self._config.vocab_size), np.float32) if want_logits else None
         nxt = np.empty(self.batch, np.uint32)
         _check(self._lib.hm_decode_step(self._h, _ptr(t), _ptr(logits), _ptr(nxt)), self._h)
+        return logits, nxt
+
+    def decode_step_sampled(self, tokens, sampling: "SamplingConfig", rng_states, want_logits: bool = False):
+        """decode_step + sample_token for every sequence.  rng_states: one xorshift64 word per sequence
+        (numpy uint64 array, updated in place).  Returns ([batch, vocab] logits or None, sampled tokens)."""
+        t = np.ascontiguousarray(np.atleast_1d(tokens), dtype=np.uint32)
+        if t.size != self.batch or rng_states.size != self.batch or rng_states.dtype != np.uint64:
+            raise HomuraError(HM_ERR_INVALID, f"decode_step_sampled wants {self.batch} tokens and uint64 RNG words")
+        logits = np.empty((self.batch, self._config.vocab_size), np.float32) if want_logits else None
+        nxt = np.empty(self.batch, np.uint32)
+        sc = sampling._to_c()
+        _check(self._lib.hm_decode_step_sampled(self._h, _ptr(t), C.byref(sc), _ptr(rng_states), _ptr(logits), _ptr(nxt)), self._h)
         return logits, nxt
 
     def decode_greedy_n(self, first_tokens, steps: int) -> np.ndarray:
@@ -649,3 +669,15 @@ def attn_decode_paged(q, k_pages: DeviceBuffer, v_pages: DeviceBuffer, kv_dtype:
 
 def dev_sync():
     _check(load_library().hm_dev_sync())
+
+
+def dev_set(device: int):
+    """Make `device` current on this thread for DeviceBuffer and the standalone kernels."""
+    _check(load_library().hm_dev_set(device))
+
+
+def dev_mem_info():
+    """(free, total) bytes of the current device."""
+    f, t = C.c_size_t(0), C.c_size_t(0)
+    _check(load_library().hm_dev_mem_info(C.byref(f), C.byref(t)))
+    return int(f.value), int(t.value)

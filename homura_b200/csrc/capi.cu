@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -346,34 +347,55 @@ static int load_views(Engine* eng, const std::vector<TensorView>& views, std::st
     return HM_OK;
 }
 
+// model.safetensors, else the shards named by model.safetensors.index.json in file-name order, each once
+// (src/hf/model.rs:86-127).
+static int safetensors_files(const std::string& dir, std::vector<std::string>* files, std::string* err) {
+    MappedFile probe;
+    std::string e2;
+    if (probe.open(dir + "/model.safetensors", &e2)) {
+        files->push_back(dir + "/model.safetensors");
+        return HM_OK;
+    }
+    MappedFile idx;
+    if (!idx.open(dir + "/model.safetensors.index.json", &e2)) {
+        *err = "no model.safetensors or model.safetensors.index.json found in " + dir;
+        return HM_ERR_IO;
+    }
+    Json j;
+    if (!json_parse((const char*)idx.data(), idx.size(), &j, err)) return HM_ERR_IO;
+    const Json* wm = j.get("weight_map");
+    if (!wm || wm->kind != Json::Obj) {
+        *err = "model.safetensors.index.json missing weight_map";
+        return HM_ERR_IO;
+    }
+    for (auto& kv : wm->obj)
+        if (kv.second.kind == Json::Str) files->push_back(dir + "/" + kv.second.str);
+    std::sort(files->begin(), files->end());
+    files->erase(std::unique(files->begin(), files->end()), files->end());
+    if (files->empty()) {
+        *err = "model.safetensors.index.json names no shard";
+        return HM_ERR_IO;
+    }
+    return HM_OK;
+}
+
 int hm_model_load(const char* model_dir, int weight_dtype, int device, hm_engine** out) {
     if (!model_dir || !out) return gfail(HM_ERR_INVALID, "hm_model_load: null argument");
-    if (weight_dtype != HM_BF16)
-        return gfail(HM_ERR_UNSUPPORTED, "hm_model_load: only HM_BF16 projection weights are supported (Homura's --dtype bf16 path)");
+    // HM_F32 is HfModel::load's default (src/hf/model.rs:37-39): the reference widens the file's weights to f32 and
+    // multiplies f32 x f32.  For a bf16 checkpoint the widened values are the bf16 values, so keeping them as bf16
+    // gives the same products; files whose projections really are f32 / f16 are refused when their first
+    // projection tensor is loaded (an f32-weight streaming kernel is not built).
+    if (weight_dtype != HM_BF16 && weight_dtype != HM_F32)
+        return gfail(HM_ERR_UNSUPPORTED, "hm_model_load: weight_dtype must be HM_BF16 or HM_F32 (Homura's --dtype bf16 / f32)");
     const std::string dir(model_dir);
     hm_config cfg;
     std::string err;
     if (!parse_config_json(dir + "/config.json", &cfg, &err)) return gfail(HM_ERR_IO, err);
     NEED_DEVICE();
-    // model.safetensors, else the shards named by model.safetensors.index.json (src/hf/model.rs:86-127)
     std::vector<std::string> files;
     {
-        MappedFile probe;
-        std::string e2;
-        if (probe.open(dir + "/model.safetensors", &e2)) {
-            files.push_back(dir + "/model.safetensors");
-        } else {
-            MappedFile idx;
-            if (!idx.open(dir + "/model.safetensors.index.json", &e2)) return gfail(HM_ERR_IO, "no model.safetensors or index found in " + dir);
-            Json j;
-            if (!json_parse((const char*)idx.data(), idx.size(), &j, &err)) return gfail(HM_ERR_IO, err);
-            const Json* wm = j.get("weight_map");
-            if (!wm || wm->kind != Json::Obj) return gfail(HM_ERR_IO, "model.safetensors.index.json missing weight_map");
-            for (auto& kv : wm->obj)
-                if (kv.second.kind == Json::Str) files.push_back(dir + "/" + kv.second.str);
-            std::sort(files.begin(), files.end());
-            files.erase(std::unique(files.begin(), files.end()), files.end());
-        }
+        const int frc = safetensors_files(dir, &files, &err);
+        if (frc) return gfail(frc, err);
     }
     Engine* eng = nullptr;
     int rc = Engine::create(cfg, device, &eng, &err);
@@ -454,6 +476,7 @@ int hm_checkpoint_info(const char* path, char* buf, size_t cap, size_t* needed) 
     hm_config cfg;
     std::vector<TensorView> views;
     MappedFile mf;
+    std::vector<std::unique_ptr<MappedFile>> shards;  // the views point into these
     GgufFile g;
     const bool is_gguf = p.size() > 5 && p.compare(p.size() - 5, 5, ".gguf") == 0;
     if (is_gguf) {
@@ -465,10 +488,18 @@ int hm_checkpoint_info(const char* path, char* buf, size_t cap, size_t* needed) 
     } else {
         fmt = "safetensors";
         if (!parse_config_json(p + "/config.json", &cfg, &err)) return gfail(HM_ERR_IO, err);
-        if (!mf.open(p + "/model.safetensors", &err)) return gfail(HM_ERR_IO, err);
-        if (!parse_safetensors(mf, &views, &err)) return gfail(HM_ERR_IO, err);
+        std::vector<std::string> files;
+        const int frc = safetensors_files(p, &files, &err);
+        if (frc) return gfail(frc, err);
+        for (size_t i = 0; i < files.size(); ++i) {
+            std::vector<TensorView> part;
+            shards.emplace_back(new MappedFile());
+            if (!shards[i]->open(files[i], &err)) return gfail(HM_ERR_IO, err);
+            if (!parse_safetensors(*shards[i], &part, &err)) return gfail(HM_ERR_IO, err);
+            views.insert(views.end(), part.begin(), part.end());
+        }
     }
-    static const char* dn[] = {"F32", "BF16", "F16", "Q8_0", "Q4_0", "I64", "I32", "U8"};
+    static const char* dn[] = {"F32", "BF16", "F16", "Q8_0", "Q4_0", "I64", "I32", "U8", "Q4_K", "Q6_K"};
     std::string o = "{\"format\":\"" + fmt + "\",\"config\":{";
     char tmp[512];
     std::snprintf(tmp, sizeof(tmp),
@@ -487,7 +518,7 @@ int hm_checkpoint_info(const char* path, char* buf, size_t cap, size_t* needed) 
         o += "{\"name\":\"";
         json_escape(t.name, &o);
         o += "\",\"dtype\":\"";
-        o += (t.dtype >= 0 && t.dtype < 8) ? dn[t.dtype] : "UNSUPPORTED";
+        o += (t.dtype >= 0 && t.dtype < 10) ? dn[t.dtype] : "UNSUPPORTED";
         o += "\",\"shape\":[";
         for (size_t i = 0; i < t.shape.size(); ++i) {
             if (i) o += ",";
@@ -504,6 +535,7 @@ int hm_checkpoint_info(const char* path, char* buf, size_t cap, size_t* needed) 
 }
 
 int hm_kv_alloc(hm_engine* e, int batch, int max_seq_len, int page_tokens, int kv_dtype) { return e ? e->impl->kv_alloc(batch, max_seq_len, page_tokens, kv_dtype) : gfail(HM_ERR_INVALID, "null engine"); }
+int hm_kv_free(hm_engine* e) { return e ? e->impl->kv_free() : gfail(HM_ERR_INVALID, "null engine"); }
 int hm_kv_reset(hm_engine* e, int seq) { return e ? e->impl->kv_reset(seq) : gfail(HM_ERR_INVALID, "null engine"); }
 int hm_kv_len(hm_engine* e, int seq, int* out) { return e ? e->impl->kv_len(seq, out) : gfail(HM_ERR_INVALID, "null engine"); }
 int hm_kv_append(hm_engine* e, int seq, int layer, const float* k_rows, const float* v_rows, int n_new, int advance) {
@@ -530,8 +562,6 @@ int hm_sample_token(const float* logits, int n, const hm_sampling* cfg, const ui
 }
 int hm_sample_token_device(const float* logits, int n, const hm_sampling* cfg, const uint32_t* generated, int n_generated, uint64_t* rng_state, uint32_t* out) {
     if (!logits || n < 1 || !cfg || !rng_state || !out || n_generated < 0 || (n_generated > 0 && !generated)) return gfail(HM_ERR_INVALID, "hm_sample_token_device: bad arguments");
-    if (!(cfg->temperature > 0.f) || cfg->top_k < 1 || cfg->top_k > SAMPLER_MAX_K)
-        return gfail(HM_ERR_UNSUPPORTED, "hm_sample_token_device: needs temperature > 0 and 1 <= top_k <= 1024 (use hm_sample_token otherwise)");
     NEED_DEVICE();
     Staging sg(nullptr);
     SamplerArgs a{};
@@ -545,12 +575,42 @@ int hm_sample_token_device(const float* logits, int n, const hm_sampling* cfg, c
     a.scaled = (float*)sg.scratch((size_t)n * 4, false);
     a.count = (int*)sg.scratch((size_t)n * 4, true);
     a.next_tok = (uint32_t*)sg.scratch(4, false);
-    if (!a.logits || !a.rng || !a.scaled || !a.count || !a.next_tok || (n_generated && !a.generated)) return sg.finish(cudaErrorMemoryAllocation);
+    a.overflow = (int*)sg.scratch(4, true);
+    if (!a.logits || !a.rng || !a.scaled || !a.count || !a.next_tok || !a.overflow || (n_generated && !a.generated)) return sg.finish(cudaErrorMemoryAllocation);
     sg.ok(cudaMemcpyAsync(a.rng, rng_state, 8, cudaMemcpyHostToDevice, nullptr));
     cudaError_t ce = launch_sample(a, 1, nullptr);
-    if (ce == cudaSuccess) ce = cudaMemcpyAsync(rng_state, a.rng, 8, cudaMemcpyDeviceToHost, nullptr);
+    int over = 0;
+    uint64_t rng_after = *rng_state;
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(&rng_after, a.rng, 8, cudaMemcpyDeviceToHost, nullptr);
     if (ce == cudaSuccess) ce = cudaMemcpyAsync(out, a.next_tok, 4, cudaMemcpyDeviceToHost, nullptr);
-    return sg.finish(ce);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(&over, a.overflow, 4, cudaMemcpyDeviceToHost, nullptr);
+    const int rc = sg.finish(ce);
+    if (rc != HM_OK) return rc;
+    if (over && cfg->temperature > 0.f) {
+        // the top-p prefix reaches beyond the candidates the kernel gathers (top-k disabled or above 1024 on a
+        // nearly flat row): the kernel left token and RNG untouched and the host sampler finishes the token
+        std::vector<float> lh;
+        std::vector<uint32_t> gh;
+        const float* lp = logits;
+        const uint32_t* gp = generated;
+        if (is_device_ptr(logits)) {
+            lh.resize(n);
+            if (cudaMemcpy(lh.data(), logits, (size_t)n * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return gfail(HM_ERR_CUDA, "hm_sample_token_device: logits read-back failed");
+            lp = lh.data();
+        }
+        if (n_generated && is_device_ptr(generated)) {
+            gh.resize(n_generated);
+            if (cudaMemcpy(gh.data(), generated, (size_t)n_generated * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return gfail(HM_ERR_CUDA, "hm_sample_token_device: history read-back failed");
+            gp = gh.data();
+        }
+        *out = host_sample_token(lp, n, *cfg, gp, n_generated, rng_state);
+        return HM_OK;
+    }
+    *rng_state = rng_after;
+    return HM_OK;
+}
+int hm_decode_step_sampled(hm_engine* e, const uint32_t* tokens, const hm_sampling* sampling, uint64_t* rng_state, float* logits_or_null, uint32_t* next_tokens) {
+    return e ? e->impl->decode_step_sampled(tokens, sampling, rng_state, logits_or_null, next_tokens) : gfail(HM_ERR_INVALID, "null engine");
 }
 int hm_time_decode(hm_engine* e, int warmup, int steps, float* ms_total) { return e ? e->impl->time_decode(warmup, steps, ms_total) : gfail(HM_ERR_INVALID, "null engine"); }
 int hm_profile_decode(hm_engine* e, int steps, hm_kernel_stat* out, int cap, int* n_out) {
@@ -903,6 +963,19 @@ int hm_dev_copy(void* dst, const void* src, size_t nbytes) {
     NEED_DEVICE();
     cudaError_t e = cudaMemcpy(dst, src, nbytes, cudaMemcpyDefault);
     if (e != cudaSuccess) return gfail(HM_ERR_CUDA, std::string("cudaMemcpy: ") + cudaGetErrorString(e));
+    return HM_OK;
+}
+int hm_dev_set(int device) {
+    NEED_DEVICE();
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return gfail(HM_ERR_INVALID, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+    return HM_OK;
+}
+int hm_dev_mem_info(size_t* free_bytes, size_t* total_bytes) {
+    if (!free_bytes || !total_bytes) return gfail(HM_ERR_INVALID, "null argument");
+    NEED_DEVICE();
+    cudaError_t e = cudaMemGetInfo(free_bytes, total_bytes);
+    if (e != cudaSuccess) return gfail(HM_ERR_CUDA, std::string("cudaMemGetInfo: ") + cudaGetErrorString(e));
     return HM_OK;
 }
 int hm_dev_sync(void) {

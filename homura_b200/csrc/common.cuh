@@ -380,6 +380,7 @@ cudaError_t launch_dequant(const uint8_t* blocks, size_t nblocks, int q4, float*
 cudaError_t launch_gemv_quant(const QuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
 // quant plan helpers: PostQKV (src/hf/emitter_quant.rs:800-905) and SiLU*Up (:1078-1099)
 cudaError_t launch_post_qkv(const float* qkv, int M, int heads, int kv_heads, int hd, int has_qk_norm, const float* q_norm_w, const float* k_norm_w, float eps, const float* rope_cos, const float* rope_sin, const int32_t* row_pos, const int32_t* row_seq, const KvDesc& kv, float* q_out, cudaStream_t st, bool pdl);
+cudaError_t launch_hist_set(const uint32_t* tokens, const int32_t* pos, uint32_t* hist, int hist_stride, int batch, cudaStream_t st);
 // one-CTA kernel whose second mbarrier wait runs out after `limit` polls and raises *err_flag to 2 (self-test of the give-up path)
 cudaError_t launch_bounded_wait_probe(const void* src16, int* err_flag, unsigned long long limit, int* landed, cudaStream_t st);
 cudaError_t launch_silu_mul(const float* gate_up, int M, int I, float* act, cudaStream_t st, bool pdl);

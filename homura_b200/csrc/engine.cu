@@ -113,7 +113,7 @@ Engine::~Engine() {
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
-    fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_);
+    fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_); fr(smp_overflow_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -137,7 +137,7 @@ int Engine::stage(const void* host, size_t nbytes, void** dev) {
 int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes) {
     const bool kq = dtype == HM_Q4_K || dtype == HM_Q6_K;
     if (dtype != HM_BF16 && dtype != HM_Q8_0 && dtype != HM_Q4_0 && !kq)
-        return fail(HM_ERR_UNSUPPORTED, "projection weights must be bf16, Q8_0, Q4_0, Q4_K or Q6_K (f32/f16 projections are outside this engine's path)");
+        return fail(HM_ERR_UNSUPPORTED, "projection weights must be stored as bf16, Q8_0, Q4_0, Q4_K or Q6_K: this checkpoint holds f32 / f16 projections, and the f32-weight streaming kernel they need is not built");
     // Q4_K and Q6_K mix freely (per 32-row tile), as the Q4_K_M files of the Hub do; they are one family here
     const int family = kq ? (int)HM_Q4_K : dtype;
     if (L.kind >= 0 && L.kind != family) return fail(HM_ERR_UNSUPPORTED, "parts of a fused projection have different dtypes");
@@ -477,10 +477,17 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     HM_CUDA(cudaMalloc(&pf_tokens_, (size_t)max_seq_len * 4));
     HM_CUDA(cudaMalloc(&pf_pos_, (size_t)max_seq_len * 4));
     HM_CUDA(cudaMalloc(&pf_seq_, (size_t)max_seq_len * 4));
-    pin_u32_cap_ = std::max<size_t>((size_t)3 * max_seq_len, (size_t)batch * (max_seq_len + 2)) + 16;  // the last word receives the device error word
+    pin_u32_cap_ = std::max<size_t>((size_t)3 * max_seq_len, (size_t)batch * (max_seq_len + 6)) + 16;  // the last word receives the device error word
     HM_CUDA(cudaMallocHost(&pin_u32_, pin_u32_cap_ * 4));
     pin_u32_[pin_u32_cap_ - 1] = 0;
+    HM_CUDA(cudaMalloc(&smp_rng_, (size_t)batch * 8));
+    HM_CUDA(cudaMemset(smp_rng_, 0, (size_t)batch * 8));
+    HM_CUDA(cudaMalloc(&smp_gen_start_, (size_t)batch * 4));
+    HM_CUDA(cudaMemset(smp_gen_start_, 0, (size_t)batch * 4));
+    HM_CUDA(cudaMalloc(&smp_overflow_, (size_t)batch * 4));
+    HM_CUDA(cudaMemset(smp_overflow_, 0, (size_t)batch * 4));
     len_.assign(batch, 0);
+    gen_start_.assign(batch, 0);
     batch_ = batch;
     max_seq_ = max_seq_len;
     int rc = ensure_scratch(std::max(batch, MAX_M));
@@ -510,6 +517,38 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     }
 #endif
     return capture_decode_graph();
+}
+
+// Releases the KV cache and everything sized by it (decode graph, token history, staging, sampler state), so
+// that kv_alloc may be called again with another batch, length or page dtype.  Weights stay resident.
+int Engine::kv_free() {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return HM_OK;
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    if (graph_) cudaGraphDestroy(graph_);
+    graph_exec_ = nullptr;
+    graph_ = nullptr;
+    auto fr = [](auto*& p) {
+        if (p) cudaFree(p);
+        p = nullptr;
+    };
+    for (void*& p : k_pool_) fr(p);
+    for (void*& p : v_pool_) fr(p);
+    k_pool_.clear();
+    v_pool_.clear();
+    fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
+    fr(att_acc_); fr(att_ml_); fr(att_tickets_);
+    fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_); fr(smp_overflow_);
+    if (pin_u32_) cudaFreeHost(pin_u32_);
+    pin_u32_ = nullptr;
+    pin_u32_cap_ = 0;
+    len_.clear();
+    gen_start_.clear();
+    batch_ = 0;
+    max_seq_ = 0;
+    launches_per_step_ = 0;
+    return HM_OK;
 }
 
 int Engine::launch_step() {
@@ -983,6 +1022,8 @@ int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t*
     // pos_dev[seq] = len0+n-1; the argmax finish of the last chunk advances it to len0+n
     st[3 * n] = (uint32_t)(len0 + n - 1);
     HM_CUDA(cudaMemcpyAsync(pos_dev_ + seq, st + 3 * n, 4, cudaMemcpyHostToDevice, stream_));
+    st[3 * n + 2] = (uint32_t)(len0 + n);
+    HM_CUDA(cudaMemcpyAsync(smp_gen_start_ + seq, st + 3 * n + 2, 4, cudaMemcpyHostToDevice, stream_));
     int launches = 0;
     const int chunk = (use_tc_ && !quant_) ? TC_ROWS : MAX_M;
     for (int c0 = 0; c0 < n; c0 += chunk) {
@@ -1001,6 +1042,7 @@ int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t*
     if (rc) return rc;
     if (first_token) *first_token = *tok_pin;
     len_[seq] = len0 + n;
+    gen_start_[seq] = len0 + n;  // what follows this prompt is "generated" for the penalties (src/generate.rs:150-152)
     return HM_OK;
 }
 
@@ -1231,6 +1273,95 @@ int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) 
 // sample_token on the host (defined in capi.cu)
 uint32_t host_sample_token(const float* logits, int n, const hm_sampling& cfg, const uint32_t* generated, int ngen, uint64_t* rng);
 
+int Engine::ensure_sampler_scratch() {
+    if (smp_scaled_) return HM_OK;
+    HM_CUDA(cudaMalloc(&smp_scaled_, (size_t)batch_ * V_ * 4));
+    HM_CUDA(cudaMalloc(&smp_count_, (size_t)batch_ * V_ * 4));
+    HM_CUDA(cudaMemset(smp_count_, 0, (size_t)batch_ * V_ * 4));
+    return HM_OK;
+}
+
+// The sampler kernel over the engine's own state: logits of the last pass, token history by position
+// (generated tokens = positions from the end of the sequence's last prefill on), one RNG word per sequence.
+SamplerArgs Engine::sampler_args(const hm_sampling& s) const {
+    SamplerArgs sa{};
+    sa.logits = logits_;
+    sa.ld_logits = V_;
+    sa.n = V_;
+    sa.cfg = s;
+    sa.hist = hist_dev_;
+    sa.hist_stride = max_seq_ + 1;
+    sa.gen_start = smp_gen_start_;
+    sa.pos = pos_dev_;
+    sa.rng = smp_rng_;
+    sa.scaled = smp_scaled_;
+    sa.count = smp_count_;
+    sa.next_tok = next_dev_;
+    sa.feed_tok = tokens_dev_;
+    sa.overflow = smp_overflow_;
+    return sa;
+}
+
+// decode_step + sample_token for every sequence (src/hf/model.rs:359-371 followed by src/generate.rs:698-801):
+// the fed tokens enter the history (the penalties look at them), the decode graph runs, the sampler kernel
+// picks one token per sequence with that sequence's RNG word.  Rows the kernel hands back (top-k disabled
+// or above SAMPLER_MAX_K on a nearly flat distribution) are finished by the host sampler on their logits.
+int Engine::decode_step_sampled(const uint32_t* tokens, const hm_sampling* sp, uint64_t* rng_state, float* logits, uint32_t* next_tokens) {
+    if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
+    if (batch_ == 0) return fail(HM_ERR_STATE, "decode_step_sampled before kv_alloc");
+    if (!tokens || !sp || !rng_state) return fail(HM_ERR_INVALID, "decode_step_sampled: null argument");
+    const hm_sampling s = *sp;
+    const bool pure_greedy = !(s.temperature > 0.f) && s.repetition_penalty == 1.0f && s.frequency_penalty == 0.f && s.presence_penalty == 0.f;
+    if (pure_greedy) return decode_step(tokens, logits, next_tokens);
+    for (int b = 0; b < batch_; ++b) {
+        if (len_[b] + 1 > max_seq_) return fail(HM_ERR_KV_FULL, "KV cache full (" + std::to_string(len_[b]) + " + 1 > " + std::to_string(max_seq_) + ")");
+        if (tokens[b] >= (uint32_t)V_) return fail(HM_ERR_INVALID, "decode_step_sampled: token id out of range");
+    }
+    int rc = ensure_sampler_scratch();
+    if (rc) return rc;
+    // staging: [0, B) tokens in, [B, 2B) tokens out, [2B, 3B) overflow words, then B RNG words (8-byte aligned)
+    uint32_t* pin = pin_u32_;
+    const size_t B = (size_t)batch_;
+    uint64_t* pin_rng = reinterpret_cast<uint64_t*>(pin + ((3 * B + 1) & ~(size_t)1));
+    std::memcpy(pin, tokens, B * 4);
+    std::memcpy(pin_rng, rng_state, B * 8);
+    HM_CUDA(cudaMemcpyAsync(tokens_dev_, pin, B * 4, cudaMemcpyHostToDevice, stream_));
+    HM_CUDA(cudaMemcpyAsync(smp_rng_, pin_rng, B * 8, cudaMemcpyHostToDevice, stream_));
+    HM_CUDA(launch_hist_set(tokens_dev_, pos_dev_, hist_dev_, max_seq_ + 1, batch_, stream_));
+    rc = launch_step();
+    if (rc) return rc;
+    const SamplerArgs sa = sampler_args(s);
+    HM_CUDA(launch_sample(sa, batch_, stream_));
+    HM_CUDA(cudaMemcpyAsync(pin + B, next_dev_, B * 4, cudaMemcpyDeviceToHost, stream_));
+    HM_CUDA(cudaMemcpyAsync(pin + 2 * B, smp_overflow_, B * 4, cudaMemcpyDeviceToHost, stream_));
+    HM_CUDA(cudaMemcpyAsync(pin_rng, smp_rng_, B * 8, cudaMemcpyDeviceToHost, stream_));
+    if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, B * V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    rc = queue_error_copy();
+    if (rc) return rc;
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    rc = check_device_error();
+    if (rc) return rc;
+    std::memcpy(rng_state, pin_rng, B * 8);
+    std::vector<float> row;
+    std::vector<uint32_t> gen;
+    for (int b = 0; b < batch_; ++b) {
+        uint32_t tok = pin[B + b];
+        if (s.temperature > 0.f && pin[2 * B + b]) {
+            row.resize(V_);
+            const int ngen = std::max(0, len_[b] + 1 - gen_start_[b]);
+            gen.resize(ngen);
+            HM_CUDA(cudaMemcpy(row.data(), logits_ + (size_t)b * V_, (size_t)V_ * 4, cudaMemcpyDeviceToHost));
+            if (ngen) HM_CUDA(cudaMemcpy(gen.data(), hist_dev_ + (size_t)b * (max_seq_ + 1) + gen_start_[b], (size_t)ngen * 4, cudaMemcpyDeviceToHost));
+            tok = host_sample_token(row.data(), V_, s, gen.data(), ngen, &rng_state[b]);
+            HM_CUDA(cudaMemcpy(tokens_dev_ + b, &tok, 4, cudaMemcpyHostToDevice));
+            HM_CUDA(cudaMemcpy(hist_dev_ + (size_t)b * (max_seq_ + 1) + len_[b] + 1, &tok, 4, cudaMemcpyHostToDevice));
+        }
+        if (next_tokens) next_tokens[b] = tok;
+    }
+    for (int b = 0; b < batch_; ++b) len_[b] += 1;
+    return HM_OK;
+}
+
 // generate_streaming_core (src/generate.rs:100-315) without the text side.
 int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, const hm_sampling* sp, uint32_t* out_ids, int* n_out) {
     if (!n_out || !out_ids) return fail(HM_ERR_INVALID, "generate: null output");
@@ -1278,41 +1409,24 @@ int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, 
             clock_gettime(CLOCK_REALTIME, &ts);
             rng = ((uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec) | 1ull;
         }
-        const char* hs = std::getenv("HM_HOST_SAMPLER");
-        const bool device_sampler = s.temperature > 0.f && s.top_k >= 1 && s.top_k <= SAMPLER_MAX_K && !(hs && hs[0] == '1');
-        if (device_sampler) {
+        const char* hs = std::getenv("HM_HOST_SAMPLER");  // test knob: every token through the host sampler
+        if (!(hs && hs[0] == '1')) {
             // Sampled tokens never leave the device between steps: every step replays the decode graph
-            // (which also leaves the greedy token in the feed slot) and then the sampler kernel
-            // replaces it; EOS is looked for in blocks, as on the greedy path.
-            if (!smp_scaled_) {
-                HM_CUDA(cudaMalloc(&smp_scaled_, (size_t)batch_ * V_ * 4));
-                HM_CUDA(cudaMalloc(&smp_count_, (size_t)batch_ * V_ * 4));
-                HM_CUDA(cudaMemset(smp_count_, 0, (size_t)batch_ * V_ * 4));
-                HM_CUDA(cudaMalloc(&smp_rng_, (size_t)batch_ * 8));
-                HM_CUDA(cudaMalloc(&smp_gen_start_, (size_t)batch_ * 4));
-            }
-            const int32_t gstart = real_pos;  // the first generated token sits at the position after the prompt
-            HM_CUDA(cudaMemcpyAsync(smp_gen_start_ + seq, &gstart, 4, cudaMemcpyHostToDevice, stream_));
+            // (which also leaves the plain argmax in the feed slot) and then the sampler kernel
+            // replaces it; EOS is looked for in blocks, as on the greedy path.  Settings for which the
+            // kernel may have to hand a token to the host sampler (top-k disabled or above
+            // SAMPLER_MAX_K) synchronise after every token instead.
+            rc = ensure_sampler_scratch();
+            if (rc) return rc;
+            const bool exact = !(s.temperature > 0.f) || (s.top_k >= 1 && s.top_k <= SAMPLER_MAX_K) || V_ <= SAMPLER_MAX_K;
             HM_CUDA(cudaMemcpyAsync(smp_rng_ + seq, &rng, 8, cudaMemcpyHostToDevice, stream_));
             HM_CUDA(cudaMemcpyAsync(tokens_dev_ + seq, &first, 4, cudaMemcpyHostToDevice, stream_));
-            SamplerArgs sa{};
-            sa.logits = logits_;
-            sa.ld_logits = V_;
-            sa.n = V_;
-            sa.cfg = s;
-            sa.hist = hist_dev_;
-            sa.hist_stride = max_seq_ + 1;
-            sa.gen_start = smp_gen_start_;
-            sa.pos = pos_dev_;
-            sa.rng = smp_rng_;
-            sa.scaled = smp_scaled_;
-            sa.count = smp_count_;
-            sa.next_tok = next_dev_;
-            sa.feed_tok = tokens_dev_;
+            SamplerArgs sa = sampler_args(s);
             bool stop = false;
             std::vector<uint32_t> blk(32);
+            std::vector<float> logits;
             while (!stop && (int)gen.size() < max_new && real_pos < max_seq_) {
-                const int want = std::min({32, max_new - (int)gen.size(), max_seq_ - real_pos});
+                const int want = exact ? std::min({32, max_new - (int)gen.size(), max_seq_ - real_pos}) : 1;
                 for (int i = 0; i < want; ++i) {
                     rc = launch_step();
                     if (rc) return rc;
@@ -1321,12 +1435,25 @@ int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, 
                 }
                 // the sampled tokens of the block are the history entries after the last known position
                 HM_CUDA(cudaMemcpyAsync(blk.data(), hist_dev_ + (size_t)seq * (max_seq_ + 1) + real_pos + 1, (size_t)want * 4, cudaMemcpyDeviceToHost, stream_));
+                int over = 0;
+                if (!exact) HM_CUDA(cudaMemcpyAsync(&over, smp_overflow_ + seq, 4, cudaMemcpyDeviceToHost, stream_));
                 rc = queue_error_copy();
                 if (rc) return rc;
                 HM_CUDA(cudaStreamSynchronize(stream_));
                 rc = check_device_error();
                 if (rc) return rc;
                 len_[seq] = real_pos + want;
+                if (over) {
+                    // the top-p prefix reaches beyond the candidates the kernel gathers: this token comes from the
+                    // host sampler on the step's logits, with the RNG word the kernel left untouched
+                    logits.resize(V_);
+                    HM_CUDA(cudaMemcpy(logits.data(), logits_ + (size_t)seq * V_, (size_t)V_ * 4, cudaMemcpyDeviceToHost));
+                    HM_CUDA(cudaMemcpy(&rng, smp_rng_ + seq, 8, cudaMemcpyDeviceToHost));
+                    blk[0] = host_sample_token(logits.data(), V_, s, gen.data(), (int)gen.size(), &rng);
+                    HM_CUDA(cudaMemcpy(smp_rng_ + seq, &rng, 8, cudaMemcpyHostToDevice));
+                    HM_CUDA(cudaMemcpy(tokens_dev_ + seq, &blk[0], 4, cudaMemcpyHostToDevice));
+                    HM_CUDA(cudaMemcpy(hist_dev_ + (size_t)seq * (max_seq_ + 1) + real_pos + 1, &blk[0], 4, cudaMemcpyHostToDevice));
+                }
                 for (int i = 0; i < want; ++i) {
                     if (blk[i] == eos) {
                         len_[seq] = real_pos + i + 1;  // tokens after EOS were speculative: roll the cache length back
@@ -1339,17 +1466,17 @@ int Engine::generate(int seq, const int64_t* prompt, int n_prompt, int max_new, 
                 real_pos = len_[seq];
             }
         } else {
-        std::vector<float> logits(V_);
-        uint32_t cur = first;
-        for (int step = 1; step < max_new; ++step) {
-            if (real_pos >= max_seq_) break;
-            rc = decode_step(&cur, logits.data(), nullptr);
-            if (rc) return rc;
-            cur = host_sample_token(logits.data(), V_, s, gen.data(), (int)gen.size(), &rng);
-            real_pos += 1;
-            if (cur == eos) break;
-            gen.push_back(cur);
-        }
+            std::vector<float> logits(V_);
+            uint32_t cur = first;
+            for (int step = 1; step < max_new; ++step) {
+                if (real_pos >= max_seq_) break;
+                rc = decode_step(&cur, logits.data(), nullptr);
+                if (rc) return rc;
+                cur = host_sample_token(logits.data(), V_, s, gen.data(), (int)gen.size(), &rng);
+                real_pos += 1;
+                if (cur == eos) break;
+                gen.push_back(cur);
+            }
         }
     }
     std::memcpy(out_ids, gen.data(), gen.size() * 4);

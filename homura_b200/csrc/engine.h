@@ -12,6 +12,7 @@
 
 #include "../../include/homura_b200.h"
 #include "common.cuh"
+#include "sampler.h"
 
 namespace hm {
 
@@ -48,6 +49,7 @@ class Engine {
     int finalize();
 
     int kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype);
+    int kv_free();
     int kv_reset(int seq);
     int kv_len(int seq, int* out);
     int kv_append(int seq, int layer, const float* k_rows, const float* v_rows, int n_new, int advance);
@@ -55,6 +57,7 @@ class Engine {
 
     int prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t* first_token);
     int decode_step(const uint32_t* tokens, float* logits, uint32_t* next_tokens);
+    int decode_step_sampled(const uint32_t* tokens, const hm_sampling* s, uint64_t* rng_state, float* logits, uint32_t* next_tokens);
     int decode_greedy_n(const uint32_t* first_tokens, int steps, uint32_t* out_ids);
     int generate(int seq, const int64_t* prompt, int n_prompt, int max_new, const hm_sampling* s, uint32_t* out_ids, int* n_out);
     int time_decode(int warmup, int steps, float* ms_total);
@@ -83,6 +86,8 @@ class Engine {
     int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, int* launches,
                           const unsigned char* prepacked = nullptr, unsigned char* pack_out = nullptr);
     int capture_decode_graph();
+    int ensure_sampler_scratch();
+    SamplerArgs sampler_args(const hm_sampling& s) const;
     int launch_step();        // replay the captured decode graph
     int queue_error_copy();    // device error word -> pinned host word, on the engine's stream
     int check_device_error();  // after the synchronisation that follows queue_error_copy()
@@ -154,6 +159,8 @@ class Engine {
     int* smp_count_ = nullptr;
     unsigned long long* smp_rng_ = nullptr;
     int32_t* smp_gen_start_ = nullptr;
+    int* smp_overflow_ = nullptr;
+    std::vector<int> gen_start_;  // host mirror of smp_gen_start_
 };
 
 }  // namespace hm

@@ -327,6 +327,13 @@ inline unsigned grid_for(size_t n, int block) {
     return (unsigned)(g > 148u * 16u ? 148u * 16u : (g ? g : 1));
 }
 
+// hist[b][pos[b]] = tokens[b]: the token a host feeds into a decode step enters the sequence's history
+// (the sampler's penalties count occurrences in it).
+__global__ void hist_set_kernel(const uint32_t* tokens, const int32_t* pos, uint32_t* hist, int hist_stride, int batch) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < batch) hist[(size_t)b * hist_stride + pos[b]] = tokens[b];
+}
+
 // Self-test of the give-up path every bounded wait in this library takes.  One CTA: a real 16-byte bulk copy
 // completes on barrier A (waited for, so nothing is in flight when the CTA returns); barrier B is armed for 16
 // bytes that nobody sends, and its wait runs out after `limit` polls, raises the error word and returns.
@@ -413,6 +420,10 @@ cudaError_t launch_post_qkv(const float* qkv, int M, int heads, int kv_heads, in
     if (hd != 64 && hd != 128) return cudaErrorInvalidValue;
     const int warps = M * (heads + 2 * kv_heads);
     return launch_pdl(post_qkv_kernel, dim3((warps + 3) / 4), dim3(128), st, pdl, qkv, M, heads, kv_heads, hd, has_qk_norm, q_norm_w, k_norm_w, eps, rope_cos, rope_sin, row_pos, row_seq, kv, q_out);
+}
+cudaError_t launch_hist_set(const uint32_t* tokens, const int32_t* pos, uint32_t* hist, int hist_stride, int batch, cudaStream_t st) {
+    hist_set_kernel<<<(batch + 127) / 128, 128, 0, st>>>(tokens, pos, hist, hist_stride, batch);
+    return cudaGetLastError();
 }
 cudaError_t launch_bounded_wait_probe(const void* src16, int* err_flag, unsigned long long limit, int* landed, cudaStream_t st) {
     bounded_wait_probe_kernel<<<1, 32, 0, st>>>(src16, err_flag, limit, landed);

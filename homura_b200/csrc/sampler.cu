@@ -7,7 +7,13 @@
 // is found by a 4-pass radix select on the float's order-preserving bit pattern, the <= k survivors are
 // gathered and sorted (probability descending, index ascending on ties -- the reference's unstable sort
 // leaves ties unspecified), and one thread walks them exactly as the reference walks its sorted list.
-// Supported for 1 <= top_k <= SAMPLER_MAX_K; other settings stay on the host sampler.
+// With 1 <= top_k <= SAMPLER_MAX_K that is the whole story.  With top-k disabled (0, or >= the vocabulary) or
+// larger than SAMPLER_MAX_K the kernel still gathers the SAMPLER_MAX_K largest: when the top-p prefix ends
+// inside them the result is what the reference's full sort gives; when it does not (a nearly flat
+// distribution) the kernel raises the row's `overflow` word, leaves token and RNG untouched, and the host
+// finishes that one token with the host sampler.
+// temperature <= 0 is the reference's greedy mode: the penalties are applied, then argmax with ties to the
+// highest index (src/generate.rs:707-745), and the RNG is not advanced.
 //
 // Exactness: the penalties, the maximum, the candidate order and the integer RNG are exact; the
 // softmax denominator is a tree sum (the reference adds 151k terms in sequence) and expf differs from
@@ -75,7 +81,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
     __shared__ int hist[256];
     __shared__ unsigned long long cand[SAMPLER_MAX_K];  // (order key << 32) | ~index: descending = prob desc, index asc
     __shared__ int tie_idx[SAMPLER_MAX_K];
-    __shared__ int n_cand, n_tie, s_k, s_bin;
+    __shared__ int n_cand, n_tie, s_k, s_bin, s_base;
+    __shared__ int wcnt[ST / 32];
     __shared__ uint32_t s_prefix;
 
     const int b = blockIdx.x, tid = threadIdx.x;
@@ -97,7 +104,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
     }
 
     // ---- penalties, temperature, maximum ----
-    const float inv_temp = 1.0f / a.cfg.temperature;
+    const bool greedy = !(a.cfg.temperature > 0.0f);
+    const float inv_temp = greedy ? 1.0f : 1.0f / a.cfg.temperature;
     float mx = -INFINITY;
     auto adjust = [&](float l, int c) {  // penalties per occurrence / per count, then temperature
         if (c > 0) {
@@ -108,7 +116,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
                 l -= a.cfg.presence_penalty;
             }
         }
-        return l * inv_temp;
+        return greedy ? l : l * inv_temp;
     };
     int done = 0;
     if (((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(sl) | reinterpret_cast<uintptr_t>(count)) & 15) == 0) {
@@ -131,13 +139,44 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
     __syncthreads();  // the passes below read sl with a different thread-to-element mapping than its stores (tail elements)
     mx = block_max(mx, sw);
 
+    if (greedy) {
+        // argmax of the penalised logits, ties to the highest index (Iterator::max_by keeps the last maximum)
+        int bi = -1;
+        scan_row(sl, V, tid, [&](int v, float l) {
+            if (l == mx && v > bi) bi = v;
+        });
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bi = max(bi, __shfl_xor_sync(0xffffffffu, bi, o));
+        if ((tid & 31) == 0) wcnt[tid >> 5] = bi;
+        __syncthreads();
+        if (tid == 0) {
+            int best = -1;
+            for (int i = 0; i < ST / 32; ++i) best = max(best, wcnt[i]);
+            const uint32_t tok = best < 0 ? 0u : (uint32_t)best;
+            a.next_tok[b] = tok;
+            if (a.feed_tok) a.feed_tok[b] = tok;
+            if (a.hist && a.pos) a.hist[(size_t)b * a.hist_stride + a.pos[b]] = tok;
+        }
+        if (pen) {
+            __syncthreads();
+            for (int i = tid; i < ngen; i += ST) {
+                const uint32_t t = gen[i];
+                if (t < (uint32_t)V) count[t] = 0;
+            }
+        }
+        return;
+    }
+
     // ---- softmax denominator ----
     float part = 0.f;
     scan_row(sl, V, tid, [&](int, float l) { part += expf(l - mx); });
     const float sum = block_sum_fixed(part, sw);
 
     // ---- radix select: order key of the k-th largest scaled logit ----
-    const int k = min(a.cfg.top_k, V);
+    // top-k outside 1..SAMPLER_MAX_K (disabled, or wider than the list): the SAMPLER_MAX_K largest are gathered and
+    // the walk below decides whether they were enough
+    const bool exact_k = (a.cfg.top_k >= 1 && a.cfg.top_k <= SAMPLER_MAX_K) || V <= SAMPLER_MAX_K;
+    const int k = min(exact_k && a.cfg.top_k >= 1 ? a.cfg.top_k : SAMPLER_MAX_K, V);
     if (tid == 0) {
         s_prefix = 0u;
         s_k = k;
@@ -185,6 +224,32 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
         }
     });
     __syncthreads();
+    if (n_tie > SAMPLER_MAX_K) {
+        // Degenerate rows (flat or masked logits) have more entries equal to the k-th key than the list holds, and
+        // the slots above were handed out in arrival order.  Take the ties again in index order: chunks of ST
+        // consecutive elements, every thread's rank from a ballot prefix count, until want_ties are found.
+        if (tid == 0) s_base = 0;
+        __syncthreads();
+        for (int c0 = 0; c0 < V && s_base < want_ties; c0 += ST) {
+            const int v = c0 + tid;
+            const bool is = v < V && order_key(sl[v]) == kth;
+            const unsigned bal = __ballot_sync(0xffffffffu, is);
+            if ((tid & 31) == 0) wcnt[tid >> 5] = __popc(bal);
+            __syncthreads();
+            int before = 0, total = 0;
+            for (int w = 0; w < ST / 32; ++w) {
+                if (w < (tid >> 5)) before += wcnt[w];
+                total += wcnt[w];
+            }
+            const int rank = s_base + before + __popc(bal & ((1u << (tid & 31)) - 1u));
+            if (is && rank < SAMPLER_MAX_K) tie_idx[rank] = v;
+            __syncthreads();
+            if (tid == 0) s_base += total;
+            __syncthreads();
+        }
+        if (tid == 0) n_tie = min(s_base, SAMPLER_MAX_K);
+        __syncthreads();
+    }
     if (tid == 0) {
         // ties: ascending index, the first want_ties of them (n_tie is tiny except for degenerate logits)
         const int nt = min(n_tie, SAMPLER_MAX_K);
@@ -248,6 +313,12 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
                 break;
             }
         }
+        if (!exact_k && cutoff == nc && !(cumulative >= a.cfg.top_p)) {
+            // the top-p prefix does not end inside the gathered candidates: this token is the host sampler's
+            if (a.overflow) a.overflow[b] = 1;
+            goto done_walk;
+        }
+        if (a.overflow) a.overflow[b] = 0;
         float total = 0.0f;
         for (int i = 0; i < cutoff; ++i) total += probs[i];
         unsigned long long s = a.rng[b];  // xorshift64 (13, 7, 17), src/generate.rs:634-641
@@ -270,6 +341,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
         if (a.feed_tok) a.feed_tok[b] = tok;
         if (a.hist && a.pos) a.hist[(size_t)b * a.hist_stride + a.pos[b]] = tok;  // replaces the greedy token of this step
     }
+done_walk:
 
     // ---- leave the occurrence counts clean for the next call ----
     if (pen) {
@@ -284,7 +356,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const SamplerArgs a) {
 }  // namespace
 
 cudaError_t launch_sample(const SamplerArgs& a, int batch, cudaStream_t st) {
-    if (a.cfg.top_k < 1 || a.cfg.top_k > SAMPLER_MAX_K || !(a.cfg.temperature > 0.f)) return cudaErrorInvalidValue;
+    const bool exact_k = (a.cfg.top_k >= 1 && a.cfg.top_k <= SAMPLER_MAX_K) || a.n <= SAMPLER_MAX_K;
+    if (a.cfg.temperature > 0.f && !exact_k && !a.overflow) return cudaErrorInvalidValue;  // the caller must be able to learn that a row needs the host sampler
     sample_kernel<<<batch, ST, 0, st>>>(a);
     return cudaGetLastError();
 }

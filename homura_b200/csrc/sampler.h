@@ -7,7 +7,7 @@
 
 namespace hm {
 
-constexpr int SAMPLER_MAX_K = 1024;  // largest top_k the device sampler serves
+constexpr int SAMPLER_MAX_K = 1024;  // candidates the device sampler gathers and sorts
 
 struct SamplerArgs {
     const float* logits;  // [batch][ld_logits]
@@ -26,6 +26,8 @@ struct SamplerArgs {
     int* count;               // scratch [batch][n], all zero on entry and on exit
     uint32_t* next_tok;       // [batch] out
     uint32_t* feed_tok;       // [batch] optional: input token of the next decode step
+    int* overflow;            // [batch] out, required when top_k is outside 1..SAMPLER_MAX_K: 1 = the top-p prefix did not end
+                              // inside the SAMPLER_MAX_K largest candidates (token and RNG untouched; sample this row on the host)
 };
 
 cudaError_t launch_sample(const SamplerArgs& a, int batch, cudaStream_t st);

@@ -186,22 +186,63 @@ def write_hf_model(model_dir: str, cfg: DecoderConfig, seed: int, norm_jitter: f
     hjson = json.dumps(header, separators=(",", ":")).encode()
     hjson += b" " * ((8 - len(hjson) % 8) % 8)
     path = os.path.join(model_dir, "model.safetensors")
-    with open(path, "wb") as f:
+
+    def make(spec):
+        name, shape, kind = spec
+        if kind in ("w", "bias"):
+            return normal_bf16(seed, name, shape, 0.02)
+        if norm_jitter > 0:
+            v = 1.0 + norm_jitter * _rng(seed, name).standard_normal(shape, dtype=np.float32)
+            return f32_to_bf16_rne(v)
+        return ones_bf16(shape)
+
+    # every tensor has its own generator (seed, name), so they can be drawn by several threads (numpy's
+    # generators release the GIL) and still be written in file order
+    from concurrent.futures import ThreadPoolExecutor
+
+    with open(path, "wb") as f, ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as pool:
         f.write(struct.pack("<Q", len(hjson)))
         f.write(hjson)
-        for name, shape, kind in specs:
-            if kind == "w":
-                arr = normal_bf16(seed, name, shape, 0.02)
-            elif kind == "bias":
-                arr = normal_bf16(seed, name, shape, 0.02)
-            else:
-                if norm_jitter > 0:
-                    v = 1.0 + norm_jitter * _rng(seed, name).standard_normal(shape, dtype=np.float32)
-                    arr = f32_to_bf16_rne(v)
-                else:
-                    arr = ones_bf16(shape)
+        window = 32
+        futs = [pool.submit(make, sp) for sp in specs[:window]]
+        for i in range(len(specs)):
+            arr = futs[i].result()
+            futs[i] = None
+            if i + window < len(specs):
+                futs.append(pool.submit(make, specs[i + window]))
             f.write(arr.tobytes())
     return model_dir
+
+
+def shard_hf_model(src_dir: str, dst_dir: str, n_shards: int = 2) -> str:
+    """Rewrite a single-file checkpoint as `n_shards` safetensors files plus model.safetensors.index.json,
+    the layout HfModel::load_with_dtype falls back to (src/hf/model.rs:86-127).  Tensors are dealt out
+    round-robin, so every shard holds pieces of every layer."""
+    os.makedirs(dst_dir, exist_ok=True)
+    with open(os.path.join(src_dir, "config.json")) as f, open(os.path.join(dst_dir, "config.json"), "w") as g:
+        g.write(f.read())
+    tensors = read_safetensors(os.path.join(src_dir, "model.safetensors"))
+    names = list(tensors)
+    weight_map = {}
+    for sh in range(n_shards):
+        fname = f"model-{sh + 1:05d}-of-{n_shards:05d}.safetensors"
+        mine = names[sh::n_shards]
+        header, off = {}, 0
+        for name in mine:
+            dt, shape, arr = tensors[name]
+            header[name] = {"dtype": dt, "shape": list(shape), "data_offsets": [off, off + arr.nbytes]}
+            off += arr.nbytes
+            weight_map[name] = fname
+        hjson = json.dumps(header, separators=(",", ":")).encode()
+        hjson += b" " * ((8 - len(hjson) % 8) % 8)
+        with open(os.path.join(dst_dir, fname), "wb") as f:
+            f.write(struct.pack("<Q", len(hjson)))
+            f.write(hjson)
+            for name in mine:
+                f.write(np.ascontiguousarray(tensors[name][2]).tobytes())
+    with open(os.path.join(dst_dir, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {"total_size": sum(t[2].nbytes for t in tensors.values())}, "weight_map": weight_map}, f)
+    return dst_dir
 
 
 def read_safetensors(path: str) -> Dict[str, Tuple[str, Tuple[int, ...], np.ndarray]]:

@@ -95,7 +95,10 @@ HM_API const char* hm_last_error_global(void);
 
 /* ---- model lifecycle ---------------------------------------------------------------- */
 /* HfModel::load_with_dtype, src/hf/model.rs:79-145: config.json + model.safetensors (or the
- * sharded index) from `model_dir`; weight_dtype HM_BF16 keeps bf16 projections. */
+ * sharded index) from `model_dir`.  weight_dtype HM_BF16 keeps bf16 projections; HM_F32 (what
+ * HfModel::load asks for, src/hf/model.rs:37-39) is accepted for checkpoints stored in bf16, where
+ * widening to f32 changes no value; a checkpoint whose projections are stored as f32 / f16 is
+ * HM_ERR_UNSUPPORTED (no f32-weight kernel). */
 HM_API int hm_model_load(const char* model_dir, int weight_dtype, int device, hm_engine** out);
 /* HfModel::load_gguf, src/hf/model.rs:46-75: config from `<arch>.*` metadata, blk.N.* tensors. */
 HM_API int hm_model_load_gguf(const char* gguf_path, int device, hm_engine** out);
@@ -123,6 +126,10 @@ HM_API int hm_checkpoint_info(const char* path, char* buf, size_t cap, size_t* n
  * `batch` independent sequences of up to max_seq_len tokens in pages of page_tokens (16);
  * kv_dtype HM_F32 (Homura's cache dtype) or HM_BF16. */
 HM_API int hm_kv_alloc(hm_engine* e, int batch, int max_seq_len, int page_tokens, int kv_dtype);
+/* Drops the cache (weights stay resident) so that hm_kv_alloc can be called again with another batch,
+ * length or dtype: what init_kv_cache does when called on a model that already has a cache,
+ * src/runtime.rs:1898-1938. */
+HM_API int hm_kv_free(hm_engine* e);
 /* reset_kv_cache, src/hf/model.rs:232-237; seq < 0 resets every sequence. */
 HM_API int hm_kv_reset(hm_engine* e, int seq);
 /* kv_cache_len, src/hf/model.rs:240-243 */
@@ -142,8 +149,19 @@ HM_API int hm_prefill(hm_engine* e, int seq, const int64_t* ids, int n, float* l
  * tokens[batch] in; greedy next tokens out (argmax, ties to the highest index,
  * src/generate.rs:457-468); logits_or_null is [batch, vocab] f32 when wanted. */
 HM_API int hm_decode_step(hm_engine* e, const uint32_t* tokens, float* logits_or_null, uint32_t* next_tokens);
+/* The same step followed by sample_token (src/generate.rs:698-801) for every sequence, with the sampler
+ * options of SamplingConfig (src/generate.rs:648-667): what the reference's loop does per token
+ * (decode_step, then sample_token, src/generate.rs:187-230), for `batch` sequences in one call.  The fed
+ * tokens enter each sequence's history; the penalties look at the tokens since that sequence's last
+ * hm_prefill.  rng_state[batch] holds one xorshift64 word per sequence (seed | 1, src/generate.rs:626-632),
+ * advanced by one draw when temperature > 0.  temperature <= 0 is the reference's greedy mode: penalties,
+ * then argmax.  Runs on the device for every setting; rows whose top-p prefix reaches beyond the 1024
+ * largest candidates (possible only with top_k disabled or above 1024) are finished by the host sampler
+ * on that row's logits inside the call. */
+HM_API int hm_decode_step_sampled(hm_engine* e, const uint32_t* tokens, const hm_sampling* sampling, uint64_t* rng_state, float* logits_or_null, uint32_t* next_tokens);
 /* generate_streaming_core, src/generate.rs:100-315, on sequence `seq`: prefill + up to
- * max_new_tokens-1 decode steps, sampling per `sampling` (greedy stays on the device);
+ * max_new_tokens-1 decode steps, sampling per `sampling` (tokens stay on the device between steps for
+ * every setting, the reference CLI's `--temperature 0` with its default repetition penalty included);
  * stops at EOS or at max_seq_len.  out_ids receives the generated ids, *n_out their count. */
 HM_API int hm_generate(hm_engine* e, int seq, const int64_t* prompt, int n_prompt, int max_new_tokens, const hm_sampling* sampling, uint32_t* out_ids, int* n_out);
 /* Greedy decode of `steps` tokens for every sequence with the token fed back on the device
@@ -151,11 +169,12 @@ HM_API int hm_generate(hm_engine* e, int seq, const int64_t* prompt, int n_promp
 HM_API int hm_decode_greedy_n(hm_engine* e, const uint32_t* first_tokens, int steps, uint32_t* out_ids);
 /* sample_token, src/generate.rs:698-801, on host logits (state is the xorshift64 word). */
 HM_API int hm_sample_token(const float* logits, int n, const hm_sampling* cfg, const uint32_t* generated, int n_generated, uint64_t* rng_state, uint32_t* out);
-/* The same sampler as one GPU kernel (what hm_generate uses when 1 <= top_k <= 1024 and
- * temperature > 0): logits may be a host or a device pointer.  Penalties, candidate order and the
- * xorshift64 draw are exact; probabilities can differ from the host path in their last bits (tree
- * sum, device expf), so in rare cases the draw falls on the other side of a boundary.
- * HM_ERR_UNSUPPORTED outside that range of settings. */
+/* The same sampler as one GPU kernel (what hm_generate and hm_decode_step_sampled use): logits may be a
+ * host or a device pointer.  Penalties, candidate order and the xorshift64 draw are exact; probabilities
+ * can differ from the host path in their last bits (tree sum, device expf), so in rare cases the draw
+ * falls on the other side of a boundary.  temperature <= 0: penalties, then argmax (ties to the highest
+ * index).  With top_k disabled or above 1024 a row whose top-p prefix does not end inside the 1024 largest
+ * candidates is finished by the host sampler inside the call. */
 HM_API int hm_sample_token_device(const float* logits, int n, const hm_sampling* cfg, const uint32_t* generated, int n_generated, uint64_t* rng_state, uint32_t* out);
 
 /* ---- timing on the engine's stream (CUDA events) ------------------------------------ */
@@ -252,6 +271,8 @@ HM_API int hm_dev_alloc(size_t nbytes, void** out);
 HM_API int hm_dev_free(void* p);
 HM_API int hm_dev_copy(void* dst, const void* src, size_t nbytes); /* any direction, synchronous */
 HM_API int hm_dev_sync(void);
+HM_API int hm_dev_set(int device);                               /* device the helpers above (and the standalone kernels) use on this thread */
+HM_API int hm_dev_mem_info(size_t* free_bytes, size_t* total_bytes); /* cudaMemGetInfo of the current device */
 
 #ifdef __cplusplus
 }

@@ -28,6 +28,25 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
+def build_native() -> str:
+    """The same source built -march=native on the machine that runs it (the benchmark's CPU arm).  Falls back
+    to the portable build when the host has no compiler."""
+    path = os.path.join(_HERE, "libhomura_oracle_native.so")
+    try:
+        subprocess.check_call(["make", "-C", _HERE, "-s", "-B", "native"])
+        return path
+    except Exception:
+        return build()
+
+
+def use_native_build():
+    """Call before the first use of the library: load the -march=native build (timing runs only)."""
+    global _LIB_PATH
+    if _lib is not None:
+        raise RuntimeError("oracle library already loaded")
+    _LIB_PATH = build_native()
+
+
 class OrcConfig(C.Structure):
     _fields_ = [
         ("hidden_size", C.c_int32),
@@ -63,7 +82,8 @@ def lib():
     global _lib
     if _lib is not None:
         return _lib
-    build()
+    if not _LIB_PATH.endswith("_native.so"):
+        build()
     L = C.CDLL(_LIB_PATH)
     f32p, u8p, u16p, i64p, u32p, vp = (C.POINTER(C.c_float), C.POINTER(C.c_uint8), C.POINTER(C.c_uint16), C.POINTER(C.c_int64), C.POINTER(C.c_uint32), C.c_void_p)
     sig = {

@@ -76,6 +76,30 @@ def test_safetensors_listing_matches_writer(hm):
         assert got[name]["fnv1a"] == fnv1a(np.array(arr).tobytes())
 
 
+def test_sharded_safetensors_index_is_followed(hm):
+    # src/hf/model.rs:86-127: without model.safetensors the loader reads model.safetensors.index.json and
+    # loads every shard its weight_map names, each once
+    cfg = synth.tiny_config(num_hidden_layers=2, vocab_size=64, hidden_size=64, intermediate_size=64, num_attention_heads=1, num_key_value_heads=1)
+    d = synth.write_hf_model(tempfile.mkdtemp(), cfg, seed=3)
+    whole = {t["name"]: t for t in hm.checkpoint_info(d)["tensors"]}
+    for n_shards in (2, 3):
+        sd = synth.shard_hf_model(d, tempfile.mkdtemp(), n_shards)
+        assert not os.path.exists(os.path.join(sd, "model.safetensors"))
+        info = hm.checkpoint_info(sd)
+        got = {t["name"]: t for t in info["tensors"]}
+        assert len(info["tensors"]) == len(whole) and got == whole  # same names, dtypes, shapes, bytes (fnv1a)
+        assert info["config"] == hm.checkpoint_info(d)["config"]
+    # an index that names a missing shard, and an index without weight_map
+    os.remove(os.path.join(sd, "model-00002-of-00003.safetensors"))
+    with pytest.raises(hm.HomuraError) as e:
+        hm.checkpoint_info(sd)
+    assert e.value.status == hm.HM_ERR_IO
+    json.dump({"metadata": {}}, open(os.path.join(sd, "model.safetensors.index.json"), "w"))
+    with pytest.raises(hm.HomuraError) as e:
+        hm.checkpoint_info(sd)
+    assert "weight_map" in e.value.message
+
+
 def test_gguf_listing_matches_writer(hm):
     # container rules of src/gguf.rs:1055-1172: dims reversed to outermost-first, aligned data
     cfg = synth.tiny_config(num_hidden_layers=1, vocab_size=64, hidden_size=64, intermediate_size=64, num_attention_heads=1, num_key_value_heads=1,

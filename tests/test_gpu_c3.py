@@ -1,0 +1,61 @@
+"""Full-size parity of the GGUF workload on a B200: the TinyLlama-1.1B-architecture model (22 layers,
+hidden 2048, 32/4 heads, head_dim 64, SwiGLU 5632, vocab 32000, untied head) with every linear in Q8_0 or
+in Q4_0 blocks, a 256-token prompt and greedy decoding.
+
+Checked against the CPU oracle's GGUF plan (the restatement of src/hf/emitter_quant.rs:1207-1440): the first
+64 greedy token ids identical (f32 KV pages) and teacher-forced final logits within the stated bar, held
+here to 1e-4 of the largest reference logit.  Q4_0 has no counterpart in the reference (src/gguf.rs:94-109):
+for it the oracle is the definition and its parity is unpinned."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from conftest import record_error
+from homura_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def cosine(a, b):
+    a, b = a.astype(np.float64), b.astype(np.float64)
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+
+
+@pytest.mark.parametrize("fmt,gt", [("q8_0", synth.GGML_Q8_0), ("q4_0", synth.GGML_Q4_0)])
+def test_c3_greedy_64_tokens_and_logits(hm, oracle, fmt, gt):
+    cfg = synth.TINYLLAMA_11B
+    d = os.path.join(tempfile.gettempdir(), f"homura_b200_test_tinyllama_{fmt}_seed13")
+    p = os.path.join(d, "model.gguf")
+    if not os.path.exists(os.path.join(d, ".complete")):
+        os.makedirs(d, exist_ok=True)
+        synth.write_gguf_model(p, cfg, 13, gt)
+        open(os.path.join(d, ".complete"), "w").write("ok")
+    ids = synth.prompt_ids(13, 256, cfg.vocab_size)
+    om = oracle.OracleModel.from_gguf(p, max_seq_len=336)
+    m = hm.HfModel.load_gguf(p)
+    m.init_kv_cache(336)
+    tok_o, lg_o = om.prefill(ids)
+    tok_g, lg_g = m.prefill(ids, want_logits=True)
+    ref = max(1.0, float(np.abs(lg_o).max()))
+    err = float(np.abs(lg_g - lg_o).max())
+    record_error(f"C3 full-size logits ({fmt})", err, ref)
+    assert err <= 1e-4 * ref and cosine(lg_g, lg_o) >= 0.9995
+    assert tok_g == tok_o
+    want = [tok_o]
+    for step in range(63):
+        lo = om.decode_step(want[-1])
+        want.append(oracle.argmax(lo))
+        if step % 8 == 0:
+            lgd, nxt = m.decode_step([want[-2]])
+            err = float(np.abs(lgd[0] - lo).max())
+            record_error(f"C3 full-size logits ({fmt})", err, max(1.0, float(np.abs(lo).max())))
+            assert err <= 1e-4 * max(1.0, float(np.abs(lo).max())) and cosine(lgd[0], lo) >= 0.9995
+        else:
+            _, nxt = m.decode_step([want[-2]], want_logits=False)
+        assert int(nxt[0]) == want[-1], f"greedy token differs at generated index {step + 1}"
+    # the on-device loop gives the same 64 tokens
+    m.reset_kv_cache()
+    assert m.generate_ids(ids, 64, hm.SamplingConfig.greedy()) == want
+    m.close()

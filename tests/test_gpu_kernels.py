@@ -208,6 +208,59 @@ def test_attention_long_context_property(hm):
         np.testing.assert_allclose(got[h], mean_v[h // 2], atol=2e-5)
 
 
+def _attention_oracle_rows(oracle, q, k, v, heads, kvh, head_list):
+    """oracle.gqa_attention for the KV heads that serve `head_list`, returned as {head: row}."""
+    g = heads // kvh
+    out = {}
+    for kh in sorted({h // g for h in head_list}):
+        # a one-KV-head problem with that head's g query heads: same floordiv map, 1/kvh of the work
+        want = oracle.gqa_attention(q[None, kh * g : (kh + 1) * g], k[kh : kh + 1], v[kh : kh + 1], np.zeros((1, k.shape[1]), np.float32), g, 1)
+        for h in head_list:
+            if h // g == kh:
+                out[h] = want[0].reshape(g, -1)[h - kh * g]
+    return out
+
+
+@pytest.mark.parametrize("B,L,bf16", [(1, 32768, True), (1, 32768, False), (64, 4096, True)])
+def test_attention_full_size_against_oracle(hm, oracle, B, L, bf16):
+    # the attention configuration at its real sizes (16/8 heads, head_dim 128, page 16): KV length 32768 for
+    # one sequence, and 64 sequences of 4096; compared with the oracle on a sample of (sequence, head)
+    heads, kvh, hd, PT = 16, 8, 128, 16
+    rng = np.random.default_rng(B * 7 + L + bf16)
+    pages = L // PT
+    n_pages = B * pages
+    perm = rng.permutation(n_pages).astype(np.int32).reshape(B, pages)
+    dt = np.uint16 if bf16 else np.float32
+    kpool = np.empty((n_pages, kvh, PT, hd), dt)
+    vpool = np.empty_like(kpool)
+    sample = sorted({0, B - 1, B // 2, B // 3})  # sequences whose K/V are kept for the oracle
+    keep = {}
+    for b in range(B):
+        k = rng.standard_normal((kvh, L, hd), dtype=np.float32)
+        v = rng.standard_normal((kvh, L, hd), dtype=np.float32)
+        if bf16:
+            kb, vb = synth.f32_to_bf16_rne(k), synth.f32_to_bf16_rne(v)
+            k, v = synth.bf16_to_f32(kb), synth.bf16_to_f32(vb)
+        else:
+            kb, vb = k, v
+        # logical page p of sequence b lives at physical page perm[b, p]
+        kpool[perm[b]] = kb.reshape(kvh, pages, PT, hd).transpose(1, 0, 2, 3)
+        vpool[perm[b]] = vb.reshape(kvh, pages, PT, hd).transpose(1, 0, 2, 3)
+        if b in sample:
+            keep[b] = (k, v)
+    kd, vd = hm.DeviceBuffer(kpool.nbytes), hm.DeviceBuffer(vpool.nbytes)
+    kd.upload(np.ascontiguousarray(kpool.reshape(n_pages, kvh, PT, hd // 4, 4).transpose(0, 1, 3, 2, 4)))  # K tiles are chunk-major
+    vd.upload(vpool)
+    del kpool, vpool
+    q = rng.standard_normal((B, heads, hd), dtype=np.float32)
+    got = hm.attn_decode_paged(q, kd, vd, hm.DType.BF16 if bf16 else hm.DType.F32, perm, [L] * B, heads, kvh, hd, pages).reshape(B, heads, hd)
+    for b in sample:
+        head_list = [0, 5, 15] if B > 1 else list(range(heads))
+        want = _attention_oracle_rows(oracle, q[b], keep[b][0], keep[b][1], heads, kvh, head_list)
+        for h, row in want.items():
+            np.testing.assert_allclose(got[b, h], row, rtol=0, atol=3e-6 * max(1.0, float(np.abs(row).max())))
+
+
 def test_attention_rejects_bad_arguments(hm):
     d = hm.DeviceBuffer(16 * 64 * 4 * 2)
     q = np.zeros((1, 2, 64), np.float32)

@@ -10,6 +10,7 @@ import tempfile
 import numpy as np
 import pytest
 
+from conftest import record_error
 from homura_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -22,11 +23,22 @@ def cosine(a, b):
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
 
 
-def assert_logits_close(got, want, scale_tol=True):
-    # MAX_ABS is stated for logits of order one; for larger logits (block-quantised random
-    # weights) it is applied relative to the largest reference logit.
-    ref = max(1.0, float(np.abs(want).max())) if scale_tol else 1.0
-    assert float(np.abs(got - want).max()) <= MAX_ABS * ref, (float(np.abs(got - want).max()), ref)
+MAX_REL = 1e-4  # of the largest reference logit
+
+
+def assert_logits_close(got, want, scale_tol=True, what="model logits (bf16 weights)", rel=MAX_REL):
+    """The stated bar is max-abs 2e-2 and cosine >= 0.9995 against the CPU path.  The kernels themselves agree
+    with the oracle to ~1e-5 relative, so the tests hold the logits to a bound that scales with them instead:
+    max-abs <= 1e-4 x max(1, largest reference logit).  That is 200 times tighter than 2e-2 for logits of
+    order one, and it stays meaningful for the block-quantised synthetic models whose logits reach the
+    hundreds.  scale_tol=False (bf16 KV pages, whose rounding is not a kernel error): plain 2e-2."""
+    err = float(np.abs(got - want).max())
+    ref = max(1.0, float(np.abs(want).max()))
+    record_error(what, err, ref)
+    if scale_tol:
+        assert err <= rel * ref, (err, ref)
+    else:
+        assert err <= MAX_ABS, (err, ref)
     assert cosine(got, want) >= MIN_COS
 
 
@@ -176,14 +188,14 @@ def test_gguf_quantised_model_matches_oracle(hm, oracle, gt, kind, tied):
     ids = synth.prompt_ids(8, 19, cfg.vocab_size)
     tok_o, lg_o = om.prefill(ids)
     tok_g, lg_g = m.prefill(ids, want_logits=True)
-    assert_logits_close(lg_g, lg_o)
+    assert_logits_close(lg_g, lg_o, what=f"model logits ({kind})")
     assert tok_g == tok_o
     want = [tok_o]
     cur = tok_o
     for _ in range(40):
         lo = om.decode_step(cur)
         lgd, nxt = m.decode_step([cur])
-        assert_logits_close(lgd[0], lo)
+        assert_logits_close(lgd[0], lo, what=f"model logits ({kind})")
         cur = oracle.argmax(lo)
         assert int(nxt[0]) == cur
 
@@ -227,6 +239,27 @@ def test_bf16_kv_pages_within_logit_tolerance(hm, oracle):
         lgd, _ = m.decode_step([cur])
         assert_logits_close(lgd[0], lo, scale_tol=False)
         cur = oracle.argmax(lo)
+
+
+def test_sharded_checkpoint_and_f32_request_load_the_same_model(hm, oracle):
+    # the sharded-index layout (src/hf/model.rs:86-127) and HfModel::load's default dtype request
+    # (load_with_dtype(dir, F32), src/hf/model.rs:37-39) on a bf16 checkpoint: same engine, same logits
+    cfg, d = make_hf("qwen2")
+    sd = synth.shard_hf_model(d, tempfile.mkdtemp(), 3)
+    ids = synth.prompt_ids(3, 21, cfg.vocab_size)
+    om = oracle.OracleModel.from_hf_dir(d, max_seq_len=64)
+    tok_o, lg_o = om.prefill(ids)
+    ref = None
+    for path, dt in ((d, hm.DType.BF16), (sd, hm.DType.BF16), (d, hm.DType.F32), (sd, hm.DType.F32)):
+        m = hm.HfModel.load_with_dtype(path, dt)
+        m.init_kv_cache(64)
+        tok, lg = m.prefill(ids, want_logits=True)
+        assert tok == tok_o
+        assert_logits_close(lg, lg_o)
+        if ref is None:
+            ref = lg
+        np.testing.assert_array_equal(lg, ref)
+        m.close()
 
 
 def test_incremental_prefill_and_reset(hm, oracle):
@@ -298,14 +331,15 @@ def test_error_statuses(hm):
     m.prefill(list(range(16)))
     with pytest.raises(hm.KvCacheFull):
         m.decode_step([1])
-    with pytest.raises(hm.HomuraError) as e:
-        m.init_kv_cache(16)
-    assert e.value.status == hm.HM_ERR_STATE
+    # a second hm_kv_alloc without hm_kv_free is a call-order error; init_kv_cache frees first and replaces the cache
+    assert hm.load_library().hm_kv_alloc(m._h, 1, 16, 16, int(hm.DType.F32)) == hm.HM_ERR_STATE
+    m.init_kv_cache(24, batch=2, kv_dtype=hm.DType.BF16)
+    assert m.kv_cache_len(1) == 0 and m.prefill(list(range(20)), seq=1) >= 0 and m.kv_cache_len(1) == 20
     with pytest.raises(hm.HomuraError) as e:
         hm.HfModel.load(os.path.join(d, "nope"))
     assert e.value.status == hm.HM_ERR_IO
     with pytest.raises(hm.HomuraError) as e:
-        hm.HfModel.load_with_dtype(d, hm.DType.F32)
+        hm.HfModel.load_with_dtype(d, hm.DType.F16)
     assert e.value.status == hm.HM_ERR_UNSUPPORTED
 
 
@@ -416,6 +450,12 @@ def test_decode_batches_spanning_launch_groups(hm, oracle, monkeypatch, B, no_tc
     m.close()
 
 
+# The K-quant projections round every activation to an 8-bit code (emit_quant.rs:409-460).  RMSNorm and SiLU
+# differ from the CPU path in the last ulp, so now and then an activation lands on the other side of a .5 and
+# one code moves by one step: an error of 1/127 of one term of one dot product, far above f32 rounding.
+KQ_REL = 2e-3
+
+
 @pytest.mark.parametrize("case", ["q4_k", "q6_k", "mix_quant_embed", "mix_tied"])
 def test_kquant_gguf_model_matches_oracle(hm, oracle, case):
     tied = case == "mix_tied"
@@ -430,12 +470,12 @@ def test_kquant_gguf_model_matches_oracle(hm, oracle, case):
     ids = synth.prompt_ids(8, 19, cfg.vocab_size)
     tok_o, lg_o = om.prefill(ids)
     tok_g, lg_g = m.prefill(ids, want_logits=True)
-    assert_logits_close(lg_g, lg_o)
+    assert_logits_close(lg_g, lg_o, what="model logits (Q4_K/Q6_K, Q8_K activations)", rel=KQ_REL)
     assert tok_g == tok_o
     cur = tok_o
     for _ in range(40):
         lo = om.decode_step(cur)
         lgd, nxt = m.decode_step([cur])
-        assert_logits_close(lgd[0], lo)
+        assert_logits_close(lgd[0], lo, what="model logits (Q4_K/Q6_K, Q8_K activations)", rel=KQ_REL)
         cur = oracle.argmax(lo)
         assert int(nxt[0]) == cur

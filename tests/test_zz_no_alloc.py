@@ -79,3 +79,38 @@ def test_noalloc_rejects_what_it_cannot_serve(hm):
     with pytest.raises(hm.HomuraError) as e:  # split-K partials beyond the built-in 4 MiB
         hm.gemv_bf16_noalloc(xd.ptr, wd.ptr, hm.LAYOUT_SLAB128, 8, 16384, 128 * 600, yd.ptr)
     assert e.value.status == hm.HM_ERR_UNSUPPORTED
+
+
+def test_noalloc_leaves_free_memory_unchanged(hm):
+    # after one warm-up call (the first call on a device resolves the array's address and loads the kernels)
+    # further calls must not move the device's free-memory figure
+    rng = np.random.default_rng(5)
+    M, K, N = 1, 4864, 896
+    w = hm.pack_bf16_slabs(synth.f32_to_bf16_rne(rng.standard_normal((K, N), dtype=np.float32) * np.float32(0.02)))
+    xd, wd, yd = _dev(hm, rng.standard_normal((M, K), dtype=np.float32)), _dev(hm, w), hm.DeviceBuffer(M * N * 4)
+    hm.gemv_bf16_noalloc(xd.ptr, wd.ptr, hm.LAYOUT_SLAB128, M, K, N, yd.ptr)
+    hm.dev_sync()
+    before = hm.dev_mem_info()[0]
+    for _ in range(5):
+        hm.gemv_bf16_noalloc(xd.ptr, wd.ptr, hm.LAYOUT_SLAB128, M, K, N, yd.ptr)
+    hm.dev_sync()
+    assert abs(hm.dev_mem_info()[0] - before) < (1 << 20)  # cudaMalloc hands out device memory in pieces of 2 MiB
+
+
+def test_noalloc_rejects_buffers_of_another_gpu(hm):
+    if hm.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    x = np.zeros((1, 64), np.float32)
+    w = np.zeros((64, 128), np.uint16)
+    hm.dev_set(1)
+    try:
+        x1 = _dev(hm, x)  # lives on GPU 1
+    finally:
+        hm.dev_set(0)
+    wd, yd = _dev(hm, w), hm.DeviceBuffer(128 * 4)
+    with pytest.raises(hm.HomuraError) as e:  # the kernel on GPU 0 would read GPU 1's memory without peer access
+        hm.gemv_bf16_noalloc(x1.ptr, wd.ptr, hm.LAYOUT_KN, 1, 64, 128, yd.ptr)
+    assert e.value.status == hm.HM_ERR_INVALID and "current device" in e.value.message
+    hm.dev_set(1)
+    x1.free()
+    hm.dev_set(0)
