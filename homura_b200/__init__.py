@@ -156,9 +156,10 @@ def load_library() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
-        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m homura_b200.build` (nvcc, sm_100a)")
-    lib = C.CDLL(LIB_PATH)
+    path = os.environ.get("HOMURA_B200_LIB") or LIB_PATH  # e.g. the phase-trace build of `python -m homura_b200.build --trace`
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: build it with `python -m homura_b200.build` (nvcc, sm_100a)")
+    lib = C.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = res

@@ -35,15 +35,22 @@ def stale() -> bool:
     return any(os.path.getmtime(os.path.join(CSRC, f)) > t for f in SOURCES + HEADERS)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """trace=True: a second library with -DHM_PHASE_TRACE (phase stamps inside the decode kernels), written next to
+    the product library as libhomura_b200_trace.so; HOMURA_B200_LIB=<path> makes the package load it."""
+    if trace:
+        return _build(os.path.join(HERE, "libhomura_b200_trace.so"), os.path.join(HERE, "build", "trace"), ["-DHM_PHASE_TRACE"], verbose)
     if not force and not stale():
         return LIB
+    return _build(LIB, os.path.join(HERE, "build"), [], verbose)
+
+
+def _build(LIB: str, bdir: str, extra_flags, verbose: bool) -> str:
     objs = []
     env = dict(os.environ)
     # the image exports CC/CXX that point at a compiler without libgomp; nvcc should use the system g++
-    cmd_base = [nvcc()] + NVCC_FLAGS + ["-ccbin", "g++"]
+    cmd_base = [nvcc()] + NVCC_FLAGS + list(extra_flags) + ["-ccbin", "g++"]
     procs = []
-    bdir = os.path.join(HERE, "build")
     os.makedirs(bdir, exist_ok=True)
     for src in SOURCES:
         obj = os.path.join(bdir, src + ".o")
@@ -66,4 +73,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

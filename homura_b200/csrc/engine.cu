@@ -498,7 +498,10 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     // per split while the context allows (a page is about 0.65 us of dependent instructions, so pages of a
     // split cost more than the wider merge); longer caches need more CTAs than a cluster holds and merge
     // through global scratch + ticket
-    att_cluster_ = use_clusters_ && max_pages_ <= 64;
+    // ... and only while the (row, KV head) pairs alone do not fill the GPU: with half an SM's worth of pairs or more
+    // the launch is a throughput problem (64 sequences stream 39 MB of pages per layer), which the cost model
+    // of attn_pick_nsplit answers with few splits of many pages each, i.e. the bulk-copy ring kernel
+    att_cluster_ = use_clusters_ && max_pages_ <= 64 && (long)batch * kvh_ < sm_count_ / 2;
     att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 16)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
     if (const char* ns = std::getenv("HM_ATT_NSPLIT")) {  // tuning knob: CTAs per (row, KV head)
         const int v = std::atoi(ns);
@@ -653,7 +656,11 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
         if (tc_xpack_bytes(mc, L.K) > xpack_bytes_) return fail(HM_ERR_STATE, "activation pack scratch too small");
         cudaError_t ce = cudaSuccess;
         if (!prepacked) {  // the producer did not write the tile image itself
-            ce = launch_tc_pack_x(x + (size_t)m0 * ldx, ldx, mc, L.K, norm_w, (float)cfg_.rms_norm_eps, xpack_, stream_, pdl_);
+            unsigned long long* ptr = nullptr;
+#ifdef HM_PHASE_TRACE
+            if (gemv_trace_ && *launches < 512) ptr = gemv_trace_ + (size_t)*launches * 16;
+#endif
+            ce = launch_tc_pack_x(x + (size_t)m0 * ldx, ldx, mc, L.K, norm_w, (float)cfg_.rms_norm_eps, xpack_, stream_, pdl_, ptr);
             if (ce != cudaSuccess) return cuda_fail(ce, "activation pack launch");
             ++*launches;
         }
@@ -693,6 +700,9 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
             a.amax_idx = amax_idx_ + (size_t)m0 * nblocks;
         }
         a.err_flag = err_flag_;
+#ifdef HM_PHASE_TRACE
+        if (gemv_trace_ && *launches < 512) a.trace = gemv_trace_ + (size_t)*launches * 16;
+#endif
         ce = launch_gemm_tc(a, stream_, pdl_);
         if (ce != cudaSuccess) return cuda_fail(ce, "tensor-core projection launch");
         ++*launches;
@@ -1133,7 +1143,19 @@ int Engine::time_decode(int warmup, int steps, float* ms_total) {
         if (erc) return erc;
     }
 #ifdef HM_PHASE_TRACE
-    if (gemv_trace_) {
+    if (gemv_trace_ && std::getenv("HM_TRACE_DUMP")) {
+        // raw stamps of the last step, one line per launch of the pass: for offline reading
+        std::vector<unsigned long long> t(512 * 16);
+        HM_CUDA(cudaMemcpy(t.data(), gemv_trace_, t.size() * 8, cudaMemcpyDeviceToHost));
+        if (FILE* f = std::fopen(std::getenv("HM_TRACE_DUMP"), "w")) {
+            for (int l = 0; l < 512; ++l) {
+                std::fprintf(f, "%d", l);
+                for (int i = 0; i < 16; ++i) std::fprintf(f, " %llu", t[(size_t)l * 16 + i]);
+                std::fprintf(f, "\n");
+            }
+            std::fclose(f);
+        }
+    } else if (gemv_trace_) {
         // HM_GEMV_TRACE=1: %globaltimer stamps of CTA 0 of every projection launch of the last step:
         // resident -> predecessor done -> activations staged -> weights multiplied -> partials published ->
         // split-K reduced -> stored.  Averaged per launch position within a layer.

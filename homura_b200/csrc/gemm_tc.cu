@@ -75,9 +75,12 @@ struct TcShared {
 // out: [k-block][term][mpad][64] bf16, rows of 128 B, 16-byte chunks XOR-swizzled by (row & 7) where
 // row = term * mpad + m.  One block per padded row; an RMSNorm is folded in when norm_w is given
 // (x' = (x * inv_rms) * w, src/graph_builder/emit_linalg.rs:7-26).
-__global__ void __launch_bounds__(256) tc_pack_x_kernel(const float* __restrict__ x, int ldx, int M, int mpad, int K, int Kp, const float* __restrict__ norm_w, float eps, unsigned char* __restrict__ out) {
+__global__ void __launch_bounds__(256) tc_pack_x_kernel(const float* __restrict__ x, int ldx, int M, int mpad, int K, int Kp, const float* __restrict__ norm_w, float eps, unsigned char* __restrict__ out, unsigned long long* trace) {
+    HM_TRACE(const bool tr = trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;)
+    HM_TRACE(if (tr) trace[0] = global_timer();)
     pdl_launch_dependents();
     pdl_wait();
+    HM_TRACE(if (tr) trace[2] = global_timer();)
     const int m = blockIdx.x, tid = threadIdx.x;
     const bool row_ok = m < M;
     const float* xr = x + (size_t)m * ldx;
@@ -127,6 +130,7 @@ __global__ void __launch_bounds__(256) tc_pack_x_kernel(const float* __restrict_
             *reinterpret_cast<uint4*>(out + off) = make_uint4(term[t][0], term[t][1], term[t][2], term[t][3]);
         }
     }
+    HM_TRACE(if (trace && threadIdx.x == 0) atomicMax(trace + 12, global_timer());)
 }
 
 // ---- epilogues on rows [m_lo, m_hi) of the f32 tile [m][128] (output features n0 .. n0+127) ----
@@ -262,6 +266,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
     const int nkb = max(0, kb1 - kb0);
     const int nst = a.nstage;
+    HM_TRACE(const bool tr = a.trace != nullptr && blockIdx.x == 0;)
+    HM_TRACE(if (tr && tid == 0) a.trace[0] = global_timer();)
+    HM_TRACE(if (a.trace && tid == 0) atomicMax(a.trace + 11, global_timer());)
 
     if (tid == 0) {
         for (int s = 0; s < nst; ++s) {
@@ -281,6 +288,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sh.tmem_base;
+    HM_TRACE(if (tr && tid == 0) a.trace[1] = global_timer();)
 
     pdl_launch_dependents();
 
@@ -296,6 +304,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
                 bulk_copy(stage0 + (size_t)i * stage_bytes, wsrc + (size_t)i * W_TILE, W_TILE, &sh.full[i]);
             }
             pdl_wait();
+            HM_TRACE(if (tr) a.trace[2] = global_timer();)
             for (int i = 0; i < pre; ++i) bulk_copy(stage0 + (size_t)i * stage_bytes + W_TILE, xsrc + (size_t)i * x_tile, x_tile, &sh.full[i]);
             for (int i = pre; i < nkb; ++i) {
                 const int s = i % nst;
@@ -313,6 +322,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
                 const int s = i % nst;
                 const uint32_t par = (i / nst) & 1u;
                 if (!mb_wait(&sh.full[s], par, a.err_flag, &sh.abort_flag)) break;
+                HM_TRACE(if (tr && i == 0) a.trace[3] = global_timer();)
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t wa = s32(stage0 + (size_t)s * stage_bytes);
                 const uint32_t xa = wa + W_TILE;
@@ -322,10 +332,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
                 umma_commit(&sh.empty[s]);  // stage reusable once these MMAs have read it
             }
             umma_commit(&sh.acc_full);
+            HM_TRACE(if (tr) a.trace[4] = global_timer();)
         }
     } else {
         // ---- accumulator -> registers (three terms summed) -> f32 tile in shared memory [m][128]
         const bool acc_ok = __all_sync(0xffffffffu, mb_wait(&sh.acc_full, 0, a.err_flag, &sh.abort_flag));
+        HM_TRACE(if (tr && tid == 64) a.trace[5] = global_timer();)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int lane_base = (warp & 3) * 32;  // a warp may only touch its own quarter of the TMEM lanes
         const int n_local = lane_base + lane;   // output feature within the CTA's 128
@@ -361,9 +373,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     //      distributed shared memory: each CTA sums, in rank order, its share of the rows (peers only
     //      read rows that are not theirs, so the sums can be written back in place)
     pdl_wait();
+    HM_TRACE(if (tr && tid == 0) a.trace[6] = global_timer();)
     int m_lo = 0, m_hi = a.M;
     if (CL) {
         cluster_sync_all();
+        HM_TRACE(if (tr && tid == 0) a.trace[7] = global_timer();)
         const int rows_per = (a.M + cs - 1) / cs;
         m_lo = min(a.M, split * rows_per);
         m_hi = min(a.M, m_lo + rows_per);
@@ -375,8 +389,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         }
         __syncthreads();
     }
+    HM_TRACE(if (tr && tid == 0) a.trace[8] = global_timer();)
     tc_epilogue(a, out_tile, m_lo, m_hi, nblk, tid);
+    HM_TRACE(if (tr && tid == 0) a.trace[9] = global_timer();)
     if (CL) cluster_sync_all();  // a CTA may exit only after its tile was read by its peers
+    HM_TRACE(if (tr && tid == 0) a.trace[10] = global_timer();)
+    HM_TRACE(if (a.trace && tid == 0) atomicMax(a.trace + 12, global_timer());)
 }
 
 }  // namespace
@@ -396,7 +414,7 @@ int tc_pick_split(int K, int N, int sm_count) {
     return s < 1 ? 1 : s;
 }
 
-cudaError_t launch_tc_pack_x(const float* x, int ldx, int M, int K, const float* norm_w, float eps, void* xp, cudaStream_t st, bool pdl) {
+cudaError_t launch_tc_pack_x(const float* x, int ldx, int M, int K, const float* norm_w, float eps, void* xp, cudaStream_t st, bool pdl, unsigned long long* trace) {
     if (M < 1 || M > MR) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)tc_mpad(M));
@@ -407,7 +425,7 @@ cudaError_t launch_tc_pack_x(const float* x, int ldx, int M, int K, const float*
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, tc_pack_x_kernel, x, ldx, M, tc_mpad(M), K, tc_padded_k(K), norm_w, eps, (unsigned char*)xp);
+    return cudaLaunchKernelEx(&cfg, tc_pack_x_kernel, x, ldx, M, tc_mpad(M), K, tc_padded_k(K), norm_w, eps, (unsigned char*)xp, trace);
 }
 
 cudaError_t launch_gemm_tc(const TcArgs& a_in, cudaStream_t st, bool pdl) {

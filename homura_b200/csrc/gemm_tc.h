@@ -34,6 +34,7 @@ struct TcArgs {
     float* amax_val;
     int32_t* amax_idx;
     int* err_flag;  // set to 2 when a bounded wait ran out
+    unsigned long long* trace;  // builds with -DHM_PHASE_TRACE: 16 %globaltimer stamps of CTA 0 of this launch
 };
 
 size_t tc_xpack_bytes(int M, int K);  // bytes of the packed activations of M rows
@@ -43,7 +44,7 @@ int tc_mpad(int M);  // rows padded to 16 / 32 / 64
 int tc_pick_split(int K, int N, int sm_count);  // cluster size that fills the SMs once
 // f32 rows -> three bf16 terms per element in the tile layout the GEMM copies in bulk; folds an
 // RMSNorm (weight norm_w, epsilon eps) when norm_w is not NULL.
-cudaError_t launch_tc_pack_x(const float* x, int ldx, int M, int K, const float* norm_w, float eps, void* xp, cudaStream_t st, bool pdl);
+cudaError_t launch_tc_pack_x(const float* x, int ldx, int M, int K, const float* norm_w, float eps, void* xp, cudaStream_t st, bool pdl, unsigned long long* trace = nullptr);
 cudaError_t launch_gemm_tc(const TcArgs& a, cudaStream_t st, bool pdl);
 // src is [N][K] (src_is_kn = false) or [K][N]; rows land at n_off + n, or interleaved 64/64 per
 // 128-row block when interleave_which is 0 (gate) or 1 (up).
