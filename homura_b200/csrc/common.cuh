@@ -51,6 +51,12 @@ __device__ __forceinline__ void st_async_f32x4(uint32_t addr, float4 v, uint32_t
                  "r"(__float_as_uint(v.z)), "r"(__float_as_uint(v.w)), "r"(mbar)
                  : "memory");
 }
+// not volatile: several of these may be in flight at once (callers order them with barriers)
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
+    float4 v;
+    asm("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -246,6 +252,33 @@ __device__ __forceinline__ void tc_xpack_store(unsigned char* xp, int mpad, int 
     for (int t = 0; t < 3; ++t) {
         const int row = t * mpad + m;
         *reinterpret_cast<uint16_t*>(tile + (size_t)row * 128 + ((chunk ^ (row & 7)) << 4) + e * 2) = term[t];
+    }
+}
+
+// Eight consecutive activations (k0 a multiple of 8) as one 16-byte chunk per term.
+__device__ __forceinline__ void tc_xpack_store8(unsigned char* xp, int mpad, int m, int k0, const float (&v)[8]) {
+    uint32_t w[3][4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        uint16_t h[2], md[2], lo[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const float x = v[2 * e + u];
+            h[u] = f32_to_bf16_rne(x);
+            const float r1 = x - bf16_bits_to_f32(h[u]);
+            md[u] = f32_to_bf16_rne(r1);
+            lo[u] = f32_to_bf16_rne(r1 - bf16_bits_to_f32(md[u]));
+        }
+        w[0][e] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+        w[1][e] = (uint32_t)md[0] | ((uint32_t)md[1] << 16);
+        w[2][e] = (uint32_t)lo[0] | ((uint32_t)lo[1] << 16);
+    }
+    const int kb = k0 >> 6, chunk = (k0 & 63) >> 3;
+    unsigned char* tile = xp + (size_t)kb * (3 * mpad * 128);
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        const int row = t * mpad + m;
+        *reinterpret_cast<uint4*>(tile + (size_t)row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[t][0], w[t][1], w[t][2], w[t][3]);
     }
 }
 

@@ -109,7 +109,7 @@ Engine::~Engine() {
         for (LinearW* w : {&l.qkv, &l.o, &l.gu, &l.down}) { fr(w->slabs); fr(w->tc); fr(w->scales); fr(w->codes); fr(w->kq_data); fr(w->kq_tile_type); }
     }
     fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes); fr(lm_head_.kq_data); fr(lm_head_.kq_tile_type);
-    fr(xpack_); fr(xpack_attn_); fr(xpack_act_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
+    fr(xpack_); fr(xpack_attn_); fr(xpack_act_); fr(xpack_h_); fr(xpack_h2_); fr(ss_h_); fr(ss_h2_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
@@ -408,6 +408,10 @@ int Engine::ensure_scratch(int rows) {
             HM_CUDA(re(&xpack_, xpack_bytes_));
             HM_CUDA(re(&xpack_attn_, tc_xpack_bytes(TC_ROWS, qdim_)));
             HM_CUDA(re(&xpack_act_, tc_xpack_bytes(TC_ROWS, I_)));
+            HM_CUDA(re(&xpack_h_, tc_xpack_bytes(TC_ROWS, H_)));
+            HM_CUDA(re(&xpack_h2_, tc_xpack_bytes(TC_ROWS, H_)));
+            HM_CUDA(re(&ss_h_, (size_t)((H_ + 127) / 128) * TC_ROWS));
+            HM_CUDA(re(&ss_h2_, (size_t)((H_ + 127) / 128) * TC_ROWS));
         }
     }
     // split-K scratch sized for the worst projection at M = 8
@@ -649,7 +653,7 @@ static int pad_m(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
 // Projection over up to TC_ROWS rows per launch on the tensor cores (gemm_tc.cu): one kernel packs
 // the activations (folding an RMSNorm when norm_w is given), the GEMM applies bias and residual on store.
 int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos,
-                              const int32_t* row_seq, int* launches, const unsigned char* prepacked, unsigned char* pack_out) {
+                              const int32_t* row_seq, int* launches, const unsigned char* prepacked, unsigned char* pack_out, const TcFuse* fuse) {
     if (!L.tc) return fail(HM_ERR_STATE, "tensor-core weight copy missing");
     for (int m0 = 0; m0 < M; m0 += TC_ROWS) {
         const int mc = std::min(TC_ROWS, M - m0);
@@ -674,6 +678,13 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
         a.xp = prepacked ? prepacked : xpack_;
         a.xp_out = pack_out;
         a.xp_mpad = tc_mpad(mc);
+        if (fuse) {
+            a.ss_in = fuse->ss_in;
+            a.ss_parts = fuse->ss_parts;
+            a.xp_next = fuse->xp_next;
+            a.next_norm_w = fuse->next_norm_w;
+            a.ss_out = fuse->ss_out;
+        }
         a.epi = epi;
         a.bias = bias;
         a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
@@ -844,10 +855,23 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
     };
     constexpr size_t LM_PF = 24u << 20;  // the LM head does not fit the L2: only its first 2 x 24 MB are fetched early
     int rc;
+    // passes of 9..64 rows: the attention output and the SwiGLU output go straight into the packed
+    // activation tiles of the next tensor-core GEMM (no packing launch in between) ...
+    const bool direct_pack = tall && M <= TC_ROWS && qdim_ % 64 == 0 && I_ % 64 == 0;
+    // ... and so does the hidden state after the O and down projections, whose RMSNorm is split between the
+    // producer's epilogue (weight multiply, sums of squares) and the consumer's (row factor)
+    const bool fused = direct_pack && H_ % 128 == 0;
     for (int l = 0; l < L_; ++l) {
         const LayerW& w = layers_[l];
         KvDesc kv{k_pool_[l], v_pool_[l], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
         if (!want(PC_QKV)) {
+        } else if (tall && fused && l > 0) {
+            // the previous layer's down projection left (hidden * input_layernorm weight) packed, with the rows' sums of squares
+            TcFuse f;
+            f.ss_in = ss_h_;
+            f.ss_parts = H_ / 128;
+            rc = enqueue_linear_tc(w.qkv, M, h_, H_, nullptr, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, launches, xpack_h_, nullptr, &f);
+            if (rc) return rc;
         } else if (tall) {
             rc = enqueue_linear_tc(w.qkv, M, h_, H_, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, launches);
             if (rc) return rc;
@@ -880,9 +904,6 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.nsplit = std::min(att_nsplit_, att_cluster_ ? std::max(1, (2 * sm_count_ + M * kvh_ - 1) / (M * kvh_)) : attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));
         at.cluster = att_cluster_ ? 1 : 0;
         at.stream_pages = 1;
-        // passes of 9..64 rows: the attention output and the SwiGLU output go straight into the packed
-        // activation tiles of the next tensor-core GEMM (no packing launch in between)
-        const bool direct_pack = tall && M <= TC_ROWS && qdim_ % 64 == 0 && I_ % 64 == 0;
         if (direct_pack) {
             at.xp_out = xpack_attn_;
             at.xp_mpad = tc_mpad(M);
@@ -909,7 +930,13 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             ++*launches;
         }
         if (want(PC_O) && tall) {
-            rc = enqueue_linear_tc(w.o, M, attn_, qdim_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches, direct_pack ? xpack_attn_ : nullptr);
+            TcFuse f;
+            if (fused) {
+                f.xp_next = xpack_h2_;
+                f.next_norm_w = w.post_ln;
+                f.ss_out = ss_h2_;
+            }
+            rc = enqueue_linear_tc(w.o, M, attn_, qdim_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches, direct_pack ? xpack_attn_ : nullptr, nullptr, fused ? &f : nullptr);
             if (rc) return rc;
         } else if (want(PC_O)) {
             prefetch(&w.down);
@@ -917,6 +944,12 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             if (rc) return rc;
         }
         if (!want(PC_GATE_UP)) {
+        } else if (tall && fused) {
+            TcFuse f;
+            f.ss_in = ss_h2_;
+            f.ss_parts = H_ / 128;
+            rc = enqueue_linear_tc(w.gu, M, h_, H_, nullptr, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, launches, xpack_h2_, xpack_act_, &f);
+            if (rc) return rc;
         } else if (tall) {
             rc = enqueue_linear_tc(w.gu, M, h_, H_, w.post_ln, EPI_SWIGLU, act_, I_, nullptr, nullptr, l, row_pos, row_seq, launches, nullptr, direct_pack ? xpack_act_ : nullptr);
             if (rc) return rc;
@@ -931,7 +964,13 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             if (rc) return rc;
         }
         if (want(PC_DOWN) && tall) {
-            rc = enqueue_linear_tc(w.down, M, act_, I_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches, direct_pack ? xpack_act_ : nullptr);
+            TcFuse f;
+            if (fused) {  // for the next layer's QKV projection, or for the LM head after the last layer
+                f.xp_next = xpack_h_;
+                f.next_norm_w = l + 1 < L_ ? layers_[l + 1].in_ln : final_norm_;
+                f.ss_out = ss_h_;
+            }
+            rc = enqueue_linear_tc(w.down, M, act_, I_, nullptr, EPI_STORE, h_, H_, nullptr, h_, l, row_pos, row_seq, launches, direct_pack ? xpack_act_ : nullptr, nullptr, fused ? &f : nullptr);
             if (rc) return rc;
         } else if (want(PC_DOWN)) {
             if (l + 1 == L_ && lm_rows > 0) prefetch(&lm_head_, LM_PF, LM_PF);
@@ -944,7 +983,13 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         const float* x = h_ + (size_t)lm_row0 * H_;
         const bool lm_tall = use_tc_ && lm_head_.kind == HM_BF16 && lm_head_.tc && lm_rows > MAX_M;
         const bool slab_argmax = lm_head_.kind == HM_BF16;  // per-block argmax partials from the projection's epilogue
-        if (want(PC_LM_HEAD) && lm_tall) {
+        if (want(PC_LM_HEAD) && lm_tall && fused && lm_row0 == 0 && lm_rows == M) {
+            TcFuse f;
+            f.ss_in = ss_h_;
+            f.ss_parts = H_ / 128;
+            rc = enqueue_linear_tc(lm_head_, lm_rows, x, H_, nullptr, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, launches, xpack_h_, nullptr, &f);
+            if (rc) return rc;
+        } else if (want(PC_LM_HEAD) && lm_tall) {
             rc = enqueue_linear_tc(lm_head_, lm_rows, x, H_, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, launches);
             if (rc) return rc;
         } else if (want(PC_LM_HEAD)) {

@@ -83,8 +83,16 @@ class Engine {
     // sequence).  lm_row0/lm_rows select the rows that go through the LM head.
     int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);
     int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches);
+    // RMSNorm handed from one tensor-core GEMM to the next without a packing launch (see TcArgs)
+    struct TcFuse {
+        const float* ss_in = nullptr;   // consumer: partial sums of squares of the rows of `prepacked`
+        int ss_parts = 0;
+        unsigned char* xp_next = nullptr;  // producer: activation image of the next GEMM, scaled by next_norm_w
+        const float* next_norm_w = nullptr;
+        float* ss_out = nullptr;
+    };
     int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, int* launches,
-                          const unsigned char* prepacked = nullptr, unsigned char* pack_out = nullptr);
+                          const unsigned char* prepacked = nullptr, unsigned char* pack_out = nullptr, const TcFuse* fuse = nullptr);
     int capture_decode_graph();
     int ensure_sampler_scratch();
     SamplerArgs sampler_args(const hm_sampling& s) const;
@@ -118,6 +126,8 @@ class Engine {
     float *h_ = nullptr, *q_ = nullptr, *attn_ = nullptr, *act_ = nullptr, *qkv_raw_ = nullptr, *gu_raw_ = nullptr, *logits_ = nullptr;
     unsigned char* xpack_ = nullptr;  // packed activations of one tensor-core projection (gemm_tc.h)
     unsigned char *xpack_attn_ = nullptr, *xpack_act_ = nullptr;  // written directly by the attention kernel / the SwiGLU epilogue
+    unsigned char *xpack_h_ = nullptr, *xpack_h2_ = nullptr;      // written by the down / O epilogues: (hidden * next norm weight) for the next QKV or LM head / gate-up GEMM
+    float *ss_h_ = nullptr, *ss_h2_ = nullptr;                    // [H/128][64] partial sums of squares of those rows
     size_t xpack_bytes_ = 0;
     float* amax_val_ = nullptr;
     int32_t* amax_idx_ = nullptr;

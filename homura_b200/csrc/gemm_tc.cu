@@ -69,6 +69,7 @@ struct TcShared {
     uint64_t full[NSTG], empty[NSTG], acc_full;
     uint32_t tmem_base;
     volatile int abort_flag;
+    float inv[MR];  // per activation row: the RMSNorm factor applied to the accumulators (ss_in given)
 };
 
 // ---- activation packing: f32 rows -> three bf16 terms in the shared-memory image of the B tiles ----
@@ -142,24 +143,82 @@ __device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, in
     const int lane = tid & 31, warp = tid >> 5;
     constexpr int NW = TC_THREADS / 32;
     if (a.epi == EPI_STORE) {
-        for (int idx = tid; idx < rows * BM; idx += TC_THREADS) {
-            const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
-            if (n < a.N) {
-                float v = tile[m * BM + c];
-                if (a.bias) v += __ldg(a.bias + n);
-                if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
-                a.y[(size_t)m * a.ldy + n] = v;
+        const bool vec = (a.ldy & 3) == 0 && ((reinterpret_cast<uintptr_t>(a.y) | reinterpret_cast<uintptr_t>(a.resid) | reinterpret_cast<uintptr_t>(a.bias)) & 15) == 0 && n0 + BM <= a.N;
+        if (vec) {
+            // eight consecutive features per thread (one 16-byte chunk of the next GEMM's activation image); the 16
+            // threads of a row are half a warp, which is where the row's sum of squares is reduced
+            const int items = rows * (BM / 8);
+            for (int base = 0; base < items; base += TC_THREADS) {
+                const int idx = base + tid;
+                const bool ok = idx < items;
+                const int m = m_lo + (ok ? idx : 0) / (BM / 8), c = ((ok ? idx : 0) % (BM / 8)) * 8;
+                float v[8];
+                {
+                    const float4 t0 = *reinterpret_cast<const float4*>(tile + m * BM + c), t1 = *reinterpret_cast<const float4*>(tile + m * BM + c + 4);
+                    v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
+                }
+                if (ok && a.resid) {
+                    const float4 r0 = ld_cg_f32x4(a.resid + (size_t)m * a.ldy + n0 + c), r1 = ld_cg_f32x4(a.resid + (size_t)m * a.ldy + n0 + c + 4);
+                    float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+                    if (a.bias) { b0 = __ldg(reinterpret_cast<const float4*>(a.bias + n0 + c)); b1 = __ldg(reinterpret_cast<const float4*>(a.bias + n0 + c + 4)); }
+                    v[0] = r0.x + (v[0] + b0.x); v[1] = r0.y + (v[1] + b0.y); v[2] = r0.z + (v[2] + b0.z); v[3] = r0.w + (v[3] + b0.w);
+                    v[4] = r1.x + (v[4] + b1.x); v[5] = r1.y + (v[5] + b1.y); v[6] = r1.z + (v[6] + b1.z); v[7] = r1.w + (v[7] + b1.w);
+                } else if (ok && a.bias) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(a.bias + n0 + c)), b1 = __ldg(reinterpret_cast<const float4*>(a.bias + n0 + c + 4));
+                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w; v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                }
+                if (ok) {
+                    *reinterpret_cast<float4*>(a.y + (size_t)m * a.ldy + n0 + c) = make_float4(v[0], v[1], v[2], v[3]);
+                    *reinterpret_cast<float4*>(a.y + (size_t)m * a.ldy + n0 + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                }
+                if (a.xp_next) {
+                    float ss = 0.f;
+                    if (ok) {
+                        const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.next_norm_w + n0 + c)), w1 = __ldg(reinterpret_cast<const float4*>(a.next_norm_w + n0 + c + 4));
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+                        const float xs[8] = {v[0] * w0.x, v[1] * w0.y, v[2] * w0.z, v[3] * w0.w, v[4] * w1.x, v[5] * w1.y, v[6] * w1.z, v[7] * w1.w};
+                        tc_xpack_store8(a.xp_next, a.xp_mpad, m, n0 + c, xs);
+                    }
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (ok && (idx & 15) == 0) a.ss_out[nblk * MR + m] = ss;
+                }
+            }
+        } else {
+            for (int idx = tid; idx < rows * BM; idx += TC_THREADS) {
+                const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
+                if (n < a.N) {
+                    float v = tile[m * BM + c];
+                    if (a.bias) v += __ldg(a.bias + n);
+                    if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
+                    a.y[(size_t)m * a.ldy + n] = v;
+                }
             }
         }
     } else if (a.epi == EPI_SWIGLU) {
         // block = 64 gate features followed by the 64 matching up features (src/hf/emitter.rs SwiGLU)
-        for (int idx = tid; idx < rows * 64; idx += TC_THREADS) {
-            const int m = m_lo + idx / 64, c = idx % 64, j = nblk * 64 + c;
-            if (j < a.N / 2) {
-                const float g = tile[m * BM + c], u = tile[m * BM + 64 + c];
-                const float act = (g / (1.0f + expf(-g))) * u;
-                if (a.xp_out) tc_xpack_store(a.xp_out, a.xp_mpad, m, j, act);
-                else a.y[(size_t)m * a.ldy + j] = act;
+        if (a.xp_out && nblk * 64 + 64 <= a.N / 2) {
+            // eight consecutive outputs per thread, written as one 16-byte chunk per bf16 term of the next GEMM's activation image
+            for (int idx = tid; idx < rows * 8; idx += TC_THREADS) {
+                const int m = m_lo + idx / 8, c = (idx % 8) * 8;
+                float act[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float g = tile[m * BM + c + e], u = tile[m * BM + 64 + c + e];
+                    act[e] = (g / (1.0f + expf(-g))) * u;
+                }
+                tc_xpack_store8(a.xp_out, a.xp_mpad, m, nblk * 64 + c, act);
+            }
+        } else {
+            for (int idx = tid; idx < rows * 64; idx += TC_THREADS) {
+                const int m = m_lo + idx / 64, c = idx % 64, j = nblk * 64 + c;
+                if (j < a.N / 2) {
+                    const float g = tile[m * BM + c], u = tile[m * BM + 64 + c];
+                    const float act = (g / (1.0f + expf(-g))) * u;
+                    if (a.xp_out) tc_xpack_store(a.xp_out, a.xp_mpad, m, j, act);
+                    else a.y[(size_t)m * a.ldy + j] = act;
+                }
             }
         }
     } else if (a.epi == EPI_LOGITS) {
@@ -336,6 +395,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         }
     } else {
         // ---- accumulator -> registers (three terms summed) -> f32 tile in shared memory [m][128]
+        if (a.ss_in) {
+            // deferred RMSNorm: the row factors from the producer's partial sums of squares, while the MMAs run
+            if (warp == 2) {
+                pdl_wait();
+                for (int m = lane; m < MR; m += 32) {
+                    float ssum = 0.f;
+                    for (int p = 0; p < a.ss_parts; ++p) ssum += ld_cg_f32(a.ss_in + p * MR + m);
+                    sh.inv[m] = 1.0f / sqrtf(ssum / (float)a.K + a.eps);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four accumulator warps
+        }
+        const bool scale_rows = a.ss_in != nullptr;
         const bool acc_ok = __all_sync(0xffffffffu, mb_wait(&sh.acc_full, 0, a.err_flag, &sh.abort_flag));
         HM_TRACE(if (tr && tid == 64) a.trace[5] = global_timer();)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -358,7 +430,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
                 for (int j = 0; j < 16; ++j) {
                     // small terms first: lo + mid, then + hi
                     const float v = (__uint_as_float(r[2][j]) + __uint_as_float(r[1][j])) + __uint_as_float(r[0][j]);
-                    out_tile[(c0 + j) * BM + n_local] = v;
+                    out_tile[(c0 + j) * BM + n_local] = scale_rows ? v * sh.inv[c0 + j] : v;
                 }
             }
         } else {
@@ -381,11 +453,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         const int rows_per = (a.M + cs - 1) / cs;
         m_lo = min(a.M, split * rows_per);
         m_hi = min(a.M, m_lo + rows_per);
-        for (int idx = tid; idx < (m_hi - m_lo) * BM; idx += TC_THREADS) {
-            const int off = (m_lo + idx / BM) * BM + (idx % BM);
-            float v = 0.f;
-            for (int r = 0; r < cs; ++r) v += ld_dsmem_f32(dsmem_addr(out_tile + off, (uint32_t)r));
-            out_tile[off] = v;
+        // four consecutive features per thread, every rank's copy requested before the first add (a loop of
+        // dependent remote loads costs one DSMEM round trip per rank: 4 us for eight ranks)
+        for (int idx = tid; idx < (m_hi - m_lo) * (BM / 4); idx += TC_THREADS) {
+            const int off = (m_lo + idx / (BM / 4)) * BM + (idx % (BM / 4)) * 4;
+            float4 v[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r)
+                if (r < cs) v[r] = ld_dsmem_f32x4(dsmem_addr(out_tile + off, (uint32_t)r));
+            float4 t = v[0];
+#pragma unroll
+            for (int r = 1; r < 16; ++r)
+                if (r < cs) { t.x += v[r].x; t.y += v[r].y; t.z += v[r].z; t.w += v[r].w; }
+            *reinterpret_cast<float4*>(out_tile + off) = t;
         }
         __syncthreads();
     }

@@ -23,6 +23,15 @@ struct TcArgs {
     int ldy;
     unsigned char* xp_out;   // EPI_SWIGLU only, optional: write the result as packed activations for the next GEMM instead of y
     int xp_mpad;
+    // RMSNorm across two GEMMs without a packing launch in between.  Producer side (EPI_STORE): besides y, the
+    // epilogue writes (y * next_norm_w) as the packed activations of the next GEMM and, per 128-feature block,
+    // every row's sum of y^2.  Consumer side: the accumulators are scaled by 1 / sqrt(sum of the row's partial
+    // sums / K + eps) before the epilogue, i.e. y = inv_rms * (W . (x * w)) instead of W . ((x * inv_rms) * w).
+    unsigned char* xp_next;      // producer: activation image of the next GEMM (rows padded to xp_mpad)
+    const float* next_norm_w;    // producer: [N] norm weights of the next GEMM's RMSNorm
+    float* ss_out;               // producer: [ceil(N/128)][64] partial sums of squares
+    const float* ss_in;          // consumer: [ss_parts][64] partial sums of squares of the activation rows, or NULL
+    int ss_parts;
     // EPI_QKV_ROPE
     int q_dim, kv_dim, hd, has_qk_norm;
     float eps;
