@@ -599,6 +599,36 @@ __device__ __forceinline__ float4 ld_chunk4(const void* tile, int elem) {  // 4 
     return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(tile) + elem);
 }
 
+// ---- bf16 pages on the tensor cores ---------------------------------------------------------------
+// With six or seven query heads per KV head the f32 FMAs of a page outweigh its bytes (6 flop per byte of bf16
+// cache), so on bf16 pages the two contractions of a page run as warp-level MMAs (m16n8k16, f32 accumulate):
+//   scores^T [16 tokens x 8 heads]  = K tile [16 tokens x hd]   . Q^T [hd x 8 heads]
+//   out^T    [hd x 8 heads]        += V^T    [hd x 16 tokens]   . P^T [16 tokens x 8 heads]
+// K and V are bf16 already; the f32 operands (Q, P) are split into three bf16 terms each (hi + mid + lo is
+// exact to 2^-24), one MMA per term, so the products are the f32 x bf16 products of the reference and only
+// the order of the f32 accumulation differs.  (The 8 heads of the MMA's N are the <= 8 query heads of the
+// KV head: the floordiv head map again.)
+__device__ __forceinline__ void mma_bf16_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// four 8x8 bf16 matrices, each delivered transposed (thread i supplies the address of row i % 8 of matrix i / 8)
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s32(row_addr)));
+}
+// two f32 values -> their three bf16 terms, packed (x low half, y high half)
+__device__ __forceinline__ void split3_pack(float x, float y, uint32_t (&t)[3]) {
+    const uint16_t hx = f32_to_bf16_rne(x), hy = f32_to_bf16_rne(y);
+    const float rx = x - bf16_bits_to_f32(hx), ry = y - bf16_bits_to_f32(hy);
+    const uint16_t mx = f32_to_bf16_rne(rx), my = f32_to_bf16_rne(ry);
+    const uint16_t lx = f32_to_bf16_rne(rx - bf16_bits_to_f32(mx)), ly = f32_to_bf16_rne(ry - bf16_bits_to_f32(my));
+    t[0] = (uint32_t)hx | ((uint32_t)hy << 16);
+    t[1] = (uint32_t)mx | ((uint32_t)my << 16);
+    t[2] = (uint32_t)lx | ((uint32_t)ly << 16);
+}
+__host__ __device__ constexpr size_t st_q_bytes(int hd) { return 3 * (size_t)(hd / 16) * 32 * 8 > (size_t)G_MAX * hd * 4 ? 3 * (size_t)(hd / 16) * 32 * 8 : (size_t)G_MAX * hd * 4; }
+
 template <int HD, bool BF16, bool CL>
 __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnArgs a) {
     using ST = StTile<HD, BF16>;
@@ -607,8 +637,8 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     constexpr int NCH = HD / 8;  // 4-element chunks per half row (lane = token, half)
     extern __shared__ __align__(128) unsigned char st_sm[];
     unsigned char* ring = st_sm;                                                 // [STAGES][K tile | V tile]
-    float* q_s = reinterpret_cast<float*>(ring + ST::STAGES * ST::STAGE_BYTES);  // [G_MAX][NCH][2 halves][4]
-    float* p_s = q_s + G_MAX * HD;                                               // [ATT_WARPS][G_MAX][16]
+    float* q_s = reinterpret_cast<float*>(ring + ST::STAGES * ST::STAGE_BYTES);  // f32 pages: [G_MAX][NCH][2 halves][4]; bf16 pages: MMA fragments [3 terms][HD/16][32 lanes] x 8 B
+    float* p_s = q_s + st_q_bytes(HD) / 4;                                       // [ATT_WARPS][G_MAX][16]
     const int g_early = a.heads / a.kv_heads;
     float* c_o = p_s + ATT_WARPS * G_MAX * PT;                                   // cluster mode, rank 0: [nsplit][g][HD]
     float* c_ml = c_o + (CL ? merge_slot_cap(a.nsplit) : 1) * g_early * HD;     // [slots][g][2]
@@ -648,14 +678,36 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     const int np = max(0, p1 - p0);
     const int32_t* pt = a.page_table + (size_t)seq * a.max_pages;
     for (int i = tid; i < np; i += ST_THREADS) pt_s[i] = pt[p0 + i];
-    // query rows re-ordered so that the two halves' copies of chunk c are adjacent: q_s[j][c][half][4]
-    for (int i = tid; i < g * HD; i += ST_THREADS) {
-        const int jj = i / HD, d = i % HD;
-        const int hfq = d / (HD / 2), c = (d % (HD / 2)) >> 2;
-        q_s[jj * HD + (c * 2 + hfq) * 4 + (d & 3)] = a.q[(size_t)m * a.heads * HD + (head0 + jj) * HD + d];
+    if constexpr (BF16) {
+        // B fragments of Q^T for every 16-dim step: lane (head = lane / 4, pair = lane % 4) holds dims 2*pair, 2*pair+1
+        // (b0) and 2*pair+8, 2*pair+9 (b1) of its head, per bf16 term; heads beyond g are zero
+        uint2* qf = reinterpret_cast<uint2*>(q_s);
+        for (int i = tid; i < (HD / 16) * 32; i += ST_THREADS) {
+            const int kt = i >> 5, ln = i & 31, hh = ln >> 2, d0 = kt * 16 + (ln & 3) * 2;
+            uint32_t lo[3] = {0u, 0u, 0u}, hi[3] = {0u, 0u, 0u};
+            if (hh < g) {
+                const float* qr = a.q + (size_t)m * a.heads * HD + (size_t)(head0 + hh) * HD + d0;
+                split3_pack(qr[0], qr[1], lo);
+                split3_pack(qr[8], qr[9], hi);
+            }
+#pragma unroll
+            for (int t3 = 0; t3 < 3; ++t3) qf[(t3 * (HD / 16) + kt) * 32 + ln] = make_uint2(lo[t3], hi[t3]);
+        }
+    } else {
+        // query rows re-ordered so that the two halves' copies of chunk c are adjacent: q_s[j][c][half][4]
+        for (int i = tid; i < g * HD; i += ST_THREADS) {
+            const int jj = i / HD, d = i % HD;
+            const int hfq = d / (HD / 2), c = (d % (HD / 2)) >> 2;
+            q_s[jj * HD + (c * 2 + hfq) * 4 + (d & 3)] = a.q[(size_t)m * a.heads * HD + (head0 + jj) * HD + d];
+        }
     }
     __syncthreads();
 
+    // tensor-core path (bf16 pages): running state of heads 2 * (lane % 4) and 2 * (lane % 4) + 1, out^T accumulators
+    float tm[2] = {-INFINITY, -INFINITY}, tl[2] = {0.f, 0.f};
+    float to[BF16 ? HD / 16 : 1][4];
+#pragma unroll
+    for (int mt = 0; mt < (BF16 ? HD / 16 : 1); ++mt) to[mt][0] = to[mt][1] = to[mt][2] = to[mt][3] = 0.f;
     // per-warp running softmax state of every head; the page loop leaves warps with different maxima
     float run_m[G_MAX], run_l[G_MAX], acc[G_MAX][EPL];
 #pragma unroll
@@ -680,6 +732,83 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
                 mb_expect_tx(&full[s], ST::STAGE_BYTES);
                 bulk_copy(dst, kpool + tile, ST::TILE_BYTES, &full[s]);
                 bulk_copy(dst + ST::TILE_BYTES, vpool + tile, ST::TILE_BYTES, &full[s]);
+            }
+        }
+    } else if (warp < ST::CW && BF16) {
+        if constexpr (BF16) {
+            const int gid = lane >> 2, tig = lane & 3;
+            float* pw = p_s + warp * (G_MAX * PT);  // [8 heads][16 tokens]: the page's probabilities, transposed for the second MMA
+            const uint2* qf = reinterpret_cast<const uint2*>(q_s);
+            for (int i = warp; i < np; i += ST::CW) {  // this warp's pages
+                const int s = i % ST::STAGES;
+                const uint32_t par = (i / ST::STAGES) & 1u;
+                const bool ok = __all_sync(0xffffffffu, mb_wait(&full[s], par, a.err_flag, &s_abort));
+                if (!ok) break;
+                const uint32_t* kt32 = reinterpret_cast<const uint32_t*>(ring + (size_t)s * ST::STAGE_BYTES);
+                const unsigned char* vt = ring + (size_t)s * ST::STAGE_BYTES + ST::TILE_BYTES;
+                const int p = p0 + i;
+                // ---- scores^T = K tile . Q^T ----
+                float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int kt = 0; kt < HD / 16; ++kt) {
+                    // chunk-major K tile: element (token, dim) at ((dim / 4) * 16 + token) * 4 + dim % 4
+                    const int w0 = ((kt * 4 + (tig >> 1)) * 16 + gid) * 2 + (tig & 1);
+                    const uint32_t a0 = kt32[w0], a1 = kt32[w0 + 16], a2 = kt32[w0 + 64], a3 = kt32[w0 + 80];
+#pragma unroll
+                    for (int t3 = 0; t3 < 3; ++t3) {
+                        const uint2 b = qf[(t3 * (HD / 16) + kt) * 32 + lane];
+                        mma_bf16_m16n8k16(sc, a0, a1, a2, a3, b.x, b.y);
+                    }
+                }
+                // ---- online softmax: this thread follows heads 2*tig and 2*tig+1 (replicated over the 8 token lanes) ----
+                const bool v0 = (p * PT + gid) < kvlen, v1 = (p * PT + gid + 8) < kvlen;
+                float corr[2];
+                float pr[4];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float s0 = v0 ? sc[hh] * a.scale : -INFINITY, s1 = v1 ? sc[2 + hh] * a.scale : -INFINITY;
+                    float mx = fmaxf(s0, s1);
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    const float m_new = fmaxf(tm[hh], mx);
+                    const float p0v = v0 ? expf(s0 - m_new) : 0.f, p1v = v1 ? expf(s1 - m_new) : 0.f;
+                    float ps = p0v + p1v;
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                    corr[hh] = expf(tm[hh] - m_new);  // exp(-inf) = 0 on the first page
+                    tl[hh] = tl[hh] * corr[hh] + ps;
+                    tm[hh] = m_new;
+                    pr[hh] = p0v;
+                    pr[2 + hh] = p1v;
+                }
+                pw[(tig * 2) * PT + gid] = pr[0];
+                pw[(tig * 2 + 1) * PT + gid] = pr[1];
+                pw[(tig * 2) * PT + gid + 8] = pr[2];
+                pw[(tig * 2 + 1) * PT + gid + 8] = pr[3];
+                __syncwarp();
+                uint32_t b0[3], b1[3];  // P^T fragments: head = gid, tokens 2*tig, 2*tig+1 and +8
+                {
+                    const float2 x = *reinterpret_cast<const float2*>(pw + gid * PT + tig * 2), y = *reinterpret_cast<const float2*>(pw + gid * PT + tig * 2 + 8);
+                    split3_pack(x.x, x.y, b0);
+                    split3_pack(y.x, y.y, b1);
+                }
+                __syncwarp();
+                // ---- out^T += V^T . P^T ----
+                const int mj = lane >> 3, mr = lane & 7;  // ldmatrix: this lane addresses row mr of matrix mj
+                const unsigned char* vrow = vt + ((size_t)((mj >> 1) * 8 + mr) * HD + (mj & 1) * 8) * 2;
+#pragma unroll
+                for (int mt = 0; mt < HD / 16; ++mt) {
+                    to[mt][0] *= corr[0];
+                    to[mt][1] *= corr[1];
+                    to[mt][2] *= corr[0];
+                    to[mt][3] *= corr[1];
+                    uint32_t av[4];
+                    ldmatrix_x4_trans(av, vrow + mt * 32);
+#pragma unroll
+                    for (int t3 = 0; t3 < 3; ++t3) mma_bf16_m16n8k16(to[mt], av[0], av[1], av[2], av[3], b0[t3], b1[t3]);
+                }
+                __syncwarp();
+                if (lane == 0) mb_arrive(&empty[s]);  // the stage may be refilled
             }
         }
     } else if (warp < ST::CW) {
@@ -774,7 +903,25 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
         }
     }
     __syncthreads();  // every page consumed: the ring becomes the merge scratch
-    if (warp < ST::CW) {
+    if (warp < ST::CW && BF16) {
+        const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int jj = tig * 2 + hh;
+            if (jj < g) {
+                const int w = warp * g + jj;
+                if (gid == 0) {
+                    w_ml[w * 2 + 0] = tm[hh];
+                    w_ml[w * 2 + 1] = tl[hh];
+                }
+#pragma unroll
+                for (int mt = 0; mt < (BF16 ? HD / 16 : 1); ++mt) {
+                    w_acc[w * HD + mt * 16 + gid] = to[mt][hh];
+                    w_acc[w * HD + mt * 16 + gid + 8] = to[mt][2 + hh];
+                }
+            }
+        }
+    } else if (warp < ST::CW) {
         // publish this warp's state: slot = warp, entry (warp * g + head)
 #pragma unroll
         for (int jj = 0; jj < G_MAX; ++jj) {
@@ -796,7 +943,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
 template <int HD, bool BF16>
 size_t stream_smem_bytes(int pages_per_cta, int g, int slots) {
     using ST = StTile<HD, BF16>;
-    return (size_t)ST::STAGES * ST::STAGE_BYTES + sizeof(float) * ((size_t)G_MAX * HD + ATT_WARPS * G_MAX * PT + (size_t)slots * g * (HD + 2)) + (size_t)pages_per_cta * 4 + 128;
+    return (size_t)ST::STAGES * ST::STAGE_BYTES + st_q_bytes(HD) + sizeof(float) * (ATT_WARPS * G_MAX * PT + (size_t)slots * g * (HD + 2)) + (size_t)pages_per_cta * 4 + 128;
 }
 
 template <int HD, bool BF16>
