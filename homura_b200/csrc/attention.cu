@@ -668,7 +668,12 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     if (a.pf_bytes && tid < 32)
         l2_prefetch_slice(a.pf_ptr, a.pf_bytes, (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x), (int)(gridDim.x * gridDim.y * gridDim.z), tid);
     if (CL && cluster_ctarank() == 0) fill_neutral_slots<HD>(a, a.nsplit, g, c_o, c_ml);  // merge slots past the split count
-    pdl_wait();
+    // Decode passes (one row per sequence, early_pages != 0): lengths and the page table were final before this
+    // step's launches began, and every page below the one that receives the new token is complete, so the page
+    // table is read and the first ring-full of those pages requested BEFORE the dependency wait.  Prefill chunks
+    // (several rows of one sequence, pages being written by the launch before this one) wait first.
+    const bool early = a.early_pages != 0;
+    if (!early) pdl_wait();
 
     const int seq = a.row_seq ? a.row_seq[m] : m;
     const int kvlen = a.kv_len ? a.kv_len[m] : a.row_pos[m] + 1;
@@ -678,6 +683,25 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     const int np = max(0, p1 - p0);
     const int32_t* pt = a.page_table + (size_t)seq * a.max_pages;
     for (int i = tid; i < np; i += ST_THREADS) pt_s[i] = pt[p0 + i];
+    int n_pre = 0;  // pages requested before the dependency wait (producer thread only)
+    if (early) {
+        __syncthreads();
+        if (warp == ATT_WARPS && lane == 0) {
+            using TE = typename std::conditional<BF16, uint16_t, float>::type;
+            const TE* kpool = reinterpret_cast<const TE*>(a.k_pool);
+            const TE* vpool = reinterpret_cast<const TE*>(a.v_pool);
+            const int new_page = (kvlen - 1) / PT;  // the page the new token's K/V are being written to
+            while (n_pre < np && n_pre < ST::STAGES && p0 + n_pre < new_page) {
+                const size_t tile = ((size_t)pt_s[n_pre] * a.kv_heads + kvh) * PT * HD;
+                unsigned char* dst = ring + (size_t)n_pre * ST::STAGE_BYTES;
+                mb_expect_tx(&full[n_pre], ST::STAGE_BYTES);
+                bulk_copy(dst, kpool + tile, ST::TILE_BYTES, &full[n_pre]);
+                bulk_copy(dst + ST::TILE_BYTES, vpool + tile, ST::TILE_BYTES, &full[n_pre]);
+                ++n_pre;
+            }
+        }
+        pdl_wait();
+    }
     if constexpr (BF16) {
         // B fragments of Q^T for every 16-dim step: lane (head = lane / 4, pair = lane % 4) holds dims 2*pair, 2*pair+1
         // (b0) and 2*pair+8, 2*pair+9 (b1) of its head, per bf16 term; heads beyond g are zero
@@ -723,7 +747,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
         if (lane == 0) {
             const T* kpool = reinterpret_cast<const T*>(a.k_pool);
             const T* vpool = reinterpret_cast<const T*>(a.v_pool);
-            for (int i = 0; i < np; ++i) {
+            for (int i = n_pre; i < np; ++i) {
                 const int s = i % ST::STAGES;
                 const uint32_t par = ((i / ST::STAGES) & 1u) ^ 1u;
                 if (!mb_wait(&empty[s], par, a.err_flag, &s_abort)) break;

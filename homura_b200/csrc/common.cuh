@@ -332,6 +332,15 @@ struct GemvArgs {
     // EPI_LOGITS: per-slab argmax partials
     float* amax_val;     // [M][nslabs]
     int32_t* amax_idx;   // [M][nslabs]
+    // EPI_LOGITS, optional: the CTA whose epilogue finishes last (a ticket over the slabs) also reduces the slab
+    // partials to the greedy token of every row, stores it as the next step's input, advances the position and
+    // appends to the history: what a separate argmax launch would do
+    unsigned int* fin_ticket;  // one word, zero between launches
+    uint32_t* next_tok;        // [M]
+    uint32_t* feed_tok;        // [M] or null
+    int32_t* pos;              // [M] or null
+    uint32_t* hist;            // [M][hist_stride] or null
+    int hist_stride;
     // split-K scratch
     float* partial;      // [nslabs*ksplit][M][128]
     unsigned int* tickets;  // [nslabs], zero between launches

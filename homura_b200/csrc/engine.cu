@@ -110,7 +110,7 @@ Engine::~Engine() {
     }
     fr(lm_head_.slabs); fr(lm_head_.tc); fr(lm_head_.scales); fr(lm_head_.codes); fr(lm_head_.kq_data); fr(lm_head_.kq_tile_type);
     fr(xpack_); fr(xpack_attn_); fr(xpack_act_); fr(xpack_h_); fr(xpack_h2_); fr(ss_h_); fr(ss_h2_); fr(h_); fr(q_); fr(attn_); fr(act_); fr(qkv_raw_); fr(gu_raw_); fr(logits_); fr(amax_val_); fr(amax_idx_);
-    fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_);
+    fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_); fr(fin_ticket_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
     fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_); fr(smp_overflow_);
@@ -368,6 +368,8 @@ int Engine::finalize() {
     HM_CUDA(cudaMemcpy(rope_sin_, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
     HM_CUDA(cudaMalloc(&err_flag_, 4));
     HM_CUDA(cudaMemset(err_flag_, 0, 4));
+    HM_CUDA(cudaMalloc(&fin_ticket_, 4));
+    HM_CUDA(cudaMemset(fin_ticket_, 0, 4));
     finalized_ = true;
     return HM_OK;
 }
@@ -722,7 +724,7 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
 }
 
 int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer,
-                           const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches) {
+                           const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches, const ArgmaxFold* fold) {
     for (int m0 = 0; m0 < M; m0 += MAX_M) {
         const int mv = std::min(MAX_M, M - m0), mp = pad_m(mv);
         cudaError_t ce;
@@ -779,6 +781,14 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.amax_idx = amax_idx ? amax_idx + (size_t)m0 * nslabs : nullptr;
             a.partial = partial_;
             a.tickets = tickets_;
+            if (fold) {
+                a.fin_ticket = fin_ticket_;
+                a.next_tok = fold->next_tok + m0;
+                a.feed_tok = fold->feed_tok ? fold->feed_tok + m0 : nullptr;
+                a.pos = fold->pos ? fold->pos + m0 : nullptr;
+                a.hist = fold->hist ? fold->hist + (size_t)m0 * fold->hist_stride : nullptr;
+                a.hist_stride = fold->hist_stride;
+            }
             if (a.cluster == 0 && gemv_partial_floats(L.N, a.ksplit, mp) > partial_floats_) return fail(HM_ERR_STATE, "split-K scratch too small");
             ce = launch_gemv_bf16(a, mp, stream_, pdl_);
         } else if (L.kind == HM_Q4_K) {
@@ -983,6 +993,8 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         const float* x = h_ + (size_t)lm_row0 * H_;
         const bool lm_tall = use_tc_ && lm_head_.kind == HM_BF16 && lm_head_.tc && lm_rows > MAX_M;
         const bool slab_argmax = lm_head_.kind == HM_BF16;  // per-block argmax partials from the projection's epilogue
+        const bool fold_argmax = slab_argmax && !lm_tall;    // the streaming kernel's last epilogue also produces the greedy token
+        lm_folds_argmax_ = fold_argmax;
         if (want(PC_LM_HEAD) && lm_tall && fused && lm_row0 == 0 && lm_rows == M) {
             TcFuse f;
             f.ss_in = ss_h_;
@@ -993,11 +1005,12 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             rc = enqueue_linear_tc(lm_head_, lm_rows, x, H_, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, launches);
             if (rc) return rc;
         } else if (want(PC_LM_HEAD)) {
-            rc = slab_argmax ? enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches)
+            const ArgmaxFold fold{next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1};
+            rc = slab_argmax ? enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches, &fold)
                              : enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_STORE, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, nullptr, nullptr, launches);
             if (rc) return rc;
         }
-        if (want(PC_SAMPLE)) {
+        if (want(PC_SAMPLE) && !fold_argmax) {
             ce = slab_argmax ? launch_argmax_finish(amax_val_, amax_idx_, nslabs, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_)
                              : launch_argmax_finish(logits_, nullptr, V_, lm_rows, next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1, stream_, pdl_);
             if (ce != cudaSuccess) return cuda_fail(ce, "argmax_finish");
@@ -1300,7 +1313,8 @@ int Engine::profile_decode(int steps, hm_kernel_stat* out, int cap, int* n_out) 
             cudaGraphExec_t ge = nullptr;
             ce = cudaGraphInstantiate(&ge, g, 0);
             if (ce == cudaSuccess) {
-                for (int w = 0; w < 2 && c != PC_SAMPLE; ++w) cudaGraphLaunch(ge, stream_);  // warm-up (not for the class that moves the position)
+                const bool moves_pos = c == PC_SAMPLE || (c == PC_LM_HEAD && lm_folds_argmax_);
+                for (int w = 0; w < 2 && !moves_pos; ++w) cudaGraphLaunch(ge, stream_);  // warm-up (not for the class that moves the position)
                 cudaEventRecord(e0, stream_);
                 for (int s = 0; s < steps; ++s) cudaGraphLaunch(ge, stream_);
                 cudaEventRecord(e1, stream_);

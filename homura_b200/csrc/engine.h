@@ -40,6 +40,14 @@ struct LayerW {
     LinearW qkv, o, gu, down;
 };
 
+// final argmax folded into the LM-head launch (see GemvArgs::fin_ticket)
+struct ArgmaxFold {
+    uint32_t *next_tok, *feed_tok;
+    int32_t* pos;
+    uint32_t* hist;
+    int hist_stride;
+};
+
 class Engine {
    public:
     static int create(const hm_config& cfg, int device, Engine** out, std::string* err);
@@ -82,7 +90,7 @@ class Engine {
     // Enqueue one pass over M rows (decode: one row per sequence; prefill: a chunk of one
     // sequence).  lm_row0/lm_rows select the rows that go through the LM head.
     int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);
-    int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches);
+    int enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches, const struct ArgmaxFold* fold = nullptr);
     // RMSNorm handed from one tensor-core GEMM to the next without a packing launch (see TcArgs)
     struct TcFuse {
         const float* ss_in = nullptr;   // consumer: partial sums of squares of the rows of `prepacked`
@@ -139,6 +147,7 @@ class Engine {
     int att_nsplit_ = 1;
     bool att_cluster_ = true;
     int* err_flag_ = nullptr;
+    unsigned int* fin_ticket_ = nullptr;  // ticket of the LM head's folded argmax
 
     // KV cache
     int batch_ = 0, max_seq_ = 0, page_tokens_ = 16, max_pages_ = 0;
@@ -162,6 +171,7 @@ class Engine {
     int launches_per_step_ = 0;
 
     int only_class_ = -1;
+    bool lm_folds_argmax_ = false;  // the LM-head launch of the last enqueued pass also did the final argmax
     unsigned long long* gemv_trace_ = nullptr;  // builds with -DHM_PHASE_TRACE and HM_GEMV_TRACE=1: [512][16] timestamps, one row per launch of a pass
 
     // device-side sampler scratch (sampler.cu), allocated on first sampled generation

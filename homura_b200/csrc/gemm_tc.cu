@@ -70,6 +70,7 @@ struct TcShared {
     uint32_t tmem_base;
     volatile int abort_flag;
     float inv[MR];  // per activation row: the RMSNorm factor applied to the accumulators (ss_in given)
+    int pos[MR], page[MR];  // QKV epilogue: position and KV page of every row's token, fetched while the MMAs run
 };
 
 // ---- activation packing: f32 rows -> three bf16 terms in the shared-memory image of the B tiles ----
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(256) tc_pack_x_kernel(const float* __restrict_
 // The same four epilogues as the streaming projection kernel (gemv_bf16.cu), for up to 64 rows.
 __device__ __forceinline__ bool tc_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i > bi); }
 
-__device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, int nblk, int tid) {
+__device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, int nblk, int tid, const int* s_pos, const int* s_page) {
     const int n0 = nblk * BM, rows = m_hi - m_lo;
     const int lane = tid & 31, warp = tid >> 5;
     constexpr int NW = TC_THREADS / 32;
@@ -273,33 +274,47 @@ __device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, in
             }
             __syncthreads();
         }
-        for (int idx = tid; idx < rows * BM; idx += TC_THREADS) {
-            const int m = m_lo + idx / BM, c = idx % BM, n = n0 + c;
-            if (n >= a.N) continue;
-            const int hh = c / hd, d = c % hd;
+        // Rotation and stores, four dims of the first half of a head and their partners in the second half per
+        // thread: one 16-byte read of the cos and sin rows serves both (the two halves of a row are equal,
+        // src/hf/precompute.rs:10-40), and Q / K / V leave as 16-byte (f32) or 8-byte (bf16 page) stores.  The
+        // K tile is chunk-major, so four consecutive dims of one token are contiguous there as well.
+        const int ipr = BM / 8, iph = hd / 8;
+        for (int idx = tid; idx < rows * ipr; idx += TC_THREADS) {
+            const int m = m_lo + idx / ipr, it = idx % ipr;
+            const int hh = it / iph, d0 = (it % iph) * 4;
             const int nh = n0 + hh * hd;
-            const int pos = a.row_pos[m];
-            float v = tile[m * BM + c];
+            if (nh >= a.N) continue;
+            const float4 lo = *reinterpret_cast<const float4*>(tile + m * BM + hh * hd + d0);
+            const float4 hi = *reinterpret_cast<const float4*>(tile + m * BM + hh * hd + half + d0);
+            float4 olo = lo, ohi = hi;
+            const int pos = s_pos[m];
             if (nh < a.q_dim + a.kv_dim) {
-                const float other = (d < half) ? -tile[m * BM + c + half] : tile[m * BM + c - half];
-                const float cs = __ldg(a.rope_cos + (size_t)pos * hd + d);
-                const float sn = __ldg(a.rope_sin + (size_t)pos * hd + d);
-                v = fmaf(other, sn, v * cs);
+                const float4 cs = __ldg(reinterpret_cast<const float4*>(a.rope_cos + (size_t)pos * hd + d0));
+                const float4 sn = __ldg(reinterpret_cast<const float4*>(a.rope_sin + (size_t)pos * hd + d0));
+                olo = make_float4(fmaf(-hi.x, sn.x, lo.x * cs.x), fmaf(-hi.y, sn.y, lo.y * cs.y), fmaf(-hi.z, sn.z, lo.z * cs.z), fmaf(-hi.w, sn.w, lo.w * cs.w));
+                ohi = make_float4(fmaf(lo.x, sn.x, hi.x * cs.x), fmaf(lo.y, sn.y, hi.y * cs.y), fmaf(lo.z, sn.z, hi.z * cs.z), fmaf(lo.w, sn.w, hi.w * cs.w));
             }
             if (nh < a.q_dim) {
-                a.y[(size_t)m * a.ldy + n] = v;
+                float* q = a.y + (size_t)m * a.ldy + nh;
+                *reinterpret_cast<float4*>(q + d0) = olo;
+                *reinterpret_cast<float4*>(q + half + d0) = ohi;
             } else {
                 const bool is_k = nh < a.q_dim + a.kv_dim;
                 const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
-                const int seq = a.row_seq ? a.row_seq[m] : a.seq_base + m;
-                const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
                 const int tok = pos % a.kv.page_tokens;
-                const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd));
+                const size_t base = ((size_t)s_page[m] * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd;
+                const size_t o0 = base + (is_k ? k_tile_off(tok, d0) : v_tile_off(tok, d0, hd));
+                const size_t o1 = base + (is_k ? k_tile_off(tok, half + d0) : v_tile_off(tok, half + d0, hd));
                 void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
-                if (a.kv.bf16)
-                    reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(v);
-                else
-                    reinterpret_cast<float*>(pool)[off] = v;
+                if (a.kv.bf16) {
+                    uint16_t* pp = reinterpret_cast<uint16_t*>(pool);
+                    *reinterpret_cast<uint2*>(pp + o0) = make_uint2((uint32_t)f32_to_bf16_rne(olo.x) | ((uint32_t)f32_to_bf16_rne(olo.y) << 16), (uint32_t)f32_to_bf16_rne(olo.z) | ((uint32_t)f32_to_bf16_rne(olo.w) << 16));
+                    *reinterpret_cast<uint2*>(pp + o1) = make_uint2((uint32_t)f32_to_bf16_rne(ohi.x) | ((uint32_t)f32_to_bf16_rne(ohi.y) << 16), (uint32_t)f32_to_bf16_rne(ohi.z) | ((uint32_t)f32_to_bf16_rne(ohi.w) << 16));
+                } else {
+                    float* pp = reinterpret_cast<float*>(pool);
+                    *reinterpret_cast<float4*>(pp + o0) = olo;
+                    *reinterpret_cast<float4*>(pp + o1) = ohi;
+                }
             }
         }
     }
@@ -395,6 +410,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         }
     } else {
         // ---- accumulator -> registers (three terms summed) -> f32 tile in shared memory [m][128]
+        if (a.epi == EPI_QKV_ROPE) {
+            // positions and the page table were final before this pass began: fetched while the MMAs run
+            for (int mm = tid - 64; mm < a.M; mm += 128) {
+                const int pos = a.row_pos[mm], seq = a.row_seq ? a.row_seq[mm] : a.seq_base + mm;
+                sh.pos[mm] = pos;
+                sh.page[mm] = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
+            }
+        }
         if (a.ss_in) {
             // deferred RMSNorm: the row factors from the producer's partial sums of squares, while the MMAs run
             if (warp == 2) {
@@ -470,7 +493,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         __syncthreads();
     }
     HM_TRACE(if (tr && tid == 0) a.trace[8] = global_timer();)
-    tc_epilogue(a, out_tile, m_lo, m_hi, nblk, tid);
+    tc_epilogue(a, out_tile, m_lo, m_hi, nblk, tid, sh.pos, sh.page);
     HM_TRACE(if (tr && tid == 0) a.trace[9] = global_timer();)
     if (CL) cluster_sync_all();  // a CTA may exit only after its tile was read by its peers
     HM_TRACE(if (tr && tid == 0) a.trace[10] = global_timer();)

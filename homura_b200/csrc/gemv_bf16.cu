@@ -465,6 +465,50 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
                 a.amax_idx[m * nslabs + slab] = bi;
             }
         }
+        if (a.fin_ticket) {
+            // last epilogue of the launch: every slab's partial is in place, reduce them (ties to the higher index)
+            const int nslabs = (a.N + SLAB - 1) / SLAB;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) s_last = atomicAdd(a.fin_ticket, 1u) == (unsigned int)(nslabs - 1);
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                float* rv = red;                                  // [8 warps] values, reused per row
+                int* ri = reinterpret_cast<int*>(red + 8);        // [8 warps] indices
+                for (int m = 0; m < a.m_valid; ++m) {
+                    float bv = -INFINITY;
+                    int bi = -1;
+                    for (int sidx = tid; sidx < nslabs; sidx += GEMV_THREADS) {
+                        const float v = ld_cg_f32(a.amax_val + (size_t)m * nslabs + sidx);
+                        const int i = __ldcg(a.amax_idx + (size_t)m * nslabs + sidx);
+                        if (i >= 0 && (bi < 0 || better(v, i, bv, bi))) { bv = v; bi = i; }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                        if (oi >= 0 && (bi < 0 || better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+                    }
+                    __syncthreads();
+                    if (lane == 0) { rv[warp] = bv; ri[warp] = bi; }
+                    __syncthreads();
+                    if (tid == 0) {
+                        for (int w = 0; w < 8; ++w)
+                            if (ri[w] >= 0 && (bi < 0 || better(rv[w], ri[w], bv, bi))) { bv = rv[w]; bi = ri[w]; }
+                        const uint32_t tok = bi < 0 ? 0u : (uint32_t)bi;
+                        a.next_tok[m] = tok;
+                        if (a.feed_tok) a.feed_tok[m] = tok;
+                        if (a.pos) {
+                            const int np = a.pos[m] + 1;
+                            a.pos[m] = np;
+                            if (a.hist) a.hist[(size_t)m * a.hist_stride + np] = tok;
+                        }
+                    }
+                }
+                if (tid == 0) *a.fin_ticket = 0u;  // clean for the next launch
+            }
+        }
     } else {  // EPI_QKV_ROPE
         const int hd = a.hd, half = hd >> 1, hps = SLAB / hd;
         // head_dim and the page size are powers of two in every supported model: shifts instead of divisions
