@@ -815,6 +815,7 @@ int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, i
     cudaError_t ce = launch_split_blocks(bd, N, K, q4, 0, -1, scales, codes, st);
     if (ce == cudaSuccess) {
         QuantArgs a{};
+        ce = get_wait_err(&a.err_flag);
         a.scales = scales;
         a.codes = codes;
         a.q4 = q4;
@@ -827,9 +828,12 @@ int hm_gemv_quant(const float* x, const void* blocks, int dtype, int M, int K, i
         a.epi = EPI_STORE;
         a.y = yd;
         a.ldy = N;
-        ce = launch_gemv_quant(a, mp, sm_count_of_current_device(), st, false);
+        if (ce == cudaSuccess) ce = launch_gemv_quant(a, mp, sm_count_of_current_device(), st, false);
     }
-    return sg.finish(ce);
+    const int rc = sg.finish(ce);  // the scratch copies above always stage, so this call synchronised
+    if (rc != HM_OK) return rc;
+    if (take_wait_err()) return gfail(HM_ERR_TIMEOUT, "hm_gemv_quant: a bounded device-side wait ran out");
+    return HM_OK;
 }
 
 int hm_dequant(const void* blocks, int dtype, size_t n_blocks, float* out, void* stream) {

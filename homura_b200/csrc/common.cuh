@@ -373,6 +373,7 @@ struct AttnArgs {
 };
 
 struct QuantArgs {
+    int* err_flag;           // optional: raised to 2 when the bounded wait for the staged weights runs out
     const uint16_t* scales;  // [N/32][K/32][32] f16 bits (launch_split_blocks)
     const uint8_t* codes;    // [N/32][K/32][chunk][32][16 B]: 2 chunks per Q8_0 block, 1 per Q4_0 block
     int q4;                  // 0 = Q8_0, 1 = Q4_0

@@ -813,6 +813,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             ce = launch_gemv_kquant(a, mp, sm_count_, stream_, pdl_);
         } else {
             QuantArgs a{};
+            a.err_flag = err_flag_;
             a.scales = L.scales;
             a.codes = L.codes;
             a.q4 = L.kind == HM_Q4_0;

@@ -252,6 +252,8 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
     const int npieces = ttype == 2 ? 13 : 9;
 
     pdl_launch_dependents();
+    // weights never depend on the previous kernel: ask the L2 for this CTA's super-blocks before the dependency wait
+    if (tid < 32 && nkb > 0) l2_prefetch_slice(tbase, (unsigned long long)nkb * KQ_SLOT_BYTES, 0, 1, tid);
     pdl_wait();
 
     // ---- prologue: activations of this CTA's K range (RMSNorm with an f64 sum of squares on request,
@@ -260,10 +262,27 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
 #pragma unroll
     for (int m = 0; m < M; ++m) inv[m] = 1.0f;
     if (a.pro == PRO_RMSNORM) {
+        constexpr int XV = 8;  // rows of up to 8192 elements: every 16-byte piece requested before the first use
+        const bool vec_row = (a.K & 3) == 0 && a.K <= XV * 4 * KT && (a.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             double s = 0.0;
             const float* xr = a.x + (size_t)m * a.ldx;
+            if (vec_row) {
+                float4 xv[XV];
+#pragma unroll
+                for (int i = 0; i < XV; ++i) {
+                    const int idx = tid + i * KT;
+                    xv[i] = idx < (a.K >> 2) ? ld_cg_f32x4(xr + 4 * (size_t)idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < XV; ++i) {
+                    s += (double)xv[i].x * (double)xv[i].x;
+                    s += (double)xv[i].y * (double)xv[i].y;
+                    s += (double)xv[i].z * (double)xv[i].z;
+                    s += (double)xv[i].w * (double)xv[i].w;
+                }
+            } else
             for (int k = tid; k < a.K; k += KT) {
                 const double v = (double)xr[k];
                 s += v * v;

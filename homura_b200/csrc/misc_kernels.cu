@@ -77,8 +77,33 @@ __global__ void argmax_finish_kernel(const float* amax_val, const int32_t* amax_
     const int m = blockIdx.x;
     float bv = -INFINITY;
     int bi = -1;
-    for (int s = threadIdx.x; s < nslabs; s += blockDim.x) {
-        const float v = amax_val[(size_t)m * nslabs + s];
+    const float* row = amax_val + (size_t)m * nslabs;
+    int done = 0;
+    if (!amax_idx && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // plain logits: 16-byte loads, four in flight per thread (a scalar loop pays one L2 round trip per element)
+        const int n4 = nslabs >> 2;
+        for (int b = threadIdx.x; b < n4; b += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = b + u * blockDim.x;
+                v[u] = idx < n4 ? *reinterpret_cast<const float4*>(row + 4 * (size_t)idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = b + u * blockDim.x;
+                if (idx < n4) {
+                    const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (bi < 0 || better(e[k], 4 * idx + k, bv, bi)) { bv = e[k]; bi = 4 * idx + k; }
+                }
+            }
+        }
+        done = n4 << 2;
+    }
+    for (int s = done + threadIdx.x; s < nslabs; s += blockDim.x) {
+        const float v = row[s];
         const int i = amax_idx ? amax_idx[(size_t)m * nslabs + s] : s;
         if (i >= 0 && (bi < 0 || better(v, i, bv, bi))) { bv = v; bi = i; }
     }

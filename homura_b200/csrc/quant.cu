@@ -18,6 +18,7 @@
 
 #include "common.cuh"
 #include "launch_attrs.h"
+#include "mbarrier.cuh"
 
 namespace hm {
 
@@ -129,12 +130,22 @@ __device__ __forceinline__ void q_block(const uint4 (&c)[2], float d, const floa
     for (int m = 0; m < M; ++m) acc[m] = fmaf(d, p[m], acc[m]);
 }
 
-template <int M, bool Q4, bool CL>
+// ST: the CTA's whole slice of codes and scales (two contiguous byte ranges of the tiled arrays) is pulled into
+// shared memory by two bulk copies issued BEFORE the dependency wait, so that in the decode chain the weights'
+// HBM latency overlaps the launch before this one and the multiply runs out of shared memory.
+template <int M, bool Q4, bool CL, bool ST>
 __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
-    extern __shared__ __align__(16) float qsm[];
+    extern __shared__ __align__(128) float qsm[];
     const int kspan = a.kb_per_split * 32;  // activations this CTA needs
-    float* xs = qsm;                        // [M][kspan]
-    float* red = qsm + M * kspan;           // [8 warps][M][32], then vals [M][32] at red[0..]
+    constexpr int CHB = (Q4 ? 1 : 2) * 512;  // code bytes of one k-block of a 32-row tile
+    // staged weights first (bulk copies want 16-byte aligned destinations): codes, then scales
+    const unsigned char* codes_s = reinterpret_cast<const unsigned char*>(qsm);
+    const uint16_t* scales_s = reinterpret_cast<const uint16_t*>(codes_s + (size_t)a.kb_per_split * CHB);
+    float* xs = ST ? qsm + ((size_t)a.kb_per_split * (CHB + 64)) / 4 : qsm;  // [M][kspan]
+    float* red = xs + M * kspan;            // [8 warps][M][32], then vals [M][32] at red[0..]
+    constexpr int NCHUNK = 4;           // the slice arrives in up to four pieces, each on its own barrier, so that the
+    __shared__ uint64_t s_wbar[NCHUNK];  // multiply of a CTA that started late overlaps the rest of its copies
+    __shared__ volatile int s_abort;
     __shared__ double s_wsum[8][MAX_M];
     __shared__ float s_inv[MAX_M];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -148,22 +159,98 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
 
     pdl_launch_dependents();
 
-    // first batch of weight loads before the dependency wait: weights never depend on a previous kernel
+    // weights never depend on a previous kernel: the whole slice into shared memory (ST), or the first batch of
+    // streaming loads into registers, before the dependency wait
     uint4 c[QU][2];
     uint16_t sc[QU];
+    const int ck = max(8, ((nkb + NCHUNK - 1) / NCHUNK + 7) / 8 * 8);  // k-blocks per piece: a multiple of the 8 warps
+    if (ST) {
+        if (tid == 0) {
+            for (int ch = 0; ch < NCHUNK; ++ch) mb_init(&s_wbar[ch], 1);
+            s_abort = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            const unsigned char* csrc = reinterpret_cast<const unsigned char*>(a.codes) + ((size_t)tile * nb + kb0) * CHB;
+            for (int ch = 0; ch < NCHUNK; ++ch) {
+                const int k_lo = min(nkb, ch * ck), k_hi = min(nkb, k_lo + ck);
+                if (k_hi <= k_lo) break;
+                const uint32_t cbytes = (uint32_t)(k_hi - k_lo) * CHB, sbytes = ch == 0 ? (uint32_t)nkb * 64u : 0u;
+                mb_expect_tx(&s_wbar[ch], cbytes + sbytes);
+                if (sbytes) bulk_copy(const_cast<uint16_t*>(scales_s), a.scales + ((size_t)tile * nb + kb0) * 32, sbytes, &s_wbar[0]);
+                bulk_copy(const_cast<unsigned char*>(codes_s) + (size_t)k_lo * CHB, csrc + (size_t)k_lo * CHB, cbytes, &s_wbar[ch]);
+            }
+        }
+    } else {
 #pragma unroll
-    for (int u = 0; u < QU; ++u) {
-        const int kb = warp + 8 * u;
-        const bool ok = kb < nkb;
+        for (int u = 0; u < QU; ++u) {
+            const int kb = warp + 8 * u;
+            const bool ok = kb < nkb;
 #pragma unroll
-        for (int h = 0; h < CH; ++h) c[u][h] = ok ? ld_stream_u4(cbase + ((size_t)kb * CH + h) * 32) : make_uint4(0, 0, 0, 0);
-        sc[u] = ok ? sbase[(size_t)kb * 32] : (uint16_t)0;
+            for (int h = 0; h < CH; ++h) c[u][h] = ok ? ld_stream_u4(cbase + ((size_t)kb * CH + h) * 32) : make_uint4(0, 0, 0, 0);
+            sc[u] = ok ? sbase[(size_t)kb * 32] : (uint16_t)0;
+        }
+    }
+
+    // RMSNorm weights of the whole row (they do not depend on the previous kernel either): up to XV 16-byte pieces
+    // per thread, requested before the dependency wait
+    constexpr int XV = 8;  // rows of up to 8192 elements take the one-round-trip path below
+    const bool vec_row = a.pro == PRO_RMSNORM && (a.K & 3) == 0 && a.K <= XV * 4 * QT && (a.ldx & 3) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.norm_w)) & 15) == 0;
+    const int k4 = a.K >> 2;
+    float4 nwv[XV];
+    if (vec_row) {
+#pragma unroll
+        for (int i = 0; i < XV; ++i) {
+            const int idx = tid + i * QT;
+            nwv[i] = idx < k4 ? __ldg(reinterpret_cast<const float4*>(a.norm_w) + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
 
     pdl_wait();
 
     // ---- prologue: this CTA's K range of every activation row into shared memory ----
-    if (a.pro == PRO_RMSNORM) {
+    if (vec_row) {
+        // one L2 round trip per row: every piece of the row is requested before the first use, the sum of squares
+        // runs in f64 as the reference's GGUF path does (emitter_quant.rs:713-791), and the pieces that fall into
+        // this CTA's K range go to shared memory straight from the registers
+        const int lo = kb0 * 32, hi = lo + nkb * 32;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float4* xr4 = reinterpret_cast<const float4*>(a.x + (size_t)m * a.ldx);
+            float4 xv[XV];
+#pragma unroll
+            for (int i = 0; i < XV; ++i) {
+                const int idx = tid + i * QT;
+                xv[i] = idx < k4 ? ld_cg_f32x4(reinterpret_cast<const float*>(xr4 + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            double s = 0.0;
+#pragma unroll
+            for (int i = 0; i < XV; ++i) {
+                s += (double)xv[i].x * (double)xv[i].x;
+                s += (double)xv[i].y * (double)xv[i].y;
+                s += (double)xv[i].z * (double)xv[i].z;
+                s += (double)xv[i].w * (double)xv[i].w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) s_wsum[warp][m] = s;
+            __syncthreads();
+            if (tid == 0) {
+                double t = 0.0;
+                for (int wv = 0; wv < 8; ++wv) t += s_wsum[wv][m];
+                const float mean = (float)(t * (1.0 / (double)a.K));
+                s_inv[m] = 1.0f / sqrtf(mean + a.eps);
+            }
+            __syncthreads();
+            const float inv = s_inv[m];
+#pragma unroll
+            for (int i = 0; i < XV; ++i) {
+                const int e = (tid + i * QT) * 4;
+                if (e >= lo && e < hi)
+                    *reinterpret_cast<float4*>(xs + m * kspan + (e - lo)) =
+                        make_float4((xv[i].x * inv) * nwv[i].x, (xv[i].y * inv) * nwv[i].y, (xv[i].z * inv) * nwv[i].z, (xv[i].w * inv) * nwv[i].w);
+            }
+        }
+    } else if (a.pro == PRO_RMSNORM) {
         // sum of squares in f64 over the whole row (emitter_quant.rs:713-791)
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -192,17 +279,32 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
             for (int k = tid; k < nkb * 32; k += QT) xs[m * kspan + k] = (xr[k] * inv) * a.norm_w[kb0 * 32 + k];
         }
     } else {
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const float* xr = a.x + (size_t)m * a.ldx + kb0 * 32;
-            for (int k = tid; k < nkb * 32; k += QT) xs[m * kspan + k] = xr[k];
-        }
+        // the loads of all rows are issued before the first store (one L2 round trip per 1024 elements of a row)
+        stage_rows<QT, M>(a.x + kb0 * 32, a.ldx, xs, kspan, nkb * 32, tid);
     }
     __syncthreads();
 
     float acc[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    if (ST) {
+        // every thread waits (bounded) for the two bulk copies, then the warp's k-blocks come from shared memory:
+        // lane = output row, 16-byte reads of consecutive lanes are consecutive (no bank conflicts)
+        int waited = -1;
+        bool ok = true;
+        for (int kb = warp; kb < nkb && ok; kb += 8) {
+            const int ch = kb / ck;
+            while (waited < ch && ok) {
+                ++waited;
+                ok = __all_sync(0xffffffffu, mb_wait(&s_wbar[waited], 0, a.err_flag, &s_abort));
+            }
+            if (!ok) break;
+            uint4 cc[2];
+#pragma unroll
+            for (int h = 0; h < CH; ++h) cc[h] = *reinterpret_cast<const uint4*>(codes_s + ((size_t)(kb * CH + h) * 32 + lane) * 16);
+            q_block<M, Q4>(cc, f16_bits_to_f32(scales_s[kb * 32 + lane]), xs + kb * 32, kspan, acc);
+        }
+    } else
     for (int base = warp; base < nkb; base += 8 * QU) {
         // issue the next batch, then consume the current one
         uint4 cn[QU][2];
@@ -278,12 +380,29 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
     }
 }
 
+constexpr size_t QUANT_STAGE_MAX = 96 * 1024;  // largest weight slice staged in shared memory (two CTAs per SM stay resident)
+
+template <int M, bool Q4, bool CL, bool ST>
+cudaError_t launch_q4(const QuantArgs& a, size_t smem, cudaStream_t st, bool pdl);
+
 template <int M, bool Q4, bool CL>
 cudaError_t launch_q3(const QuantArgs& a, cudaStream_t st, bool pdl) {
-    const size_t smem = sizeof(float) * ((size_t)M * a.kb_per_split * 32 + 8 * M * 32 + (CL ? (size_t)a.ksplit * M * 32 : 0));
+    size_t smem = sizeof(float) * ((size_t)M * a.kb_per_split * 32 + 8 * M * 32 + (CL ? (size_t)a.ksplit * M * 32 : 0));
+    const size_t slice = (size_t)a.kb_per_split * ((Q4 ? 1 : 2) * 512 + 64);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.scales)) & 15) == 0;
+#ifndef HM_QUANT_NO_STAGE
+    if (aligned && slice <= QUANT_STAGE_MAX && smem + slice <= 110 * 1024) return launch_q4<M, Q4, CL, true>(a, smem + slice, st, pdl);
+#endif
+    (void)slice;
+    (void)aligned;
+    return launch_q4<M, Q4, CL, false>(a, smem, st, pdl);
+}
+
+template <int M, bool Q4, bool CL, bool ST>
+cudaError_t launch_q4(const QuantArgs& a, size_t smem, cudaStream_t st, bool pdl) {
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     {
-        cudaError_t e = ensure_dyn_smem(gemv_quant_kernel<M, Q4, CL>, smem);
+        cudaError_t e = ensure_dyn_smem(gemv_quant_kernel<M, Q4, CL, ST>, smem);
         if (e != cudaSuccess) return e;
     }
     const int tiles = (a.N + 31) / 32;
@@ -308,7 +427,7 @@ cudaError_t launch_q3(const QuantArgs& a, cudaStream_t st, bool pdl) {
     }
     cfg.attrs = at;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, gemv_quant_kernel<M, Q4, CL>, a);
+    return cudaLaunchKernelEx(&cfg, gemv_quant_kernel<M, Q4, CL, ST>, a);
 }
 
 template <int M>
@@ -317,7 +436,7 @@ cudaError_t launch_qm(const QuantArgs& a_in, int sm_count, cudaStream_t st, bool
     const int nb = a.K / 32, tiles = (a.N + 31) / 32;
     // K split: enough CTAs for two per SM, at most 8 per cluster, at least one k-block per warp, and
     // an activation slice of at most 48 KB
-    int ks = (2 * sm_count + tiles - 1) / tiles;
+    int ks = (2 * sm_count + tiles - 1) / tiles;  // measured: one or three and more CTAs per SM are slower on every format
     if (ks > 8) ks = 8;
     while (ks > 1 && nb / ks < 8) --ks;
     const int max_kb = std::max(1, (12288 / M) / 32);
