@@ -428,11 +428,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
                 const int slot = idx / TL::PIECES, piece = idx % TL::PIECES;
                 const int p = pbase + slot;
                 if (p >= lo && p < hi) {
-                    const int e = piece * TL::PER16, t = e / HD, d = e % HD;
+                    const int e = piece * TL::PER16;
                     float* base = tiles + (slot_base + slot) * TL::SLOT_FLOATS;
-                    // K pages are chunk-major (k_tile_off) and stay so in shared memory: a straight copy
+                    // K pages are chunk-major (k_tile_off) and stay so in shared memory: a straight copy;
+                    // V pages (chunks of 8 elements, v_tile_off) become rows [token][dim] here
+                    const int vt_tok = (e >> 3) & (PT - 1), vd = ((e >> 7) << 3) | (e & 7);
                     unpack_store<BF16>(base + e, kreg[i]);
-                    unpack_store<BF16>(base + PT * TL::KLD + t * HD + d, vreg[i]);
+                    unpack_store<BF16>(base + PT * TL::KLD + vt_tok * HD + vd, vreg[i]);
                 }
             }
         }
@@ -819,7 +821,8 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
                 __syncwarp();
                 // ---- out^T += V^T . P^T ----
                 const int mj = lane >> 3, mr = lane & 7;  // ldmatrix: this lane addresses row mr of matrix mj
-                const unsigned char* vrow = vt + ((size_t)((mj >> 1) * 8 + mr) * HD + (mj & 1) * 8) * 2;
+                // V tile: chunks of 8 dims, V[d / 8][token][d % 8]; matrix mj = tokens (mj / 2) * 8 .. + 7 of chunk 2 * mt + mj % 2
+                const unsigned char* vrow = vt + ((size_t)((mj & 1) * PT + (mj >> 1) * 8 + mr) * 8) * 2;
 #pragma unroll
                 for (int mt = 0; mt < HD / 16; ++mt) {
                     to[mt][0] *= corr[0];
@@ -827,7 +830,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
                     to[mt][2] *= corr[0];
                     to[mt][3] *= corr[1];
                     uint32_t av[4];
-                    ldmatrix_x4_trans(av, vrow + mt * 32);
+                    ldmatrix_x4_trans(av, vrow + (size_t)mt * (2 * PT * 8 * 2));
 #pragma unroll
                     for (int t3 = 0; t3 < 3; ++t3) mma_bf16_m16n8k16(to[mt], av[0], av[1], av[2], av[3], b0[t3], b1[t3]);
                 }
@@ -899,11 +902,11 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     if (BF16) {
-                        const uint16_t* vr = reinterpret_cast<const uint16_t*>(vt) + (t4 + u) * HD + lane * EPL;
+                        const uint16_t* vr = reinterpret_cast<const uint16_t*>(vt) + v_tile_off(t4 + u, lane * EPL, HD);
 #pragma unroll
                         for (int e = 0; e < EPL; ++e) vv[u][e] = bf16_bits_to_f32(vr[e]);
                     } else {
-                        const float* vr = reinterpret_cast<const float*>(vt) + (t4 + u) * HD + lane * EPL;
+                        const float* vr = reinterpret_cast<const float*>(vt) + v_tile_off(t4 + u, lane * EPL, HD);
 #pragma unroll
                         for (int e = 0; e < EPL; ++e) vv[u][e] = vr[e];
                     }
