@@ -87,8 +87,6 @@ int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* 
     const char* nocl = std::getenv("HM_NO_CLUSTER");
     e->use_clusters_ = !(nocl && nocl[0] == '1');
     e->max_cluster_ = gemv_max_cluster();
-    const char* nopf = std::getenv("HM_NO_PREFETCH");
-    e->use_prefetch_ = !(nopf && nopf[0] == '1');
     const char* notc = std::getenv("HM_NO_TC");
     e->use_tc_ = !(notc && notc[0] == '1');
     *out = e;
@@ -509,10 +507,6 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     // of attn_pick_nsplit answers with few splits of many pages each, i.e. the bulk-copy ring kernel
     att_cluster_ = use_clusters_ && max_pages_ <= 64 && (long)batch * kvh_ < sm_count_ / 2;
     att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 16)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
-    if (const char* ns = std::getenv("HM_ATT_NSPLIT")) {  // tuning knob: CTAs per (row, KV head)
-        const int v = std::atoi(ns);
-        if (v >= 1 && v <= (att_cluster_ ? std::min(max_cluster_, 16) : sm_count_)) att_nsplit_ = v;
-    }
     HM_CUDA(cudaMalloc(&att_acc_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * hd_ * 4));
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
     HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));

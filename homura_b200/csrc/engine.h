@@ -115,7 +115,7 @@ class Engine {
     bool finalized_ = false, quant_ = false, pdl_ = true;
     bool use_clusters_ = true;  // split reductions through thread-block clusters / DSMEM (HM_NO_CLUSTER=1: global scratch + tickets)
     int max_cluster_ = 8;
-    bool use_prefetch_ = true;  // decode kernels pull the weights of the kernel two launches ahead into the L2 (HM_NO_PREFETCH=1 disables)
+    bool use_prefetch_ = true;  // decode kernels pull the weights of the kernel two launches ahead into the L2
     const void* pf_ptr_ = nullptr;  // prefetch target handed to the next projection launch
     unsigned long long pf_bytes_ = 0;
     bool use_tc_ = true;  // bf16 models: passes over more than 8 rows run the tcgen05 GEMM (HM_NO_TC=1: 8-row groups of the streaming kernel)

@@ -616,10 +616,8 @@ cudaError_t launch_mc(const GemvArgs& a_in, cudaStream_t st, bool pdl) {
     if (a.epi == EPI_QKV_ROPE) floats += 2 * (size_t)M * SLAB + SLAB;  // pre-fetched RoPE rows and bias
     size_t smem = sizeof(float) * floats;
     // cluster launches over the slab layout whose slice fits: weights staged in shared memory before the dependency wait
-    static const bool no_stage = [] { const char* e = std::getenv("HM_NO_STAGE"); return e && e[0] == '1'; }();
     const size_t slice = (size_t)a.rows_per_split * SLAB * 2;
-    static const size_t stage_max = [] { const char* e = std::getenv("HM_STAGE_MAX_KB"); return e ? (size_t)std::atoi(e) * 1024 : GEMV_STAGE_MAX; }();  // tuning knob
-    if (CL && !no_stage && a.row_stride == SLAB * 2 && slice <= stage_max && ((uintptr_t)a.W & 15) == 0) {
+    if (CL && a.row_stride == SLAB * 2 && slice <= GEMV_STAGE_MAX && ((uintptr_t)a.W & 15) == 0) {
         smem += slice;
         return launch_mcs<M, true, true>(a, smem, nslabs, st, pdl);
     }
@@ -663,10 +661,7 @@ void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_p
 // max_cluster, at least 32 rows each.
 void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* cluster, int* rows_per_split) {
     const int nslabs = (N + SLAB - 1) / SLAB;
-    static const int per_sm = [] { const char* e = std::getenv("HM_GEMV_CTAS_PER_SM"); const int v = e ? std::atoi(e) : 0; return v >= 1 && v <= 8 ? v : 2; }();
-    int cs = (per_sm * sm_count) / nslabs;  // two CTAs per SM resident at once (tuning knob: HM_GEMV_CTAS_PER_SM)
-    static const int wide_cs = [] { const char* e = std::getenv("HM_GEMV_WIDE_CLUSTER"); return e ? std::atoi(e) : 0; }();  // tuning knob: cluster size of projections with 32 slabs or more
-    if (wide_cs >= 1 && nslabs >= 32) cs = wide_cs;
+    int cs = (2 * sm_count) / nslabs;  // two CTAs per SM resident at once (one per SM measured 1.5x slower on the widest projection)
     if (cs > max_cluster) cs = max_cluster;
     if (cs < 1) cs = 1;
     while (cs > 1 && K / cs < 32) --cs;
