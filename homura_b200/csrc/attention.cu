@@ -431,8 +431,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
                     const int e = piece * TL::PER16;
                     float* base = tiles + (slot_base + slot) * TL::SLOT_FLOATS;
                     // K pages are chunk-major (k_tile_off) and stay so in shared memory: a straight copy;
-                    // V pages (chunks of 8 elements, v_tile_off) become rows [token][dim] here
-                    const int vt_tok = (e >> 3) & (PT - 1), vd = ((e >> 7) << 3) | (e & 7);
+                    // V pages (bf16: chunks of 8 elements, v_tile_off; f32: rows already) become rows [token][dim] here
+                    const int vt_tok = BF16 ? (e >> 3) & (PT - 1) : e / HD, vd = BF16 ? ((e >> 7) << 3) | (e & 7) : e % HD;
                     unpack_store<BF16>(base + e, kreg[i]);
                     unpack_store<BF16>(base + PT * TL::KLD + vt_tok * HD + vd, vreg[i]);
                 }
@@ -902,11 +902,11 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     if (BF16) {
-                        const uint16_t* vr = reinterpret_cast<const uint16_t*>(vt) + v_tile_off(t4 + u, lane * EPL, HD);
+                        const uint16_t* vr = reinterpret_cast<const uint16_t*>(vt) + v_tile_off(t4 + u, lane * EPL, HD, BF16 ? 1 : 0);
 #pragma unroll
                         for (int e = 0; e < EPL; ++e) vv[u][e] = bf16_bits_to_f32(vr[e]);
                     } else {
-                        const float* vr = reinterpret_cast<const float*>(vt) + v_tile_off(t4 + u, lane * EPL, HD);
+                        const float* vr = reinterpret_cast<const float*>(vt) + v_tile_off(t4 + u, lane * EPL, HD, BF16 ? 1 : 0);
 #pragma unroll
                         for (int e = 0; e < EPL; ++e) vv[u][e] = vr[e];
                     }

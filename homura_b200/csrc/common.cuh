@@ -229,18 +229,16 @@ __device__ __forceinline__ float warp_max(float v) {
 enum Prologue { PRO_PLAIN = 0, PRO_RMSNORM = 1 };
 enum Epilogue { EPI_STORE = 0, EPI_QKV_ROPE = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
 
-// Element offsets inside one [16 tokens][hd] page tile.  Both tiles are chunk-major: the chunk c of every token is
-// stored together, so that the 16 tokens' copies of one chunk are one contiguous run and the tile is still one
+// Element offsets inside one [16 tokens][hd] page tile.  Chunk-major means: the chunk c of every token is stored
+// together, so that the 16 tokens' copies of one chunk are one contiguous run; either way the tile is one
 // contiguous block of the pool (one bulk copy).
 //   K: chunks of 4 elements, K[d / 4][token][d % 4]: attention lanes that own one token each read a chunk
 //      without bank conflicts while the matching query chunk is a broadcast.
-//   V: chunks of 8 elements, V[d / 8][token][d % 8]: on bf16 pages a chunk is 16 bytes, so the eight rows of
-//      an 8x8 matrix that ldmatrix fetches for the P.V MMA (8 tokens of one chunk) are 128 contiguous bytes.
+//   V on bf16 pages: chunks of 8 elements, V[d / 8][token][d % 8]: a chunk is 16 bytes, so the eight rows of an
+//      8x8 matrix that ldmatrix fetches for the P.V MMA (8 tokens of one chunk) are 128 contiguous bytes.
+//   V on f32 pages: rows, V[token][d]: the CUDA-core kernels read one token's row with consecutive lanes.
 __host__ __device__ __forceinline__ int k_tile_off(int t, int d) { return ((((d >> 2) << 4) + t) << 2) | (d & 3); }
-__host__ __device__ __forceinline__ int v_tile_off(int t, int d, int hd) {
-    (void)hd;
-    return ((((d >> 3) << 4) + t) << 3) | (d & 7);
-}
+__host__ __device__ __forceinline__ int v_tile_off(int t, int d, int hd, int bf16) { return bf16 ? (((((d >> 3) << 4) + t) << 3) | (d & 7)) : t * hd + d; }
 
 // One activation value into the packed bf16 x 3 tile image the tensor-core GEMM copies in bulk
 // (gemm_tc.cu: [k-block][term][mpad rows][64 k], rows of 128 B, 16-byte chunks XOR-swizzled by row & 7):

@@ -303,8 +303,8 @@ __device__ void tc_epilogue(const TcArgs& a, float* tile, int m_lo, int m_hi, in
                 const int kvh = (nh - a.q_dim - (is_k ? 0 : a.kv_dim)) / hd;
                 const int tok = pos % a.kv.page_tokens;
                 const size_t base = ((size_t)s_page[m] * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd;
-                const size_t o0 = base + (is_k ? k_tile_off(tok, d0) : v_tile_off(tok, d0, hd));
-                const size_t o1 = base + (is_k ? k_tile_off(tok, half + d0) : v_tile_off(tok, half + d0, hd));
+                const size_t o0 = base + (is_k ? k_tile_off(tok, d0) : v_tile_off(tok, d0, hd, a.kv.bf16));
+                const size_t o1 = base + (is_k ? k_tile_off(tok, half + d0) : v_tile_off(tok, half + d0, hd, a.kv.bf16));
                 void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
                 if (a.kv.bf16) {
                     uint16_t* pp = reinterpret_cast<uint16_t*>(pool);

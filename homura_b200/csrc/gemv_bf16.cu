@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
                 const int kvh = p2 ? rel >> hs : rel / hd;
                 const int page = s_page[m];
                 const int tok = p2 ? pos & (a.kv.page_tokens - 1) : pos % a.kv.page_tokens;
-                const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd));
+                const size_t off = ((size_t)page * a.kv.kv_heads + kvh) * a.kv.page_tokens * hd + (is_k ? k_tile_off(tok, d) : v_tile_off(tok, d, hd, a.kv.bf16));
                 void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
                 if (a.kv.bf16)
                     reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(v);

@@ -239,7 +239,7 @@ __global__ void kv_write_rows_kernel(KvDesc kv, int seq, int pos0, const float* 
         const int pos = pos0 + s;
         const int page = kv.page_table[(size_t)seq * kv.max_pages + pos / kv.page_tokens];
         const size_t tile = ((size_t)page * kv.kv_heads + h) * kv.page_tokens * kv.hd;
-        const size_t ko = tile + k_tile_off(pos % kv.page_tokens, d), vo = tile + v_tile_off(pos % kv.page_tokens, d, kv.hd);
+        const size_t ko = tile + k_tile_off(pos % kv.page_tokens, d), vo = tile + v_tile_off(pos % kv.page_tokens, d, kv.hd, kv.bf16);
         if (kv.bf16) {
             if (k_rows) reinterpret_cast<uint16_t*>(kv.k_pool)[ko] = f32_to_bf16_rne(k_rows[i]);
             if (v_rows) reinterpret_cast<uint16_t*>(kv.v_pool)[vo] = f32_to_bf16_rne(v_rows[i]);
@@ -258,7 +258,7 @@ __global__ void kv_read_rows_kernel(KvDesc kv, int seq, int len, float* k_out, f
         const int h = (int)(i / ((size_t)kv.hd * len));
         const int page = kv.page_table[(size_t)seq * kv.max_pages + pos / kv.page_tokens];
         const size_t tile = ((size_t)page * kv.kv_heads + h) * kv.page_tokens * kv.hd;
-        const size_t ko = tile + k_tile_off(pos % kv.page_tokens, d), vo = tile + v_tile_off(pos % kv.page_tokens, d, kv.hd);
+        const size_t ko = tile + k_tile_off(pos % kv.page_tokens, d), vo = tile + v_tile_off(pos % kv.page_tokens, d, kv.hd, kv.bf16);
         if (kv.bf16) {
             k_out[i] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(kv.k_pool)[ko]);
             v_out[i] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(kv.v_pool)[vo]);
@@ -328,7 +328,7 @@ __global__ void post_qkv_kernel(const float* qkv, int M, int heads, int kv_heads
         void* pool = is_k ? kv.k_pool : kv.v_pool;
         for (int e = 0; e < per; ++e) {
             const int d = lane + 32 * e;
-            const size_t off = tile + (is_k ? k_tile_off(pos % kv.page_tokens, d) : v_tile_off(pos % kv.page_tokens, d, hd));
+            const size_t off = tile + (is_k ? k_tile_off(pos % kv.page_tokens, d) : v_tile_off(pos % kv.page_tokens, d, hd, kv.bf16));
             if (kv.bf16) reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(val[e]);
             else reinterpret_cast<float*>(pool)[off] = val[e];
         }

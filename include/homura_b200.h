@@ -255,10 +255,10 @@ HM_API int hm_rms_norm(const float* x, const float* w, float eps, int rows, int 
 HM_API int hm_qknorm_rope(float* x, int rows, int heads, int hd, const float* norm_w, float eps, const float* cos_rows, const float* sin_rows, void* stream);
 /* GQA decode attention over a paged cache (src/hf/emitter.rs:683-737, floordiv head map of
  * src/graph_builder/emit_linalg.rs:93-245): q [B, heads, hd] f32; k_pages and v_pages are blocks
- * [n_pages, kv_heads] of one [page_tokens, hd] tile each, of kv_dtype, stored chunk-major the way the
- * engine's KV-write epilogues lay them out: K in chunks of 4 elements, [hd/4][page_tokens][4] (element
- * (t, d) at ((d/4)*page_tokens + t)*4 + d%4), V in chunks of 8, [hd/8][page_tokens][8] (element (t, d) at
- * ((d/8)*page_tokens + t)*8 + d%8);
+ * [n_pages, kv_heads] of one [page_tokens, hd] tile each, of kv_dtype, stored the way the engine's
+ * KV-write epilogues lay them out: K chunk-major in chunks of 4 elements, [hd/4][page_tokens][4] (element
+ * (t, d) at ((d/4)*page_tokens + t)*4 + d%4); V as rows [page_tokens][hd] on f32 pages and chunk-major in
+ * chunks of 8 on bf16 pages, [hd/8][page_tokens][8] (element (t, d) at ((d/8)*page_tokens + t)*8 + d%8);
  * page_table [B, max_pages] int32;
  * kv_len [B] int32; out [B, heads*hd] f32.  A host kv_len is range-checked; a kv_len in device
  * memory is trusted (entries must lie in [1, max_pages*page_tokens]) and the call stays asynchronous

@@ -150,9 +150,10 @@ def _paged(rng, B, kvh, hd, lens, bf16, hm):
         ks.append(k)
         vs.append(v)
     kd, vd = hm.DeviceBuffer(kpool.nbytes), hm.DeviceBuffer(vpool.nbytes)
-    # tiles are stored chunk-major inside a page: K as [hd/4][16 tokens][4], V as [hd/8][16 tokens][8]
+    # K tiles are stored chunk-major inside a page, [hd/4][16 tokens][4]; V tiles are rows [16 tokens][hd] on f32 pages
+    # and chunk-major [hd/8][16 tokens][8] on bf16 pages
     kd.upload(np.ascontiguousarray(kpool.reshape(n_pages, kvh, PT, hd // 4, 4).transpose(0, 1, 3, 2, 4)))
-    vd.upload(np.ascontiguousarray(vpool.reshape(n_pages, kvh, PT, hd // 8, 8).transpose(0, 1, 3, 2, 4)))
+    vd.upload(np.ascontiguousarray(vpool.reshape(n_pages, kvh, PT, hd // 8, 8).transpose(0, 1, 3, 2, 4)) if bf16 else vpool)
     return kd, vd, perm, max_pages, ks, vs
 
 
@@ -200,7 +201,7 @@ def test_attention_long_context_property(hm):
     v = rng.standard_normal((pages, kvh, PT, hd), dtype=np.float32)
     kd, vd = hm.DeviceBuffer(k.nbytes), hm.DeviceBuffer(v.nbytes)
     kd.upload(k)  # all ones: any layout
-    vd.upload(np.ascontiguousarray(v.reshape(pages, kvh, PT, hd // 8, 8).transpose(0, 1, 3, 2, 4)))  # V tiles: chunks of 8
+    vd.upload(v)  # f32 pages: V tiles are rows
     q = rng.standard_normal((1, heads, hd), dtype=np.float32)
     got = hm.attn_decode_paged(q, kd, vd, hm.DType.F32, perm, [L], heads, kvh, hd, pages).reshape(heads, hd)
     mean_v = v.astype(np.float64).mean(axis=(0, 2))  # [kvh, hd]
@@ -250,7 +251,7 @@ def test_attention_full_size_against_oracle(hm, oracle, B, L, bf16):
             keep[b] = (k, v)
     kd, vd = hm.DeviceBuffer(kpool.nbytes), hm.DeviceBuffer(vpool.nbytes)
     kd.upload(np.ascontiguousarray(kpool.reshape(n_pages, kvh, PT, hd // 4, 4).transpose(0, 1, 3, 2, 4)))  # K tiles: chunks of 4
-    vd.upload(np.ascontiguousarray(vpool.reshape(n_pages, kvh, PT, hd // 8, 8).transpose(0, 1, 3, 2, 4)))  # V tiles: chunks of 8
+    vd.upload(np.ascontiguousarray(vpool.reshape(n_pages, kvh, PT, hd // 8, 8).transpose(0, 1, 3, 2, 4)) if bf16 else vpool)  # V tiles: chunks of 8 on bf16 pages
     del kpool, vpool
     q = rng.standard_normal((B, heads, hd), dtype=np.float32)
     got = hm.attn_decode_paged(q, kd, vd, hm.DType.BF16 if bf16 else hm.DType.F32, perm, [L] * B, heads, kvh, hd, pages).reshape(B, heads, hd)
