@@ -329,7 +329,19 @@ def main():
     m.decode_greedy_n(first, 0)
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
+    rt = None
+    if args.device_only:
+        # a profiler started with `--profile-from-start off` sees the timed decode steps only (not the load and prefill launches)
+        try:
+            import torch
+
+            rt = torch.cuda.cudart()
+            rt.cudaProfilerStart()
+        except Exception:
+            rt = None
     ms = m.time_decode(W, K)
+    if rt is not None:
+        rt.cudaProfilerStop()
     barrier()
     clocks = sampler.stop() if sampler else None
     ms_max = vmax(ms)
