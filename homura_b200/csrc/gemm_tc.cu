@@ -329,7 +329,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     const int mpad = a.mpad;
     const uint32_t x_tile = (uint32_t)(TERMS * mpad * 128);
     const uint32_t stage_bytes = W_TILE + x_tile;  // multiple of 1024 for mpad in {16, 32, 64}
-    float* out_tile = reinterpret_cast<float*>(stage0 + (size_t)a.nstage * stage_bytes);  // [mpad][BM] f32
+    // [mpad][BM] f32, written only after the last MMA has completed: it reuses the first stage of the ring (by then
+    // every bulk copy has landed and every operand has been read), which keeps the CTA's footprint to the ring alone
+    float* out_tile = reinterpret_cast<float*>(stage0);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cs = CL ? a.ksplit : 1;
@@ -503,8 +505,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
 }  // namespace
 
 int tc_mpad(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
-static int tc_nstage(int mpad) { return mpad == 64 ? 4 : 6; }
-static size_t tc_smem_for(int mpad) { return (size_t)tc_nstage(mpad) * (W_TILE + (size_t)TERMS * mpad * 128) + (size_t)mpad * BM * 4 + 1024; }
+// Stages of the ring.  Launches of one wave (at most one CTA per SM: every layer projection of the 0.5-1.5 B
+// models) take the deep ring, because the main loop of a lone CTA is bound by the bytes it keeps in flight
+// (measured on the 1.5 B x 64 step: 2.02 ms with 4 stages, 2.10 with 3, 2.30 with 2).  Launches of several
+// waves (the LM head: 1187 blocks) take two stages, which lets two CTAs share an SM (81 KB and 256 TMEM columns
+// each): the head and tail of one CTA overlap the main loop of the other (LM head 194 -> 152 us).
+static int tc_nstage(int mpad, bool multi_wave) {
+    if (mpad == 64) return multi_wave ? 2 : 4;
+    return multi_wave ? 3 : 6;
+}
+static size_t tc_smem_for(int mpad, bool multi_wave) { return (size_t)tc_nstage(mpad, multi_wave) * (W_TILE + (size_t)TERMS * mpad * 128) + 1024; }
 size_t tc_packed_elems(int K, int N) { return (size_t)((N + BM - 1) / BM) * ((K + BK - 1) / BK) * BM * BK; }
 int tc_padded_k(int K) { return (K + BK - 1) / BK * BK; }
 size_t tc_xpack_bytes(int M, int K) { return (size_t)(tc_padded_k(K) / BK) * TERMS * tc_mpad(M) * 128; }
@@ -535,13 +545,16 @@ cudaError_t launch_gemm_tc(const TcArgs& a_in, cudaStream_t st, bool pdl) {
     TcArgs a = a_in;
     if (a.M < 1 || a.M > MR || a.Kp % BK != 0 || !a.xp) return cudaErrorInvalidValue;
     a.mpad = tc_mpad(a.M);
-    a.nstage = tc_nstage(a.mpad);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const bool multi_wave = (long)((a.N + BM - 1) / BM) * (a.ksplit > 1 ? a.ksplit : 1) >= 2L * sms;
+    a.nstage = tc_nstage(a.mpad, multi_wave);
     a.tmem_cols = a.mpad == 16 ? 64 : a.mpad == 32 ? 128 : 256;  // power of two >= 3 * mpad
     const int nblk = (a.N + BM - 1) / BM;
     const bool cl = a.ksplit > 1;
-    const size_t smem = tc_smem_for(a.mpad);
+    const size_t smem = tc_smem_for(a.mpad, multi_wave);
     {
-        const size_t mx = tc_smem_for(64) > tc_smem_for(32) ? tc_smem_for(64) : tc_smem_for(32);
+        const size_t mx = tc_smem_for(64, false) > tc_smem_for(32, false) ? tc_smem_for(64, false) : tc_smem_for(32, false);
         cudaError_t e = cl ? ensure_dyn_smem(gemm_tc_kernel<true>, mx) : ensure_dyn_smem(gemm_tc_kernel<false>, mx);
         if (e != cudaSuccess) return e;
     }
