@@ -1048,7 +1048,9 @@ int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
         const long waves = (pairs * n + slots - 1) / slots;
         // doubled so that the half page per partial stays an integer; a page costs the short-context
         // kernel about twice what it costs the streaming one (every query head re-reads the tile)
-        const long cost = 2 * waves * (8 + (streaming ? ppc : 2 * ppc)) + n;
+        // having any split at all costs a round trip of the partial triples through global memory, a ticket and a
+        // second merge by the last CTA: about twenty pages' worth (64 sequences at 36 pages: one split 15.4 us, two 17.1)
+        const long cost = 2 * waves * (8 + (streaming ? ppc : 2 * ppc)) + n + (n > 1 ? 40 : 0);
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best = n;

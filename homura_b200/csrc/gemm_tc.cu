@@ -67,6 +67,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 
 struct TcShared {
     uint64_t full[NSTG], empty[NSTG], acc_full;
+    uint64_t rbar;  // split-K: counts the bytes of the other ranks' partial rows arriving in this CTA's receive slots
     uint32_t tmem_base;
     volatile int abort_flag;
     float inv[MR];  // per activation row: the RMSNorm factor applied to the accumulators (ss_in given)
@@ -332,6 +333,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     // [mpad][BM] f32, written only after the last MMA has completed: it reuses the first stage of the ring (by then
     // every bulk copy has landed and every operand has been read), which keeps the CTA's footprint to the ring alone
     float* out_tile = reinterpret_cast<float*>(stage0);
+    // split-K: receive slots [rank][this CTA's rows][BM] behind the ring (peers write here while this CTA's ring is
+    // still in use, so they cannot share its memory)
+    float* recv = reinterpret_cast<float*>(stage0 + (size_t)a.nstage * stage_bytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cs = CL ? a.ksplit : 1;
@@ -353,8 +357,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
         }
         mb_init(&sh.acc_full, 1);
         sh.abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (CL) {
+            // the other ranks push their partial sums of this CTA's rows with asynchronous stores that count bytes
+            // on this barrier: armed now, published by the cluster barrier below (both before the dependency wait)
+            mb_init(&sh.rbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            const int rows_per0 = (a.M + cs - 1) / cs;
+            const int lo0 = min(a.M, split * rows_per0), hi0 = min(a.M, lo0 + rows_per0);
+            mb_expect_tx(&sh.rbar, (uint32_t)(cs - 1) * (uint32_t)(hi0 - lo0) * (uint32_t)(BM * 4));
+        } else {
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
     }
+    if (CL) cluster_sync_all(); else
     __syncthreads();
     if (warp == 1) {  // TMEM: allocated and later freed by this warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh.tmem_base)), "r"(a.tmem_cols) : "memory");
@@ -466,38 +481,47 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs a) 
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
 
-    // ---- with split-K the accumulators are first reduce-scattered by activation row through
-    //      distributed shared memory: each CTA sums, in rank order, its share of the rows (peers only
-    //      read rows that are not theirs, so the sums can be written back in place)
+    // ---- with split-K the accumulators are first reduce-scattered by activation row: every CTA pushes the rows
+    //      that belong to a peer into that peer's receive slot `rank` with 16-byte asynchronous stores that count
+    //      bytes on the peer's mbarrier, waits (bounded) for its own rows from the other ranks, and adds them in
+    //      rank order.  No cluster barrier after the dependency wait, and a CTA is free to exit once it has its rows.
     pdl_wait();
     HM_TRACE(if (tr && tid == 0) a.trace[6] = global_timer();)
     int m_lo = 0, m_hi = a.M;
     if (CL) {
-        cluster_sync_all();
-        HM_TRACE(if (tr && tid == 0) a.trace[7] = global_timer();)
         const int rows_per = (a.M + cs - 1) / cs;
         m_lo = min(a.M, split * rows_per);
         m_hi = min(a.M, m_lo + rows_per);
-        // four consecutive features per thread, every rank's copy requested before the first add (a loop of
-        // dependent remote loads costs one DSMEM round trip per rank: 4 us for eight ranks)
-        for (int idx = tid; idx < (m_hi - m_lo) * (BM / 4); idx += TC_THREADS) {
-            const int off = (m_lo + idx / (BM / 4)) * BM + (idx % (BM / 4)) * 4;
-            float4 v[16];
+        for (int idx = tid; idx < a.M * (BM / 4); idx += TC_THREADS) {
+            const int m = idx / (BM / 4), c = (idx % (BM / 4)) * 4;
+            const int owner = m / rows_per;
+            if (owner == split) continue;
+            const float4 v = *reinterpret_cast<const float4*>(out_tile + m * BM + c);
+            float* dst = recv + ((size_t)split * rows_per + (m - owner * rows_per)) * BM + c;
+            st_async_f32x4(dsmem_addr(dst, (uint32_t)owner), v, dsmem_addr(&sh.rbar, (uint32_t)owner));
+        }
+        HM_TRACE(if (tr && tid == 0) a.trace[7] = global_timer();)
+        const bool got = cs == 1 || mb_wait_cluster(&sh.rbar, 0, a.err_flag, &sh.abort_flag);
+        if (got) {
+            // four consecutive features per thread; every rank's piece is read before the first add
+            for (int idx = tid; idx < (m_hi - m_lo) * (BM / 4); idx += TC_THREADS) {
+                const int ml = idx / (BM / 4), c = (idx % (BM / 4)) * 4;
+                float4 v[16];
 #pragma unroll
-            for (int r = 0; r < 16; ++r)
-                if (r < cs) v[r] = ld_dsmem_f32x4(dsmem_addr(out_tile + off, (uint32_t)r));
-            float4 t = v[0];
+                for (int r = 0; r < 16; ++r)
+                    if (r < cs) v[r] = r == split ? *reinterpret_cast<const float4*>(out_tile + (m_lo + ml) * BM + c) : *reinterpret_cast<const float4*>(recv + ((size_t)r * rows_per + ml) * BM + c);
+                float4 t = v[0];
 #pragma unroll
-            for (int r = 1; r < 16; ++r)
-                if (r < cs) { t.x += v[r].x; t.y += v[r].y; t.z += v[r].z; t.w += v[r].w; }
-            *reinterpret_cast<float4*>(out_tile + off) = t;
+                for (int r = 1; r < 16; ++r)
+                    if (r < cs) { t.x += v[r].x; t.y += v[r].y; t.z += v[r].z; t.w += v[r].w; }
+                *reinterpret_cast<float4*>(out_tile + (m_lo + ml) * BM + c) = t;
+            }
         }
         __syncthreads();
     }
     HM_TRACE(if (tr && tid == 0) a.trace[8] = global_timer();)
     tc_epilogue(a, out_tile, m_lo, m_hi, nblk, tid, sh.pos, sh.page);
     HM_TRACE(if (tr && tid == 0) a.trace[9] = global_timer();)
-    if (CL) cluster_sync_all();  // a CTA may exit only after its tile was read by its peers
     HM_TRACE(if (tr && tid == 0) a.trace[10] = global_timer();)
     HM_TRACE(if (a.trace && tid == 0) atomicMax(a.trace + 12, global_timer());)
 }
@@ -515,6 +539,8 @@ static int tc_nstage(int mpad, bool multi_wave) {
     return multi_wave ? 3 : 6;
 }
 static size_t tc_smem_for(int mpad, bool multi_wave) { return (size_t)tc_nstage(mpad, multi_wave) * (W_TILE + (size_t)TERMS * mpad * 128) + 1024; }
+// receive slots of a split-K launch: one slot of ceil(M / ksplit) rows per rank
+static size_t tc_recv_bytes(int M, int ksplit) { return (size_t)ksplit * ((M + ksplit - 1) / ksplit) * BM * 4; }
 size_t tc_packed_elems(int K, int N) { return (size_t)((N + BM - 1) / BM) * ((K + BK - 1) / BK) * BM * BK; }
 int tc_padded_k(int K) { return (K + BK - 1) / BK * BK; }
 size_t tc_xpack_bytes(int M, int K) { return (size_t)(tc_padded_k(K) / BK) * TERMS * tc_mpad(M) * 128; }
@@ -552,9 +578,9 @@ cudaError_t launch_gemm_tc(const TcArgs& a_in, cudaStream_t st, bool pdl) {
     a.tmem_cols = a.mpad == 16 ? 64 : a.mpad == 32 ? 128 : 256;  // power of two >= 3 * mpad
     const int nblk = (a.N + BM - 1) / BM;
     const bool cl = a.ksplit > 1;
-    const size_t smem = tc_smem_for(a.mpad, multi_wave);
+    const size_t smem = tc_smem_for(a.mpad, multi_wave) + (cl ? tc_recv_bytes(a.M, a.ksplit) : 0);
     {
-        const size_t mx = tc_smem_for(64, false) > tc_smem_for(32, false) ? tc_smem_for(64, false) : tc_smem_for(32, false);
+        const size_t mx = (tc_smem_for(64, false) > tc_smem_for(32, false) ? tc_smem_for(64, false) : tc_smem_for(32, false)) + (cl ? (size_t)(MR + 16) * BM * 4 : 0);
         cudaError_t e = cl ? ensure_dyn_smem(gemm_tc_kernel<true>, mx) : ensure_dyn_smem(gemm_tc_kernel<false>, mx);
         if (e != cudaSuccess) return e;
     }
