@@ -21,6 +21,8 @@
 // cluster barrier.
 #include <type_traits>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "launch_attrs.h"
 #include "mbarrier.cuh"
@@ -573,7 +575,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const AttnArgs
 // one-warp-per-head, which is what bounds the kernel above on long contexts.  Used when a CTA has at
 // least ST_MIN_PAGES pages to read.
 constexpr int ST_THREADS = ATT_THREADS + 32;
-constexpr int ST_MAX_STAGES = 16;
+constexpr int ST_MAX_STAGES = 24;
 constexpr int ST_RING_BYTES = 64 * 1024;  // per CTA; two CTAs per SM keep 128 KB of pages in flight
 constexpr int ST_MAX_PT = 4096;  // page-table entries of one CTA staged in shared memory
 
@@ -639,7 +641,8 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     constexpr int NCH = HD / 8;  // 4-element chunks per half row (lane = token, half)
     extern __shared__ __align__(128) unsigned char st_sm[];
     unsigned char* ring = st_sm;                                                 // [STAGES][K tile | V tile]
-    float* q_s = reinterpret_cast<float*>(ring + ST::STAGES * ST::STAGE_BYTES);  // f32 pages: [G_MAX][NCH][2 halves][4]; bf16 pages: MMA fragments [3 terms][HD/16][32 lanes] x 8 B
+    const int NST = a.st_stages;  // ST::STAGES, or more when the launch has an SM to itself per CTA (see launch_tc)
+    float* q_s = reinterpret_cast<float*>(ring + NST * ST::STAGE_BYTES);  // f32 pages: [G_MAX][NCH][2 halves][4]; bf16 pages: MMA fragments [3 terms][HD/16][32 lanes] x 8 B
     float* p_s = q_s + st_q_bytes(HD) / 4;                                       // [ATT_WARPS][G_MAX][16]
     const int g_early = a.heads / a.kv_heads;
     float* c_o = p_s + ATT_WARPS * G_MAX * PT;                                   // cluster mode, rank 0: [nsplit][g][HD]
@@ -659,7 +662,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     const int head0 = kvh * g;
 
     if (tid == 0) {
-        for (int s = 0; s < ST::STAGES; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mb_init(&full[s], 1);
             mb_init(&empty[s], 1);
         }
@@ -693,7 +696,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
             const TE* kpool = reinterpret_cast<const TE*>(a.k_pool);
             const TE* vpool = reinterpret_cast<const TE*>(a.v_pool);
             const int new_page = (kvlen - 1) / PT;  // the page the new token's K/V are being written to
-            while (n_pre < np && n_pre < ST::STAGES && p0 + n_pre < new_page) {
+            while (n_pre < np && n_pre < NST && p0 + n_pre < new_page) {
                 const size_t tile = ((size_t)pt_s[n_pre] * a.kv_heads + kvh) * PT * HD;
                 unsigned char* dst = ring + (size_t)n_pre * ST::STAGE_BYTES;
                 mb_expect_tx(&full[n_pre], ST::STAGE_BYTES);
@@ -749,9 +752,14 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
         if (lane == 0) {
             const T* kpool = reinterpret_cast<const T*>(a.k_pool);
             const T* vpool = reinterpret_cast<const T*>(a.v_pool);
-            for (int i = n_pre; i < np; ++i) {
-                const int s = i % ST::STAGES;
-                const uint32_t par = ((i / ST::STAGES) & 1u) ^ 1u;
+            // stage and phase advance with the page index (no division in the loop: the ring depth is a run-time value)
+            int s = n_pre % NST;
+            uint32_t par = ((n_pre / NST) & 1u) ^ 1u;
+            for (int i = n_pre; i < np; ++i, ++s) {
+                if (s == NST) {
+                    s = 0;
+                    par ^= 1u;
+                }
                 if (!mb_wait(&empty[s], par, a.err_flag, &s_abort)) break;
                 const size_t tile = ((size_t)pt_s[i] * a.kv_heads + kvh) * PT * HD;
                 unsigned char* dst = ring + (size_t)s * ST::STAGE_BYTES;
@@ -765,9 +773,13 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
             const int gid = lane >> 2, tig = lane & 3;
             float* pw = p_s + warp * (G_MAX * PT);  // [8 heads][16 tokens]: the page's probabilities, transposed for the second MMA
             const uint2* qf = reinterpret_cast<const uint2*>(q_s);
-            for (int i = warp; i < np; i += ST::CW) {  // this warp's pages
-                const int s = i % ST::STAGES;
-                const uint32_t par = (i / ST::STAGES) & 1u;
+            int s = warp;  // this warp's pages: i = warp, warp + 8, ...; their stages advance by 8 modulo the ring depth
+            uint32_t par = 0u;
+            for (int i = warp; i < np; i += ST::CW, s += ST::CW) {
+                if (s >= NST) {
+                    s -= NST;
+                    par ^= 1u;
+                }
                 const bool ok = __all_sync(0xffffffffu, mb_wait(&full[s], par, a.err_flag, &s_abort));
                 if (!ok) break;
                 const uint32_t* kt32 = reinterpret_cast<const uint32_t*>(ring + (size_t)s * ST::STAGE_BYTES);
@@ -841,9 +853,13 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
     } else if (warp < ST::CW) {
         const int t = lane & 15, hf = lane >> 4;
         float* pw = p_s + warp * (G_MAX * PT);
-        for (int i = warp; i < np; i += ST::CW) {  // this warp's pages
-            const int s = i % ST::STAGES;
-            const uint32_t par = (i / ST::STAGES) & 1u;
+        int s = warp;  // this warp's pages and their stages, as above
+        uint32_t par = 0u;
+        for (int i = warp; i < np; i += ST::CW, s += ST::CW) {
+            if (s >= NST) {
+                s -= NST;
+                par ^= 1u;
+            }
             const bool ok = __all_sync(0xffffffffu, mb_wait(&full[s], par, a.err_flag, &s_abort));
             if (!ok) break;
             const unsigned char* kt = ring + (size_t)s * ST::STAGE_BYTES;
@@ -968,9 +984,9 @@ __global__ void __launch_bounds__(ST_THREADS, 2) attn_stream_kernel(const AttnAr
 }
 
 template <int HD, bool BF16>
-size_t stream_smem_bytes(int pages_per_cta, int g, int slots) {
+size_t stream_smem_bytes(int pages_per_cta, int g, int slots, int stages) {
     using ST = StTile<HD, BF16>;
-    return (size_t)ST::STAGES * ST::STAGE_BYTES + st_q_bytes(HD) + sizeof(float) * (ATT_WARPS * G_MAX * PT + (size_t)slots * g * (HD + 2)) + (size_t)pages_per_cta * 4 + 128;
+    return (size_t)stages * ST::STAGE_BYTES + st_q_bytes(HD) + sizeof(float) * (ATT_WARPS * G_MAX * PT + (size_t)slots * g * (HD + 2)) + (size_t)pages_per_cta * 4 + 128;
 }
 
 template <int HD, bool BF16>
@@ -986,7 +1002,22 @@ cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
     // long contexts: the bulk-copy ring; a slot layout needs ATT_WARPS / g >= 1 as in the kernel above
     const bool stream = a.stream_pages > 0 && pages_per_cta >= ST_MIN_PAGES && pages_per_cta <= ST_MAX_PT;
     const int slots = CL ? merge_slot_cap(a.nsplit) : 1;  // rank 0 of a cluster receives every split's triples
-    const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots) : smem_bytes<HD, BF16>(g, slots, pick_nslots<HD, BF16>(g, a.early_pages, a.max_pages, a.nsplit));
+    // The ring bounds what one CTA keeps in flight (a warp asks for its next page only when it has freed a stage).
+    // Launches that leave every CTA an SM to itself (64 sequences x 2 KV heads, one split: 128 CTAs) get as deep a
+    // ring as shared memory holds, in multiples of the eight consumer warps; larger launches keep two CTAs per SM.
+    using STT = StTile<HD, BF16>;
+    int stages = STT::STAGES;
+    if (stream) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if ((long)a.nsplit * a.kv_heads * M <= sms) {
+            const int want = std::min(ST_MAX_STAGES, (pages_per_cta + ATT_WARPS - 1) / ATT_WARPS * ATT_WARPS);
+            while (stages + ATT_WARPS <= want && stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots, stages + ATT_WARPS) <= 216 * 1024) stages += ATT_WARPS;
+        }
+    }
+    AttnArgs a2 = a;
+    a2.st_stages = stages;
+    const size_t smem = stream ? stream_smem_bytes<HD, BF16>(pages_per_cta, g, slots, stages) : smem_bytes<HD, BF16>(g, slots, pick_nslots<HD, BF16>(g, a.early_pages, a.max_pages, a.nsplit));
     // per device, and only ever raised: launches captured in a graph must stay valid after later calls
     {
         cudaError_t e = stream ? ensure_dyn_smem(attn_stream_kernel<HD, BF16, CL>, smem) : ensure_dyn_smem(attn_decode_kernel<HD, BF16, CL>, smem);
@@ -1014,7 +1045,7 @@ cudaError_t launch_tc(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
     }
     cfg.attrs = at;
     cfg.numAttrs = n;
-    return stream ? cudaLaunchKernelEx(&cfg, attn_stream_kernel<HD, BF16, CL>, a) : cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, BF16, CL>, a);
+    return stream ? cudaLaunchKernelEx(&cfg, attn_stream_kernel<HD, BF16, CL>, a2) : cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, BF16, CL>, a2);
 }
 
 template <int HD, bool BF16>

@@ -357,6 +357,7 @@ struct AttnArgs {
     int early_pages;     // >= 1: every row is its own sequence (decode), so the pages below the one of the new token may be read before the dependency wait;
                          // 2: and every page of a split gets its own shared-memory slot (small launches, where latency counts and occupancy does not)
     int stream_pages;    // > 0: long contexts may use the bulk-copy ring variant (pages per CTA decided from max_pages / nsplit)
+    int st_stages;       // stages of that variant's page ring, a multiple of its 8 consumer warps (filled in by the launcher)
     int* err_flag;       // raised to 2 when a bounded wait of that variant runs out
     unsigned long long* trace;  // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA (0,0,0) of the short-context kernel
     const float* q;       // [M][heads*hd]
