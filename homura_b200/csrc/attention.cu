@@ -1060,7 +1060,7 @@ cudaError_t launch_t(const AttnArgs& a, int M, cudaStream_t st, bool pdl) {
 }  // namespace
 
 // Enough (row, KV head, split) CTAs to cover the SMs about twice, at least two pages each.
-int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
+int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count, bool bf16_pages) {
     // Splits per (row, KV head): minimise waves x (fixed cost per CTA + pages per CTA) + merge cost.
     // Units are "pages streamed by one CTA": the fixed cost (launch, query and page-table loads) is
     // worth about eight pages, merging one more partial about half a page.  The streaming variant
@@ -1081,7 +1081,12 @@ int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count) {
         // kernel about twice what it costs the streaming one (every query head re-reads the tile)
         // having any split at all costs a round trip of the partial triples through global memory, a ticket and a
         // second merge by the last CTA: about twenty pages' worth (64 sequences at 36 pages: one split 15.4 us, two 17.1)
-        const long cost = 2 * waves * (8 + (streaming ? ppc : 2 * ppc)) + n + (n > 1 ? 40 : 0);
+        // a streaming launch that leaves every CTA an SM to itself gets the deep page ring (launch_tc), which about
+        // halves what a page costs its CTA while the cache is short (measured on bf16 pages: 64 x 2 CTAs at 43 pages, one
+        // split 11.9 us, two 18.7); on long caches two CTAs per SM stream faster than one with a deep ring, and on f32
+        // pages fewer splits lost at every length
+        const bool deep = streaming && bf16_pages && max_pages <= 64 && pairs * n <= sm_count;
+        const long cost = 2 * waves * (8 + (streaming ? ppc : 2 * ppc)) / (deep ? 2 : 1) + (deep ? 8 : 0) + n + (n > 1 ? 40 : 0);
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best = n;

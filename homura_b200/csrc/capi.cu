@@ -918,7 +918,7 @@ int hm_attn_decode_paged(const float* q, const void* k_pages, const void* v_page
     a.heads = heads;
     a.kv_heads = kv_heads;
     a.hd = hd;
-    a.nsplit = attn_pick_nsplit(B, kv_heads, (longest + page_tokens - 1) / page_tokens, sm_count_of_current_device());
+    a.nsplit = attn_pick_nsplit(B, kv_heads, (longest + page_tokens - 1) / page_tokens, sm_count_of_current_device(), kv_dtype == HM_BF16);
     a.scale = (float)(1.0 / std::sqrt((double)hd));
     a.stream_pages = 1;
     if (!sg.ok(get_wait_err(&a.err_flag))) return sg.finish(cudaSuccess);

@@ -378,6 +378,7 @@ struct AttnArgs {
 
 struct QuantArgs {
     int* err_flag;           // optional: raised to 2 when the bounded wait for the staged weights runs out
+    unsigned long long* trace;  // optional, builds with -DHM_PHASE_TRACE: %globaltimer stamps of CTA 0 (indices as in GemvArgs; 7 = rows staged, before the digit pass)
     const uint16_t* scales;  // [N/32][K/32][32] f16 bits (launch_split_blocks)
     const uint8_t* codes;    // [N/32][K/32][chunk][32][16 B]: 2 chunks per Q8_0 block, 1 per Q4_0 block
     int q4;                  // 0 = Q8_0, 1 = Q4_0
@@ -388,11 +389,20 @@ struct QuantArgs {
     int pro;                 // PRO_PLAIN / PRO_RMSNORM (f64 sum of squares, emitter_quant.rs:713-791)
     const float* norm_w;
     float eps;
-    int epi;                 // EPI_STORE, or EPI_SWIGLU (gate/up rows interleaved 16 + 16 per tile, y = silu(gate) * up, [M][N/2])
+    int epi;                 // EPI_STORE, EPI_SWIGLU (gate/up rows interleaved 16 + 16 per tile, y = silu(gate) * up, [M][N/2]), or
+                             // EPI_QKV_ROPE (q and k rows laid out by launch_split_blocks(rope_hd): y = rotated q [M][q_dim], k and v into the KV pages)
     float* y;
     int ldy;
     const float* bias;
     const float* resid;
+    // EPI_QKV_ROPE (no QK-norm on this path)
+    int q_dim, kv_dim, hd;
+    const float* rope_cos;   // [max_pos][hd]
+    const float* rope_sin;
+    const int32_t* row_pos;  // [M] position of each row's token
+    const int32_t* row_seq;  // [M] sequence of each row; null: row m is sequence seq_base + m
+    int seq_base;
+    KvDesc kv;
 };
 
 // ---- launchers (defined in the .cu files) ----------------------------------------------
@@ -404,7 +414,7 @@ void gemv_pick_split(int K, int N, int M, int sm_count, int* ksplit, int* rows_p
 void gemv_pick_cluster(int K, int N, int M, int sm_count, int max_cluster, int* cluster, int* rows_per_split);
 int gemv_max_cluster();  // largest cluster size the device schedules for the projection kernel (8 or 16)
 cudaError_t launch_attn_decode(const AttnArgs& a, int M, bool kv_bf16, cudaStream_t st, bool pdl);
-int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count);
+int attn_pick_nsplit(int M, int kv_heads, int max_pages, int sm_count, bool bf16_pages);
 int attn_pick_cluster(int max_pages, int max_cluster);
 
 cudaError_t launch_pack_slabs_from_nk(const uint16_t* src_nk, int N, int K, uint16_t* dst, int n_off, int interleave_which, cudaStream_t st);
@@ -422,7 +432,9 @@ cudaError_t launch_convert_to_f32(const void* src, int dtype, size_t n, float* d
 // must hold quant_scale_elems / quant_code_bytes of the whole projection and start zeroed.
 size_t quant_scale_elems(int K, int N);
 size_t quant_code_bytes(int K, int N, int q4);
-cudaError_t launch_split_blocks(const uint8_t* blocks, int n_rows, int K, int q4, int n_off, int interleave_which, uint16_t* scales, uint8_t* codes, cudaStream_t st);
+// rope_hd > 0 (q and k parts of a fused QKV projection whose epilogue rotates): the rows of every head are re-ordered so that a
+// 32-row tile holds 16 dimensions of the head's first half followed by their 16 rotation partners (d + rope_hd / 2).
+cudaError_t launch_split_blocks(const uint8_t* blocks, int n_rows, int K, int q4, int n_off, int interleave_which, uint16_t* scales, uint8_t* codes, cudaStream_t st, int rope_hd = 0);
 cudaError_t launch_dequant(const uint8_t* blocks, size_t nblocks, int q4, float* out, cudaStream_t st);
 cudaError_t launch_gemv_quant(const QuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
 // quant plan helpers: PostQKV (src/hf/emitter_quant.rs:800-905) and SiLU*Up (:1078-1099)

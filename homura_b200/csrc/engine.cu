@@ -132,7 +132,8 @@ int Engine::stage(const void* host, size_t nbytes, void** dev) {
 // One part (n_part outputs starting at n_off) of a possibly fused projection with N_total
 // outputs.  bf16 [out,in] goes to the slab layout; GGUF blocks [out, in/32] are split into
 // scale and code arrays (rows of the parts are simply concatenated).
-int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes) {
+// rope_part: 1 = q or k rows, 2 = v rows of the fused QKV projection (0: any other projection)
+int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes, int rope_part) {
     const bool kq = dtype == HM_Q4_K || dtype == HM_Q6_K;
     if (dtype != HM_BF16 && dtype != HM_Q8_0 && dtype != HM_Q4_0 && !kq)
         return fail(HM_ERR_UNSUPPORTED, "projection weights must be stored as bf16, Q8_0, Q4_0, Q4_K or Q6_K: this checkpoint holds f32 / f16 projections, and the f32-weight streaming kernel they need is not built");
@@ -196,7 +197,15 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
             if (ce == cudaSuccess) ce = cudaMemsetAsync(L.scales, 0, quant_scale_elems(K, N_total) * 2, stream_);
             if (ce == cudaSuccess) ce = cudaMemsetAsync(L.codes, 0, quant_code_bytes(K, N_total, q4), stream_);
         }
-        if (ce == cudaSuccess) ce = launch_split_blocks((const uint8_t*)tmp, n_part, K, q4, n_off, interleave_which, L.scales, L.codes, stream_);
+        // the QKV projection of a Q8_0 / Q4_0 model rotates in its own epilogue when a rotation pair can share a 32-row tile
+        // and there is no QK-norm (which needs a whole head in one CTA); all three parts must then agree
+        const bool rope_rows = rope_part != 0 && !cfg_.has_qk_norm && (hd_ / 2) % 16 == 0 && qdim_ % 32 == 0 && kvdim_ % 32 == 0;
+        if (rope_part != 0 && L.loaded_parts > 0 && L.rope_rows != rope_rows) {
+            cudaFree(tmp);
+            return fail(HM_ERR_STATE, "q, k and v projections of a layer disagree on their row layout");
+        }
+        if (rope_part != 0) L.rope_rows = rope_rows;
+        if (ce == cudaSuccess) ce = launch_split_blocks((const uint8_t*)tmp, n_part, K, q4, n_off, interleave_which, L.scales, L.codes, stream_, rope_rows && rope_part == 1 ? hd_ : 0);
         quant_ = true;
     }
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
@@ -320,9 +329,9 @@ int Engine::load_tensor(const char* cname, int dtype, const int64_t* shape, int 
     const int QKV = qdim_ + 2 * kvdim_;
     if (is("input_layernorm.weight", "attn_norm.weight")) return shape1(H_) ? load_vec_f32(&Lw.in_ln, H_, 0, dtype, host, n, nbytes) : bad_shape();
     if (is("post_attention_layernorm.weight", "ffn_norm.weight")) return shape1(H_) ? load_vec_f32(&Lw.post_ln, H_, 0, dtype, host, n, nbytes) : bad_shape();
-    if (is("self_attn.q_proj.weight", "attn_q.weight")) return shape2(qdim_, H_) ? load_linear(Lw.qkv, H_, QKV, 0, qdim_, -1, dtype, host, nbytes) : bad_shape();
-    if (is("self_attn.k_proj.weight", "attn_k.weight")) return shape2(kvdim_, H_) ? load_linear(Lw.qkv, H_, QKV, qdim_, kvdim_, -1, dtype, host, nbytes) : bad_shape();
-    if (is("self_attn.v_proj.weight", "attn_v.weight")) return shape2(kvdim_, H_) ? load_linear(Lw.qkv, H_, QKV, qdim_ + kvdim_, kvdim_, -1, dtype, host, nbytes) : bad_shape();
+    if (is("self_attn.q_proj.weight", "attn_q.weight")) return shape2(qdim_, H_) ? load_linear(Lw.qkv, H_, QKV, 0, qdim_, -1, dtype, host, nbytes, 1) : bad_shape();
+    if (is("self_attn.k_proj.weight", "attn_k.weight")) return shape2(kvdim_, H_) ? load_linear(Lw.qkv, H_, QKV, qdim_, kvdim_, -1, dtype, host, nbytes, 1) : bad_shape();
+    if (is("self_attn.v_proj.weight", "attn_v.weight")) return shape2(kvdim_, H_) ? load_linear(Lw.qkv, H_, QKV, qdim_ + kvdim_, kvdim_, -1, dtype, host, nbytes, 2) : bad_shape();
     if (is("self_attn.o_proj.weight", "attn_output.weight")) return shape2(H_, qdim_) ? load_linear(Lw.o, qdim_, H_, 0, H_, -1, dtype, host, nbytes) : bad_shape();
     if (is("mlp.gate_proj.weight", "ffn_gate.weight")) return shape2(I_, H_) ? load_linear(Lw.gu, H_, 2 * I_, 0, I_, 0, dtype, host, nbytes) : bad_shape();
     if (is("mlp.up_proj.weight", "ffn_up.weight")) return shape2(I_, H_) ? load_linear(Lw.gu, H_, 2 * I_, I_, I_, 1, dtype, host, nbytes) : bad_shape();
@@ -506,7 +515,7 @@ int Engine::kv_alloc(int batch, int max_seq_len, int page_tokens, int kv_dtype) 
     // the launch is a throughput problem (64 sequences stream 39 MB of pages per layer), which the cost model
     // of attn_pick_nsplit answers with few splits of many pages each, i.e. the bulk-copy ring kernel
     att_cluster_ = use_clusters_ && max_pages_ <= 64 && (long)batch * kvh_ < sm_count_ / 2;
-    att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 16)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_);
+    att_nsplit_ = att_cluster_ ? attn_pick_cluster(max_pages_, std::min(max_cluster_, 16)) : attn_pick_nsplit(batch, kvh_, max_pages_, sm_count_, kv_bf16_);
     HM_CUDA(cudaMalloc(&att_acc_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * hd_ * 4));
     HM_CUDA(cudaMalloc(&att_ml_, (size_t)scratch_rows_ * heads_ * att_nsplit_ * 2 * 4));
     HM_CUDA(cudaMalloc(&att_tickets_, (size_t)scratch_rows_ * kvh_ * 4));
@@ -808,6 +817,9 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
         } else {
             QuantArgs a{};
             a.err_flag = err_flag_;
+#ifdef HM_PHASE_TRACE
+            if (gemv_trace_ && *launches < 512) a.trace = gemv_trace_ + (size_t)*launches * 16;
+#endif
             a.scales = L.scales;
             a.codes = L.codes;
             a.q4 = L.kind == HM_Q4_0;
@@ -824,6 +836,18 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.ldy = ldy;
             a.bias = bias;
             a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+            if (epi == EPI_QKV_ROPE) {
+                if (!L.rope_rows || layer < 0) return fail(HM_ERR_STATE, "projection rows are not in rotation-pair order");
+                a.q_dim = qdim_;
+                a.kv_dim = kvdim_;
+                a.hd = hd_;
+                a.rope_cos = rope_cos_;
+                a.rope_sin = rope_sin_;
+                a.row_pos = row_pos + m0;
+                a.row_seq = row_seq ? row_seq + m0 : nullptr;
+                a.seq_base = m0;
+                a.kv = KvDesc{k_pool_[layer], v_pool_[layer], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+            }
             ce = launch_gemv_quant(a, mp, sm_count_, stream_, pdl_);
         }
         if (ce != cudaSuccess) return cuda_fail(ce, "projection launch");
@@ -880,7 +904,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         } else if (tall) {
             rc = enqueue_linear_tc(w.qkv, M, h_, H_, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, launches);
             if (rc) return rc;
-        } else if (w.qkv.kind == HM_BF16) {
+        } else if (w.qkv.kind == HM_BF16 || w.qkv.rope_rows) {
             prefetch(&w.o);
             rc = enqueue_linear(w.qkv, M, h_, H_, PRO_RMSNORM, w.in_ln, EPI_QKV_ROPE, q_, qdim_, w.qkv_bias, nullptr, l, row_pos, row_seq, nullptr, nullptr, launches);
             if (rc) return rc;
@@ -906,7 +930,7 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
         at.hd = hd_;
         // fewer splits when the rows alone fill the SMs: about two CTAs per SM on the cluster path (caches
         // of up to 1024 tokens), the kernel's cost model on the long-context path
-        at.nsplit = std::min(att_nsplit_, att_cluster_ ? std::max(1, (2 * sm_count_ + M * kvh_ - 1) / (M * kvh_)) : attn_pick_nsplit(M, kvh_, max_pages_, sm_count_));
+        at.nsplit = std::min(att_nsplit_, att_cluster_ ? std::max(1, (2 * sm_count_ + M * kvh_ - 1) / (M * kvh_)) : attn_pick_nsplit(M, kvh_, max_pages_, sm_count_, kv_bf16_));
         at.cluster = att_cluster_ ? 1 : 0;
         at.stream_pages = 1;
         if (direct_pack) {

@@ -28,6 +28,7 @@ struct LinearW {
     size_t kq_bytes = 0;              // GGUF bytes loaded into it (what a step streams)
     int kq_part_type = -1;            // type of the part loaded last (gate and up must agree: they share tiles)
     int loaded_parts = 0;
+    bool rope_rows = false;  // Q8_0 / Q4_0 fused QKV: q and k rows stored in rotation-pair tiles (launch_split_blocks rope_hd), epilogue rotates
     size_t bytes() const;
 };
 
@@ -84,7 +85,7 @@ class Engine {
     int cuda_fail(cudaError_t e, const char* what);
     bool set_device();
     int stage(const void* host, size_t nbytes, void** dev);  // temp device copy of a host tensor
-    int load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes);
+    int load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes, int rope_part = 0);
     int load_vec_f32(float** dst, size_t n_total, size_t off, int dtype, const void* host, size_t n, size_t nbytes);
     int ensure_scratch(int rows);
     // Enqueue one pass over M rows (decode: one row per sequence; prefill: a chunk of one
