@@ -384,6 +384,8 @@ struct QuantArgs {
     int q4;                  // 0 = Q8_0, 1 = Q4_0
     int K, N, m_valid;
     int ksplit, kb_per_split;  // filled in by launch_gemv_quant: CTAs per 32-row tile and k-blocks per CTA
+    int from_regs;             // filled in by launch_gemv_quant: activation rows are read with 16-byte loads and never staged as f32
+    int reg_tail;              // filled in by launch_gemv_quant: 1 = the last eight k-blocks of a staged slice are not staged (one per warp, from global memory)
     const float* x;
     int ldx;
     int pro;                 // PRO_PLAIN / PRO_RMSNORM (f64 sum of squares, emitter_quant.rs:713-791)

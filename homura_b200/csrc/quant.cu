@@ -88,95 +88,81 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ blocks, size_t nblock
 
 constexpr int QU = 4;  // k-blocks a warp keeps in flight
 
+// D = A * B with a zero accumulator
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
 // Shared-memory image of the activations, per k-block and per pair of rows (one MMA's eight B columns = two rows x
 // four digit planes):  img [kb][pair][half of the block][column][4 B = k 4q..4q+3]  (lane 4 * column + q reads word
-// `lane` of each half), bs [kb][pair][2] the rows' block scales 2^s, cs [kb][pair][4] eight times the digit sums of
-// the column pairs (Q4_0's offset; combined like the dots: 128 * even plane + odd plane).
-constexpr int IMG_WORDS = 64;  // per (k-block, row pair)
-
-// A block's elements become q = rint(x * 2^(26 - e)) with e the exponent of the block's largest magnitude (|q| <= 2^27),
-// then q = ((d0 * 128 + d1) * 128 + d2) * 128 + d3 with d1..d3 in 0..127 and d0 in -64..64.  Blocks below 2^-100 count
-// as zero; a block holding an infinity or a NaN gets a NaN scale.
+// `lane` of each half) and bs [kb][pair][2], the rows' block scales 2^s.  A single row (M = 1) keeps four columns;
+// the lanes of the other four read the same words and their results are dropped.
 template <int M>
-__device__ __forceinline__ void build_digit_image(const float* __restrict__ xs, int kspan, int nkb, uint32_t* __restrict__ img, float* __restrict__ bs, int* __restrict__ cs, int tid) {
-    constexpr int NG = (M + 1) / 2;
+struct Img {
+    static constexpr int NG = (M + 1) / 2;
+    static constexpr int HALF = M == 1 ? 16 : 32;  // words per half block
+    static constexpr int WORDS = 2 * HALF;          // per (k-block, row pair)
+};
+
+// One 16-byte piece (elements 4 * sub .. 4 * sub + 3 of a 32-element block, the block's eight pieces held by eight
+// consecutive lanes) becomes four digit words.  The block's elements are q = rint(x * 2^(29 - e)) with e the exponent
+// of the block's largest magnitude (|q| <= 2^30), and q = ((b3 * 256 + b2) * 256 + b1) * 256 + b0 with every b in
+// -128..127: adding 0x808080 and flipping those three bits again turns the bytes of q into exactly these digits.
+// Blocks below 2^-96 count as zero; a block holding an infinity or a NaN gets a NaN scale.  Every lane of the warp
+// must call this (shuffles); only lanes with `store` write.
+template <int M>
+__device__ __forceinline__ void emit_digits(float4 v, bool store, int slot, int m, int sub, uint32_t* __restrict__ img, float* __restrict__ bs) {
+    float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    // fmaxf drops a NaN operand: carry the "not finite" bit of every element beside the maximum
+    unsigned nonfinite = ((__float_as_uint(v.x) & 0x7F800000u) == 0x7F800000u) | ((__float_as_uint(v.y) & 0x7F800000u) == 0x7F800000u) |
+                         ((__float_as_uint(v.z) & 0x7F800000u) == 0x7F800000u) | ((__float_as_uint(v.w) & 0x7F800000u) == 0x7F800000u);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        nonfinite |= __shfl_xor_sync(0xffffffffu, nonfinite, o);
+    }
+    const int e = (int)((__float_as_uint(mx) >> 23) & 255u);
+    const bool live = e >= 31 && !nonfinite;
+    const float mult = live ? __uint_as_float((uint32_t)(283 - e) << 23) : 0.f;
+    const float scale = nonfinite ? __uint_as_float(0x7FC00000u) : (live ? __uint_as_float((uint32_t)(e - 29) << 23) : 0.f);
+    uint32_t d[4];
+    const float xv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d[j] = ((uint32_t)__float2int_rn(xv[j] * mult) + 0x00808080u) ^ 0x00808080u;
+    // 4 x 4 byte transpose: word t = digit t of the four elements
+    const uint32_t t01 = __byte_perm(d[0], d[1], 0x5140), t23 = __byte_perm(d[2], d[3], 0x5140);
+    const uint32_t u01 = __byte_perm(d[0], d[1], 0x7362), u23 = __byte_perm(d[2], d[3], 0x7362);
+    if (store) {
+        uint32_t* dst = img + (size_t)slot * Img<M>::WORDS + (sub >> 2) * Img<M>::HALF + (m & 1) * 16 + (sub & 3);
+        dst[0] = __byte_perm(t01, t23, 0x5410);
+        dst[4] = __byte_perm(t01, t23, 0x7632);
+        dst[8] = __byte_perm(u01, u23, 0x5410);
+        dst[12] = __byte_perm(u01, u23, 0x7632);
+        if (sub == 0) bs[slot * 2 + (m & 1)] = scale;
+    }
+}
+
+// rows staged as f32 [M][kspan] -> digit image (the path for rows that the register path below cannot take)
+template <int M>
+__device__ __forceinline__ void build_digit_image(const float* __restrict__ xs, int kspan, int nkb, uint32_t* __restrict__ img, float* __restrict__ bs, int tid) {
     const int sub = tid & 7, total = nkb * M;
     for (int base = 0; base < total; base += QT / 8) {
         const int it = base + (tid >> 3);
         const bool valid = it < total;
         const int kb = it / M, m = it - kb * M;
         const float4 v = valid ? *reinterpret_cast<const float4*>(xs + (size_t)m * kspan + kb * 32 + sub * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-        // fmaxf drops a NaN operand: carry the "not finite" bit of every element beside the maximum
-        unsigned nonfinite = ((__float_as_uint(v.x) & 0x7F800000u) == 0x7F800000u) | ((__float_as_uint(v.y) & 0x7F800000u) == 0x7F800000u) |
-                             ((__float_as_uint(v.z) & 0x7F800000u) == 0x7F800000u) | ((__float_as_uint(v.w) & 0x7F800000u) == 0x7F800000u);
-#pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            nonfinite |= __shfl_xor_sync(0xffffffffu, nonfinite, o);
-        }
-        const int e = (int)((__float_as_uint(mx) >> 23) & 255u);
-        const bool live = e >= 27 && !nonfinite;
-        const float mult = live ? __uint_as_float((uint32_t)(280 - e) << 23) : 0.f;
-        const float scale = nonfinite ? __uint_as_float(0x7FC00000u) : (live ? __uint_as_float((uint32_t)(e - 26) << 23) : 0.f);
-        const float xv[4] = {v.x, v.y, v.z, v.w};
-        uint32_t w[4] = {0u, 0u, 0u, 0u};
-        int s01 = 0, s23 = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int q = nonfinite ? 0 : __float2int_rn(xv[j] * mult);
-            const int d3 = q & 127;
-            q >>= 7;
-            const int d2 = q & 127;
-            q >>= 7;
-            const int d1 = q & 127;
-            const int d0 = q >> 7;
-            w[0] |= (uint32_t)(d0 & 255) << (8 * j);
-            w[1] |= (uint32_t)d1 << (8 * j);
-            w[2] |= (uint32_t)d2 << (8 * j);
-            w[3] |= (uint32_t)d3 << (8 * j);
-            s01 += d0 * 128 + d1;
-            s23 += d2 * 128 + d3;
-        }
-#pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-            s01 += __shfl_xor_sync(0xffffffffu, s01, o);
-            s23 += __shfl_xor_sync(0xffffffffu, s23, o);
-        }
-        if (valid) {
-            const int slot = kb * NG + (m >> 1);
-            uint32_t* dst = img + (size_t)slot * IMG_WORDS + (sub >> 2) * 32 + (m & 1) * 16 + (sub & 3);
-#pragma unroll
-            for (int t = 0; t < 4; ++t) dst[t * 4] = w[t];
-            if (M == 1) {  // the pair's second row does not exist
-#pragma unroll
-                for (int t = 0; t < 4; ++t) dst[16 + t * 4] = 0u;
-            }
-            if (sub == 0) {
-                bs[slot * 2 + (m & 1)] = scale;
-                cs[slot * 4 + (m & 1) * 2] = 8 * s01;
-                cs[slot * 4 + (m & 1) * 2 + 1] = 8 * s23;
-                if (M == 1) {
-                    bs[slot * 2 + 1] = 0.f;
-                    cs[slot * 4 + 2] = 0;
-                    cs[slot * 4 + 3] = 0;
-                }
-            }
-        }
+        emit_digits<M>(v, valid, kb * Img<M>::NG + (m >> 1), m, sub, img, bs);
     }
 }
 
 // One k-block of a 32-row tile against NG row pairs.  Lane 4g + q ends up with, for the tile rows g, g + 8, g + 16,
 // g + 24 and activation row 2 * pair + (q >> 1), the partial over the digit planes 2 * (q & 1) and 2 * (q & 1) + 1;
-// the caller weights the two halves by 2^14 and 1 and adds them.
-template <int NG, bool Q4>
-__device__ __forceinline__ void q_block(const uint4 (&c)[2], uint2 sc, const uint32_t* __restrict__ img, const float* __restrict__ bs, const int* __restrict__ cs, int lane, float (&acc)[NG][4]) {
+// the caller weights the two halves by 1 and 2^16 and adds them.
+template <int M, bool Q4>
+__device__ __forceinline__ void q_block(const uint4 (&c)[2], uint2 sc, const uint32_t* __restrict__ img, const float* __restrict__ bs, int lane, float (&acc)[Img<M>::NG][4]) {
+    constexpr int NG = Img<M>::NG;
     uint32_t a[2][4];
     if (Q4) {
         // word r8: bytes 4q..4q+3 of row g + 8 * r8; low nibbles = elements 4q.., high nibbles = elements 16 + 4q..
@@ -199,17 +185,23 @@ __device__ __forceinline__ void q_block(const uint4 (&c)[2], uint2 sc, const uin
     }
     const float2 d01 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x)), d23 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
     const float d[4] = {d01.x, d01.y, d23.x, d23.y};
-    const int q = lane & 3;
+    const int li = M == 1 ? (lane & 15) : lane;
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
-        const uint32_t b0 = img[ng * IMG_WORDS + lane], b1 = img[ng * IMG_WORDS + 32 + lane];
-        const float bsv = bs[ng * 2 + (q >> 1)];
-        const int off = Q4 ? cs[ng * 4 + q] : 0;
+        const uint32_t b0 = img[ng * Img<M>::WORDS + li], b1 = img[ng * Img<M>::WORDS + Img<M>::HALF + li];
+        const float bsv = bs[ng * 2 + ((lane >> 1) & 1)];
+        int off = 0;
+        if (Q4) {
+            // the nibbles enter as 0..15: take 8 x the digit sums of the block off again (an all-ones A gives them in every row)
+            int cs[4];
+            mma_s8(cs, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1);
+            off = (cs[1] * 256 + cs[0]) * 8;
+        }
 #pragma unroll
         for (int rg = 0; rg < 2; ++rg) {
-            int cc[4] = {0, 0, 0, 0};
+            int cc[4];
             mma_s8(cc, a[rg][0], a[rg][1], a[rg][2], a[rg][3], b0, b1);
-            const int i0 = cc[0] * 128 + cc[1] - off, i1 = cc[2] * 128 + cc[3] - off;
+            const int i0 = cc[1] * 256 + cc[0] - off, i1 = cc[3] * 256 + cc[2] - off;
             acc[ng][2 * rg] = fmaf(d[2 * rg] * bsv, (float)i0, acc[ng][2 * rg]);
             acc[ng][2 * rg + 1] = fmaf(d[2 * rg + 1] * bsv, (float)i1, acc[ng][2 * rg + 1]);
         }
@@ -220,24 +212,29 @@ __device__ __forceinline__ void q_block(const uint4 (&c)[2], uint2 sc, const uin
 // shared memory by two bulk copies issued BEFORE the dependency wait, so that in the decode chain the weights'
 // HBM latency overlaps the launch before this one and the multiply runs out of shared memory.
 template <int M, bool Q4, bool CL, bool ST>
-__global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
+__global__ void __launch_bounds__(QT, (M == 1 && ST) ? 3 : 1) gemv_quant_kernel(const QuantArgs a) {
     extern __shared__ __align__(128) float qsm[];
+    // A staged slice may leave its last eight k-blocks (one per warp) in global memory: 8.5 KB less per CTA is what lets
+    // three CTAs of the Q8_0 gate/up projection share an SM, i.e. the whole launch be resident at once.
+    const int tail = ST ? a.reg_tail : 0;
+    const int kbs_st = a.kb_per_split - 8 * tail;  // staged k-blocks (capacity)
     const int kspan = a.kb_per_split * 32;  // activations this CTA needs
     constexpr int CHB = (Q4 ? 1 : 2) * 512;  // code bytes of one k-block of a 32-row tile
     // staged weights first (bulk copies want 16-byte aligned destinations): codes, then scales
     const unsigned char* codes_s = reinterpret_cast<const unsigned char*>(qsm);
-    const uint16_t* scales_s = reinterpret_cast<const uint16_t*>(codes_s + (size_t)a.kb_per_split * CHB);
-    constexpr int NG = (M + 1) / 2;  // pairs of activation rows = MMAs per block and row group
-    float* xs = ST ? qsm + ((size_t)a.kb_per_split * (CHB + 64)) / 4 : qsm;  // [M][kspan] f32, read once by the digit pass
-    uint32_t* img = reinterpret_cast<uint32_t*>(xs + M * kspan);                  // [kb][NG][IMG_WORDS]
-    float* bsc = reinterpret_cast<float*>(img + (size_t)a.kb_per_split * NG * IMG_WORDS);  // [kb][NG][2]
-    int* csum = reinterpret_cast<int*>(bsc + a.kb_per_split * NG * 2);            // [kb][NG][4]
-    float* red = reinterpret_cast<float*>(csum + a.kb_per_split * NG * 4);        // [8 warps][M][32], then vals [M][32] at red[0..]
+    const uint16_t* scales_s = reinterpret_cast<const uint16_t*>(codes_s + (size_t)kbs_st * CHB);
+    constexpr int NG = Img<M>::NG;  // pairs of activation rows = MMAs per block and row group
+    constexpr int IW = Img<M>::WORDS;
+    float* xs = ST ? qsm + ((size_t)kbs_st * (CHB + 64)) / 4 : qsm;  // [M][kspan] f32, only when the rows cannot go from registers to digits
+    uint32_t* img = reinterpret_cast<uint32_t*>(xs + (a.from_regs ? 0 : M * kspan));  // [kb][NG][IW]
+    float* bsc = reinterpret_cast<float*>(img + (size_t)a.kb_per_split * NG * IW);     // [kb][NG][2]
+    float* red = bsc + a.kb_per_split * NG * 2;                                        // [8 warps][M][32], then vals [M][32] at red[0..]
     constexpr int NCHUNK = 4;           // the slice arrives in up to four pieces, each on its own barrier, so that the
     __shared__ uint64_t s_wbar[NCHUNK];  // multiply of a CTA that started late overlaps the rest of its copies
     __shared__ volatile int s_abort;
     __shared__ double s_wsum[8][MAX_M];
     __shared__ float s_inv[MAX_M];
+    __shared__ float s_post[MAX_M];  // RMSNorm factor still to be applied to the finished dot (1 when the rows were scaled before the digits)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nb = a.K / 32;
     const int tile = blockIdx.x / a.ksplit, split = blockIdx.x - tile * a.ksplit;
@@ -256,7 +253,8 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
     // streaming loads into registers, before the dependency wait
     uint4 c[QU][2];
     uint2 sc[QU];
-    const int ck = max(8, ((nkb + NCHUNK - 1) / NCHUNK + 7) / 8 * 8);  // k-blocks per piece: a multiple of the 8 warps
+    const int nkb_s = nkb - 8 * tail;  // staged k-blocks of this CTA (the launcher asks for a tail only on unsplit K of at least 16 blocks)
+    const int ck = max(8, ((nkb_s + NCHUNK - 1) / NCHUNK + 7) / 8 * 8);  // k-blocks per piece: a multiple of the 8 warps
     if (ST) {
         if (tid == 0) {
             for (int ch = 0; ch < NCHUNK; ++ch) mb_init(&s_wbar[ch], 1);
@@ -264,9 +262,9 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             const unsigned char* csrc = reinterpret_cast<const unsigned char*>(a.codes) + ((size_t)tile * nb + kb0) * CHB;
             for (int ch = 0; ch < NCHUNK; ++ch) {
-                const int k_lo = min(nkb, ch * ck), k_hi = min(nkb, k_lo + ck);
+                const int k_lo = min(nkb_s, ch * ck), k_hi = min(nkb_s, k_lo + ck);
                 if (k_hi <= k_lo) break;
-                const uint32_t cbytes = (uint32_t)(k_hi - k_lo) * CHB, sbytes = ch == 0 ? (uint32_t)nkb * 64u : 0u;
+                const uint32_t cbytes = (uint32_t)(k_hi - k_lo) * CHB, sbytes = ch == 0 ? (uint32_t)nkb_s * 64u : 0u;
                 mb_expect_tx(&s_wbar[ch], cbytes + sbytes);
                 if (sbytes) bulk_copy(const_cast<uint16_t*>(scales_s), a.scales + ((size_t)tile * nb + kb0) * 32, sbytes, &s_wbar[0]);
                 bulk_copy(const_cast<unsigned char*>(codes_s) + (size_t)k_lo * CHB, csrc + (size_t)k_lo * CHB, cbytes, &s_wbar[ch]);
@@ -286,8 +284,7 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
     // RMSNorm weights of the whole row (they do not depend on the previous kernel either): up to XV 16-byte pieces
     // per thread, requested before the dependency wait
     constexpr int XV = 8;  // rows of up to 8192 elements take the one-round-trip path below
-    const bool vec_row = a.pro == PRO_RMSNORM && (a.K & 3) == 0 && a.K <= XV * 4 * QT && (a.ldx & 3) == 0 &&
-                         ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.norm_w)) & 15) == 0;
+    const bool vec_row = a.from_regs && a.pro == PRO_RMSNORM;
     const int k4 = a.K >> 2;
     float4 nwv[XV];
     if (vec_row) {
@@ -301,11 +298,13 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
     pdl_wait();
     HM_TRACE(if (tr) a.trace[1] = global_timer();)
 
-    // ---- prologue: this CTA's K range of every activation row into shared memory ----
+    // ---- prologue: this CTA's K range of every activation row becomes the digit image ----
+    if (tid < M) s_post[tid] = 1.0f;
     if (vec_row) {
-        // one L2 round trip per row: every piece of the row is requested before the first use, the sum of squares
-        // runs in f64 as the reference's GGUF path does (emitter_quant.rs:713-791), and the pieces that fall into
-        // this CTA's K range go to shared memory straight from the registers
+        // One L2 round trip per row: every piece of the row is requested before the first use.  The pieces in this
+        // CTA's K range go from the registers to digits at once, as x * norm_weight; the RMSNorm factor is a scalar of
+        // the row and multiplies the finished dot instead (s_post), so that nothing waits for the sum of squares, which
+        // runs in f64 as the reference's GGUF path does (emitter_quant.rs:713-791) and is only reduced after the multiply.
         const int lo = kb0 * 32, hi = lo + nkb * 32;
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -316,69 +315,76 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
                 const int idx = tid + i * QT;
                 xv[i] = idx < k4 ? ld_cg_f32x4(reinterpret_cast<const float*>(xr4 + idx)) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            double s = 0.0;
 #pragma unroll
             for (int i = 0; i < XV; ++i) {
-                s += (double)xv[i].x * (double)xv[i].x;
-                s += (double)xv[i].y * (double)xv[i].y;
-                s += (double)xv[i].z * (double)xv[i].z;
-                s += (double)xv[i].w * (double)xv[i].w;
+                if (i * QT >= k4) break;  // uniform: the row ends before this round of pieces
+                const int el = (tid + i * QT) * 4;
+                const bool in = el >= lo && el < hi;
+                if (!__any_sync(0xffffffffu, in)) continue;
+                const float4 v = make_float4(xv[i].x * nwv[i].x, xv[i].y * nwv[i].y, xv[i].z * nwv[i].z, xv[i].w * nwv[i].w);
+                emit_digits<M>(v, in, ((el - lo) >> 5) * NG + (m >> 1), m, tid & 7, img, bsc);
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) s_wsum[warp][m] = s;
-            __syncthreads();
-            if (tid == 0) {
-                double t = 0.0;
-                for (int wv = 0; wv < 8; ++wv) t += s_wsum[wv][m];
-                const float mean = (float)(t * (1.0 / (double)a.K));
-                s_inv[m] = 1.0f / sqrtf(mean + a.eps);
-            }
-            __syncthreads();
-            const float inv = s_inv[m];
+            double ssq = 0.0;
 #pragma unroll
             for (int i = 0; i < XV; ++i) {
-                const int e = (tid + i * QT) * 4;
-                if (e >= lo && e < hi)
-                    *reinterpret_cast<float4*>(xs + m * kspan + (e - lo)) =
-                        make_float4((xv[i].x * inv) * nwv[i].x, (xv[i].y * inv) * nwv[i].y, (xv[i].z * inv) * nwv[i].z, (xv[i].w * inv) * nwv[i].w);
-            }
-        }
-    } else if (a.pro == PRO_RMSNORM) {
-        // sum of squares in f64 over the whole row (emitter_quant.rs:713-791)
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-            double s = 0.0;
-            const float* xr = a.x + (size_t)m * a.ldx;
-            for (int k = tid; k < a.K; k += QT) {
-                const double v = (double)xr[k];
-                s += v * v;
+                if (i * QT >= k4) break;
+                ssq += (double)xv[i].x * (double)xv[i].x;
+                ssq += (double)xv[i].y * (double)xv[i].y;
+                ssq += (double)xv[i].z * (double)xv[i].z;
+                ssq += (double)xv[i].w * (double)xv[i].w;
             }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) s_wsum[warp][m] = s;
+            for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+            if (lane == 0) s_wsum[warp][m] = ssq;
         }
-        __syncthreads();
-        if (tid < M) {
-            double s = 0.0;
-            for (int wv = 0; wv < 8; ++wv) s += s_wsum[wv][tid];
-            const float mean = (float)(s * (1.0 / (double)a.K));
-            s_inv[tid] = 1.0f / sqrtf(mean + a.eps);
-        }
-        __syncthreads();
+    } else if (a.from_regs) {
+        // plain rows: this CTA's range, 16 bytes per lane, all rows requested before the first use
+        const int n4 = nkb * 8;
+        for (int p0 = 0; p0 < n4; p0 += QT) {
+            const int p = p0 + tid;
+            const bool in = p < n4;
+            float4 xv[M];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const float inv = s_inv[m];
-            const float* xr = a.x + (size_t)m * a.ldx + kb0 * 32;
-            for (int k = tid; k < nkb * 32; k += QT) xs[m * kspan + k] = (xr[k] * inv) * a.norm_w[kb0 * 32 + k];
+            for (int m = 0; m < M; ++m) xv[m] = in ? ld_cg_f32x4(a.x + (size_t)m * a.ldx + kb0 * 32 + 4 * (size_t)p) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!__any_sync(0xffffffffu, in)) continue;
+#pragma unroll
+            for (int m = 0; m < M; ++m) emit_digits<M>(xv[m], in, (p >> 3) * NG + (m >> 1), m, tid & 7, img, bsc);
         }
     } else {
-        // the loads of all rows are issued before the first store (one L2 round trip per 1024 elements of a row)
-        stage_rows<QT, M>(a.x + kb0 * 32, a.ldx, xs, kspan, nkb * 32, tid);
+        if (a.pro == PRO_RMSNORM) {
+            // sum of squares in f64 over the whole row (emitter_quant.rs:713-791)
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                double ssq = 0.0;
+                const float* xr = a.x + (size_t)m * a.ldx;
+                for (int k = tid; k < a.K; k += QT) {
+                    const double v = (double)xr[k];
+                    ssq += v * v;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+                if (lane == 0) s_wsum[warp][m] = ssq;
+            }
+            __syncthreads();
+            if (tid < M) {
+                double t = 0.0;
+                for (int wv = 0; wv < 8; ++wv) t += s_wsum[wv][tid];
+                const float mean = (float)(t * (1.0 / (double)a.K));
+                s_inv[tid] = 1.0f / sqrtf(mean + a.eps);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const float inv = s_inv[m];
+                const float* xr = a.x + (size_t)m * a.ldx + kb0 * 32;
+                for (int k = tid; k < nkb * 32; k += QT) xs[m * kspan + k] = (xr[k] * inv) * a.norm_w[kb0 * 32 + k];
+            }
+        } else {
+            stage_rows<QT, M>(a.x + kb0 * 32, a.ldx, xs, kspan, nkb * 32, tid);
+        }
+        __syncthreads();
+        build_digit_image<M>(xs, kspan, nkb, img, bsc, tid);
     }
-    __syncthreads();
-    HM_TRACE(if (tr) a.trace[7] = global_timer();)
-    build_digit_image<M>(xs, kspan, nkb, img, bsc, csum, tid);
     __syncthreads();
     HM_TRACE(if (tr) a.trace[2] = global_timer();)
 
@@ -392,9 +398,17 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
         // lane = output row, 16-byte reads of consecutive lanes are consecutive (no bank conflicts)
         int waited = -1;
         bool ok = true;
-        for (int kb = warp; kb < nkb && ok; kb += 8) {
-            const int ch = kb / ck;
-            while (waited < ch && ok) {
+        // the warp's unstaged block, requested now and multiplied last
+        const int kbt = nkb_s + ((warp - nkb_s) & 7);
+        uint4 tc[2];
+        uint2 tsc = make_uint2(0u, 0u);
+        if (tail) {
+#pragma unroll
+            for (int h = 0; h < CH; ++h) tc[h] = ld_stream_u4(cbase + ((size_t)kbt * CH + h) * 32);
+            tsc = __ldg(sbase + (size_t)kbt * 8);
+        }
+        for (int kb = warp; kb < nkb_s && ok; kb += 8) {
+            while (kb >= (waited + 1) * ck && ok) {  // the piece that holds this k-block
                 ++waited;
                 ok = __all_sync(0xffffffffu, mb_wait(&s_wbar[waited], 0, a.err_flag, &s_abort));
                 HM_TRACE(if (tr && waited == 0) a.trace[10] = global_timer();)  // first piece of the staged weights has landed
@@ -403,8 +417,9 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
             uint4 cc[2];
 #pragma unroll
             for (int h = 0; h < CH; ++h) cc[h] = *reinterpret_cast<const uint4*>(codes_s + ((size_t)(kb * CH + h) * 32 + lane) * 16);
-            q_block<NG, Q4>(cc, *reinterpret_cast<const uint2*>(scales_s + kb * 32 + (lane >> 2) * 4), img + (size_t)kb * NG * IMG_WORDS, bsc + kb * NG * 2, csum + kb * NG * 4, lane, acc);
+            q_block<M, Q4>(cc, *reinterpret_cast<const uint2*>(scales_s + kb * 32 + (lane >> 2) * 4), img + (size_t)kb * NG * IW, bsc + kb * NG * 2, lane, acc);
         }
+        if (tail && ok) q_block<M, Q4>(tc, tsc, img + (size_t)kbt * NG * IW, bsc + kbt * NG * 2, lane, acc);
     } else
     for (int base = warp; base < nkb; base += 8 * QU) {
         // issue the next batch, then consume the current one
@@ -421,7 +436,7 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
 #pragma unroll
         for (int u = 0; u < QU; ++u) {
             const int kb = base + 8 * u;
-            if (kb < nkb) q_block<NG, Q4>(c[u], sc[u], img + (size_t)kb * NG * IMG_WORDS, bsc + kb * NG * 2, csum + kb * NG * 4, lane, acc);
+            if (kb < nkb) q_block<M, Q4>(c[u], sc[u], img + (size_t)kb * NG * IW, bsc + kb * NG * 2, lane, acc);
         }
 #pragma unroll
         for (int u = 0; u < QU; ++u) {
@@ -433,10 +448,10 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
 
     // ---- sum the 8 warps (fixed order), then the cluster ranks (fixed order) ----
     HM_TRACE(if (tr) a.trace[3] = global_timer();)
-    // the lane pair (q even, q odd) holds the two halves of a dot: planes 0,1 weigh 2^14, planes 2,3 weigh 1
+    // the lane pair (q even, q odd) holds the two halves of a dot: planes 0,1 weigh 1, planes 2,3 weigh 2^16
     {
         const int q = lane & 3, g = lane >> 2;
-        const float wgt = (q & 1) ? 1.0f : 16384.0f;
+        const float wgt = (q & 1) ? 65536.0f : 1.0f;
 #pragma unroll
         for (int ng = 0; ng < NG; ++ng) {
             const int m = 2 * ng + (q >> 1);
@@ -453,6 +468,14 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
     if (tid < M * 32) {
 #pragma unroll
         for (int w = 0; w < 8; ++w) v += red[w * M * 32 + tid];
+    }
+    if (vec_row && tid >= QT - M) {
+        // the rows' RMSNorm factors, by threads that have no part in the sum above
+        const int m = tid - (QT - M);
+        double t = 0.0;
+        for (int wv = 0; wv < 8; ++wv) t += s_wsum[wv][m];
+        const float mean = (float)(t * (1.0 / (double)a.K));
+        s_post[m] = 1.0f / sqrtf(mean + a.eps);
     }
     __syncthreads();
     if (tid < M * 32) red[tid] = v;  // vals [M][32]
@@ -477,6 +500,7 @@ __global__ void __launch_bounds__(QT) gemv_quant_kernel(const QuantArgs a) {
             for (int r = 1; r < a.ksplit; ++r) v += slots[r * (M * 32) + tid];
         }
     }
+    if (tid < M * 32) v *= s_post[tid >> 5];
     HM_TRACE(if (tr) a.trace[5] = global_timer();)
     if (a.epi == EPI_SWIGLU) {
         // tile = 16 gate rows followed by the 16 matching up rows
@@ -548,13 +572,26 @@ template <int M, bool Q4, bool CL, bool ST>
 cudaError_t launch_q4(const QuantArgs& a, size_t smem, cudaStream_t st, bool pdl);
 
 template <int M, bool Q4, bool CL>
-cudaError_t launch_q3(const QuantArgs& a, cudaStream_t st, bool pdl) {
-    constexpr int NG = (M + 1) / 2;
-    size_t smem = sizeof(float) * ((size_t)M * a.kb_per_split * 32 + (size_t)a.kb_per_split * NG * (IMG_WORDS + 6) + 8 * M * 32 + (CL ? (size_t)a.ksplit * M * 32 : 0));
-    const size_t slice = (size_t)a.kb_per_split * ((Q4 ? 1 : 2) * 512 + 64);
+cudaError_t launch_q3(const QuantArgs& a_in, int sm_count, cudaStream_t st, bool pdl) {
+    QuantArgs a = a_in;
+    // rows go from registers straight to digits when 16-byte loads can address them (RMSNorm: whole rows of up to 8192 elements)
+    a.from_regs = (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.ldx & 3) == 0 &&
+                  (a.pro != PRO_RMSNORM || ((reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0 && (a.K & 3) == 0 && a.K <= 8 * 4 * QT));
+    size_t smem = sizeof(float) * ((a.from_regs ? 0 : (size_t)M * a.kb_per_split * 32) + (size_t)a.kb_per_split * Img<M>::NG * (Img<M>::WORDS + 2) + 8 * M * 32 + (CL ? (size_t)a.ksplit * M * 32 : 0));
+    constexpr size_t BLK = (Q4 ? 1 : 2) * 512 + 64;  // staged bytes per k-block
+    size_t slice = (size_t)a.kb_per_split * BLK;
     const bool aligned = ((reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.scales)) & 15) == 0;
 #ifndef HM_QUANT_NO_STAGE
-    if (aligned && slice <= QUANT_STAGE_MAX && smem + slice <= 110 * 1024) return launch_q4<M, Q4, CL, true>(a, smem + slice, st, pdl);
+    if (aligned && slice <= QUANT_STAGE_MAX && smem + slice <= 110 * 1024) {
+        // CTAs an SM holds: three by registers (M = 1), fewer by shared memory (1 KB per CTA is the system's)
+        const auto per_sm = [](size_t bytes) { return (int)std::min<size_t>(M == 1 ? 3 : 2, (227 * 1024) / (bytes + 1024 + 1024)); };
+        const long ctas = (long)((a.N + 31) / 32) * a.ksplit;
+        if (a.ksplit == 1 && a.kb_per_split >= 16 && ctas > (long)per_sm(smem + slice) * sm_count && ctas <= (long)per_sm(smem + slice - 8 * BLK) * sm_count) {
+            a.reg_tail = 1;  // the whole launch becomes resident at once
+            slice -= 8 * BLK;
+        }
+        return launch_q4<M, Q4, CL, true>(a, smem + slice, st, pdl);
+    }
 #endif
     (void)slice;
     (void)aligned;
@@ -607,8 +644,8 @@ cudaError_t launch_qm(const QuantArgs& a_in, int sm_count, cudaStream_t st, bool
     if (ks < 1) ks = 1;
     a.kb_per_split = (nb + ks - 1) / ks;
     a.ksplit = (nb + a.kb_per_split - 1) / a.kb_per_split;
-    if (a.q4) return a.ksplit > 1 ? launch_q3<M, true, true>(a, st, pdl) : launch_q3<M, true, false>(a, st, pdl);
-    return a.ksplit > 1 ? launch_q3<M, false, true>(a, st, pdl) : launch_q3<M, false, false>(a, st, pdl);
+    if (a.q4) return a.ksplit > 1 ? launch_q3<M, true, true>(a, sm_count, st, pdl) : launch_q3<M, true, false>(a, sm_count, st, pdl);
+    return a.ksplit > 1 ? launch_q3<M, false, true>(a, sm_count, st, pdl) : launch_q3<M, false, false>(a, sm_count, st, pdl);
 }
 
 }  // namespace
