@@ -296,6 +296,66 @@ struct KvDesc {
     int bf16;                // page element type: 0 = f32, 1 = bf16
 };
 
+// Fused-QKV epilogue of the 32-row-tile projections (Q8_0 / Q4_0 / K-quants; no QK-norm on this path).  The q and k rows
+// of every head are stored so that a tile holds 16 dimensions of the head's first half followed by their 16 rotation
+// partners (rope_tile_row); v rows keep their order.
+struct RopeEpi {
+    int q_dim, kv_dim, hd;
+    const float* rope_cos;   // [max_pos][hd]
+    const float* rope_sin;
+    const int32_t* row_pos;  // [M] position of each row's token
+    const int32_t* row_seq;  // [M] sequence of each row; null: row m is sequence seq_base + m
+    int seq_base;
+    KvDesc kv;
+};
+
+// row nl of a q or k part (rows n_off ..) -> its place in the tiled weight arrays
+__host__ __device__ __forceinline__ int rope_tile_row(int nl, int n_off, int hd) {
+    const int head = nl / hd, d = nl - head * hd, half = hd >> 1;
+    const int hi = d >= half ? 1 : 0, dd = d - hi * half;
+    return n_off + head * hd + (dd >> 4) * 32 + hi * 16 + (dd & 15);
+}
+
+// Bias, half rotation (src/hf/emitter.rs:560-640; the operation order of post_qkv_kernel) and the KV-page write for one
+// value of a finished tile: vals = the tile's sums [M][32] in shared memory, v = vals[tid].
+__device__ __forceinline__ void rope_tile_epilogue(const RopeEpi& r, const float* vals, float v, int tid, int tile, int m_valid, int N, const float* bias, float* y, int ldy) {
+    const int m = tid >> 5, p = tid & 31, n0 = tile * 32;
+    if (m >= m_valid || n0 >= N) return;
+    const int pos = r.row_pos[m];
+    const int seq = r.row_seq ? r.row_seq[m] : r.seq_base + m;
+    const bool is_q = n0 < r.q_dim, is_k = !is_q && n0 < r.q_dim + r.kv_dim;
+    const int part_off = is_q ? 0 : (is_k ? r.q_dim : r.q_dim + r.kv_dim);
+    const int head = (n0 - part_off) / r.hd;
+    int d;
+    float val;
+    if (is_q || is_k) {
+        const int half = r.hd >> 1, hi = p >> 4;
+        d = (((n0 - part_off) - head * r.hd) >> 5) * 16 + (p & 15) + hi * half;
+        const int dp = hi ? d - half : d + half, base = part_off + head * r.hd;
+        val = v;
+        float oth = vals[tid ^ 16];
+        if (bias) {
+            val += bias[base + d];
+            oth += bias[base + dp];
+        }
+        oth = hi ? oth : -oth;
+        val = fmaf(oth, r.rope_sin[(size_t)pos * r.hd + d], val * r.rope_cos[(size_t)pos * r.hd + d]);
+    } else {
+        d = (n0 - part_off) - head * r.hd + p;
+        val = bias ? v + bias[n0 + p] : v;
+    }
+    if (is_q) {
+        y[(size_t)m * ldy + head * r.hd + d] = val;
+    } else {
+        const int page = r.kv.page_table[(size_t)seq * r.kv.max_pages + pos / r.kv.page_tokens];
+        const size_t off = ((size_t)page * r.kv.kv_heads + head) * r.kv.page_tokens * r.hd +
+                           (is_k ? k_tile_off(pos % r.kv.page_tokens, d) : v_tile_off(pos % r.kv.page_tokens, d, r.hd, r.kv.bf16));
+        void* pool = is_k ? r.kv.k_pool : r.kv.v_pool;
+        if (r.kv.bf16) reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(val);
+        else reinterpret_cast<float*>(pool)[off] = val;
+    }
+}
+
 struct GemvArgs {
     int* err_flag;                 // optional: raised to 2 when the bounded wait for the staged weights runs out
     unsigned long long* trace;     // optional (HM_GEMV_TRACE=1): 8 %globaltimer stamps of CTA 0 of this launch
@@ -397,14 +457,7 @@ struct QuantArgs {
     int ldy;
     const float* bias;
     const float* resid;
-    // EPI_QKV_ROPE (no QK-norm on this path)
-    int q_dim, kv_dim, hd;
-    const float* rope_cos;   // [max_pos][hd]
-    const float* rope_sin;
-    const int32_t* row_pos;  // [M] position of each row's token
-    const int32_t* row_seq;  // [M] sequence of each row; null: row m is sequence seq_base + m
-    int seq_base;
-    KvDesc kv;
+    RopeEpi rope;            // EPI_QKV_ROPE
 };
 
 // ---- launchers (defined in the .cu files) ----------------------------------------------

@@ -173,6 +173,19 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
             }
             if (ce == cudaSuccess) ce = launch_pack_tc((const uint16_t*)tmp, n_part, K, false, L.tc, n_off, interleave_which, stream_);
         }
+    }
+    // the QKV projection of a quantised model rotates in its own epilogue when a rotation pair can share a 32-row tile
+    // and there is no QK-norm (which needs a whole head in one CTA); all three parts must then agree
+    const bool rope_rows = q && rope_part != 0 && !cfg_.has_qk_norm && (hd_ / 2) % 16 == 0 && qdim_ % 32 == 0 && kvdim_ % 32 == 0;
+    if (q && rope_part != 0) {
+        if (L.loaded_parts > 0 && L.rope_rows != rope_rows) {
+            cudaFree(tmp);
+            return fail(HM_ERR_STATE, "q, k and v projections of a layer disagree on their row layout");
+        }
+        L.rope_rows = rope_rows;
+    }
+    const int rope_hd = rope_rows && rope_part == 1 ? hd_ : 0;
+    if (!q) {
     } else if (kq) {
         if (!L.kq_data) {
             ce = cudaMalloc(&L.kq_data, kquant_data_bytes(K, N_total));
@@ -186,7 +199,7 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
             return fail(HM_ERR_UNSUPPORTED, "gate and up projections of a layer must share one K-quant type");
         }
         L.kq_part_type = dtype;
-        if (ce == cudaSuccess) ce = launch_kquant_split((const uint8_t*)tmp, n_part, K, dtype == HM_Q6_K, n_off, interleave_which, L.kq_data, L.kq_tile_type, stream_);
+        if (ce == cudaSuccess) ce = launch_kquant_split((const uint8_t*)tmp, n_part, K, dtype == HM_Q6_K, n_off, interleave_which, L.kq_data, L.kq_tile_type, stream_, rope_hd);
         L.kq_bytes += nbytes;
         quant_ = true;
     } else {
@@ -197,15 +210,7 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
             if (ce == cudaSuccess) ce = cudaMemsetAsync(L.scales, 0, quant_scale_elems(K, N_total) * 2, stream_);
             if (ce == cudaSuccess) ce = cudaMemsetAsync(L.codes, 0, quant_code_bytes(K, N_total, q4), stream_);
         }
-        // the QKV projection of a Q8_0 / Q4_0 model rotates in its own epilogue when a rotation pair can share a 32-row tile
-        // and there is no QK-norm (which needs a whole head in one CTA); all three parts must then agree
-        const bool rope_rows = rope_part != 0 && !cfg_.has_qk_norm && (hd_ / 2) % 16 == 0 && qdim_ % 32 == 0 && kvdim_ % 32 == 0;
-        if (rope_part != 0 && L.loaded_parts > 0 && L.rope_rows != rope_rows) {
-            cudaFree(tmp);
-            return fail(HM_ERR_STATE, "q, k and v projections of a layer disagree on their row layout");
-        }
-        if (rope_part != 0) L.rope_rows = rope_rows;
-        if (ce == cudaSuccess) ce = launch_split_blocks((const uint8_t*)tmp, n_part, K, q4, n_off, interleave_which, L.scales, L.codes, stream_, rope_rows && rope_part == 1 ? hd_ : 0);
+        if (ce == cudaSuccess) ce = launch_split_blocks((const uint8_t*)tmp, n_part, K, q4, n_off, interleave_which, L.scales, L.codes, stream_, rope_hd);
         quant_ = true;
     }
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
@@ -726,6 +731,20 @@ int Engine::enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, 
     return HM_OK;
 }
 
+RopeEpi Engine::rope_epi(int layer, const int32_t* row_pos, const int32_t* row_seq, int m0) const {
+    RopeEpi r{};
+    r.q_dim = qdim_;
+    r.kv_dim = kvdim_;
+    r.hd = hd_;
+    r.rope_cos = rope_cos_;
+    r.rope_sin = rope_sin_;
+    r.row_pos = row_pos + m0;
+    r.row_seq = row_seq ? row_seq + m0 : nullptr;
+    r.seq_base = m0;
+    r.kv = KvDesc{k_pool_[layer], v_pool_[layer], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+    return r;
+}
+
 int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer,
                            const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches, const ArgmaxFold* fold) {
     for (int m0 = 0; m0 < M; m0 += MAX_M) {
@@ -813,6 +832,10 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.ldy = ldy;
             a.bias = bias;
             a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+            if (epi == EPI_QKV_ROPE) {
+                if (!L.rope_rows || layer < 0) return fail(HM_ERR_STATE, "projection rows are not in rotation-pair order");
+                a.rope = rope_epi(layer, row_pos, row_seq, m0);
+            }
             ce = launch_gemv_kquant(a, mp, sm_count_, stream_, pdl_);
         } else {
             QuantArgs a{};
@@ -838,15 +861,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
             if (epi == EPI_QKV_ROPE) {
                 if (!L.rope_rows || layer < 0) return fail(HM_ERR_STATE, "projection rows are not in rotation-pair order");
-                a.q_dim = qdim_;
-                a.kv_dim = kvdim_;
-                a.hd = hd_;
-                a.rope_cos = rope_cos_;
-                a.rope_sin = rope_sin_;
-                a.row_pos = row_pos + m0;
-                a.row_seq = row_seq ? row_seq + m0 : nullptr;
-                a.seq_base = m0;
-                a.kv = KvDesc{k_pool_[layer], v_pool_[layer], page_table_, max_pages_, page_tokens_, kvh_, hd_, kv_bf16_ ? 1 : 0};
+                a.rope = rope_epi(layer, row_pos, row_seq, m0);
             }
             ce = launch_gemv_quant(a, mp, sm_count_, stream_, pdl_);
         }

@@ -28,7 +28,7 @@ struct LinearW {
     size_t kq_bytes = 0;              // GGUF bytes loaded into it (what a step streams)
     int kq_part_type = -1;            // type of the part loaded last (gate and up must agree: they share tiles)
     int loaded_parts = 0;
-    bool rope_rows = false;  // Q8_0 / Q4_0 fused QKV: q and k rows stored in rotation-pair tiles (launch_split_blocks rope_hd), epilogue rotates
+    bool rope_rows = false;  // quantised fused QKV: q and k rows stored in rotation-pair tiles (rope_tile_row), the projection's epilogue rotates
     size_t bytes() const;
 };
 
@@ -88,6 +88,7 @@ class Engine {
     int load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, int interleave_which, int dtype, const void* host, size_t nbytes, int rope_part = 0);
     int load_vec_f32(float** dst, size_t n_total, size_t off, int dtype, const void* host, size_t n, size_t nbytes);
     int ensure_scratch(int rows);
+    RopeEpi rope_epi(int layer, const int32_t* row_pos, const int32_t* row_seq, int m0) const;
     // Enqueue one pass over M rows (decode: one row per sequence; prefill: a chunk of one
     // sequence).  lm_row0/lm_rows select the rows that go through the LM head.
     int enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_pos, const int32_t* row_seq, int lm_row0, int lm_rows, bool advance, uint32_t* next_dev, uint32_t* feed_dev, int32_t* pos_dev, uint32_t* hist_dev, int* launches);

@@ -80,12 +80,12 @@ __global__ void dequant_k_kernel(const uint8_t* __restrict__ blocks, size_t nblo
 }
 
 // ---- re-layout of GGUF blocks [rows][K/256] into the tiled array ------------------------------
-__global__ void kq_split_kernel(const uint8_t* __restrict__ blocks, size_t nblocks, int nb, int q6, int n_off, int interleave_which, uint8_t* __restrict__ data, uint8_t* __restrict__ tile_type) {
+__global__ void kq_split_kernel(const uint8_t* __restrict__ blocks, size_t nblocks, int nb, int q6, int n_off, int interleave_which, int rope_hd, uint8_t* __restrict__ data, uint8_t* __restrict__ tile_type) {
     const int bsz = q6 ? 210 : 144;
     for (size_t b = blockIdx.x * (size_t)blockDim.x + threadIdx.x; b < nblocks; b += (size_t)gridDim.x * blockDim.x) {
         const uint8_t* s = blocks + b * bsz;
         const int nl = (int)(b / nb), kb = (int)(b % nb);
-        const int n = interleave_which >= 0 ? (nl >> 4) * 32 + interleave_which * 16 + (nl & 15) : n_off + nl;
+        const int n = rope_hd > 0 ? rope_tile_row(nl, n_off, rope_hd) : interleave_which >= 0 ? (nl >> 4) * 32 + interleave_which * 16 + (nl & 15) : n_off + nl;
         const int tile = n >> 5, r = n & 31;
         uint8_t* dst = data + ((size_t)tile * nb + kb) * KQ_SLOT_BYTES;
         const int pieces = q6 ? 13 : 9;
@@ -401,6 +401,10 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
                 a.y[(size_t)m * a.ldy + j] = (g / (1.0f + expf(-g))) * u;
             }
         }
+    } else if (a.epi == EPI_QKV_ROPE) {
+        if (writer && tid < M * 32) red[tid] = v;
+        __syncthreads();
+        if (writer && tid < M * 32) rope_tile_epilogue(a.rope, red, v, tid, tile, a.m_valid, a.N, a.bias, a.y, a.ldy);
     } else if (writer && tid < M * 32) {
         const int m = tid >> 5, n = tile * 32 + (tid & 31);
         if (m < a.m_valid && n < a.N) {
@@ -467,11 +471,12 @@ cudaError_t launch_km(const KQuantArgs& a_in, int sm_count, cudaStream_t st, boo
 size_t kquant_data_bytes(int K, int N) { return (size_t)((N + 31) / 32) * (K / 256) * KQ_SLOT_BYTES; }
 size_t kquant_tiles(int N) { return (size_t)(N + 31) / 32; }
 
-cudaError_t launch_kquant_split(const uint8_t* blocks, int n_rows, int K, int q6, int n_off, int interleave_which, uint8_t* data, uint8_t* tile_type, cudaStream_t st) {
+cudaError_t launch_kquant_split(const uint8_t* blocks, int n_rows, int K, int q6, int n_off, int interleave_which, uint8_t* data, uint8_t* tile_type, cudaStream_t st, int rope_hd) {
+    if (rope_hd > 0 && ((rope_hd >> 1) % 16 != 0 || n_rows % rope_hd != 0 || n_off % 32 != 0 || interleave_which >= 0)) return cudaErrorInvalidValue;
     const size_t nblocks = (size_t)n_rows * (K / 256);
     size_t g = (nblocks + 127) / 128;
     g = std::min<size_t>(std::max<size_t>(g, 1), 148 * 32);
-    kq_split_kernel<<<(unsigned)g, 128, 0, st>>>(blocks, nblocks, K / 256, q6, n_off, interleave_which, data, tile_type);
+    kq_split_kernel<<<(unsigned)g, 128, 0, st>>>(blocks, nblocks, K / 256, q6, n_off, interleave_which, rope_hd, data, tile_type);
     return cudaGetLastError();
 }
 

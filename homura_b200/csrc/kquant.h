@@ -18,18 +18,20 @@ struct KQuantArgs {
     int pro;  // PRO_PLAIN / PRO_RMSNORM (f64 sum of squares)
     const float* norm_w;
     float eps;
-    int epi;  // EPI_STORE or EPI_SWIGLU (gate / up rows interleaved 16 + 16 per tile)
+    int epi;  // EPI_STORE, EPI_SWIGLU (gate / up rows interleaved 16 + 16 per tile) or EPI_QKV_ROPE (q and k rows in rotation-pair tiles)
     float* y;
     int ldy;
     const float* bias;
     const float* resid;
+    RopeEpi rope;  // EPI_QKV_ROPE
 };
 
 size_t kquant_data_bytes(int K, int N);
 size_t kquant_tiles(int N);
 // GGUF super-blocks of n_rows output rows (q6 = 0: Q4_K, 144 B; 1: Q6_K, 210 B) -> tiled array; rows land at n_off + n,
 // or interleaved 16 + 16 per tile when interleave_which is 0 (gate) or 1 (up).  data must start zeroed.
-cudaError_t launch_kquant_split(const uint8_t* blocks, int n_rows, int K, int q6, int n_off, int interleave_which, uint8_t* data, uint8_t* tile_type, cudaStream_t st);
+// rope_hd > 0: q or k rows of a fused QKV projection, stored in rotation-pair tiles (rope_tile_row).
+cudaError_t launch_kquant_split(const uint8_t* blocks, int n_rows, int K, int q6, int n_off, int interleave_which, uint8_t* data, uint8_t* tile_type, cudaStream_t st, int rope_hd = 0);
 cudaError_t launch_dequant_k(const uint8_t* blocks, size_t nblocks, int q6, float* out, cudaStream_t st);
 cudaError_t launch_gemv_kquant(const KQuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
 

@@ -49,11 +49,7 @@ __global__ void split_blocks_kernel(const uint8_t* __restrict__ blocks, size_t n
         const uint8_t* s = blocks + b * bsz;
         const int nl = (int)(b / nb), kb = (int)(b % nb);
         int n = interleave_which >= 0 ? (nl >> 4) * 32 + interleave_which * 16 + (nl & 15) : n_off + nl;
-        if (rope_hd > 0) {
-            const int head = nl / rope_hd, d = nl - head * rope_hd, half = rope_hd >> 1;
-            const int hi = d >= half ? 1 : 0, dd = d - hi * half;
-            n = n_off + head * rope_hd + (dd >> 4) * 32 + hi * 16 + (dd & 15);
-        }
+        if (rope_hd > 0) n = rope_tile_row(nl, n_off, rope_hd);
         const size_t tk = (size_t)(n >> 5) * nb + kb;
         const int r = n & 31, g = r & 7, r8 = r >> 3;  // row = g + 8 * r8
         scales[tk * 32 + g * 4 + r8] = (uint16_t)(s[0] | (s[1] << 8));
@@ -514,46 +510,10 @@ __global__ void __launch_bounds__(QT, (M == 1 && ST) ? 3 : 1) gemv_quant_kernel(
             }
         }
     } else if (a.epi == EPI_QKV_ROPE) {
-        // bias, half rotation (src/hf/emitter.rs:560-640; same operation order as the separate kernel of the K-quant plan) and the
-        // KV-page write: a q or k tile holds 16 dimensions of a head's first half and, 16 rows further, their partners
+        // a q or k tile holds 16 dimensions of a head's first half and, 16 rows further, their rotation partners
         if (writer && tid < M * 32) red[tid] = v;
         __syncthreads();
-        const int m = tid >> 5, p = tid & 31, n0 = tile * 32;
-        if (writer && tid < M * 32 && m < a.m_valid && n0 < a.N) {
-            const int pos = a.row_pos[m];
-            const int seq = a.row_seq ? a.row_seq[m] : a.seq_base + m;
-            const bool is_q = n0 < a.q_dim, is_k = !is_q && n0 < a.q_dim + a.kv_dim;
-            const int part_off = is_q ? 0 : (is_k ? a.q_dim : a.q_dim + a.kv_dim);
-            const int head = (n0 - part_off) / a.hd;
-            int d;
-            float val;
-            if (is_q || is_k) {
-                const int half = a.hd >> 1, hi = p >> 4;
-                d = (((n0 - part_off) - head * a.hd) >> 5) * 16 + (p & 15) + hi * half;
-                const int dp = hi ? d - half : d + half, base = part_off + head * a.hd;
-                val = v;
-                float oth = red[tid ^ 16];
-                if (a.bias) {
-                    val += a.bias[base + d];
-                    oth += a.bias[base + dp];
-                }
-                oth = hi ? oth : -oth;
-                val = fmaf(oth, a.rope_sin[(size_t)pos * a.hd + d], val * a.rope_cos[(size_t)pos * a.hd + d]);
-            } else {
-                d = (n0 - part_off) - head * a.hd + p;
-                val = a.bias ? v + a.bias[n0 + p] : v;
-            }
-            if (is_q) {
-                a.y[(size_t)m * a.ldy + head * a.hd + d] = val;
-            } else {
-                const int page = a.kv.page_table[(size_t)seq * a.kv.max_pages + pos / a.kv.page_tokens];
-                const size_t off = ((size_t)page * a.kv.kv_heads + head) * a.kv.page_tokens * a.hd +
-                                   (is_k ? k_tile_off(pos % a.kv.page_tokens, d) : v_tile_off(pos % a.kv.page_tokens, d, a.hd, a.kv.bf16));
-                void* pool = is_k ? a.kv.k_pool : a.kv.v_pool;
-                if (a.kv.bf16) reinterpret_cast<uint16_t*>(pool)[off] = f32_to_bf16_rne(val);
-                else reinterpret_cast<float*>(pool)[off] = val;
-            }
-        }
+        if (writer && tid < M * 32) rope_tile_epilogue(a.rope, red, v, tid, tile, a.m_valid, a.N, a.bias, a.y, a.ldy);
     } else if (writer && tid < M * 32) {
         const int m = tid >> 5, n = tile * 32 + (tid & 31);
         if (m < a.m_valid && n < a.N) {

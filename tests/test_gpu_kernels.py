@@ -97,6 +97,27 @@ def test_gemv_quant_matches_oracle(hm, oracle, kind, dt, M, K, N):
     assert rel_err(got, want) < 2e-5
 
 
+@pytest.mark.parametrize("kind,dt", [("q8_0", "Q8_0"), ("q4_0", "Q4_0")])
+def test_gemv_quant_wide_dynamic_range(hm, oracle, kind, dt):
+    # The projection rewrites every 32-element block of a row as one power-of-two scale and 31-bit integers: rows whose
+    # blocks differ by many orders of magnitude, all-zero blocks, a lone outlier inside a block and exact powers of two.
+    gt = synth.GGML_Q8_0 if kind == "q8_0" else synth.GGML_Q4_0
+    M, K, N = 4, 2048, 512
+    blocks = synth.quant_blocks(11, f"w{K}x{N}", N, K, gt)
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    x[0] *= np.exp(6.0 * rng.standard_normal(K)).astype(np.float32)         # element-wise spread of e^+-18
+    x[1].reshape(-1, 32)[::3] = 0.0                                           # zero blocks
+    x[1] *= np.repeat(np.exp(10.0 * rng.standard_normal(K // 32)), 32).astype(np.float32)  # block-wise spread
+    x[2] *= 1e-3
+    x[2, 5::64] = 1e4                                                         # outliers: the rest of their blocks keeps 2^-30 of them
+    x[3] = np.ldexp(1.0, rng.integers(-20, 20, K)).astype(np.float32) * rng.choice([-1.0, 1.0], K).astype(np.float32)
+    want = oracle.matmul_q(x, blocks, N, kind)
+    got = hm.gemv_quant(x, blocks, hm.DType[dt], N)
+    for m in range(M):
+        assert rel_err(got[m], want[m]) < 2e-5, m
+
+
 def test_rms_norm_and_rope(hm, oracle):
     rng = np.random.default_rng(3)
     x = rng.standard_normal((5, 896), dtype=np.float32)
