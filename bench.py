@@ -21,6 +21,7 @@ Prints ONE JSON line (rank 0):
              live after the timed region), against the measured HBM copy bandwidth;
   e2e_logits the same per-token call with the [vocab] f32 logits copied back every step, which is what
              the reference's trait returns (decode_step -> Vec<f32>, src/hf/model.rs:359-371);
+  e2e_sampled  hm_generate at the reference's default sampling settings (batch-1 workloads), prefill excluded;
   c5         the batched configuration (Qwen2.5-1.5B architecture, 64 sequences per GPU, 512-token
              prompts) timed the same way on bf16 and on f32 KV pages, with its prefill rate;
   cpu_baseline  the CPU oracle (a restatement of Homura's CPU path) on a bounded sample.
@@ -377,6 +378,25 @@ def main():
     e2e_lg_s = time.perf_counter() - t
     barrier()
     e2e_lg_tps = world * B * K / vmax(e2e_lg_s)
+    # sampled generation at the reference's default settings (temperature 0.7, top-k 50, top-p 0.9, repetition
+    # penalty 1.1; src/generate.rs:648-683) through hm_generate, the sampler on the device
+    e2e_smp = None
+    if B == 1:
+        # two generations from an empty cache that differ only in length: the difference leaves the prefill out, as the
+        # reference's decode rate does (src/generate.rs:820-841)
+        n_short = 8
+        n_long = min(n_short + K, max_seq - PL - 1)
+        times = []
+        for n_new in (n_short, n_long):
+            m.reset_kv_cache(seq=0)
+            t = time.perf_counter()
+            got = m.generate_ids(prompts[0], n_new, hm.SamplingConfig(seed=SEED))
+            times.append((time.perf_counter() - t, len(got)))
+        barrier()
+        (t_s, g_s), (t_l, g_l) = times
+        if g_l > g_s and t_l > t_s:
+            e2e_smp = {"value": world * (g_l - g_s) / vmax(t_l - t_s), "unit": "tok/s", "new_tokens": g_l - g_s, "d2h_bytes_per_step": 4,
+                       "api": "hm_generate with SamplingConfig defaults, sampler on the device; rate over the tokens by which a long generation exceeds a short one (prefill excluded)"}
 
     # ---- per-kernel-class device times (launch by launch, CUDA events) ----
     prof = m.profile_decode(8)
@@ -402,7 +422,7 @@ def main():
     step_bytes = weight_bytes + B * (kv_bytes_tok * T_avg + kv_bytes_tok)  # weights once per step, every sequence's cache
     step_gbs = step_bytes * (tok_per_s / world / B) / 1e9
     if fmt != "bf16":
-        kern = "gemv_kquant_kernel<1> (Q4_K/Q6_K projections: Q8_K activations, dp4a; LM head in f32)" if fmt == "q4_k_m" else "gemv_quant_kernel<1> (Q8_0/Q4_0 dequantising projections; LM head included)"
+        kern = "gemv_kquant_kernel<1> (Q4_K/Q6_K projections: Q8_K activations, dp4a; LM head in f32)" if fmt == "q4_k_m" else "gemv_quant_kernel<1> (Q8_0/Q4_0 projections, block dots on mma.sync s8; LM head included)"
     elif B > 8:
         kern = "gemm_tc_kernel (tcgen05 projections over 64 rows; LM head included)"
     else:
@@ -424,6 +444,7 @@ def main():
         "e2e": {"value": e2e_tps, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "api": "hm_decode_step (host token ids in, greedy next token ids out, one stream sync per step)"},
         "e2e_logits": {"value": e2e_lg_tps, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B + 4 * B * cfg.vocab_size,
                        "api": "hm_decode_step with the [vocab] f32 logits returned (the reference trait's decode_step -> Vec<f32>)"},
+        "e2e_sampled": e2e_smp,
         "gpu_launches": launches_per_step * K,
         "roofline": {
             "bound": "hbm", "kernel": kern, "achieved": achieved, "peak": peak, "unit": "GB/s",

@@ -546,8 +546,8 @@ cudaError_t launch_q3(const QuantArgs& a_in, int sm_count, cudaStream_t st, bool
         // CTAs an SM holds: three by registers (M = 1), fewer by shared memory (1 KB per CTA is the system's)
         const auto per_sm = [](size_t bytes) { return (int)std::min<size_t>(M == 1 ? 3 : 2, (227 * 1024) / (bytes + 1024 + 1024)); };
         const long ctas = (long)((a.N + 31) / 32) * a.ksplit;
-        if (a.ksplit == 1 && a.kb_per_split >= 16 && ctas > (long)per_sm(smem + slice) * sm_count && ctas <= (long)per_sm(smem + slice - 8 * BLK) * sm_count) {
-            a.reg_tail = 1;  // the whole launch becomes resident at once
+        if (a.ksplit == 1 && a.kb_per_split >= 16 && ctas > (long)per_sm(smem + slice) * sm_count && per_sm(smem + slice - 8 * BLK) > per_sm(smem + slice)) {
+            a.reg_tail = 1;  // one more CTA per SM: the Q8_0 gate/up launch becomes resident at once, the LM head runs fewer waves
             slice -= 8 * BLK;
         }
         return launch_q4<M, Q4, CL, true>(a, smem + slice, st, pdl);
