@@ -331,17 +331,22 @@ int hm_weight_bytes(hm_engine* e, uint64_t* out) {
     return HM_OK;
 }
 
+// Vectors (norm weights, biases) first: whether a model has QK-norm is inferred from its tensors, and the layout of
+// a quantised QKV projection (rotation in its epilogue or not) is fixed when its first part is loaded.
 static int load_views(Engine* eng, const std::vector<TensorView>& views, std::string* err) {
-    for (const TensorView& t : views) {
-        if (t.dtype < 0) {
-            *err = "unsupported GGML type for tensor '" + t.name + "'";
-            return HM_ERR_UNSUPPORTED;
-        }
-        if (t.name.find("rotary_emb.inv_freq") != std::string::npos) continue;
-        int rc = eng->load_tensor(t.name.c_str(), t.dtype, t.shape.data(), (int)t.shape.size(), t.data, t.nbytes);
-        if (rc) {
-            *err = eng->err;
-            return rc;
+    for (int pass = 0; pass < 2; ++pass) {
+        for (const TensorView& t : views) {
+            if (t.dtype < 0) {
+                *err = "unsupported GGML type for tensor '" + t.name + "'";
+                return HM_ERR_UNSUPPORTED;
+            }
+            if (t.name.find("rotary_emb.inv_freq") != std::string::npos) continue;
+            if ((t.shape.size() == 1) != (pass == 0)) continue;
+            int rc = eng->load_tensor(t.name.c_str(), t.dtype, t.shape.data(), (int)t.shape.size(), t.data, t.nbytes);
+            if (rc) {
+                *err = eng->err;
+                return rc;
+            }
         }
     }
     return HM_OK;

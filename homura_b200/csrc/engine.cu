@@ -348,6 +348,9 @@ int Engine::load_tensor(const char* cname, int dtype, const int64_t* shape, int 
     if (is("self_attn.k_proj.bias", "attn_k.bias")) return shape1(kvdim_) ? load_vec_f32(&Lw.qkv_bias, QKV, qdim_, dtype, host, n, nbytes) : bad_shape();
     if (is("self_attn.v_proj.bias", "attn_v.bias")) return shape1(kvdim_) ? load_vec_f32(&Lw.qkv_bias, QKV, qdim_ + kvdim_, dtype, host, n, nbytes) : bad_shape();
     if (is("self_attn.q_norm.weight", "attn_q_norm.weight")) {
+        // a quantised QKV projection stored for rotation in its own epilogue cannot take a QK-norm afterwards
+        for (const LayerW& l : layers_)
+            if (l.qkv.rope_rows) return fail(HM_ERR_STATE, "QK-norm weights must be loaded before the quantised q / k / v projections (hm_model_load does so)");
         cfg_.has_qk_norm = 1;
         return shape1(hd_) ? load_vec_f32(&Lw.q_norm, hd_, 0, dtype, host, n, nbytes) : bad_shape();
     }

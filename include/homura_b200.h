@@ -103,7 +103,9 @@ HM_API int hm_model_load(const char* model_dir, int weight_dtype, int device, hm
 /* HfModel::load_gguf, src/hf/model.rs:46-75: config from `<arch>.*` metadata, blk.N.* tensors. */
 HM_API int hm_model_load_gguf(const char* gguf_path, int device, hm_engine** out);
 /* Build from tensors handed over one by one (what a caller that already parsed a checkpoint
- * does): load_transformer_weights, src/hf/weights.rs:267-417 / src/gguf.rs:589-708. */
+ * does): load_transformer_weights, src/hf/weights.rs:267-417 / src/gguf.rs:589-708.  Whether the model has
+ * QK-norm is inferred from its tensors and decides how quantised q / k / v projections are stored: hand over the
+ * q_norm / k_norm weights before those projections (HM_ERR_STATE otherwise; hm_model_load* do so). */
 HM_API int hm_engine_create(const hm_config* cfg, int device, hm_engine** out);
 HM_API int hm_load_tensor(hm_engine* e, const char* name, int dtype, const int64_t* shape, int ndim, const void* host_data, size_t nbytes);
 HM_API int hm_finalize_weights(hm_engine* e);

@@ -421,6 +421,48 @@ def test_batch_20_decode_on_tensor_cores(hm, oracle):
         assert [int(v) for v in out[b]] == want
 
 
+@pytest.mark.parametrize("gt,kind", [(synth.GGML_Q8_0, "Q8_0"), (synth.GGML_Q4_0, "Q4_0"), (synth.GGML_Q4_K, "Q4_K")])
+@pytest.mark.parametrize("variant", ["bias", "hd128", "qk_norm"])
+def test_gguf_qkv_epilogue_variants(hm, oracle, gt, kind, variant):
+    # The quantised QKV projection rotates and writes the KV pages in its own epilogue when a rotation pair fits a
+    # 32-row tile: with biases (Qwen2 files), with 128-wide heads (pairs 64 rows apart: four tiles per head), and
+    # not at all with QK-norm (Qwen3 files keep the separate rotation launch).  Three sequences decode together, so
+    # every row must reach its own sequence's pages, and the prompt spans two 8-row launch groups.
+    kw = dict(tie_word_embeddings=True, rope_theta=1e4, rms_norm_eps=1e-5, intermediate_size=768)
+    if variant == "bias":
+        cfg = synth.tiny_config(qkv_bias=True, **kw)
+    elif variant == "hd128":
+        cfg = synth.tiny_config(qkv_bias=False, num_attention_heads=4, num_key_value_heads=2, head_dim=128, **kw)
+    else:
+        cfg = synth.tiny_config(qkv_bias=False, qk_norm=True, head_dim=128, **kw)
+    # Q4_K: Q8_K activation codes, see KQ_REL below.  Q8_0 / Q4_0: 3e-4 of the largest logit; measured 1.4e-4 on the
+    # 128-wide-head Q8_0 model (512-wide attention on a 256-wide hidden state, random blocks: near-ties in the
+    # softmax amplify last-ulp differences of expf), 2e-5 .. 6e-5 on the others.
+    rel = 1e-2 if kind == "Q4_K" else 3e-4
+    p = os.path.join(tempfile.mkdtemp(), "m.gguf")
+    synth.write_gguf_model(p, cfg, seed=9, ggml_type=gt, norm_jitter=0.1)
+    m = hm.HfModel.load_gguf(p)
+    B = 3
+    m.init_kv_cache(64, batch=B)
+    oms = [oracle.OracleModel.from_gguf(p, max_seq_len=64) for _ in range(B)]
+    cur = []
+    for b in range(B):
+        ids = synth.prompt_ids(40 + b, 11 + 3 * b, cfg.vocab_size)
+        t_o, lg_o = oms[b].prefill(ids)
+        t_g, lg_g = m.prefill(ids, seq=b, want_logits=True)
+        assert_logits_close(lg_g, lg_o, what=f"model logits ({kind}, QKV epilogue variants)", rel=rel)
+        assert t_g == t_o
+        cur.append(t_o)
+    for _ in range(6):
+        lg, nxt = m.decode_step(cur)
+        for b in range(B):
+            lo = oms[b].decode_step(cur[b])
+            assert_logits_close(lg[b], lo, what=f"model logits ({kind}, QKV epilogue variants)", rel=rel)
+            assert int(nxt[b]) == oracle.argmax(lo)
+            cur[b] = oracle.argmax(lo)
+    m.close()
+
+
 # ---- K-quant GGUF models (Q4_K / Q6_K, the mix of a Q4_K_M file) ---------------------------------
 
 
