@@ -463,6 +463,33 @@ def test_gguf_qkv_epilogue_variants(hm, oracle, gt, kind, variant):
     m.close()
 
 
+@pytest.mark.parametrize("gt,kind", [(synth.GGML_Q8_0, "Q8_0"), (synth.GGML_Q4_0, "Q4_0")])
+def test_gguf_hidden_rows_beyond_the_register_prologue(hm, oracle, gt, kind):
+    # Rows of more than 8192 elements do not fit the prologue that turns a row into digit planes straight from
+    # registers: the RMSNorm projections of such a model stage the normalised row as f32 first (one layer, narrow
+    # heads and MLP keep the model small).
+    cfg = synth.tiny_config(hidden_size=8448, num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512, num_hidden_layers=1,
+                            vocab_size=512, qkv_bias=False, tie_word_embeddings=True, rope_theta=1e4, rms_norm_eps=1e-5)
+    p = os.path.join(tempfile.mkdtemp(), "m.gguf")
+    synth.write_gguf_model(p, cfg, seed=13, ggml_type=gt, norm_jitter=0.1)
+    om = oracle.OracleModel.from_gguf(p, max_seq_len=48)
+    m = hm.HfModel.load_gguf(p)
+    m.init_kv_cache(48)
+    ids = synth.prompt_ids(21, 10, cfg.vocab_size)
+    tok_o, lg_o = om.prefill(ids)
+    tok_g, lg_g = m.prefill(ids, want_logits=True)
+    assert_logits_close(lg_g, lg_o, what=f"model logits ({kind}, 8448-wide rows)", rel=3e-4)
+    assert tok_g == tok_o
+    cur = tok_o
+    for _ in range(8):
+        lo = om.decode_step(cur)
+        lgd, nxt = m.decode_step([cur])
+        assert_logits_close(lgd[0], lo, what=f"model logits ({kind}, 8448-wide rows)", rel=3e-4)
+        cur = oracle.argmax(lo)
+        assert int(nxt[0]) == cur
+    m.close()
+
+
 # ---- K-quant GGUF models (Q4_K / Q6_K, the mix of a Q4_K_M file) ---------------------------------
 
 
