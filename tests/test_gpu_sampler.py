@@ -117,11 +117,13 @@ def test_top_k_disabled_or_wide_on_device(hm, oracle):
         assert hm.sample_token_device(logits, cfg, [], seed) == hm.sample_token(logits, cfg, [], seed)
 
 
-def test_batched_sampled_decode_step(hm, oracle):
-    # hm_decode_step_sampled: decode_step + sample_token for every sequence of a batch, one RNG word each
+@pytest.mark.parametrize("vocab", [1024, 20000])
+def test_batched_sampled_decode_step(hm, oracle, vocab):
+    # hm_decode_step_sampled: decode_step + sample_token for every sequence of a batch, one RNG word each.  The small
+    # vocabulary runs the one-CTA kernel, the large one a cluster of eight CTAs per sequence.
     import tempfile
 
-    cfg = synth.tiny_config()
+    cfg = synth.tiny_config(vocab_size=vocab)
     d = synth.write_hf_model(tempfile.mkdtemp(), cfg, seed=7, norm_jitter=0.1)
     B = 3
     m = hm.HfModel.load(d)
