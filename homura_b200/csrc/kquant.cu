@@ -261,7 +261,101 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
     float inv[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) inv[m] = 1.0f;
-    if (a.pro == PRO_RMSNORM) {
+    // One-round-trip prologue (quantised activations behind an RMSNorm, up to four 256-value blocks per warp): every
+    // block of every row is read once, 8 values per lane, and stays in registers while the sums of squares meet in
+    // shared memory; the blocks of this CTA's K range are then normalised and quantised from the registers, in the
+    // reference's operation order ((x * inv) * w, emitter_quant.rs:713-791, then Q8_K as emit_quant.rs:409-460).
+    // (Quantising x * w and applying inv to the finished dot would save the barrier as well, and Q8_K codes are
+    // invariant under a positive row factor in exact arithmetic; but a product that rounds the other way moves a
+    // code that sits exactly on .5, which the quantised embeddings and bf16 norm weights of the test models produce
+    // often enough to leave the tolerance.)
+    constexpr int IT = 4;
+    const bool one_pass = ACTQ && a.pro == PRO_RMSNORM && (a.ldx & 3) == 0 && M * nb <= 8 * IT &&
+                          ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.norm_w)) & 15) == 0;
+    if (one_pass) {
+        float4 xa[IT][2];
+        double ss[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) ss[m] = 0.0;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int item = warp + 8 * it;
+            xa[it][0] = xa[it][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (item < M * nb) {
+                const int m = item / nb, kb = item - m * nb;
+                const float* xr = a.x + (size_t)m * a.ldx + (size_t)kb * 256 + lane * 8;
+                xa[it][0] = ld_cg_f32x4(xr);
+                xa[it][1] = ld_cg_f32x4(xr + 4);
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int item = warp + 8 * it;
+            if (item < M * nb) {
+                const int m = item / nb;
+                const float xv[8] = {xa[it][0].x, xa[it][0].y, xa[it][0].z, xa[it][0].w, xa[it][1].x, xa[it][1].y, xa[it][1].z, xa[it][1].w};
+                double sq = 0.0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sq += (double)xv[i] * (double)xv[i];
+#pragma unroll
+                for (int mm = 0; mm < M; ++mm)
+                    if (mm == m) ss[mm] += sq;
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            double t = ss[m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (lane == 0) s_wsum[warp][m] = t;
+        }
+        __syncthreads();
+        if (tid < M) {
+            double t = 0.0;
+            for (int wv = 0; wv < 8; ++wv) t += s_wsum[wv][tid];
+            const float mean = (float)(t * (1.0 / (double)a.K));
+            s_inv[tid] = 1.0f / sqrtf(mean + a.eps);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int item = warp + 8 * it;
+            if (item >= M * nb) continue;
+            const int m = item / nb, kb = item - m * nb;
+            if (kb < kb0 || kb >= kb1) continue;  // warp-uniform
+            const int kbl = kb - kb0;
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)kb * 256 + lane * 8));
+            const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)kb * 256 + lane * 8 + 4));
+            const float xv[8] = {xa[it][0].x, xa[it][0].y, xa[it][0].z, xa[it][0].w, xa[it][1].x, xa[it][1].y, xa[it][1].z, xa[it][1].w};
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            const float rinv = s_inv[m];
+            float v[8];
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = (xv[i] * rinv) * wv[i];
+                amax = fmaxf(amax, fabsf(v[i]));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float iscale = amax == 0.f ? 0.f : __fdiv_rn(127.0f, amax);
+            int sum = 0;
+            uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float r = rintf(__fmul_rn(v[i], iscale));
+                r = fminf(r, 127.0f);
+                r = fmaxf(r, -127.0f);
+                const int q = (int)r;
+                sum += q;
+                packed[i >> 2] |= ((uint32_t)(q & 0xFF)) << (8 * (i & 3));
+            }
+            *reinterpret_cast<uint2*>(q8 + (size_t)m * kspan + kbl * 256 + lane * 8) = make_uint2(packed[0], packed[1]);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // groups of 16 codes = two lanes
+            if ((lane & 1) == 0) bsums[((size_t)m * nbspan + kbl) * 16 + (lane >> 1)] = sum;
+            if (lane == 0) act_d[m * nbspan + kbl] = __fdiv_rn(amax, 127.0f);
+        }
+    } else if (a.pro == PRO_RMSNORM) {
         constexpr int XV = 8;  // rows of up to 8192 elements: every 16-byte piece requested before the first use
         const bool vec_row = (a.K & 3) == 0 && a.K <= XV * 4 * KT && (a.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
 #pragma unroll
@@ -303,7 +397,7 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
         for (int m = 0; m < M; ++m) inv[m] = s_inv[m];
     }
     // a warp takes whole 256-value blocks: lane holds 8 consecutive values
-    for (int item = warp; item < M * nkb; item += 8) {
+    for (int item = warp; item < (one_pass ? 0 : M * nkb); item += 8) {
         const int m = item / nkb, kbl = item - m * nkb;
         const float* xr = a.x + (size_t)m * a.ldx + (size_t)(kb0 + kbl) * 256 + lane * 8;
         float v[8];
