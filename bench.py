@@ -358,7 +358,9 @@ def main():
     # ---- end to end through the per-token C-ABI call (host token in, host token out) ----
     for b in range(B):
         m.reset_kv_cache(seq=b)
+    t = time.perf_counter()
     cur = [m.prefill(prompts[b], seq=b) for b in range(B)]
+    prefill_s = time.perf_counter() - t  # hm_prefill per sequence: host ids in, first token out (the kernels are warm from the device-timed region)
     for _ in range(W):
         _, nxt = m.decode_step(cur, want_logits=False)
         cur = [int(v) for v in nxt]
@@ -445,6 +447,7 @@ def main():
         "e2e_logits": {"value": e2e_lg_tps, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B + 4 * B * cfg.vocab_size,
                        "api": "hm_decode_step with the [vocab] f32 logits returned (the reference trait's decode_step -> Vec<f32>)"},
         "e2e_sampled": e2e_smp,
+        "prefill": {"tok_per_s": world * B * PL / vmax(prefill_s), "prompt_tokens": PL, "api": "hm_prefill, one call per sequence, end to end"},
         "gpu_launches": launches_per_step * K,
         "roofline": {
             "bound": "hbm", "kernel": kern, "achieved": achieved, "peak": peak, "unit": "GB/s",

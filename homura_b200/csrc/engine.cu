@@ -398,8 +398,8 @@ uint64_t Engine::weight_bytes() const {
 // ---- scratch ---------------------------------------------------------------------------------
 
 int Engine::ensure_scratch(int rows) {
-    const bool tall = use_tc_ && !quant_;  // prefill chunks of TC_ROWS rows
-    if (tall) rows = std::max(rows, TC_ROWS);
+    const bool tall = use_tc_ && !quant_;  // prefill chunks of TC_ROWS rows on the tensor-core GEMM
+    if (tall || quant_) rows = std::max(rows, TC_ROWS);
     const int cap = (rows + MAX_M - 1) / MAX_M * MAX_M;
     if (cap <= scratch_rows_) return HM_OK;
     auto re = [&](auto** p, size_t count) -> cudaError_t {
@@ -1130,7 +1130,9 @@ int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t*
     st[3 * n + 2] = (uint32_t)(len0 + n);
     HM_CUDA(cudaMemcpyAsync(smp_gen_start_ + seq, st + 3 * n + 2, 4, cudaMemcpyHostToDevice, stream_));
     int launches = 0;
-    const int chunk = (use_tc_ && !quant_) ? TC_ROWS : MAX_M;
+    // GGUF models run a chunk's projections as 8-row groups of the quantised kernels, launched back to back: the groups after
+    // the first find the projection's weights in the L2, and attention, embedding and LM head run once per chunk
+    const int chunk = (use_tc_ || quant_) ? TC_ROWS : MAX_M;
     for (int c0 = 0; c0 < n; c0 += chunk) {
         const int mc = std::min(chunk, n - c0);
         const bool last = c0 + mc >= n;
