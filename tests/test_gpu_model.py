@@ -490,6 +490,20 @@ def test_gguf_hidden_rows_beyond_the_register_prologue(hm, oracle, gt, kind):
     m.close()
 
 
+def test_qk_norm_after_quantised_projections_is_refused(hm):
+    # A host that hands tensors over one by one decides the row order of a quantised q projection by loading it; the
+    # engine cannot add a QK-norm to a projection stored for the rotating epilogue afterwards and must say so.
+    cfg = synth.tiny_config(qkv_bias=False, qk_norm=True, head_dim=64, num_hidden_layers=1)
+    tc = hm.TransformerConfig(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size, num_attention_heads=cfg.num_attention_heads,
+                              num_hidden_layers=1, num_key_value_heads=cfg.num_key_value_heads, vocab_size=cfg.vocab_size, head_dim=64)
+    q = synth.quant_blocks(3, "q", cfg.q_dim, cfg.hidden_size, synth.GGML_Q8_0)
+    qn = np.ones(64, np.float32)
+    late = [("blk.0.attn_q.weight", hm.DType.Q8_0, (cfg.q_dim, cfg.hidden_size), q), ("blk.0.attn_q_norm.weight", hm.DType.F32, (64,), qn)]
+    with pytest.raises(hm.HomuraError) as e:
+        hm.HfModel.from_tensors(tc, late)
+    assert e.value.status == hm.HM_ERR_STATE and "QK-norm" in e.value.message
+
+
 # ---- K-quant GGUF models (Q4_K / Q6_K, the mix of a Q4_K_M file) ---------------------------------
 
 
