@@ -253,7 +253,11 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
 
     pdl_launch_dependents();
     // weights never depend on the previous kernel: ask the L2 for this CTA's super-blocks before the dependency wait
-    if (tid < 32 && nkb > 0) l2_prefetch_slice(tbase, (unsigned long long)nkb * KQ_SLOT_BYTES, 0, 1, tid);
+    // (a Q4_K tile fills 9 of its slot's 13 pieces and no scale words: only the bytes that will be read are asked for)
+    if (ttype != 0) {
+        const unsigned used = ttype == 2 ? (unsigned)KQ_SLOT_BYTES : 9u * 512u;
+        for (int kbl = tid; kbl < nkb; kbl += KT) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(tbase + (size_t)kbl * KQ_SLOT_BYTES), "r"(used) : "memory");
+    }
     pdl_wait();
 
     // ---- prologue: activations of this CTA's K range (RMSNorm with an f64 sum of squares on request,
