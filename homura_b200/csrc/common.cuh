@@ -458,6 +458,9 @@ struct QuantArgs {
     const float* bias;
     const float* resid;
     RopeEpi rope;            // EPI_QKV_ROPE
+    // launch_gemm_quant: the rows as digit planes, written by its packing launch
+    const uint32_t* img_in;  // [K/32][32 row pairs][64 words]
+    const float* bs_in;      // [K/32][32 row pairs][2]
 };
 
 // ---- launchers (defined in the .cu files) ----------------------------------------------
@@ -492,6 +495,11 @@ size_t quant_code_bytes(int K, int N, int q4);
 cudaError_t launch_split_blocks(const uint8_t* blocks, int n_rows, int K, int q4, int n_off, int interleave_which, uint16_t* scales, uint8_t* codes, cudaStream_t st, int rope_hd = 0);
 cudaError_t launch_dequant(const uint8_t* blocks, size_t nblocks, int q4, float* out, cudaStream_t st);
 cudaError_t launch_gemv_quant(const QuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
+// Q8_0 / Q4_0 projection over up to 64 rows (a.m_valid): a packing launch (rows -> digit planes in img / bs) and the multiply.
+size_t quant_rows_image_words(int K);
+size_t quant_rows_scale_floats(int K);
+bool quant_rows_supported(const QuantArgs& a);
+cudaError_t launch_gemm_quant(const QuantArgs& a, uint32_t* img, float* bs, int sm_count, cudaStream_t st, bool pdl, int* launches);
 // quant plan helpers: PostQKV (src/hf/emitter_quant.rs:800-905) and SiLU*Up (:1078-1099)
 cudaError_t launch_post_qkv(const float* qkv, int M, int heads, int kv_heads, int hd, int has_qk_norm, const float* q_norm_w, const float* k_norm_w, float eps, const float* rope_cos, const float* rope_sin, const int32_t* row_pos, const int32_t* row_seq, const KvDesc& kv, float* q_out, cudaStream_t st, bool pdl);
 cudaError_t launch_hist_set(const uint32_t* tokens, const int32_t* pos, uint32_t* hist, int hist_stride, int batch, cudaStream_t st);

@@ -111,6 +111,7 @@ Engine::~Engine() {
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_); fr(fin_ticket_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
+    fr(qrows_img_); fr(qrows_bs_);
     fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_); fr(smp_overflow_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
@@ -417,6 +418,12 @@ int Engine::ensure_scratch(int rows) {
     HM_CUDA(re(&logits_, (size_t)cap * V_));
     HM_CUDA(re(&amax_val_, (size_t)cap * nslabs_v));
     HM_CUDA(re(&amax_idx_, (size_t)cap * nslabs_v));
+    if (quant_) {
+        // digit planes of up to 64 rows of the widest projection input (launch_gemm_quant)
+        qrows_k_ = std::max(std::max(H_, qdim_), I_);
+        HM_CUDA(re(&qrows_img_, quant_rows_image_words(qrows_k_)));
+        HM_CUDA(re(&qrows_bs_, quant_rows_scale_floats(qrows_k_)));
+    }
     if (quant_ || tall) {
         HM_CUDA(re(&qkv_raw_, (size_t)cap * (qdim_ + 2 * kvdim_)));
         HM_CUDA(re(&gu_raw_, (size_t)cap * 2 * I_));
@@ -750,6 +757,48 @@ RopeEpi Engine::rope_epi(int layer, const int32_t* row_pos, const int32_t* row_s
 
 int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int pro, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer,
                            const int32_t* row_pos, const int32_t* row_seq, float* amax_val, int32_t* amax_idx, int* launches, const ArgmaxFold* fold) {
+    // Q8_0 / Q4_0 projections over more than eight rows (prefill chunks, larger batches): the rows become digit planes once
+    // and 64-row launches multiply them, instead of every CTA of an 8-row launch packing its own
+    if ((L.kind == HM_Q8_0 || L.kind == HM_Q4_0) && M > MAX_M && qrows_img_ && L.K <= qrows_k_ && (epi == EPI_STORE || epi == EPI_SWIGLU || epi == EPI_QKV_ROPE)) {
+        QuantArgs probe{};
+        probe.x = x;
+        probe.ldx = ldx;
+        probe.K = L.K;
+        probe.norm_w = pro == PRO_RMSNORM ? norm_w : nullptr;
+        probe.codes = L.codes;
+        probe.scales = L.scales;
+        if (quant_rows_supported(probe)) {
+            for (int m0 = 0; m0 < M; m0 += TC_ROWS) {
+                QuantArgs a{};
+                a.err_flag = err_flag_;
+                a.scales = L.scales;
+                a.codes = L.codes;
+                a.q4 = L.kind == HM_Q4_0;
+                a.K = L.K;
+                a.N = L.N;
+                a.m_valid = std::min(TC_ROWS, M - m0);
+                a.x = x + (size_t)m0 * ldx;
+                a.ldx = ldx;
+                a.pro = pro;
+                a.norm_w = norm_w;
+                a.eps = (float)cfg_.rms_norm_eps;
+                a.epi = epi;
+                a.y = y + (size_t)m0 * ldy;
+                a.ldy = ldy;
+                a.bias = bias;
+                a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+                if (epi == EPI_QKV_ROPE) {
+                    if (!L.rope_rows || layer < 0) return fail(HM_ERR_STATE, "projection rows are not in rotation-pair order");
+                    a.rope = rope_epi(layer, row_pos, row_seq, m0);
+                }
+                const cudaError_t ce = launch_gemm_quant(a, qrows_img_, qrows_bs_, sm_count_, stream_, pdl_, launches);
+                if (ce != cudaSuccess) return cuda_fail(ce, "quantised projection over a row block");
+            }
+            pf_ptr_ = nullptr;
+            pf_bytes_ = 0;
+            return HM_OK;
+        }
+    }
     for (int m0 = 0; m0 < M; m0 += MAX_M) {
         const int mv = std::min(MAX_M, M - m0), mp = pad_m(mv);
         cudaError_t ce;

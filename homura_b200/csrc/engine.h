@@ -138,6 +138,9 @@ class Engine {
     unsigned char *xpack_attn_ = nullptr, *xpack_act_ = nullptr;  // written directly by the attention kernel / the SwiGLU epilogue
     unsigned char *xpack_h_ = nullptr, *xpack_h2_ = nullptr;      // written by the down / O epilogues: (hidden * next norm weight) for the next QKV or LM head / gate-up GEMM
     float *ss_h_ = nullptr, *ss_h2_ = nullptr;                    // [H/128][64] partial sums of squares of those rows
+    uint32_t* qrows_img_ = nullptr;  // Q8_0 / Q4_0 models: digit planes of the up to 64 rows a projection launch multiplies (launch_gemm_quant)
+    float* qrows_bs_ = nullptr;      // their block scales
+    int qrows_k_ = 0;                // widest projection input the two buffers hold
     size_t xpack_bytes_ = 0;
     float* amax_val_ = nullptr;
     int32_t* amax_idx_ = nullptr;

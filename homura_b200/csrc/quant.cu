@@ -608,6 +608,263 @@ cudaError_t launch_qm(const QuantArgs& a_in, int sm_count, cudaStream_t st, bool
     return a.ksplit > 1 ? launch_q3<M, false, true>(a, sm_count, st, pdl) : launch_q3<M, false, false>(a, sm_count, st, pdl);
 }
 
+
+// ---- passes over 9..64 rows (prefill chunks, batches of more than eight sequences) -------------------------------
+// The 1..8-row kernel lets every CTA rewrite the activation rows as digit planes for itself; with tens of rows that
+// prologue outweighs the multiply.  Here one small launch rewrites the rows once (into global memory, which is the
+// L2 for the launch that follows), and the multiply's eight warps own eight rows each: every warp walks all k-blocks
+// of the CTA's range, the tile's codes staged in shared memory once and read by all of them, so a weight byte that
+// crosses the SM's load path serves 64 rows instead of 8 and no sum across warps is needed.
+constexpr int GR = 64;                 // rows per launch
+constexpr int GPAIRS = GR / 2;         // row pairs per k-block in the image
+constexpr int GW = Img<2>::WORDS;      // 64 words per (k-block, pair)
+
+__global__ void __launch_bounds__(QT) quant_pack_rows_kernel(const float* __restrict__ x, int ldx, int M, int K, const float* __restrict__ norm_w, float eps,
+                                                             uint32_t* __restrict__ img, float* __restrict__ bs) {
+    __shared__ double s_w[8];
+    __shared__ float s_inv;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool row_ok = m < M;  // rows up to GR are written (as zeros) so that the multiply never reads stale planes
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * ldx);
+    const int k4 = K >> 2;
+    float inv = 1.0f;
+    if (norm_w) {
+        // sum of squares in f64 (emitter_quant.rs:713-791), then (x * inv) * w as the reference orders it
+        double ssq = 0.0;
+        if (row_ok)
+            for (int p = tid; p < k4; p += QT) {
+                const float4 v = ld_cg_f32x4(reinterpret_cast<const float*>(xr + p));
+                ssq += (double)v.x * (double)v.x + (double)v.y * (double)v.y;
+                ssq += (double)v.z * (double)v.z + (double)v.w * (double)v.w;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        if (lane == 0) s_w[warp] = ssq;
+        __syncthreads();
+        if (tid == 0) {
+            double t = 0.0;
+            for (int w = 0; w < 8; ++w) t += s_w[w];
+            s_inv = 1.0f / sqrtf((float)(t * (1.0 / (double)K)) + eps);
+        }
+        __syncthreads();
+        inv = s_inv;
+    }
+    for (int p0 = 0; p0 < k4; p0 += QT) {
+        const int p = p0 + tid;
+        const bool in = p < k4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in && row_ok) {
+            v = ld_cg_f32x4(reinterpret_cast<const float*>(xr + p));
+            if (norm_w) {
+                const float4 w = __ldg(reinterpret_cast<const float4*>(norm_w) + p);
+                v = make_float4((v.x * inv) * w.x, (v.y * inv) * w.y, (v.z * inv) * w.z, (v.w * inv) * w.w);
+            }
+        }
+        if (!__any_sync(0xffffffffu, in)) continue;
+        emit_digits<2>(v, in, (p >> 3) * GPAIRS + (m >> 1), m, tid & 7, img, bs);
+    }
+}
+
+template <bool Q4, bool CL>
+__global__ void __launch_bounds__(QT) gemm_quant_kernel(const QuantArgs a) {
+    extern __shared__ __align__(128) float gsm[];
+    constexpr int CHB = (Q4 ? 1 : 2) * 512;
+    constexpr int CH = Q4 ? 1 : 2;
+    const unsigned char* codes_s = reinterpret_cast<const unsigned char*>(gsm);
+    const uint16_t* scales_s = reinterpret_cast<const uint16_t*>(codes_s + (size_t)a.kb_per_split * CHB);
+    float* vals = gsm + ((size_t)a.kb_per_split * (CHB + 64)) / 4;  // [GR][32] sums of this tile
+    float* slots = vals + GR * 32;                                     // cluster: [ksplit][GR][32]
+    constexpr int NCHUNK = 4;
+    __shared__ uint64_t s_wbar[NCHUNK];
+    __shared__ volatile int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nb = a.K / 32;
+    const int tile = blockIdx.x / a.ksplit, split = blockIdx.x - tile * a.ksplit;
+    const int kb0 = split * a.kb_per_split, kb1 = min(nb, kb0 + a.kb_per_split);
+    const int nkb = max(0, kb1 - kb0);
+    pdl_launch_dependents();
+    // the tile's codes and scales do not depend on the launch in front: staged before the dependency wait, in pieces
+    const int ck = max(8, ((nkb + NCHUNK - 1) / NCHUNK + 7) / 8 * 8);
+    if (tid == 0) {
+        for (int ch = 0; ch < NCHUNK; ++ch) mb_init(&s_wbar[ch], 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const unsigned char* csrc = reinterpret_cast<const unsigned char*>(a.codes) + ((size_t)tile * nb + kb0) * CHB;
+        for (int ch = 0; ch < NCHUNK; ++ch) {
+            const int k_lo = min(nkb, ch * ck), k_hi = min(nkb, k_lo + ck);
+            if (k_hi <= k_lo) break;
+            const uint32_t cbytes = (uint32_t)(k_hi - k_lo) * CHB, sbytes = ch == 0 ? (uint32_t)nkb * 64u : 0u;
+            mb_expect_tx(&s_wbar[ch], cbytes + sbytes);
+            if (sbytes) bulk_copy(const_cast<uint16_t*>(scales_s), a.scales + ((size_t)tile * nb + kb0) * 32, sbytes, &s_wbar[0]);
+            bulk_copy(const_cast<unsigned char*>(codes_s) + (size_t)k_lo * CHB, csrc + (size_t)k_lo * CHB, cbytes, &s_wbar[ch]);
+        }
+    }
+    pdl_wait();
+    __syncthreads();  // barrier words initialised before anybody polls them
+
+    // this warp's eight rows: pairs 4 * warp .. 4 * warp + 3 of every k-block
+    const uint32_t* imgw = a.img_in + ((size_t)kb0 * GPAIRS + 4 * warp) * GW + lane;
+    const float* bsw = a.bs_in + ((size_t)kb0 * GPAIRS + 4 * warp) * 2 + ((lane >> 1) & 1);
+    float acc[4][4];
+#pragma unroll
+    for (int ng = 0; ng < 4; ++ng)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[ng][i] = 0.f;
+    uint32_t nb0[4], nb1[4];
+    float nbs[4];
+    auto fetch = [&](int kb) {
+#pragma unroll
+        for (int ng = 0; ng < 4; ++ng) {
+            nb0[ng] = __ldg(imgw + ((size_t)kb * GPAIRS + ng) * GW);
+            nb1[ng] = __ldg(imgw + ((size_t)kb * GPAIRS + ng) * GW + 32);
+            nbs[ng] = __ldg(bsw + ((size_t)kb * GPAIRS + ng) * 2);
+        }
+    };
+    if (nkb > 0) fetch(0);
+    int waited = -1;
+    bool ok = true;
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+        uint32_t b0[4], b1[4];
+        float bsv[4];
+#pragma unroll
+        for (int ng = 0; ng < 4; ++ng) {
+            b0[ng] = nb0[ng];
+            b1[ng] = nb1[ng];
+            bsv[ng] = nbs[ng];
+        }
+        if (kb + 1 < nkb) fetch(kb + 1);
+        while (kb >= (waited + 1) * ck && ok) {
+            ++waited;
+            ok = __all_sync(0xffffffffu, mb_wait(&s_wbar[waited], 0, a.err_flag, &s_abort));
+        }
+        if (!ok) break;
+        uint4 c[2];
+#pragma unroll
+        for (int h = 0; h < CH; ++h) c[h] = *reinterpret_cast<const uint4*>(codes_s + ((size_t)(kb * CH + h) * 32 + lane) * 16);
+        const uint2 sc = *reinterpret_cast<const uint2*>(scales_s + kb * 32 + (lane >> 2) * 4);
+        uint32_t av[2][4];
+        if (Q4) {
+            const uint32_t w[4] = {c[0].x, c[0].y, c[0].z, c[0].w};
+#pragma unroll
+            for (int rg = 0; rg < 2; ++rg) {
+                av[rg][0] = w[2 * rg] & 0x0F0F0F0Fu;
+                av[rg][1] = w[2 * rg + 1] & 0x0F0F0F0Fu;
+                av[rg][2] = (w[2 * rg] >> 4) & 0x0F0F0F0Fu;
+                av[rg][3] = (w[2 * rg + 1] >> 4) & 0x0F0F0F0Fu;
+            }
+        } else {
+#pragma unroll
+            for (int rg = 0; rg < 2; ++rg) {
+                av[rg][0] = c[rg].x;
+                av[rg][1] = c[rg].y;
+                av[rg][2] = c[rg].z;
+                av[rg][3] = c[rg].w;
+            }
+        }
+        const float2 d01 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x)), d23 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
+        const float d[4] = {d01.x, d01.y, d23.x, d23.y};
+#pragma unroll
+        for (int ng = 0; ng < 4; ++ng) {
+            int off = 0;
+            if (Q4) {
+                int cs[4];
+                mma_s8(cs, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0[ng], b1[ng]);
+                off = (cs[1] * 256 + cs[0]) * 8;
+            }
+#pragma unroll
+            for (int rg = 0; rg < 2; ++rg) {
+                int cc[4];
+                mma_s8(cc, av[rg][0], av[rg][1], av[rg][2], av[rg][3], b0[ng], b1[ng]);
+                const int i0 = cc[1] * 256 + cc[0] - off, i1 = cc[3] * 256 + cc[2] - off;
+                acc[ng][2 * rg] = fmaf(d[2 * rg] * bsv[ng], (float)i0, acc[ng][2 * rg]);
+                acc[ng][2 * rg + 1] = fmaf(d[2 * rg + 1] * bsv[ng], (float)i1, acc[ng][2 * rg + 1]);
+            }
+        }
+    }
+    // the lane pair (q even, q odd) holds the two halves of a dot: planes 0,1 weigh 1, planes 2,3 weigh 2^16
+    {
+        const int q = lane & 3, g = lane >> 2;
+        const float wgt = (q & 1) ? 65536.0f : 1.0f;
+#pragma unroll
+        for (int ng = 0; ng < 4; ++ng) {
+            const int m = 8 * warp + 2 * ng + (q >> 1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float mine = acc[ng][i] * wgt;
+                const float sum = mine + __shfl_xor_sync(0xffffffffu, mine, 1);
+                if ((q & 1) == 0) vals[m * 32 + 8 * i + g] = sum;
+            }
+        }
+    }
+    __syncthreads();
+    if (CL) {
+        // every rank pushes its sums into rank 0's slots and is done; rank 0 adds them in rank order
+        for (int t = tid; t < GR * 32; t += QT) {
+            if (split == 0) slots[t] = vals[t];
+            else st_dsmem_f32(dsmem_addr(slots + (size_t)split * (GR * 32) + t, 0u), vals[t]);
+        }
+        cluster_arrive_release();
+        if (split != 0) return;
+        cluster_wait_acquire();
+        for (int t = tid; t < GR * 32; t += QT) {
+            float v = slots[t];
+            for (int r = 1; r < a.ksplit; ++r) v += slots[(size_t)r * (GR * 32) + t];
+            vals[t] = v;
+        }
+        __syncthreads();
+    }
+    for (int t = tid; t < GR * 32; t += QT) {
+        const int m = t >> 5, p = t & 31;
+        float v = vals[t];
+        if (a.epi == EPI_SWIGLU) {
+            const int j = tile * 16 + p;
+            if (p < 16 && m < a.m_valid && j < a.N / 2) {
+                const float g = v, u = vals[t + 16];
+                a.y[(size_t)m * a.ldy + j] = (g / (1.0f + expf(-g))) * u;
+            }
+        } else if (a.epi == EPI_QKV_ROPE) {
+            rope_tile_epilogue(a.rope, vals, v, t, tile, a.m_valid, a.N, a.bias, a.y, a.ldy);
+        } else {
+            const int n = tile * 32 + p;
+            if (m < a.m_valid && n < a.N) {
+                if (a.bias) v += a.bias[n];
+                if (a.resid) v = a.resid[(size_t)m * a.ldy + n] + v;
+                a.y[(size_t)m * a.ldy + n] = v;
+            }
+        }
+    }
+}
+
+template <bool Q4, bool CL>
+cudaError_t launch_gq2(const QuantArgs& a, size_t smem, cudaStream_t st, bool pdl) {
+    cudaError_t e = ensure_dyn_smem(gemm_quant_kernel<Q4, CL>, smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(((a.N + 31) / 32) * a.ksplit));
+    cfg.blockDim = dim3(QT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (CL) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = (unsigned)a.ksplit;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, gemm_quant_kernel<Q4, CL>, a);
+}
+
 }  // namespace
 
 size_t quant_scale_elems(int K, int N) { return (size_t)((N + 31) / 32) * (K / 32) * 32; }
@@ -639,6 +896,53 @@ cudaError_t launch_gemv_quant(const QuantArgs& a, int M, int sm_count, cudaStrea
         case 8: return launch_qm<8>(a, sm_count, st, pdl);
         default: return cudaErrorInvalidValue;
     }
+}
+
+size_t quant_rows_image_words(int K) { return (size_t)(K / 32) * GPAIRS * GW; }
+size_t quant_rows_scale_floats(int K) { return (size_t)(K / 32) * GPAIRS * 2; }
+bool quant_rows_supported(const QuantArgs& a) {
+    return (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (a.ldx & 3) == 0 && (a.K & 31) == 0 && (!a.norm_w || (reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0) &&
+           ((reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.scales)) & 15) == 0;
+}
+
+// Up to 64 rows: one launch that writes the rows' digit planes (img, bs: quant_rows_image_words / quant_rows_scale_floats of
+// the projection's K), one that multiplies.  a.m_valid = rows; a.pro / a.norm_w as for launch_gemv_quant.
+cudaError_t launch_gemm_quant(const QuantArgs& a_in, uint32_t* img, float* bs, int sm_count, cudaStream_t st, bool pdl, int* launches) {
+    QuantArgs a = a_in;
+    if (a.m_valid < 1 || a.m_valid > GR || !quant_rows_supported(a)) return cudaErrorInvalidValue;
+    cudaError_t e;
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(GR);
+        cfg.blockDim = dim3(QT);
+        cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = pdl ? 1 : 0;
+        e = cudaLaunchKernelEx(&cfg, quant_pack_rows_kernel, a.x, a.ldx, a.m_valid, a.K, a.pro == PRO_RMSNORM ? a.norm_w : (const float*)nullptr, a.eps, img, bs);
+    }
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
+    a.img_in = img;
+    a.bs_in = bs;
+    const int nb = a.K / 32, tiles = (a.N + 31) / 32;
+    const size_t BLK = (a.q4 ? 1 : 2) * 512 + 64;
+    // K split: about one CTA per SM, at most 8 per cluster, a staged slice of at most 96 KB
+    int ks = (sm_count + tiles - 1) / tiles;
+    if (ks > 8) ks = 8;
+    while (ks > 1 && nb / ks < 8) --ks;
+    while (ks < 8 && (size_t)((nb + ks - 1) / ks) * BLK > QUANT_STAGE_MAX) ++ks;
+    if (ks < 1) ks = 1;
+    a.kb_per_split = (nb + ks - 1) / ks;
+    a.ksplit = (nb + a.kb_per_split - 1) / a.kb_per_split;
+    if ((size_t)a.kb_per_split * BLK > QUANT_STAGE_MAX + 32 * 1024) return cudaErrorInvalidValue;  // K beyond what eight ranks can stage
+    const size_t smem = (size_t)a.kb_per_split * BLK + sizeof(float) * GR * 32 * (1 + (a.ksplit > 1 ? a.ksplit : 0));
+    if (a.q4) e = a.ksplit > 1 ? launch_gq2<true, true>(a, smem, st, pdl) : launch_gq2<true, false>(a, smem, st, pdl);
+    else e = a.ksplit > 1 ? launch_gq2<false, true>(a, smem, st, pdl) : launch_gq2<false, false>(a, smem, st, pdl);
+    if (e == cudaSuccess && launches) ++*launches;
+    return e;
 }
 
 }  // namespace hm
