@@ -418,6 +418,11 @@ int Engine::ensure_scratch(int rows) {
     HM_CUDA(re(&logits_, (size_t)cap * V_));
     HM_CUDA(re(&amax_val_, (size_t)cap * nslabs_v));
     HM_CUDA(re(&amax_idx_, (size_t)cap * nslabs_v));
+    if (!tall && use_tc_ && lm_head_.kind == HM_BF16 && lm_head_.tc) {
+        // a GGUF model whose LM head is the bf16 embedding: passes over more than 8 rows run that one projection on the tensor cores
+        xpack_bytes_ = tc_xpack_bytes(TC_ROWS, H_);
+        HM_CUDA(re(&xpack_, xpack_bytes_));
+    }
     if (quant_) {
         // digit planes of up to 64 rows of the widest projection input (launch_gemm_quant)
         qrows_k_ = std::max(std::max(H_, qdim_), I_);

@@ -504,6 +504,32 @@ def test_qk_norm_after_quantised_projections_is_refused(hm):
     assert e.value.status == hm.HM_ERR_STATE and "QK-norm" in e.value.message
 
 
+@pytest.mark.parametrize("gt,kind,B", [(synth.GGML_Q8_0, "Q8_0", 20), (synth.GGML_Q4_0, "Q4_0", 70)])
+def test_gguf_decode_batches_on_the_row_block_kernel(hm, oracle, gt, kind, B):
+    # more than eight rows per pass run the 64-row launches of the Q8_0 / Q4_0 projections (rows rewritten as digit planes
+    # once per projection); 70 sequences span two row blocks, and every row's K/V must land in its own sequence's pages
+    cfg = synth.tiny_config(qkv_bias=True, tie_word_embeddings=True, rope_theta=1e4, rms_norm_eps=1e-5)
+    p = os.path.join(tempfile.mkdtemp(), "m.gguf")
+    synth.write_gguf_model(p, cfg, seed=17, ggml_type=gt, norm_jitter=0.1)
+    m = hm.HfModel.load_gguf(p)
+    m.init_kv_cache(32, batch=B)
+    oms = [oracle.OracleModel.from_gguf(p, max_seq_len=32) for _ in range(B)]
+    cur = []
+    for b in range(B):
+        ids = synth.prompt_ids(500 + b, 2 + (b % 5), cfg.vocab_size)
+        t_o, _ = oms[b].prefill(ids)
+        assert m.prefill(ids, seq=b) == t_o
+        cur.append(t_o)
+    for _ in range(4):
+        lg, nxt = m.decode_step(cur)
+        for b in range(B):
+            lo = oms[b].decode_step(cur[b])
+            assert_logits_close(lg[b], lo, what=f"model logits ({kind}, row-block kernel)", rel=3e-4)
+            cur[b] = oracle.argmax(lo)
+            assert int(nxt[b]) == cur[b]
+    m.close()
+
+
 # ---- K-quant GGUF models (Q4_K / Q6_K, the mix of a Q4_K_M file) ---------------------------------
 
 
