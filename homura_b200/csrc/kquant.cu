@@ -273,73 +273,82 @@ __global__ void __launch_bounds__(KT) gemv_kquant_kernel(const KQuantArgs a) {
     // invariant under a positive row factor in exact arithmetic; but a product that rounds the other way moves a
     // code that sits exactly on .5, which the quantised embeddings and bf16 norm weights of the test models produce
     // often enough to leave the tolerance.)
-    constexpr int IT = 4;
-    const bool one_pass = ACTQ && a.pro == PRO_RMSNORM && (a.ldx & 3) == 0 && M * nb <= 8 * IT &&
-                          ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.norm_w)) & 15) == 0;
+    // Plain rows (O and down projections) take the same path over the blocks of this CTA's K range only.
+    constexpr int IT = M == 1 ? 4 : 8;  // a single row keeps its register count (three CTAs per SM)
+    const bool normed = a.pro == PRO_RMSNORM;
+    const int nbi = normed ? nb : nkb, kbi0 = normed ? 0 : kb0;  // blocks visited per row, and the first of them
+    const bool one_pass = ACTQ && (a.ldx & 3) == 0 && M * nbi <= 8 * IT && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
+                          (!normed || (reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0);
     if (one_pass) {
         float4 xa[IT][2];
-        double ss[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) ss[m] = 0.0;
 #pragma unroll
         for (int it = 0; it < IT; ++it) {
             const int item = warp + 8 * it;
             xa[it][0] = xa[it][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (item < M * nb) {
-                const int m = item / nb, kb = item - m * nb;
+            if (item < M * nbi) {
+                const int m = item / nbi, kb = kbi0 + item - m * nbi;
                 const float* xr = a.x + (size_t)m * a.ldx + (size_t)kb * 256 + lane * 8;
                 xa[it][0] = ld_cg_f32x4(xr);
                 xa[it][1] = ld_cg_f32x4(xr + 4);
             }
         }
+        if (normed) {
+            double ss[M];
 #pragma unroll
-        for (int it = 0; it < IT; ++it) {
-            const int item = warp + 8 * it;
-            if (item < M * nb) {
-                const int m = item / nb;
-                const float xv[8] = {xa[it][0].x, xa[it][0].y, xa[it][0].z, xa[it][0].w, xa[it][1].x, xa[it][1].y, xa[it][1].z, xa[it][1].w};
-                double sq = 0.0;
+            for (int m = 0; m < M; ++m) ss[m] = 0.0;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) sq += (double)xv[i] * (double)xv[i];
+            for (int it = 0; it < IT; ++it) {
+                const int item = warp + 8 * it;
+                if (item < M * nbi) {
+                    const int m = item / nbi;
+                    const float xv[8] = {xa[it][0].x, xa[it][0].y, xa[it][0].z, xa[it][0].w, xa[it][1].x, xa[it][1].y, xa[it][1].z, xa[it][1].w};
+                    double sq = 0.0;
 #pragma unroll
-                for (int mm = 0; mm < M; ++mm)
-                    if (mm == m) ss[mm] += sq;
+                    for (int i = 0; i < 8; ++i) sq += (double)xv[i] * (double)xv[i];
+#pragma unroll
+                    for (int mm = 0; mm < M; ++mm)
+                        if (mm == m) ss[mm] += sq;
+                }
             }
-        }
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            double t = ss[m];
+            for (int m = 0; m < M; ++m) {
+                double t = ss[m];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-            if (lane == 0) s_wsum[warp][m] = t;
+                for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+                if (lane == 0) s_wsum[warp][m] = t;
+            }
+            __syncthreads();
+            if (tid < M) {
+                double t = 0.0;
+                for (int wv = 0; wv < 8; ++wv) t += s_wsum[wv][tid];
+                const float mean = (float)(t * (1.0 / (double)a.K));
+                s_inv[tid] = 1.0f / sqrtf(mean + a.eps);
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        if (tid < M) {
-            double t = 0.0;
-            for (int wv = 0; wv < 8; ++wv) t += s_wsum[wv][tid];
-            const float mean = (float)(t * (1.0 / (double)a.K));
-            s_inv[tid] = 1.0f / sqrtf(mean + a.eps);
-        }
-        __syncthreads();
 #pragma unroll
         for (int it = 0; it < IT; ++it) {
             const int item = warp + 8 * it;
-            if (item >= M * nb) continue;
-            const int m = item / nb, kb = item - m * nb;
+            if (item >= M * nbi) continue;
+            const int m = item / nbi, kb = kbi0 + item - m * nbi;
             if (kb < kb0 || kb >= kb1) continue;  // warp-uniform
             const int kbl = kb - kb0;
-            const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)kb * 256 + lane * 8));
-            const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)kb * 256 + lane * 8 + 4));
             const float xv[8] = {xa[it][0].x, xa[it][0].y, xa[it][0].z, xa[it][0].w, xa[it][1].x, xa[it][1].y, xa[it][1].z, xa[it][1].w};
-            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-            const float rinv = s_inv[m];
             float v[8];
+            if (normed) {
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)kb * 256 + lane * 8));
+                const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.norm_w + (size_t)kb * 256 + lane * 8 + 4));
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const float rinv = s_inv[m];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (xv[i] * rinv) * wv[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = xv[i];
+            }
             float amax = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                v[i] = (xv[i] * rinv) * wv[i];
-                amax = fmaxf(amax, fabsf(v[i]));
-            }
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const float iscale = amax == 0.f ? 0.f : __fdiv_rn(127.0f, amax);
