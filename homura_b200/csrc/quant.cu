@@ -667,6 +667,16 @@ __global__ void __launch_bounds__(QT) quant_pack_rows_kernel(const float* __rest
     }
 }
 
+// per-warp ring of B fragments: 16-byte asynchronous copies, four k-blocks ahead
+constexpr int GB_STAGES = 4;
+constexpr int GB_WORDS = 4 * GW + 8;  // a warp's four row pairs of one k-block (1 KB) + their eight block scales
+__device__ __forceinline__ void cp_async16(void* dst_shared, const void* src_global) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst_shared)), "l"(src_global) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <bool Q4, bool CL>
 __global__ void __launch_bounds__(QT) gemm_quant_kernel(const QuantArgs a) {
     extern __shared__ __align__(128) float gsm[];
@@ -675,7 +685,8 @@ __global__ void __launch_bounds__(QT) gemm_quant_kernel(const QuantArgs a) {
     const unsigned char* codes_s = reinterpret_cast<const unsigned char*>(gsm);
     const uint16_t* scales_s = reinterpret_cast<const uint16_t*>(codes_s + (size_t)a.kb_per_split * CHB);
     float* vals = gsm + ((size_t)a.kb_per_split * (CHB + 64)) / 4;  // [GR][32] sums of this tile
-    float* slots = vals + GR * 32;                                     // cluster: [ksplit][GR][32]
+    uint32_t* bring = reinterpret_cast<uint32_t*>(vals + GR * 32);    // [8 warps][GB_STAGES][GB_WORDS]
+    float* slots = reinterpret_cast<float*>(bring + 8 * GB_STAGES * GB_WORDS);  // cluster: [ksplit][GR][32]
     constexpr int NCHUNK = 4;
     __shared__ uint64_t s_wbar[NCHUNK];
     __shared__ volatile int s_abort;
@@ -704,37 +715,46 @@ __global__ void __launch_bounds__(QT) gemm_quant_kernel(const QuantArgs a) {
     pdl_wait();
     __syncthreads();  // barrier words initialised before anybody polls them
 
-    // this warp's eight rows: pairs 4 * warp .. 4 * warp + 3 of every k-block
-    const uint32_t* imgw = a.img_in + ((size_t)kb0 * GPAIRS + 4 * warp) * GW + lane;
-    const float* bsw = a.bs_in + ((size_t)kb0 * GPAIRS + 4 * warp) * 2 + ((lane >> 1) & 1);
+    // this warp's eight rows: pairs 4 * warp .. 4 * warp + 3 of every k-block, 1 KB of planes + 32 B of scales, fetched by
+    // asynchronous copies into the warp's own ring, GB_STAGES k-blocks ahead of the multiply
+    const uint32_t* imgw = a.img_in + ((size_t)kb0 * GPAIRS + 4 * warp) * GW;
+    const float* bsw = a.bs_in + ((size_t)kb0 * GPAIRS + 4 * warp) * 2;
+    uint32_t* myring = bring + (size_t)warp * GB_STAGES * GB_WORDS;
     float acc[4][4];
 #pragma unroll
     for (int ng = 0; ng < 4; ++ng)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[ng][i] = 0.f;
-    uint32_t nb0[4], nb1[4];
-    float nbs[4];
-    auto fetch = [&](int kb) {
-#pragma unroll
-        for (int ng = 0; ng < 4; ++ng) {
-            nb0[ng] = __ldg(imgw + ((size_t)kb * GPAIRS + ng) * GW);
-            nb1[ng] = __ldg(imgw + ((size_t)kb * GPAIRS + ng) * GW + 32);
-            nbs[ng] = __ldg(bsw + ((size_t)kb * GPAIRS + ng) * 2);
+    auto issue = [&](int kb) {
+        if (kb < nkb) {
+            const uint32_t* src = imgw + (size_t)kb * GPAIRS * GW;
+            uint32_t* dst = myring + (kb % GB_STAGES) * GB_WORDS;
+            cp_async16(dst + lane * 4, src + lane * 4);
+            cp_async16(dst + 128 + lane * 4, src + 128 + lane * 4);
+            if (lane < 2) cp_async16(dst + 4 * GW + lane * 4, bsw + (size_t)kb * GPAIRS * 2 + lane * 4);
         }
+        cp_async_commit();  // (an empty group past the end keeps the count per k-block uniform)
     };
-    if (nkb > 0) fetch(0);
+#pragma unroll
+    for (int s0 = 0; s0 < GB_STAGES; ++s0) issue(s0);
     int waited = -1;
     bool ok = true;
     for (int kb = 0; kb < nkb && ok; ++kb) {
+        cp_async_wait<GB_STAGES - 1>();
+        __syncwarp();
         uint32_t b0[4], b1[4];
         float bsv[4];
+        {
+            const uint32_t* stg = myring + (kb % GB_STAGES) * GB_WORDS;
 #pragma unroll
-        for (int ng = 0; ng < 4; ++ng) {
-            b0[ng] = nb0[ng];
-            b1[ng] = nb1[ng];
-            bsv[ng] = nbs[ng];
+            for (int ng = 0; ng < 4; ++ng) {
+                b0[ng] = stg[ng * GW + lane];
+                b1[ng] = stg[ng * GW + 32 + lane];
+                bsv[ng] = __uint_as_float(stg[4 * GW + ng * 2 + ((lane >> 1) & 1)]);
+            }
         }
-        if (kb + 1 < nkb) fetch(kb + 1);
+        __syncwarp();
+        issue(kb + GB_STAGES);
         while (kb >= (waited + 1) * ck && ok) {
             ++waited;
             ok = __all_sync(0xffffffffu, mb_wait(&s_wbar[waited], 0, a.err_flag, &s_abort));
@@ -938,7 +958,7 @@ cudaError_t launch_gemm_quant(const QuantArgs& a_in, uint32_t* img, float* bs, i
     a.kb_per_split = (nb + ks - 1) / ks;
     a.ksplit = (nb + a.kb_per_split - 1) / a.kb_per_split;
     if ((size_t)a.kb_per_split * BLK > QUANT_STAGE_MAX + 32 * 1024) return cudaErrorInvalidValue;  // K beyond what eight ranks can stage
-    const size_t smem = (size_t)a.kb_per_split * BLK + sizeof(float) * GR * 32 * (1 + (a.ksplit > 1 ? a.ksplit : 0));
+    const size_t smem = (size_t)a.kb_per_split * BLK + sizeof(float) * GR * 32 * (1 + (a.ksplit > 1 ? a.ksplit : 0)) + sizeof(uint32_t) * 8 * GB_STAGES * GB_WORDS;
     if (a.q4) e = a.ksplit > 1 ? launch_gq2<true, true>(a, smem, st, pdl) : launch_gq2<true, false>(a, smem, st, pdl);
     else e = a.ksplit > 1 ? launch_gq2<false, true>(a, smem, st, pdl) : launch_gq2<false, false>(a, smem, st, pdl);
     if (e == cudaSuccess && launches) ++*launches;
