@@ -461,6 +461,7 @@ struct QuantArgs {
     // launch_gemm_quant: the rows as digit planes, written by its packing launch
     const uint32_t* img_in;  // [K/32][32 row pairs][64 words]
     const float* bs_in;      // [K/32][32 row pairs][2]
+    int alias_slots;         // filled in by launch_gemm_quant: rank 0's split-K receive slots reuse the staged slice (one more cluster barrier)
 };
 
 // ---- launchers (defined in the .cu files) ----------------------------------------------

@@ -684,9 +684,14 @@ __global__ void __launch_bounds__(QT) gemm_quant_kernel(const QuantArgs a) {
     constexpr int CH = Q4 ? 1 : 2;
     const unsigned char* codes_s = reinterpret_cast<const unsigned char*>(gsm);
     const uint16_t* scales_s = reinterpret_cast<const uint16_t*>(codes_s + (size_t)a.kb_per_split * CHB);
-    float* vals = gsm + ((size_t)a.kb_per_split * (CHB + 64)) / 4;  // [GR][32] sums of this tile
+    // cluster: rank 0's receive slots [ksplit][GR][32] follow the ring, or (alias_slots: when that is what lets two CTAs share
+    // an SM) take the place of the staged slice once every rank is done with its own, at the price of a cluster barrier
+    const size_t slice_b = (size_t)a.kb_per_split * (CHB + 64), slots_b = CL ? sizeof(float) * GR * 32 * (size_t)a.ksplit : (size_t)0;
+    const bool alias = CL && a.alias_slots;
+    const size_t head = alias && slots_b > slice_b ? slots_b : slice_b;
+    float* vals = gsm + head / 4;                                      // [GR][32] sums of this tile
     uint32_t* bring = reinterpret_cast<uint32_t*>(vals + GR * 32);    // [8 warps][GB_STAGES][GB_WORDS]
-    float* slots = reinterpret_cast<float*>(bring + 8 * GB_STAGES * GB_WORDS);  // cluster: [ksplit][GR][32]
+    float* slots = alias ? gsm : reinterpret_cast<float*>(bring + 8 * GB_STAGES * GB_WORDS);
     constexpr int NCHUNK = 4;
     __shared__ uint64_t s_wbar[NCHUNK];
     __shared__ volatile int s_abort;
@@ -821,6 +826,7 @@ __global__ void __launch_bounds__(QT) gemm_quant_kernel(const QuantArgs a) {
     __syncthreads();
     if (CL) {
         // every rank pushes its sums into rank 0's slots and is done; rank 0 adds them in rank order
+        if (alias) cluster_sync_all();  // nobody reads staged codes any more: the slots may overwrite them
         for (int t = tid; t < GR * 32; t += QT) {
             if (split == 0) slots[t] = vals[t];
             else st_dsmem_f32(dsmem_addr(slots + (size_t)split * (GR * 32) + t, 0u), vals[t]);
@@ -958,7 +964,14 @@ cudaError_t launch_gemm_quant(const QuantArgs& a_in, uint32_t* img, float* bs, i
     a.kb_per_split = (nb + ks - 1) / ks;
     a.ksplit = (nb + a.kb_per_split - 1) / a.kb_per_split;
     if ((size_t)a.kb_per_split * BLK > QUANT_STAGE_MAX + 32 * 1024) return cudaErrorInvalidValue;  // K beyond what eight ranks can stage
-    const size_t smem = (size_t)a.kb_per_split * BLK + sizeof(float) * GR * 32 * (1 + (a.ksplit > 1 ? a.ksplit : 0)) + sizeof(uint32_t) * 8 * GB_STAGES * GB_WORDS;
+    const size_t slice_b = (size_t)a.kb_per_split * BLK, slots_b = a.ksplit > 1 ? sizeof(float) * GR * 32 * (size_t)a.ksplit : (size_t)0;
+    const size_t rest_b = sizeof(float) * GR * 32 + sizeof(uint32_t) * 8 * GB_STAGES * GB_WORDS;
+    size_t smem = slice_b + slots_b + rest_b;
+    const size_t two_per_sm = 112 * 1024;  // 2 x (this + 1 KB) fits the SM's 227 KB
+    if (slots_b && smem > two_per_sm && std::max(slice_b, slots_b) + rest_b <= two_per_sm) {
+        a.alias_slots = 1;  // measured: worth the extra cluster barrier only where it doubles the CTAs per SM
+        smem = std::max(slice_b, slots_b) + rest_b;
+    }
     if (a.q4) e = a.ksplit > 1 ? launch_gq2<true, true>(a, smem, st, pdl) : launch_gq2<true, false>(a, smem, st, pdl);
     else e = a.ksplit > 1 ? launch_gq2<false, true>(a, smem, st, pdl) : launch_gq2<false, false>(a, smem, st, pdl);
     if (e == cudaSuccess && launches) ++*launches;
