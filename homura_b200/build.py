@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhomura_b200.so")
-SOURCES = ["gemv_bf16.cu", "gemm_tc.cu", "attention.cu", "quant.cu", "kquant.cu", "sampler.cu", "misc_kernels.cu", "engine.cu", "capi.cu", "loaders.cpp", "launch_attrs.cpp"]
+SOURCES = ["gemv_bf16.cu", "gemm_tc.cu", "attention.cu", "quant.cu", "kquant.cu", "kquant_gemm.cu", "sampler.cu", "misc_kernels.cu", "engine.cu", "capi.cu", "loaders.cpp", "launch_attrs.cpp"]
 HEADERS = ["common.cuh", "engine.h", "gemm_tc.h", "mbarrier.cuh", "kquant.h", "sampler.h", "loaders.h", "launch_attrs.h", os.path.join("..", "..", "include", "homura_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

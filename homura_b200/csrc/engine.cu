@@ -111,7 +111,7 @@ Engine::~Engine() {
     fr(partial_); fr(tickets_); fr(att_acc_); fr(att_ml_); fr(att_tickets_); fr(err_flag_); fr(fin_ticket_);
     for (void* p : k_pool_) fr(p);
     for (void* p : v_pool_) fr(p);
-    fr(qrows_img_); fr(qrows_bs_);
+    fr(qrows_img_); fr(qrows_bs_); fr(kqrows_codes_); fr(kqrows_actd_);
     fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_); fr(smp_overflow_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
@@ -200,6 +200,7 @@ int Engine::load_linear(LinearW& L, int K, int N_total, int n_off, int n_part, i
             return fail(HM_ERR_UNSUPPORTED, "gate and up projections of a layer must share one K-quant type");
         }
         L.kq_part_type = dtype;
+        if (dtype == HM_Q6_K) L.kq_has_q6 = true;
         if (ce == cudaSuccess) ce = launch_kquant_split((const uint8_t*)tmp, n_part, K, dtype == HM_Q6_K, n_off, interleave_which, L.kq_data, L.kq_tile_type, stream_, rope_hd);
         L.kq_bytes += nbytes;
         quant_ = true;
@@ -424,8 +425,12 @@ int Engine::ensure_scratch(int rows) {
         HM_CUDA(re(&xpack_, xpack_bytes_));
     }
     if (quant_) {
-        // digit planes of up to 64 rows of the widest projection input (launch_gemm_quant)
+        // digit planes / Q8_K codes of up to 64 rows of the widest projection input (launch_gemm_quant, launch_gemm_q4k)
         qrows_k_ = std::max(std::max(H_, qdim_), I_);
+        if (qrows_k_ % 256 == 0) {
+            HM_CUDA(re(&kqrows_codes_, kquant_rows_code_bytes(qrows_k_)));
+            HM_CUDA(re(&kqrows_actd_, kquant_rows_scale_floats(qrows_k_)));
+        }
         HM_CUDA(re(&qrows_img_, quant_rows_image_words(qrows_k_)));
         HM_CUDA(re(&qrows_bs_, quant_rows_scale_floats(qrows_k_)));
     }
@@ -798,6 +803,48 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
                 }
                 const cudaError_t ce = launch_gemm_quant(a, qrows_img_, qrows_bs_, sm_count_, stream_, pdl_, launches);
                 if (ce != cudaSuccess) return cuda_fail(ce, "quantised projection over a row block");
+            }
+            pf_ptr_ = nullptr;
+            pf_bytes_ = 0;
+            return HM_OK;
+        }
+    }
+    // Q4_K projections (every tile Q4_K, quantised activations) over more than eight rows: the rows are quantised to Q8_K once
+    // and 64-row launches multiply the codes on the integer tensor-core path
+    if (L.kind == HM_Q4_K && !L.kq_has_q6 && &L != &lm_head_ && M > MAX_M && kqrows_codes_ && L.K <= qrows_k_ && L.K % 256 == 0 &&
+        (epi == EPI_STORE || epi == EPI_SWIGLU || epi == EPI_QKV_ROPE)) {
+        KQuantArgs probe{};
+        probe.x = x;
+        probe.ldx = ldx;
+        probe.K = L.K;
+        probe.norm_w = pro == PRO_RMSNORM ? norm_w : nullptr;
+        probe.data = L.kq_data;
+        if (kquant_rows_supported(probe)) {
+            for (int m0 = 0; m0 < M; m0 += TC_ROWS) {
+                KQuantArgs a{};
+                a.err_flag = err_flag_;
+                a.data = L.kq_data;
+                a.tile_type = L.kq_tile_type;
+                a.K = L.K;
+                a.N = L.N;
+                a.m_valid = std::min(TC_ROWS, M - m0);
+                a.act_quant = 1;
+                a.x = x + (size_t)m0 * ldx;
+                a.ldx = ldx;
+                a.pro = pro;
+                a.norm_w = norm_w;
+                a.eps = (float)cfg_.rms_norm_eps;
+                a.epi = epi;
+                a.y = y + (size_t)m0 * ldy;
+                a.ldy = ldy;
+                a.bias = bias;
+                a.resid = resid ? resid + (size_t)m0 * ldy : nullptr;
+                if (epi == EPI_QKV_ROPE) {
+                    if (!L.rope_rows || layer < 0) return fail(HM_ERR_STATE, "projection rows are not in rotation-pair order");
+                    a.rope = rope_epi(layer, row_pos, row_seq, m0);
+                }
+                const cudaError_t ce = launch_gemm_q4k(a, kqrows_codes_, kqrows_actd_, sm_count_, stream_, pdl_, launches);
+                if (ce != cudaSuccess) return cuda_fail(ce, "Q4_K projection over a row block");
             }
             pf_ptr_ = nullptr;
             pf_bytes_ = 0;

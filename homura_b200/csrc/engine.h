@@ -27,6 +27,7 @@ struct LinearW {
     uint8_t* kq_tile_type = nullptr;  // per 32-row tile: 1 = Q4_K, 2 = Q6_K
     size_t kq_bytes = 0;              // GGUF bytes loaded into it (what a step streams)
     int kq_part_type = -1;            // type of the part loaded last (gate and up must agree: they share tiles)
+    bool kq_has_q6 = false;           // some tile is Q6_K: passes over more than 8 rows keep the 8-row launches (the row-block kernel is Q4_K only)
     int loaded_parts = 0;
     bool rope_rows = false;  // quantised fused QKV: q and k rows stored in rotation-pair tiles (rope_tile_row), the projection's epilogue rotates
     size_t bytes() const;
@@ -141,6 +142,8 @@ class Engine {
     uint32_t* qrows_img_ = nullptr;  // Q8_0 / Q4_0 models: digit planes of the up to 64 rows a projection launch multiplies (launch_gemm_quant)
     float* qrows_bs_ = nullptr;      // their block scales
     int qrows_k_ = 0;                // widest projection input the two buffers hold
+    int8_t* kqrows_codes_ = nullptr;  // K-quant models: Q8_K codes of the up to 64 rows a projection launch multiplies (launch_gemm_q4k)
+    float* kqrows_actd_ = nullptr;    // their block scales
     size_t xpack_bytes_ = 0;
     float* amax_val_ = nullptr;
     int32_t* amax_idx_ = nullptr;

@@ -94,6 +94,15 @@ __global__ void kq_split_kernel(const uint8_t* __restrict__ blocks, size_t nbloc
         if (q6) {
             dst[13 * 512 + r * 2 + 0] = s[208];
             dst[13 * 512 + r * 2 + 1] = s[209];
+        } else {
+            // piece 9 (unused by the format's 9 pieces): the eight sub-block scales and minima as bytes, for the row-block kernel
+            const uint8_t* sr = s + 4;
+            for (int i = 0; i < 4; ++i) {
+                dst[(9 * 32 + r) * 16 + i] = sr[i] & 0x3F;
+                dst[(9 * 32 + r) * 16 + 8 + i] = sr[4 + i] & 0x3F;
+                dst[(9 * 32 + r) * 16 + 4 + i] = (uint8_t)((sr[8 + i] & 0x0F) | ((sr[i] >> 6) << 4));
+                dst[(9 * 32 + r) * 16 + 12 + i] = (uint8_t)((sr[8 + i] >> 4) | ((sr[4 + i] >> 6) << 4));
+            }
         }
         if (kb == 0) tile_type[tile] = (uint8_t)(q6 ? 2 : 1);
     }

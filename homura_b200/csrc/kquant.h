@@ -24,6 +24,9 @@ struct KQuantArgs {
     const float* bias;
     const float* resid;
     RopeEpi rope;  // EPI_QKV_ROPE
+    int* err_flag;            // launch_gemm_q4k: raised to 2 when the bounded wait for the staged slots runs out
+    const int8_t* codes_in;   // launch_gemm_q4k: Q8_K codes of the rows [K/256][64][256], written by its packing launch
+    const float* actd_in;     // and their block scales [K/256][64]
 };
 
 size_t kquant_data_bytes(int K, int N);
@@ -34,5 +37,11 @@ size_t kquant_tiles(int N);
 cudaError_t launch_kquant_split(const uint8_t* blocks, int n_rows, int K, int q6, int n_off, int interleave_which, uint8_t* data, uint8_t* tile_type, cudaStream_t st, int rope_hd = 0);
 cudaError_t launch_dequant_k(const uint8_t* blocks, size_t nblocks, int q6, float* out, cudaStream_t st);
 cudaError_t launch_gemv_kquant(const KQuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
+// Q4_K projection (every tile Q4_K, quantised activations) over up to 64 rows (a.m_valid): a launch that quantises the rows to
+// Q8_K (codes / act_d: kquant_rows_code_bytes / kquant_rows_scale_floats of the projection's K) and the multiply.
+size_t kquant_rows_code_bytes(int K);
+size_t kquant_rows_scale_floats(int K);
+bool kquant_rows_supported(const KQuantArgs& a);
+cudaError_t launch_gemm_q4k(const KQuantArgs& a, int8_t* codes, float* act_d, int sm_count, cudaStream_t st, bool pdl, int* launches);
 
 }  // namespace hm
