@@ -809,9 +809,9 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
             return HM_OK;
         }
     }
-    // Q4_K projections (every tile Q4_K, quantised activations) over more than eight rows: the rows are quantised to Q8_K once
+    // K-quant projections (quantised activations) over more than eight rows: the rows are quantised to Q8_K once
     // and 64-row launches multiply the codes on the integer tensor-core path
-    if (L.kind == HM_Q4_K && !L.kq_has_q6 && &L != &lm_head_ && M > MAX_M && kqrows_codes_ && L.K <= qrows_k_ && L.K % 256 == 0 &&
+    if (L.kind == HM_Q4_K && &L != &lm_head_ && M > MAX_M && kqrows_codes_ && L.K <= qrows_k_ && L.K % 256 == 0 &&
         (epi == EPI_STORE || epi == EPI_SWIGLU || epi == EPI_QKV_ROPE)) {
         KQuantArgs probe{};
         probe.x = x;
@@ -829,6 +829,7 @@ int Engine::enqueue_linear(const LinearW& L, int M, const float* x, int ldx, int
                 a.N = L.N;
                 a.m_valid = std::min(TC_ROWS, M - m0);
                 a.act_quant = 1;
+                a.has_q6 = L.kq_has_q6 ? 1 : 0;
                 a.x = x + (size_t)m0 * ldx;
                 a.ldx = ldx;
                 a.pro = pro;

@@ -27,6 +27,8 @@ struct KQuantArgs {
     int* err_flag;            // launch_gemm_q4k: raised to 2 when the bounded wait for the staged slots runs out
     const int8_t* codes_in;   // launch_gemm_q4k: Q8_K codes of the rows [K/256][64][256], written by its packing launch
     const float* actd_in;     // and their block scales [K/256][64]
+    int has_q6;               // launch_gemm_q4k: the projection holds Q6_K tiles (slots are staged whole)
+    int stage_bytes;          // filled in by launch_gemm_q4k
 };
 
 size_t kquant_data_bytes(int K, int N);
@@ -37,7 +39,7 @@ size_t kquant_tiles(int N);
 cudaError_t launch_kquant_split(const uint8_t* blocks, int n_rows, int K, int q6, int n_off, int interleave_which, uint8_t* data, uint8_t* tile_type, cudaStream_t st, int rope_hd = 0);
 cudaError_t launch_dequant_k(const uint8_t* blocks, size_t nblocks, int q6, float* out, cudaStream_t st);
 cudaError_t launch_gemv_kquant(const KQuantArgs& a, int M, int sm_count, cudaStream_t st, bool pdl);
-// Q4_K projection (every tile Q4_K, quantised activations) over up to 64 rows (a.m_valid): a launch that quantises the rows to
+// K-quant projection (Q4_K and Q6_K tiles, quantised activations) over up to 64 rows (a.m_valid): a launch that quantises the rows to
 // Q8_K (codes / act_d: kquant_rows_code_bytes / kquant_rows_scale_floats of the projection's K) and the multiply.
 size_t kquant_rows_code_bytes(int K);
 size_t kquant_rows_scale_floats(int K);

@@ -8,7 +8,9 @@
 // in shared memory once for all eight warps.  Per sub-block one more MMA with the sub-block's minimum replicated in A
 // accumulates sum(min * code), so the per-(row, row) work outside the MMAs is four integer multiply-adds per sub-block
 // and one float expression per super-block, the same expression as the 1..8-row kernel evaluates.
-// Tiles of other types (Q6_K) are not handled here: projections that hold any keep the 8-row launches.
+// Q6_K tiles (a Q4_K_M file keeps attn_v and ffn_down in Q6_K) have sixteen sub-blocks of 16 weights with signed 8-bit scales:
+// their codes are put together from the low nibbles and the 2-bit planes, shifted to -32..31 per byte, and go through
+// mma.sync.m16n8k16; no minima.
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -24,6 +26,7 @@ namespace {
 constexpr int KT = 256;
 constexpr int GR = 64;                     // activation rows per launch
 constexpr int Q4_STAGED = 10 * 512;        // pieces 0..9 of a slot: header, nibbles, unpacked scales / minima
+constexpr int Q6_STAGED = KQ_SLOT_BYTES;   // the whole slot: 8 ql + 4 qh + 1 scale piece, then the rows' f16 super-block scales
 constexpr int ROWB = 272;                  // a row's 256 codes in the ring, padded so that the eight rows of a B fragment hit 32 banks
 constexpr int RING_STAGE = 8 * ROWB;       // a warp's eight rows of one super-block
 constexpr int RING_STAGES = 2;
@@ -37,6 +40,17 @@ __device__ __forceinline__ void mma_s8_acc(int (&c)[4], uint32_t a0, uint32_t a1
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+// four 6-bit codes (low nibbles | 2-bit plane << 4), each minus 32, as signed bytes
+__device__ __forceinline__ uint32_t q6_codes(uint32_t lw, uint32_t hw, int group) {
+    const uint32_t lo = (group >= 2 ? (lw >> 4) : lw) & 0x0F0F0F0Fu, hi = (hw >> (2 * group)) & 0x03030303u;
+    const uint32_t c = lo | (hi << 4);                      // 0..63 per byte
+    return ((c | 0x80808080u) - 0x20202020u) ^ 0x80808080u;  // per-byte c - 32 (no borrow crosses a byte)
 }
 __device__ __forceinline__ void cp_async16(void* dst_shared, const void* src_global) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst_shared)), "l"(src_global) : "memory");
@@ -122,8 +136,10 @@ __global__ void __launch_bounds__(KT) gemm_q4k_kernel(const KQuantArgs a) {
     const int tile = blockIdx.x / a.ksplit, split = blockIdx.x - tile * a.ksplit;
     const int kb0 = split * a.kb_per_split, kb1 = min(nb, kb0 + a.kb_per_split);
     const int nkb = max(0, kb1 - kb0);
-    unsigned char* slice = ksm;                                                        // [kb_per_split][Q4_STAGED]
-    float* vals = reinterpret_cast<float*>(ksm + (size_t)a.kb_per_split * Q4_STAGED);  // [GR][32]
+    const int ttype = a.tile_type[tile];                                               // 1 = Q4_K, 2 = Q6_K (0: no rows)
+    const int staged = ttype == 2 ? Q6_STAGED : Q4_STAGED;                             // bytes of a slot this tile needs
+    unsigned char* slice = ksm;                                                        // [kb_per_split][staged]
+    float* vals = reinterpret_cast<float*>(ksm + (size_t)a.kb_per_split * a.stage_bytes);  // [GR][32]
     unsigned char* ring = reinterpret_cast<unsigned char*>(vals + GR * 32);            // [8 warps][RING_STAGES][RING_STAGE]
     float* slots = reinterpret_cast<float*>(ring + 8 * RING_STAGES * RING_STAGE);      // cluster: [ksplit][GR][32]
     constexpr int NCHUNK = 4;
@@ -140,8 +156,8 @@ __global__ void __launch_bounds__(KT) gemm_q4k_kernel(const KQuantArgs a) {
         for (int ch = 0; ch < NCHUNK; ++ch) {
             const int k_lo = min(nkb, ch * ck), k_hi = min(nkb, k_lo + ck);
             if (k_hi <= k_lo) break;
-            mb_expect_tx(&s_wbar[ch], (uint32_t)(k_hi - k_lo) * Q4_STAGED);
-            for (int kbl = k_lo; kbl < k_hi; ++kbl) bulk_copy(slice + (size_t)kbl * Q4_STAGED, tbase + (size_t)kbl * KQ_SLOT_BYTES, Q4_STAGED, &s_wbar[ch]);
+            mb_expect_tx(&s_wbar[ch], (uint32_t)(k_hi - k_lo) * staged);
+            for (int kbl = k_lo; kbl < k_hi; ++kbl) bulk_copy(slice + (size_t)kbl * staged, tbase + (size_t)kbl * KQ_SLOT_BYTES, staged, &s_wbar[ch]);
         }
     }
     pdl_wait();
@@ -179,8 +195,38 @@ __global__ void __launch_bounds__(KT) gemm_q4k_kernel(const KQuantArgs a) {
             ok = __all_sync(0xffffffffu, mb_wait(&s_wbar[waited], 0, a.err_flag, &s_abort));
         }
         if (!ok) break;
-        const unsigned char* slot = slice + (size_t)kbl * Q4_STAGED;
+        const unsigned char* slot = slice + (size_t)kbl * staged;
         const unsigned char* brow = myring + (kbl % RING_STAGES) * RING_STAGE + g * ROWB + 4 * q;
+        if (ttype == 2) {
+#pragma unroll
+            for (int rg = 0; rg < 2; ++rg) {
+                const int rA = 16 * rg + g, rB = rA + 8;
+                const uint4 scA = *reinterpret_cast<const uint4*>(slot + (12 * 32 + rA) * 16), scB = *reinterpret_cast<const uint4*>(slot + (12 * 32 + rB) * 16);
+                const uint32_t sAw[4] = {scA.x, scA.y, scA.z, scA.w}, sBw[4] = {scB.x, scB.y, scB.z, scB.w};
+                int sacc[2][2] = {{0, 0}, {0, 0}};
+#pragma unroll
+                for (int sb = 0; sb < 16; ++sb) {
+                    const int chunk = sb >> 3, group = (sb & 7) >> 1, parity = sb & 1;
+                    const int pl = chunk * 4 + (group & 1) * 2 + parity, ph = 8 + chunk * 2 + parity;
+                    const uint32_t a0 = q6_codes(*reinterpret_cast<const uint32_t*>(slot + (pl * 32 + rA) * 16 + 4 * q), *reinterpret_cast<const uint32_t*>(slot + (ph * 32 + rA) * 16 + 4 * q), group);
+                    const uint32_t a1 = q6_codes(*reinterpret_cast<const uint32_t*>(slot + (pl * 32 + rB) * 16 + 4 * q), *reinterpret_cast<const uint32_t*>(slot + (ph * 32 + rB) * 16 + 4 * q), group);
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + sb * 16);
+                    int cc[4];
+                    mma_s8_k16(cc, a0, a1, b0);
+                    const int sA = (int)(int8_t)(sAw[sb >> 2] >> (8 * (sb & 3))), sB = (int)(int8_t)(sBw[sb >> 2] >> (8 * (sb & 3)));
+                    sacc[0][0] += sA * cc[0];
+                    sacc[0][1] += sA * cc[1];
+                    sacc[1][0] += sB * cc[2];
+                    sacc[1][1] += sB * cc[3];
+                }
+                const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(slot + 13 * 512 + rA * 2)));
+                const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(slot + 13 * 512 + rB * 2)));
+                acc[rg][0][0] = __fadd_rn(acc[rg][0][0], __fmul_rn(__fmul_rn(dA, ad0), (float)sacc[0][0]));
+                acc[rg][0][1] = __fadd_rn(acc[rg][0][1], __fmul_rn(__fmul_rn(dA, ad1), (float)sacc[0][1]));
+                acc[rg][1][0] = __fadd_rn(acc[rg][1][0], __fmul_rn(__fmul_rn(dB, ad0), (float)sacc[1][0]));
+                acc[rg][1][1] = __fadd_rn(acc[rg][1][1], __fmul_rn(__fmul_rn(dB, ad1), (float)sacc[1][1]));
+            }
+        } else
 #pragma unroll
         for (int rg = 0; rg < 2; ++rg) {
             const int rA = 16 * rg + g, rB = rA + 8;
@@ -327,12 +373,13 @@ cudaError_t launch_gemm_q4k(const KQuantArgs& a_in, int8_t* codes, float* act_d,
     // K split: about one CTA per SM, at most 8 per cluster, a staged slice of at most 96 KB
     int ks = (sm_count + tiles - 1) / tiles;
     ks = std::min(ks, std::min(8, nb));
-    while (ks < 8 && ks < nb && (size_t)((nb + ks - 1) / ks) * Q4_STAGED > 96 * 1024) ++ks;
+    a.stage_bytes = a.has_q6 ? Q6_STAGED : Q4_STAGED;
+    while (ks < 8 && ks < nb && (size_t)((nb + ks - 1) / ks) * a.stage_bytes > 96 * 1024) ++ks;
     ks = std::max(ks, 1);
     a.kb_per_split = (nb + ks - 1) / ks;
     a.ksplit = (nb + a.kb_per_split - 1) / a.kb_per_split;
-    if ((size_t)a.kb_per_split * Q4_STAGED > 128 * 1024) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)a.kb_per_split * Q4_STAGED + sizeof(float) * GR * 32 * (1 + (a.ksplit > 1 ? a.ksplit : 0)) + (size_t)8 * RING_STAGES * RING_STAGE;
+    if ((size_t)a.kb_per_split * a.stage_bytes > 128 * 1024) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)a.kb_per_split * a.stage_bytes + sizeof(float) * GR * 32 * (1 + (a.ksplit > 1 ? a.ksplit : 0)) + (size_t)8 * RING_STAGES * RING_STAGE;
     e = a.ksplit > 1 ? launch_gk<true>(a, smem, st, pdl) : launch_gk<false>(a, smem, st, pdl);
     if (e == cudaSuccess && launches) ++*launches;
     return e;
