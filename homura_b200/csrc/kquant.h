@@ -29,6 +29,7 @@ struct KQuantArgs {
     const float* actd_in;     // and their block scales [K/256][64]
     int has_q6;               // launch_gemm_q4k: the projection holds Q6_K tiles (slots are staged whole)
     int stage_bytes;          // filled in by launch_gemm_q4k
+    int alias_slots;          // filled in by launch_gemm_q4k: rank 0's split-K receive slots reuse the staged slots (one more cluster barrier)
 };
 
 size_t kquant_data_bytes(int K, int N);

@@ -139,9 +139,13 @@ __global__ void __launch_bounds__(KT) gemm_q4k_kernel(const KQuantArgs a) {
     const int ttype = a.tile_type[tile];                                               // 1 = Q4_K, 2 = Q6_K (0: no rows)
     const int staged = ttype == 2 ? Q6_STAGED : Q4_STAGED;                             // bytes of a slot this tile needs
     unsigned char* slice = ksm;                                                        // [kb_per_split][staged]
-    float* vals = reinterpret_cast<float*>(ksm + (size_t)a.kb_per_split * a.stage_bytes);  // [GR][32]
+    // cluster: rank 0's receive slots [ksplit][GR][32] follow the ring, or (alias_slots: when that is what lets two CTAs share
+    // an SM) take the place of the staged slots once every rank is done with its own, at the price of a cluster barrier
+    const size_t slice_b = (size_t)a.kb_per_split * a.stage_bytes, slots_b = CL ? sizeof(float) * GR * 32 * (size_t)a.ksplit : (size_t)0;
+    const bool alias = CL && a.alias_slots;
+    float* vals = reinterpret_cast<float*>(ksm + (alias && slots_b > slice_b ? slots_b : slice_b));  // [GR][32]
     unsigned char* ring = reinterpret_cast<unsigned char*>(vals + GR * 32);            // [8 warps][RING_STAGES][RING_STAGE]
-    float* slots = reinterpret_cast<float*>(ring + 8 * RING_STAGES * RING_STAGE);      // cluster: [ksplit][GR][32]
+    float* slots = alias ? reinterpret_cast<float*>(ksm) : reinterpret_cast<float*>(ring + 8 * RING_STAGES * RING_STAGE);
     constexpr int NCHUNK = 4;
     __shared__ uint64_t s_wbar[NCHUNK];
     __shared__ volatile int s_abort;
@@ -276,6 +280,7 @@ __global__ void __launch_bounds__(KT) gemm_q4k_kernel(const KQuantArgs a) {
             for (int c = 0; c < 2; ++c) vals[(8 * warp + 2 * q + c) * 32 + 16 * rg + 8 * rs + g] = acc[rg][rs][c];
     __syncthreads();
     if (CL) {
+        if (alias) cluster_sync_all();  // nobody reads staged slots any more: the receive slots may overwrite them
         for (int t = tid; t < GR * 32; t += KT) {
             if (split == 0) slots[t] = vals[t];
             else st_dsmem_f32(dsmem_addr(slots + (size_t)split * (GR * 32) + t, 0u), vals[t]);
@@ -379,7 +384,14 @@ cudaError_t launch_gemm_q4k(const KQuantArgs& a_in, int8_t* codes, float* act_d,
     a.kb_per_split = (nb + ks - 1) / ks;
     a.ksplit = (nb + a.kb_per_split - 1) / a.kb_per_split;
     if ((size_t)a.kb_per_split * a.stage_bytes > 128 * 1024) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)a.kb_per_split * a.stage_bytes + sizeof(float) * GR * 32 * (1 + (a.ksplit > 1 ? a.ksplit : 0)) + (size_t)8 * RING_STAGES * RING_STAGE;
+    const size_t slice_b = (size_t)a.kb_per_split * a.stage_bytes, slots_b = a.ksplit > 1 ? sizeof(float) * GR * 32 * (size_t)a.ksplit : (size_t)0;
+    const size_t rest_b = sizeof(float) * GR * 32 + (size_t)8 * RING_STAGES * RING_STAGE;
+    size_t smem = slice_b + slots_b + rest_b;
+    const size_t two_per_sm = 112 * 1024;  // 2 x (this + 1 KB) fits the SM's 227 KB
+    if (slots_b && smem > two_per_sm && std::max(slice_b, slots_b) + rest_b <= two_per_sm) {
+        a.alias_slots = 1;
+        smem = std::max(slice_b, slots_b) + rest_b;
+    }
     e = a.ksplit > 1 ? launch_gk<true>(a, smem, st, pdl) : launch_gk<false>(a, smem, st, pdl);
     if (e == cudaSuccess && launches) ++*launches;
     return e;
