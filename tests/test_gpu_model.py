@@ -504,7 +504,8 @@ def test_qk_norm_after_quantised_projections_is_refused(hm):
     assert e.value.status == hm.HM_ERR_STATE and "QK-norm" in e.value.message
 
 
-@pytest.mark.parametrize("gt,kind,B", [(synth.GGML_Q8_0, "Q8_0", 20), (synth.GGML_Q4_0, "Q4_0", 70), (synth.GGML_Q4_K, "Q4_K_M", 20), (synth.GGML_Q6_K, "Q6_K", 70)])
+@pytest.mark.parametrize("gt,kind,B", [(synth.GGML_Q8_0, "Q8_0", 20), (synth.GGML_Q8_0, "Q8_0 with its own quantised LM head", 12), (synth.GGML_Q4_0, "Q4_0", 70),
+                                       (synth.GGML_Q4_K, "Q4_K_M", 20), (synth.GGML_Q6_K, "Q6_K", 70)])
 def test_gguf_decode_batches_on_the_row_block_kernel(hm, oracle, gt, kind, B):
     # more than eight rows per pass run the 64-row launches of the quantised projections (rows rewritten as digit planes, or
     # quantised to Q8_K, once per projection); 70 sequences span two row blocks, and every row's K/V must land in its own
@@ -513,7 +514,7 @@ def test_gguf_decode_batches_on_the_row_block_kernel(hm, oracle, gt, kind, B):
     # the mixed model, on the one-row path just the same), so the tight comparison is between the row-block launches and the
     # one-row launches of a second engine that replays every sequence alone, and the oracle bounds both loosely.
     kq = kind in ("Q4_K_M", "Q6_K")
-    cfg = synth.tiny_config(qkv_bias=True, tie_word_embeddings=True, rope_theta=1e4, rms_norm_eps=1e-5, intermediate_size=768 if kq else 640)
+    cfg = synth.tiny_config(qkv_bias=True, tie_word_embeddings="LM head" not in kind, rope_theta=1e4, rms_norm_eps=1e-5, intermediate_size=768 if kq else 640)
     p = os.path.join(tempfile.mkdtemp(), "m.gguf")
     synth.write_gguf_model(p, cfg, seed=17, ggml_type=gt, norm_jitter=0.1, k_mix=kind == "Q4_K_M")
     m = hm.HfModel.load_gguf(p)
