@@ -553,6 +553,42 @@ def test_gguf_decode_batches_on_the_row_block_kernel(hm, oracle, gt, kind, B):
         m1.close()
 
 
+@pytest.mark.parametrize("gt,kind", [(synth.GGML_Q8_0, "Q8_0"), (synth.GGML_Q4_0, "Q4_0"), (synth.GGML_Q4_K, "Q4_K")])
+def test_gguf_model_on_bf16_kv_pages(hm, oracle, gt, kind):
+    # the quantised projections' own QKV epilogue writes K and V into bf16 pages (chunk-major K, 8-element V chunks): a prompt
+    # that takes the row-block launches, then single-row steps.  Layer 0 sees the same input as the oracle, so its cached
+    # K and V must be the oracle's values rounded to bf16 (relative 2^-8), whichever launch wrote the row.  The logits are
+    # held to the bound of bf16 pages, except for the synthetic Q8_0 model: its keys reach 50, its softmax is that sharp,
+    # and rounding the keys moves single logits by up to 0.1 (with f32 pages the same model agrees to 7e-6).
+    cfg = synth.tiny_config(qkv_bias=True, tie_word_embeddings=True, rope_theta=1e4, rms_norm_eps=1e-5, intermediate_size=768)
+    p = os.path.join(tempfile.mkdtemp(), "m.gguf")
+    synth.write_gguf_model(p, cfg, seed=23, ggml_type=gt, norm_jitter=0.1)
+    om = oracle.OracleModel.from_gguf(p, max_seq_len=64)
+    m = hm.HfModel.load_gguf(p)
+    m.init_kv_cache(64, kv_dtype=hm.DType.BF16)
+    ids = synth.prompt_ids(31, 21, cfg.vocab_size)
+    tok_o, lg_o = om.prefill(ids)
+    _, lg_g = m.prefill(ids, want_logits=True)
+    pairs = [(lg_g, lg_o)]
+    cur = tok_o
+    for _ in range(8):
+        lo = om.decode_step(cur)
+        lgd, _ = m.decode_step([cur])
+        pairs.append((lgd[0], lo))
+        cur = oracle.argmax(lo)
+    gk, gv = m.kv_view(0)
+    ok, ov = om.kv_view(0)
+    assert ok.shape[-2] == 29
+    for g, o in ((gk[0], ok), (gv[0], ov)):
+        assert np.all(np.abs(g - o) <= 2.0 ** -8 * np.abs(o) + 1e-6)
+    for g, o in pairs:
+        cos = float(np.dot(g, o) / (np.linalg.norm(g) * np.linalg.norm(o)))
+        assert cos >= (0.99 if kind == "Q8_0" else 0.9995), cos
+        if kind != "Q8_0":
+            assert_logits_close(g, o, scale_tol=False)
+    m.close()
+
+
 # ---- K-quant GGUF models (Q4_K / Q6_K, the mix of a Q4_K_M file) ---------------------------------
 
 
