@@ -96,6 +96,7 @@ int Engine::create(const hm_config& cfg, int device, Engine** out, std::string* 
 Engine::~Engine() {
     if (!set_device()) return;
     if (stream_) cudaStreamSynchronize(stream_);
+    drop_host_logits_graph();
     if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
     if (graph_) cudaGraphDestroy(graph_);
     auto fr = [](void* p) {
@@ -115,6 +116,7 @@ Engine::~Engine() {
     fr(gemv_trace_); fr(smp_scaled_); fr(smp_count_); fr(smp_rng_); fr(smp_gen_start_); fr(smp_overflow_);
     fr(page_table_); fr(pos_dev_); fr(tokens_dev_); fr(next_dev_); fr(hist_dev_); fr(pf_tokens_); fr(pf_pos_); fr(pf_seq_);
     if (pin_u32_) cudaFreeHost(pin_u32_);
+    if (pin_logits_) cudaFreeHost(pin_logits_);
     if (stream_) cudaStreamDestroy(stream_);
 }
 
@@ -562,6 +564,7 @@ int Engine::kv_free() {
     if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
     if (batch_ == 0) return HM_OK;
     HM_CUDA(cudaStreamSynchronize(stream_));
+    drop_host_logits_graph();
     if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
     if (graph_) cudaGraphDestroy(graph_);
     graph_exec_ = nullptr;
@@ -1145,7 +1148,8 @@ int Engine::enqueue_pass(int M, const uint32_t* tokens_dev, const int32_t* row_p
             if (rc) return rc;
         } else if (want(PC_LM_HEAD)) {
             const ArgmaxFold fold{next_dev, feed_dev, pos_dev, hist_dev, max_seq_ + 1};
-            rc = slab_argmax ? enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches, &fold)
+            float* lm_dst = (lm_out_ && fold_argmax) ? lm_out_ : logits_;
+            rc = slab_argmax ? enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_LOGITS, lm_dst, V_, nullptr, nullptr, -1, nullptr, nullptr, amax_val_, amax_idx_, launches, &fold)
                              : enqueue_linear(lm_head_, lm_rows, x, H_, PRO_RMSNORM, final_norm_, EPI_STORE, logits_, V_, nullptr, nullptr, -1, nullptr, nullptr, nullptr, nullptr, launches);
             if (rc) return rc;
         }
@@ -1208,6 +1212,72 @@ int Engine::selftest_expire_wait() {
 
 // ---- GenerativeModel ---------------------------------------------------------------------------
 
+// Where a device-to-host copy of logits lands.  Into pageable memory the driver stages such a copy piece by piece (about 80 us for
+// one 608 KB row); into pinned memory it is one DMA.  A pageable destination therefore receives its rows through a pinned buffer of
+// the engine (one DMA, then a host copy after the stream synchronisation); a pinned or registered destination is written directly.
+bool Engine::alloc_pin_logits(size_t bytes) {
+    bytes = std::max(bytes, (size_t)std::max(batch_, 1) * V_ * 4);
+    if (pin_logits_bytes_ >= bytes) return true;
+    drop_host_logits_graph();  // it stores into the buffer that is about to be replaced
+    if (pin_logits_) cudaFreeHost(pin_logits_);
+    pin_logits_ = pin_logits_dev_ = nullptr;
+    pin_logits_bytes_ = 0;
+    void* dev = nullptr;
+    if (cudaHostAlloc(&pin_logits_, bytes, cudaHostAllocMapped) != cudaSuccess || cudaHostGetDevicePointer(&dev, pin_logits_, 0) != cudaSuccess) {
+        cudaGetLastError();
+        if (pin_logits_) cudaFreeHost(pin_logits_);
+        pin_logits_ = nullptr;
+        return false;
+    }
+    pin_logits_dev_ = static_cast<float*>(dev);
+    pin_logits_bytes_ = bytes;
+    return true;
+}
+
+float* Engine::logits_landing(float* user, size_t bytes) {
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, user) == cudaSuccess && at.type != cudaMemoryTypeUnregistered) return user;
+    cudaGetLastError();
+    return alloc_pin_logits(bytes) ? pin_logits_ : user;
+}
+
+void Engine::drop_host_logits_graph() {
+    if (graph_exec_host_) cudaGraphExecDestroy(graph_exec_host_);
+    if (graph_host_) cudaGraphDestroy(graph_host_);
+    graph_exec_host_ = nullptr;
+    graph_host_ = nullptr;
+    host_graph_tried_ = false;
+}
+
+// A second decode graph for callers that take the logits of every step (the reference trait's decode_step returns them).  Its LM
+// head stores the rows straight into the mapped pinned buffer: posted writes over PCIe that overlap the launch's weight stream, so
+// no device-to-host copy follows the step (that copy costs more than the LM head itself for a 608 KB row).  Built only where the
+// LM-head launch also produces the greedy token, so that nothing on the device reads the logits of such a step afterwards.
+int Engine::ensure_host_logits_graph() {
+    if (graph_exec_host_ || host_graph_tried_) return HM_OK;
+    host_graph_tried_ = true;
+    if (lm_head_.kind != HM_BF16 || batch_ > MAX_M || !graph_exec_) return HM_OK;
+    if (!alloc_pin_logits((size_t)batch_ * V_ * 4)) return HM_OK;
+    host_graph_tried_ = true;  // alloc_pin_logits may have cleared it
+    HM_CUDA(cudaStreamSynchronize(stream_));
+    int launches = 0;
+    HM_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+    lm_out_ = pin_logits_dev_;
+    int rc = enqueue_pass(batch_, tokens_dev_, pos_dev_, nullptr, 0, batch_, true, next_dev_, tokens_dev_, pos_dev_, hist_dev_, &launches);
+    const bool folded = lm_folds_argmax_;
+    lm_out_ = nullptr;
+    cudaGraph_t g = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(stream_, &g);
+    if (rc || ce != cudaSuccess || !folded) {
+        if (g) cudaGraphDestroy(g);
+        cudaGetLastError();
+        return rc ? rc : (ce != cudaSuccess ? cuda_fail(ce, "cudaStreamEndCapture") : HM_OK);
+    }
+    graph_host_ = g;
+    HM_CUDA(cudaGraphInstantiate(&graph_exec_host_, graph_host_, 0));
+    return HM_OK;
+}
+
 int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t* first_token) {
     if (!set_device()) return fail(HM_ERR_CUDA, "cudaSetDevice failed");
     if (batch_ == 0) return fail(HM_ERR_STATE, "prefill before kv_alloc");
@@ -1244,11 +1314,13 @@ int Engine::prefill(int seq, const int64_t* ids, int n, float* logits, uint32_t*
     }
     uint32_t* tok_pin = st + 3 * n + 1;
     HM_CUDA(cudaMemcpyAsync(tok_pin, next_dev_ + seq, 4, cudaMemcpyDeviceToHost, stream_));
-    if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, (size_t)V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    float* land = logits ? logits_landing(logits, (size_t)V_ * 4) : nullptr;
+    if (logits) HM_CUDA(cudaMemcpyAsync(land, logits_, (size_t)V_ * 4, cudaMemcpyDeviceToHost, stream_));
     if (int qrc = queue_error_copy()) return qrc;
     HM_CUDA(cudaStreamSynchronize(stream_));
     int rc = check_device_error();
     if (rc) return rc;
+    if (logits && land != logits) std::memcpy(logits, land, (size_t)V_ * 4);
     if (first_token) *first_token = *tok_pin;
     len_[seq] = len0 + n;
     gen_start_[seq] = len0 + n;  // what follows this prompt is "generated" for the penalties (src/generate.rs:150-152)
@@ -1265,18 +1337,27 @@ int Engine::decode_step(const uint32_t* tokens, float* logits, uint32_t* next_to
     }
     std::memcpy(pin_u32_, tokens, (size_t)batch_ * 4);
     HM_CUDA(cudaMemcpyAsync(tokens_dev_, pin_u32_, (size_t)batch_ * 4, cudaMemcpyHostToDevice, stream_));
-    {
+    float* land = nullptr;
+    if (logits) {
+        int grc = ensure_host_logits_graph();
+        if (grc) return grc;
+        land = graph_exec_host_ ? pin_logits_ : logits_landing(logits, (size_t)batch_ * V_ * 4);
+    }
+    if (logits && graph_exec_host_) {
+        HM_CUDA(cudaGraphLaunch(graph_exec_host_, stream_));  // the LM head writes the rows into pin_logits_ itself
+    } else {
         int lrc = launch_step();
         if (lrc) return lrc;
     }
     HM_CUDA(cudaMemcpyAsync(pin_u32_ + batch_, next_dev_, (size_t)batch_ * 4, cudaMemcpyDeviceToHost, stream_));
-    if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, (size_t)batch_ * V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    if (logits && !graph_exec_host_) HM_CUDA(cudaMemcpyAsync(land, logits_, (size_t)batch_ * V_ * 4, cudaMemcpyDeviceToHost, stream_));
     if (int qrc = queue_error_copy()) return qrc;
     HM_CUDA(cudaStreamSynchronize(stream_));
     {
         int erc = check_device_error();
         if (erc) return erc;
     }
+    if (logits && land != logits) std::memcpy(logits, land, (size_t)batch_ * V_ * 4);
     if (next_tokens) std::memcpy(next_tokens, pin_u32_ + batch_, (size_t)batch_ * 4);
     for (int b = 0; b < batch_; ++b) len_[b] += 1;
     return HM_OK;
@@ -1557,12 +1638,14 @@ int Engine::decode_step_sampled(const uint32_t* tokens, const hm_sampling* sp, u
     HM_CUDA(cudaMemcpyAsync(pin + B, next_dev_, B * 4, cudaMemcpyDeviceToHost, stream_));
     HM_CUDA(cudaMemcpyAsync(pin + 2 * B, smp_overflow_, B * 4, cudaMemcpyDeviceToHost, stream_));
     HM_CUDA(cudaMemcpyAsync(pin_rng, smp_rng_, B * 8, cudaMemcpyDeviceToHost, stream_));
-    if (logits) HM_CUDA(cudaMemcpyAsync(logits, logits_, B * V_ * 4, cudaMemcpyDeviceToHost, stream_));
+    float* land = logits ? logits_landing(logits, B * V_ * 4) : nullptr;
+    if (logits) HM_CUDA(cudaMemcpyAsync(land, logits_, B * V_ * 4, cudaMemcpyDeviceToHost, stream_));
     rc = queue_error_copy();
     if (rc) return rc;
     HM_CUDA(cudaStreamSynchronize(stream_));
     rc = check_device_error();
     if (rc) return rc;
+    if (logits && land != logits) std::memcpy(logits, land, B * V_ * 4);
     std::memcpy(rng_state, pin_rng, B * 8);
     std::vector<float> row;
     std::vector<uint32_t> gen;

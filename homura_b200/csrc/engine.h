@@ -105,6 +105,7 @@ class Engine {
     int enqueue_linear_tc(const LinearW& L, int M, const float* x, int ldx, const float* norm_w, int epi, float* y, int ldy, const float* bias, const float* resid, int layer, const int32_t* row_pos, const int32_t* row_seq, int* launches,
                           const unsigned char* prepacked = nullptr, unsigned char* pack_out = nullptr, const TcFuse* fuse = nullptr);
     int capture_decode_graph();
+    int ensure_host_logits_graph();
     int ensure_sampler_scratch();
     SamplerArgs sampler_args(const hm_sampling& s) const;
     int launch_step();        // replay the captured decode graph
@@ -173,6 +174,17 @@ class Engine {
     // pinned host staging
     uint32_t* pin_u32_ = nullptr;
     size_t pin_u32_cap_ = 0;
+    float* pin_logits_ = nullptr;      // mapped pinned buffer: landing place of logits on their way to pageable memory
+    float* pin_logits_dev_ = nullptr;  // the same buffer as the device addresses it
+    size_t pin_logits_bytes_ = 0;
+    bool alloc_pin_logits(size_t bytes);
+    float* logits_landing(float* user, size_t bytes);
+    // decode graph whose LM head stores the logits straight into pin_logits_ (see ensure_host_logits_graph)
+    cudaGraph_t graph_host_ = nullptr;
+    cudaGraphExec_t graph_exec_host_ = nullptr;
+    bool host_graph_tried_ = false;
+    float* lm_out_ = nullptr;  // LM-head destination override while that graph is being captured
+    void drop_host_logits_graph();
 
     cudaGraph_t graph_ = nullptr;
     cudaGraphExec_t graph_exec_ = nullptr;

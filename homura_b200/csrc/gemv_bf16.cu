@@ -436,10 +436,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
             }
         }
     } else if (a.epi == EPI_LOGITS) {
-        for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
-            const int m = idx / SLAB, n = n0 + (idx % SLAB);
-            if (n < a.N && m < a.m_valid) a.y[(size_t)m * a.ldy + n] = vals[idx];
-        }
         if (warp < M && warp < a.m_valid) {
             const int m = warp;
             float bv = -INFINITY;
@@ -474,8 +470,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
             __syncthreads();
             if (s_last) {
                 __threadfence();
-                float* rv = red;                                  // [8 warps] values, reused per row
-                int* ri = reinterpret_cast<int*>(red + 8);        // [8 warps] indices
+                float* rv = red + M * SLAB;                       // [8 warps] values, reused per row (behind vals, which is stored below)
+                int* ri = reinterpret_cast<int*>(rv + 8);         // [8 warps] indices
                 for (int m = 0; m < a.m_valid; ++m) {
                     float bv = -INFINITY;
                     int bi = -1;
@@ -508,6 +504,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, CL ? (M <= 4 ? 2 : 1) : (M == 1 
                 }
                 if (tid == 0) *a.fin_ticket = 0u;  // clean for the next launch
             }
+        }
+        // the rows themselves go out last: when they go to mapped host memory, the fence in front of the ticket must not wait
+        // for them to cross PCIe
+        for (int idx = tid; idx < M * SLAB; idx += GEMV_THREADS) {
+            const int m = idx / SLAB, n = n0 + (idx % SLAB);
+            if (n < a.N && m < a.m_valid) a.y[(size_t)m * a.ldy + n] = vals[idx];
         }
     } else {  // EPI_QKV_ROPE
         const int hd = a.hd, half = hd >> 1, hps = SLAB / hd;
