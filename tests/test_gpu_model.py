@@ -241,6 +241,32 @@ def test_bf16_kv_pages_within_logit_tolerance(hm, oracle):
         cur = oracle.argmax(lo)
 
 
+def test_steps_with_and_without_logits_interleave(hm, oracle):
+    # a step whose logits the caller takes replays a second graph (its LM head stores the rows into mapped host memory); steps
+    # without logits replay the first.  Both advance the same cache, in any order, and a new cache of another batch rebuilds it.
+    cfg, d = make_hf("qwen2")
+    m = hm.HfModel.load(d)
+    for batch in (1, 3, 1):
+        om = oracle.OracleModel.from_hf_dir(d, max_seq_len=64)
+        m.init_kv_cache(64, batch=batch)
+        ids = synth.prompt_ids(7, 9, cfg.vocab_size)
+        cur = om.prefill(ids)[0]
+        for b in range(batch):
+            assert m.prefill(ids, seq=b) == cur
+        for step in range(9):
+            lo = om.decode_step(cur)
+            want = step % 3 != 1
+            lg, nxt = m.decode_step([cur] * batch, want_logits=want)
+            cur = oracle.argmax(lo)
+            assert [int(t) for t in nxt] == [cur] * batch
+            if want:
+                for b in range(batch):
+                    assert_logits_close(lg[b], lo)
+            else:
+                assert lg is None
+    m.close()
+
+
 def test_sharded_checkpoint_and_f32_request_load_the_same_model(hm, oracle):
     # the sharded-index layout (src/hf/model.rs:86-127) and HfModel::load's default dtype request
     # (load_with_dtype(dir, F32), src/hf/model.rs:37-39) on a bf16 checkpoint: same engine, same logits
