@@ -149,7 +149,8 @@ HM_API int hm_kv_view(hm_engine* e, int seq, int layer, float* k_out, float* v_o
 HM_API int hm_prefill(hm_engine* e, int seq, const int64_t* ids, int n, float* logits_or_null, uint32_t* first_token);
 /* HfGenerationContext::decode_step, src/hf/model.rs:359-371, for all `batch` sequences at once:
  * tokens[batch] in; greedy next tokens out (argmax, ties to the highest index,
- * src/generate.rs:457-468); logits_or_null is [batch, vocab] f32 when wanted. */
+ * src/generate.rs:457-468); logits_or_null is [batch, vocab] f32 when wanted (any host memory: pageable
+ * destinations are filled through a pinned buffer of the engine). */
 HM_API int hm_decode_step(hm_engine* e, const uint32_t* tokens, float* logits_or_null, uint32_t* next_tokens);
 /* The same step followed by sample_token (src/generate.rs:698-801) for every sequence, with the sampler
  * options of SamplingConfig (src/generate.rs:648-667): what the reference's loop does per token
