@@ -51,9 +51,12 @@ def test_incremental_decode_equals_full_pass(oracle):
     assert om.kv_len() == 10
 
 
-@pytest.mark.parametrize("gt,kind", [(synth.GGML_Q8_0, "q8_0"), (synth.GGML_Q4_0, "q4_0")])
+@pytest.mark.parametrize("gt,kind", [(synth.GGML_Q8_0, "q8_0"), (synth.GGML_Q4_0, "q4_0"), (synth.GGML_Q4_K, "q4_k"), (synth.GGML_Q6_K, "q6_k")])
 def test_gguf_plan_against_float64(oracle, gt, kind):
-    cfg = synth.tiny_config(qkv_bias=False, tie_word_embeddings=False, rope_theta=1e4, rms_norm_eps=1e-5)
+    # K-quant projections multiply Q8_K-quantised activations (8-bit codes per 256 values), so against an evaluation
+    # with exact activations they carry that quantisation's noise; the block formats with f32 activations do not
+    kq = kind in ("q4_k", "q6_k")
+    cfg = synth.tiny_config(qkv_bias=False, tie_word_embeddings=False, rope_theta=1e4, rms_norm_eps=1e-5, intermediate_size=768 if kq else 640)
     path = os.path.join(tempfile.mkdtemp(), "m.gguf")
     synth.write_gguf_model(path, cfg, seed=5, ggml_type=gt, norm_jitter=0.1)
     om = oracle.OracleModel.from_gguf(path)
@@ -66,7 +69,8 @@ def test_gguf_plan_against_float64(oracle, gt, kind):
 
     def lin(name):
         shape, g, raw = T[name]
-        return oracle.dequant(np.array(raw), kind).reshape(shape).astype(np.float64).T  # [in,out]
+        tkind = {synth.GGML_Q8_0: "q8_0", synth.GGML_Q4_0: "q4_0", synth.GGML_Q4_K: "q4_k", synth.GGML_Q6_K: "q6_k"}[g]
+        return oracle.dequant(np.array(raw), tkind).reshape(shape).astype(np.float64).T  # [in,out]
 
     def vec(name):
         return synth.bf16_to_f32(np.array(T[name][2]).view(np.uint16)).astype(np.float64)
@@ -104,4 +108,4 @@ def test_gguf_plan_against_float64(oracle, gt, kind):
         h = r + (g / (1 + np.exp(-g)) * u) @ lin(p + "ffn_down.weight")
     exp = rms(h, vec("output_norm.weight"), cfg.rms_norm_eps) @ lin("output.weight")
     scale = np.abs(exp).max()
-    assert np.abs(got - exp).max() <= 2e-5 * scale
+    assert np.abs(got - exp).max() <= (3e-2 if kq else 2e-5) * scale
