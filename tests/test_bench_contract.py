@@ -28,3 +28,17 @@ def test_reference_arm_prints_one_contract_line():
 
     assert d["config"] == bench.headline_config(1, "f32", 987_922_432 / 1e6)
     assert "128-token prompt" in d["config"]["workload"]
+
+
+def test_reference_arm_under_two_ranks_prints_from_rank_zero_only():
+    # launched the way the harness launches N > 1: rank 0 alone runs the CPU arm and prints; rank 1 exits 0 without work
+    env = dict(os.environ, OMP_NUM_THREADS=str(min(8, os.cpu_count() or 1)))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29541",
+                        os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip().startswith("{")]
+    assert len(lines) == 1, lines
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 2 and d["value"] > 0
+    assert "replicas x2" in d["config"]["parallelism"]
